@@ -1,0 +1,512 @@
+"""Rollout engine: continuous batching over a paged KV cache, token-in-token-out.
+
+This is the in-repo equivalent of the external inference server the reference launches
+(`python -m sglang.launch_server`, miles/backends/sglang_utils/sglang_engine.py:37-211) and talks to
+over HTTP (miles/backends/sglang_utils/sglang_api_client.py:58-460).  The method names follow that
+HTTP surface (`generate`, `pause_generation`, `continue_generation`, `flush_cache`,
+`update_weights_from_tensor`, `release_memory_occupation`, `resume_memory_occupation`,
+`update_weight_version` …); `miles_b200.engine.server` serves them over HTTP.
+
+Scheduling: a step is either a prefill batch (new requests, up to `max_prefill_tokens`) or one decode
+step for all running requests.  When blocks run out the youngest running request is retracted
+(its blocks freed, it re-enters the waiting queue with prompt+output as the new prompt).
+The engine can run on its own weights or *borrow the trainer's model object* (colocated mode): the
+weight hand-over is then a pointer swap and `update_weights` is a version bump.
+"""
+from __future__ import annotations
+
+import itertools
+import threading
+import time
+import zlib
+from collections import deque
+from dataclasses import dataclass, field
+from typing import Any
+
+import numpy as np
+import torch
+
+from ..models.config import ModelConfig
+from ..models.qwen3 import ForwardMeta, Qwen3Model, build_model
+from ..parallel.state import ParallelState
+from ..types import encode_routed_experts
+from .kv_cache import KVCache, make_allocator
+from .sampler import SamplingParams, sample
+
+
+@dataclass
+class Request:
+    rid: str
+    input_ids: list[int]
+    sampling: SamplingParams
+    return_logprob: bool = True
+    return_routed_experts: bool = False
+    output_ids: list[int] = field(default_factory=list)
+    output_logprobs: list[float] = field(default_factory=list)
+    routed: list[np.ndarray] = field(default_factory=list)   # per forward pass: [tokens, L_moe, k]
+    blocks: list[int] = field(default_factory=list)
+    num_cached: int = 0            # tokens whose KV is in the cache
+    finish_reason: dict | None = None
+    weight_versions: list[list[int]] = field(default_factory=list)  # [version, num_tokens]
+    arrival: float = field(default_factory=time.time)
+    done: threading.Event = field(default_factory=threading.Event)
+    retractions: int = 0
+    seed: int = 0
+    on_done: Any = None            # callable(Request), invoked from the engine thread
+
+    @property
+    def all_ids(self) -> list[int]:
+        return self.input_ids + self.output_ids
+
+    @property
+    def finished(self) -> bool:
+        return self.finish_reason is not None
+
+    def to_response(self, engine: "Engine") -> dict:
+        meta: dict[str, Any] = {
+            "id": self.rid,
+            "finish_reason": self.finish_reason,
+            "prompt_tokens": len(self.input_ids),
+            "completion_tokens": len(self.output_ids),
+            "cached_tokens": 0,
+            "weight_version": str(self.weight_versions[-1][0]) if self.weight_versions else str(engine.weight_version),
+            "weight_version_spans": self.weight_versions,
+        }
+        if self.return_logprob:
+            meta["output_token_logprobs"] = [(lp, t, None) for lp, t in zip(self.output_logprobs, self.output_ids)]
+        if self.return_routed_experts and self.routed:
+            arr = np.concatenate(self.routed, axis=0)
+            n = len(self.input_ids) + len(self.output_ids) - 1
+            meta["routed_experts"] = encode_routed_experts(arr[:n])
+        text = engine.tokenizer.decode(self.output_ids) if engine.tokenizer is not None else ""
+        return {"text": text, "output_ids": list(self.output_ids), "meta_info": meta}
+
+
+class Engine:
+    def __init__(self, cfg: ModelConfig, *, model: Qwen3Model | None = None, ps: ParallelState | None = None,
+                 device="cpu", dtype=torch.bfloat16, num_blocks: int | None = None, block_size: int | None = None,
+                 mem_fraction_static: float = 0.7, max_running_requests: int = 512, max_prefill_tokens: int = 16384,
+                 max_context_len: int | None = None, eos_token_ids: list[int] | None = None, tokenizer=None,
+                 seed: int = 0, use_cuda_graph: bool = True, record_routing: bool | None = None):
+        self.cfg = cfg
+        self.ps = ps or ParallelState.single()
+        self.device = torch.device(device)
+        self.dtype = dtype
+        self.model = model if model is not None else build_model(cfg, self.ps, dtype=dtype, device=device, seed=seed)
+        self.owns_model = model is None
+        self.block_size = block_size or (64 if self.device.type == "cuda" else 16)
+        self.max_running = max_running_requests
+        self.max_prefill_tokens = max_prefill_tokens
+        self.max_context_len = max_context_len or cfg.max_position
+        self.eos_token_ids = set(eos_token_ids or [])
+        self.tokenizer = tokenizer
+        self.mem_fraction_static = mem_fraction_static
+        self.use_cuda_graph = use_cuda_graph and self.device.type == "cuda"
+        hkv = cfg.num_kv_heads // self.ps.tp_size
+        if num_blocks is None:
+            if self.device.type == "cuda":
+                free, total = torch.cuda.mem_get_info(self.device)
+                budget = int(free - (1.0 - mem_fraction_static) * total)
+                budget = max(budget, 1 << 30)
+                num_blocks = KVCache.blocks_for_budget(budget, len(self.model.layers), self.block_size, hkv, cfg.head_dim, dtype)
+            else:
+                num_blocks = 512
+        lo, hi = self.model.layer_range
+        self.kv = KVCache(hi - lo, num_blocks, self.block_size, hkv, cfg.head_dim, dtype, self.device,
+                          layer_ids=list(range(lo, hi)))
+        self.allocator = make_allocator(num_blocks)
+        self.waiting: deque[Request] = deque()
+        self.running: list[Request] = []
+        self.requests: dict[str, Request] = {}
+        self.weight_version = 0
+        self.paused = False
+        self.lock = threading.RLock()
+        self._rid = itertools.count()
+        self.seed = seed
+        self._step_count = 0
+        self.stats = {"prefill_tokens": 0, "decode_tokens": 0, "steps": 0, "retractions": 0}
+        self._loop_thread: threading.Thread | None = None
+        self._stop_loop = False
+        self._graphs: dict[int, Any] = {}
+        # expert-parallel engines step in lockstep over the EP group (see `_step_lockstep`)
+        self.lockstep_group = self.ps.ep_group if (self.ps.ep_size > 1 and cfg.is_moe) else None
+        self.local_done = True
+        self.global_done = True
+
+    # ---------------------------------------------------------------------------------------
+    # request API
+    # ---------------------------------------------------------------------------------------
+    def add_request(self, input_ids: list[int], sampling_params: dict | SamplingParams | None = None,
+                    return_logprob: bool = True, return_routed_experts: bool = False, rid: str | None = None,
+                    on_done=None) -> Request:
+        sp = sampling_params if isinstance(sampling_params, SamplingParams) else SamplingParams.from_dict(sampling_params)
+        with self.lock:
+            rid = rid or f"req-{next(self._rid)}"
+            req = Request(rid=rid, input_ids=list(input_ids), sampling=sp, return_logprob=return_logprob,
+                          return_routed_experts=return_routed_experts and self.cfg.is_moe,
+                          seed=(sp.seed if sp.seed is not None else (self.seed * 1000003 + zlib.crc32(rid.encode())) % (2 ** 31)),
+                          on_done=on_done)
+            budget = self.max_context_len - len(input_ids)
+            if budget <= 0 or sp.max_new_tokens <= 0:
+                req.finish_reason = {"type": "length", "length": 0}
+                req.done.set()
+                if on_done is not None:
+                    on_done(req)
+                return req
+            sp.max_new_tokens = min(sp.max_new_tokens, budget)
+            self.requests[rid] = req
+            self.waiting.append(req)
+        return req
+
+    def abort_request(self, rid: str | None = None):
+        """Abort one request (or all when rid is None); partial output is kept in the reply."""
+        with self.lock:
+            targets = [self.requests[rid]] if rid is not None and rid in self.requests else \
+                (list(self.requests.values()) if rid is None else [])
+            for r in targets:
+                if not r.finished:
+                    self._finish(r, {"type": "abort"})
+            self.running = [r for r in self.running if not r.finished]
+            self.waiting = deque(r for r in self.waiting if not r.finished)
+
+    def generate(self, input_ids: list[int] | list[list[int]], sampling_params: dict | list[dict] | None = None,
+                 return_logprob: bool = True, return_routed_experts: bool = False) -> dict | list[dict]:
+        """Blocking generate; drives the step loop itself unless a background loop is running."""
+        single = bool(input_ids) and isinstance(input_ids[0], int)
+        batch = [input_ids] if single else list(input_ids)
+        sps = sampling_params if isinstance(sampling_params, list) else [sampling_params] * len(batch)
+        reqs = [self.add_request(ids, dict(sp) if isinstance(sp, dict) else sp, return_logprob, return_routed_experts)
+                for ids, sp in zip(batch, sps)]
+        if self.lockstep_group is not None:
+            self.begin_rollout()
+            while True:
+                if all(r.done.is_set() for r in reqs):
+                    self.finish_rollout()
+                if not self.step() and self.global_done:
+                    break
+        elif self._loop_thread is None:
+            while not all(r.done.is_set() for r in reqs):
+                if not self.step():
+                    if self.paused:
+                        time.sleep(0.001)
+                    elif not self.waiting and not self.running:
+                        break
+        else:
+            for r in reqs:
+                r.done.wait()
+        out = [r.to_response(self) for r in reqs]
+        return out[0] if single else out
+
+    # ---------------------------------------------------------------------------------------
+    # control surface (names follow the HTTP endpoints the reference calls)
+    # ---------------------------------------------------------------------------------------
+    def pause_generation(self, mode: str = "retract"):
+        """abort: finish running requests with reason abort; retract: push them back to waiting and free
+        their KV; in_place: keep KV, just stop stepping."""
+        with self.lock:
+            self.paused = True
+            if mode == "abort":
+                self.abort_request(None)
+            elif mode == "retract":
+                for r in list(self.running):
+                    self._retract(r)
+
+    def continue_generation(self):
+        with self.lock:
+            self.paused = False
+
+    def flush_cache(self) -> bool:
+        with self.lock:
+            if self.running:
+                return False
+            self.allocator.reset()
+            return True
+
+    def update_weight_version(self, version: int):
+        self.weight_version = int(version)
+
+    def get_weight_version(self) -> int:
+        return self.weight_version
+
+    def update_weights_from_tensor(self, named_tensors, weight_version: int | None = None, load_format: str | None = None):
+        """Copy (or alias) tensors into the engine's model. Names are this package's parameter names for
+        this rank's shard; HF-named full tensors go through `miles_b200.models.convert.load_hf_into`."""
+        from ..models.convert import load_named_into_model
+
+        with self.lock:
+            load_named_into_model(self.model, named_tensors, self.cfg, self.ps)
+            if weight_version is not None:
+                self.weight_version = int(weight_version)
+        return {"success": True}
+
+    def release_memory_occupation(self, tags: list[str] | None = None):
+        tags = tags or ["kv_cache", "weights", "cuda_graph"]
+        with self.lock:
+            assert not self.running, "release_memory_occupation with requests in flight; pause (retract) first"
+            if "kv_cache" in tags:
+                self.kv.free()
+                self.allocator.reset()
+            if "cuda_graph" in tags:
+                self._graphs.clear()
+            if "weights" in tags and self.owns_model:
+                self._weights_host = {n: p.data.to("cpu") for n, p in self.model.named_parameters()}
+                for p in self.model.parameters():
+                    p.data = torch.empty(0, dtype=p.dtype, device=p.device)
+            if torch.cuda.is_available():
+                torch.cuda.empty_cache()
+
+    def resume_memory_occupation(self, tags: list[str] | None = None):
+        tags = tags or ["kv_cache", "weights", "cuda_graph"]
+        with self.lock:
+            if "weights" in tags and getattr(self, "_weights_host", None):
+                for n, p in self.model.named_parameters():
+                    p.data = self._weights_host[n].to(self.device)
+                self._weights_host = None
+            if "kv_cache" in tags and not self.kv.allocated:
+                self.kv.allocate()
+
+    def health(self) -> dict:
+        return {"status": "ok", "running": len(self.running), "waiting": len(self.waiting),
+                "free_blocks": self.allocator.num_free, "weight_version": self.weight_version, "paused": self.paused}
+
+    # ---------------------------------------------------------------------------------------
+    # background loop (server mode)
+    # ---------------------------------------------------------------------------------------
+    def start_loop(self):
+        if self._loop_thread is not None:
+            return
+        self._stop_loop = False
+
+        def run():
+            if self.device.type == "cuda":
+                torch.cuda.set_device(self.device)
+            while not self._stop_loop:
+                if not self.step():
+                    time.sleep(0.0005)
+
+        self._loop_thread = threading.Thread(target=run, daemon=True, name="engine-loop")
+        self._loop_thread.start()
+
+    def stop_loop(self):
+        self._stop_loop = True
+        if self._loop_thread is not None:
+            self._loop_thread.join(timeout=10)
+            self._loop_thread = None
+
+    # ---------------------------------------------------------------------------------------
+    # scheduler
+    # ---------------------------------------------------------------------------------------
+    def _blocks_needed(self, num_tokens: int) -> int:
+        return (num_tokens + self.block_size - 1) // self.block_size
+
+    def _finish(self, r: Request, reason: dict):
+        r.finish_reason = reason
+        if r.blocks:
+            self.allocator.release(r.blocks)
+            r.blocks = []
+        self.requests.pop(r.rid, None)
+        r.done.set()
+        if r.on_done is not None:
+            r.on_done(r)
+
+    def _retract(self, r: Request):
+        """Give the blocks back; the request restarts from a prefill of prompt+output."""
+        if r.blocks:
+            self.allocator.release(r.blocks)
+        r.blocks, r.num_cached = [], 0
+        r.retractions += 1
+        self.stats["retractions"] += 1
+        if r in self.running:
+            self.running.remove(r)
+        self.waiting.appendleft(r)
+
+    @torch.no_grad()
+    def step(self) -> bool:
+        """One scheduling step. Returns False when there was nothing to do."""
+        with self.lock:
+            if self.lockstep_group is not None:
+                return self._step_lockstep()
+            if self.paused or not self.kv.allocated:
+                return False
+            batch = self._schedule_prefill()
+            if batch:
+                self._run_prefill(batch)
+            elif self.running:
+                if not self._ensure_decode_blocks():
+                    return True
+                self._run_decode()
+            else:
+                return False
+            self.stats["steps"] += 1
+            self._step_count += 1
+            return True
+
+    def _step_lockstep(self) -> bool:
+        """Expert-parallel engines run the same kind of step at the same time because every MoE layer is a
+        collective: ranks agree (one 3-int all-reduce) on prefill vs decode; a rank without work of that kind
+        runs an empty batch.  `global_done` turns true once every rank called `finish_rollout()` and is idle."""
+        import torch.distributed as dist
+
+        batch = [] if self.paused else self._schedule_prefill()
+        want_decode = bool(self.running) and not self.paused and not batch
+        if want_decode and not self._ensure_decode_blocks():
+            want_decode = False
+        flags = torch.tensor([int(bool(batch)), int(want_decode), int(not self.local_done)], dtype=torch.int32,
+                             device=self.device if self.device.type == "cuda" else "cpu")
+        dist.all_reduce(flags, op=dist.ReduceOp.MAX, group=self.lockstep_group)
+        any_prefill, any_decode, any_active = (int(v) for v in flags.tolist())
+        self.global_done = not any_active and not any_prefill and not any_decode
+        if any_prefill:
+            self._run_prefill(batch)
+        elif any_decode:
+            self._run_decode()
+        else:
+            return False
+        self.stats["steps"] += 1
+        self._step_count += 1
+        return True
+
+    def begin_rollout(self):
+        self.local_done = False
+        self.global_done = False
+
+    def finish_rollout(self):
+        self.local_done = True
+
+    def _schedule_prefill(self) -> list[Request]:
+        batch, tokens = [], 0
+        while self.waiting and len(self.running) + len(batch) < self.max_running:
+            r = self.waiting[0]
+            n = len(r.all_ids)
+            if batch and tokens + n > self.max_prefill_tokens:
+                break
+            need = self._blocks_needed(n + 1)
+            # keep headroom so running requests can still grow by one block each
+            if need + len(self.running) > self.allocator.num_free and (self.running or batch):
+                break
+            blocks = self.allocator.alloc(need)
+            if blocks is None:
+                if not self.running and not batch:
+                    self.waiting.popleft()
+                    self._finish(r, {"type": "abort", "message": "prompt does not fit in the KV cache"})
+                    continue
+                break
+            self.waiting.popleft()
+            r.blocks = blocks
+            batch.append(r)
+            tokens += n
+        return batch
+
+    def _ensure_decode_blocks(self) -> bool:
+        """Every running request needs a slot for its next token; retract the youngest on shortage."""
+        while True:
+            short = [r for r in self.running if len(r.all_ids) + 1 > len(r.blocks) * self.block_size]
+            if len(short) <= self.allocator.num_free:
+                for r in short:
+                    r.blocks += self.allocator.alloc(1)
+                return True
+            victim = max(self.running, key=lambda r: r.arrival)
+            self._retract(victim)
+            if not self.running:
+                return False
+
+    # ---------------------------------------------------------------------------------------
+    # model execution
+    # ---------------------------------------------------------------------------------------
+    def _slots(self, r: Request, start: int, end: int) -> list[int]:
+        bs = self.block_size
+        return [r.blocks[p // bs] * bs + p % bs for p in range(start, end)]
+
+    def _block_table(self, reqs: list[Request]) -> torch.Tensor:
+        mx = max((len(r.blocks) for r in reqs), default=1)
+        bt = torch.zeros(len(reqs), mx, dtype=torch.int32)
+        for i, r in enumerate(reqs):
+            bt[i, :len(r.blocks)] = torch.tensor(r.blocks, dtype=torch.int32)
+        return bt.to(self.device)
+
+    def _run_prefill(self, batch: list[Request]):
+        toks, pos, slots, cu = [], [], [], [0]
+        for r in batch:
+            ids = r.all_ids
+            toks += ids
+            pos += list(range(len(ids)))
+            slots += self._slots(r, 0, len(ids))
+            cu.append(cu[-1] + len(ids))
+        dev = self.device
+        record = [] if any(r.return_routed_experts for r in batch) else None
+        meta = ForwardMeta(
+            positions=torch.tensor(pos, dtype=torch.int32, device=dev),
+            cu_seqlens=torch.tensor(cu, dtype=torch.int32, device=dev),
+            max_seqlen=max((len(r.all_ids) for r in batch), default=0),
+            kv_cache=self.kv.layers, slot_mapping=torch.tensor(slots, dtype=torch.int64, device=dev),
+            record_topk=record)
+        hidden = self.model(torch.tensor(toks, dtype=torch.int32, device=dev), meta)
+        if not batch:
+            return
+        hidden = self.ps.sp_gather(hidden)
+        last = torch.tensor([c - 1 for c in cu[1:]], dtype=torch.int64, device=dev)
+        logits = self.model.logits(hidden[last])
+        self.stats["prefill_tokens"] += len(toks)
+        if record is not None:
+            rec = torch.stack(record, dim=1).cpu().numpy().astype(np.int32)  # [T, L_moe, k]
+            for r, a, b in zip(batch, cu[:-1], cu[1:]):
+                if r.return_routed_experts:
+                    # after a retraction the request already holds rows for its first num-recorded tokens
+                    have = sum(x.shape[0] for x in r.routed)
+                    r.routed.append(rec[a + have:b])
+        for r in batch:
+            r.num_cached = len(r.all_ids)
+        self._sample_and_append(batch, logits)
+        for r in batch:
+            if not r.finished:
+                self.running.append(r)
+
+    def _run_decode(self):
+        reqs = self.running
+        dev = self.device
+        toks = [r.all_ids[-1] for r in reqs]
+        pos = [len(r.all_ids) - 1 for r in reqs]
+        slots = [self._slots(r, p, p + 1)[0] for r, p in zip(reqs, pos)]
+        record = [] if any(r.return_routed_experts for r in reqs) else None
+        meta = ForwardMeta(
+            positions=torch.tensor(pos, dtype=torch.int32, device=dev), cu_seqlens=None, max_seqlen=1,
+            kv_cache=self.kv.layers, block_table=self._block_table(reqs),
+            seq_lens=torch.tensor([p + 1 for p in pos], dtype=torch.int32, device=dev),
+            slot_mapping=torch.tensor(slots, dtype=torch.int64, device=dev), record_topk=record)
+        hidden = self.model(torch.tensor(toks, dtype=torch.int32, device=dev), meta)
+        if not reqs:
+            return
+        hidden = self.ps.sp_gather(hidden)
+        logits = self.model.logits(hidden)
+        self.stats["decode_tokens"] += len(toks)
+        if record is not None:
+            rec = torch.stack(record, dim=1).cpu().numpy().astype(np.int32)
+            for i, r in enumerate(reqs):
+                if r.return_routed_experts:
+                    r.routed.append(rec[i:i + 1])
+        self._sample_and_append(reqs, logits)
+        self.running = [r for r in reqs if not r.finished]
+
+    def _sample_and_append(self, reqs: list[Request], logits: torch.Tensor):
+        dev = self.device
+        temp = torch.tensor([r.sampling.temperature for r in reqs], dtype=torch.float32, device=dev)
+        top_p = torch.tensor([r.sampling.top_p for r in reqs], dtype=torch.float32, device=dev)
+        top_k = torch.tensor([r.sampling.top_k for r in reqs], dtype=torch.int64, device=dev)
+        seeds = torch.tensor([r.seed for r in reqs], dtype=torch.int64, device=dev)
+        gen = None
+        if dev.type == "cpu":
+            gen = torch.Generator().manual_seed((self.seed * 7919 + self._step_count) % (2 ** 31))
+        tok, lp = sample(logits.float(), temp, top_p, top_k, generator=gen, seeds=seeds, step=self._step_count)
+        tok_l, lp_l = tok.tolist(), lp.tolist()
+        for r, t, l in zip(reqs, tok_l, lp_l):
+            r.output_ids.append(int(t))
+            r.output_logprobs.append(float(l))
+            if r.weight_versions and r.weight_versions[-1][0] == self.weight_version:
+                r.weight_versions[-1][1] += 1
+            else:
+                r.weight_versions.append([self.weight_version, 1])
+            stop = set(r.sampling.stop_token_ids) | (set() if r.sampling.ignore_eos else self.eos_token_ids)
+            if int(t) in stop:
+                self._finish(r, {"type": "stop", "matched": int(t)})
+            elif len(r.output_ids) >= r.sampling.max_new_tokens:
+                self._finish(r, {"type": "length", "length": len(r.output_ids)})

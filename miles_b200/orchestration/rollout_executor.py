@@ -1,0 +1,140 @@
+"""RolloutExecutor: run the rollout function, convert samples to train data, split by DP.
+
+Reference: miles/ray/rollout/rollout_executor.py:53-338 (get / eval / save / load /
+set_weight_version) and train_data_conversion.py.  Process model here is SPMD: every rank owns a
+rollout-DP slice of the prompt groups (its engine, or its TP/EP group of engines, generates them);
+the slices are exchanged with one object all-gather so every rank sees the same global batch, which
+is then partitioned over the trainer's data-parallel ranks.
+"""
+from __future__ import annotations
+
+import json
+import os
+import time
+from typing import Any
+
+import torch
+import torch.distributed as dist
+
+from ..rollout.inference_rollout import InferenceRolloutFn, RolloutFnEvalInput, RolloutFnTrainInput
+from ..train.data import convert_samples_to_train_data, split_train_data_by_dp
+from ..types import RolloutDataPack, Sample
+from ..utils import object_store
+from ..utils.misc import load_function
+
+
+class RolloutExecutor:
+    def __init__(self, args, data_source, client, *, ps=None, rollout_dp_size: int = 1, rollout_dp_rank: int = 0,
+                 gather_group=None, eval_sources=None, tracker=None):
+        self.args, self.data_source, self.client = args, data_source, client
+        self.ps = ps
+        self.rollout_dp_size, self.rollout_dp_rank = rollout_dp_size, rollout_dp_rank
+        self.gather_group = gather_group
+        self.tracker = tracker
+        self.weight_version = 0
+        path = getattr(args, "rollout_function_path", None)
+        fn_cls = load_function(path) if path else InferenceRolloutFn
+        self.local_args = self._localise(args)
+        self.rollout_fn = fn_cls(self.local_args, data_source, client, eval_sources) if isinstance(fn_cls, type) else fn_cls
+        self.eval_fn = self.rollout_fn
+        if getattr(args, "eval_function_path", None):
+            ef = load_function(args.eval_function_path)
+            self.eval_fn = ef(self.local_args, data_source, client, eval_sources) if isinstance(ef, type) else ef
+
+    def _localise(self, args):
+        """Each rollout-DP rank produces its share of the rollout batch."""
+        import copy
+
+        a = copy.copy(args)
+        if self.rollout_dp_size > 1:
+            assert args.rollout_batch_size % self.rollout_dp_size == 0, "rollout_batch_size must divide rollout DP"
+            a.rollout_batch_size = args.rollout_batch_size // self.rollout_dp_size
+            a.over_sampling_batch_size = max(1, (args.over_sampling_batch_size or args.rollout_batch_size) // self.rollout_dp_size)
+        return a
+
+    # ---------------------------------------------------------------------------------------
+    def get(self, rollout_id: int) -> RolloutDataPack:
+        args = self.args
+        t0 = time.time()
+        if getattr(args, "load_debug_rollout_data", None):
+            path = args.load_debug_rollout_data.format(rollout_id=rollout_id)
+            raw = torch.load(path, weights_only=False)
+            groups = [[Sample.from_dict(d) for d in g] for g in raw["samples"]]
+            metrics = {}
+        else:
+            out = self._call(self.rollout_fn, RolloutFnTrainInput(rollout_id))
+            groups, metrics = out.samples, dict(out.metrics)
+        groups = self._exchange(groups)
+        if getattr(args, "save_debug_rollout_data", None) and (not dist.is_initialized() or dist.get_rank() == 0):
+            path = args.save_debug_rollout_data.format(rollout_id=rollout_id)
+            os.makedirs(os.path.dirname(path) or ".", exist_ok=True)
+            torch.save({"rollout_id": rollout_id, "samples": [[s.to_dict() for s in g] for g in groups]}, path)
+        data = convert_samples_to_train_data(args, groups)
+        metrics.update(self._rollout_metrics(groups, data, time.time() - t0))
+        dp = self.ps.dp_size if self.ps is not None else 1
+        shards = split_train_data_by_dp(args, data, dp)
+        mine = self.ps.dp_rank if self.ps is not None else 0
+        ref = object_store.put(shards[mine])
+        return RolloutDataPack(rollout_id=rollout_id, sample_indices=data["sample_indices"], data_ref=ref, metrics=metrics)
+
+    def eval(self, rollout_id: int) -> dict:
+        out = self._call(self.eval_fn, RolloutFnEvalInput(rollout_id))
+        metrics = {}
+        for name, d in out.data.items():
+            r = d["rewards"]
+            metrics[f"eval/{name}"] = sum(r) / max(1, len(r))
+            metrics[f"eval/{name}-truncated_ratio"] = sum(d["truncated"]) / max(1, len(r))
+        if self.tracker is not None:
+            self.tracker.log(metrics, step=rollout_id, step_key="eval/step")
+        return metrics
+
+    def _call(self, fn, inp):
+        return fn(inp)
+
+    def _exchange(self, groups: list[list[Sample]]) -> list[list[Sample]]:
+        if self.rollout_dp_size <= 1 or not dist.is_initialized():
+            return groups
+        world = dist.get_world_size(self.gather_group)
+        payload = [[s.to_dict() for s in g] for g in groups] if self._is_rollout_leader() else None
+        gathered: list = [None] * world
+        dist.all_gather_object(gathered, payload, group=self.gather_group)
+        out = []
+        for part in gathered:
+            if part:
+                out.extend([[Sample.from_dict(d) for d in g] for g in part])
+        out.sort(key=lambda g: g[0].index if g[0].index is not None else 0)
+        return out
+
+    def _is_rollout_leader(self) -> bool:
+        # within a TP/EP engine group every rank holds identical samples; one of them contributes
+        return getattr(self, "is_leader", True)
+
+    def _rollout_metrics(self, groups, data, dt) -> dict:
+        flat = [s for g in groups for s in g]
+        if not flat:
+            return {}
+        resp = [s.response_length for s in flat]
+        m = {
+            "rollout/raw_reward": sum(data["raw_reward"]) / len(flat),
+            "rollout/response_len/mean": sum(resp) / len(resp),
+            "rollout/response_len/max": max(resp),
+            "rollout/response_len/min": min(resp),
+            "rollout/truncated_ratio": sum(data["truncated"]) / len(flat),
+            "rollout/total_tokens": float(sum(data["total_lengths"])),
+            "perf/rollout_time": dt,
+            "perf/tokens_per_gpu_per_sec": sum(resp) / max(dt, 1e-9) / max(1, getattr(self.args, "rollout_num_gpus", 1) or 1),
+        }
+        if "rollout_log_probs" in data:
+            tot = sum(sum(x) for x in data["rollout_log_probs"])
+            m["rollout/log_probs"] = tot / max(1, sum(resp))
+        return m
+
+    # ---------------------------------------------------------------------------------------
+    def save(self, rollout_id: int):
+        self.data_source.save(rollout_id)
+
+    def load(self, rollout_id: int | None):
+        self.data_source.load(rollout_id)
+
+    def set_weight_version(self, v: int):
+        self.weight_version = v

@@ -1,0 +1,119 @@
+"""Wiring helpers used by the entry points: parallel state, trainer(s), rollout components, weight push.
+
+Names follow the reference's helpers (`create_rollout_components`, `create_training_models`,
+`update_weights`: miles/ray/placement_group.py:216-255,295-321,371-404).  Instead of Ray placement groups
+the process model is SPMD — one process per GPU started by torchrun (or a single process on CPU) — and
+the "controllers" are plain objects in each rank.
+"""
+from __future__ import annotations
+
+import os
+from dataclasses import dataclass
+from typing import Any
+
+import torch
+import torch.distributed as dist
+
+from ..args import model_config_from_args
+from ..parallel.state import ParallelState, init_distributed
+
+
+@dataclass
+class RolloutComponents:
+    engines: list
+    client: Any
+    executor: Any
+    data_source: Any
+
+
+def create_parallel_state(args) -> ParallelState:
+    rank, world, local = init_distributed()
+    if world == 1:
+        return ParallelState.single()
+    ps = ParallelState.build(
+        tp=args.tensor_model_parallel_size, cp=args.context_parallel_size, pp=args.pipeline_model_parallel_size,
+        ep=args.expert_model_parallel_size, sequence_parallel=args.sequence_parallel, cp_comm_type=args.cp_comm_type)
+    ps.fused = not getattr(args, "disable_fused_comm", False)
+    if torch.cuda.is_available() and ps.fused and (ps.tp_size > 1 or ps.ep_size > 1 or ps.dp_size > 1):
+        from ..parallel.fabric import Fabric
+
+        ps.fabric = Fabric.create(ps)
+    return ps
+
+
+def load_tokenizer(args):
+    path = getattr(args, "tokenizer_path", None) or getattr(args, "hf_checkpoint", None)
+    if not path or not os.path.isdir(path):
+        return None
+    try:
+        from transformers import AutoTokenizer
+
+        return AutoTokenizer.from_pretrained(path, trust_remote_code=True)
+    except Exception:
+        return None
+
+
+def create_training_models(args, ps: ParallelState):
+    from ..train.actor import TrainActor
+
+    actor = TrainActor(args, ps, role="actor")
+    start = actor.init()
+    critic = None
+    if args.advantage_estimator == "ppo":
+        critic = TrainActor(args, ps, role="critic")
+        critic.init()
+    return actor, critic, start
+
+
+def create_rollout_components(args, ps: ParallelState, actor=None, tracker=None) -> RolloutComponents:
+    from ..engine.engine import Engine
+    from ..rollout.client import HttpEngineClient, InProcEngineClient
+    from ..utils.misc import load_function
+    from .rollout_executor import RolloutExecutor
+
+    cfg = actor.cfg if actor is not None else model_config_from_args(args)
+    tok = load_tokenizer(args)
+    ds_cls = load_function(args.data_source_path)
+    data_source = ds_cls(args, tok)
+    kind = getattr(args, "rollout_engine", "native")
+    engines: list = []
+    if kind == "http":
+        client = HttpEngineClient(args.engine_kwargs["router_url"], tokenizer=tok,
+                                  num_moe_layers=sum(cfg.layer_is_moe(l) for l in range(cfg.num_layers)), moe_topk=cfg.moe_topk)
+    else:
+        ek = dict(getattr(args, "engine_kwargs", {}) or {})
+        device = actor.device if actor is not None else ("cuda" if torch.cuda.is_available() else "cpu")
+        dtype = next(actor.model.parameters()).dtype if actor is not None else torch.bfloat16
+        share = actor is not None and getattr(args, "colocate", False) and not ek.get("own_weights", False)
+        eos = ek.get("eos_token_ids") or ([tok.eos_token_id] if tok is not None and tok.eos_token_id is not None else [])
+        engine = Engine(cfg, model=actor.model if share else None, ps=ps, device=device, dtype=dtype,
+                        num_blocks=ek.get("num_blocks"), block_size=ek.get("block_size"),
+                        mem_fraction_static=ek.get("mem_fraction_static", 0.7),
+                        max_running_requests=ek.get("max_running_requests", 512),
+                        max_prefill_tokens=ek.get("max_prefill_tokens", 16384),
+                        max_context_len=getattr(args, "rollout_max_context_len", None), eos_token_ids=eos, tokenizer=tok,
+                        seed=args.rollout_seed, use_cuda_graph=not ek.get("disable_cuda_graph", False))
+        engines = [engine]
+        client = InProcEngineClient(engines, tokenizer=tok, policy=getattr(args, "router_policy", "least_active"))
+    # rollout data parallelism: one engine group per (tp × ep-within-dp) block; groups take disjoint prompts
+    # (ranks of one TP group replicate the same requests; EP is orthogonal: DP attention + EP experts)
+    assert ps.pp_size == 1 or kind == "http", "the in-process engine runs without pipeline parallelism"
+    rollout_dp = max(1, ps.world_size // ps.tp_size)
+    rollout_dp_rank = ps.rank // ps.tp_size
+    ex = RolloutExecutor(args, data_source, client, ps=ps, rollout_dp_size=rollout_dp, rollout_dp_rank=rollout_dp_rank,
+                         tracker=tracker)
+    ex.is_leader = ps.tp_rank == 0 and ps.pp_rank == 0
+    # distinct prompts per rollout-DP rank: advance the data source by rank-dependent seeds
+    if hasattr(data_source, "gen"):
+        data_source.gen.manual_seed(args.rollout_seed * 9973 + rollout_dp_rank)
+    return RolloutComponents(engines=engines, client=client, executor=ex, data_source=data_source)
+
+
+def update_weights(args, actor, rollout: RolloutComponents, updater=None) -> dict:
+    """start → actor.update_weights → end; publishes the new weight version to the executor."""
+    from ..weight_update.updater import WeightUpdater
+
+    updater = updater or WeightUpdater(args, actor, rollout.engines)
+    info = actor.update_weights(updater)
+    rollout.executor.set_weight_version(actor.weight_version)
+    return info

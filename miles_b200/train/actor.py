@@ -1,0 +1,398 @@
+"""Trainer worker: owns one rank's model shard, optimizer shard and weight tags.
+
+The worker contract is the reference's `TrainRayActor` (miles/ray/train_actor.py:56-243;
+Megatron subclass miles/backends/megatron_utils/actor.py:105-1008): `init`, `train`,
+`update_weights`, `save_model`, `sleep`, `wake_up`, plus log-prob-only passes for the reference
+and old-actor tags.  One RL step (reference call stack: actor.py:657-812 → model.py:281-872):
+
+    shard of rollout data → micro-batches → [ref log-probs] → [old log-probs] → advantages
+    → for each optimizer step: forward/backward over micro-batches → grad reduce → Adam
+"""
+from __future__ import annotations
+
+import os
+import time
+from argparse import Namespace
+from contextlib import contextmanager
+from typing import Any
+
+import torch
+import torch.distributed as dist
+
+from ..args import model_config_from_args
+from ..models.config import ModelConfig
+from ..models.qwen3 import ForwardMeta, Qwen3Model, build_model
+from ..parallel.state import ParallelState
+from ..utils.timer import Timer
+from . import math_utils as mu
+from .advantages import compute_advantages_and_returns
+from .data import PackedBatch, flat_per_token, make_micro_batches, pack_micro_batch
+from .losses import LossBatch, loss_function
+from .optimizer import DistributedAdam, LRScheduler, mark_expert_params
+
+
+class TensorBackuper:
+    """Named snapshots of the model weights in pinned host memory (`actor`, `ref`, `old_actor`,
+    `teacher`), swapped into the live parameters for log-prob passes
+    (reference: weights_backuper in miles/backends/megatron_utils/actor.py:418-434,787-790)."""
+
+    def __init__(self, model: torch.nn.Module):
+        self.model = model
+        self.tags: dict[str, dict[str, torch.Tensor]] = {}
+
+    def backup(self, tag: str):
+        store = self.tags.setdefault(tag, {})
+        for n, p in self.model.named_parameters():
+            if n not in store:
+                t = torch.empty(p.shape, dtype=p.dtype, device="cpu")
+                if torch.cuda.is_available():
+                    t = t.pin_memory()
+                store[n] = t
+            store[n].copy_(p.data, non_blocking=True)
+        if torch.cuda.is_available():
+            torch.cuda.current_stream().synchronize()
+
+    def restore(self, tag: str):
+        store = self.tags[tag]
+        for n, p in self.model.named_parameters():
+            p.data.copy_(store[n], non_blocking=True)
+        if torch.cuda.is_available():
+            torch.cuda.current_stream().synchronize()
+
+    def has(self, tag: str) -> bool:
+        return tag in self.tags
+
+
+class TrainActor:
+    def __init__(self, args: Namespace, ps: ParallelState | None = None, device: str | torch.device | None = None,
+                 role: str = "actor"):
+        self.args = args
+        self.ps = ps or ParallelState.single()
+        self.role = role
+        if device is None:
+            device = torch.device("cuda", torch.cuda.current_device()) if torch.cuda.is_available() else "cpu"
+        self.device = torch.device(device)
+        self.timer = Timer()
+        self.model: Qwen3Model | None = None
+        self.optimizer: DistributedAdam | None = None
+        self.cfg: ModelConfig | None = None
+        self.asleep = False
+        self.weight_version = 0
+        self.global_step = 0
+        self.start_rollout_id = 0
+
+    # ---------------------------------------------------------------------------------------
+    # init
+    # ---------------------------------------------------------------------------------------
+    def init(self, cfg: ModelConfig | None = None, with_ref: bool | None = None) -> int:
+        args = self.args
+        self.cfg = cfg or model_config_from_args(args)
+        dtype = torch.float32 if getattr(args, "fp32", False) or not getattr(args, "bf16", True) else torch.bfloat16
+        torch.manual_seed(args.seed)
+        provider = getattr(args, "custom_model_provider_path", None)
+        if provider:
+            from ..utils.misc import load_function
+            self.model = load_function(provider)(args, self.cfg, self.ps, dtype, self.device)
+        else:
+            self.model = build_model(self.cfg, self.ps, dtype=dtype, device=self.device, seed=args.seed)
+        if getattr(args, "lora_rank", 0) > 0:
+            from .lora import apply_lora
+            apply_lora(self.model, args)
+        if self.role == "critic":
+            from .critic import attach_value_head
+            attach_value_head(self.model, self.cfg, dtype, self.device)
+        mark_expert_params(self.model)
+        named = list(self.model.named_parameters())
+        self.optimizer = DistributedAdam(
+            named, lr=args.lr if self.role == "actor" else args.critic_lr, betas=(args.adam_beta1, args.adam_beta2),
+            eps=args.adam_eps, weight_decay=args.weight_decay, clip_grad=args.clip_grad, ps=self.ps,
+            allocator=self._symmetric_allocator())
+        self.tp_replicated = {n for n, p in named if _tp_replicated(n)}
+        if self.ps.tp_size > 1:
+            self.optimizer.mark_tp_replicated(self.tp_replicated, named)
+        self.scheduler = LRScheduler(self.optimizer.lr, args.min_lr, args.lr_warmup_iters, args.lr_decay_iters,
+                                     args.lr_decay_style)
+        self.backuper = TensorBackuper(self.model)
+        # checkpoints
+        from ..checkpoint import manager as ckpt
+        loaded_iter = ckpt.load_into_actor(self, args)
+        if loaded_iter is not None:
+            self.start_rollout_id = loaded_iter + 1
+        need_ref = getattr(args, "need_ref", False) if with_ref is None else with_ref
+        if need_ref and self.role == "actor":
+            if getattr(args, "ref_load", None) and args.ref_load != getattr(args, "hf_checkpoint", None):
+                self.backuper.backup("actor")
+                ckpt.load_weights_only(self, args.ref_load)
+                self.backuper.backup("ref")
+                self.backuper.restore("actor")
+            else:
+                self.backuper.backup("ref")
+        return self.start_rollout_id
+
+    def _symmetric_allocator(self):
+        """Flat param/grad buffers come from the fabric's symmetric heap so peers can address them."""
+        fab = self.ps.fabric
+        if fab is None:
+            return None
+        return lambda n, dtype, device, tag: fab.alloc(n, dtype, tag=tag)
+
+    # ---------------------------------------------------------------------------------------
+    # forward helpers
+    # ---------------------------------------------------------------------------------------
+    def _meta(self, pb: PackedBatch, replay: bool) -> ForwardMeta:
+        rec = getattr(self.args, "recompute_granularity", None) == "full"
+        return ForwardMeta(positions=pb.positions, cu_seqlens=pb.cu_seqlens, max_seqlen=pb.max_seqlen,
+                           replay_topk=pb.replay_topk if replay else None, recompute=rec)
+
+    def _forward_logprobs(self, pb: PackedBatch, with_entropy: bool, replay: bool):
+        hidden = self.model(pb.tokens, self._meta(pb, replay))
+        if self.role == "critic":
+            h = self.ps.sp_gather(hidden)
+            return self.model.value_head(h[pb.gather_index].float()).squeeze(-1), None
+        h = self.ps.sp_gather(hidden)[pb.gather_index]
+        temp = getattr(self.args, "rollout_temperature", 1.0)
+        return self.ps.vocab_parallel_logprob(h, self.model.head_weight(), pb.targets, temp, with_entropy,
+                                              self.cfg.vocab_size)
+
+    @torch.no_grad()
+    def compute_log_probs(self, shard: dict, micro_batches: list[list[int]], tag: str | None = None) -> list[list[float]]:
+        """Forward-only pass; returns per-sample log-prob lists aligned with the shard order."""
+        if tag is not None and tag != "actor":
+            self.backuper.backup("actor")
+            self.backuper.restore(tag)
+        out: dict[int, torch.Tensor] = {}
+        replay = getattr(self.args, "use_routing_replay", False)
+        self.model.eval()
+        for idx in micro_batches:
+            pb = pack_micro_batch(shard, idx, self.device, pad_multiple=self._pad_multiple(), with_replay=replay)
+            lp, _ = self._forward_logprobs(pb, False, replay)
+            for i, piece in zip(idx, lp.float().split(pb.response_lengths)):
+                out[i] = piece
+        if tag is not None and tag != "actor":
+            self.backuper.restore("actor")
+        return [out[i] for i in sorted(out)]
+
+    def _pad_multiple(self) -> int:
+        return max(1, self.ps.tp_size) * (128 if self.device.type == "cuda" else 1)
+
+    # ---------------------------------------------------------------------------------------
+    # train
+    # ---------------------------------------------------------------------------------------
+    def train(self, rollout_id: int, shard: dict[str, Any]) -> dict[str, float]:
+        """One rollout's worth of optimisation on this rank's data shard."""
+        args = self.args
+        if self.asleep:
+            self.wake_up()
+        t0 = time.time()
+        n = len(shard["tokens"])
+        dev = self.device
+        ps = self.ps
+        dp_group = ps.dp_group
+        with self.timer.span("data_preprocess"):
+            mbs = make_micro_batches(args, shard["total_lengths"], dp_group=dp_group, cp_size=ps.cp_size)
+        metrics: dict[str, float] = {}
+        # ---- forward-only passes ----------------------------------------------------------
+        ref_lp = old_lp = None
+        if self.role == "actor":
+            if getattr(args, "need_ref", False) and self.backuper.has("ref"):
+                with self.timer.span("ref_log_probs"):
+                    ref_lp = self.compute_log_probs(shard, mbs, tag="ref")
+            if not getattr(args, "skip_actor_forward_only", False) and not getattr(args, "use_rollout_logprobs", False):
+                with self.timer.span("log_probs"):
+                    old_lp = self.compute_log_probs(shard, mbs, tag=None)
+            elif getattr(args, "use_rollout_logprobs", False):
+                assert "rollout_log_probs" in shard, "--use-rollout-logprobs needs engine log-probs"
+        values = None
+        if self.role == "critic" or "values" in shard:
+            values = shard.get("values")
+            if values is None:
+                with self.timer.span("values"):
+                    values = self.compute_log_probs(shard, mbs, tag=None)
+                shard["values"] = values
+        # ---- advantages ---------------------------------------------------------------------
+        order = list(range(n))
+        resp = shard["response_lengths"]
+        lm_flat = flat_per_token(shard, "loss_masks", order, dev)
+        if "advantages" not in shard:
+            lp_flat = torch.cat(old_lp) if old_lp else (flat_per_token(shard, "rollout_log_probs", order, dev)
+                                                        if "rollout_log_probs" in shard else None)
+            ref_flat = torch.cat(ref_lp) if ref_lp else None
+            val_flat = torch.cat([torch.as_tensor(v, device=dev, dtype=torch.float32) for v in values]) if values is not None else None
+            adv, ret = compute_advantages_and_returns(
+                args, rewards=torch.tensor(shard["rewards"], device=dev), response_lengths=resp, loss_mask=lm_flat,
+                log_probs=lp_flat, ref_log_probs=ref_flat, values=val_flat, dp_group=dp_group)
+            shard["advantages"] = list(adv.split(resp))
+            shard["returns"] = list(ret.split(resp))
+        if getattr(args, "ci_test", False) and old_lp is not None and ref_lp is not None and rollout_id == 0 \
+                and not getattr(args, "ref_load", None):
+            kl0 = (torch.cat(old_lp) - torch.cat(ref_lp)).abs().max().item()
+            assert kl0 < 1e-5, f"KL between actor and reference must be 0 at step 0, got {kl0}"
+        # ---- optimisation -------------------------------------------------------------------
+        steps = max(1, getattr(args, "num_steps_per_rollout", 1) or 1)
+        self.model.train()
+        agg: dict[str, list] = {}
+        with self.timer.span("actor_train" if self.role == "actor" else "critic_train"):
+            per_step = _split_steps(mbs, steps)
+            for step_mbs in per_step:
+                step_metrics = self._train_one_step(shard, step_mbs, old_lp, ref_lp)
+                for k, v in step_metrics.items():
+                    agg.setdefault(k, []).append(v)
+        for k, v in agg.items():
+            metrics[f"train/{k}"] = float(sum(v) / len(v))
+        metrics["perf/train_time"] = time.time() - t0
+        tok = float(sum(shard["total_lengths"]))
+        metrics["perf/actor_train_tok_per_s"] = tok / max(metrics["perf/train_time"], 1e-9)
+        for k, v in self.timer.pop_all().items():
+            metrics[f"perf/{k}_time"] = v
+        self.weight_version += 1
+        return metrics
+
+    def _train_one_step(self, shard, mbs: list[list[int]], old_lp, ref_lp) -> dict[str, float]:
+        args, ps, dev = self.args, self.ps, self.device
+        self.optimizer.zero_grad()
+        replay = getattr(args, "use_routing_replay", False)
+        # global batch of this optimizer step = Σ over DP ranks of local samples
+        local_n = sum(len(m) for m in mbs)
+        local_tok = sum(sum(shard["loss_masks"][i]) for m in mbs for i in m)
+        counts = torch.tensor([float(local_n), float(local_tok)], device=dev)
+        if ps.dp_size > 1 and ps.dp_group is not None:
+            dist.all_reduce(counts, group=ps.dp_group)
+        gbs, gtok = max(1.0, counts[0].item()), max(1.0, counts[1].item())
+        sums: dict[str, torch.Tensor] = {}
+        count_sum = torch.zeros((), device=dev)
+        want_entropy = getattr(args, "entropy_coef", 0.0) != 0 or getattr(args, "log_entropy", True)
+        for idx in mbs:
+            pb = pack_micro_batch(shard, idx, dev, pad_multiple=self._pad_multiple(), with_replay=replay)
+            out, ent = self._forward_logprobs(pb, want_entropy and self.role == "actor", replay)
+            lb = LossBatch(
+                response_lengths=pb.response_lengths, loss_mask=pb.loss_mask, seq_ids=pb.seq_ids,
+                advantages=_cat(shard.get("advantages"), idx, dev), returns=_cat(shard.get("returns"), idx, dev),
+                old_log_probs=_cat(old_lp, idx, dev) if old_lp is not None else None,
+                ref_log_probs=_cat(ref_lp, idx, dev) if ref_lp is not None else None,
+                rollout_log_probs=flat_per_token(shard, "rollout_log_probs", idx, dev),
+                old_values=_cat(shard.get("values"), idx, dev) if self.role == "critic" else None,
+                denominators=torch.tensor([shard["rollout_mask_sums"][i] for i in idx], device=dev, dtype=torch.float32)
+                if "rollout_mask_sums" in shard else None)
+            if not idx:  # empty micro-batch keeps collectives aligned across DP ranks
+                loss = out.sum() * 0.0
+                loss.backward()
+                continue
+            loss, m, count = loss_function(self._loss_args(), lb, out, ent, global_batch_size=gbs,
+                                           global_num_tokens=gtok)
+            loss.backward()
+            for k, v in m.items():
+                sums[k] = sums.get(k, 0) + v.detach().float()
+            count_sum = count_sum + count
+        self._finalize_grads()
+        lr = self.scheduler.get()
+        stats = self.optimizer.step(lr)
+        self.scheduler.step()
+        self.global_step += 1
+        # metrics: Σ over micro-batches and DP ranks of reduced values / global count
+        keys = sorted(sums)
+        if ps.dp_size > 1 and ps.dp_group is not None:
+            # ranks may have seen different key sets only if some had empty batches; unify by name
+            all_keys = [None] * ps.dp_size
+            dist.all_gather_object(all_keys, keys, group=ps.dp_group)
+            keys = sorted(set(k for ks in all_keys for k in ks))
+        vec = torch.stack([count_sum] + [torch.as_tensor(sums.get(k, 0.0), device=dev, dtype=torch.float32) for k in keys]) \
+            if keys else count_sum[None]
+        if ps.dp_size > 1 and ps.dp_group is not None:
+            dist.all_reduce(vec, group=ps.dp_group)
+        denom = vec[0].clamp_min(1.0)
+        out_metrics = {k: (vec[1 + j] / denom).item() for j, k in enumerate(keys)}
+        out_metrics["grad_norm"] = stats["grad_norm"]
+        out_metrics["lr-pg_0"] = lr
+        return out_metrics
+
+    def _loss_args(self):
+        if self.role != "critic":
+            return self.args
+        a = Namespace(**vars(self.args))
+        a.loss_type = "value_loss"
+        return a
+
+    def _finalize_grads(self):
+        """Sum the partial gradients of tensor-parallel-replicated parameters over the TP group
+        (each TP rank saw a different sequence slice under sequence parallelism)."""
+        ps = self.ps
+        if ps.tp_size > 1 and ps.tp_group is not None:
+            grads = [p.main_grad for n, p in self.model.named_parameters() if n in self.tp_replicated and p.requires_grad]
+            if grads:
+                flat = torch.cat([g.reshape(-1) for g in grads])
+                dist.all_reduce(flat, group=ps.tp_group)
+                off = 0
+                for g in grads:
+                    g.copy_(flat[off:off + g.numel()].view_as(g))
+                    off += g.numel()
+
+    # ---------------------------------------------------------------------------------------
+    # weights: export / sync / save / sleep
+    # ---------------------------------------------------------------------------------------
+    def update_weights(self, engine_or_updater) -> dict:
+        """Push current weights to the rollout engine(s); see `miles_b200.weight_update`."""
+        from ..weight_update.updater import WeightUpdater
+
+        upd = engine_or_updater if isinstance(engine_or_updater, WeightUpdater) else \
+            WeightUpdater(self.args, self, engine_or_updater)
+        with self.timer.span("update_weights"):
+            info = upd.update_weights()
+        return info
+
+    def save_model(self, iteration: int, with_optimizer: bool = True):
+        from ..checkpoint import manager as ckpt
+        ckpt.save_from_actor(self, self.args, iteration, with_optimizer)
+
+    def sleep(self, tags=("optimizer", "grad")):
+        """Release trainer memory for the rollout phase (colocated mode): optimizer shards move to
+        pinned host memory, gradient buffers are dropped; the bf16 weights stay (the engine reads them)."""
+        from ..utils.memory import offload_tensors
+        if self.asleep:
+            return
+        groups = self.optimizer.tensors_by_tag()
+        self._offloaded = {}
+        if "optimizer" in tags:
+            self._offloaded["optimizer"] = offload_tensors(groups["optimizer"])
+        if "grad" in tags:
+            self.optimizer.release_grads()
+        self.asleep = True
+
+    def wake_up(self):
+        from ..utils.memory import onload_tensors
+        if not self.asleep:
+            return
+        for t, saved in self._offloaded.items():
+            onload_tensors(saved)
+        self._offloaded = {}
+        self.optimizer.restore_grads()
+        self.asleep = False
+
+    def named_weights(self):
+        """This rank's shard, named by our layout (for checkpointing and weight sync)."""
+        return [(n, p.data) for n, p in self.model.named_parameters()]
+
+
+def _tp_replicated(name: str) -> bool:
+    last = name.rsplit(".", 1)[-1]
+    return last in ("ln1", "ln2", "norm", "q_norm", "k_norm", "router")
+
+
+def _cat(lst, idx, dev):
+    if lst is None:
+        return None
+    parts = [torch.as_tensor(lst[i], device=dev, dtype=torch.float32) for i in idx]
+    return torch.cat(parts) if parts else torch.zeros(0, device=dev)
+
+
+def _split_steps(mbs: list[list[int]], steps: int) -> list[list[list[int]]]:
+    """Distribute micro-batches over `steps` optimizer steps (contiguous, as even as possible)."""
+    if steps <= 1:
+        return [mbs]
+    flat = [i for m in mbs for i in m]
+    per = (len(flat) + steps - 1) // steps
+    mb_size = max(1, max((len(m) for m in mbs), default=1))
+    out = []
+    for s in range(steps):
+        chunk = flat[s * per:(s + 1) * per]
+        out.append([chunk[i:i + mb_size] for i in range(0, len(chunk), mb_size)] or [[]])
+    return out

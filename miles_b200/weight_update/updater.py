@@ -1,0 +1,140 @@
+"""Trainer → rollout weight synchronisation.
+
+Session frame (reference: weight_update/session.py:14-99, updater.py:123-171):
+    pause_generation → flush_cache → begin_weight_update → [bucket stream] → end_weight_update
+    → update_weight_version → continue_generation
+with gloo-style barriers between phases when several trainer ranks take part.
+
+Transfer protocols (`--update-weight-transfer-mode`):
+* `alias`   colocated engine built on the trainer's own model object: nothing moves, version bump only.
+* `nvlink`  colocated engine with its own buffers in the same layout on the same / a peer GPU: one fused
+            kernel per bucket reshards (and, when the engine serves fp8/MXFP8, block-quantises) trainer
+            shards straight into the engine's buffers through peer pointers (`fused_weight_sync`).
+* `tensor`  bucket stream of HF-named full tensors handed to `engine.update_weights_from_tensor`
+            (the CUDA-IPC path of the reference, protocols/cuda_ipc.py:34-264, without serialisation
+            because the engine lives in this process).
+* `broadcast` HF-named buckets broadcast from trainer rank 0 over a process group that includes remote
+            engine processes (reference protocols/broadcast.py:21-208); HTTP engines are told names,
+            dtypes and shapes first.
+* `disk`    HF safetensors snapshot + `update_weights_from_disk` (reference protocols/delta.py, simplified
+            to full snapshots; deltas are computed by `miles_b200.weight_update.delta`).
+"""
+from __future__ import annotations
+
+import time
+from typing import Any
+
+import torch
+import torch.distributed as dist
+
+from .hf_iterator import iter_hf_weights
+
+
+class WeightUpdater:
+    def __init__(self, args, actor, engines, mode: str | None = None, quant: str | None = None):
+        self.args, self.actor = args, actor
+        self.engines = list(engines) if isinstance(engines, (list, tuple)) else [engines]
+        mode = mode or getattr(args, "update_weight_transfer_mode", "auto")
+        if mode == "auto":
+            if all(getattr(e, "model", None) is actor.model for e in self.engines):
+                mode = "alias"
+            elif all(hasattr(e, "model") for e in self.engines) and actor.device.type == "cuda" and \
+                    all(_same_layout(e, actor) for e in self.engines):
+                mode = "nvlink"
+            else:
+                mode = "tensor"
+        self.mode = mode
+        self.quant = quant
+        self.last_seconds = 0.0
+        self.connected_engines_hash = None
+
+    # ---- session frame -------------------------------------------------------------------
+    def _is_leader(self) -> bool:
+        return not dist.is_initialized() or dist.get_rank() == 0
+
+    def _barrier(self):
+        if dist.is_initialized() and dist.get_world_size() > 1:
+            dist.barrier()
+
+    def update_weights(self) -> dict:
+        t0 = time.perf_counter()
+        version = self.actor.weight_version
+        for e in self.engines:
+            e.pause_generation("retract")
+            e.flush_cache()
+        self._barrier()
+        t1 = time.perf_counter()
+        nbytes = getattr(self, f"_send_{self.mode}")()
+        if self.actor.device.type == "cuda":
+            torch.cuda.synchronize()
+        self._barrier()
+        t2 = time.perf_counter()
+        for e in self.engines:
+            e.update_weight_version(version)
+            e.continue_generation()
+        if getattr(self.args, "ci_test", False):
+            for e in self.engines:
+                assert e.get_weight_version() == version, "engine weight version differs from the trainer's"
+        if getattr(self.args, "check_weight_update_equal", False):
+            self.check_equal()
+        self.last_seconds = t2 - t1
+        return {"mode": self.mode, "bytes": nbytes, "seconds": t2 - t1, "total_seconds": time.perf_counter() - t0,
+                "weight_version": version}
+
+    # ---- protocols -----------------------------------------------------------------------
+    def _send_alias(self) -> int:
+        return 0
+
+    def _send_nvlink(self) -> int:
+        from ..parallel import weight_sync
+
+        n = 0
+        for e in self.engines:
+            n += weight_sync.fused_weight_sync(self.actor, e, quant=self.quant)
+        return n
+
+    def _send_tensor(self) -> int:
+        n = 0
+        size = getattr(self.args, "update_weight_buffer_size", 512 << 20)
+        for bucket in iter_hf_weights(self.actor, bucket_bytes=size, quant=self.quant):
+            n += sum(t.numel() * t.element_size() for _, t in bucket)
+            for e in self.engines:
+                e.update_weights_from_tensor(bucket, load_format="flattened_bucket")
+        return n
+
+    def _send_broadcast(self) -> int:
+        from .broadcast import broadcast_buckets
+
+        return broadcast_buckets(self)
+
+    def _send_disk(self) -> int:
+        import os
+        import tempfile
+
+        from ..checkpoint import hf_io
+
+        d = getattr(self.args, "update_weight_disk_dir", None) or tempfile.mkdtemp(prefix="miles_sync_")
+        d = os.path.join(d, f"v{self.actor.weight_version}")
+        hf_io.save_hf_sharded(d, iter_hf_weights(self.actor, bucket_bytes=None, quant=self.quant), self.actor.cfg,
+                              write=self._is_leader())
+        self._barrier()
+        for e in self.engines:
+            e.update_weights_from_disk(d)
+        return sum(p.numel() * p.element_size() for p in self.actor.model.parameters())
+
+    # ---- verification --------------------------------------------------------------------
+    def check_equal(self):
+        """Engine-side tensor compare (`--check-weight-update-equal`)."""
+        for e in self.engines:
+            if not hasattr(e, "model"):
+                continue
+            mine = dict(self.actor.model.named_parameters())
+            for n, p in e.model.named_parameters():
+                if n in mine and not torch.equal(p.data, mine[n].data):
+                    raise AssertionError(f"weight {n} differs between trainer and engine after update")
+
+
+def _same_layout(engine, actor) -> bool:
+    a, b = engine.ps, actor.ps
+    return (a.tp_size, a.ep_size, a.pp_size, a.tp_rank, a.ep_rank, a.pp_rank) == \
+           (b.tp_size, b.ep_size, b.pp_size, b.tp_rank, b.ep_rank, b.pp_rank)

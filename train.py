@@ -1,0 +1,89 @@
+"""Synchronous (optionally colocated) RL training loop.
+
+    rollout → [offload rollout / onload train] → critic/actor train → save → [offload train / onload
+    rollout] → update_weights → eval
+
+Same loop and flags as the reference's `train.py` (train.py:25-176); launch one process per GPU with
+torchrun (`python -m torch.distributed.run --nproc-per-node N train.py …`) or run directly on one
+device / CPU.
+"""
+from __future__ import annotations
+
+import os
+
+from miles_b200.args import parse_args
+from miles_b200.orchestration.wiring import (create_parallel_state, create_rollout_components, create_training_models,
+                                             update_weights)
+from miles_b200.utils import object_store
+from miles_b200.utils.tracking import Tracker
+
+
+def _should(interval, i, total=None):
+    if not interval:
+        return False
+    return (i + 1) % interval == 0 or (total is not None and i + 1 == total)
+
+
+def train(args):
+    ps = create_parallel_state(args)
+    tracker = Tracker(args, stdout=ps.rank == 0)
+    actor, critic, start_rollout_id = create_training_models(args, ps)
+    rollout = create_rollout_components(args, ps, actor, tracker)
+    rollout.executor.load(start_rollout_id - 1 if start_rollout_id > 0 else None)
+    if args.num_rollout is None:
+        assert args.num_epoch and len(rollout.data_source), "--num-rollout or --num-epoch (with --prompt-data) required"
+        args.num_rollout = args.num_epoch * len(rollout.data_source) // args.rollout_batch_size
+
+    if not args.debug_train_only:
+        update_weights(args, actor, rollout)           # initial push (and consistency check)
+    if args.offload_train and not args.debug_rollout_only:
+        actor.sleep()
+    if args.eval_interval and not args.skip_eval_before_train and start_rollout_id == 0:
+        rollout.executor.eval(0)
+
+    for rollout_id in range(start_rollout_id, args.num_rollout):
+        pack = rollout.executor.get(rollout_id)
+        if args.debug_rollout_only:
+            tracker.log(pack.metrics, rollout_id)
+            continue
+        if args.colocate and args.offload_rollout:
+            for e in rollout.engines:
+                e.pause_generation("retract")
+                e.release_memory_occupation(["kv_cache", "cuda_graph"])
+        shard = object_store.get(pack.data_ref)
+        metrics = dict(pack.metrics)
+        if critic is not None:
+            cm = critic.train(rollout_id, shard)
+            metrics.update({k.replace("train/", "train/critic-"): v for k, v in cm.items()})
+        if critic is None or rollout_id >= args.num_critic_only_steps:
+            metrics.update(actor.train(rollout_id, shard))
+        object_store.remove(pack.data_ref)
+
+        sentinel = args.save_trigger_sentinel and os.path.exists(args.save_trigger_sentinel)
+        if args.save and (_should(args.save_interval, rollout_id, args.num_rollout) or sentinel):
+            actor.save_model(rollout_id)
+            rollout.executor.save(rollout_id)
+            if sentinel and ps.rank == 0:
+                os.remove(args.save_trigger_sentinel)
+
+        if args.offload_train:
+            actor.sleep()
+        if args.colocate and args.offload_rollout:
+            for e in rollout.engines:
+                e.resume_memory_occupation(["weights"])
+        if _should(args.update_weights_interval, rollout_id):
+            info = update_weights(args, actor, rollout)
+            metrics["perf/update_weights_time"] = info["seconds"]
+        if args.colocate and args.offload_rollout:
+            for e in rollout.engines:
+                e.resume_memory_occupation(["kv_cache", "cuda_graph"])
+                e.continue_generation()
+        if _should(args.eval_interval, rollout_id):
+            metrics.update(rollout.executor.eval(rollout_id))
+        tracker.log(metrics, rollout_id)
+    tracker.finish()
+    return tracker
+
+
+if __name__ == "__main__":
+    train(parse_args())
