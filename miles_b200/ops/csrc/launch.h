@@ -1,0 +1,81 @@
+// C entry points of the kernels (raw pointers + stream); the torch bindings and C callers use these.
+#pragma once
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+// ---- gemm.cu ----
+int mb_gemm_bf16(const void* A, const void* B, void* C, int M, int N, int K, long long lda, long long ldb, long long ldc,
+                 int a_mn, int b_mn, int out_fp32, int accumulate, const void* bias, int force_bn, int* error_flag,
+                 cudaStream_t stream);
+int mb_gemm_bf16_grouped(const void* A, const void* B, void* C, int M_pad, int N, int K, int num_experts,
+                         const int* tile_expert, int b_mn, int out_fp32, int force_bn, int* error_flag, cudaStream_t stream);
+int mb_gemm_bf16_grouped_wgrad(const void* dY, const void* X, void* dW, int M_pad, int N, int K, int num_experts,
+                               const int* seg_offsets, int out_fp32, int accumulate, int force_bn, int* error_flag,
+                               cudaStream_t stream);
+
+// ---- elementwise.cu ----
+int mb_rmsnorm_fwd(const void* x, const void* residual, const void* w, void* y, void* res_out, float* rstd, long long T, int H,
+                   float eps, cudaStream_t s);
+int mb_rmsnorm_bwd_blocks(long long T);
+int mb_rmsnorm_bwd(const void* x, const void* w, const void* dy, const void* dres, const float* rstd, void* dx, float* dw_partial,
+                   void* dw_out, int dw_fp32, long long T, int H, cudaStream_t s);
+int mb_colsum(const float* partial, void* out, int R, int C, int out_fp32, cudaStream_t s);
+int mb_swiglu_fwd(const void* in, void* out, long long T, int F, cudaStream_t s);
+int mb_swiglu_bwd(const void* in, const void* dout, void* din, long long T, int F, cudaStream_t s);
+int mb_qk_norm_rope_fwd(const void* q, const void* k, long long q_stride, long long k_stride, const void* qw, const void* kw,
+                        const int* positions, void* qo, void* ko, float* q_rstd, float* k_rstd, long long T, int Hq, int Hk, int D,
+                        float theta, float eps, cudaStream_t s);
+int mb_qk_norm_rope_bwd_blocks(long long T, int Hn);
+int mb_qk_norm_rope_bwd(const void* x, long long x_stride, const void* w, const float* rstd, const void* dy, const int* positions,
+                        void* dx, long long dx_stride, float* dw_partial, void* dw_out, long long T, int Hn, int D, float theta,
+                        cudaStream_t s);
+int mb_kv_cache_write(const void* k, const void* v, long long k_stride, long long v_stride, void* kc, void* vc,
+                      const long long* slots, long long T, int row_elems, cudaStream_t s);
+int mb_adamw(float* master, const float* grad, float* m, float* v, const float* decay_mask, const float* scale_ptr, void* param_out,
+             int out_bf16, long long n, float lr, float b1, float b2, float eps, float wd, int step, cudaStream_t s);
+
+// ---- attention.cu ----
+int mb_flash_fwd(const void* q, const void* k, const void* v, void* o, float* lse, const int* cu_seqlens, int batch, int max_seqlen,
+                 int total_tokens, long long q_stride, long long k_stride, long long v_stride, int Hq, int Hkv, int D, float scale,
+                 int causal, cudaStream_t s);
+int mb_flash_bwd(const void* q, const void* k, const void* v, const void* o, const void* dout, const float* lse, float* delta,
+                 void* dq, void* dk, void* dv, const int* cu_seqlens, int batch, int max_seqlen, int total_tokens, long long q_stride,
+                 long long k_stride, long long v_stride, int Hq, int Hkv, int D, float scale, int causal, cudaStream_t s);
+int mb_paged_decode(const void* q, const void* kc, const void* vc, const int* block_table, const int* seq_lens, void* out,
+                    float* part_o, float* part_ml, int batch, int max_blocks, int block_size, int Hq, int Hkv, int D, float scale,
+                    int num_splits, cudaStream_t s);
+
+// ---- moe.cu ----
+int mb_router_topk(const float* logits, float* probs, float* topk_w, int* topk_idx, long long T, int E, int K, int normalize,
+                   cudaStream_t s);
+int mb_moe_align(const int* idx, int n, int E, int expert_offset, int* seg_offsets, int* tile_expert, int* row_src, int* dst_row,
+                 int max_rows, cudaStream_t s);
+int mb_moe_gather(const void* x, void* x_perm, const int* row_src, const int* seg_offsets, int E, int k, int H, int max_rows,
+                  cudaStream_t s);
+int mb_moe_combine(const void* y_perm, const float* w, const int* dst_row, void* out, long long T, int k, int H, cudaStream_t s);
+int mb_moe_combine_bwd(const void* dout, const void* y_perm, const float* w, const int* row_src, const int* seg_offsets, int E,
+                       void* dy_perm, float* dw, int k, int H, int max_rows, cudaStream_t s);
+
+// ---- misc.cu ----
+int mb_sample_logprob(const float* logits, const float* temperature, const uint8_t* greedy, const long long* seeds, long long step,
+                      long long* tokens, float* logprobs, int B, int V, cudaStream_t s);
+int mb_logit_stats(const float* logits, long long ld, const long long* targets, float* stats, long long R, int Vc, int v0,
+                   float inv_temp, int first, cudaStream_t s);
+int mb_logit_stats_finish(const float* stats, float* logp, float* ent, float* lse, long long R, cudaStream_t s);
+int mb_logit_grad(const float* logits, long long ld, const long long* targets, const float* lse, const float* ent, const float* g_lp,
+                  const float* g_ent, void* dlogits, long long ldd, long long R, int Vc, int v0, float inv_temp, cudaStream_t s);
+
+// ---- quant.cu ----
+int mb_mxfp8_quant(const void* x, void* q, void* scales, long long numel, cudaStream_t s);
+int mb_fp8_block_quant(const void* w, void* q, float* scale_inv, int M, int N, cudaStream_t s);
+int mb_int4_fake_quant(const void* x, void* y, float* scales, int M, int N, int bm, int bn, int symmetric, cudaStream_t s);
+int mb_nvfp4_qdq(const void* x, void* y, const float* global_amax, long long numel, cudaStream_t s);
+int mb_absmax(const void* x, float* out, long long numel, cudaStream_t s);
+
+#ifdef __cplusplus
+}
+#endif

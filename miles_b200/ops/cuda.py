@@ -1,0 +1,253 @@
+"""CUDA execution of the op layer: autograd Functions over the sm_100a extension (`miles_b200_C`).
+
+Importing this module loads the in-tree `.so`; it raises if the extension has not been built, so a
+GPU run can never silently fall back to library kernels.  All tensors are bf16 unless noted; fp32 is
+used for statistics, router maths, gradients-in-accumulation and optimizer state.
+"""
+from __future__ import annotations
+
+import math
+
+import torch
+
+from . import build as _build
+from . import reference as ref
+
+C = _build.load()
+
+BF16 = torch.bfloat16
+
+
+def check_error_flag(like: torch.Tensor | None = None) -> int:
+    """Value of the device error flag raised by a kernel whose bounded wait expired (0 = healthy).
+    Synchronises the device; call at step boundaries and in tests, not per op."""
+    t = like if like is not None else torch.empty(0, device="cuda")
+    return int(C.error_flag(t).item())
+
+
+def _c(x: torch.Tensor) -> torch.Tensor:
+    return x if x.is_contiguous() else x.contiguous()
+
+
+# ---------------------------------------------------------------------------------------------
+# GEMM
+# ---------------------------------------------------------------------------------------------
+
+def gemm_nt(a: torch.Tensor, b: torch.Tensor, out: torch.Tensor | None = None, *, bias=None, out_dtype=None,
+            accumulate: bool = False, force_bn: int = 0) -> torch.Tensor:
+    """a [M,K] · b [N,K]ᵀ → [M,N]."""
+    a, b = _c(a), _c(b)
+    M, K = a.shape
+    N = b.shape[0]
+    assert b.shape[1] == K and a.dtype == BF16 and b.dtype == BF16 and K % 8 == 0, (a.shape, b.shape, a.dtype)
+    if out is None:
+        out = torch.empty(M, N, dtype=out_dtype or BF16, device=a.device)
+    if M and N:
+        C.gemm(a, b, out, M, N, K, K, K, out.stride(0), False, False, accumulate, bias, force_bn)
+    return out
+
+
+def gemm_nn(a: torch.Tensor, b: torch.Tensor, out: torch.Tensor | None = None, *, out_dtype=None, force_bn: int = 0):
+    """a [M,K] · b [K,N] → [M,N] (b read as an MN-major operand; no transpose copy)."""
+    a, b = _c(a), _c(b)
+    M, K = a.shape
+    N = b.shape[1]
+    assert b.shape[0] == K and K % 8 == 0 and N % 8 == 0
+    if out is None:
+        out = torch.empty(M, N, dtype=out_dtype or BF16, device=a.device)
+    if M and N:
+        C.gemm(a, b, out, M, N, K, K, N, out.stride(0), False, True, False, None, force_bn)
+    return out
+
+
+def gemm_tn(a: torch.Tensor, b: torch.Tensor, out: torch.Tensor | None = None, *, out_dtype=None, accumulate=False,
+            force_bn: int = 0):
+    """a [K,M]ᵀ · b [K,N] → [M,N] (both MN-major: the weight-gradient form, reduction over rows)."""
+    a, b = _c(a), _c(b)
+    K, M = a.shape
+    N = b.shape[1]
+    assert b.shape[0] == K and M % 8 == 0 and N % 8 == 0
+    if out is None:
+        out = torch.empty(M, N, dtype=out_dtype or BF16, device=a.device)
+    if M and N:
+        if K == 0:
+            if not accumulate:
+                out.zero_()
+        else:
+            C.gemm(a, b, out, M, N, K, M, N, out.stride(0), True, True, accumulate, None, force_bn)
+    return out
+
+
+class _Linear(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, w, bias):
+        shp = x.shape
+        x2 = x.reshape(-1, shp[-1])
+        ctx.save_for_backward(x2, w)
+        ctx.has_bias = bias is not None
+        ctx.shp = shp
+        y = gemm_nt(x2, w, bias=bias)
+        return y.view(*shp[:-1], w.shape[0])
+
+    @staticmethod
+    def backward(ctx, gy):
+        x2, w = ctx.saved_tensors
+        gy2 = _c(gy.reshape(-1, gy.shape[-1]))
+        gx = gemm_nn(gy2, w).view(ctx.shp) if ctx.needs_input_grad[0] else None
+        gw = gemm_tn(gy2, x2) if ctx.needs_input_grad[1] else None
+        gb = gy2.float().sum(0).to(gy.dtype) if ctx.has_bias else None
+        return gx, gw, gb
+
+
+def linear(x, w, bias=None):
+    if x.dtype != BF16:
+        return torch.nn.functional.linear(x, w.to(x.dtype), bias)
+    return _Linear.apply(x, w, bias)
+
+
+def linear_dgrad(gy, w):
+    return gemm_nn(gy, w)
+
+
+def linear_wgrad(gy, x):
+    return gemm_tn(gy, x)
+
+
+# ---------------------------------------------------------------------------------------------
+# norms / activations
+# ---------------------------------------------------------------------------------------------
+
+class _RMSNorm(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, w, eps):
+        x = _c(x)
+        y = torch.empty_like(x)
+        rstd = torch.empty(x.numel() // x.shape[-1], dtype=torch.float32, device=x.device)
+        C.rmsnorm_fwd(x, None, w, y, None, rstd, eps)
+        ctx.save_for_backward(x, w, rstd)
+        return y
+
+    @staticmethod
+    def backward(ctx, gy):
+        x, w, rstd = ctx.saved_tensors
+        dx = torch.empty_like(x)
+        dw = C.rmsnorm_bwd(x, w, _c(gy), None, rstd, dx)
+        return dx, dw, None
+
+
+class _AddRMSNorm(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, residual, w, eps):
+        x, residual = _c(x), _c(residual)
+        y = torch.empty_like(x)
+        r = torch.empty_like(x)
+        rstd = torch.empty(x.numel() // x.shape[-1], dtype=torch.float32, device=x.device)
+        C.rmsnorm_fwd(x, residual, w, y, r, rstd, eps)
+        ctx.save_for_backward(r, w, rstd)
+        return y, r
+
+    @staticmethod
+    def backward(ctx, gy, gr):
+        r, w, rstd = ctx.saved_tensors
+        dx = torch.empty_like(r)
+        dw = C.rmsnorm_bwd(r, w, _c(gy), _c(gr) if gr is not None else None, rstd, dx)
+        return dx, dx, dw, None
+
+
+def rmsnorm(x, w, eps=1e-6):
+    if x.dtype != BF16:
+        return ref.rmsnorm(x, w, eps)
+    return _RMSNorm.apply(x, w, eps)
+
+
+def add_rmsnorm(x, residual, w, eps=1e-6):
+    if x.dtype != BF16:
+        return ref.add_rmsnorm(x, residual, w, eps)
+    return _AddRMSNorm.apply(x, residual, w, eps)
+
+
+class _SwiGLU(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, gate_up):
+        gate_up = _c(gate_up)
+        out = torch.empty(*gate_up.shape[:-1], gate_up.shape[-1] // 2, dtype=gate_up.dtype, device=gate_up.device)
+        C.swiglu_fwd(gate_up, out)
+        ctx.save_for_backward(gate_up)
+        return out
+
+    @staticmethod
+    def backward(ctx, g):
+        (gate_up,) = ctx.saved_tensors
+        din = torch.empty_like(gate_up)
+        C.swiglu_bwd(gate_up, _c(g), din)
+        return din
+
+
+def swiglu(gate_up):
+    if gate_up.dtype != BF16:
+        return ref.swiglu(gate_up)
+    return _SwiGLU.apply(gate_up)
+
+
+class _QKNormRope(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, q, k, qw, kw, positions, theta, eps):
+        T, Hq, D = q.shape
+        Hk = k.shape[1]
+        assert q.stride(2) == 1 and q.stride(1) == D and k.stride(2) == 1 and k.stride(1) == D
+        qo = torch.empty(T, Hq, D, dtype=q.dtype, device=q.device)
+        ko = torch.empty(T, Hk, D, dtype=k.dtype, device=k.device)
+        need = qw is not None
+        q_rstd = torch.empty(T * Hq, dtype=torch.float32, device=q.device) if need else None
+        k_rstd = torch.empty(T * Hk, dtype=torch.float32, device=q.device) if need else None
+        positions = positions.to(torch.int32)
+        C.qk_norm_rope_fwd(q, k, qw, kw, positions, qo, ko, q_rstd, k_rstd, theta, eps)
+        ctx.save_for_backward(q, k, qw, kw, positions, q_rstd, k_rstd)
+        ctx.theta = theta
+        return qo, ko
+
+    @staticmethod
+    def backward(ctx, gq, gk):
+        q, k, qw, kw, positions, q_rstd, k_rstd = ctx.saved_tensors
+        dq = torch.empty(q.shape, dtype=q.dtype, device=q.device)
+        dk = torch.empty(k.shape, dtype=k.dtype, device=k.device)
+        dqw = C.qk_norm_rope_bwd(q, qw, q_rstd, _c(gq), positions, dq, ctx.theta)
+        dkw = C.qk_norm_rope_bwd(k, kw, k_rstd, _c(gk), positions, dk, ctx.theta)
+        return dq, dk, (dqw if qw is not None else None), (dkw if kw is not None else None), None, None, None
+
+
+def qk_norm_rope(q, k, q_w, k_w, positions, theta, eps=1e-6):
+    if q.dtype != BF16 or q.shape[-1] not in (64, 128):
+        if q_w is not None:
+            q, k = ref.rmsnorm(q, q_w, eps), ref.rmsnorm(k, k_w, eps)
+        return ref.rope(q, positions, theta), ref.rope(k, positions, theta)
+    return _QKNormRope.apply(q, k, q_w, k_w, positions, float(theta), float(eps))
+
+
+def rope(x, positions, theta, inverse=False):
+    return ref.rope(x, positions, theta, inverse)
+
+
+def kv_cache_write(k, v, k_cache, v_cache, slot_mapping):
+    assert k.stride(2) == 1 and k.stride(1) == k.shape[2]
+    C.kv_cache_write(k.detach(), v.detach(), k_cache, v_cache, slot_mapping.to(torch.int64))
+
+
+# ---------------------------------------------------------------------------------------------
+# optimizer
+# ---------------------------------------------------------------------------------------------
+
+def adamw_step_masked(master, grad, exp_avg, exp_avg_sq, decay_mask, lr, b1, b2, eps, wd, step, scale, param_out):
+    if not torch.is_tensor(scale):
+        scale = torch.tensor([float(scale)], dtype=torch.float32, device=master.device)
+    else:
+        scale = scale.reshape(1).float()
+    C.adamw(master, grad, exp_avg, exp_avg_sq, decay_mask, scale, param_out, lr, b1, b2, eps, wd, step)
+
+
+def adamw_step(master, grad, exp_avg, exp_avg_sq, lr, beta1, beta2, eps, weight_decay, step, grad_scale=1.0, param_out=None):
+    adamw_step_masked(master, grad.float(), exp_avg, exp_avg_sq, None, lr, beta1, beta2, eps, weight_decay, step, grad_scale,
+                      param_out)
+
+
+from .cuda_more import *  # noqa: E402,F401,F403  (attention, MoE, log-prob, sampling, quantisation)

@@ -1,0 +1,295 @@
+"""Second half of the CUDA op layer: attention, MoE, log-prob head, sampling, quantisation."""
+from __future__ import annotations
+
+import math
+
+import torch
+
+from . import reference as ref
+from .cuda import BF16, C, _c, gemm_nn, gemm_nt, gemm_tn
+
+# ---------------------------------------------------------------------------------------------
+# attention
+# ---------------------------------------------------------------------------------------------
+
+
+class _FlashAttn(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, q, k, v, cu_seqlens, max_seqlen, causal):
+        T, Hq, D = q.shape
+        assert q.stride(2) == 1 and q.stride(1) == D and k.stride(1) == D and v.stride(1) == D and v.stride(2) == 1
+        scale = 1.0 / math.sqrt(D)
+        o = torch.empty(T, Hq, D, dtype=q.dtype, device=q.device)
+        lse = torch.empty(Hq, T, dtype=torch.float32, device=q.device)
+        if max_seqlen <= 0:
+            max_seqlen = int((cu_seqlens[1:] - cu_seqlens[:-1]).max().item())
+        C.flash_fwd(q, k, v, o, lse, cu_seqlens, max_seqlen, scale, causal)
+        ctx.save_for_backward(q, k, v, o, lse, cu_seqlens)
+        ctx.max_seqlen, ctx.causal, ctx.scale = max_seqlen, causal, scale
+        return o
+
+    @staticmethod
+    def backward(ctx, do):
+        q, k, v, o, lse, cu = ctx.saved_tensors
+        do = _c(do)
+        dq = torch.empty(q.shape, dtype=q.dtype, device=q.device)
+        dk = torch.empty(k.shape, dtype=k.dtype, device=k.device)
+        dv = torch.empty(v.shape, dtype=v.dtype, device=v.device)
+        delta = torch.empty_like(lse)
+        C.flash_bwd(q, k, v, o, do, lse, delta, dq, dk, dv, cu, ctx.max_seqlen, ctx.scale, ctx.causal)
+        return dq, dk, dv, None, None, None
+
+
+def attention_varlen(q, k, v, cu_seqlens, max_seqlen=0, causal=True):
+    if q.dtype != BF16 or q.shape[-1] not in (64, 128):
+        return ref.attention_varlen(q, k, v, cu_seqlens, causal)
+    return _FlashAttn.apply(q, k, v, cu_seqlens.to(torch.int32), int(max_seqlen), bool(causal))
+
+
+_DECODE_SPLITS = 8
+
+
+def paged_attention(q, k_cache, v_cache, block_table, seq_lens, q_lens=None, max_q_len=1):
+    """Decode (one new token per request) over the paged cache. Chunked prefill with a prefix is not a CUDA path."""
+    assert q_lens is None, "paged_attention on CUDA serves decode steps (q_len = 1)"
+    B, Hq, D = q.shape
+    group = Hq // k_cache.shape[2]
+    if q.dtype != BF16 or D not in (64, 128) or group not in (1, 2, 4, 8):
+        return ref.paged_attention(q, k_cache, v_cache, block_table, seq_lens)
+    q = _c(q)
+    out = torch.empty_like(q)
+    splits = _DECODE_SPLITS
+    part_o = torch.empty(B * Hq * splits * D, dtype=torch.float32, device=q.device)
+    part_ml = torch.empty(B * Hq * splits * 2, dtype=torch.float32, device=q.device)
+    C.paged_decode(q, k_cache, v_cache, block_table, seq_lens, out, part_o, part_ml, 1.0 / math.sqrt(D), splits)
+    return out
+
+
+# ---------------------------------------------------------------------------------------------
+# router
+# ---------------------------------------------------------------------------------------------
+
+class _RouterTopK(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, logits, k, normalize):
+        w, idx, probs = C.router_topk(_c(logits.float()), k, normalize, True)
+        ctx.save_for_backward(probs, idx, w)
+        ctx.normalize = normalize
+        ctx.mark_non_differentiable(idx)
+        return w, idx, probs
+
+    @staticmethod
+    def backward(ctx, gw, _gidx, gprobs):
+        probs, idx, w = ctx.saved_tensors
+        li = idx.long()
+        gw = gw.float()
+        if ctx.normalize:
+            # w_j = p_j / S, S = Σ_sel p  ⇒  dL/dp_j = (g_j − Σ_i g_i w_i) / S
+            S = probs.gather(1, li).sum(-1, keepdim=True).clamp_min(1e-20)
+            gp_sel = (gw - (gw * w).sum(-1, keepdim=True)) / S
+        else:
+            gp_sel = gw
+        gp = torch.zeros_like(probs).scatter_add_(1, li, gp_sel)
+        if gprobs is not None:
+            gp = gp + gprobs
+        # softmax backward
+        gl = probs * (gp - (gp * probs).sum(-1, keepdim=True))
+        return gl, None, None
+
+
+def router_topk(logits, k, normalize=True):
+    if logits.shape[-1] > 256:
+        return ref.router_topk(logits, k, normalize)
+    return _RouterTopK.apply(logits, int(k), bool(normalize))
+
+
+# ---------------------------------------------------------------------------------------------
+# MoE FFN (single rank or the local part of an expert-parallel layer)
+# ---------------------------------------------------------------------------------------------
+
+def moe_max_rows(n_pairs: int, num_experts: int) -> int:
+    """Worst-case padded row count: every expert's segment rounded up to 128."""
+    return (n_pairs + num_experts * 127 + 127) // 128 * 128
+
+
+class _MoEFFN(torch.autograd.Function):
+    """y[t] = Σ_j w[t,j] · W2[e]·swiglu(W13[e]·x[t]) with e = idx[t,j] − expert_offset ∈ [0, E_local) (others skipped)."""
+
+    @staticmethod
+    def forward(ctx, x, w13, w2, topk_w, topk_idx, expert_offset):
+        T, H = x.shape
+        E, F2, _ = w13.shape
+        F = F2 // 2
+        k = topk_idx.shape[1]
+        x = _c(x)
+        idx32 = _c(topk_idx.to(torch.int32)).view(-1)
+        wf = _c(topk_w.float())
+        max_rows = moe_max_rows(T * k, E)
+        seg, tile, row_src, dst_row = C.moe_align(idx32, E, expert_offset, max_rows)
+        x_perm = torch.empty(max_rows, H, dtype=x.dtype, device=x.device)
+        C.moe_gather(x, x_perm, row_src, seg, k)
+        h1 = torch.empty(max_rows, F2, dtype=x.dtype, device=x.device)
+        C.gemm_grouped(x_perm, w13, h1, max_rows, F2, H, E, tile, False, 0)
+        act = torch.empty(max_rows, F, dtype=x.dtype, device=x.device)
+        C.swiglu_fwd(h1, act)
+        y_perm = torch.empty(max_rows, H, dtype=x.dtype, device=x.device)
+        C.gemm_grouped(act, w2, y_perm, max_rows, H, F, E, tile, False, 0)
+        out = torch.empty(T, H, dtype=x.dtype, device=x.device)
+        C.moe_combine(y_perm, wf, dst_row, out, k)
+        ctx.save_for_backward(x, w13, w2, wf, seg, tile, row_src, dst_row, h1, y_perm)
+        ctx.k = k
+        return out
+
+    @staticmethod
+    def backward(ctx, dout):
+        x, w13, w2, wf, seg, tile, row_src, dst_row, h1, y_perm = ctx.saved_tensors
+        k = ctx.k
+        T, H = x.shape
+        E, F2, _ = w13.shape
+        F = F2 // 2
+        max_rows = h1.shape[0]
+        dout = _c(dout)
+        dy_perm = torch.empty(max_rows, H, dtype=x.dtype, device=x.device)
+        dw_flat = torch.zeros(T * k, dtype=torch.float32, device=x.device)
+        C.moe_combine_bwd(dout, y_perm, wf.view(-1), row_src, seg, dy_perm, dw_flat, k)
+        # through W2: dact = dy_perm · W2 ; dW2[e] = dy_permᵀ · act
+        act = torch.empty(max_rows, F, dtype=x.dtype, device=x.device)
+        C.swiglu_fwd(h1, act)
+        dact = torch.empty(max_rows, F, dtype=x.dtype, device=x.device)
+        C.gemm_grouped(dy_perm, w2, dact, max_rows, F, H, E, tile, True, 0)
+        dw2 = torch.empty_like(w2)
+        C.gemm_grouped_wgrad(dy_perm, act, dw2, max_rows, H, F, E, seg, False, 0)
+        # padded rows of `act`/`h1` hold garbage only where tiles were skipped; zero dact there via swiglu_bwd on zeros:
+        dh1 = torch.empty(max_rows, F2, dtype=x.dtype, device=x.device)
+        C.swiglu_bwd(h1, dact, dh1)
+        x_perm = torch.empty(max_rows, H, dtype=x.dtype, device=x.device)
+        C.moe_gather(x, x_perm, row_src, seg, k)
+        dw13 = torch.empty_like(w13)
+        C.gemm_grouped_wgrad(dh1, x_perm, dw13, max_rows, F2, H, E, seg, False, 0)
+        dx_perm = torch.empty(max_rows, H, dtype=x.dtype, device=x.device)
+        C.gemm_grouped(dh1, w13, dx_perm, max_rows, H, F2, E, tile, True, 0)
+        dx = torch.empty_like(x)
+        C.moe_combine(dx_perm, None, dst_row, dx, k)
+        return dx, dw13, dw2, dw_flat.view(T, k), None, None
+
+
+def moe_ffn(x, w13, w2, topk_w, topk_idx, expert_offset: int = 0):
+    if x.dtype != BF16:
+        return ref.moe_ffn(x, w13, w2, topk_w, topk_idx)
+    return _MoEFFN.apply(x, w13, w2, topk_w, topk_idx, int(expert_offset))
+
+
+# ---------------------------------------------------------------------------------------------
+# log-prob / entropy head: vocabulary streamed in chunks, logits never materialised in full
+# ---------------------------------------------------------------------------------------------
+_VOCAB_CHUNK = 16384
+_ROW_CHUNK = 16384
+
+
+def _vocab_chunks(V):
+    return [(v0, min(V, v0 + _VOCAB_CHUNK)) for v0 in range(0, V, _VOCAB_CHUNK)]
+
+
+class _LogProbEntropy(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, hidden, w, targets, temperature, with_entropy, vocab_offset):
+        R, H = hidden.shape
+        V = w.shape[0]
+        hidden = _c(hidden)
+        tg = _c(targets.to(torch.int64)) - vocab_offset
+        inv_t = 1.0 / temperature
+        logp = torch.empty(R, dtype=torch.float32, device=hidden.device)
+        ent = torch.empty(R, dtype=torch.float32, device=hidden.device)
+        lse = torch.empty(R, dtype=torch.float32, device=hidden.device)
+        for r0 in range(0, R, _ROW_CHUNK):
+            r1 = min(R, r0 + _ROW_CHUNK)
+            stats = torch.empty(r1 - r0, 4, dtype=torch.float32, device=hidden.device)
+            for ci, (v0, v1) in enumerate(_vocab_chunks(V)):
+                logits = gemm_nt(hidden[r0:r1], w[v0:v1], out_dtype=torch.float32)
+                C.logit_stats(logits, tg[r0:r1], stats, v0, inv_t, ci == 0)
+            C.logit_stats_finish(stats, logp[r0:r1], ent[r0:r1], lse[r0:r1])
+        ctx.save_for_backward(hidden, w, tg, lse, ent)
+        ctx.inv_t, ctx.with_entropy = inv_t, with_entropy
+        ctx.mark_non_differentiable(lse)
+        return logp, ent, lse
+
+    @staticmethod
+    def backward(ctx, g_lp, g_ent, _g_lse):
+        hidden, w, tg, lse, ent = ctx.saved_tensors
+        R, H = hidden.shape
+        V = w.shape[0]
+        g_lp = _c(g_lp.float()) if g_lp is not None else None
+        g_ent = _c(g_ent.float()) if (g_ent is not None and ctx.with_entropy) else None
+        dh = torch.zeros(R, H, dtype=torch.float32, device=hidden.device)
+        dw = torch.empty_like(w)
+        for (v0, v1) in _vocab_chunks(V):
+            dwc = None
+            for r0 in range(0, R, _ROW_CHUNK):
+                r1 = min(R, r0 + _ROW_CHUNK)
+                logits = gemm_nt(hidden[r0:r1], w[v0:v1], out_dtype=torch.float32)
+                dl = torch.empty(r1 - r0, v1 - v0, dtype=BF16, device=hidden.device)
+                C.logit_grad(logits, tg[r0:r1], lse[r0:r1], ent[r0:r1] if g_ent is not None else None,
+                             g_lp[r0:r1] if g_lp is not None else None, g_ent[r0:r1] if g_ent is not None else None, dl, v0,
+                             ctx.inv_t)
+                # dH[r0:r1] += dl · W_c   (fp32 accumulate in place)
+                Mr, Kc, Nh = r1 - r0, v1 - v0, H
+                C.gemm(dl, w[v0:v1], dh[r0:r1], Mr, Nh, Kc, Kc, Nh, H, False, True, True, None, 0)
+                # dW_c (+)= dlᵀ · H
+                if dwc is None:
+                    dwc = torch.empty(v1 - v0, H, dtype=torch.float32, device=hidden.device) if R > _ROW_CHUNK else dw[v0:v1]
+                    gemm_tn(dl, hidden[r0:r1], out=dwc)
+                else:
+                    gemm_tn(dl, hidden[r0:r1], out=dwc, accumulate=True)
+            if dwc.dtype != dw.dtype:
+                dw[v0:v1].copy_(dwc)
+        return dh.to(hidden.dtype), dw, None, None, None, None
+
+
+def logprob_entropy(hidden, w, targets, temperature=1.0, with_entropy=False, vocab_offset: int = 0, return_lse=False):
+    if hidden.dtype != BF16:
+        lp, ent = ref.logprob_entropy(hidden, w, targets, temperature, with_entropy=with_entropy)
+        return lp, ent
+    logp, ent, lse = _LogProbEntropy.apply(hidden, w, targets, float(temperature), bool(with_entropy), int(vocab_offset))
+    if return_lse:
+        return logp, ent, lse
+    return logp, (ent if with_entropy else None)
+
+
+# ---------------------------------------------------------------------------------------------
+# sampling / quantisation
+# ---------------------------------------------------------------------------------------------
+
+def sample_logprob(logits, temperature, greedy, seeds=None, step: int = 0):
+    logits = _c(logits.float())
+    return tuple(C.sample_logprob(logits, _c(temperature.float()), _c(greedy.to(torch.uint8)),
+                                  _c(seeds.to(torch.int64)) if seeds is not None else None, int(step)))
+
+
+def mxfp8_quant(x):
+    assert x.dtype == BF16 and x.shape[-1] % 32 == 0
+    q, s = C.mxfp8_quant(_c(x))
+    return q, s
+
+
+def fp8_blockwise_quant(w):
+    assert w.dtype == BF16 and w.dim() == 2
+    q, s = C.fp8_block_quant(_c(w))
+    return q, s
+
+
+def int4_fake_quant(x, block_m=1, block_n=32, symmetric=True):
+    assert x.dtype == BF16 and x.dim() == 2
+    y, s = C.int4_fake_quant(_c(x), block_m, block_n, symmetric)
+    return y, s
+
+
+def absmax(x):
+    return C.absmax(_c(x))
+
+
+def nvfp4_qdq(x, global_amax=None):
+    assert x.dtype == BF16 and x.numel() % 16 == 0
+    x = _c(x)
+    if global_amax is None:
+        global_amax = C.absmax(x)
+    return C.nvfp4_qdq(x, global_amax.reshape(1).float())

@@ -1,0 +1,172 @@
+"""Numerics of the attention / MoE / log-prob / sampling / quantisation kernels vs fp32 PyTorch statements."""
+import math
+
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+from miles_b200.ops import reference as ref  # noqa: E402
+
+
+def _k():
+    from miles_b200.ops import cuda
+
+    return cuda
+
+
+def _rel(a, b):
+    a, b = a.float(), b.float()
+    return ((a - b).norm() / b.norm().clamp_min(1e-12)).item()
+
+
+def _attn_ref(q, k, v, cu, causal=True):
+    return ref.attention_varlen(q.float(), k.float(), v.float(), cu, causal)
+
+
+@pytest.mark.parametrize("D", [64, 128])
+@pytest.mark.parametrize("lens", [[1], [64], [65, 3, 200], [513, 128, 77, 1000]])
+@pytest.mark.parametrize("heads", [(4, 4), (8, 2)])
+def test_flash_attention_fwd_bwd(D, lens, heads):
+    torch.manual_seed(0)
+    Hq, Hkv = heads
+    T = sum(lens)
+    cu = torch.tensor([0] + list(torch.tensor(lens).cumsum(0)), dtype=torch.int32, device="cuda")
+    qkv = torch.randn(T, (Hq + 2 * Hkv) * D, device="cuda", dtype=torch.bfloat16, requires_grad=True)
+    q, k, v = qkv.split([Hq * D, Hkv * D, Hkv * D], dim=-1)
+    o = _k().attention_varlen(q.view(T, Hq, D), k.view(T, Hkv, D), v.view(T, Hkv, D), cu, max(lens))
+    g = torch.randn_like(o)
+    o.backward(g)
+    xf = qkv.detach().float().requires_grad_()
+    qf, kf, vf = xf.split([Hq * D, Hkv * D, Hkv * D], dim=-1)
+    of = _attn_ref(qf.view(T, Hq, D), kf.view(T, Hkv, D), vf.view(T, Hkv, D), cu)
+    of.backward(g.float())
+    assert _rel(o, of) < 2e-2, _rel(o, of)
+    assert _rel(qkv.grad, xf.grad) < 3e-2, _rel(qkv.grad, xf.grad)
+
+
+@pytest.mark.parametrize("D,Hq,Hkv", [(128, 32, 4), (128, 8, 8), (64, 4, 2)])
+def test_paged_decode(D, Hq, Hkv):
+    torch.manual_seed(1)
+    bs, nblocks, B = 64, 64, 5
+    kc = torch.randn(nblocks, bs, Hkv, D, device="cuda", dtype=torch.bfloat16)
+    vc = torch.randn(nblocks, bs, Hkv, D, device="cuda", dtype=torch.bfloat16)
+    seq_lens = torch.tensor([1, 63, 64, 65, 700], dtype=torch.int32, device="cuda")
+    perm = torch.randperm(nblocks)[: B * 11].view(B, 11).to(torch.int32).cuda()
+    q = torch.randn(B, Hq, D, device="cuda", dtype=torch.bfloat16)
+    out = _k().paged_attention(q, kc, vc, perm, seq_lens)
+    want = ref.paged_attention(q.float(), kc.float(), vc.float(), perm, seq_lens)
+    assert _rel(out, want) < 2e-2, _rel(out, want)
+
+
+def test_router_topk_matches_reference():
+    torch.manual_seed(2)
+    T, E, K = 1000, 128, 8
+    logits = torch.randn(T, E, device="cuda", requires_grad=True)
+    w, idx, probs = _k().router_topk(logits, K, True)
+    lr = logits.detach().clone().requires_grad_()
+    wr, ir, pr = ref.router_topk(lr, K, True)
+    assert torch.equal(idx.long().sort(-1).values, ir.long().sort(-1).values)
+    assert torch.allclose(probs, pr, atol=1e-6)
+    assert torch.allclose(w.sort(-1).values, wr.sort(-1).values, atol=1e-6)
+    g = torch.randn_like(w)
+    # compare gradients with the same (sorted-by-index) slot order
+    order, order_r = idx.long().argsort(-1), ir.long().argsort(-1)
+    (w.gather(1, order) * g).sum().backward()
+    (wr.gather(1, order_r) * g).sum().backward()
+    assert torch.allclose(logits.grad, lr.grad, atol=1e-5)
+
+
+@pytest.mark.parametrize("T,E,K,H,F", [(64, 8, 2, 256, 128), (1000, 16, 8, 1024, 384), (3, 16, 4, 512, 256)])
+def test_moe_ffn_fwd_bwd(T, E, K, H, F):
+    torch.manual_seed(3)
+    x = (0.5 * torch.randn(T, H, device="cuda")).to(torch.bfloat16).requires_grad_()
+    w13 = (0.05 * torch.randn(E, 2 * F, H, device="cuda")).to(torch.bfloat16).requires_grad_()
+    w2 = (0.05 * torch.randn(E, H, F, device="cuda")).to(torch.bfloat16).requires_grad_()
+    logits = torch.randn(T, E, device="cuda")
+    tw, ti, _ = ref.router_topk(logits, K, True)
+    tw = tw.detach().requires_grad_()
+    y = _k().moe_ffn(x, w13, w2, tw, ti)
+    g = torch.randn_like(y)
+    y.backward(g)
+    assert _k().check_error_flag() == 0
+    xf, w13f, w2f, twf = (t.detach().float().requires_grad_() for t in (x, w13, w2, tw))
+    yf = ref.moe_ffn(xf, w13f, w2f, twf, ti)
+    yf.backward(g.float())
+    assert _rel(y, yf) < 2e-2, _rel(y, yf)
+    assert _rel(x.grad, xf.grad) < 3e-2, _rel(x.grad, xf.grad)
+    assert _rel(w13.grad, w13f.grad) < 3e-2, _rel(w13.grad, w13f.grad)
+    assert _rel(w2.grad, w2f.grad) < 3e-2, _rel(w2.grad, w2f.grad)
+    assert _rel(tw.grad, twf.grad) < 3e-2, _rel(tw.grad, twf.grad)
+
+
+def test_moe_ffn_expert_offset_skips_foreign_experts():
+    torch.manual_seed(4)
+    T, E, K, H, F = 200, 8, 2, 256, 128
+    x = (0.5 * torch.randn(T, H, device="cuda")).to(torch.bfloat16)
+    w13 = (0.05 * torch.randn(E, 2 * F, H, device="cuda")).to(torch.bfloat16)
+    w2 = (0.05 * torch.randn(E, H, F, device="cuda")).to(torch.bfloat16)
+    tw, ti, _ = ref.router_topk(torch.randn(T, 2 * E, device="cuda"), K, True)   # ids in [0, 16); this rank owns [8, 16)
+    y = _k().moe_ffn(x, w13, w2, tw, ti, expert_offset=E)
+    mask = (ti >= E)
+    want = ref.moe_ffn(x.float(), w13.float(), w2.float(), tw * mask, (ti - E).clamp_min(0))
+    assert _rel(y, want) < 2e-2
+
+
+@pytest.mark.parametrize("R,H,V,temp", [(100, 256, 1000, 1.0), (700, 1024, 40000, 0.7)])
+def test_logprob_entropy_fwd_bwd(R, H, V, temp):
+    torch.manual_seed(5)
+    h = torch.randn(R, H, device="cuda", dtype=torch.bfloat16, requires_grad=True)
+    w = (0.05 * torch.randn(V, H, device="cuda")).to(torch.bfloat16).requires_grad_()
+    tg = torch.randint(0, V, (R,), device="cuda")
+    lp, ent = _k().logprob_entropy(h, w, tg, temp, True)
+    g1, g2 = torch.randn_like(lp), torch.randn_like(ent)
+    torch.autograd.backward([lp, ent], [g1, g2])
+    hf, wf = h.detach().float().requires_grad_(), w.detach().float().requires_grad_()
+    logits = (hf @ wf.t()) / temp
+    lse = torch.logsumexp(logits, -1)
+    lpr = logits.gather(1, tg[:, None]).squeeze(1) - lse
+    entr = lse - (torch.softmax(logits, -1) * logits).sum(-1)
+    torch.autograd.backward([lpr, entr], [g1, g2])
+    assert torch.allclose(lp, lpr, atol=2e-2, rtol=1e-2), (lp - lpr).abs().max()
+    assert torch.allclose(ent, entr, atol=2e-2, rtol=1e-2)
+    assert _rel(h.grad, hf.grad) < 3e-2, _rel(h.grad, hf.grad)
+    assert _rel(w.grad, wf.grad) < 3e-2, _rel(w.grad, wf.grad)
+
+
+def test_sample_logprob_distribution_and_logprob():
+    torch.manual_seed(6)
+    V = 50
+    logits = torch.randn(1, V, device="cuda").repeat(20000, 1)
+    temp = torch.full((20000,), 0.8, device="cuda")
+    greedy = torch.zeros(20000, dtype=torch.bool, device="cuda")
+    seeds = torch.arange(20000, device="cuda")
+    tok, lp = _k().sample_logprob(logits, temp, greedy, seeds, 3)
+    p = torch.softmax(logits[0] / 0.8, -1)
+    freq = torch.bincount(tok, minlength=V).float() / 20000
+    assert (freq - p).abs().max() < 0.02
+    assert torch.allclose(lp, torch.log(p)[tok], atol=1e-4)
+    tok_g, lp_g = _k().sample_logprob(logits[:4], temp[:4], torch.ones(4, dtype=torch.bool, device="cuda"), None, 0)
+    assert (tok_g == logits[0].argmax()).all()
+
+
+def test_quant_kernels_match_reference():
+    torch.manual_seed(7)
+    x = (torch.randn(256, 512, device="cuda") * torch.rand(256, 1, device="cuda") * 10).to(torch.bfloat16)
+    q, s = _k().mxfp8_quant(x)
+    qr, sr = ref.mxfp8_quant(x)
+    assert torch.equal(s, sr)
+    assert torch.equal(q.view(torch.uint8), qr.view(torch.uint8))
+    w = torch.randn(300, 520, device="cuda").to(torch.bfloat16)
+    q, si = _k().fp8_blockwise_quant(w)
+    qr, sir = ref.fp8_blockwise_quant(w)
+    assert torch.allclose(si, sir, rtol=1e-6)
+    assert _rel(ref.fp8_blockwise_dequant(q, si, dtype=torch.float32), ref.fp8_blockwise_dequant(qr, sir, dtype=torch.float32)) < 1e-3
+    for sym in (True, False):
+        for bm, bn in ((1, 32), (32, 1), (16, 16)):
+            y, sc = _k().int4_fake_quant(x, bm, bn, sym)
+            yr, scr = ref.int4_fake_quant(x, bm, bn, sym)
+            assert _rel(y, yr) < 2e-2, (sym, bm, bn, _rel(y, yr))
+    y = _k().nvfp4_qdq(x)
+    yr = ref.nvfp4_qdq(x)
+    assert _rel(y, yr) < 2e-2, _rel(y, yr)
