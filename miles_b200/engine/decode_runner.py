@@ -1,0 +1,204 @@
+"""Decode-step runner with static buffers and CUDA graphs.
+
+Running requests own a fixed row of a set of static device buffers (last token, position, cache slot, block table,
+sampling parameters).  A decode step copies the host mirrors of those buffers to the device (three pinned-memory
+copies), replays the CUDA graph captured for the smallest batch bucket that covers the occupied rows, and reads the
+sampled ids / log-probs (and routed experts) back with one device→host copy.  Rows of finished requests are padding
+(seq_len 0, slot −1: no KV write, attention over zero keys) until the rows are compacted.
+
+The graph contains the whole model forward, the LM head, and the fused sample+log-prob kernel, so a decode step is one
+graph launch instead of ~25 launches per layer.
+"""
+from __future__ import annotations
+
+import zlib
+
+import numpy as np
+import torch
+
+from ..models.qwen3 import ForwardMeta
+
+BUCKETS = [1, 2, 4, 8, 16, 24, 32, 48, 64, 96, 128, 192, 256, 384, 512, 768, 1024]
+
+
+class DecodeRunner:
+    def __init__(self, engine, max_rows: int, use_graph: bool):
+        self.e = engine
+        self.dev = engine.device
+        self.use_graph = use_graph
+        self.max_rows = max_rows
+        self.max_blocks = (engine.max_context_len + engine.block_size - 1) // engine.block_size + 1
+        cfg = engine.cfg
+        self.n_moe = engine.model.num_moe_layers if cfg.is_moe else 0
+        self.topk = cfg.moe_topk
+        R, MB = max_rows, self.max_blocks
+        # host mirrors (pinned) — int32 pack: tokens | positions | seq_lens | block_table ; int64 pack: slots | seeds
+        self.h_i32 = torch.zeros(3 * R + R * MB, dtype=torch.int32).pin_memory()
+        self.h_i64 = torch.zeros(2 * R, dtype=torch.int64).pin_memory()
+        self.h_f32 = torch.ones(R, dtype=torch.float32).pin_memory()
+        self.h_u8 = torch.zeros(R, dtype=torch.uint8).pin_memory()
+        self.d_i32 = torch.zeros_like(self.h_i32, device=self.dev)
+        self.d_i64 = torch.zeros_like(self.h_i64, device=self.dev)
+        self.d_f32 = torch.ones_like(self.h_f32, device=self.dev)
+        self.d_u8 = torch.zeros_like(self.h_u8, device=self.dev)
+        self.np_i32 = self.h_i32.numpy()
+        self.np_i64 = self.h_i64.numpy()
+        self.np_f32 = self.h_f32.numpy()
+        self.np_u8 = self.h_u8.numpy()
+        self.tok_np = self.np_i32[0:R]
+        self.pos_np = self.np_i32[R:2 * R]
+        self.len_np = self.np_i32[2 * R:3 * R]
+        self.bt_np = self.np_i32[3 * R:].reshape(R, MB)
+        self.slot_np = self.np_i64[0:R]
+        self.seed_np = self.np_i64[R:2 * R]
+        self.slot_np[:] = -1
+        # outputs
+        self.o_tok = torch.zeros(R, dtype=torch.int64, device=self.dev)
+        self.o_lp = torch.zeros(R, dtype=torch.float32, device=self.dev)
+        self.o_routed = torch.zeros(R, max(self.n_moe, 1), max(self.topk, 1), dtype=torch.int32, device=self.dev)
+        self.h_tok = torch.zeros(R, dtype=torch.int64).pin_memory()
+        self.h_lp = torch.zeros(R, dtype=torch.float32).pin_memory()
+        self.h_routed = torch.zeros(R, max(self.n_moe, 1), max(self.topk, 1), dtype=torch.int32).pin_memory()
+        self.rows: list = [None] * R          # row → Request
+        self.free_rows = list(range(R - 1, -1, -1))
+        self.high = 0                         # 1 + highest occupied row
+        self.graphs: dict[int, tuple] = {}
+        self.launches_per_graph: dict[int, int] = {}
+        self.pool = None
+
+    # ---- row bookkeeping -------------------------------------------------------------------
+    def attach(self, req):
+        row = self.free_rows.pop()
+        req.row = row
+        self.rows[row] = req
+        self.bt_np[row, :len(req.blocks)] = req.blocks
+        req.bt_len = len(req.blocks)
+        self.np_f32[row] = req.sampling.temperature if req.sampling.temperature > 0 else 1.0
+        self.np_u8[row] = 1 if req.sampling.temperature <= 0 else 0
+        self.high = max(self.high, row + 1)
+
+    def detach(self, req):
+        row = getattr(req, "row", None)
+        if row is None:
+            return
+        self.rows[row] = None
+        self.len_np[row] = 0
+        self.slot_np[row] = -1
+        self.free_rows.append(row)
+        req.row = None
+        while self.high > 0 and self.rows[self.high - 1] is None:
+            self.high -= 1
+
+    def compact(self):
+        """Move the highest rows into holes so that the occupied rows form a prefix."""
+        self.free_rows.sort(reverse=True)
+        while self.free_rows and self.free_rows[-1] < self.high - 1:
+            hole = self.free_rows[-1]
+            src = self.high - 1
+            if self.rows[src] is None:
+                self.high -= 1
+                continue
+            req = self.rows[src]
+            self.free_rows.pop()
+            self.rows[hole], self.rows[src] = req, None
+            req.row = hole
+            self.bt_np[hole, :req.bt_len] = self.bt_np[src, :req.bt_len]
+            self.np_f32[hole], self.np_u8[hole] = self.np_f32[src], self.np_u8[src]
+            self.len_np[src] = 0
+            self.slot_np[src] = -1
+            self.free_rows.append(src)
+            self.free_rows.sort(reverse=True)
+            while self.high > 0 and self.rows[self.high - 1] is None:
+                self.high -= 1
+
+    # ---- one decode step -------------------------------------------------------------------
+    def _bucket(self, n: int) -> int:
+        for b in BUCKETS:
+            if b >= n:
+                return min(b, self.max_rows)
+        return self.max_rows
+
+    def _forward(self, B: int, record: bool):
+        e = self.e
+        R, MB = self.max_rows, self.max_blocks
+        tokens = self.d_i32[0:B]
+        meta = ForwardMeta(
+            positions=self.d_i32[R:R + B], cu_seqlens=None, max_seqlen=1, kv_cache=e.kv.layers,
+            block_table=self.d_i32[3 * R:].view(R, MB)[:B], seq_lens=self.d_i32[2 * R:2 * R + B],
+            slot_mapping=self.d_i64[0:B], record_topk=[] if record else None)
+        hidden = e.model(tokens, meta)
+        hidden = e.ps.sp_gather(hidden)
+        logits = e.model.logits(hidden)
+        from .. import ops
+
+        tok, lp = ops._k().sample_logprob(logits, self.d_f32[:B], self.d_u8[:B], self.d_i64[R:R + B], 0)
+        self.o_tok[:B].copy_(tok)
+        self.o_lp[:B].copy_(lp)
+        if record and meta.record_topk:
+            self.o_routed[:B].copy_(torch.stack(meta.record_topk, dim=1))
+
+    def step(self, reqs: list, step_no: int):
+        """Run one decode step for the attached requests; returns (tokens, logprobs, routed | None) as numpy views
+        indexed by row."""
+        e = self.e
+        bs = e.block_size
+        if len(self.free_rows) and (self.high - len(reqs)) > max(8, len(reqs) // 4):
+            self.compact()
+        for r in reqs:
+            row = r.row
+            n = len(r.input_ids) + len(r.output_ids)
+            pos = n - 1
+            if len(r.blocks) != r.bt_len:
+                self.bt_np[row, r.bt_len:len(r.blocks)] = r.blocks[r.bt_len:]
+                r.bt_len = len(r.blocks)
+            self.tok_np[row] = r.output_ids[-1] if r.output_ids else r.input_ids[-1]
+            self.pos_np[row] = pos
+            self.len_np[row] = n
+            self.slot_np[row] = r.blocks[pos // bs] * bs + pos % bs
+            self.seed_np[row] = (r.seed * 1000003 + n) & 0x7FFFFFFFFFFFFFFF
+        B = self._bucket(max(self.high, 1))
+        record = self.n_moe > 0 and any(r.return_routed_experts for r in reqs)
+        self.d_i32.copy_(self.h_i32, non_blocking=True)
+        self.d_i64.copy_(self.h_i64, non_blocking=True)
+        self.d_f32.copy_(self.h_f32, non_blocking=True)
+        self.d_u8.copy_(self.h_u8, non_blocking=True)
+        e.stats["h2d_bytes"] = e.stats.get("h2d_bytes", 0) + self.h_i32.numel() * 4 + self.h_i64.numel() * 8 + 5 * self.max_rows
+        key = (B, record)
+        if self.use_graph:
+            if key not in self.graphs:
+                self._capture(key)
+            self.graphs[key].replay()
+            from .. import ops
+
+            ops._k().C.count_launches(self.launches_per_graph[key])
+        else:
+            self._forward(B, record)
+        self.h_tok[:B].copy_(self.o_tok[:B], non_blocking=True)
+        self.h_lp[:B].copy_(self.o_lp[:B], non_blocking=True)
+        nbytes = 12 * B
+        if record:
+            self.h_routed[:B].copy_(self.o_routed[:B], non_blocking=True)
+            nbytes += self.h_routed[:B].numel() * 4
+        e.stats["d2h_bytes"] = e.stats.get("d2h_bytes", 0) + nbytes
+        torch.cuda.current_stream().synchronize()
+        return self.h_tok.numpy(), self.h_lp.numpy(), (self.h_routed.numpy() if record else None)
+
+    def _capture(self, key):
+        from .. import ops
+
+        B, record = key
+        # eager warm-up with the same shapes (initialises per-kernel attributes and the allocator pool)
+        self._forward(B, record)
+        torch.cuda.synchronize()
+        g = torch.cuda.CUDAGraph()
+        n0 = ops._k().launch_count()
+        with torch.cuda.graph(g, pool=self.pool):
+            self._forward(B, record)
+        self.launches_per_graph[key] = ops._k().launch_count() - n0
+        if self.pool is None:
+            self.pool = g.pool()
+        self.graphs[key] = g
+
+    def reset_graphs(self):
+        self.graphs.clear()
+        self.pool = None

@@ -53,6 +53,9 @@ class Request:
     retractions: int = 0
     seed: int = 0
     on_done: Any = None            # callable(Request), invoked from the engine thread
+    stop_set: frozenset = frozenset()
+    row: Any = None                # row in the decode runner's static buffers
+    bt_len: int = 0
 
     @property
     def all_ids(self) -> list[int]:
@@ -132,6 +135,13 @@ class Engine:
         self.lockstep_group = self.ps.ep_group if (self.ps.ep_size > 1 and cfg.is_moe) else None
         self.local_done = True
         self.global_done = True
+        self.runner = None
+        if self.device.type == "cuda" and dtype == torch.bfloat16:
+            from .decode_runner import DecodeRunner
+
+            # expert-parallel dispatch over NCCL synchronises with the host, so it cannot be captured
+            graphable = self.use_cuda_graph and (self.ps.ep_size == 1 or (self.ps.fabric is not None and self.ps.fused))
+            self.runner = DecodeRunner(self, max_running_requests, graphable)
 
     # ---------------------------------------------------------------------------------------
     # request API
@@ -154,6 +164,7 @@ class Engine:
                     on_done(req)
                 return req
             sp.max_new_tokens = min(sp.max_new_tokens, budget)
+            req.stop_set = frozenset(sp.stop_token_ids) | (frozenset() if sp.ignore_eos else frozenset(self.eos_token_ids))
             self.requests[rid] = req
             self.waiting.append(req)
         return req
@@ -248,6 +259,8 @@ class Engine:
                 self.allocator.reset()
             if "cuda_graph" in tags:
                 self._graphs.clear()
+                if self.runner is not None:
+                    self.runner.reset_graphs()
             if "weights" in tags and self.owns_model:
                 self._weights_host = {n: p.data.to("cpu") for n, p in self.model.named_parameters()}
                 for p in self.model.parameters():
@@ -301,6 +314,8 @@ class Engine:
 
     def _finish(self, r: Request, reason: dict):
         r.finish_reason = reason
+        if self.runner is not None:
+            self.runner.detach(r)
         if r.blocks:
             self.allocator.release(r.blocks)
             r.blocks = []
@@ -315,6 +330,8 @@ class Engine:
             self.allocator.release(r.blocks)
         r.blocks, r.num_cached = [], 0
         r.retractions += 1
+        if self.runner is not None:
+            self.runner.detach(r)
         self.stats["retractions"] += 1
         if r in self.running:
             self.running.remove(r)
@@ -460,8 +477,12 @@ class Engine:
         for r in batch:
             if not r.finished:
                 self.running.append(r)
+                if self.runner is not None:
+                    self.runner.attach(r)
 
     def _run_decode(self):
+        if self.runner is not None:
+            return self._run_decode_static()
         reqs = self.running
         dev = self.device
         toks = [r.all_ids[-1] for r in reqs]
@@ -487,6 +508,30 @@ class Engine:
         self._sample_and_append(reqs, logits)
         self.running = [r for r in reqs if not r.finished]
 
+    def _run_decode_static(self):
+        """CUDA path: static buffers + (optionally) a CUDA graph per batch bucket; see `decode_runner`."""
+        reqs = self.running
+        tok, lp, routed = self.runner.step(reqs, self._step_count)
+        self.stats["decode_tokens"] += len(reqs)
+        for r in reqs:
+            row = r.row
+            if routed is not None and r.return_routed_experts:
+                r.routed.append(routed[row:row + 1].copy())
+            self._append_token(r, int(tok[row]), float(lp[row]))
+        self.running = [r for r in reqs if not r.finished]
+
+    def _append_token(self, r: Request, t: int, l: float):
+        r.output_ids.append(t)
+        r.output_logprobs.append(l)
+        if r.weight_versions and r.weight_versions[-1][0] == self.weight_version:
+            r.weight_versions[-1][1] += 1
+        else:
+            r.weight_versions.append([self.weight_version, 1])
+        if t in r.stop_set:
+            self._finish(r, {"type": "stop", "matched": t})
+        elif len(r.output_ids) >= r.sampling.max_new_tokens:
+            self._finish(r, {"type": "length", "length": len(r.output_ids)})
+
     def _sample_and_append(self, reqs: list[Request], logits: torch.Tensor):
         dev = self.device
         temp = torch.tensor([r.sampling.temperature for r in reqs], dtype=torch.float32, device=dev)
@@ -499,14 +544,4 @@ class Engine:
         tok, lp = sample(logits.float(), temp, top_p, top_k, generator=gen, seeds=seeds, step=self._step_count)
         tok_l, lp_l = tok.tolist(), lp.tolist()
         for r, t, l in zip(reqs, tok_l, lp_l):
-            r.output_ids.append(int(t))
-            r.output_logprobs.append(float(l))
-            if r.weight_versions and r.weight_versions[-1][0] == self.weight_version:
-                r.weight_versions[-1][1] += 1
-            else:
-                r.weight_versions.append([self.weight_version, 1])
-            stop = set(r.sampling.stop_token_ids) | (set() if r.sampling.ignore_eos else self.eos_token_ids)
-            if int(t) in stop:
-                self._finish(r, {"type": "stop", "matched": int(t)})
-            elif len(r.output_ids) >= r.sampling.max_new_tokens:
-                self._finish(r, {"type": "length", "length": len(r.output_ids)})
+            self._append_token(r, int(t), float(l))

@@ -246,7 +246,7 @@ class Qwen3Model(nn.Module):
     def logits(self, hidden: torch.Tensor) -> torch.Tensor:
         """Full logits (engine sampling / tests). hidden [T,H] → [T,V] fp32 (TP: gathered)."""
         hidden = self.ps.sp_gather(hidden)
-        lg = ops.linear(hidden, self.head_weight()).float()
+        lg = ops.linear_fp32(hidden, self.head_weight())
         return self.ps.tp_all_gather_last(lg)
 
     def log_probs(self, hidden, targets, temperature: float = 1.0, with_entropy: bool = False):

@@ -41,6 +41,13 @@ def linear(x, w, bias=None):
     return F.linear(x, w, bias)
 
 
+def linear_fp32(x, w):
+    """x·Wᵀ with an fp32 result (LM-head logits for sampling: no bf16 rounding of the logits)."""
+    if x.is_cuda:
+        return _k().linear_fp32(x, w)
+    return F.linear(x, w).float()
+
+
 def linear_dgrad(gy, w):
     """dX = dY · W for y = x·Wᵀ (W [N,K])."""
     if gy.is_cuda:

@@ -12,6 +12,7 @@ namespace {
 // clear it before launching so that the launcher's own cudaGetLastError() reports only its launch.
 inline cudaStream_t cur_stream() {
   (void)cudaGetLastError();
+  mb_count_launch(1);
   return at::cuda::getCurrentCUDAStream().stream();
 }
 inline const void* cptr(const c10::optional<at::Tensor>& t) { return t.has_value() && t->defined() ? t->data_ptr() : nullptr; }
@@ -156,6 +157,8 @@ void register_more(pybind11::module& m);  // bindings_more.cpp: attention, MoE, 
 
 PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("error_flag", &error_flag);
+  m.def("launch_count", []() { return static_cast<int64_t>(mb_launch_count()); });
+  m.def("count_launches", [](int64_t n) { mb_count_launch(static_cast<int>(n)); });
   m.def("gemm", &gemm);
   m.def("gemm_grouped", &gemm_grouped);
   m.def("gemm_grouped_wgrad", &gemm_grouped_wgrad);

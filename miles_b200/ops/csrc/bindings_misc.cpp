@@ -9,6 +9,7 @@ namespace {
 
 inline cudaStream_t cur_stream() {
   (void)cudaGetLastError();
+  mb_count_launch(1);
   return at::cuda::getCurrentCUDAStream().stream();
 }
 inline float* fptr(const c10::optional<at::Tensor>& t) { return t.has_value() && t->defined() ? t->data_ptr<float>() : nullptr; }

@@ -9,6 +9,7 @@ namespace {
 
 inline cudaStream_t cur_stream() {
   (void)cudaGetLastError();
+  mb_count_launch(1);
   return at::cuda::getCurrentCUDAStream().stream();
 }
 inline void check(int rc, const char* what) {

@@ -11,7 +11,8 @@
 namespace {
 
 inline cudaStream_t cur_stream() {
-  (void)cudaGetLastError();  // drop a stale per-thread error left by other code
+  (void)cudaGetLastError();
+  mb_count_launch(1);  // drop a stale per-thread error left by other code
   return at::cuda::getCurrentCUDAStream().stream();
 }
 inline const void* cptr(const c10::optional<at::Tensor>& t) { return t.has_value() && t->defined() ? t->data_ptr() : nullptr; }

@@ -7,6 +7,10 @@
 extern "C" {
 #endif
 
+// ---- counter.cpp ----
+void mb_count_launch(int n);
+long long mb_launch_count();
+
 // ---- gemm.cu ----
 int mb_gemm_bf16(const void* A, const void* B, void* C, int M, int N, int K, long long lda, long long ldb, long long ldc,
                  int a_mn, int b_mn, int out_fp32, int accumulate, const void* bias, int force_bn, int* error_flag,

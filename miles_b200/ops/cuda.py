@@ -25,6 +25,11 @@ def check_error_flag(like: torch.Tensor | None = None) -> int:
     return int(C.error_flag(t).item())
 
 
+def launch_count() -> int:
+    """Number of kernel-launcher calls made by this extension so far (CUDA-graph replays add their captured count)."""
+    return int(C.launch_count())
+
+
 def _c(x: torch.Tensor) -> torch.Tensor:
     return x if x.is_contiguous() else x.contiguous()
 
@@ -103,6 +108,12 @@ def linear(x, w, bias=None):
     if x.dtype != BF16:
         return torch.nn.functional.linear(x, w.to(x.dtype), bias)
     return _Linear.apply(x, w, bias)
+
+
+def linear_fp32(x, w):
+    if x.dtype != BF16:
+        return torch.nn.functional.linear(x, w.to(x.dtype)).float()
+    return gemm_nt(x.reshape(-1, x.shape[-1]), w, out_dtype=torch.float32).view(*x.shape[:-1], w.shape[0])
 
 
 def linear_dgrad(gy, w):
