@@ -733,7 +733,8 @@ extern "C" int mb_flash_bwd(const void* q, const void* k, const void* v, const v
 }
 
 // part_o: [B·Hq·splits·D] floats, part_ml: [B·Hq·splits·2] floats
-extern "C" int mb_paged_decode(const void* q, const void* kc, const void* vc, const int* block_table, const int* seq_lens, void* out,
+// SIMT variant (one key per warp step); `mb_paged_decode` in paged_decode.cu is the tensor-core kernel used by default.
+extern "C" int mb_paged_decode_simt(const void* q, const void* kc, const void* vc, const int* block_table, const int* seq_lens, void* out,
                                float* part_o, float* part_ml, int batch, int max_blocks, int block_size, int Hq, int Hkv, int D,
                                float scale, int num_splits, cudaStream_t s) {
   if (batch == 0) return 0;

@@ -85,16 +85,20 @@ at::Tensor rmsnorm_bwd(const at::Tensor& x, const at::Tensor& w, const at::Tenso
   return dw;
 }
 
-void swiglu_fwd(const at::Tensor& in, at::Tensor& out) {
+void swiglu_fwd(const at::Tensor& in, at::Tensor& out, const c10::optional<at::Tensor>& rows) {
   c10::cuda::CUDAGuard g(in.device());
   const int64_t F = out.size(-1), T = out.numel() / std::max<int64_t>(F, 1);
-  check(mb_swiglu_fwd(in.data_ptr(), out.data_ptr(), T, F, cur_stream()), "mb_swiglu_fwd");
+  check(mb_swiglu_fwd(in.data_ptr(), out.data_ptr(), T, F, rows.has_value() && rows->defined() ? rows->data_ptr<int>() : nullptr,
+                      cur_stream()),
+        "mb_swiglu_fwd");
 }
 
-void swiglu_bwd(const at::Tensor& in, const at::Tensor& dout, at::Tensor& din) {
+void swiglu_bwd(const at::Tensor& in, const at::Tensor& dout, at::Tensor& din, const c10::optional<at::Tensor>& rows) {
   c10::cuda::CUDAGuard g(in.device());
   const int64_t F = dout.size(-1), T = dout.numel() / std::max<int64_t>(F, 1);
-  check(mb_swiglu_bwd(in.data_ptr(), dout.data_ptr(), din.data_ptr(), T, F, cur_stream()), "mb_swiglu_bwd");
+  check(mb_swiglu_bwd(in.data_ptr(), dout.data_ptr(), din.data_ptr(), T, F,
+                      rows.has_value() && rows->defined() ? rows->data_ptr<int>() : nullptr, cur_stream()),
+        "mb_swiglu_bwd");
 }
 
 void qk_norm_rope_fwd(const at::Tensor& q, const at::Tensor& k, const c10::optional<at::Tensor>& qw,

@@ -35,15 +35,17 @@ std::vector<at::Tensor> router_topk(const at::Tensor& logits, int64_t K, bool no
 }
 
 // idx int32 [n] global expert ids → seg_offsets [E+1], tile_expert [max_rows/128], row_src [max_rows], dst_row [n]
-std::vector<at::Tensor> moe_align(const at::Tensor& idx, int64_t E, int64_t expert_offset, int64_t max_rows) {
+std::vector<at::Tensor> moe_align(const at::Tensor& idx, int64_t E, int64_t expert_offset, int64_t max_rows,
+                                  const c10::optional<at::Tensor>& n_dev) {
   c10::cuda::CUDAGuard g(idx.device());
   const int64_t n = idx.numel();
+  const int* n_ptr = n_dev.has_value() && n_dev->defined() ? n_dev->data_ptr<int>() : nullptr;
   auto opt = idx.options().dtype(at::kInt);
   auto seg = at::empty({E + 1}, opt);
   auto tile = at::empty({max_rows / 128}, opt);
   auto row_src = at::empty({max_rows}, opt);
   auto dst_row = at::empty({n}, opt);
-  check(mb_moe_align(idx.data_ptr<int>(), n, E, expert_offset, seg.data_ptr<int>(), tile.data_ptr<int>(), row_src.data_ptr<int>(),
+  check(mb_moe_align(idx.data_ptr<int>(), n, n_ptr, E, expert_offset, seg.data_ptr<int>(), tile.data_ptr<int>(), row_src.data_ptr<int>(),
                      dst_row.data_ptr<int>(), max_rows, cur_stream()),
         "mb_moe_align");
   return {seg, tile, row_src, dst_row};

@@ -80,6 +80,7 @@ void paged_decode(const at::Tensor& q, const at::Tensor& kc, const at::Tensor& v
 
 void register_moe(pybind11::module& m);    // bindings_moe.cpp
 void register_misc(pybind11::module& m);   // bindings_misc.cpp
+void register_fabric(pybind11::module& m); // bindings_fabric.cpp
 
 void register_more(pybind11::module& m) {
   m.def("install_crash_handler", &install_crash_handler);
@@ -88,4 +89,5 @@ void register_more(pybind11::module& m) {
   m.def("paged_decode", &paged_decode);
   register_moe(m);
   register_misc(m);
+  register_fabric(m);
 }

@@ -200,8 +200,9 @@ __global__ void colsum_kernel(const float* __restrict__ partial, void* __restric
 // SwiGLU: in [T, 2F] (gate | up) → out [T, F]
 // ---------------------------------------------------------------------------------------------
 __global__ void __launch_bounds__(256) swiglu_fwd_kernel(const __nv_bfloat16* __restrict__ in, __nv_bfloat16* __restrict__ out,
-                                                         long long T, int F) {
+                                                         long long T, int F, const int* __restrict__ rows_ptr) {
   const int nvec = F / 8;
+  if (rows_ptr != nullptr) T = min(T, static_cast<long long>(*rows_ptr));  // device-side row count (MoE padded buffers)
   const long long total = T * nvec;
   for (long long i = blockIdx.x * 256ll + threadIdx.x; i < total; i += static_cast<long long>(gridDim.x) * 256) {
     const long long t = i / nvec;
@@ -216,8 +217,10 @@ __global__ void __launch_bounds__(256) swiglu_fwd_kernel(const __nv_bfloat16* __
 }
 
 __global__ void __launch_bounds__(256) swiglu_bwd_kernel(const __nv_bfloat16* __restrict__ in, const __nv_bfloat16* __restrict__ dout,
-                                                         __nv_bfloat16* __restrict__ din, long long T, int F) {
+                                                         __nv_bfloat16* __restrict__ din, long long T, int F,
+                                                         const int* __restrict__ rows_ptr) {
   const int nvec = F / 8;
+  if (rows_ptr != nullptr) T = min(T, static_cast<long long>(*rows_ptr));
   const long long total = T * nvec;
   for (long long i = blockIdx.x * 256ll + threadIdx.x; i < total; i += static_cast<long long>(gridDim.x) * 256) {
     const long long t = i / nvec;
@@ -506,20 +509,21 @@ extern "C" int mb_colsum(const float* partial, void* out, int R, int C, int out_
   return static_cast<int>(cudaGetLastError());
 }
 
-extern "C" int mb_swiglu_fwd(const void* in, void* out, long long T, int F, cudaStream_t s) {
+// rows_ptr (optional, device): only the first min(T, *rows_ptr) rows are processed
+extern "C" int mb_swiglu_fwd(const void* in, void* out, long long T, int F, const int* rows_ptr, cudaStream_t s) {
   if (T == 0) return 0;
   if (F % 8) return -1;
   swiglu_fwd_kernel<<<grid_for(T * (F / 8), 256), 256, 0, s>>>(reinterpret_cast<const __nv_bfloat16*>(in),
-                                                                reinterpret_cast<__nv_bfloat16*>(out), T, F);
+                                                                reinterpret_cast<__nv_bfloat16*>(out), T, F, rows_ptr);
   return static_cast<int>(cudaGetLastError());
 }
 
-extern "C" int mb_swiglu_bwd(const void* in, const void* dout, void* din, long long T, int F, cudaStream_t s) {
+extern "C" int mb_swiglu_bwd(const void* in, const void* dout, void* din, long long T, int F, const int* rows_ptr, cudaStream_t s) {
   if (T == 0) return 0;
   if (F % 8) return -1;
   swiglu_bwd_kernel<<<grid_for(T * (F / 8), 256), 256, 0, s>>>(reinterpret_cast<const __nv_bfloat16*>(in),
                                                                 reinterpret_cast<const __nv_bfloat16*>(dout),
-                                                                reinterpret_cast<__nv_bfloat16*>(din), T, F);
+                                                                reinterpret_cast<__nv_bfloat16*>(din), T, F, rows_ptr);
   return static_cast<int>(cudaGetLastError());
 }
 

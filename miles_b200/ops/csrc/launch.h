@@ -28,8 +28,8 @@ int mb_rmsnorm_bwd_blocks(long long T);
 int mb_rmsnorm_bwd(const void* x, const void* w, const void* dy, const void* dres, const float* rstd, void* dx, float* dw_partial,
                    void* dw_out, int dw_fp32, long long T, int H, cudaStream_t s);
 int mb_colsum(const float* partial, void* out, int R, int C, int out_fp32, cudaStream_t s);
-int mb_swiglu_fwd(const void* in, void* out, long long T, int F, cudaStream_t s);
-int mb_swiglu_bwd(const void* in, const void* dout, void* din, long long T, int F, cudaStream_t s);
+int mb_swiglu_fwd(const void* in, void* out, long long T, int F, const int* rows_ptr, cudaStream_t s);
+int mb_swiglu_bwd(const void* in, const void* dout, void* din, long long T, int F, const int* rows_ptr, cudaStream_t s);
 int mb_qk_norm_rope_fwd(const void* q, const void* k, long long q_stride, long long k_stride, const void* qw, const void* kw,
                         const int* positions, void* qo, void* ko, float* q_rstd, float* k_rstd, long long T, int Hq, int Hk, int D,
                         float theta, float eps, cudaStream_t s);
@@ -56,8 +56,8 @@ int mb_paged_decode(const void* q, const void* kc, const void* vc, const int* bl
 // ---- moe.cu ----
 int mb_router_topk(const float* logits, float* probs, float* topk_w, int* topk_idx, long long T, int E, int K, int normalize,
                    cudaStream_t s);
-int mb_moe_align(const int* idx, int n, int E, int expert_offset, int* seg_offsets, int* tile_expert, int* row_src, int* dst_row,
-                 int max_rows, cudaStream_t s);
+int mb_moe_align(const int* idx, int n, const int* n_ptr, int E, int expert_offset, int* seg_offsets, int* tile_expert, int* row_src,
+                 int* dst_row, int max_rows, cudaStream_t s);
 int mb_moe_gather(const void* x, void* x_perm, const int* row_src, const int* seg_offsets, int E, int k, int H, int max_rows,
                   cudaStream_t s);
 int mb_moe_combine(const void* y_perm, const float* w, const int* dst_row, void* out, long long T, int k, int H, cudaStream_t s);
@@ -79,6 +79,33 @@ int mb_fp8_block_quant(const void* w, void* q, float* scale_inv, int M, int N, c
 int mb_int4_fake_quant(const void* x, void* y, float* scales, int M, int N, int bm, int bn, int symmetric, cudaStream_t s);
 int mb_nvfp4_qdq(const void* x, void* y, const float* global_amax, long long numel, cudaStream_t s);
 int mb_absmax(const void* x, float* out, long long numel, cudaStream_t s);
+
+// ---- comm.cu (peer-memory kernels; *_ptrs are host arrays of `world` device addresses, one per rank) ----
+int mb_barrier(const long long* flag_ptrs, int rank, int world, int channel, int* epochs, int* err, cudaStream_t s);
+int mb_ar_add_rmsnorm(const long long* partial_ptrs, int world, const void* residual, const void* w, void* y, void* res_out,
+                      long long T, int H, float eps, cudaStream_t s);
+int mb_rs_reduce_sqnorm(const long long* grad_ptrs, int world, int rank, long long lo, long long hi, const float* norm_weight,
+                        float* sqnorm, cudaStream_t s);
+int mb_adam_allgather(float* master, const float* grad_shard, float* m, float* v, const float* decay_mask, const float* sqnorm,
+                      float clip, const long long* param_ptrs, int world, long long lo, long long n, float lr, float b1, float b2,
+                      float eps, float wd, int step, cudaStream_t s);
+int mb_moe_dispatch(const void* x, const int* topk_idx, long long n_pairs, int k, int H, int e_local, int rank,
+                    const long long* recv_x_ptrs, const long long* recv_meta_ptrs, const long long* counter_ptrs, int world,
+                    int capacity, int* sent_row, int* err, cudaStream_t s);
+int mb_moe_scatter_known(const void* rows_in, int src_by_pair, const int* topk_idx, const int* sent_row, long long n_pairs, int k,
+                         int H, int e_local, const long long* recv_x_ptrs, int world, cudaStream_t s);
+int mb_moe_return(const void* y_perm, const int* row_src, const void* meta, const int* seg_offsets, int E, int H, int max_rows,
+                  const long long* ret_ptrs, int world, cudaStream_t s);
+int mb_recv_expert_ids(const void* meta, const int* counter, int capacity, int* expert_ids, int* n_out, cudaStream_t s);
+int mb_sum_rows(const long long* src_ptrs, int world, void* out, long long numel, cudaStream_t s);
+int mb_gather_rows(const long long* src_ptrs, int world, void* out, long long bytes_per_rank, cudaStream_t s);
+int mb_stats_merge(const long long* stats_ptrs, int world, long long R, float* logp, float* ent, float* lse, cudaStream_t s);
+
+// ---- gemm_comm.cu ----
+int mb_ag_gemm(const long long* x_ptrs, const void* W, void* Y, int rows_per_rank, int N, int K, int rank, int world,
+               const long long* flag_ptrs, int channel, int epoch, int* error_flag, cudaStream_t s);
+int mb_gemm_rs(const void* X, const void* W, const long long* partial_ptrs, void* out, int* counters, int T, int N, int K, int rank,
+               int world, const long long* flag_ptrs, int channel, int epoch, int* error_flag, cudaStream_t s);
 
 #ifdef __cplusplus
 }

@@ -89,10 +89,11 @@ __global__ void __launch_bounds__(256) router_topk_kernel(const float* __restric
 // ---------------------------------------------------------------------------------------------
 // Single-CTA counting sort.  idx[n] holds global expert ids; local expert = id − expert_offset, others skipped.
 // Outputs: seg_offsets[E+1] (padded to 128), tile_expert[max_tiles], row_src[max_rows], dst_row[n].
-__global__ void __launch_bounds__(1024) moe_align_kernel(const int* __restrict__ idx, int n, int E, int expert_offset,
-                                                         int* __restrict__ seg_offsets, int* __restrict__ tile_expert,
+__global__ void __launch_bounds__(1024) moe_align_kernel(const int* __restrict__ idx, int n, const int* __restrict__ n_ptr, int E,
+                                                         int expert_offset, int* __restrict__ seg_offsets, int* __restrict__ tile_expert,
                                                          int* __restrict__ row_src, int* __restrict__ dst_row, int max_rows) {
   extern __shared__ int sh[];  // counts[E], cursor[E], seg[E+1]
+  if (n_ptr != nullptr) n = min(n, *n_ptr);   // device-side entry count (expert-parallel receive buffers)
   int* counts = sh;
   int* cursor = sh + E;
   int* seg = sh + 2 * E;
@@ -127,7 +128,8 @@ __global__ void __launch_bounds__(1024) moe_align_kernel(const int* __restrict__
     }
     tile_expert[t] = ex;
   }
-  for (int r = threadIdx.x; r < max_rows; r += blockDim.x) row_src[r] = -1;
+  // rows at or beyond seg[E] are never read (every consumer stops at seg[E]), so only the used prefix is cleared
+  for (int r = threadIdx.x; r < seg[E] && r < max_rows; r += blockDim.x) row_src[r] = -1;
   __syncthreads();
   for (int i = threadIdx.x; i < n; i += blockDim.x) {
     const int e = idx[i] - expert_offset;
@@ -256,11 +258,11 @@ extern "C" int mb_router_topk(const float* logits, float* probs, float* topk_w, 
   return static_cast<int>(cudaGetLastError());
 }
 
-extern "C" int mb_moe_align(const int* idx, int n, int E, int expert_offset, int* seg_offsets, int* tile_expert, int* row_src,
-                            int* dst_row, int max_rows, cudaStream_t s) {
+extern "C" int mb_moe_align(const int* idx, int n, const int* n_ptr, int E, int expert_offset, int* seg_offsets, int* tile_expert,
+                            int* row_src, int* dst_row, int max_rows, cudaStream_t s) {
   if (E > 2048) return -1;
-  moe_align_kernel<<<1, 1024, (3 * E + 1) * sizeof(int), s>>>(idx, n, E, expert_offset, seg_offsets, tile_expert, row_src, dst_row,
-                                                              max_rows);
+  moe_align_kernel<<<1, 1024, (3 * E + 1) * sizeof(int), s>>>(idx, n, n_ptr, E, expert_offset, seg_offsets, tile_expert, row_src,
+                                                              dst_row, max_rows);
   return static_cast<int>(cudaGetLastError());
 }
 

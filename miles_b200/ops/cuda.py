@@ -182,7 +182,7 @@ class _SwiGLU(torch.autograd.Function):
     def forward(ctx, gate_up):
         gate_up = _c(gate_up)
         out = torch.empty(*gate_up.shape[:-1], gate_up.shape[-1] // 2, dtype=gate_up.dtype, device=gate_up.device)
-        C.swiglu_fwd(gate_up, out)
+        C.swiglu_fwd(gate_up, out, None)
         ctx.save_for_backward(gate_up)
         return out
 
@@ -190,7 +190,7 @@ class _SwiGLU(torch.autograd.Function):
     def backward(ctx, g):
         (gate_up,) = ctx.saved_tensors
         din = torch.empty_like(gate_up)
-        C.swiglu_bwd(gate_up, _c(g), din)
+        C.swiglu_bwd(gate_up, _c(g), din, None)
         return din
 
 

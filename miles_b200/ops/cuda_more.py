@@ -112,6 +112,40 @@ def moe_max_rows(n_pairs: int, num_experts: int) -> int:
     return (n_pairs + num_experts * 127 + 127) // 128 * 128
 
 
+def experts_forward(x_perm, w13, w2, seg, tile):
+    """Grouped expert FFN on expert-sorted, 128-padded rows. Returns (h1 pre-activation, y_perm)."""
+    max_rows, H = x_perm.shape
+    E, F2, _ = w13.shape
+    h1 = torch.empty(max_rows, F2, dtype=x_perm.dtype, device=x_perm.device)
+    C.gemm_grouped(x_perm, w13, h1, max_rows, F2, H, E, tile, False, 0)
+    act = torch.empty(max_rows, F2 // 2, dtype=x_perm.dtype, device=x_perm.device)
+    C.swiglu_fwd(h1, act, seg[-1:])
+    y_perm = torch.empty(max_rows, H, dtype=x_perm.dtype, device=x_perm.device)
+    C.gemm_grouped(act, w2, y_perm, max_rows, H, F2 // 2, E, tile, False, 0)
+    return h1, y_perm
+
+
+def experts_backward(dy_perm, x_perm, h1, w13, w2, seg, tile):
+    """Backward of `experts_forward`: returns (dx_perm, dw13, dw2)."""
+    max_rows, H = x_perm.shape
+    E, F2, _ = w13.shape
+    F = F2 // 2
+    dt, dev = x_perm.dtype, x_perm.device
+    act = torch.empty(max_rows, F, dtype=dt, device=dev)
+    C.swiglu_fwd(h1, act, seg[-1:])
+    dact = torch.empty(max_rows, F, dtype=dt, device=dev)
+    C.gemm_grouped(dy_perm, w2, dact, max_rows, F, H, E, tile, True, 0)
+    dw2 = torch.empty_like(w2)
+    C.gemm_grouped_wgrad(dy_perm, act, dw2, max_rows, H, F, E, seg, False, 0)
+    dh1 = torch.empty(max_rows, F2, dtype=dt, device=dev)
+    C.swiglu_bwd(h1, dact, dh1, seg[-1:])
+    dw13 = torch.empty_like(w13)
+    C.gemm_grouped_wgrad(dh1, x_perm, dw13, max_rows, F2, H, E, seg, False, 0)
+    dx_perm = torch.empty(max_rows, H, dtype=dt, device=dev)
+    C.gemm_grouped(dh1, w13, dx_perm, max_rows, H, F2, E, tile, True, 0)
+    return dx_perm, dw13, dw2
+
+
 class _MoEFFN(torch.autograd.Function):
     """y[t] = Σ_j w[t,j] · W2[e]·swiglu(W13[e]·x[t]) with e = idx[t,j] − expert_offset ∈ [0, E_local) (others skipped)."""
 
@@ -125,13 +159,13 @@ class _MoEFFN(torch.autograd.Function):
         idx32 = _c(topk_idx.to(torch.int32)).view(-1)
         wf = _c(topk_w.float())
         max_rows = moe_max_rows(T * k, E)
-        seg, tile, row_src, dst_row = C.moe_align(idx32, E, expert_offset, max_rows)
+        seg, tile, row_src, dst_row = C.moe_align(idx32, E, expert_offset, max_rows, None)
         x_perm = torch.empty(max_rows, H, dtype=x.dtype, device=x.device)
         C.moe_gather(x, x_perm, row_src, seg, k)
         h1 = torch.empty(max_rows, F2, dtype=x.dtype, device=x.device)
         C.gemm_grouped(x_perm, w13, h1, max_rows, F2, H, E, tile, False, 0)
         act = torch.empty(max_rows, F, dtype=x.dtype, device=x.device)
-        C.swiglu_fwd(h1, act)
+        C.swiglu_fwd(h1, act, seg[-1:])
         y_perm = torch.empty(max_rows, H, dtype=x.dtype, device=x.device)
         C.gemm_grouped(act, w2, y_perm, max_rows, H, F, E, tile, False, 0)
         out = torch.empty(T, H, dtype=x.dtype, device=x.device)
@@ -154,14 +188,13 @@ class _MoEFFN(torch.autograd.Function):
         C.moe_combine_bwd(dout, y_perm, wf.view(-1), row_src, seg, dy_perm, dw_flat, k)
         # through W2: dact = dy_perm · W2 ; dW2[e] = dy_permᵀ · act
         act = torch.empty(max_rows, F, dtype=x.dtype, device=x.device)
-        C.swiglu_fwd(h1, act)
+        C.swiglu_fwd(h1, act, seg[-1:])
         dact = torch.empty(max_rows, F, dtype=x.dtype, device=x.device)
         C.gemm_grouped(dy_perm, w2, dact, max_rows, F, H, E, tile, True, 0)
         dw2 = torch.empty_like(w2)
         C.gemm_grouped_wgrad(dy_perm, act, dw2, max_rows, H, F, E, seg, False, 0)
-        # padded rows of `act`/`h1` hold garbage only where tiles were skipped; zero dact there via swiglu_bwd on zeros:
         dh1 = torch.empty(max_rows, F2, dtype=x.dtype, device=x.device)
-        C.swiglu_bwd(h1, dact, dh1)
+        C.swiglu_bwd(h1, dact, dh1, seg[-1:])
         x_perm = torch.empty(max_rows, H, dtype=x.dtype, device=x.device)
         C.moe_gather(x, x_perm, row_src, seg, k)
         dw13 = torch.empty_like(w13)

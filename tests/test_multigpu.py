@@ -1,0 +1,297 @@
+"""Fused compute+collective kernels on 2+ GPUs: each case runs as `world` child processes over NCCL on 127.0.0.1 and
+compares the fabric path with the same math done by NCCL collectives + single-GPU kernels (or a plain fp32 statement).
+NVLS is switched off in NCCL and the fabric kernels use plain peer loads/stores."""
+import os
+import socket
+import sys
+import traceback
+
+import pytest
+import torch
+
+pytestmark = [pytest.mark.gpu, pytest.mark.multigpu]
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def _free_port():
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        return s.getsockname()[1]
+
+
+def _entry(rank, world, port, fn_name, errq):
+    os.environ.update(RANK=str(rank), WORLD_SIZE=str(world), LOCAL_RANK=str(rank), MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port),
+                      NCCL_NVLS_ENABLE="0")
+    sys.path.insert(0, ROOT)
+    import datetime
+
+    import torch.distributed as dist
+
+    try:
+        torch.cuda.set_device(rank)
+        dist.init_process_group("nccl", rank=rank, world_size=world, timeout=datetime.timedelta(seconds=120))
+        globals()[fn_name](rank, world)
+        torch.cuda.synchronize()
+        dist.barrier()
+        dist.destroy_process_group()
+    except Exception:
+        errq.put((rank, traceback.format_exc()))
+        raise
+
+
+def _run(fn_name, world=2, timeout=300):
+    if torch.cuda.device_count() < world:
+        pytest.skip(f"needs {world} GPUs")
+    ctx = torch.multiprocessing.get_context("spawn")
+    errq = ctx.SimpleQueue()
+    port = _free_port()
+    procs = [ctx.Process(target=_entry, args=(r, world, port, fn_name, errq)) for r in range(world)]
+    for p in procs:
+        p.start()
+    for p in procs:
+        p.join(timeout)
+    bad = []
+    for p in procs:
+        if p.is_alive():
+            p.terminate()
+            bad.append("timeout")
+        elif p.exitcode != 0:
+            bad.append(f"exit {p.exitcode}")
+    msgs = []
+    while not errq.empty():
+        msgs.append("rank %d:\n%s" % errq.get())
+    assert not bad, ", ".join(bad) + "\n" + "\n".join(msgs)
+
+
+def _rel(a, b):
+    return ((a.float() - b.float()).norm() / b.float().norm().clamp_min(1e-12)).item()
+
+
+# ---- cases (run inside the child processes) ------------------------------------------------------------
+
+def _case_barrier_and_symmetric(rank, world):
+    import torch.distributed as dist
+
+    from miles_b200.parallel.fabric import CH_WORLD, Fabric
+    from miles_b200.parallel.state import ParallelState
+
+    ps = ParallelState.build(tp=1, ep=world)
+    fab = Fabric.create(ps)
+    buf = fab.alloc(1024, torch.float32, "t")
+    buf.fill_(float(rank + 1))
+    ranks = list(range(world))
+    for _ in range(5):
+        fab.barrier(ranks, CH_WORLD)
+    torch.cuda.synchronize()
+    fab.check()
+    sym, off = fab.sym_of(buf)
+    assert off == 0 and len(sym.views) == world
+    ptrs = fab.peer_ptrs(buf, ranks)
+    assert ptrs[rank].item() == buf.data_ptr() and len(set(ptrs.tolist())) == world
+    assert fab.K.check_error_flag() == 0
+
+
+def _case_fused_moe(rank, world):
+    import torch.distributed as dist
+
+    from miles_b200.ops import reference as ref
+    from miles_b200.parallel import ep as ep_mod
+    from miles_b200.parallel.fabric import Fabric
+    from miles_b200.parallel.state import ParallelState
+
+    torch.manual_seed(0)
+    E, K, H, F = 8 * world, 4, 512, 256
+    ps = ParallelState.build(tp=1, ep=world)
+    ps.fabric = Fabric.create(ps)
+    ps.fabric.moe_max_tokens = 1024
+    e_local = E // world
+    g = torch.Generator(device="cuda").manual_seed(1)
+    w13_all = (0.05 * torch.randn(E, 2 * F, H, device="cuda", generator=g)).to(torch.bfloat16)
+    w2_all = (0.05 * torch.randn(E, H, F, device="cuda", generator=g)).to(torch.bfloat16)
+    for T in (300 + 17 * rank, 5, 0 if rank == 1 else 64):
+        gr = torch.Generator(device="cuda").manual_seed(100 + rank)
+        x = (0.5 * torch.randn(T, H, device="cuda", generator=gr)).to(torch.bfloat16).requires_grad_()
+        tw, ti, _ = ref.router_topk(torch.randn(T, E, device="cuda", generator=gr), K, True)
+        tw = tw.detach().requires_grad_()
+        w13 = w13_all[rank * e_local:(rank + 1) * e_local].clone().requires_grad_()
+        w2 = w2_all[rank * e_local:(rank + 1) * e_local].clone().requires_grad_()
+        gy = torch.randn(T, H, device="cuda", generator=gr).to(torch.bfloat16)
+        # fused fabric path
+        ps.fused = True
+        y = ps.moe_ffn(x, w13, w2, tw, ti, E)
+        y.backward(gy)
+        ps.fabric.check()
+        got = (y.detach().clone(), x.grad.clone(), w13.grad.clone(), w2.grad.clone(), tw.grad.clone())
+        # oracle: every rank evaluates its own tokens against ALL experts in fp32
+        xf, twf = x.detach().float().requires_grad_(), tw.detach().float().requires_grad_()
+        w13f, w2f = w13_all.float().requires_grad_(), w2_all.float().requires_grad_()
+        yf = ref.moe_ffn(xf, w13f, w2f, twf, ti)
+        yf.backward(gy.float())
+        gw13, gw2 = w13f.grad.clone(), w2f.grad.clone()
+        dist.all_reduce(gw13)
+        dist.all_reduce(gw2)
+        if T:
+            assert _rel(got[0], yf) < 2e-2, ("y", T, _rel(got[0], yf))
+            assert _rel(got[1], xf.grad) < 3e-2, ("dx", T, _rel(got[1], xf.grad))
+            assert _rel(got[4], twf.grad) < 3e-2, ("dw_topk", T)
+        assert _rel(got[2], gw13[rank * e_local:(rank + 1) * e_local]) < 3e-2, ("dw13", T)
+        assert _rel(got[3], gw2[rank * e_local:(rank + 1) * e_local]) < 3e-2, ("dw2", T)
+
+
+def _case_fused_optimizer(rank, world):
+    import torch.distributed as dist
+
+    from miles_b200.parallel.fabric import Fabric
+    from miles_b200.parallel.state import ParallelState
+    from miles_b200.train.optimizer import DistributedAdam
+
+    def make(fused):
+        torch.manual_seed(0)
+        ps = ParallelState.build(tp=1, ep=1)
+        ps.fused = fused
+        if fused:
+            ps.fabric = Fabric.create(ps)
+        lin = torch.nn.ModuleList([torch.nn.Linear(256, 512, bias=True), torch.nn.Linear(512, 100, bias=False)]).cuda().bfloat16()
+        alloc = (lambda n, dt, dev, tag: ps.fabric.alloc(n, dt, tag)) if fused else None
+        opt = DistributedAdam(list(lin.named_parameters()), lr=1e-2, weight_decay=0.1, clip_grad=0.5, ps=ps, allocator=alloc)
+        return lin, opt
+
+    ref_m, ref_o = make(False)
+    fus_m, fus_o = make(True)
+    for step in range(3):
+        for m, o in ((ref_m, ref_o), (fus_m, fus_o)):
+            o.zero_grad()
+            g = torch.Generator(device="cuda").manual_seed(10 * step + rank)
+            x = torch.randn(64, 256, device="cuda", generator=g).bfloat16()
+            loss = m[1](torch.relu(m[0](x))).float().pow(2).mean()
+            loss.backward()
+        s1 = ref_o.step()
+        s2 = fus_o.step()
+        fus_o.ps.fabric.check()
+        assert abs(s1["grad_norm"] - s2["grad_norm"]) < 1e-3 * max(1.0, s1["grad_norm"]), (s1, s2)
+        for (n, a), (_, b) in zip(ref_m.named_parameters(), fus_m.named_parameters()):
+            assert torch.allclose(a.float(), b.float(), atol=1e-2, rtol=1e-2), (step, n, (a.float() - b.float()).abs().max())
+
+
+def _case_allreduce_rmsnorm(rank, world):
+    import torch.distributed as dist
+
+    from miles_b200.ops import reference as ref
+    from miles_b200.parallel.fabric import Fabric
+    from miles_b200.parallel.state import ParallelState
+
+    ps = ParallelState.build(tp=world, sequence_parallel=False)
+    ps.fabric = Fabric.create(ps)
+    torch.manual_seed(3)
+    T, H = 77, 2048
+    g = torch.Generator(device="cuda").manual_seed(rank)
+    partial = torch.randn(T, H, device="cuda", generator=g).bfloat16()
+    res = torch.randn(T, H, device="cuda").bfloat16()
+    w = (1 + 0.1 * torch.randn(H, device="cuda")).bfloat16()
+    for _ in range(3):
+        y, r = ps.fabric.allreduce_add_rmsnorm(partial, res, w, 1e-6, ps)
+    ps.fabric.check()
+    tot = partial.float().clone()
+    dist.all_reduce(tot)
+    yr, rr = ref.add_rmsnorm(tot.bfloat16(), res, w, 1e-6)
+    assert _rel(y, yr) < 2e-2 and _rel(r, rr) < 2e-2
+
+
+def _case_tp_fused_linears(rank, world):
+    import torch.distributed as dist
+
+    from miles_b200.parallel import tp as tpmod
+    from miles_b200.parallel.fabric import Fabric
+    from miles_b200.parallel.state import ParallelState
+
+    ps = ParallelState.build(tp=world, sequence_parallel=True)
+    ps.fabric = Fabric.create(ps)
+    T, K, N = 256 * world, 1024, 1536
+    g = torch.Generator(device="cuda").manual_seed(7)          # same on every rank
+    x_full = (0.5 * torch.randn(T, K, device="cuda", generator=g)).bfloat16()
+    w_col = (0.05 * torch.randn(N, K, device="cuda", generator=g)).bfloat16()       # column-parallel weight (full)
+    w_row = (0.05 * torch.randn(K, N, device="cuda", generator=g)).bfloat16()       # row-parallel weight (full) [out=K, in=N]
+    n = T // world
+    for it in range(3):
+        # column: y = gather(x) · w_shardᵀ
+        xs = x_full[rank * n:(rank + 1) * n].clone().requires_grad_()
+        wc = w_col.chunk(world, 0)[rank].clone().requires_grad_()
+        ps.fused = True
+        y = tpmod.column_parallel_linear(xs, wc, None, ps)
+        want = x_full.float() @ wc.detach().float().t()
+        assert _rel(y, want) < 1e-2, ("ag_gemm", it, _rel(y, want))
+        # row: z = reduce_scatter(y · w_row_shardᵀ)
+        wr = w_row.chunk(world, 1)[rank].clone().requires_grad_()
+        z = tpmod.row_parallel_linear(y, wr, ps)
+        full = y.detach().float() @ wr.detach().float().t()
+        dist.all_reduce(full)
+        assert _rel(z, full[rank * n:(rank + 1) * n]) < 2e-2, ("gemm_rs", it, _rel(z, full[rank * n:(rank + 1) * n]))
+        gz = torch.randn_like(z)
+        z.backward(gz)
+        ps.fabric.check()
+        # same graph through the NCCL path
+        ps.fused = False
+        xs2, wc2, wr2 = xs.detach().clone().requires_grad_(), wc.detach().clone().requires_grad_(), wr.detach().clone().requires_grad_()
+        z2 = tpmod.row_parallel_linear(tpmod.column_parallel_linear(xs2, wc2, None, ps), wr2, ps)
+        z2.backward(gz)
+        assert _rel(xs.grad, xs2.grad) < 2e-2 and _rel(wc.grad, wc2.grad) < 2e-2 and _rel(wr.grad, wr2.grad) < 2e-2
+
+
+def _case_vocab_logprob(rank, world):
+    from miles_b200.parallel import tp as tpmod
+    from miles_b200.parallel.fabric import Fabric
+    from miles_b200.parallel.state import ParallelState
+
+    ps = ParallelState.build(tp=world, sequence_parallel=False)
+    ps.fabric = Fabric.create(ps)
+    R, H, V = 300, 512, 4096 * world
+    g = torch.Generator(device="cuda").manual_seed(11)
+    h0 = torch.randn(R, H, device="cuda", generator=g).bfloat16()
+    w_full = (0.05 * torch.randn(V, H, device="cuda", generator=g)).bfloat16()
+    tg = torch.randint(0, V, (R,), device="cuda", generator=g)
+    g1 = torch.randn(R, device="cuda", generator=g)
+    g2 = torch.randn(R, device="cuda", generator=g)
+    h = h0.clone().requires_grad_()
+    w = w_full.chunk(world, 0)[rank].clone().requires_grad_()
+    ps.fused = True
+    lp, ent = tpmod.vocab_parallel_logprob(h, w, tg, 0.9, True, ps)
+    torch.autograd.backward([lp, ent], [g1, g2])
+    ps.fabric.check()
+    hf, wf = h0.float().requires_grad_(), w_full.float().requires_grad_()
+    logits = (hf @ wf.t()) / 0.9
+    lse = torch.logsumexp(logits, -1)
+    lpr = logits.gather(1, tg[:, None]).squeeze(1) - lse
+    entr = lse - (torch.softmax(logits, -1) * logits).sum(-1)
+    torch.autograd.backward([lpr, entr], [g1, g2])
+    assert torch.allclose(lp, lpr, atol=2e-2, rtol=1e-2) and torch.allclose(ent, entr, atol=2e-2, rtol=1e-2)
+    assert _rel(h.grad, hf.grad) < 3e-2, _rel(h.grad, hf.grad)
+    vl = V // world
+    assert _rel(w.grad, wf.grad[rank * vl:(rank + 1) * vl]) < 3e-2
+
+
+# ---- pytest entry points -----------------------------------------------------------------------------------
+
+def test_tp_fused_ag_gemm_and_gemm_rs():
+    _run("_case_tp_fused_linears")
+
+
+def test_fused_vocab_parallel_logprob():
+    _run("_case_vocab_logprob")
+
+
+
+def test_fabric_barrier_and_symmetric_memory():
+    _run("_case_barrier_and_symmetric")
+
+
+def test_fused_moe_dispatch_combine_matches_oracle():
+    _run("_case_fused_moe")
+
+
+def test_fused_optimizer_step_matches_collective_path():
+    _run("_case_fused_optimizer")
+
+
+def test_allreduce_add_rmsnorm():
+    _run("_case_allreduce_rmsnorm")
