@@ -183,13 +183,26 @@ class DecodeRunner:
         torch.cuda.current_stream().synchronize()
         return self.h_tok.numpy(), self.h_lp.numpy(), (self.h_routed.numpy() if record else None)
 
+    def warmup(self):
+        """One eager decode step on padding rows only (no KV writes): initialises per-kernel attributes before any
+        graph capture.  Expert-parallel ranks call this together (every MoE layer is a collective)."""
+        if getattr(self, "_warm", False):
+            return
+        self.d_i32.copy_(self.h_i32)
+        self.d_i64.copy_(self.h_i64)
+        self._forward(1, self.n_moe > 0)
+        torch.cuda.synchronize()
+        self._warm = True
+
     def _capture(self, key):
         from .. import ops
 
         B, record = key
-        # eager warm-up with the same shapes (initialises per-kernel attributes and the allocator pool)
-        self._forward(B, record)
-        torch.cuda.synchronize()
+        if self.e.lockstep_group is None:
+            # eager warm-up with the same shapes (initialises per-kernel attributes and the allocator pool); lockstep
+            # engines must not run an extra forward here because their peers would not match its collectives
+            self._forward(B, record)
+            torch.cuda.synchronize()
         g = torch.cuda.CUDAGraph()
         n0 = ops._k().launch_count()
         with torch.cuda.graph(g, pool=self.pool):

@@ -386,6 +386,8 @@ class Engine:
     def begin_rollout(self):
         self.local_done = False
         self.global_done = False
+        if self.runner is not None and self.lockstep_group is not None and self.kv.allocated:
+            self.runner.warmup()
 
     def finish_rollout(self):
         self.local_done = True
