@@ -195,7 +195,22 @@ def main():
     Rollout.executor = executor
     counters = {"tokens": 0, "h2d": 0, "d2h": 0, "sync_s": 0.0, "rollout_s": 0.0, "train_s": 0.0}
 
+    stall_s = int(os.environ.get("MILES_STALL_DUMP_S", "0"))
+
     def step(i):
+        if stall_s:   # dump every thread's python stack and exit if one step takes longer than this
+            import faulthandler
+
+            faulthandler.dump_traceback_later(stall_s, exit=True)
+        try:
+            return _step(i)
+        finally:
+            if stall_s:
+                import faulthandler
+
+                faulthandler.cancel_dump_traceback_later()
+
+    def _step(i):
         t0 = time.perf_counter()
         pack = executor.get(i)
         t1 = time.perf_counter()

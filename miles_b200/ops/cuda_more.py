@@ -21,9 +21,10 @@ class _FlashAttn(torch.autograd.Function):
         scale = 1.0 / math.sqrt(D)
         o = torch.empty(T, Hq, D, dtype=q.dtype, device=q.device)
         lse = torch.empty(Hq, T, dtype=torch.float32, device=q.device)
-        if max_seqlen <= 0:
-            max_seqlen = int((cu_seqlens[1:] - cu_seqlens[:-1]).max().item())
-        C.flash_fwd(q, k, v, o, lse, cu_seqlens, max_seqlen, scale, causal)
+        if T > 0 and cu_seqlens.numel() > 1:
+            if max_seqlen <= 0:
+                max_seqlen = int((cu_seqlens[1:] - cu_seqlens[:-1]).max().item())
+            C.flash_fwd(q, k, v, o, lse, cu_seqlens, max_seqlen, scale, causal)
         ctx.save_for_backward(q, k, v, o, lse, cu_seqlens)
         ctx.max_seqlen, ctx.causal, ctx.scale = max_seqlen, causal, scale
         return o

@@ -23,6 +23,7 @@ class InProcEngineClient:
         self.moe_topk = cfg.moe_topk
         self._driver: asyncio.Task | None = None
         self.sync_drive = True   # step engines from the event loop instead of background threads
+        self._pending: set = set()
 
     async def start(self):
         if self.sync_drive:
@@ -33,6 +34,15 @@ class InProcEngineClient:
                 e.start_loop()
 
     async def _drive(self):
+        try:
+            await self._drive_loop()
+        except BaseException as exc:   # surface engine failures to every waiting generate() call
+            for fut in list(self._pending):
+                if not fut.done():
+                    fut.set_exception(RuntimeError(f"engine step failed: {type(exc).__name__}: {exc}"))
+            raise
+
+    async def _drive_loop(self):
         idle = 0
         lockstep = any(e.lockstep_group is not None for e in self.engines)
         while True:
@@ -80,6 +90,7 @@ class InProcEngineClient:
             loop.call_soon_threadsafe(lambda: fut.done() or fut.set_result(req))
 
         self._active[i] += 1
+        self._pending.add(fut)
         try:
             eng.add_request(payload["input_ids"], payload.get("sampling_params"), payload.get("return_logprob", True),
                             payload.get("return_routed_experts", False), on_done=on_done)
@@ -87,6 +98,7 @@ class InProcEngineClient:
             req = await fut
         finally:
             self._active[i] -= 1
+            self._pending.discard(fut)
         return req.to_response(eng)
 
     async def abort_all(self):
