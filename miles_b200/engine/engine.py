@@ -250,6 +250,17 @@ class Engine:
                 self.weight_version = int(weight_version)
         return {"success": True}
 
+    def update_weights_from_disk(self, model_path: str, weight_version: int | None = None):
+        """Load an HF safetensors directory (full tensors, HF names) into this rank's shard."""
+        from ..checkpoint import hf_io
+        from ..models.convert import load_named_into_model
+
+        with self.lock:
+            load_named_into_model(self.model, hf_io.load_hf_dir(model_path).items(), self.cfg, self.ps)
+            if weight_version is not None:
+                self.weight_version = int(weight_version)
+        return {"success": True}
+
     def release_memory_occupation(self, tags: list[str] | None = None):
         tags = tags or ["kv_cache", "weights", "cuda_graph"]
         with self.lock:
