@@ -53,6 +53,16 @@ void flash_fwd(const at::Tensor& q, const at::Tensor& k, const at::Tensor& v, at
         "mb_flash_fwd");
 }
 
+void flash_fwd_tc(const at::Tensor& q, const at::Tensor& k, const at::Tensor& v, at::Tensor& o, const c10::optional<at::Tensor>& lse,
+                  const at::Tensor& cu_seqlens, int64_t max_seqlen, double scale, bool causal, at::Tensor& err) {
+  c10::cuda::CUDAGuard g(q.device());
+  const int64_t T = q.size(0), Hq = q.size(1), Hkv = k.size(1);
+  check(mb_flash_fwd_tc(q.data_ptr(), k.data_ptr(), v.data_ptr(), o.data_ptr(), fptr(lse), cu_seqlens.data_ptr<int>(),
+                        cu_seqlens.numel() - 1, max_seqlen, T, q.stride(0), k.stride(0), v.stride(0), Hq, Hkv, scale, causal,
+                        err.data_ptr<int>(), cur_stream()),
+        "mb_flash_fwd_tc");
+}
+
 void flash_bwd(const at::Tensor& q, const at::Tensor& k, const at::Tensor& v, const at::Tensor& o, const at::Tensor& dout,
                const at::Tensor& lse, at::Tensor& delta, at::Tensor& dq, at::Tensor& dk, at::Tensor& dv, const at::Tensor& cu_seqlens,
                int64_t max_seqlen, double scale, bool causal) {
@@ -85,6 +95,7 @@ void register_fabric(pybind11::module& m); // bindings_fabric.cpp
 void register_more(pybind11::module& m) {
   m.def("install_crash_handler", &install_crash_handler);
   m.def("flash_fwd", &flash_fwd);
+  m.def("flash_fwd_tc", &flash_fwd_tc);
   m.def("flash_bwd", &flash_bwd);
   m.def("paged_decode", &paged_decode);
   register_moe(m);

@@ -53,6 +53,11 @@ int mb_paged_decode(const void* q, const void* kc, const void* vc, const int* bl
                     float* part_o, float* part_ml, int batch, int max_blocks, int block_size, int Hq, int Hkv, int D, float scale,
                     int num_splits, cudaStream_t s);
 
+// ---- attention_tc.cu (tcgen05 forward, head_dim 128) ----
+int mb_flash_fwd_tc(const void* q, const void* k, const void* v, void* o, float* lse, const int* cu_seqlens, int batch, int max_seqlen,
+                    int total_tokens, long long q_stride, long long k_stride, long long v_stride, int Hq, int Hkv, float scale,
+                    int causal, int* error_flag, cudaStream_t s);
+
 // ---- moe.cu ----
 int mb_router_topk(const float* logits, float* probs, float* topk_w, int* topk_idx, long long T, int E, int K, int normalize,
                    cudaStream_t s);

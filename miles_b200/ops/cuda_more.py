@@ -2,6 +2,7 @@
 from __future__ import annotations
 
 import math
+import os
 
 import torch
 
@@ -11,6 +12,9 @@ from .cuda import BF16, C, _c, gemm_nn, gemm_nt, gemm_tn
 # ---------------------------------------------------------------------------------------------
 # attention
 # ---------------------------------------------------------------------------------------------
+
+
+USE_TC_ATTENTION = os.environ.get("MILES_TC_ATTENTION", "1") != "0"
 
 
 class _FlashAttn(torch.autograd.Function):
@@ -24,7 +28,11 @@ class _FlashAttn(torch.autograd.Function):
         if T > 0 and cu_seqlens.numel() > 1:
             if max_seqlen <= 0:
                 max_seqlen = int((cu_seqlens[1:] - cu_seqlens[:-1]).max().item())
-            C.flash_fwd(q, k, v, o, lse, cu_seqlens, max_seqlen, scale, causal)
+            if D == 128 and USE_TC_ATTENTION and q.stride(0) % 8 == 0 and k.stride(0) % 8 == 0 and v.stride(0) % 8 == 0:
+                # tcgen05 forward (TMA-fed, accumulators in tensor memory)
+                C.flash_fwd_tc(q, k, v, o, lse, cu_seqlens, max_seqlen, scale, causal, C.error_flag(q))
+            else:
+                C.flash_fwd(q, k, v, o, lse, cu_seqlens, max_seqlen, scale, causal)
         ctx.save_for_backward(q, k, v, o, lse, cu_seqlens)
         ctx.max_seqlen, ctx.causal, ctx.scale = max_seqlen, causal, scale
         return o
