@@ -592,3 +592,62 @@ extern "C" int mb_adamw(float* master, const float* grad, float* m, float* v, co
                                                 wd, bc1, bc2);
   return static_cast<int>(cudaGetLastError());
 }
+
+// ---------------------------------------------------------------------------------------------
+// RMSNorm backward without any allocation (declared in launch.h)
+// ---------------------------------------------------------------------------------------------
+// Same two kernels as mb_rmsnorm_bwd, but the per-CTA partial weight-gradient rows live in a fixed array in device
+// global memory instead of a buffer supplied by the caller.  Nothing is allocated here, by CUDA or by a library.
+// The array is one per device and shared by every call on that device:
+//   * it keeps whatever the previous call left in it; nothing has to be cleared, because each call first writes every
+//     element (rows 0..blocks-1, columns 0..H-1) that its reduction then reads;
+//   * two calls that overlap in time on one device (different streams, or threads) write the same rows and race:
+//     the caller orders them.
+// Limit: H ≤ MB_RMSNORM_BWD_STATIC_MAX_H; larger H is refused with MB_ERR_STATIC_SCRATCH_TOO_SMALL.
+static constexpr int kStaticBwdMaxBlocks = 148 * 4;   // the largest grid mb_rmsnorm_bwd_blocks() returns
+static __device__ __align__(256) float g_rmsnorm_bwd_scratch[static_cast<size_t>(kStaticBwdMaxBlocks) * MB_RMSNORM_BWD_STATIC_MAX_H];
+
+namespace {
+constexpr int kMaxDevices = 64;
+float* g_static_scratch_addr[kMaxDevices];   // device address of the array, looked up once per device
+}  // namespace
+
+extern "C" const char* mb_rmsnorm_bwd_static_strerror(int code) {
+  switch (code) {
+    case 0: return "ok";
+    case -1: return "mb_rmsnorm_bwd_static: H must be a multiple of 8";
+    case MB_ERR_STATIC_SCRATCH_TOO_SMALL:
+      return "mb_rmsnorm_bwd_static: H exceeds MB_RMSNORM_BWD_STATIC_MAX_H (4096), the width the fixed scratch array holds; "
+             "use mb_rmsnorm_bwd with a caller-provided buffer";
+    case MB_ERR_STATIC_SCRATCH_SETUP: return "mb_rmsnorm_bwd_static: could not resolve the scratch array's device address";
+    default: return code > 0 ? cudaGetErrorString(static_cast<cudaError_t>(code)) : "mb_rmsnorm_bwd_static: unknown error";
+  }
+}
+
+extern "C" int mb_rmsnorm_bwd_static(const void* x, const void* w, const void* dy, const void* dres, const float* rstd, void* dx,
+                                     void* dw_out, int dw_fp32, long long T, int H, cudaStream_t s) {
+  if (H % 8) return -1;
+  if (H > MB_RMSNORM_BWD_STATIC_MAX_H) return MB_ERR_STATIC_SCRATCH_TOO_SMALL;
+  int dev = 0;
+  cudaError_t rc = cudaGetDevice(&dev);
+  if (rc != cudaSuccess) return static_cast<int>(rc);
+  if (dev < 0 || dev >= kMaxDevices) return MB_ERR_STATIC_SCRATCH_SETUP;
+  float* scratch = __atomic_load_n(&g_static_scratch_addr[dev], __ATOMIC_ACQUIRE);
+  if (scratch == nullptr) {
+    // First call on this device: resolve the symbol (this may load the module, so it belongs before any stream capture).
+    void* p = nullptr;
+    rc = cudaGetSymbolAddress(&p, g_rmsnorm_bwd_scratch);
+    if (rc != cudaSuccess) return static_cast<int>(rc);
+    if (p == nullptr) return MB_ERR_STATIC_SCRATCH_SETUP;
+    scratch = static_cast<float*>(p);
+    __atomic_store_n(&g_static_scratch_addr[dev], scratch, __ATOMIC_RELEASE);   // racing first calls store the same value
+  }
+  if (T == 0) return 0;
+  const int blocks = mb_rmsnorm_bwd_blocks(T);
+  if (blocks > kStaticBwdMaxBlocks) return MB_ERR_STATIC_SCRATCH_TOO_SMALL;
+  mb::rmsnorm_bwd_kernel<<<blocks, 256, 0, s>>>(reinterpret_cast<const __nv_bfloat16*>(x), reinterpret_cast<const __nv_bfloat16*>(w),
+                                                reinterpret_cast<const __nv_bfloat16*>(dy), reinterpret_cast<const __nv_bfloat16*>(dres),
+                                                rstd, reinterpret_cast<__nv_bfloat16*>(dx), scratch, static_cast<int>(T), H);
+  mb::colsum_kernel<<<(H + 255) / 256, 256, 0, s>>>(scratch, dw_out, blocks, H, dw_fp32);
+  return static_cast<int>(cudaGetLastError());
+}

@@ -27,6 +27,24 @@ int mb_rmsnorm_fwd(const void* x, const void* residual, const void* w, void* y, 
 int mb_rmsnorm_bwd_blocks(long long T);
 int mb_rmsnorm_bwd(const void* x, const void* w, const void* dy, const void* dres, const float* rstd, void* dx, float* dw_partial,
                    void* dw_out, int dw_fp32, long long T, int H, cudaStream_t s);
+// RMSNorm backward that allocates nothing.  This entry point has no counterpart in the reference framework, whose
+// kernels all take their workspaces from the PyTorch caching allocator; it exists for callers that cannot allocate:
+// a C or C++ host without torch, code running under an allocator that is frozen or being snapshotted (the sleep /
+// wake-up window in which the trainer's device memory is handed to the rollout engine), and latency-critical paths
+// where an allocator call may synchronise the device.
+//   * Same arguments and results as mb_rmsnorm_bwd minus `dw_partial`: the partial sums go to a fixed array in device
+//     memory (592 × MB_RMSNORM_BWD_STATIC_MAX_H floats ≈ 9.7 MB, one per device, reserved when the module loads).
+//   * H > MB_RMSNORM_BWD_STATIC_MAX_H returns MB_ERR_STATIC_SCRATCH_TOO_SMALL; mb_rmsnorm_bwd_static_strerror() gives text.
+//   * The first call on each device looks up the array's address with cudaGetSymbolAddress; make that call before any
+//     stream capture begins.  Later calls only launch the two kernels.
+//   * The array is shared by all calls on a device and keeps its last contents.  Nothing needs to be zeroed: each call
+//     writes every element it later reads.  Calls that overlap on one device race on it; the caller serialises them.
+#define MB_RMSNORM_BWD_STATIC_MAX_H 4096
+#define MB_ERR_STATIC_SCRATCH_TOO_SMALL (-2)
+#define MB_ERR_STATIC_SCRATCH_SETUP (-3)
+int mb_rmsnorm_bwd_static(const void* x, const void* w, const void* dy, const void* dres, const float* rstd, void* dx, void* dw_out,
+                          int dw_fp32, long long T, int H, cudaStream_t s);
+const char* mb_rmsnorm_bwd_static_strerror(int code);
 int mb_colsum(const float* partial, void* out, int R, int C, int out_fp32, cudaStream_t s);
 int mb_swiglu_fwd(const void* in, void* out, long long T, int F, const int* rows_ptr, cudaStream_t s);
 int mb_swiglu_bwd(const void* in, const void* dout, void* din, long long T, int F, const int* rows_ptr, cudaStream_t s);

@@ -1,0 +1,93 @@
+"""The allocation-free RMSNorm backward (`mb_rmsnorm_bwd_static`) called through its exported C symbol.
+
+It must give bit-identical results to `mb_rmsnorm_bwd` (same kernels, same grid; only the home of the partial sums
+differs), on consecutive calls that reuse the fixed scratch array with stale contents in it, and it must refuse widths
+the array cannot hold.  The file name sorts last so that it also runs after every other test has used the device.
+"""
+import ctypes
+
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+
+def _lib():
+    from miles_b200.ops import build
+    from miles_b200.ops import cuda as _cuda  # noqa: F401  (loads the extension, and with it libtorch, into the process)
+
+    lib = ctypes.CDLL(str(build.so_path()))
+    vp, ll, i = ctypes.c_void_p, ctypes.c_longlong, ctypes.c_int
+    lib.mb_rmsnorm_bwd_static.argtypes = [vp, vp, vp, vp, vp, vp, vp, i, ll, i, vp]
+    lib.mb_rmsnorm_bwd_static.restype = i
+    lib.mb_rmsnorm_bwd.argtypes = [vp, vp, vp, vp, vp, vp, vp, vp, i, ll, i, vp]
+    lib.mb_rmsnorm_bwd.restype = i
+    lib.mb_rmsnorm_bwd_blocks.argtypes = [ll]
+    lib.mb_rmsnorm_bwd_blocks.restype = i
+    lib.mb_rmsnorm_bwd_static_strerror.argtypes = [i]
+    lib.mb_rmsnorm_bwd_static_strerror.restype = ctypes.c_char_p
+    return lib
+
+
+def _case(T, H, seed, with_dres):
+    g = torch.Generator(device="cuda").manual_seed(seed)
+    x = torch.randn(T, H, device="cuda", generator=g).bfloat16()
+    w = (1 + 0.1 * torch.randn(H, device="cuda", generator=g)).bfloat16()
+    dy = torch.randn(T, H, device="cuda", generator=g).bfloat16()
+    dres = torch.randn(T, H, device="cuda", generator=g).bfloat16() if with_dres else None
+    rstd = torch.rsqrt(x.float().pow(2).mean(-1) + 1e-6)
+    return x, w, dy, dres, rstd
+
+
+def _run_both(lib, x, w, dy, dres, rstd, dw_fp32):
+    T, H = x.shape
+    stream = ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
+    p = lambda t: ctypes.c_void_p(t.data_ptr() if t is not None else None)
+    dw_dtype = torch.float32 if dw_fp32 else torch.bfloat16
+    # every buffer is allocated before the call under test, which must allocate nothing itself
+    dx_a, dx_b = torch.empty_like(x), torch.empty_like(x)
+    dw_a, dw_b = torch.empty(H, device="cuda", dtype=dw_dtype), torch.empty(H, device="cuda", dtype=dw_dtype)
+    partial = torch.empty(lib.mb_rmsnorm_bwd_blocks(T), H, device="cuda", dtype=torch.float32)
+    rc = lib.mb_rmsnorm_bwd(p(x), p(w), p(dy), p(dres), p(rstd), p(dx_a), p(partial), p(dw_a), int(dw_fp32), T, H, stream)
+    assert rc == 0
+    torch.cuda.synchronize()
+    before = torch.cuda.memory_stats()["allocation.all.allocated"]
+    rc = lib.mb_rmsnorm_bwd_static(p(x), p(w), p(dy), p(dres), p(rstd), p(dx_b), p(dw_b), int(dw_fp32), T, H, stream)
+    assert rc == 0, lib.mb_rmsnorm_bwd_static_strerror(rc)
+    torch.cuda.synchronize()
+    assert torch.cuda.memory_stats()["allocation.all.allocated"] == before
+    return (dx_a, dw_a), (dx_b, dw_b)
+
+
+def test_static_matches_existing_on_consecutive_calls():
+    lib = _lib()
+    # the second call is smaller and narrower, so stale rows and columns of the first stay in the array around it
+    for T, H, seed, with_dres, dw_fp32 in [(3000, 4096, 1, True, True), (37, 2048, 2, False, False), (3000, 4096, 3, True, False)]:
+        x, w, dy, dres, rstd = _case(T, H, seed, with_dres)
+        (dx_a, dw_a), (dx_b, dw_b) = _run_both(lib, x, w, dy, dres, rstd, dw_fp32)
+        assert torch.equal(dx_a, dx_b)
+        assert torch.equal(dw_a, dw_b)
+        # and against plain fp32 PyTorch
+        xf, wf, dyf = x.float(), w.float(), dy.float()
+        xh = xf * rstd[:, None]
+        gw = dyf * wf
+        ref_dx = rstd[:, None] * (gw - xh * (gw * xh).mean(-1, keepdim=True))
+        if dres is not None:
+            ref_dx = ref_dx + dres.float()
+        ref_dw = (dyf * xh).sum(0)
+        torch.testing.assert_close(dx_b.float(), ref_dx, atol=3e-2, rtol=2e-2)
+        torch.testing.assert_close(dw_b.float(), ref_dw, atol=0.5 if not dw_fp32 else 1e-2, rtol=2e-2)
+
+
+def test_static_rejects_oversize():
+    lib = _lib()
+    H = 8192
+    x, w, dy, _, rstd = _case(4, H, 5, False)
+    dx, dw = torch.empty_like(x), torch.empty(H, device="cuda")
+    stream = ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
+    p = lambda t: ctypes.c_void_p(t.data_ptr() if t is not None else None)
+    rc = lib.mb_rmsnorm_bwd_static(p(x), p(w), p(dy), p(None), p(rstd), p(dx), p(dw), 1, 4, H, stream)
+    assert rc == -2
+    assert b"4096" in lib.mb_rmsnorm_bwd_static_strerror(rc)
+    rc = lib.mb_rmsnorm_bwd_static(p(x), p(w), p(dy), p(None), p(rstd), p(dx), p(dw), 1, 4, 4092, stream)
+    assert rc == -1
