@@ -261,6 +261,33 @@ class Engine:
                 self.weight_version = int(weight_version)
         return {"success": True}
 
+    def init_weights_update_group(self, master_address: str, master_port: int, rank_offset: int, world_size: int,
+                                  group_name: str = "weight_sync", backend: str | None = None):
+        """Join the trainer's weight-broadcast group (disaggregated sync); this engine rank becomes
+        `rank_offset + tp/ep-local rank` of it."""
+        from ..weight_update import broadcast as bc
+
+        backend = backend or ("nccl" if self.device.type == "cuda" else "gloo")
+        local = getattr(self.ps, "rank_in_engine", 0)
+        bc.make_group(backend, master_address, int(master_port), int(rank_offset) + local, int(world_size), name=group_name)
+        return {"success": True}
+
+    def update_weights_from_distributed(self, names, dtypes, shapes, group_name: str = "weight_sync",
+                                        load_format: str | None = None, weight_version: int | None = None):
+        """Receive one bucket (HF names, full tensors) broadcast by the trainer and load this rank's shard of it."""
+        from ..models.convert import load_named_into_model
+        from ..weight_update import broadcast as bc
+
+        pg = bc.get_group(group_name)
+        assert pg is not None, f"weight update group {group_name!r} was never initialised"
+        meta = {"names": list(names), "dtypes": list(dtypes), "shapes": [list(s) for s in shapes]}
+        named = bc.recv_bucket(pg, meta, load_format == "flattened_bucket", self.device)
+        with self.lock:
+            load_named_into_model(self.model, named, self.cfg, self.ps)
+            if weight_version is not None:
+                self.weight_version = int(weight_version)
+        return {"success": True}
+
     def release_memory_occupation(self, tags: list[str] | None = None):
         tags = tags or ["kv_cache", "weights", "cuda_graph"]
         with self.lock:

@@ -119,6 +119,22 @@ def build_app(engine, tokenizer=None):
             engine.update_weight_version(int(body["weight_version"]))
         return {"success": True}
 
+    @app.post("/init_weights_update_group")
+    async def init_group(request: Request):
+        import asyncio
+
+        body = await request.json()
+        # the rendezvous blocks until the trainer joins: keep the event loop free meanwhile
+        return await asyncio.get_running_loop().run_in_executor(None, lambda: engine.init_weights_update_group(**body))
+
+    @app.post("/update_weights_from_distributed")
+    async def update_from_distributed(request: Request):
+        import asyncio
+
+        body = await request.json()
+        body.pop("selector", None)
+        return await asyncio.get_running_loop().run_in_executor(None, lambda: engine.update_weights_from_distributed(**body))
+
     @app.post("/update_weight_version")
     async def set_version(request: Request):
         body = await request.json()

@@ -43,6 +43,7 @@ class ForwardMeta:
     replay_topk: torch.Tensor | None = None  # int32 [T, L_moe, k] recorded indices (-1 rows → fallthrough)
     record_topk: "list[torch.Tensor] | None" = None  # filled with int32 [T,k] per MoE layer when not None
     recompute: bool = False                  # activation checkpoint each layer
+    lora_slots: torch.Tensor | None = None   # int64 [T] adapter slot per token (None → slot 0; -1 → base model only)
 
 
 class _Init:
@@ -94,6 +95,9 @@ class Attention(nn.Module):
     def forward(self, x: torch.Tensor, meta: ForwardMeta, layer: int) -> torch.Tensor:
         cfg = self.cfg
         qkv = self.ps.column_linear(x, self.wqkv, self.bqkv)          # SP all-gather fused on GPU
+        lora = getattr(self, "lora", None)
+        if lora is not None and "wqkv" in lora:
+            qkv = qkv + lora["wqkv"](x, meta)
         T = qkv.shape[0]
         q, k, v = qkv.split([self.hq * self.d, self.hkv * self.d, self.hkv * self.d], dim=-1)
         q, k, v = q.view(T, self.hq, self.d), k.view(T, self.hkv, self.d), v.view(T, self.hkv, self.d)
@@ -108,7 +112,11 @@ class Attention(nn.Module):
             kc, vc = meta.kv_cache[layer]
             o = ops.paged_attention(q, kc, vc, meta.block_table, meta.seq_lens, q_lens=meta.q_lens,
                                     max_q_len=meta.max_seqlen)
-        return self.ps.row_linear(o.reshape(T, self.hq * self.d), self.wo)  # reduce-scatter fused on GPU
+        o = o.reshape(T, self.hq * self.d)
+        out = self.ps.row_linear(o, self.wo)                          # reduce-scatter fused on GPU
+        if lora is not None and "wo" in lora:
+            out = out + lora["wo"](o, meta)
+        return out
 
 
 class DenseFFN(nn.Module):
@@ -123,8 +131,15 @@ class DenseFFN(nn.Module):
         self.w2 = nn.Parameter(w2.chunk(tp, dim=1)[ps.tp_rank].contiguous())
 
     def forward(self, x, meta: ForwardMeta, layer: int):
-        h = ops.swiglu(self.ps.column_linear(x, self.w13))
-        return self.ps.row_linear(h, self.w2)
+        lora = getattr(self, "lora", None)
+        h13 = self.ps.column_linear(x, self.w13)
+        if lora is not None and "w13" in lora:
+            h13 = h13 + lora["w13"](x, meta)
+        h = ops.swiglu(h13)
+        out = self.ps.row_linear(h, self.w2)
+        if lora is not None and "w2" in lora:
+            out = out + lora["w2"](h, meta)
+        return out
 
 
 class MoEFFN(nn.Module):

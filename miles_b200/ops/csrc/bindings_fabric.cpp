@@ -162,9 +162,22 @@ void gemm_rs(const at::Tensor& X, const at::Tensor& W, const at::Tensor& partial
         "mb_gemm_rs");
 }
 
+// one launch per bucket: table int64 [n,4] and prefix int64 [n+1] live on the device
+void multi_copy(const at::Tensor& table, const at::Tensor& prefix, int64_t total_chunks) {
+  c10::cuda::CUDAGuard g(table.device());
+  check(mb_multi_copy(lptr(table), lptr(prefix), table.size(0), total_chunks, cur_stream()), "mb_multi_copy");
+}
+
+void multi_mxfp8(const at::Tensor& table, const at::Tensor& prefix, int64_t total_chunks, bool qdq) {
+  c10::cuda::CUDAGuard g(table.device());
+  check(mb_multi_mxfp8(lptr(table), lptr(prefix), table.size(0), total_chunks, qdq, cur_stream()), "mb_multi_mxfp8");
+}
+
 }  // namespace
 
 void register_fabric(pybind11::module& m) {
+  m.def("multi_copy", &multi_copy);
+  m.def("multi_mxfp8", &multi_mxfp8);
   m.def("ag_gemm", &ag_gemm);
   m.def("gemm_rs", &gemm_rs);
   m.def("sum_rows", &sum_rows);

@@ -124,6 +124,10 @@ int mb_sum_rows(const long long* src_ptrs, int world, void* out, long long numel
 int mb_gather_rows(const long long* src_ptrs, int world, void* out, long long bytes_per_rank, cudaStream_t s);
 int mb_stats_merge(const long long* stats_ptrs, int world, long long R, float* logp, float* ent, float* lse, cudaStream_t s);
 
+// ---- weight_sync.cu (one launch per bucket of tensors; dst may be peer memory) ----
+int mb_multi_copy(const long long* table, const long long* prefix, int n, long long total_chunks, cudaStream_t s);
+int mb_multi_mxfp8(const long long* table, const long long* prefix, int n, long long total_chunks, int qdq, cudaStream_t s);
+
 // ---- gemm_comm.cu ----
 int mb_ag_gemm(const long long* x_ptrs, const void* W, void* Y, int rows_per_rank, int N, int K, int rank, int world,
                const long long* flag_ptrs, int channel, int epoch, int* error_flag, cudaStream_t s);

@@ -102,7 +102,7 @@ class TrainActor:
             from .critic import attach_value_head
             attach_value_head(self.model, self.cfg, dtype, self.device)
         mark_expert_params(self.model)
-        named = list(self.model.named_parameters())
+        named = [(n, p) for n, p in self.model.named_parameters() if p.requires_grad]   # LoRA / critic freeze the rest
         self.optimizer = DistributedAdam(
             named, lr=args.lr if self.role == "actor" else args.critic_lr, betas=(args.adam_beta1, args.adam_beta2),
             eps=args.adam_eps, weight_decay=args.weight_decay, clip_grad=args.clip_grad, ps=self.ps,
@@ -336,7 +336,12 @@ class TrainActor:
         upd = engine_or_updater if isinstance(engine_or_updater, WeightUpdater) else \
             WeightUpdater(self.args, self, engine_or_updater)
         with self.timer.span("update_weights"):
-            info = upd.update_weights()
+            if getattr(self.model, "lora_adapters", None) and upd.mode != "alias":
+                from .lora import merged
+                with merged(self.model):          # the engine serves base + adapter as one set of weights
+                    info = upd.update_weights()
+            else:
+                info = upd.update_weights()
         return info
 
     def save_model(self, iteration: int, with_optimizer: bool = True):
@@ -374,6 +379,8 @@ class TrainActor:
 
 def _tp_replicated(name: str) -> bool:
     last = name.rsplit(".", 1)[-1]
+    if ".value_head." in name or (".lora." in name and last.endswith("_r")):
+        return True
     return last in ("ln1", "ln2", "norm", "q_norm", "k_norm", "router")
 
 

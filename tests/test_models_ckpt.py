@@ -1,0 +1,193 @@
+"""Model ⇄ HF ⇄ Megatron conversions, checkpoint formats, LoRA, critic head and weight-sync protocols (CPU)."""
+import os
+from types import SimpleNamespace
+
+import pytest
+import torch
+
+from miles_b200.models import convert
+from miles_b200.models.config import PRESETS
+from miles_b200.models.qwen3 import ForwardMeta, build_model
+from miles_b200.parallel.state import ParallelState
+
+
+def _model(name="tiny", seed=0, dtype=torch.float32):
+    cfg = PRESETS[name]
+    return cfg, build_model(cfg, ParallelState.single(), dtype=dtype, device="cpu", seed=seed)
+
+
+def _fwd(model, T=24, seed=0):
+    g = torch.Generator().manual_seed(seed)
+    toks = torch.randint(0, model.cfg.vocab_size, (T,), generator=g, dtype=torch.int32)
+    meta = ForwardMeta(positions=torch.arange(T, dtype=torch.int32), cu_seqlens=torch.tensor([0, T], dtype=torch.int32), max_seqlen=T)
+    return model(toks, meta), meta
+
+
+@pytest.mark.parametrize("name", ["tiny", "tiny-moe"])
+def test_hf_roundtrip_preserves_forward(name):
+    cfg, m = _model(name, seed=1)
+    hf = {}
+    for n, p in m.named_parameters():
+        for hn, t in convert.to_hf(n, p.detach(), cfg):
+            hf[hn] = t.clone()
+    assert "model.embed_tokens.weight" in hf and any("q_proj" in k for k in hf)
+    if cfg.num_experts:
+        assert any(".mlp.experts.0.gate_proj.weight" in k for k in hf) and any("mlp.gate.weight" in k for k in hf)
+    _, m2 = _model(name, seed=2)
+    convert.load_named_into_model(m2, hf.items(), cfg, m2.ps)
+    a, _ = _fwd(m)
+    b, _ = _fwd(m2)
+    torch.testing.assert_close(a, b)
+
+
+def test_megatron_name_and_qkv_roundtrip():
+    cfg, m = _model("tiny", seed=3)
+    ours = {n: p.detach().clone() for n, p in m.named_parameters()}
+    meg = convert.ours_to_megatron(ours, cfg)
+    assert "decoder.layers.0.self_attention.linear_qkv.weight" in meg and "embedding.word_embeddings.weight" in meg
+    back = convert.megatron_to_ours(meg, cfg)
+    assert set(back) == set(ours)
+    for k in ours:
+        assert torch.equal(back[k], ours[k]), k
+    # Megatron interleaves per query group: [g, q_per_group + 2, d, H]
+    w = meg["decoder.layers.0.self_attention.linear_qkv.weight"]
+    g, qpg, d = cfg.num_kv_heads, cfg.num_heads // cfg.num_kv_heads, cfg.head_dim
+    v = w.view(g, qpg + 2, d, cfg.hidden_size)
+    q_ours = ours["layers.0.attn.wqkv"][: cfg.q_size].view(g, qpg, d, cfg.hidden_size)
+    assert torch.equal(v[:, :qpg], q_ours)
+
+
+def test_torch_dist_roundtrip(tmp_path):
+    from miles_b200.checkpoint import torch_dist
+
+    cfg, m = _model("tiny", seed=4)
+    meg = convert.ours_to_megatron({n: p.detach() for n, p in m.named_parameters()}, cfg)
+    d = torch_dist.save_state(meg, str(tmp_path / "ckpt"), iteration=7)
+    assert torch_dist.is_torch_dist_dir(d)
+    back = torch_dist.load_state(str(tmp_path / "ckpt"))
+    assert set(back) == set(meg)
+    for k in meg:
+        assert torch.equal(back[k], meg[k])
+
+
+def test_hf_safetensors_io(tmp_path):
+    from miles_b200.checkpoint import hf_io
+
+    t = {"a.weight": torch.randn(4, 6).bfloat16(), "b": torch.arange(5, dtype=torch.int32), "c": torch.randn(3)}
+    p = str(tmp_path / "x.safetensors")
+    hf_io.save_safetensors(p, t, {"format": "pt"})
+    back = hf_io.load_safetensors(p)
+    assert all(torch.equal(back[k], t[k]) and back[k].dtype == t[k].dtype for k in t)
+    assert list(hf_io.load_safetensors(p, ["b"])) == ["b"]
+
+
+def _lora_args(**kw):
+    base = dict(lora_rank=4, lora_alpha=8.0, lora_dropout=0.0, lora_target_modules=["wqkv", "wo", "w13", "w2"], lora_num_slots=1,
+                lora_adapter_path=None, seed=0)
+    base.update(kw)
+    return SimpleNamespace(**base)
+
+
+def test_lora_zero_init_grads_merge_and_export(tmp_path):
+    from miles_b200.train import lora
+
+    cfg, m = _model("tiny", seed=5)
+    base_out, _ = _fwd(m)
+    ads = lora.apply_lora(m, _lora_args())
+    assert len(ads) == 4 * cfg.num_layers
+    out0, _ = _fwd(m)
+    torch.testing.assert_close(out0, base_out)                      # B = 0 → identity
+    trainable = [n for n, p in m.named_parameters() if p.requires_grad]
+    assert trainable and all(".lora." in n for n in trainable)
+    with torch.no_grad():
+        for ad in ads:
+            ad.b.normal_(0, 0.05)
+    out1, _ = _fwd(m)
+    assert (out1 - base_out).abs().max() > 1e-4
+    out1.float().pow(2).sum().backward()
+    assert all(p.grad is not None and torch.isfinite(p.grad).all() for n, p in m.named_parameters() if p.requires_grad)
+    # merged weights reproduce the adapter forward with the adapters switched off, and are restored afterwards
+    w_before = m.layers[0].attn.wqkv.detach().clone()
+    with lora.merged(m):
+        saved = {id(mod): mod.lora for _, _, mod in lora._targets(m)}
+        for _, _, mod in lora._targets(m):
+            mod.lora = None
+        out_m, _ = _fwd(m)
+        for _, _, mod in lora._targets(m):
+            mod.lora = saved[id(mod)]
+    torch.testing.assert_close(out_m, out1, atol=1e-5, rtol=1e-4)
+    assert torch.equal(m.layers[0].attn.wqkv, w_before)
+    # PEFT export: B of q/k/v are the row blocks of the fused B
+    d = lora.export_peft(m, str(tmp_path / "peft"))
+    from miles_b200.checkpoint import hf_io
+    t = hf_io.load_safetensors(os.path.join(d, "adapter_model.safetensors"))
+    bq = t["base_model.model.model.layers.0.self_attn.q_proj.lora_B.weight"]
+    assert bq.shape == (cfg.q_size, 4)
+    torch.testing.assert_close(bq, m.layers[0].attn.lora["wqkv"].b[0][: cfg.q_size].float())
+    # own-format save/load
+    lora.save_adapter(m, str(tmp_path / "ad"))
+    with torch.no_grad():
+        for ad in ads:
+            ad.b.zero_()
+    lora.load_adapter(m, str(tmp_path / "ad"))
+    out2, _ = _fwd(m)
+    torch.testing.assert_close(out2, out1)
+
+
+def test_lora_slots_route_tokens_and_slot_optimizer():
+    from miles_b200.train import lora
+
+    cfg, m = _model("tiny", seed=6)
+    base_out, _ = _fwd(m, T=16)
+    ads = lora.apply_lora(m, _lora_args(lora_num_slots=3))
+    with torch.no_grad():
+        for ad in ads:
+            ad.b[1].normal_(0, 0.05)                                # only slot 1 differs from the base model
+    T = 16
+    toks = torch.randint(0, cfg.vocab_size, (T,), generator=torch.Generator().manual_seed(0), dtype=torch.int32)
+
+    def run(slots):
+        meta = ForwardMeta(positions=torch.arange(T, dtype=torch.int32), cu_seqlens=torch.tensor([0, 8, 16], dtype=torch.int32),
+                           max_seqlen=8, lora_slots=slots)
+        return m(toks, meta)
+
+    s = torch.tensor([0] * 8 + [1] * 8)
+    out = run(s)
+    torch.testing.assert_close(out[:8], base_out[:8] * 0 + run(torch.zeros(T, dtype=torch.long))[:8])
+    assert (out[8:] - run(torch.zeros(T, dtype=torch.long))[8:]).abs().max() > 1e-5
+    # per-slot optimizer touches its own slot only
+    opt = lora.SlotOptimizer(m)
+    out.float().pow(2).sum().backward()
+    before = [p.detach().clone() for _, p in opt.params]
+    opt.step(slot=1, lr=1e-2)
+    for (n, p), b in zip(opt.params, before):
+        assert torch.equal(p[0], b[0]) and torch.equal(p[2], b[2])
+    assert any(not torch.equal(p[1], b[1]) for (n, p), b in zip(opt.params, before))
+
+
+def test_value_head_attach():
+    from miles_b200.train.critic import attach_value_head
+
+    cfg, m = _model("tiny", seed=7)
+    vh = attach_value_head(m, cfg, torch.float32, "cpu")
+    h, _ = _fwd(m)
+    v = vh(h).squeeze(-1)
+    assert v.shape == (h.shape[0],) and v.dtype == torch.float32
+    assert any("value_head" in n for n, _ in m.named_parameters())
+
+
+def test_fused_weight_sync_cpu_path_and_quant():
+    from miles_b200.parallel.weight_sync import fused_weight_sync
+
+    cfg, src = _model("tiny", seed=8)
+    _, dst = _model("tiny", seed=9)
+    actor = SimpleNamespace(model=src, args=SimpleNamespace(update_weight_buffer_size=1 << 16))
+    engine = SimpleNamespace(model=dst)
+    n = fused_weight_sync(actor, engine)
+    assert n == sum(p.numel() * p.element_size() for p in src.parameters())
+    for (a, p), (b, q) in zip(src.named_parameters(), dst.named_parameters()):
+        assert torch.equal(p, q), a
+    fused_weight_sync(actor, engine, quant="mxfp8_qdq")
+    w, wq = src.layers[0].attn.wo, dst.layers[0].attn.wo
+    assert not torch.equal(w, wq) and (w - wq).abs().max() < 0.07 * w.abs().max()
+    assert torch.equal(src.layers[0].ln1, dst.layers[0].ln1)        # norms are on the skip list
