@@ -182,6 +182,8 @@ def build_parser() -> argparse.ArgumentParser:
     _bool_flag(g, "--balance-data")
     g.add_argument("--log-probs-max-tokens-per-gpu", type=int, default=None)
     g.add_argument("--data-source-path", type=str, default="miles_b200.rollout.data_source.RolloutDataSourceWithBuffer")
+    g.add_argument("--synthetic-prompt-len", type=int, nargs=2, default=None, metavar=("MIN", "MAX"),
+                   help="prompt length range of miles_b200.rollout.data_source.SyntheticSource")
     g.add_argument("--tokenizer-path", type=str, default=None)
 
     g = p.add_argument_group("eval")

@@ -378,7 +378,8 @@ class Engine:
     @torch.no_grad()
     def step(self) -> bool:
         """One scheduling step. Returns False when there was nothing to do."""
-        with self.lock:
+        # the engine batches arbitrary token counts, so it runs tensor parallelism without sequence sharding
+        with self.lock, self.ps.no_sequence_parallel():
             if self.lockstep_group is not None:
                 return self._step_lockstep()
             if self.paused or not self.kv.allocated:

@@ -12,6 +12,8 @@ compute+collective kernels on CUDA tensors and `torch.distributed` collectives (
 """
 from __future__ import annotations
 
+import contextlib
+
 from dataclasses import dataclass, field
 from typing import Any
 
@@ -166,6 +168,16 @@ class ParallelState:
             return x
         from . import tp
         return tp.gather_sequence(x, self)
+
+    @contextlib.contextmanager
+    def no_sequence_parallel(self):
+        """Run tensor-parallel layers with replicated activations (all-reduce instead of reduce-scatter/all-gather)."""
+        old = self.sequence_parallel
+        self.sequence_parallel = False
+        try:
+            yield self
+        finally:
+            self.sequence_parallel = old
 
     def sp_scatter(self, x):
         if self.tp_size == 1 or not self.sequence_parallel:

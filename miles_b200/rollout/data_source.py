@@ -239,3 +239,14 @@ class SyntheticPromptSource(RolloutDataSourceWithBuffer):
             self.sample_group_index += 1
             out.append(group)
         return out
+
+
+class SyntheticSource(SyntheticPromptSource):
+    """`--data-source-path miles_b200.rollout.data_source.SyntheticSource`: random prompts sized from the model config
+    and `--synthetic-prompt-len MIN MAX` (default 16 32); for smoke runs, tests and benchmarks without a dataset."""
+
+    def __init__(self, args, tokenizer=None):
+        from ..args import model_config_from_args
+
+        lo, hi = (getattr(args, "synthetic_prompt_len", None) or (16, 32))
+        super().__init__(args, model_config_from_args(args).vocab_size, int(lo), int(hi), seed=getattr(args, "seed", 0))

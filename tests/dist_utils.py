@@ -15,8 +15,10 @@ def _free_port() -> int:
 def _entry(rank, world, port, fn, args, errq):
     os.environ.update(RANK=str(rank), WORLD_SIZE=str(world), LOCAL_RANK=str(rank), MASTER_ADDR="127.0.0.1",
                       MASTER_PORT=str(port))
+    import torch
     import torch.distributed as dist
 
+    torch.set_num_threads(2)   # ranks share the host's cores; oversubscription makes tiny ops crawl
     try:
         dist.init_process_group("gloo", rank=rank, world_size=world)
         fn(rank, world, *args)
