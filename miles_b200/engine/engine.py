@@ -578,11 +578,10 @@ class Engine:
         temp = torch.tensor([r.sampling.temperature for r in reqs], dtype=torch.float32, device=dev)
         top_p = torch.tensor([r.sampling.top_p for r in reqs], dtype=torch.float32, device=dev)
         top_k = torch.tensor([r.sampling.top_k for r in reqs], dtype=torch.int64, device=dev)
-        seeds = torch.tensor([r.seed for r in reqs], dtype=torch.int64, device=dev)
-        gen = None
-        if dev.type == "cpu":
-            gen = torch.Generator().manual_seed((self.seed * 7919 + self._step_count) % (2 ** 31))
-        tok, lp = sample(logits.float(), temp, top_p, top_k, generator=gen, seeds=seeds, step=self._step_count)
+        # the random stream of a request depends on its seed and its own token count only, never on what else is batched
+        seeds = torch.tensor([(r.seed * 1000003 + len(r.output_ids)) & 0x7FFFFFFFFFFFFFFF for r in reqs], dtype=torch.int64,
+                             device=dev)
+        tok, lp = sample(logits.float(), temp, top_p, top_k, seeds=seeds, step=0)
         tok_l, lp_l = tok.tolist(), lp.tolist()
         for r, t, l in zip(reqs, tok_l, lp_l):
             self._append_token(r, int(t), float(l))

@@ -33,6 +33,20 @@ class SamplingParams:
         return SamplingParams(**known)
 
 
+def _draw(probs: torch.Tensor, generator, seeds, step: int) -> torch.Tensor:
+    """One categorical draw per row.  With per-row `seeds` (and no shared generator) each row inverts its CDF at a
+    uniform number that depends on (seed, step) alone, so a request samples the same tokens whatever it is batched with."""
+    if generator is not None or seeds is None:
+        return torch.multinomial(probs, 1, generator=generator).squeeze(1)
+    u = torch.empty(probs.shape[0], dtype=torch.float64)
+    for i, s in enumerate(seeds.tolist()):
+        u[i] = torch.rand(1, generator=torch.Generator().manual_seed((int(s) * 2654435761 + step) % (2 ** 63 - 1)),
+                          dtype=torch.float64)
+    cdf = probs.double().cumsum(-1)
+    u = (u.to(probs.device) * cdf[:, -1]).unsqueeze(1)
+    return torch.searchsorted(cdf, u).squeeze(1).clamp_(max=probs.shape[1] - 1)
+
+
 def sample(logits: torch.Tensor, temperature: torch.Tensor, top_p: torch.Tensor | None = None,
            top_k: torch.Tensor | None = None, generator: torch.Generator | None = None,
            seeds: torch.Tensor | None = None, step: int = 0):
@@ -59,9 +73,9 @@ def sample(logits: torch.Tensor, temperature: torch.Tensor, top_p: torch.Tensor 
             keep &= torch.arange(V, device=logits.device)[None, :] < k[:, None]
         sp = sp * keep
         sp = sp / sp.sum(-1, keepdim=True)
-        pick = torch.multinomial(sp, 1, generator=generator).squeeze(1)
+        pick = _draw(sp, generator, seeds, step)
         tok = si.gather(1, pick[:, None]).squeeze(1)
     else:
-        tok = torch.multinomial(probs, 1, generator=generator).squeeze(1)
+        tok = _draw(probs, generator, seeds, step)
     tok = torch.where(greedy, logits.argmax(-1), tok)
     return tok, logp.gather(1, tok[:, None]).squeeze(1)

@@ -21,11 +21,11 @@ import time
 from typing import Any
 
 import torch
+from fastapi import FastAPI, Request   # module level: postponed annotations are resolved in module scope
+from fastapi.responses import JSONResponse, PlainTextResponse
 
 
 def build_app(engine, tokenizer=None):
-    from fastapi import FastAPI, Request
-    from fastapi.responses import JSONResponse, PlainTextResponse
 
     app = FastAPI(title="miles_b200 engine")
     state = {"updating": False, "profile": None, "started": time.time()}

@@ -47,11 +47,10 @@ def normalize_math(s: str) -> str:
     s = s.rstrip(".").replace("\\%", "").replace("%", "")
     if s.endswith("^\\circ") or s.endswith("^{\\circ}"):
         s = s[: s.rfind("^")]
-    m = re.fullmatch(r"\\frac\{(-?\d+)\}\{(-?\d+)\}", s)
-    if m and int(m.group(2)) != 0:
-        num, den = int(m.group(1)), int(m.group(2))
-        if num % den == 0:
-            s = str(num // den)
+    m = re.fullmatch(r"(-?)\\frac\{(-?\d+)\}\{(-?\d+)\}", s) or re.fullmatch(r"(-?)(\d+)/(\d+)", s)
+    if m and int(m.group(3)) != 0:
+        num, den = int(m.group(2)) * (-1 if m.group(1) else 1), int(m.group(3))
+        s = str(num // den) if num % den == 0 else repr(num / den)
     try:
         f = float(s.replace(",", ""))
         if f == int(f):

@@ -18,6 +18,8 @@ import random
 import time
 import zlib
 
+from fastapi import FastAPI, Request, Response   # module level: postponed annotations are resolved in module scope
+
 
 class _PyCore:
     def __init__(self):
@@ -163,8 +165,6 @@ class Router:
 
 
 def build_app(router: Router):
-    from fastapi import FastAPI, Request, Response
-
     app = FastAPI(title="miles_b200 router")
 
     @app.on_event("startup")

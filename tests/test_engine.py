@@ -1,0 +1,160 @@
+"""Rollout engine on CPU: paged-KV decode equals a full forward, continuous batching, retraction, pause/abort,
+weight updates and the HTTP surface."""
+import threading
+import time
+
+import pytest
+import torch
+
+from miles_b200.engine.engine import Engine
+from miles_b200.engine.kv_cache import BlockAllocator
+from miles_b200.models.config import PRESETS
+from miles_b200.models.qwen3 import ForwardMeta
+
+
+def _engine(name="tiny", **kw):
+    kw.setdefault("num_blocks", 64)
+    kw.setdefault("block_size", 4)
+    return Engine(PRESETS[name], device="cpu", dtype=torch.float32, seed=0, **kw)
+
+
+def _full_forward_logprobs(engine, ids):
+    T = len(ids)
+    meta = ForwardMeta(positions=torch.arange(T, dtype=torch.int32), cu_seqlens=torch.tensor([0, T], dtype=torch.int32), max_seqlen=T)
+    h = engine.model(torch.tensor(ids, dtype=torch.int32), meta)
+    return torch.log_softmax(engine.model.logits(h).float(), -1)
+
+
+@pytest.mark.parametrize("name", ["tiny", "tiny-moe"])
+def test_greedy_decode_matches_full_forward(name):
+    eng = _engine(name)
+    prompt = [5, 9, 13, 21, 34, 55, 89]
+    out = eng.generate(prompt, {"temperature": 0.0, "max_new_tokens": 9})
+    ids = out["output_ids"]
+    assert len(ids) == 9 and out["meta_info"]["finish_reason"]["type"] == "length"
+    lp = _full_forward_logprobs(eng, prompt + ids)
+    for i, t in enumerate(ids):
+        row = lp[len(prompt) + i - 1]
+        assert int(row.argmax()) == t
+        assert abs(float(row[t]) - out["meta_info"]["output_token_logprobs"][i][0]) < 1e-4
+
+
+def test_sampled_logprobs_are_the_models():
+    eng = _engine()
+    prompt = [3, 4, 5, 6]
+    out = eng.generate(prompt, {"temperature": 1.0, "max_new_tokens": 6, "seed": 7})
+    ids = out["output_ids"]
+    lp = _full_forward_logprobs(eng, prompt + ids)
+    for i, (t, (got, tid, _)) in enumerate(zip(ids, out["meta_info"]["output_token_logprobs"])):
+        assert tid == t and abs(float(lp[len(prompt) + i - 1, t]) - got) < 1e-4
+    again = eng.generate(prompt, {"temperature": 1.0, "max_new_tokens": 6, "seed": 7})
+    assert again["output_ids"] == ids                                   # per-request seed → reproducible
+
+
+def test_continuous_batching_equals_one_by_one():
+    eng = _engine()
+    prompts = [[7, 8, 9], [11, 12, 13, 14, 15, 16], [20], [30, 31, 32, 33]]
+    sp = {"temperature": 0.0, "max_new_tokens": 7}
+    solo = [eng.generate(p, sp)["output_ids"] for p in prompts]
+    batch = [o["output_ids"] for o in eng.generate(prompts, sp)]
+    assert solo == batch
+    assert eng.allocator.num_free == 64                                 # every block returned
+
+
+def test_stop_tokens_and_eos():
+    eng = _engine()
+    free_run = eng.generate([5, 6, 7], {"temperature": 0.0, "max_new_tokens": 8})["output_ids"]
+    stop = free_run[3]
+    out = eng.generate([5, 6, 7], {"temperature": 0.0, "max_new_tokens": 8, "stop_token_ids": [stop]})
+    assert out["output_ids"] == free_run[: free_run.index(stop) + 1]
+    assert out["meta_info"]["finish_reason"]["type"] == "stop"
+
+
+def test_retraction_under_block_pressure_keeps_results():
+    sp = {"temperature": 0.0, "max_new_tokens": 12}
+    prompts = [[i + 3, i + 4, i + 5, i + 6] for i in range(6)]
+    want = [o["output_ids"] for o in _engine(num_blocks=64).generate(prompts, sp)]
+    small = _engine(num_blocks=12)                                      # 48 slots for 6 × 16 tokens
+    got = [o["output_ids"] for o in small.generate(prompts, sp)]
+    assert got == want and small.stats["retractions"] > 0
+
+
+def test_pause_abort_and_weight_version_spans():
+    eng = _engine()
+    req = eng.add_request([4, 5, 6], {"temperature": 0.0, "max_new_tokens": 50})
+    for _ in range(4):
+        eng.step()
+    eng.pause_generation("retract")
+    assert not eng.running and eng.step() is False
+    eng.update_weight_version(3)
+    eng.continue_generation()
+    for _ in range(3):
+        eng.step()
+    eng.abort_request(None)
+    assert req.done.is_set()
+    r = req.to_response(eng)
+    assert r["meta_info"]["finish_reason"]["type"] == "abort" and len(r["output_ids"]) > 0
+    versions = [v for v, _ in r["meta_info"]["weight_version_spans"]]
+    assert versions == sorted(versions) and versions[-1] == 3
+
+
+def test_routed_experts_returned_for_moe():
+    from miles_b200.types import decode_routed_experts
+
+    eng = _engine("tiny-moe")
+    cfg = eng.cfg
+    out = eng.generate([3, 4, 5, 6, 7], {"temperature": 0.0, "max_new_tokens": 4}, return_routed_experts=True)
+    n = 5 + 4
+    n_moe = sum(cfg.layer_is_moe(i) for i in range(cfg.num_layers))
+    arr = decode_routed_experts(out["meta_info"]["routed_experts"], n, n_moe, cfg.moe_topk)
+    assert arr.shape == (n - 1, n_moe, cfg.moe_topk) and arr.max() < cfg.num_experts and arr.min() >= 0
+
+
+def test_update_weights_from_tensor_changes_outputs():
+    a, b = _engine(), Engine(PRESETS["tiny"], device="cpu", dtype=torch.float32, seed=1, num_blocks=64, block_size=4)
+    sp = {"temperature": 0.0, "max_new_tokens": 6}
+    assert a.generate([9, 8, 7], sp)["output_ids"] != b.generate([9, 8, 7], sp)["output_ids"]
+    b.update_weights_from_tensor([(n, p.detach()) for n, p in a.model.named_parameters()], weight_version=5)
+    assert a.generate([9, 8, 7], sp)["output_ids"] == b.generate([9, 8, 7], sp)["output_ids"]
+    assert b.get_weight_version() == 5
+
+
+def test_block_allocator_refcounts():
+    al = BlockAllocator(8)
+    a = al.alloc(3)
+    assert al.num_free == 5 and al.alloc(6) is None
+    al.share(a)
+    al.release(a)
+    assert al.num_free == 5
+    al.release(a)
+    assert al.num_free == 8
+
+
+def test_http_server_and_router_roundtrip():
+    import requests
+
+    from miles_b200.engine.server import serve
+    from miles_b200.router.router import Router, serve as serve_router
+
+    eng = _engine()
+    srv, _ = serve(eng, port=31731, in_thread=True)
+    router = Router()
+    router.add_worker("http://127.0.0.1:31731")
+    rsrv, _ = serve_router(router, port=31732, in_thread=True)
+    try:
+        body = {"input_ids": [5, 6, 7], "sampling_params": {"temperature": 0.0, "max_new_tokens": 5}, "return_logprob": True}
+        direct = requests.post("http://127.0.0.1:31731/generate", json=body, timeout=60).json()
+        routed = requests.post("http://127.0.0.1:31732/generate", json=body, timeout=60).json()
+        assert direct["output_ids"] == routed["output_ids"] and len(direct["output_ids"]) == 5
+        assert len(routed["meta_info"]["output_token_logprobs"]) == 5
+        assert requests.get("http://127.0.0.1:31732/list_workers", timeout=10).json()["urls"] == ["http://127.0.0.1:31731"]
+        assert requests.get("http://127.0.0.1:31731/health", timeout=10).status_code == 200
+        requests.post("http://127.0.0.1:31731/update_weight_version", json={"weight_version": 9}, timeout=10)
+        assert requests.get("http://127.0.0.1:31731/get_weight_version", timeout=10).json()["weight_version"] == "9"
+        router.remove_worker("http://127.0.0.1:31731")
+        assert requests.post("http://127.0.0.1:31732/generate", json=body, timeout=10).status_code == 503
+    finally:
+        srv.should_exit = True
+        rsrv.should_exit = True
+        eng._stop_loop = True
+        time.sleep(0.1)
