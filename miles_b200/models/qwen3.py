@@ -101,10 +101,12 @@ class Attention(nn.Module):
         T = qkv.shape[0]
         q, k, v = qkv.split([self.hq * self.d, self.hkv * self.d, self.hkv * self.d], dim=-1)
         q, k, v = q.view(T, self.hq, self.d), k.view(T, self.hkv, self.d), v.view(T, self.hkv, self.d)
-        q, k = ops.qk_norm_rope(q, k, self.q_norm, self.k_norm, meta.positions, cfg.rope_theta, cfg.rms_eps)
         if meta.kv_cache is not None:
             kc, vc = meta.kv_cache[layer]
-            ops.kv_cache_write(k, v, kc, vc, meta.slot_mapping)
+            q, k = ops.qk_norm_rope_cache(q, k, v, self.q_norm, self.k_norm, meta.positions, cfg.rope_theta, cfg.rms_eps,
+                                          kc, vc, meta.slot_mapping)
+        else:
+            q, k = ops.qk_norm_rope(q, k, self.q_norm, self.k_norm, meta.positions, cfg.rope_theta, cfg.rms_eps)
         if meta.cu_seqlens is not None:
             # training, or an engine prefill that starts from an empty cache: attend within the new tokens
             o = ops.attention_varlen(q, k, v, meta.cu_seqlens, meta.max_seqlen)
@@ -163,7 +165,7 @@ class MoEFFN(nn.Module):
 
     def forward(self, x, meta: ForwardMeta, layer: int):
         # with sequence parallelism each TP rank routes its own token slice (expert-TP is 1)
-        logits = ops.linear(x, self.router).float()
+        logits = ops.linear_fp32(x, self.router)      # router scores stay fp32 (no bf16 rounding, no cast kernel)
         k, norm = self.cfg.moe_topk, self.cfg.moe_norm_topk_prob
         if meta.replay_topk is not None:
             # R3: recorded indices replace top-k, weights come from the current scores so the gate

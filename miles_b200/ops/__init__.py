@@ -96,6 +96,15 @@ def qk_norm_rope(q, k, q_w, k_w, positions, theta, eps=1e-6):
     return ref.rope(q, positions, theta), ref.rope(k, positions, theta)
 
 
+def qk_norm_rope_cache(q, k, v, q_w, k_w, positions, theta, eps, k_cache, v_cache, slot_mapping):
+    """`qk_norm_rope` followed by `kv_cache_write` of (rotated k, v); one kernel on the GPU inference path."""
+    if q.is_cuda:
+        return _k().qk_norm_rope_cache(q, k, v, q_w, k_w, positions, theta, eps, k_cache, v_cache, slot_mapping)
+    q, k = qk_norm_rope(q, k, q_w, k_w, positions, theta, eps)
+    kv_cache_write(k, v, k_cache, v_cache, slot_mapping)
+    return q, k
+
+
 def rope(x, positions, theta, inverse=False):
     if x.is_cuda:
         return _k().rope(x, positions, theta, inverse)

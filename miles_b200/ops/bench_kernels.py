@@ -96,7 +96,7 @@ def bench_attention(a):
     bwd = timeit(lambda: torch.autograd.grad(o, (q, k, v), g, retain_graph=True), a.iters)
     f_fwd = 4.0 * B * Hq * L * L * D / 2
     return [{"kernel": "flash_fwd", "batch": B, "seqlen": L, "ms": fwd, "tflops": f_fwd / fwd / 1e9, "roofline_frac": f_fwd / (tf * 1e12) * 1e3 / fwd,
-             "roofline": tag},
+             "roofline": tag, "ctas_per_sm": K.C.flash_fwd_tc_ctas_per_sm()},
             {"kernel": "flash_bwd", "batch": B, "seqlen": L, "ms": bwd, "tflops": 2.5 * f_fwd / bwd / 1e9,
              "roofline_frac": 2.5 * f_fwd / (tf * 1e12) * 1e3 / bwd, "roofline": tag}]
 

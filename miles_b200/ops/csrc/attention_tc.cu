@@ -296,6 +296,15 @@ flash_fwd_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
 
 using namespace mb;
 
+// resident CTAs per SM of the forward kernel at its launch configuration (diagnostic; 2 is the design point)
+extern "C" int mb_flash_fwd_tc_ctas_per_sm() {
+  int n = 0;
+  (void)cudaFuncSetAttribute(fa::flash_fwd_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, fa::Smem::total);
+  (void)cudaFuncSetAttribute(fa::flash_fwd_tc_kernel, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared);
+  if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&n, fa::flash_fwd_tc_kernel, 192, fa::Smem::total) != cudaSuccess) return -1;
+  return n;
+}
+
 // q [T, Hq, 128] (token stride q_stride elements), k/v [T, Hkv, 128]; o [T, Hq, 128] contiguous; lse [Hq, T].
 extern "C" int mb_flash_fwd_tc(const void* q, const void* k, const void* v, void* o, float* lse, const int* cu_seqlens, int batch,
                                int max_seqlen, int total_tokens, long long q_stride, long long k_stride, long long v_stride, int Hq,
@@ -311,6 +320,9 @@ extern "C" int mb_flash_fwd_tc(const void* q, const void* k, const void* v, void
   static bool once = false;
   if (!once) {
     cudaError_t e = cudaFuncSetAttribute(fa::flash_fwd_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, fa::Smem::total);
+    if (e != cudaSuccess) return static_cast<int>(e);
+    // two CTAs per SM need 2 × 113.25 KB: ask for the largest shared-memory carve-out
+    e = cudaFuncSetAttribute(fa::flash_fwd_tc_kernel, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared);
     if (e != cudaSuccess) return static_cast<int>(e);
     once = true;
   }

@@ -44,6 +44,15 @@ void gemm(const at::Tensor& A, const at::Tensor& B, at::Tensor& C, int64_t M, in
         "mb_gemm_bf16");
 }
 
+void gemm_splitk(const at::Tensor& A, const at::Tensor& B, at::Tensor& C, int64_t M, int64_t N, int64_t K, int64_t ldc,
+                 bool accumulate, const c10::optional<at::Tensor>& bias, int64_t split_k, at::Tensor& ws, at::Tensor& counters) {
+  c10::cuda::CUDAGuard g(A.device());
+  int* ef = error_flag_for(A.device()).data_ptr<int>();
+  check(mb_gemm_bf16_splitk(A.data_ptr(), B.data_ptr(), C.data_ptr(), M, N, K, K, K, ldc, C.scalar_type() == at::kFloat, accumulate,
+                            cptr(bias), split_k, ws.data_ptr<float>(), counters.data_ptr<int>(), ef, cur_stream()),
+        "mb_gemm_bf16_splitk");
+}
+
 void gemm_grouped(const at::Tensor& A, const at::Tensor& B, at::Tensor& C, int64_t M_pad, int64_t N, int64_t K, int64_t E,
                   const at::Tensor& tile_expert, bool b_mn, int64_t force_bn) {
   c10::cuda::CUDAGuard g(A.device());
@@ -112,6 +121,17 @@ void qk_norm_rope_fwd(const at::Tensor& q, const at::Tensor& k, const c10::optio
         "mb_qk_norm_rope_fwd");
 }
 
+void qk_norm_rope_cache(const at::Tensor& q, const at::Tensor& k, const at::Tensor& v, const c10::optional<at::Tensor>& qw,
+                        const c10::optional<at::Tensor>& kw, const at::Tensor& positions, at::Tensor& qo, at::Tensor& ko,
+                        at::Tensor& kc, at::Tensor& vc, const at::Tensor& slots, double theta, double eps) {
+  c10::cuda::CUDAGuard g(q.device());
+  const int64_t T = q.size(0), Hq = q.size(1), Hk = k.size(1), D = q.size(2);
+  check(mb_qk_norm_rope_cache(q.data_ptr(), k.data_ptr(), v.data_ptr(), q.stride(0), k.stride(0), v.stride(0), cptr(qw), cptr(kw),
+                              positions.data_ptr<int>(), qo.data_ptr(), ko.data_ptr(), kc.data_ptr(), vc.data_ptr(),
+                              reinterpret_cast<const long long*>(slots.data_ptr<int64_t>()), T, Hq, Hk, D, theta, eps, cur_stream()),
+        "mb_qk_norm_rope_cache");
+}
+
 // returns dw (bf16 [D]) or an undefined tensor when w is absent
 at::Tensor qk_norm_rope_bwd(const at::Tensor& x, const c10::optional<at::Tensor>& w, const c10::optional<at::Tensor>& rstd,
                             const at::Tensor& dy, const at::Tensor& positions, at::Tensor& dx, double theta) {
@@ -164,6 +184,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("launch_count", []() { return static_cast<int64_t>(mb_launch_count()); });
   m.def("count_launches", [](int64_t n) { mb_count_launch(static_cast<int>(n)); });
   m.def("gemm", &gemm);
+  m.def("gemm_splitk", &gemm_splitk);
   m.def("gemm_grouped", &gemm_grouped);
   m.def("gemm_grouped_wgrad", &gemm_grouped_wgrad);
   m.def("rmsnorm_fwd", &rmsnorm_fwd);
@@ -172,6 +193,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("swiglu_bwd", &swiglu_bwd);
   m.def("qk_norm_rope_fwd", &qk_norm_rope_fwd);
   m.def("qk_norm_rope_bwd", &qk_norm_rope_bwd);
+  m.def("qk_norm_rope_cache", &qk_norm_rope_cache);
   m.def("kv_cache_write", &kv_cache_write);
   m.def("adamw", &adamw);
   register_more(m);

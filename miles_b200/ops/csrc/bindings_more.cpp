@@ -96,6 +96,7 @@ void register_more(pybind11::module& m) {
   m.def("install_crash_handler", &install_crash_handler);
   m.def("flash_fwd", &flash_fwd);
   m.def("flash_fwd_tc", &flash_fwd_tc);
+  m.def("flash_fwd_tc_ctas_per_sm", []() { return mb_flash_fwd_tc_ctas_per_sm(); });
   m.def("flash_bwd", &flash_bwd);
   m.def("paged_decode", &paged_decode);
   register_moe(m);

@@ -247,7 +247,7 @@ __global__ void __launch_bounds__(256) swiglu_bwd_kernel(const __nv_bfloat16* __
 template <int D>
 __device__ __forceinline__ void norm_rope_row(const __nv_bfloat16* __restrict__ src, __nv_bfloat16* __restrict__ dst,
                                               const __nv_bfloat16* __restrict__ w, float pos, float log2_theta, float eps,
-                                              float* rstd_out, int lane) {
+                                              float* rstd_out, int lane, __nv_bfloat16* __restrict__ dst2 = nullptr) {
   constexpr int EPL = D / 64;  // elements per lane in each half
   float a[EPL], b[EPL];
   float ss = 0.f;
@@ -274,8 +274,50 @@ __device__ __forceinline__ void norm_rope_row(const __nv_bfloat16* __restrict__ 
     const float inv_freq = exp2f(-log2_theta * (2.f * j) / D);
     float s, c;
     sincosf(pos * inv_freq, &s, &c);
-    dst[j] = __float2bfloat16(x1 * c - x2 * s);
-    dst[D / 2 + j] = __float2bfloat16(x2 * c + x1 * s);
+    const __nv_bfloat16 o1 = __float2bfloat16(x1 * c - x2 * s), o2 = __float2bfloat16(x2 * c + x1 * s);
+    dst[j] = o1;
+    dst[D / 2 + j] = o2;
+    if (dst2 != nullptr) {
+      dst2[j] = o1;
+      dst2[D / 2 + j] = o2;
+    }
+  }
+}
+
+// Engine form: the same per-head norm + rotary for q and k, with the rotated k and the raw v also written into the
+// paged KV cache at each token's slot (slot < 0: token not cached).  One warp per (token, q/k/v head).
+template <int D>
+__global__ void __launch_bounds__(256) qk_norm_rope_cache_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __restrict__ k,
+                                                                 const __nv_bfloat16* __restrict__ v, long long q_tok_stride,
+                                                                 long long k_tok_stride, long long v_tok_stride,
+                                                                 const __nv_bfloat16* __restrict__ qw, const __nv_bfloat16* __restrict__ kw,
+                                                                 const int* __restrict__ positions, __nv_bfloat16* __restrict__ qo,
+                                                                 __nv_bfloat16* __restrict__ ko, __nv_bfloat16* __restrict__ kc,
+                                                                 __nv_bfloat16* __restrict__ vc, const long long* __restrict__ slots,
+                                                                 long long T, int Hq, int Hk, float log2_theta, float eps) {
+  const int lane = threadIdx.x & 31;
+  const long long wid = (blockIdx.x * 256ll + threadIdx.x) >> 5;
+  const int heads = Hq + 2 * Hk;
+  if (wid >= T * heads) return;
+  const long long t = wid / heads;
+  const int h = static_cast<int>(wid % heads);
+  if (h < Hq) {
+    norm_rope_row<D>(q + t * q_tok_stride + h * D, qo + (t * Hq + h) * D, qw, static_cast<float>(positions[t]), log2_theta, eps,
+                     nullptr, lane);
+    return;
+  }
+  const long long slot = slots[t];
+  if (h < Hq + Hk) {
+    const int hk = h - Hq;
+    norm_rope_row<D>(k + t * k_tok_stride + hk * D, ko + (t * Hk + hk) * D, kw, static_cast<float>(positions[t]), log2_theta, eps,
+                     nullptr, lane, slot >= 0 ? kc + (slot * Hk + hk) * D : nullptr);
+  } else if (slot >= 0) {
+    const int hk = h - Hq - Hk;
+    constexpr int EPL = D / 32;   // 4 (8 bytes) or 2 (4 bytes) elements per lane
+    const __nv_bfloat16* src = v + t * v_tok_stride + hk * D + lane * EPL;
+    __nv_bfloat16* dst = vc + (slot * Hk + hk) * D + lane * EPL;
+    if (EPL == 4) *reinterpret_cast<uint2*>(dst) = *reinterpret_cast<const uint2*>(src);
+    else *reinterpret_cast<uint32_t*>(dst) = *reinterpret_cast<const uint32_t*>(src);
   }
 }
 
@@ -544,6 +586,27 @@ extern "C" int mb_qk_norm_rope_fwd(const void* q, const void* k, long long q_str
     qk_norm_rope_fwd_kernel<128><<<blocks, 256, 0, s>>>(Q, K, q_stride, k_stride, QW, KW, positions, QO, KO, q_rstd, k_rstd, T, Hq, Hk, l2t, eps);
   else if (D == 64)
     qk_norm_rope_fwd_kernel<64><<<blocks, 256, 0, s>>>(Q, K, q_stride, k_stride, QW, KW, positions, QO, KO, q_rstd, k_rstd, T, Hq, Hk, l2t, eps);
+  else
+    return -1;
+  return static_cast<int>(cudaGetLastError());
+}
+
+// Engine (no autograd) form: q/k norm + rotary, and k/v written to the paged cache [slots, Hk, D] in the same launch.
+extern "C" int mb_qk_norm_rope_cache(const void* q, const void* k, const void* v, long long q_stride, long long k_stride,
+                                     long long v_stride, const void* qw, const void* kw, const int* positions, void* qo, void* ko,
+                                     void* kc, void* vc, const long long* slots, long long T, int Hq, int Hk, int D, float theta,
+                                     float eps, cudaStream_t s) {
+  if (T == 0) return 0;
+  const int blocks = static_cast<int>((T * (Hq + 2 * Hk) + 7) / 8);
+  const float l2t = log2f(theta);
+  typedef const __nv_bfloat16* cbf;
+  typedef __nv_bfloat16* bf;
+  if (D == 128)
+    qk_norm_rope_cache_kernel<128><<<blocks, 256, 0, s>>>((cbf)q, (cbf)k, (cbf)v, q_stride, k_stride, v_stride, (cbf)qw, (cbf)kw, positions,
+                                                          (bf)qo, (bf)ko, (bf)kc, (bf)vc, slots, T, Hq, Hk, l2t, eps);
+  else if (D == 64)
+    qk_norm_rope_cache_kernel<64><<<blocks, 256, 0, s>>>((cbf)q, (cbf)k, (cbf)v, q_stride, k_stride, v_stride, (cbf)qw, (cbf)kw, positions,
+                                                         (bf)qo, (bf)ko, (bf)kc, (bf)vc, slots, T, Hq, Hk, l2t, eps);
   else
     return -1;
   return static_cast<int>(cudaGetLastError());

@@ -38,6 +38,12 @@ struct GemmParams {
   int num_groups;
   int b_group_rows;        // grouped fwd: rows of B per expert (N for K-major B, K for MN-major B)
   int* error_flag;
+  // split-K (dense, few output tiles): `split_k` CTAs share one output tile, each writing the partial sums of its K slice
+  // to its own fp32 plane of `ws` [split_k, M, N]; the last to arrive (counter per tile and 32-row quadrant) adds the
+  // planes in slice order, writes C and resets the counter
+  int split_k;
+  float* ws;
+  int* counters;
 };
 
 template <int BN>
@@ -73,7 +79,10 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
   const int m_tiles = (p.M + BM - 1) / BM;
   const int n_tiles = (p.N + BN - 1) / BN;
   const int tiles_per_group = m_tiles * n_tiles;
-  const int total_tiles = (MODE == kGroupedWgrad) ? tiles_per_group * p.num_groups : tiles_per_group;
+  const int split_k = (MODE == kDense && p.split_k > 1) ? p.split_k : 1;
+  // "group" = expert (grouped wgrad) or K slice (dense split-K): both index the outer tile dimension
+  const int total_tiles = (MODE == kGroupedWgrad) ? tiles_per_group * p.num_groups : tiles_per_group * split_k;
+  constexpr bool kOuter = (MODE == kGroupedWgrad || MODE == kDense);
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < kStages; ++s) { mbar_init(&full_bar[s], 1); mbar_init(&empty_bar[s], 1); }
@@ -97,8 +106,11 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
       k0 = p.seg_offsets[group];
       k_blocks = (p.seg_offsets[group + 1] - k0) / BK;
     } else {
-      k0 = 0;
-      k_blocks = (p.K + BK - 1) / BK;
+      const int total_kb = (p.K + BK - 1) / BK;
+      const int per = (total_kb + split_k - 1) / split_k;
+      const int lo = group * per;                       // group = K slice (0 without split-K)
+      k0 = lo * BK;
+      k_blocks = max(0, min(per, total_kb - lo));
     }
   };
 
@@ -108,8 +120,8 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
       int stage = 0;
       uint32_t phase = 0;
       for (int t = blockIdx.x; t < total_tiles && !*abort_flag; t += gridDim.x) {
-        const int group = (MODE == kGroupedWgrad) ? t / tiles_per_group : 0;
-        const int tt = (MODE == kGroupedWgrad) ? t % tiles_per_group : t;
+        const int group = kOuter ? t / tiles_per_group : 0;
+        const int tt = kOuter ? t % tiles_per_group : t;
         const int m_blk = tt % m_tiles, n_blk = tt / m_tiles;
         int b_row_off = 0;
         if (MODE == kGroupedFwd) {
@@ -152,8 +164,8 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
       int acc = 0;
       uint32_t acc_phase = 0;
       for (int t = blockIdx.x; t < total_tiles && !*abort_flag; t += gridDim.x) {
-        const int group = (MODE == kGroupedWgrad) ? t / tiles_per_group : 0;
-        const int tt = (MODE == kGroupedWgrad) ? t % tiles_per_group : t;
+        const int group = kOuter ? t / tiles_per_group : 0;
+        const int tt = kOuter ? t % tiles_per_group : t;
         const int m_blk = tt % m_tiles;
         if (MODE == kGroupedFwd && p.tile_expert[m_blk] < 0) continue;
         int k0, k_blocks;
@@ -192,8 +204,8 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
     int acc = 0;
     uint32_t acc_phase = 0;
     for (int t = blockIdx.x; t < total_tiles && !*abort_flag; t += gridDim.x) {
-      const int group = (MODE == kGroupedWgrad) ? t / tiles_per_group : 0;
-      const int tt = (MODE == kGroupedWgrad) ? t % tiles_per_group : t;
+      const int group = kOuter ? t / tiles_per_group : 0;
+      const int tt = kOuter ? t % tiles_per_group : t;
       const int m_blk = tt % m_tiles, n_blk = tt / m_tiles;
       if (MODE == kGroupedFwd && p.tile_expert[m_blk] < 0) continue;
       int k0, k_blocks;
@@ -202,6 +214,104 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
       tc_fence_after();
       const int row = m_blk * BM + q * 32 + lane;
       const uint32_t t_row = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + acc * BN;
+      if (MODE == kDense && split_k > 1) {
+        // ---- split-K: add this slice's partial sums to the workspace; the last slice to arrive finishes the tile ----
+        // ws holds one [M, N] fp32 plane per K slice: plain vector stores, no atomics
+        float* wrow = p.ws + (static_cast<long long>(group) * p.M + row) * p.N;
+#pragma unroll 1
+        for (int c = 0; c < BN / 32; ++c) {
+          uint32_t r[32];
+          tmem_ld_32x32(t_row + c * 32, r);
+          tmem_ld_wait();
+          const int col0 = n_blk * BN + c * 32;
+          if (row < p.M && col0 < p.N) {
+            if (k_blocks == 0) {
+#pragma unroll
+              for (int i = 0; i < 32; ++i) r[i] = 0u;
+            }
+            if (col0 + 32 <= p.N && (p.N & 3) == 0) {
+#pragma unroll
+              for (int i = 0; i < 32; i += 4)
+                __stcg(reinterpret_cast<float4*>(wrow + col0 + i),
+                       make_float4(__uint_as_float(r[i]), __uint_as_float(r[i + 1]), __uint_as_float(r[i + 2]),
+                                   __uint_as_float(r[i + 3])));
+            } else {
+              for (int i = 0; i < 32 && col0 + i < p.N; ++i) __stcg(wrow + col0 + i, __uint_as_float(r[i]));
+            }
+          }
+        }
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&tmem_empty[acc]);
+        if (++acc == 2) { acc = 0; acc_phase ^= 1; }
+        // one counter per (tile, 32-row quadrant): the rows a warp reduced are finished by the last warp to arrive for
+        // that quadrant, so no CTA-wide barrier is needed (and none can be left waiting on an error path)
+        __threadfence();
+        __syncwarp();
+        int last = 0;
+        if (lane == 0) last = (atomicAdd(&p.counters[tt * 4 + q], 1) == split_k - 1) ? 1 : 0;
+        last = __shfl_sync(0xffffffffu, last, 0);
+        if (last) {
+          __threadfence();
+          const int row_lo = m_blk * BM + q * 32;
+          const int col_hi = min(p.N, (n_blk + 1) * BN);
+          const long long plane_sz = static_cast<long long>(p.M) * p.N;
+          if (BN == 64 && ((p.N | p.ldc) & 3) == 0 && (n_blk + 1) * BN <= p.N && p.bias == nullptr && !p.accumulate) {
+            // fast path: 16 lanes × float4 cover the 64 columns of a row, two rows per instruction, 4 row pairs and
+            // 4 planes in flight at once (the loop is latency-bound otherwise)
+            const int half = lane >> 4, c = n_blk * BN + (lane & 15) * 4;
+#pragma unroll 1
+            for (int i0 = 0; i0 < 16 && row_lo + 2 * i0 < p.M; i0 += 4) {
+              float4 acc[4];
+#pragma unroll
+              for (int j = 0; j < 4; ++j) acc[j] = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll 4
+              for (int s = 0; s < split_k; ++s) {
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                  const int rr = row_lo + 2 * (i0 + j) + half;
+                  if (rr < p.M) {
+                    const float4 v = __ldcg(reinterpret_cast<const float4*>(p.ws + s * plane_sz + static_cast<long long>(rr) * p.N + c));
+                    acc[j].x += v.x; acc[j].y += v.y; acc[j].z += v.z; acc[j].w += v.w;
+                  }
+                }
+              }
+#pragma unroll
+              for (int j = 0; j < 4; ++j) {
+                const int rr = row_lo + 2 * (i0 + j) + half;
+                if (rr >= p.M) continue;
+                if (p.out_fp32) {
+                  *reinterpret_cast<float4*>(reinterpret_cast<float*>(p.C) + static_cast<long long>(rr) * p.ldc + c) = acc[j];
+                } else {
+                  uint2 o;
+                  o.x = pack_bf16x2(acc[j].x, acc[j].y);
+                  o.y = pack_bf16x2(acc[j].z, acc[j].w);
+                  *reinterpret_cast<uint2*>(reinterpret_cast<__nv_bfloat16*>(p.C) + static_cast<long long>(rr) * p.ldc + c) = o;
+                }
+              }
+            }
+          } else
+          for (int rr = row_lo; rr < min(p.M, row_lo + 32); ++rr) {      // lanes sweep the columns of one row: coalesced
+            const float* w = p.ws + static_cast<long long>(rr) * p.N;
+            const long long plane = static_cast<long long>(p.M) * p.N;
+            uint8_t* c_row = reinterpret_cast<uint8_t*>(p.C) + static_cast<long long>(rr) * p.ldc * (p.out_fp32 ? 4 : 2);
+            for (int col = n_blk * BN + lane; col < col_hi; col += 32) {
+              float v = 0.f;
+              for (int s = 0; s < split_k; ++s) v += __ldcg(w + s * plane + col);   // fixed order: deterministic
+              if (p.bias != nullptr) v += __bfloat162float(p.bias[col]);
+              if (p.out_fp32) {
+                float* d = reinterpret_cast<float*>(c_row) + col;
+                *d = p.accumulate ? *d + v : v;
+              } else {
+                reinterpret_cast<__nv_bfloat16*>(c_row)[col] = __float2bfloat16(v);
+              }
+            }
+          }
+          __syncwarp();
+          if (lane == 0) p.counters[tt * 4 + q] = 0;
+        }
+        continue;
+      }
       uint8_t* c_base = reinterpret_cast<uint8_t*>(p.C) +
                         (static_cast<long long>(group) * p.group_stride_c + static_cast<long long>(row) * p.ldc) *
                             (p.out_fp32 ? 4 : 2);
@@ -384,6 +494,29 @@ extern "C" int mb_gemm_bf16(const void* A, const void* B, void* C, int M, int N,
   if (!a_mn && b_mn) return launch_bn<0, 1, kDense>(bn, ta, tb, p, tiles, stream);
   if (a_mn && b_mn) return launch_bn<1, 1, kDense>(bn, ta, tb, p, tiles, stream);
   return launch_bn<1, 0, kDense>(bn, ta, tb, p, tiles, stream);
+}
+
+// Split-K form of C[M,N] = A[M,K]·B[N,K]ᵀ for decode-sized problems (few output tiles, long K): `split_k` CTAs per
+// 128×64 tile each stream a K slice, so a GEMM with 32 output tiles still pulls weights with 128 SMs.
+// ws: fp32 [split_k, M, N] workspace (contents irrelevant), counters: int [4 · tiles], zero on entry and zero again on exit.
+extern "C" int mb_gemm_bf16_splitk(const void* A, const void* B, void* C, int M, int N, int K, long long lda, long long ldb,
+                                   long long ldc, int out_fp32, int accumulate, const void* bias, int split_k, float* ws,
+                                   int* counters, int* error_flag, cudaStream_t stream) {
+  if (M <= 0 || N <= 0) return 0;
+  if (split_k < 1 || ws == nullptr || counters == nullptr) return -1;
+  CUtensorMap ta, tb;
+  int r = make_tmap_bf16_2d(&ta, A, M, K, lda, BM, BK);
+  if (r) return 1000 + r;
+  r = make_tmap_bf16_2d(&tb, B, N, K, ldb, 64, BK);
+  if (r) return 2000 + r;
+  GemmParams p{};
+  p.M = M; p.N = N; p.K = K; p.C = C; p.ldc = ldc; p.out_fp32 = out_fp32; p.accumulate = accumulate;
+  p.bias = reinterpret_cast<const __nv_bfloat16*>(bias);
+  p.error_flag = error_flag;
+  p.num_groups = 1;
+  p.split_k = split_k; p.ws = ws; p.counters = counters;
+  const int tiles = ((M + BM - 1) / BM) * ((N + 63) / 64) * split_k;
+  return launch_one<64, 0, 0, kDense>(ta, tb, p, tiles, stream);
 }
 
 // Grouped forward / dgrad: A [M_pad, K] expert-sorted rows (each expert's segment padded to 128 rows),

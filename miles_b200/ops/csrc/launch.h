@@ -15,6 +15,9 @@ long long mb_launch_count();
 int mb_gemm_bf16(const void* A, const void* B, void* C, int M, int N, int K, long long lda, long long ldb, long long ldc,
                  int a_mn, int b_mn, int out_fp32, int accumulate, const void* bias, int force_bn, int* error_flag,
                  cudaStream_t stream);
+int mb_gemm_bf16_splitk(const void* A, const void* B, void* C, int M, int N, int K, long long lda, long long ldb, long long ldc,
+                        int out_fp32, int accumulate, const void* bias, int split_k, float* ws, int* counters, int* error_flag,
+                        cudaStream_t stream);
 int mb_gemm_bf16_grouped(const void* A, const void* B, void* C, int M_pad, int N, int K, int num_experts,
                          const int* tile_expert, int b_mn, int out_fp32, int force_bn, int* error_flag, cudaStream_t stream);
 int mb_gemm_bf16_grouped_wgrad(const void* dY, const void* X, void* dW, int M_pad, int N, int K, int num_experts,
@@ -51,6 +54,9 @@ int mb_swiglu_bwd(const void* in, const void* dout, void* din, long long T, int 
 int mb_qk_norm_rope_fwd(const void* q, const void* k, long long q_stride, long long k_stride, const void* qw, const void* kw,
                         const int* positions, void* qo, void* ko, float* q_rstd, float* k_rstd, long long T, int Hq, int Hk, int D,
                         float theta, float eps, cudaStream_t s);
+int mb_qk_norm_rope_cache(const void* q, const void* k, const void* v, long long q_stride, long long k_stride, long long v_stride,
+                          const void* qw, const void* kw, const int* positions, void* qo, void* ko, void* kc, void* vc,
+                          const long long* slots, long long T, int Hq, int Hk, int D, float theta, float eps, cudaStream_t s);
 int mb_qk_norm_rope_bwd_blocks(long long T, int Hn);
 int mb_qk_norm_rope_bwd(const void* x, long long x_stride, const void* w, const float* rstd, const void* dy, const int* positions,
                         void* dx, long long dx_stride, float* dw_partial, void* dw_out, long long T, int Hn, int D, float theta,
@@ -75,6 +81,7 @@ int mb_paged_decode(const void* q, const void* kc, const void* vc, const int* bl
 int mb_flash_fwd_tc(const void* q, const void* k, const void* v, void* o, float* lse, const int* cu_seqlens, int batch, int max_seqlen,
                     int total_tokens, long long q_stride, long long k_stride, long long v_stride, int Hq, int Hkv, float scale,
                     int causal, int* error_flag, cudaStream_t s);
+int mb_flash_fwd_tc_ctas_per_sm(void);
 
 // ---- moe.cu ----
 int mb_router_topk(const float* logits, float* probs, float* topk_w, int* topk_idx, long long T, int E, int K, int normalize,

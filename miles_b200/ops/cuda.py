@@ -7,6 +7,7 @@ used for statistics, router maths, gradients-in-accumulation and optimizer state
 from __future__ import annotations
 
 import math
+import os
 
 import torch
 
@@ -48,8 +49,39 @@ def gemm_nt(a: torch.Tensor, b: torch.Tensor, out: torch.Tensor | None = None, *
     if out is None:
         out = torch.empty(M, N, dtype=out_dtype or BF16, device=a.device)
     if M and N:
-        C.gemm(a, b, out, M, N, K, K, K, out.stride(0), False, False, accumulate, bias, force_bn)
+        split = _pick_split_k(M, N, K) if not force_bn and SPLIT_K else 1
+        if split > 1:
+            ws, counters = _splitk_workspace(a.device)
+            C.gemm_splitk(a, b, out, M, N, K, out.stride(0), accumulate, bias, split, ws, counters)
+        else:
+            C.gemm(a, b, out, M, N, K, K, K, out.stride(0), False, False, accumulate, bias, force_bn)
     return out
+
+
+# Decode-sized GEMMs (a handful of 128×64 output tiles over a long K) leave most SMs idle; split-K gives every tile
+# several CTAs, each streaming a slice of the weights.  Workspace: fp32 [split, M, N] planes + arrival counters (zero
+# between calls; the kernel restores that), one per device, so such GEMMs must not overlap on two streams of one device.
+SPLIT_K = os.environ.get("MILES_SPLIT_K", "1") != "0"
+_SPLITK_MAX_M, _SPLITK_MAX_TILES = int(os.environ.get("MILES_SPLIT_K_MAX_M", "32")), 74   # measured: wins below ~32 rows
+_splitk_ws: dict = {}
+
+
+def _pick_split_k(M: int, N: int, K: int) -> int:
+    if M > _SPLITK_MAX_M or K < 1024:
+        return 1
+    tiles = ((M + 127) // 128) * ((N + 63) // 64)
+    if tiles > _SPLITK_MAX_TILES:
+        return 1
+    return max(1, min(148 // tiles, K // 512, 16))
+
+
+def _splitk_workspace(device):
+    key = device.index if device.index is not None else torch.cuda.current_device()
+    if key not in _splitk_ws:
+        # split · M · N ≤ (148 CTAs) · (128 × 64 tile) floats
+        _splitk_ws[key] = (torch.empty(148 * 128 * 64, dtype=torch.float32, device=device),
+                           torch.zeros(4 * _SPLITK_MAX_TILES * 2, dtype=torch.int32, device=device))
+    return _splitk_ws[key]
 
 
 def gemm_nn(a: torch.Tensor, b: torch.Tensor, out: torch.Tensor | None = None, *, out_dtype=None, force_bn: int = 0):
@@ -110,10 +142,30 @@ def linear(x, w, bias=None):
     return _Linear.apply(x, w, bias)
 
 
+class _LinearFP32(torch.autograd.Function):
+    """y = x·Wᵀ with the fp32 accumulator written out unrounded (router scores, sampling logits)."""
+
+    @staticmethod
+    def forward(ctx, x, w):
+        shp = x.shape
+        x2 = x.reshape(-1, shp[-1])
+        ctx.save_for_backward(x2, w)
+        ctx.shp = shp
+        return gemm_nt(x2, w, out_dtype=torch.float32).view(*shp[:-1], w.shape[0])
+
+    @staticmethod
+    def backward(ctx, gy):
+        x2, w = ctx.saved_tensors
+        gy2 = _c(gy.reshape(-1, gy.shape[-1]).to(BF16))
+        gx = gemm_nn(gy2, w).view(ctx.shp) if ctx.needs_input_grad[0] else None
+        gw = gemm_tn(gy2, x2) if ctx.needs_input_grad[1] else None
+        return gx, gw
+
+
 def linear_fp32(x, w):
     if x.dtype != BF16:
         return torch.nn.functional.linear(x, w.to(x.dtype)).float()
-    return gemm_nt(x.reshape(-1, x.shape[-1]), w, out_dtype=torch.float32).view(*x.shape[:-1], w.shape[0])
+    return _LinearFP32.apply(x, w)
 
 
 def linear_dgrad(gy, w):
@@ -233,6 +285,22 @@ def qk_norm_rope(q, k, q_w, k_w, positions, theta, eps=1e-6):
             q, k = ref.rmsnorm(q, q_w, eps), ref.rmsnorm(k, k_w, eps)
         return ref.rope(q, positions, theta), ref.rope(k, positions, theta)
     return _QKNormRope.apply(q, k, q_w, k_w, positions, float(theta), float(eps))
+
+
+def qk_norm_rope_cache(q, k, v, q_w, k_w, positions, theta, eps, k_cache, v_cache, slot_mapping):
+    """Inference form: norm + rotary on q and k and the KV-cache write of (rotated k, v) in ONE launch.  Returns (q, k)."""
+    T, Hq, D = q.shape
+    Hk = k.shape[1]
+    ok = (q.dtype == BF16 and D in (64, 128) and not torch.is_grad_enabled() and q.stride(2) == 1 and q.stride(1) == D
+          and k.stride(1) == D and v.stride(1) == D and positions.dtype == torch.int32 and slot_mapping.dtype == torch.int64)
+    if not ok:
+        q, k = qk_norm_rope(q, k, q_w, k_w, positions, theta, eps)
+        kv_cache_write(k, v, k_cache, v_cache, slot_mapping)
+        return q, k
+    qo = torch.empty(T, Hq, D, dtype=q.dtype, device=q.device)
+    ko = torch.empty(T, Hk, D, dtype=k.dtype, device=k.device)
+    C.qk_norm_rope_cache(q, k, v, q_w, k_w, positions, qo, ko, k_cache, v_cache, slot_mapping, float(theta), float(eps))
+    return qo, ko
 
 
 def rope(x, positions, theta, inverse=False):

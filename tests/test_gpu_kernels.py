@@ -162,3 +162,55 @@ def test_kv_cache_write():
     slots = torch.randperm(8 * bs, device="cuda")[:T]
     _k().kv_cache_write(k, v, kc, vc, slots)
     assert torch.equal(kc.view(-1, H, D)[slots], k) and torch.equal(vc.view(-1, H, D)[slots], v)
+
+
+@pytest.mark.parametrize("M,N,K", [(1, 2048, 4096), (64, 2048, 4096), (64, 128, 2048), (8, 4096, 2048), (200, 1000, 3072), (130, 152, 1024)])
+@pytest.mark.parametrize("fp32_out", [False, True])
+def test_gemm_split_k(M, N, K, fp32_out, monkeypatch):
+    """Decode-sized GEMMs go through the split-K path; results match, and the arrival counters are left zero."""
+    K_ = _k()
+    monkeypatch.setattr(K_, "_SPLITK_MAX_M", 256)           # the dispatch default only splits very small M
+    assert K_._pick_split_k(M, N, K) > 1
+    torch.manual_seed(1)
+    a = torch.randn(M, K, device="cuda", dtype=torch.bfloat16)
+    b = torch.randn(N, K, device="cuda", dtype=torch.bfloat16)
+    bias = torch.randn(N, device="cuda", dtype=torch.bfloat16)
+    want = a.float() @ b.float().t() + bias.float()
+    for _ in range(3):                                       # back to back: each call must find a clean workspace
+        out = K_.gemm_nt(a, b, bias=bias, out_dtype=torch.float32 if fp32_out else None)
+        torch.cuda.synchronize()
+        _flag_ok()
+        assert _rel(out, want) < (2e-3 if fp32_out else 1e-2), _rel(out, want)
+    nob = K_.gemm_nt(a, b, out_dtype=torch.float32 if fp32_out else None)          # vectorised reduction path
+    assert _rel(nob, want - bias.float()) < (2e-3 if fp32_out else 1e-2)
+    ws, counters = K_._splitk_workspace(a.device)
+    assert int(counters.abs().max()) == 0
+    plain = K_.gemm_nt(a, b, bias=bias, out_dtype=torch.float32, force_bn=64)     # force_bn bypasses split-K
+    assert _rel(out.float(), plain) < 1e-2
+
+
+@pytest.mark.parametrize("D", [64, 128])
+@pytest.mark.parametrize("norm", [True, False])
+def test_qk_norm_rope_cache_matches_separate_ops(D, norm):
+    K_ = _k()
+    torch.manual_seed(2)
+    T, Hq, Hk, bs, nb = 37, 8, 2, 16, 12
+    qkv = torch.randn(T, (Hq + 2 * Hk) * D, device="cuda", dtype=torch.bfloat16)
+    q, k, v = qkv.split([Hq * D, Hk * D, Hk * D], dim=-1)
+    q, k, v = q.view(T, Hq, D), k.view(T, Hk, D), v.view(T, Hk, D)
+    qw = (1 + 0.1 * torch.randn(D, device="cuda")).bfloat16() if norm else None
+    kw = (1 + 0.1 * torch.randn(D, device="cuda")).bfloat16() if norm else None
+    pos = torch.randint(0, 4000, (T,), device="cuda", dtype=torch.int32)
+    slots = torch.randperm(bs * nb, device="cuda")[:T].to(torch.int64)
+    slots[5] = -1                                             # a token that is not cached
+    kc0 = torch.randn(nb, bs, Hk, D, device="cuda", dtype=torch.bfloat16)
+    vc0 = torch.randn(nb, bs, Hk, D, device="cuda", dtype=torch.bfloat16)
+    with torch.no_grad():
+        q1, k1 = K_.qk_norm_rope(q, k, qw, kw, pos, 1e6, 1e-6)
+        kc1, vc1 = kc0.clone(), vc0.clone()
+        K_.kv_cache_write(k1, v, kc1, vc1, slots)
+        kc2, vc2 = kc0.clone(), vc0.clone()
+        q2, k2 = K_.qk_norm_rope_cache(q, k, v, qw, kw, pos, 1e6, 1e-6, kc2, vc2, slots)
+    torch.cuda.synchronize()
+    assert torch.equal(q1, q2) and torch.equal(k1, k2)
+    assert torch.equal(kc1, kc2) and torch.equal(vc1, vc2)

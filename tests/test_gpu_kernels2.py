@@ -170,3 +170,49 @@ def test_quant_kernels_match_reference():
     y = _k().nvfp4_qdq(x)
     yr = ref.nvfp4_qdq(x)
     assert _rel(y, yr) < 2e-2, _rel(y, yr)
+
+
+def test_fused_weight_sync_kernels():
+    """One launch per bucket: byte copy (odd sizes, unaligned tail) and MXFP8 quantise / quantise-dequantise on the way."""
+    from types import SimpleNamespace
+
+    from miles_b200.parallel.weight_sync import fused_weight_sync
+
+    class M(torch.nn.Module):
+        def __init__(self, seed):
+            super().__init__()
+            g = torch.Generator(device="cuda").manual_seed(seed)
+            mk = lambda *s, dt=torch.bfloat16: torch.nn.Parameter(torch.randn(*s, device="cuda", generator=g).to(dt))
+            self.ln1 = mk(257)                               # 514 bytes: not a multiple of 16
+            self.wqkv = mk(384, 256)
+            self.w2 = mk(3, 128, 96)                         # stacked experts
+            self.head_bias = mk(1001, dt=torch.float32)
+            self.w_small = mk(5, 7)
+
+    src, dst = M(1), M(2)
+    actor = SimpleNamespace(model=src, args=SimpleNamespace(update_weight_buffer_size=64 << 10))
+    engine = SimpleNamespace(model=dst)
+    n = fused_weight_sync(actor, engine)
+    assert n == sum(p.numel() * p.element_size() for p in src.parameters())
+    for (name, p), (_, q) in zip(src.named_parameters(), dst.named_parameters()):
+        assert torch.equal(p, q), name
+    # quantise → dequantise on the way: 2-D+ weights whose rows are multiples of 32 change, the rest are copied
+    dst2 = M(3)
+    fused_weight_sync(actor, SimpleNamespace(model=dst2), quant="mxfp8_qdq")
+    for name in ("wqkv", "w2"):
+        p = getattr(src, name).detach()
+        qd, sc = ref.mxfp8_quant(p)
+        want = ref.mxfp8_dequant(qd, sc).reshape(p.shape).bfloat16()
+        assert torch.equal(getattr(dst2, name).detach(), want), name
+    assert torch.equal(dst2.ln1, src.ln1) and torch.equal(dst2.w_small, src.w_small)
+    # payload + scales form
+    eng3 = SimpleNamespace(model=M(4), quant_buffers={
+        n_: (torch.empty(p.numel(), dtype=torch.uint8, device="cuda"), torch.empty(p.numel() // 32, dtype=torch.uint8, device="cuda"))
+        for n_, p in src.named_parameters() if n_ in ("wqkv", "w2")})
+    fused_weight_sync(actor, eng3, quant="mxfp8")
+    for name in ("wqkv", "w2"):
+        p = getattr(src, name).detach()
+        qd, sc = ref.mxfp8_quant(p)
+        payload, scales = eng3.quant_buffers[name]
+        assert torch.equal(payload.view(torch.float8_e4m3fn).float().view(-1), qd.float().view(-1)), name
+        assert torch.equal(scales.view(-1), sc.view(-1)), name
