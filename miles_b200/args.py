@@ -157,6 +157,10 @@ def build_parser() -> argparse.ArgumentParser:
     g.add_argument("--update-weights-interval", type=int, default=1)
     _bool_flag(g, "--fully-async")
     g.add_argument("--max-weight-staleness", type=int, default=1)
+    g.add_argument("--staleness-policy", choices=["drop", "retry", "keep"], default="drop")
+    g.add_argument("--fully-async-buffer-groups", type=int, default=None,
+                   help="finished prompt groups the producer keeps ready (default: one rollout batch)")
+    g.add_argument("--fully-async-take-timeout", type=float, default=None)
     g.add_argument("--rollout-engine", choices=["native", "http", "mock"], default="native")
     g.add_argument("--router-policy", choices=["least_active", "round_robin", "consistent_hashing", "random"], default="least_active")
     _bool_flag(g, "--use-miles-router", default=True)

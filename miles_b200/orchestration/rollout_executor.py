@@ -138,3 +138,9 @@ class RolloutExecutor:
 
     def set_weight_version(self, v: int):
         self.weight_version = v
+        if hasattr(self.rollout_fn, "set_weight_version"):      # staleness accounting of the fully-async producer
+            self.rollout_fn.set_weight_version(v)
+
+    def shutdown(self):
+        if hasattr(self.rollout_fn, "stop"):
+            self.rollout_fn.stop()

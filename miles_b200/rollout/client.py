@@ -56,7 +56,10 @@ class InProcEngineClient:
             else:
                 idle = 0 if busy else idle + 1
                 if idle >= 3:
-                    break
+                    if not self._pending:
+                        break
+                    # requests are waiting but the engine is paused (a weight update in progress): poll, do not spin
+                    await asyncio.sleep(0.001)
             await asyncio.sleep(0)  # let finished requests' awaiters run and new ones enqueue
 
     async def begin(self):

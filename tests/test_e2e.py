@@ -116,3 +116,59 @@ def test_grpo_two_ranks(tmp_path, extra):
     assert max(r["train/train_rollout_logprob_abs_diff"] for r in rows) < 1e-5
     assert abs(rows[0]["train/ppo_kl"]) < 1e-6
     assert all(r["train/grad_norm"] > 0 for r in rows)
+
+
+# ---- asynchronous loops --------------------------------------------------------------------------------------------
+
+ASYNC_BASE = BASE.replace("--colocate ", "")
+
+
+def _run_async(extra=""):
+    import train_async as TA
+    from miles_b200.args import parse_args
+
+    return TA.train(parse_args((ASYNC_BASE + " " + extra).split())).history
+
+
+def test_async_one_step_ahead():
+    h = _run_async("--num-rollout 3")
+    assert len(h.rows) == 3
+    # batch 0 is on-policy; later batches were sampled one optimizer step behind the weights that score them
+    diffs = h.series("train/train_rollout_logprob_abs_diff")
+    assert diffs[0] < 1e-5 and 1e-5 < max(diffs[1:]) < 0.1
+    assert all(g > 0 for g in h.series("train/grad_norm"))
+
+
+def test_fully_async_staleness_bounded():
+    h = _run_async("--num-rollout 4 --fully-async --max-weight-staleness 2 --use-tis")
+    assert len(h.rows) == 4
+    assert max(h.series("rollout/staleness/max")) <= 2
+    assert all(g > 0 for g in h.series("train/grad_norm"))
+
+
+def test_async_rejects_colocate():
+    import train_async as TA
+    from miles_b200.args import parse_args
+
+    with pytest.raises(AssertionError):
+        TA.train(parse_args(BASE.split()))
+
+
+def test_staleness_buffer_policies():
+    from miles_b200.rollout.fully_async import StalenessBuffer, SubmissionScheduler
+    from miles_b200.types import Sample, WeightVersionSpan
+
+    def grp(v):
+        return [Sample(tokens=[1, 2], weight_versions=[WeightVersionSpan(v, 1)])]
+
+    b = StalenessBuffer(max_staleness=1, policy="retry")
+    for v in (0, 1, 2, 3):
+        b.put(grp(v))
+    got = b.take(2, current_version=3, timeout=1)
+    assert [g[0].oldest_weight_version for g in got] == [2, 3]
+    assert b.stats["dropped_stale"] == 2 and len(b.pop_retries()) == 2
+    with pytest.raises(TimeoutError):
+        b.take(1, current_version=3, timeout=0.05)
+    s = SubmissionScheduler(batch=8, max_inflight=12, target_buffered=8)
+    assert s.allowance(inflight=0, buffered=0) == 12 and s.allowance(inflight=4, buffered=8) == 4
+    assert s.allowance(inflight=12, buffered=0) == 0
