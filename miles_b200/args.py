@@ -234,6 +234,12 @@ def build_parser() -> argparse.ArgumentParser:
     g.add_argument("--log-probs-chunk-size", type=int, default=-1)
     _bool_flag(g, "--skip-actor-forward-only")
     g.add_argument("--opd-kl-coef", type=float, default=0.0)
+    g.add_argument("--opd-teacher-url", type=str, default=None)
+    g.add_argument("--opd-task-rm-type", type=str, default=None)
+    g.add_argument("--multi-turn-env-path", type=str, default=None)
+    g.add_argument("--max-turns", type=int, default=8)
+    g.add_argument("--max-tokens-per-turn", type=int, default=None)
+    g.add_argument("--tools-path", type=str, default=None)
     g.add_argument("--num-critic-only-steps", type=int, default=0)
     g.add_argument("--critic-lr", type=float, default=None)
     g.add_argument("--ref-update-interval", type=int, default=None)

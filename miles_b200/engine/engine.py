@@ -56,6 +56,8 @@ class Request:
     stop_set: frozenset = frozenset()
     row: Any = None                # row in the decode runner's static buffers
     bt_len: int = 0
+    logprob_start_len: int = -1    # ≥ 0: also return log-probs of the input tokens from this position on (scoring)
+    input_logprobs: list[float] | None = None
 
     @property
     def all_ids(self) -> list[int]:
@@ -77,6 +79,12 @@ class Request:
         }
         if self.return_logprob:
             meta["output_token_logprobs"] = [(lp, t, None) for lp, t in zip(self.output_logprobs, self.output_ids)]
+        if self.input_logprobs is not None:
+            start = max(self.logprob_start_len, 0)
+            # entry i scores input token start+i given everything before it; token 0 has no context (None)
+            toks = self.input_ids[start:]
+            lps = ([None] if start == 0 else []) + list(self.input_logprobs)
+            meta["input_token_logprobs"] = [(lp, t, None) for lp, t in zip(lps, toks)]
         if self.return_routed_experts and self.routed:
             arr = np.concatenate(self.routed, axis=0)
             n = len(self.input_ids) + len(self.output_ids) - 1
@@ -148,14 +156,14 @@ class Engine:
     # ---------------------------------------------------------------------------------------
     def add_request(self, input_ids: list[int], sampling_params: dict | SamplingParams | None = None,
                     return_logprob: bool = True, return_routed_experts: bool = False, rid: str | None = None,
-                    on_done=None) -> Request:
+                    on_done=None, logprob_start_len: int = -1) -> Request:
         sp = sampling_params if isinstance(sampling_params, SamplingParams) else SamplingParams.from_dict(sampling_params)
         with self.lock:
             rid = rid or f"req-{next(self._rid)}"
             req = Request(rid=rid, input_ids=list(input_ids), sampling=sp, return_logprob=return_logprob,
                           return_routed_experts=return_routed_experts and self.cfg.is_moe,
                           seed=(sp.seed if sp.seed is not None else (self.seed * 1000003 + zlib.crc32(rid.encode())) % (2 ** 31)),
-                          on_done=on_done)
+                          on_done=on_done, logprob_start_len=int(logprob_start_len))
             budget = self.max_context_len - len(input_ids)
             if budget <= 0 or sp.max_new_tokens <= 0:
                 req.finish_reason = {"type": "length", "length": 0}
@@ -505,6 +513,15 @@ class Engine:
         last = torch.tensor([c - 1 for c in cu[1:]], dtype=torch.int64, device=dev)
         logits = self.model.logits(hidden[last])
         self.stats["prefill_tokens"] += len(toks)
+        for r, a, b in zip(batch, cu[:-1], cu[1:]):
+            if r.logprob_start_len >= 0 and r.input_logprobs is None and r.retractions == 0:
+                # score the prompt: row p predicts token p+1 (temperature 1, the teacher / reference distribution)
+                n_in = len(r.input_ids)
+                lo = max(r.logprob_start_len - 1, 0)
+                rows = torch.arange(a + lo, a + n_in - 1, device=dev)
+                tgt = torch.tensor(r.input_ids[lo + 1:n_in], dtype=torch.int64, device=dev)
+                lp, _ = self.model.log_probs(hidden[rows], tgt) if len(tgt) else (torch.empty(0), None)
+                r.input_logprobs = [float(x) for x in lp.float().tolist()]
         if record is not None:
             rec = torch.stack(record, dim=1).cpu().numpy().astype(np.int32)  # [T, L_moe, k]
             for r, a, b in zip(batch, cu[:-1], cu[1:]):

@@ -96,7 +96,8 @@ class InProcEngineClient:
         self._pending.add(fut)
         try:
             eng.add_request(payload["input_ids"], payload.get("sampling_params"), payload.get("return_logprob", True),
-                            payload.get("return_routed_experts", False), on_done=on_done)
+                            payload.get("return_routed_experts", False), on_done=on_done,
+                            logprob_start_len=payload.get("logprob_start_len", -1))
             await self.start()
             req = await fut
         finally:

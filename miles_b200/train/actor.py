@@ -220,7 +220,9 @@ class TrainActor:
             val_flat = torch.cat([torch.as_tensor(v, device=dev, dtype=torch.float32) for v in values]) if values is not None else None
             adv, ret = compute_advantages_and_returns(
                 args, rewards=torch.tensor(shard["rewards"], device=dev), response_lengths=resp, loss_mask=lm_flat,
-                log_probs=lp_flat, ref_log_probs=ref_flat, values=val_flat, dp_group=dp_group)
+                log_probs=lp_flat, ref_log_probs=ref_flat, values=val_flat, dp_group=dp_group,
+                teacher_log_probs=flat_per_token(shard, "teacher_log_probs", order, dev) if "teacher_log_probs" in shard else None,
+                opd_reverse_kl=flat_per_token(shard, "opd_reverse_kl", order, dev) if "opd_reverse_kl" in shard else None)
             shard["advantages"] = list(adv.split(resp))
             shard["returns"] = list(ret.split(resp))
         if getattr(args, "ci_test", False) and old_lp is not None and ref_lp is not None and rollout_id == 0 \

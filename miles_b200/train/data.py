@@ -72,6 +72,8 @@ def convert_samples_to_train_data(args, samples: list[Sample] | list[list[Sample
         data["rollout_routed_experts"] = [np.asarray(s.rollout_routed_experts, dtype=np.int32) for s in flat]
     if all(s.teacher_log_probs is not None for s in flat) and flat:
         data["teacher_log_probs"] = [list(s.teacher_log_probs) for s in flat]
+    if all(s.opd_reverse_kl is not None for s in flat) and flat:
+        data["opd_reverse_kl"] = [list(s.opd_reverse_kl) for s in flat]
     if any(s.weight_versions for s in flat):
         data["weight_versions"] = [s.oldest_weight_version for s in flat]
     # per-rollout mask sums: siblings of one rollout (same rollout_id) share a denominator
@@ -84,7 +86,7 @@ def convert_samples_to_train_data(args, samples: list[Sample] | list[list[Sample
 
 _PER_SAMPLE_KEYS = ("tokens", "response_lengths", "total_lengths", "rewards", "raw_reward", "truncated", "loss_masks",
                     "sample_indices", "rollout_ids", "rollout_log_probs", "rollout_routed_experts",
-                    "teacher_log_probs", "weight_versions", "rollout_mask_sums", "advantages")
+                    "teacher_log_probs", "opd_reverse_kl", "weight_versions", "rollout_mask_sums", "advantages")
 
 
 def karmarkar_karp(lengths: list[int], k: int, equal_size: bool = True) -> list[list[int]]:
