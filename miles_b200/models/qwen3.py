@@ -109,7 +109,14 @@ class Attention(nn.Module):
             q, k = ops.qk_norm_rope(q, k, self.q_norm, self.k_norm, meta.positions, cfg.rope_theta, cfg.rms_eps)
         if meta.cu_seqlens is not None:
             # training, or an engine prefill that starts from an empty cache: attend within the new tokens
-            o = ops.attention_varlen(q, k, v, meta.cu_seqlens, meta.max_seqlen)
+            if self.ps.cp_size > 1:
+                # context parallel (Ulysses): tokens are sharded in contiguous chunks; swap to a head sharding for the
+                # kernel (cu_seqlens describe the whole packed batch) and back
+                from ..parallel import cp as _cp
+                q, k, v = (_cp.seq_to_heads(t, self.ps) for t in (q, k, v))
+                o = _cp.heads_to_seq(ops.attention_varlen(q, k, v, meta.cu_seqlens, meta.max_seqlen), self.ps)
+            else:
+                o = ops.attention_varlen(q, k, v, meta.cu_seqlens, meta.max_seqlen)
         else:
             kc, vc = meta.kv_cache[layer]
             o = ops.paged_attention(q, kc, vc, meta.block_table, meta.seq_lens, q_lens=meta.q_lens,

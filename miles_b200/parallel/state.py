@@ -172,12 +172,13 @@ class ParallelState:
     @contextlib.contextmanager
     def no_sequence_parallel(self):
         """Run tensor-parallel layers with replicated activations (all-reduce instead of reduce-scatter/all-gather)."""
-        old = self.sequence_parallel
-        self.sequence_parallel = False
+        # the engine also ignores context parallelism: CP ranks serve disjoint requests like data-parallel ranks
+        old, old_cp = self.sequence_parallel, self.cp_size
+        self.sequence_parallel, self.cp_size = False, 1
         try:
             yield self
         finally:
-            self.sequence_parallel = old
+            self.sequence_parallel, self.cp_size = old, old_cp
 
     def sp_scatter(self, x):
         if self.tp_size == 1 or not self.sequence_parallel:

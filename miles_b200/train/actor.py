@@ -145,6 +145,8 @@ class TrainActor:
                            replay_topk=pb.replay_topk if replay else None, recompute=rec)
 
     def _forward_logprobs(self, pb: PackedBatch, with_entropy: bool, replay: bool):
+        if self.ps.cp_size > 1:
+            return self._forward_logprobs_cp(pb, with_entropy, replay)
         hidden = self.model(pb.tokens, self._meta(pb, replay))
         if self.role == "critic":
             h = self.ps.sp_gather(hidden)
@@ -153,6 +155,29 @@ class TrainActor:
         temp = getattr(self.args, "rollout_temperature", 1.0)
         return self.ps.vocab_parallel_logprob(h, self.model.head_weight(), pb.targets, temp, with_entropy,
                                               self.cfg.vocab_size)
+
+    def _forward_logprobs_cp(self, pb: PackedBatch, with_entropy: bool, replay: bool):
+        """Context-parallel forward: this rank runs tokens [lo, hi) of the packed batch, scores the response tokens whose
+        predicting row falls in that chunk, and the per-token results are assembled over the CP group (every rank ends
+        with the full vectors, so sequence-level losses need no further communication)."""
+        from ..parallel import cp
+
+        ps = self.ps
+        lo, hi = cp.chunk_bounds(pb.tokens.numel(), ps.cp_size, ps.cp_rank)
+        rec = getattr(self.args, "recompute_granularity", None) == "full"
+        meta = ForwardMeta(positions=pb.positions[lo:hi], cu_seqlens=pb.cu_seqlens, max_seqlen=pb.max_seqlen,
+                           replay_topk=pb.replay_topk[lo:hi] if (replay and pb.replay_topk is not None) else None, recompute=rec)
+        hidden = ps.sp_gather(self.model(pb.tokens[lo:hi], meta))
+        mine = (pb.gather_index >= lo) & (pb.gather_index < hi)
+        h = hidden[pb.gather_index[mine] - lo]
+        R = pb.gather_index.numel()
+        if self.role == "critic":
+            return cp.gather_from_cp(self.model.value_head(h.float()).squeeze(-1), mine, R, ps), None
+        temp = getattr(self.args, "rollout_temperature", 1.0)
+        lp, ent = ps.vocab_parallel_logprob(h, self.model.head_weight(), pb.targets[mine], temp, with_entropy, self.cfg.vocab_size)
+        lp = cp.gather_from_cp(lp.float(), mine, R, ps)
+        ent = cp.gather_from_cp(ent.float(), mine, R, ps) if ent is not None else None
+        return lp, ent
 
     @torch.no_grad()
     def compute_log_probs(self, shard: dict, micro_batches: list[list[int]], tag: str | None = None) -> list[list[float]]:
@@ -173,7 +198,7 @@ class TrainActor:
         return [out[i] for i in sorted(out)]
 
     def _pad_multiple(self) -> int:
-        return max(1, self.ps.tp_size) * (128 if self.device.type == "cuda" else 1)
+        return max(1, self.ps.tp_size) * max(1, self.ps.cp_size) * (128 if self.device.type == "cuda" else 1)
 
     # ---------------------------------------------------------------------------------------
     # train

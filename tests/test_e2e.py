@@ -109,6 +109,7 @@ def _dist_hist(tmp_path, extra, world=2):
     "",                                                                     # dp2
     "--tensor-model-parallel-size 2 --sequence-parallel",                   # tp2 + sp
     "--model-name tiny-moe --expert-model-parallel-size 2",                 # dp2 × ep2
+    "--context-parallel-size 2 --cp-comm-type a2a",                         # cp2 (Ulysses), dp1
 ])
 def test_grpo_two_ranks(tmp_path, extra):
     rows = _dist_hist(tmp_path, extra)
