@@ -85,7 +85,7 @@ def save_from_actor(actor, args, iteration: int, with_optimizer: bool = True):
     d = iter_dir(root, iteration)
 
     def write(directory):
-        state = {n: p.data.detach().cpu() for n, p in actor.model.named_parameters()}
+        state = {n: t.detach().cpu() for n, t in actor.named_weights()}       # model-wide names (pipeline stages too)
         meta = {"iteration": iteration, "cfg": actor.cfg.asdict(), "world_size": world,
                 "tp": actor.ps.tp_size, "pp": actor.ps.pp_size, "ep": actor.ps.ep_size,
                 "tp_rank": actor.ps.tp_rank, "pp_rank": actor.ps.pp_rank, "ep_rank": actor.ps.ep_rank,

@@ -152,7 +152,7 @@ def unshard_tp(name: str, parts: list[torch.Tensor], cfg: ModelConfig) -> torch.
 def load_named_into_model(model, named_tensors: Iterable[tuple[str, torch.Tensor]], cfg: ModelConfig, ps):
     """Copy tensors into a model. Accepts this package's names (shard or full) or HF names (full)."""
     named = list(named_tensors)
-    params = dict(model.named_parameters())
+    params = dict(model.named_parameters_global() if hasattr(model, "named_parameters_global") else model.named_parameters())
     if named and (named[0][0].startswith("model.") or named[0][0].startswith("lm_head")):
         named = list(hf_state_to_ours(dict(named), cfg).items())
     for n, t in named:

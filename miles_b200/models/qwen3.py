@@ -267,6 +267,18 @@ class Qwen3Model(nn.Module):
         h, _ = ops.add_rmsnorm(x, residual, self.norm, self.cfg.rms_eps)
         return h
 
+    def global_name(self, name: str) -> str:
+        """Parameter name with the model-wide layer index (a pipeline stage numbers its own layers from 0)."""
+        lo = self.layer_range[0]
+        if lo and name.startswith("layers."):
+            _, i, rest = name.split(".", 2)
+            return f"layers.{int(i) + lo}.{rest}"
+        return name
+
+    def named_parameters_global(self):
+        for n, p in self.named_parameters():
+            yield self.global_name(n), p
+
     def logits(self, hidden: torch.Tensor) -> torch.Tensor:
         """Full logits (engine sampling / tests). hidden [T,H] → [T,V] fp32 (TP: gathered)."""
         hidden = self.ps.sp_gather(hidden)

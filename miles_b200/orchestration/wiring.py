@@ -86,7 +86,13 @@ def create_rollout_components(args, ps: ParallelState, actor=None, tracker=None)
         dtype = next(actor.model.parameters()).dtype if actor is not None else torch.bfloat16
         share = actor is not None and getattr(args, "colocate", False) and not ek.get("own_weights", False)
         eos = ek.get("eos_token_ids") or ([tok.eos_token_id] if tok is not None and tok.eos_token_id is not None else [])
-        engine = Engine(cfg, model=actor.model if share else None, ps=ps, device=device, dtype=dtype,
+        engine_ps = ps
+        if ps.pp_size > 1:
+            # a pipeline stage holds a slice of the layers: the in-process engine then keeps a full copy of its own
+            # (every rank serves requests data-parallel) and receives weights through the HF-named tensor stream
+            assert ps.tp_size == 1 and ps.ep_size == 1, "in-process engine under PP needs tp = ep = 1; use --rollout-engine http"
+            engine_ps, share = ParallelState.single(), False
+        engine = Engine(cfg, model=actor.model if share else None, ps=engine_ps, device=device, dtype=dtype,
                         num_blocks=ek.get("num_blocks"), block_size=ek.get("block_size"),
                         mem_fraction_static=ek.get("mem_fraction_static", 0.7),
                         max_running_requests=ek.get("max_running_requests", 512),
@@ -97,12 +103,12 @@ def create_rollout_components(args, ps: ParallelState, actor=None, tracker=None)
         client = InProcEngineClient(engines, tokenizer=tok, policy=getattr(args, "router_policy", "least_active"))
     # rollout data parallelism: one engine group per (tp × ep-within-dp) block; groups take disjoint prompts
     # (ranks of one TP group replicate the same requests; EP is orthogonal: DP attention + EP experts)
-    assert ps.pp_size == 1 or kind == "http", "the in-process engine runs without pipeline parallelism"
+    # (pipeline stages each own an engine, so they count as rollout-DP ranks too)
     rollout_dp = max(1, ps.world_size // ps.tp_size)
     rollout_dp_rank = ps.rank // ps.tp_size
     ex = RolloutExecutor(args, data_source, client, ps=ps, rollout_dp_size=rollout_dp, rollout_dp_rank=rollout_dp_rank,
                          tracker=tracker)
-    ex.is_leader = ps.tp_rank == 0 and ps.pp_rank == 0
+    ex.is_leader = ps.tp_rank == 0
     # distinct prompts per rollout-DP rank: advance the data source by rank-dependent seeds
     if hasattr(data_source, "gen"):
         data_source.gen.manual_seed(args.rollout_seed * 9973 + rollout_dp_rank)

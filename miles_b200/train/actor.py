@@ -156,6 +156,33 @@ class TrainActor:
         return self.ps.vocab_parallel_logprob(h, self.model.head_weight(), pb.targets, temp, with_entropy,
                                               self.cfg.vocab_size)
 
+    def _pipe(self):
+        if getattr(self, "_pipe_stage", None) is None:
+            from ..parallel.pp import PipeStage
+
+            assert self.ps.cp_size == 1, "pipeline + context parallelism is not wired in this trainer"
+            self._pipe_stage = PipeStage(self.ps, self.cfg.hidden_size, next(self.model.parameters()).dtype, self.device)
+        return self._pipe_stage
+
+    def _forward_logprobs_pp(self, pb: PackedBatch, with_entropy: bool, replay: bool):
+        """One micro-batch through this pipeline stage.  Returns (log-probs | values, entropy, StageIO); the first two
+        are None except on the last stage."""
+        from ..parallel.pp import StageIO
+
+        stage = self._pipe()
+        grad = torch.is_grad_enabled()
+        hidden_in = stage.recv_forward(pb.tokens.numel(), requires_grad=grad)
+        hidden = self.model(pb.tokens, self._meta(pb, replay), hidden_in=hidden_in)
+        if not stage.is_last:
+            stage.send_forward(hidden)
+            return None, None, StageIO(hidden_in, hidden if grad else None)
+        h = self.ps.sp_gather(hidden)[pb.gather_index]
+        if self.role == "critic":
+            return self.model.value_head(h.float()).squeeze(-1), None, StageIO(hidden_in, None)
+        temp = getattr(self.args, "rollout_temperature", 1.0)
+        lp, ent = self.ps.vocab_parallel_logprob(h, self.model.head_weight(), pb.targets, temp, with_entropy, self.cfg.vocab_size)
+        return lp, ent, StageIO(hidden_in, None)
+
     def _forward_logprobs_cp(self, pb: PackedBatch, with_entropy: bool, replay: bool):
         """Context-parallel forward: this rank runs tokens [lo, hi) of the packed batch, scores the response tokens whose
         predicting row falls in that chunk, and the per-token results are assembled over the CP group (every rank ends
@@ -190,9 +217,19 @@ class TrainActor:
         self.model.eval()
         for idx in micro_batches:
             pb = pack_micro_batch(shard, idx, self.device, pad_multiple=self._pad_multiple(), with_replay=replay)
-            lp, _ = self._forward_logprobs(pb, False, replay)
+            if self.ps.pp_size > 1:
+                from ..parallel.pp import broadcast_from_last_stage
+
+                lp, _, _io = self._forward_logprobs_pp(pb, False, replay)
+                if lp is None:
+                    lp = torch.zeros(pb.gather_index.numel(), device=self.device)
+                lp = broadcast_from_last_stage(lp.float().contiguous(), self.ps)     # every stage keeps the same record
+            else:
+                lp, _ = self._forward_logprobs(pb, False, replay)
             for i, piece in zip(idx, lp.float().split(pb.response_lengths)):
                 out[i] = piece
+        if self.ps.pp_size > 1:
+            self._pipe().finish()
         if tag is not None and tag != "actor":
             self.backuper.restore("actor")
         return [out[i] for i in sorted(out)]
@@ -288,9 +325,17 @@ class TrainActor:
         sums: dict[str, torch.Tensor] = {}
         count_sum = torch.zeros((), device=dev)
         want_entropy = getattr(args, "entropy_coef", 0.0) != 0 or getattr(args, "log_entropy", True)
+        pipelined: list = []          # pp > 1: (loss | None, StageIO) per micro-batch, backward runs after all forwards
         for idx in mbs:
             pb = pack_micro_batch(shard, idx, dev, pad_multiple=self._pad_multiple(), with_replay=replay)
-            out, ent = self._forward_logprobs(pb, want_entropy and self.role == "actor", replay)
+            io = None
+            if ps.pp_size > 1:
+                out, ent, io = self._forward_logprobs_pp(pb, want_entropy and self.role == "actor", replay)
+                if out is None:       # not the last stage: nothing to score here
+                    pipelined.append((None, io))
+                    continue
+            else:
+                out, ent = self._forward_logprobs(pb, want_entropy and self.role == "actor", replay)
             lb = LossBatch(
                 response_lengths=pb.response_lengths, loss_mask=pb.loss_mask, seq_ids=pb.seq_ids,
                 advantages=_cat(shard.get("advantages"), idx, dev), returns=_cat(shard.get("returns"), idx, dev),
@@ -302,14 +347,25 @@ class TrainActor:
                 if "rollout_mask_sums" in shard else None)
             if not idx:  # empty micro-batch keeps collectives aligned across DP ranks
                 loss = out.sum() * 0.0
-                loss.backward()
+                if io is not None:
+                    pipelined.append((loss, io))
+                else:
+                    loss.backward()
                 continue
             loss, m, count = loss_function(self._loss_args(), lb, out, ent, global_batch_size=gbs,
                                            global_num_tokens=gtok)
-            loss.backward()
+            if io is not None:
+                pipelined.append((loss, io))
+            else:
+                loss.backward()
             for k, v in m.items():
                 sums[k] = sums.get(k, 0) + v.detach().float()
             count_sum = count_sum + count
+        if ps.pp_size > 1:
+            stage = self._pipe()
+            for loss, io in pipelined:            # same micro-batch order on every stage
+                stage.backward(io, loss)
+            stage.finish()
         self._finalize_grads()
         lr = self.scheduler.get()
         stats = self.optimizer.step(lr)
@@ -328,6 +384,10 @@ class TrainActor:
             dist.all_reduce(vec, group=ps.dp_group)
         denom = vec[0].clamp_min(1.0)
         out_metrics = {k: (vec[1 + j] / denom).item() for j, k in enumerate(keys)}
+        if ps.pp_size > 1:                        # losses exist on the last stage only
+            box = [out_metrics]
+            dist.broadcast_object_list(box, src=ps.pp_ranks[-1], group=ps.pp_group)
+            out_metrics = box[0]
         out_metrics["grad_norm"] = stats["grad_norm"]
         out_metrics["lr-pg_0"] = lr
         return out_metrics
@@ -401,7 +461,7 @@ class TrainActor:
 
     def named_weights(self):
         """This rank's shard, named by our layout (for checkpointing and weight sync)."""
-        return [(n, p.data) for n, p in self.model.named_parameters()]
+        return [(n, p.data) for n, p in self.model.named_parameters_global()]
 
 
 def _tp_replicated(name: str) -> bool:

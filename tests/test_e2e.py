@@ -110,6 +110,7 @@ def _dist_hist(tmp_path, extra, world=2):
     "--tensor-model-parallel-size 2 --sequence-parallel",                   # tp2 + sp
     "--model-name tiny-moe --expert-model-parallel-size 2",                 # dp2 × ep2
     "--context-parallel-size 2 --cp-comm-type a2a",                         # cp2 (Ulysses), dp1
+    "--pipeline-model-parallel-size 2 --micro-batch-size 8",                # pp2, 4 micro-batches per step
 ])
 def test_grpo_two_ranks(tmp_path, extra):
     rows = _dist_hist(tmp_path, extra)
