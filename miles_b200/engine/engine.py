@@ -490,6 +490,13 @@ class Engine:
             bt[i, :len(r.blocks)] = torch.tensor(r.blocks, dtype=torch.int32)
         return bt.to(self.device)
 
+    lora_slot: int | None = None     # multi-adapter serving: adapter slot applied to the engine's forward passes (−1 = base)
+
+    def _lora_slots(self, n_tokens: int):
+        if self.lora_slot is None:
+            return None
+        return torch.full((n_tokens,), int(self.lora_slot), dtype=torch.long, device=self.device)
+
     def _run_prefill(self, batch: list[Request]):
         toks, pos, slots, cu = [], [], [], [0]
         for r in batch:
@@ -505,7 +512,7 @@ class Engine:
             cu_seqlens=torch.tensor(cu, dtype=torch.int32, device=dev),
             max_seqlen=max((len(r.all_ids) for r in batch), default=0),
             kv_cache=self.kv.layers, slot_mapping=torch.tensor(slots, dtype=torch.int64, device=dev),
-            record_topk=record)
+            record_topk=record, lora_slots=self._lora_slots(len(toks)))
         hidden = self.model(torch.tensor(toks, dtype=torch.int32, device=dev), meta)
         if not batch:
             return
@@ -551,7 +558,8 @@ class Engine:
             positions=torch.tensor(pos, dtype=torch.int32, device=dev), cu_seqlens=None, max_seqlen=1,
             kv_cache=self.kv.layers, block_table=self._block_table(reqs),
             seq_lens=torch.tensor([p + 1 for p in pos], dtype=torch.int32, device=dev),
-            slot_mapping=torch.tensor(slots, dtype=torch.int64, device=dev), record_topk=record)
+            slot_mapping=torch.tensor(slots, dtype=torch.int64, device=dev), record_topk=record,
+            lora_slots=self._lora_slots(len(toks)))
         hidden = self.model(torch.tensor(toks, dtype=torch.int32, device=dev), meta)
         if not reqs:
             return

@@ -1,0 +1,220 @@
+"""Session server (token-in-token-out chat), Tinker-style multi-LoRA service, multi-policy training, delta weight
+transfer and snapshot publishing — all on the CPU engine."""
+import asyncio
+import os
+from types import SimpleNamespace
+
+import pytest
+import torch
+
+from miles_b200.engine.engine import Engine
+from miles_b200.models.config import PRESETS
+from miles_b200.models.qwen3 import build_model
+from miles_b200.parallel.state import ParallelState
+from miles_b200.rollout.client import InProcEngineClient
+from miles_b200.session.core import SessionManager
+from miles_b200.session.tito import ByteChatTokenizer, TitoTokenizer
+
+
+def _engine(model=None):
+    return Engine(PRESETS["tiny"], model=model, device="cpu", dtype=torch.float32, seed=0, num_blocks=256, block_size=8,
+                  eos_token_ids=[257])
+
+
+def test_tito_incremental_ids_are_a_pure_append():
+    tok = ByteChatTokenizer()
+    tito = TitoTokenizer(tok)
+    msgs = [{"role": "system", "content": "be brief"}, {"role": "user", "content": "2+2?"}]
+    start = tito.start(msgs)
+    assert tok.decode(start).endswith("<|im_start|>assistant\n")
+    gen = tok("4")["input_ids"] + [257]                             # model wrote "4<|im_end|>"
+    close = tito.close_assistant_turn(gen)
+    assert tok.decode(close) == "\n"
+    assert tito.close_assistant_turn(tok("4")["input_ids"]) == tok("<|im_end|>\n")["input_ids"]
+    traj = start + gen + close
+    prev = msgs + [{"role": "assistant", "content": "4"}]
+    ext = tito.extend(prev, [{"role": "tool", "content": "ok"}])
+    full = tok(tito.render(prev + [{"role": "tool", "content": "ok"}], add_generation_prompt=True))["input_ids"]
+    assert traj + ext == full                                        # same ids as a fresh render, earlier ids untouched
+
+
+def test_session_manager_keeps_exact_trajectory_and_forks():
+    eng = _engine()
+    client = InProcEngineClient([eng])
+    mgr = SessionManager(ByteChatTokenizer(), client.generate, default_sampling={"temperature": 0.0, "max_new_tokens": 6})
+
+    async def go():
+        await client.begin()
+        s = mgr.create("ep1")
+        m1 = [{"role": "user", "content": "hi"}]
+        r1 = await mgr.chat("ep1", m1)
+        m2 = m1 + [r1["choices"][0]["message"], {"role": "user", "content": "more"}]
+        r2 = await mgr.chat("ep1", m2)
+        # a request that rewrites the first user turn forks a branch instead of corrupting the stored one
+        r3 = await mgr.chat("ep1", [{"role": "user", "content": "different"}])
+        await client.finish()
+        return s, r1, r2, r3
+
+    s, r1, r2, r3 = asyncio.run(go())
+    t = s.trajectory()
+    assert t["response_length"] == len(t["loss_mask"]) == len(t["rollout_log_probs"])
+    assert sum(t["loss_mask"]) == r1["usage"]["completion_tokens"] + r2["usage"]["completion_tokens"]
+    # masked-in positions are exactly what greedy decoding of the stored prefix yields: the engine saw these very ids
+    P = t["prompt_length"]
+    first_gen = t["tokens"][P:P + r1["usage"]["completion_tokens"]]
+    again = eng.generate(t["tokens"][:P], {"temperature": 0.0, "max_new_tokens": 6})["output_ids"]
+    assert again == first_gen
+    assert r3["session_id"] != "ep1" and mgr.get(r3["session_id"]).parent == "ep1"
+    sample = mgr.to_sample("ep1")
+    assert sample.response_length == t["response_length"] and sample.loss_mask == t["loss_mask"]
+
+
+def _lora_model(slots=3):
+    from miles_b200.train import lora
+
+    cfg = PRESETS["tiny"]
+    model = build_model(cfg, ParallelState.single(), dtype=torch.float32, device="cpu", seed=0)
+    args = SimpleNamespace(lora_rank=4, lora_alpha=8.0, lora_dropout=0.0, lora_target_modules=["wqkv", "wo", "w13", "w2"],
+                           lora_num_slots=slots, lora_adapter_path=None, seed=0, model_name="tiny")
+    lora.apply_lora(model, args)
+    return model, args
+
+
+def _datum(tokens, weights=None):
+    d = {"model_input": {"chunks": [{"tokens": tokens[:-1]}]}, "loss_fn_inputs": {"target_tokens": tokens[1:]}}
+    if weights is not None:
+        d["loss_fn_inputs"]["weights"] = weights
+    return d
+
+
+def test_tinker_service_trains_tenants_independently(tmp_path):
+    from miles_b200.tinker.service import TinkerService
+
+    model, args = _lora_model()
+    eng = _engine(model)
+    svc = TinkerService(model, args, engine=eng)
+    a, b = svc.create_model("tenant-a"), svc.create_model("tenant-b")
+    assert (a.slot, b.slot) == (0, 1) and svc.capabilities()["free_slots"] == 1
+    data = [_datum([5, 9, 13, 21, 34, 55]), _datum([7, 7, 8, 9])]
+    base = svc.forward("tenant-a", data)
+    l0 = base["metrics"]["loss:sum"]
+    for _ in range(8):
+        svc.forward_backward("tenant-a", data, "cross_entropy")
+        st = svc.optim_step("tenant-a", {"learning_rate": 5e-2})
+    assert st["metrics"]["step"] == 8 and st["metrics"]["grad_norm"] > 0
+    assert svc.forward("tenant-a", data)["metrics"]["loss:sum"] < l0 - 0.05      # tenant a learned
+    assert abs(svc.forward("tenant-b", data)["metrics"]["loss:sum"] - l0) < 1e-4  # tenant b is untouched
+    # importance-sampling loss with per-token advantages runs and produces per-datum log-probs
+    lp = base["loss_fn_outputs"][0]["logprobs"]
+    d = _datum([5, 9, 13, 21, 34, 55])
+    d["loss_fn_inputs"].update(logprobs=lp, advantages=[1.0] * len(lp))
+    out = svc.forward_backward("tenant-b", [d], "importance_sampling")
+    assert len(out["loss_fn_outputs"][0]["logprobs"]) == 5
+    # sampling uses the tenant's adapter; the base model (no tenant) differs from tenant a after training
+    sp = {"temperature": 0.0, "max_tokens": 5}
+    sa = svc.sample("tenant-a", [5, 9, 13], sp)["sequences"][0]
+    s0 = svc.sample(None, [5, 9, 13], sp)["sequences"][0]
+    assert len(sa["tokens"]) == 5 and len(s0["tokens"]) == 5
+    # save → unload → new tenant in the recycled slot starts from zero → load restores
+    svc.save_weights("tenant-a", str(tmp_path / "a"), export_peft=True)
+    assert os.path.exists(tmp_path / "a" / "peft" / "adapter_config.json")
+    la = svc.forward("tenant-a", data)["metrics"]["loss:sum"]
+    svc.unload_model("tenant-a")
+    svc.create_model("filler")                          # takes the never-used slot; tenant c gets the recycled one
+    c = svc.create_model("tenant-c")
+    assert c.slot == 0 and abs(svc.forward("tenant-c", data)["metrics"]["loss:sum"] - l0) < 1e-4
+    svc.load_weights("tenant-c", str(tmp_path / "a"))
+    assert abs(svc.forward("tenant-c", data)["metrics"]["loss:sum"] - la) < 1e-4
+    fid = svc.submit(svc.optim_step, "nobody")
+    assert svc.retrieve(fid)["status"] == "error" and svc.retrieve(fid)["status"] == "unknown"
+
+
+def test_tinker_http_roundtrip():
+    from fastapi.testclient import TestClient
+
+    from miles_b200.tinker.server import build_app
+    from miles_b200.tinker.service import TinkerService
+
+    model, args = _lora_model(2)
+    svc = TinkerService(model, args, engine=_engine(model))
+    with TestClient(build_app(svc)) as c:
+        assert c.get("/api/v1/healthz").json()["status"] == "ok"
+        mid = c.post("/api/v1/create_model", json={"lora_config": {"rank": 4}}).json()["model_id"]
+        rid = c.post("/api/v1/forward_backward", json={"model_id": mid, "forward_backward_input": {
+            "data": [_datum([3, 4, 5, 6])], "loss_fn": "cross_entropy"}}).json()["request_id"]
+        out = c.post("/api/v1/retrieve_future", json={"request_id": rid}).json()
+        assert len(out["loss_fn_outputs"][0]["logprobs"]) == 3
+        rid = c.post("/api/v1/optim_step", json={"model_id": mid, "adam_params": {"learning_rate": 1e-3}}).json()["request_id"]
+        assert c.post("/api/v1/retrieve_future", json={"request_id": rid}).json()["metrics"]["step"] == 1
+        rid = c.post("/api/v1/asample", json={"model_id": mid, "prompt": {"tokens": [3, 4]}, "sampling_params": {"max_tokens": 3}}).json()["request_id"]
+        assert len(c.post("/api/v1/retrieve_future", json={"request_id": rid}).json()["sequences"][0]["tokens"]) == 3
+        assert c.post("/api/v1/create_model", json={"lora_config": {"rank": 64}}).status_code == 409
+
+
+def test_parker_and_multi_policy(tmp_path):
+    import yaml
+
+    import train_multi_policy as TMP
+    from miles_b200.args import parse_args
+
+    async def barrier_demo():
+        p, order = TMP.Parker(3), []
+
+        async def task(i):
+            await asyncio.sleep(0.01 * i)
+            await p.park(lambda: order.append("leader"))
+            order.append(i)
+
+        await asyncio.gather(*[task(i) for i in range(3)])
+        return order, p.passes
+
+    order, passes = asyncio.run(barrier_demo())
+    assert order[0] == "leader" and sorted(order[1:]) == [0, 1, 2] and passes == 1
+    cfg = tmp_path / "policies.yaml"
+    cfg.write_text(yaml.safe_dump([{"name": "small_lr", "overrides": {"lr": 1e-5}}, {"name": "big_lr", "overrides": {"lr": 1e-3, "seed": 7}}]))
+    common = parse_args(("--model-name tiny --fp32 --rollout-batch-size 4 --n-samples-per-prompt 2 --rollout-max-response-len 6 "
+                         "--num-rollout 2 --rm-type even_fraction --colocate --data-source-path miles_b200.rollout.data_source.SyntheticSource "
+                         f"--synthetic-prompt-len 4 6 --save {tmp_path / 'ck'} --save-interval 1").split())
+    shared = asyncio.run(TMP.train_multi_policy(TMP.load_policy_args(common, str(cfg))))
+    assert sorted(shared["policies"]) == ["big_lr", "small_lr"] and shared["complete_saves"] == [0, 1]
+    assert len(shared["history"]["small_lr"]) == 2 and os.path.isdir(tmp_path / "ck" / "big_lr")
+
+
+def test_delta_writer_reader_and_snapshots(tmp_path):
+    from miles_b200.weight_update.delta import DeltaReader, DeltaWriter, SnapshotPublisher
+
+    torch.manual_seed(0)
+    w = {"a.weight": torch.randn(64, 32).bfloat16(), "b.weight": torch.randn(16).float()}
+    wr = DeltaWriter(str(tmp_path / "d"), full_every=3)
+    rd = DeltaReader(str(tmp_path / "d"))
+    infos = []
+    for v in range(1, 6):
+        w = {k: (t.float() + 1e-3 * torch.randn_like(t.float()) * (k == "a.weight")).to(t.dtype) for k, t in w.items()}
+        infos.append(wr.publish(v, w.items()))
+        if v in (2, 5):                                   # the reader skips versions and walks the chain
+            st = rd.update_to()
+            assert rd.version == v and all(torch.equal(st[k], w[k]) for k in w)
+    assert [i["full"] for i in infos] == [True, False, False, True, False]
+    assert infos[1]["stored_bytes"] < infos[0]["stored_bytes"]     # unchanged tensor + sparse XOR compress well
+    fresh = DeltaReader(str(tmp_path / "d"))
+    assert all(torch.equal(fresh.update_to(5)[k], w[k]) for k in w)
+    blob = tmp_path / "d" / "v5" / "t00000.bin"
+    blob.write_bytes(b"\x00" + blob.read_bytes()[1:])
+    with pytest.raises(Exception):
+        DeltaReader(str(tmp_path / "d")).update_to(5)
+    cfg = PRESETS["tiny"]
+    model = build_model(cfg, ParallelState.single(), dtype=torch.float32, device="cpu", seed=0)
+    from miles_b200.models.convert import to_hf
+
+    def buckets():
+        yield [x for n, p in model.named_parameters() for x in to_hf(n, p.detach(), cfg)]
+
+    pub = SnapshotPublisher(str(tmp_path / "snap"), cfg, every=2, keep=1)
+    assert pub.maybe_publish(1, buckets()) is None
+    for step in (2, 4):
+        assert pub.maybe_publish(step, buckets()).endswith(f"step_{step}")
+    assert open(tmp_path / "snap" / "latest").read() == "step_4"
+    assert sorted(x for x in os.listdir(tmp_path / "snap") if x.startswith("step_")) == ["step_4"]
+    from miles_b200.checkpoint import hf_io
+
+    assert "model.embed_tokens.weight" in hf_io.load_hf_dir(str(tmp_path / "snap" / "step_4"))
