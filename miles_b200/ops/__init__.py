@@ -181,6 +181,20 @@ def fp8_blockwise_quant(w):
     return _k().fp8_blockwise_quant(w) if w.is_cuda else ref.fp8_blockwise_quant(w)
 
 
+def mxfp8_dequant(q, scales):
+    """1×32-block MXFP8 (e4m3 payload, e8m0 scales) → bf16."""
+    from . import extra
+
+    return extra.fp8_dequant(q.reshape(-1, q.shape[-1]), scales.reshape(-1, scales.shape[-1])).reshape(q.shape)
+
+
+def fp8_blockwise_dequant(q, scale_inv):
+    """128×128-block FP8 (e4m3 payload, fp32 scale_inv) → bf16."""
+    from . import extra
+
+    return extra.fp8_dequant(q, scale_inv)
+
+
 def int4_fake_quant(x, block_m=1, block_n=32, symmetric=True):
     if x.is_cuda:
         return _k().int4_fake_quant(x, block_m, block_n, symmetric)

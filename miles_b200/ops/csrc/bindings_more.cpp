@@ -91,6 +91,7 @@ void paged_decode(const at::Tensor& q, const at::Tensor& kc, const at::Tensor& v
 void register_moe(pybind11::module& m);    // bindings_moe.cpp
 void register_misc(pybind11::module& m);   // bindings_misc.cpp
 void register_fabric(pybind11::module& m); // bindings_fabric.cpp
+void register_extra(pybind11::module& m);  // bindings_extra.cpp
 
 void register_more(pybind11::module& m) {
   m.def("install_crash_handler", &install_crash_handler);
@@ -102,4 +103,5 @@ void register_more(pybind11::module& m) {
   register_moe(m);
   register_misc(m);
   register_fabric(m);
+  register_extra(m);
 }

@@ -131,6 +131,19 @@ int mb_sum_rows(const long long* src_ptrs, int world, void* out, long long numel
 int mb_gather_rows(const long long* src_ptrs, int world, void* out, long long bytes_per_rank, cudaStream_t s);
 int mb_stats_merge(const long long* stats_ptrs, int world, long long R, float* logp, float* ent, float* lse, cudaStream_t s);
 
+// ---- extra.cu (other model families, quantisation tools) ----
+int mb_grouped_rmsnorm(const void* x, int x_fp32, const float* w, float* out, float* rstd, long long T, int n, int C, float eps,
+                       cudaStream_t s);
+int mb_short_conv(const void* x, int fp32, const float* w, const int* bos, void* y, long long T, int D, int W, cudaStream_t s);
+int mb_mhc_mix(const void* x, const void* res, const float* h_res, const float* h_post, void* out, int fp32, long long T, int n, int d,
+               cudaStream_t s);
+int mb_mhc_aggregate(const void* x, int fp32, const float* pre, float* out, long long T, int n, int d, cudaStream_t s);
+int mb_hc_combine(const void* res, const void* y, const float* h_post, void* out, int fp32, long long T, int n, int C, cudaStream_t s);
+int mb_act_quant_1x128(const void* x, void* q, void* qdq, float* scales, long long M, int N, int round_scale, cudaStream_t s);
+int mb_fp8_dequant(const void* q, const float* scale_inv, const void* e8m0, void* out, long long M, int N, cudaStream_t s);
+int mb_gather_rows_host(const void* table_dev, const long long* ids, void* out, long long n, int row_bytes, long long table_rows,
+                        cudaStream_t s);
+
 // ---- weight_sync.cu (one launch per bucket of tensors; dst may be peer memory) ----
 int mb_multi_copy(const long long* table, const long long* prefix, int n, long long total_chunks, cudaStream_t s);
 int mb_multi_mxfp8(const long long* table, const long long* prefix, int n, long long total_chunks, int qdq, cudaStream_t s);

@@ -1,0 +1,122 @@
+"""Audit trail, dashboard store / API, and the checkpoint-conversion tool chain (CPU)."""
+import json
+import os
+
+import torch
+
+from miles_b200.audit import events as A
+from miles_b200.dashboard.server import DashboardBackend, GpuSampler, SeriesStore, build_app, scrape_prometheus
+from miles_b200.models import convert as mc
+from miles_b200.models.config import PRESETS
+from miles_b200.models.qwen3 import build_model
+from miles_b200.parallel.state import ParallelState
+
+
+def test_audit_rules(tmp_path):
+    log = A.EventLogger(str(tmp_path), "trainer", 0)
+    eng = A.EventLogger(str(tmp_path), "engine", 0)
+    w = {"a": torch.ones(4), "b": torch.arange(3.0)}
+    cs = A.combined_checksum(A.model_checksums(w.items()))
+    log.log("weights_published", version=1, checksum=cs)
+    eng.log("weights_received", version=1, checksum=cs, engine="e0")
+    wit = A.DataWitness(log)
+    ids = wit.allocate(0, 6)
+    wit.consumed(0, 0, ids[:3], dp_rank=0)
+    wit.consumed(0, 0, ids[3:], dp_rank=1)
+    for r in (0, 1):
+        log.log("replica_checksum", step=0, dp_rank=r, checksum="same")
+    assert A.analyze(str(tmp_path)) == []
+    # now break each rule
+    w["a"][0] = 2
+    eng.log("weights_received", version=1, checksum=A.combined_checksum(A.model_checksums(w.items())), engine="e1")
+    log.log("replica_checksum", step=1, dp_rank=0, checksum="x")
+    log.log("replica_checksum", step=1, dp_rank=1, checksum="y")
+    wit.consumed(0, 1, [ids[0]])
+    wit.allocate(1, 2)
+    found = {(f["rule"], f["problem"]) for f in A.analyze(str(tmp_path))}
+    assert ("weight_checksums", "engine weights differ from trainer") in found
+    assert ("cross_replica", "replicas diverged") in found
+    assert ("witness", "samples trained on more than once") in found and ("witness", "samples never trained on") in found
+    assert A.tensor_checksum(torch.ones(3)) != A.tensor_checksum(torch.ones(3) * (1 + 1e-7))
+
+
+def test_dashboard_store_api_and_sampler(tmp_path):
+    from fastapi.testclient import TestClient
+
+    store = SeriesStore(max_points=3, jsonl=str(tmp_path / "m.jsonl"))
+    be = DashboardBackend(store)
+    for step in range(5):
+        be.log({"train/loss": 1.0 / (step + 1), "note": "text is skipped"}, step, "rollout/step")
+    assert len(store.get("train/loss")) == 3 and store.get("train/loss")[-1] == (4.0, 0.2)
+    other = SeriesStore()
+    other.load_jsonl(str(tmp_path / "m.jsonl"))
+    assert len(other.get("train/loss")) == 5
+    with TestClient(build_app(store)) as c:
+        assert c.get("/api/names", params={"prefix": "train/"}).json() == ["train/loss"]
+        assert c.get("/api/series", params={"name": "train/loss", "last": 2}).json() == [[3.0, 0.25], [4.0, 0.2]]
+        assert "<canvas" in c.get("/").text or "canvas" in c.get("/").text
+        c.post("/api/log", json={"metrics": {"x": 1}, "step": 9})
+        assert store.get("x") == [(9.0, 1.0)]
+
+    class FakeNvml:                                       # the sampler only reads; a fake NVML stands in for the driver
+        NVML_CLOCK_SM = 1
+
+        def nvmlDeviceGetCount(self):
+            return 2
+
+        def nvmlDeviceGetHandleByIndex(self, i):
+            return i
+
+        def nvmlDeviceGetUtilizationRates(self, h):
+            return type("U", (), {"gpu": 50 + h})()
+
+        def nvmlDeviceGetMemoryInfo(self, h):
+            return type("M", (), {"used": 2 ** 31})()
+
+        def nvmlDeviceGetClockInfo(self, h, k):
+            return 1965
+
+        def nvmlDeviceGetPowerUsage(self, h):
+            return 700000
+
+        def nvmlDeviceGetCurrentClocksThrottleReasons(self, h):
+            return 4
+
+    out = GpuSampler(store, nvml=FakeNvml()).sample_once()
+    assert out["gpu1/util"] == 51 and out["gpu0/mem_used_gb"] == 2.0 and out["gpu0/power_w"] == 700.0
+    assert scrape_prometheus("# HELP x\nengine_tokens_total 12\nq{a=\"b\"} 3.5\nbad line\n") == {"engine_tokens_total": 12.0, 'q{a="b"}': 3.5}
+
+
+def test_convert_tool_chain(tmp_path):
+    from miles_b200.checkpoint import hf_io, torch_dist
+    from miles_b200.tools import convert as tool
+
+    cfg = PRESETS["tiny"]
+    model = build_model(cfg, ParallelState.single(), dtype=torch.bfloat16, device="cpu", seed=0)
+    hf_dir = str(tmp_path / "hf")
+    named = [x for n, p in model.named_parameters() for x in mc.to_hf(n, p.detach(), cfg)]
+    hf_io.save_hf_sharded(hf_dir, [named], cfg, write=True)
+    assert os.path.exists(os.path.join(hf_dir, "config.json"))
+    # HF → torch_dist → HF is the identity on every tensor
+    rel = tool.main(["hf-to-torch-dist", "--hf", hf_dir, "--out", str(tmp_path / "td")])
+    assert torch_dist.is_torch_dist_dir(rel) and open(tmp_path / "td" / "latest_checkpointed_iteration.txt").read() == "release"
+    tool.main(["torch-dist-to-hf", "--load", str(tmp_path / "td"), "--out", str(tmp_path / "hf2"), "--hf-config", hf_dir])
+    a, b = hf_io.load_hf_dir(hf_dir), hf_io.load_hf_dir(str(tmp_path / "hf2"))
+    assert set(a) == set(b) and all(torch.equal(a[k], b[k]) for k in a)
+    # quantised exports: payload + scale tensors, config gains a quantisation block; fp8 → bf16 comes back close
+    tool.main(["hf-to-fp8", "--hf", hf_dir, "--out", str(tmp_path / "fp8")])
+    q = hf_io.load_hf_dir(str(tmp_path / "fp8"))
+    name = "model.layers.0.self_attn.o_proj.weight"
+    assert q[name].dtype == torch.float8_e4m3fn and name + "_scale_inv" in q and q["model.norm.weight"].dtype == torch.bfloat16
+    assert json.load(open(tmp_path / "fp8" / "config.json"))["quantization_config"]["quant_method"] == "fp8"
+    tool.main(["fp8-to-bf16", "--hf", str(tmp_path / "fp8"), "--out", str(tmp_path / "bf16")])
+    back = hf_io.load_hf_dir(str(tmp_path / "bf16"))
+    assert set(back) == set(a) and "quantization_config" not in json.load(open(tmp_path / "bf16" / "config.json"))
+    assert (back[name].float() - a[name].float()).abs().max() < 0.08 * a[name].float().abs().max()
+    tool.main(["hf-to-mxfp8", "--hf", hf_dir, "--out", str(tmp_path / "mx")])
+    assert hf_io.load_hf_dir(str(tmp_path / "mx"))[name + "_scale_inv"].dtype == torch.uint8
+    tool.main(["hf-to-int4-qdq", "--hf", hf_dir, "--out", str(tmp_path / "i4")])
+    i4 = hf_io.load_hf_dir(str(tmp_path / "i4"))[name]
+    assert i4.dtype == torch.bfloat16 and i4.float().view(-1, 32).unique(dim=1).shape[1] <= 32
+    tool.main(["hf-to-nvfp4-qdq", "--hf", hf_dir, "--out", str(tmp_path / "n4")])
+    assert hf_io.load_hf_dir(str(tmp_path / "n4"))[name].shape == a[name].shape
