@@ -55,7 +55,7 @@ def attention_varlen(q, k, v, cu_seqlens, max_seqlen=0, causal=True):
     return _FlashAttn.apply(q, k, v, cu_seqlens.to(torch.int32), int(max_seqlen), bool(causal))
 
 
-_DECODE_SPLITS = 8
+_DECODE_SPLITS = int(os.environ.get("MILES_DECODE_SPLITS", "8"))   # KV splits per (request, kv head) in paged decode
 
 
 def paged_attention(q, k_cache, v_cache, block_table, seq_lens, q_lens=None, max_q_len=1):
