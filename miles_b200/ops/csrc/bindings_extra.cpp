@@ -80,9 +80,19 @@ void gather_rows_host(const at::Tensor& table, const at::Tensor& ids, at::Tensor
         "mb_gather_rows_host");
 }
 
+void sparse_attention_fwd(const at::Tensor& q, const at::Tensor& k, const at::Tensor& v, const at::Tensor& indices,
+                          const c10::optional<at::Tensor>& sink, at::Tensor& out, at::Tensor& lse, double scale) {
+  c10::cuda::CUDAGuard g(q.device());
+  check(mb_sparse_attention_fwd(q.data_ptr(), k.data_ptr(), v.data_ptr(), indices.data_ptr<int>(),
+                                sink.has_value() ? sink->data_ptr<float>() : nullptr, out.data_ptr(), lse.data_ptr<float>(), q.size(0), q.size(1),
+                                k.size(1), q.size(2), v.size(2), indices.size(1), k.size(0), scale, cur_stream()),
+        "mb_sparse_attention_fwd");
+}
+
 }  // namespace
 
 void register_extra(pybind11::module& m) {
+  m.def("sparse_attention_fwd", &sparse_attention_fwd);
   m.def("grouped_rmsnorm", &grouped_rmsnorm);
   m.def("short_conv", &short_conv);
   m.def("mhc_mix", &mhc_mix);

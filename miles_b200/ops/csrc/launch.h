@@ -144,6 +144,10 @@ int mb_fp8_dequant(const void* q, const float* scale_inv, const void* e8m0, void
 int mb_gather_rows_host(const void* table_dev, const long long* ids, void* out, long long n, int row_bytes, long long table_rows,
                         cudaStream_t s);
 
+// ---- sparse_attn.cu ----
+int mb_sparse_attention_fwd(const void* q, const void* k, const void* v, const int* indices, const float* sink, void* out, float* lse,
+                            long long T, int H, int Hk, int D, int Dv, int K, long long Tkv, float scale, cudaStream_t s);
+
 // ---- weight_sync.cu (one launch per bucket of tensors; dst may be peer memory) ----
 int mb_multi_copy(const long long* table, const long long* prefix, int n, long long total_chunks, cudaStream_t s);
 int mb_multi_mxfp8(const long long* table, const long long* prefix, int n, long long total_chunks, int qdq, cudaStream_t s);
