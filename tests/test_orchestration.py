@@ -124,3 +124,45 @@ def test_debug_runner(tmp_path):
     torch.save({"rollout_id": 0, "samples": [[sample]]}, dump)
     cmp = debug.main(["compare", "--model-name", "tiny", "--fp32", "--cpu", "--rollout-dump", str(dump)])
     assert cmp["max_abs_diff"] < 1e-4
+
+
+def test_inference_controller_config_framing_and_health():
+    from miles_b200.orchestration.inference_controller import (InferenceController, ServerCell, engine_launch_cmd,
+                                                               load_serving_config)
+    from miles_b200.testing.mock_engine import MockEngine
+
+    models = load_serving_config({"models": [
+        {"name": "policy", "model_path": "/ckpt/policy", "server_groups": [
+            {"worker_type": "prefill", "num_gpus": 2, "num_gpus_per_engine": 1, "overrides": {"mem_fraction_static": 0.6}},
+            {"worker_type": "decode", "num_gpus": 4, "num_gpus_per_engine": 2},
+            {"worker_type": "placeholder", "num_gpus": 2}]},
+        {"name": "teacher", "update_weights": False}]})
+    assert [g.num_engines for g in models[0].groups] == [2, 2, 0] and models[1].groups[0].worker_type == "regular"
+    cmd = engine_launch_cmd(models[0], models[0].groups[0], port=30010)
+    assert cmd[:5] == ["python", "-m", "miles_b200.engine.server", "--port", "30010"] and "--mem-fraction-static" in cmd
+    assert cmd[cmd.index("--disaggregation-mode") + 1] == "prefill"
+    with pytest.raises(ValueError):
+        load_serving_config({"models": [{"name": "x", "server_groups": [{"worker_type": "prefill"}]}]})
+
+    engines = [MockEngine(), MockEngine()]
+    ok = {id(engines[0]): True, id(engines[1]): True}
+    ctl = InferenceController([ServerCell(e, "policy", models[0].groups[1]) for e in engines], probe=lambda e: ok[id(e)],
+                              health_threshold=2)
+    targets = ctl.start_update_weights()
+    assert len(targets) == 2 and ctl.lock.holder == "update_weights" and all(e.paused for e in engines)
+    ctl.end_update_weights(5)
+    assert ctl.weight_version == 5 and all(e.weight_version == 5 and not e.paused for e in engines)
+    assert [c[0] for c in engines[0].calls] == ["pause_generation", "flush_cache", "update_weight_version", "continue_generation"]
+    ctl.offload()
+    assert all(c.state == "offloaded" for c in ctl.cells) and engines[0].calls[-1][0] == "release_memory_occupation"
+    ctl.onload()
+    assert all(c.state == "alive" for c in ctl.cells)
+    ok[id(engines[1])] = False
+    ctl.tick()
+    assert ctl.tick()["policy#1"] == "unhealthy" and ctl.engines() == [engines[0]]
+    ctl.start_update_weights()
+    ctl.end_update_weights(6)                               # the quarantined engine misses version 6
+    ok[id(engines[1])] = True
+    assert ctl.tick()["policy#1"] == "stale" and ctl.stale_engines() == [engines[1]]
+    ctl.mark_synced(engines[1])
+    assert ctl.tick()["policy#1"] == "alive"
