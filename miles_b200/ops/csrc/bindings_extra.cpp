@@ -89,9 +89,17 @@ void sparse_attention_fwd(const at::Tensor& q, const at::Tensor& k, const at::Te
         "mb_sparse_attention_fwd");
 }
 
+void gemm_mxfp8(const at::Tensor& A, const at::Tensor& sa, const at::Tensor& B, const at::Tensor& sb, at::Tensor& C, at::Tensor& err) {
+  c10::cuda::CUDAGuard g(A.device());
+  check(mb_gemm_mxfp8(A.data_ptr(), sa.data_ptr(), B.data_ptr(), sb.data_ptr(), C.data_ptr(), A.size(0), B.size(0), A.size(1), C.stride(0),
+                      err.data_ptr<int>(), cur_stream()),
+        "mb_gemm_mxfp8");
+}
+
 }  // namespace
 
 void register_extra(pybind11::module& m) {
+  m.def("gemm_mxfp8", &gemm_mxfp8);
   m.def("sparse_attention_fwd", &sparse_attention_fwd);
   m.def("grouped_rmsnorm", &grouped_rmsnorm);
   m.def("short_conv", &short_conv);

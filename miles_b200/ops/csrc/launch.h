@@ -144,6 +144,10 @@ int mb_fp8_dequant(const void* q, const float* scale_inv, const void* e8m0, void
 int mb_gather_rows_host(const void* table_dev, const long long* ids, void* out, long long n, int row_bytes, long long table_rows,
                         cudaStream_t s);
 
+// ---- gemm_mxfp8.cu (block-scaled: e4m3 payload [rows, K] + e8m0 scales [rows, K/32]; K % 128 == 0) ----
+int mb_gemm_mxfp8(const void* A, const void* sa, const void* B, const void* sb, void* C, int M, int N, int K, long long ldc,
+                  int* error_flag, cudaStream_t stream);
+
 // ---- sparse_attn.cu ----
 int mb_sparse_attention_fwd(const void* q, const void* k, const void* v, const int* indices, const float* sink, void* out, float* lse,
                             long long T, int H, int Hk, int D, int Dv, int K, long long Tkv, float scale, cudaStream_t s);

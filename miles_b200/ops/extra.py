@@ -248,6 +248,43 @@ def act_quant(x, block: int = 128, round_scale: bool = False, inplace: bool = Fa
     return q, s
 
 
+def gemm_mxfp8_ref(a_q, a_s, b_q, b_s) -> torch.Tensor:
+    """fp32 statement of the block-scaled product: dequantise both operands, multiply."""
+    from . import reference as ref
+
+    a = ref.mxfp8_dequant(a_q, a_s).reshape(a_q.shape).float()
+    b = ref.mxfp8_dequant(b_q, b_s).reshape(b_q.shape).float()
+    return a @ b.t()
+
+
+def gemm_mxfp8(a_q, a_s, b_q, b_s, out: torch.Tensor | None = None) -> torch.Tensor:
+    """C [M, N] bf16 = MXFP8(A) · MXFP8(B)ᵀ with A [M, K], B [N, K] e4m3 and e8m0 scales [rows, K/32] (what `mxfp8_quant`
+    returns).  On CUDA the scales are applied inside the tensor core (tcgen05 block-scaled MMA); K % 128 == 0."""
+    M, K = a_q.shape
+    N = b_q.shape[0]
+    if a_q.is_cuda and K % 128 == 0:
+        from . import cuda
+
+        if out is None:
+            out = torch.empty(M, N, dtype=torch.bfloat16, device=a_q.device)
+        cuda.C.gemm_mxfp8(a_q.contiguous().view(torch.uint8), a_s.contiguous(), b_q.contiguous().view(torch.uint8), b_s.contiguous(), out,
+                          cuda.C.error_flag(out))
+        return out
+    res = gemm_mxfp8_ref(a_q, a_s, b_q, b_s).bfloat16()
+    if out is not None:
+        out.copy_(res)
+        return out
+    return res
+
+
+def linear_mxfp8(x: torch.Tensor, w_q: torch.Tensor, w_s: torch.Tensor) -> torch.Tensor:
+    """y = x·Wᵀ with W held in MXFP8 (weights quantised once, e.g. by the weight sync) and x quantised on the fly."""
+    from .. import ops
+
+    xq, xs = ops.mxfp8_quant(x.reshape(-1, x.shape[-1]))
+    return gemm_mxfp8(xq, xs, w_q, w_s).view(*x.shape[:-1], w_q.shape[0])
+
+
 def fp8_dequant(q: torch.Tensor, scale: torch.Tensor) -> torch.Tensor:
     """Block-scaled FP8 weight → bf16.  `scale` fp32 [⌈M/128⌉, ⌈N/128⌉] (scale_inv of 128×128 blocks) or uint8 e8m0
     [M, N/32] (MXFP8)."""

@@ -121,6 +121,32 @@ def test_extra_kernels_match_references(dtype):
 
 
 @pytest.mark.gpu
+@pytest.mark.parametrize("M,N,K", [(128, 128, 128), (256, 384, 512), (100, 200, 1024), (1000, 1536, 2048)])
+def test_mxfp8_block_scaled_gemm(M, N, K):
+    """tcgen05 block-scaled GEMM vs dequantise-then-multiply in fp32.  Rows get very different magnitudes so that a wrong
+    scale (wrong row, wrong K block) cannot hide."""
+    from miles_b200.ops import cuda as K_
+
+    torch.manual_seed(6)
+    a = torch.randn(M, K, device="cuda") * torch.exp2(torch.randint(-6, 7, (M, 1), device="cuda").float())
+    b = torch.randn(N, K, device="cuda") * torch.exp2(torch.randint(-6, 7, (N, 1), device="cuda").float())
+    a[:, K // 2:] *= 8.0                                       # and different scales along K
+    aq, asc = ref.mxfp8_quant(a.cpu())
+    bq, bsc = ref.mxfp8_quant(b.cpu())
+    want = X.gemm_mxfp8_ref(aq, asc, bq, bsc)
+    got = X.gemm_mxfp8(aq.cuda(), asc.cuda(), bq.cuda(), bsc.cuda())
+    torch.cuda.synchronize()
+    assert K_.check_error_flag() == 0
+    rel = ((got.float().cpu() - want).norm() / want.norm()).item()
+    assert rel < 5e-3, rel                                     # bf16 rounding of the output only
+    # and against the unquantised product: the quantisation error itself is small
+    full = a.cpu() @ b.cpu().t()
+    assert ((got.float().cpu() - full).norm() / full.norm()).item() < 0.06
+    y = X.linear_mxfp8(a.bfloat16(), bq.cuda(), bsc.cuda())
+    assert y.shape == (M, N)
+
+
+@pytest.mark.gpu
 def test_quant_tool_kernels_and_host_gather():
     torch.manual_seed(5)
     x = (torch.randn(300, 512, device="cuda") * 2).bfloat16()
