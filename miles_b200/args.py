@@ -297,6 +297,8 @@ def build_parser() -> argparse.ArgumentParser:
     _bool_flag(g, "--check-weight-update-equal")
     _bool_flag(g, "--debug-deterministic-collective")
     _bool_flag(g, "--ci-test")
+    g.add_argument("--audit-dir", type=str, default=None,
+                   help="write the audit event log here (weight checksums per version; analyse with miles_b200.audit.events)")
     g.add_argument("--ci-save-grad-norm", type=str, default=None)
     g.add_argument("--ci-load-grad-norm", type=str, default=None)
     _bool_flag(g, "--use-pytorch-profiler")

@@ -122,4 +122,35 @@ def update_weights(args, actor, rollout: RolloutComponents, updater=None) -> dic
     updater = updater or WeightUpdater(args, actor, rollout.engines)
     info = actor.update_weights(updater)
     rollout.executor.set_weight_version(actor.weight_version)
+    if getattr(args, "audit_dir", None):
+        _audit_weights(args, actor, rollout, info)
     return info
+
+
+_AUDIT = {}
+
+
+def audit_logger(args, source: str, rank: int):
+    """One JSONL event log per (source, rank) under `--audit-dir` (see `miles_b200.audit.events`)."""
+    from ..audit.events import EventLogger
+
+    key = (args.audit_dir, source, rank)
+    if key not in _AUDIT:
+        _AUDIT[key] = EventLogger(args.audit_dir, source, rank)
+    return _AUDIT[key]
+
+
+def _audit_weights(args, actor, rollout: RolloutComponents, info: dict):
+    """Checksums of what the trainer published and of what each in-process engine now holds (same layout only)."""
+    from ..audit.events import combined_checksum, model_checksums
+
+    rank = actor.ps.rank
+    mine = combined_checksum(model_checksums(actor.named_weights()))
+    audit_logger(args, "trainer", rank).log("weights_published", version=actor.weight_version, checksum=mine, mode=info.get("mode"))
+    for i, e in enumerate(rollout.engines):
+        model = getattr(e, "model", None)
+        if model is None or info.get("mode") not in ("alias", "nvlink"):
+            continue
+        named = model.named_parameters_global() if hasattr(model, "named_parameters_global") else model.named_parameters()
+        got = combined_checksum(model_checksums((n, p.data) for n, p in named if ".lora." not in n or info.get("mode") == "alias"))
+        audit_logger(args, "engine", rank).log("weights_received", version=actor.weight_version, checksum=got, engine=f"rank{rank}#{i}")

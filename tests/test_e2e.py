@@ -50,6 +50,16 @@ def test_grpo_moe_with_routing_replay():
     _check_history(h)
 
 
+def test_audit_log_of_a_run_is_clean(tmp_path):
+    from miles_b200.audit import events as A
+
+    _run(f"--audit-dir {tmp_path}")
+    ev = A.read_events(str(tmp_path))
+    assert sum(e["kind"] == "weights_published" for e in ev) == 3        # initial push + one per rollout
+    assert sum(e["kind"] == "weights_received" for e in ev) == 3
+    assert A.analyze(str(tmp_path), ["weight_checksums"]) == []
+
+
 def test_ppo_with_critic():
     h = _run("--advantage-estimator ppo --critic-lr 1e-4 --num-critic-only-steps 1")
     assert len(h.rows) == 2

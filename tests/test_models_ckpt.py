@@ -191,3 +191,33 @@ def test_fused_weight_sync_cpu_path_and_quant():
     w, wq = src.layers[0].attn.wo, dst.layers[0].attn.wo
     assert not torch.equal(w, wq) and (w - wq).abs().max() < 0.07 * w.abs().max()
     assert torch.equal(src.layers[0].ln1, dst.layers[0].ln1)        # norms are on the skip list
+
+
+def test_nvme_stream_adam_matches_adamw_and_resumes(tmp_path):
+    from miles_b200.train.nvme_stream import NvmeStreamAdam
+
+    torch.manual_seed(0)
+    n = 10_000
+    p0 = torch.randn(n)
+    flat = p0.clone()
+    ref_p = torch.nn.Parameter(p0.clone())
+    ref_opt = torch.optim.AdamW([ref_p], lr=1e-2, betas=(0.9, 0.95), eps=1e-8, weight_decay=0.1)
+    opt = NvmeStreamAdam(flat, str(tmp_path), lr=1e-2, betas=(0.9, 0.95), eps=1e-8, weight_decay=0.1, bucket_numel=3000)
+    grads = [torch.randn(n) for _ in range(4)]
+    for g in grads[:2]:
+        opt.step(g)
+        ref_p.grad = g.clone()
+        ref_opt.step()
+    torch.testing.assert_close(flat, ref_p.detach(), atol=1e-6, rtol=1e-5)
+    assert opt.bytes_read == opt.bytes_written == 2 * 3 * 4 * n          # every state byte read and written once per step
+    sd = opt.state_dict()
+    opt.close()
+    # a new process picks the files up and continues
+    opt2 = NvmeStreamAdam(flat, str(tmp_path), lr=1e-2, betas=(0.9, 0.95), eps=1e-8, weight_decay=0.1, bucket_numel=4096)
+    opt2.load_state_dict(sd)
+    for g in grads[2:]:
+        opt2.step(g)
+        ref_p.grad = g.clone()
+        ref_opt.step()
+    torch.testing.assert_close(flat, ref_p.detach(), atol=1e-6, rtol=1e-5)
+    opt2.close()
