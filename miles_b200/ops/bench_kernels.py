@@ -149,9 +149,33 @@ def bench_elementwise(a):
     return out
 
 
+def bench_mxfp8(a):
+    """Block-scaled MXFP8 GEMM against the bf16 GEMM on the same shapes (fp8 peak is twice the bf16 peak)."""
+    from miles_b200.ops import cuda as K
+    from miles_b200.ops import extra as X
+
+    hbm, tf, tag = peaks()
+    out = []
+    shapes = [(a.m, a.n, a.k)] if a.m else [(8192, 8192, 8192), (16384, 5120, 2048), (16384, 2048, 4096)]
+    for M, N, Kd in shapes:
+        x = torch.randn(M, Kd, device="cuda", dtype=torch.bfloat16)
+        w = torch.randn(N, Kd, device="cuda", dtype=torch.bfloat16)
+        xq, xs = K.mxfp8_quant(x)
+        wq, ws = K.mxfp8_quant(w)
+        y = torch.empty(M, N, device="cuda", dtype=torch.bfloat16)
+        ms = timeit(lambda: X.gemm_mxfp8(xq, xs, wq, ws, out=y), a.iters)
+        ms_q = timeit(lambda: K.mxfp8_quant(x), a.iters)
+        ms_bf16 = timeit(lambda: K.gemm_nt(x, w, out=y), a.iters)
+        flops = 2.0 * M * N * Kd
+        out.append({"kernel": "gemm_mxfp8_block_scaled", "M": M, "N": N, "K": Kd, "ms": ms, "tflops": flops / ms / 1e9,
+                    "bf16_gemm_ms": ms_bf16, "vs_bf16_gemm": ms_bf16 / ms, "quant_activation_ms": ms_q,
+                    "roofline_frac": flops / (2 * tf * 1e12) * 1e3 / ms, "roofline": tag + " (2 × bf16 peak)"})
+    return out
+
+
 def main():
     p = argparse.ArgumentParser()
-    p.add_argument("what", choices=["gemm", "attention", "decode", "elementwise", "all"])
+    p.add_argument("what", choices=["gemm", "mxfp8", "attention", "decode", "elementwise", "all"])
     p.add_argument("--m", type=int, default=0)
     p.add_argument("--n", type=int, default=8192)
     p.add_argument("--k", type=int, default=8192)
@@ -165,6 +189,8 @@ def main():
     rows = []
     if a.what in ("gemm", "all"):
         rows += bench_gemm(a)
+    if a.what in ("mxfp8", "all"):
+        rows += bench_mxfp8(a)
     if a.what in ("attention", "all"):
         rows += bench_attention(a)
     if a.what in ("decode", "all"):

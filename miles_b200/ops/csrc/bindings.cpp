@@ -181,6 +181,8 @@ void register_more(pybind11::module& m);  // bindings_more.cpp: attention, MoE, 
 
 PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("error_flag", &error_flag);
+  m.def("set_pdl", [](bool on) { mb_set_pdl(on ? 1 : 0); });
+  m.def("pdl_enabled", []() { return mb_pdl_enabled() != 0; });
   m.def("launch_count", []() { return static_cast<int64_t>(mb_launch_count()); });
   m.def("count_launches", [](int64_t n) { mb_count_launch(static_cast<int>(n)); });
   m.def("gemm", &gemm);

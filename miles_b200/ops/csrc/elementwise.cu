@@ -7,6 +7,7 @@
 #include <stdint.h>
 
 #include "launch.h"
+#include "pdl.cuh"
 
 namespace mb {
 
@@ -62,6 +63,8 @@ __global__ void __launch_bounds__(256) rmsnorm_fwd_kernel(const __nv_bfloat16* _
                                                           __nv_bfloat16* __restrict__ res_out, float* __restrict__ rstd_out, int H,
                                                           float eps) {
   __shared__ float sh[32];
+  pdl_trigger();
+  pdl_wait();
   const long long row = blockIdx.x;
   const __nv_bfloat16* xr = x + row * H;
   constexpr int MAXI = 4;  // rows up to 256·8·4 = 8192 wide stay in registers
@@ -201,6 +204,8 @@ __global__ void colsum_kernel(const float* __restrict__ partial, void* __restric
 // ---------------------------------------------------------------------------------------------
 __global__ void __launch_bounds__(256) swiglu_fwd_kernel(const __nv_bfloat16* __restrict__ in, __nv_bfloat16* __restrict__ out,
                                                          long long T, int F, const int* __restrict__ rows_ptr) {
+  pdl_trigger();
+  pdl_wait();
   const int nvec = F / 8;
   if (rows_ptr != nullptr) T = min(T, static_cast<long long>(*rows_ptr));  // device-side row count (MoE padded buffers)
   const long long total = T * nvec;
@@ -295,6 +300,8 @@ __global__ void __launch_bounds__(256) qk_norm_rope_cache_kernel(const __nv_bflo
                                                                  __nv_bfloat16* __restrict__ ko, __nv_bfloat16* __restrict__ kc,
                                                                  __nv_bfloat16* __restrict__ vc, const long long* __restrict__ slots,
                                                                  long long T, int Hq, int Hk, float log2_theta, float eps) {
+  pdl_trigger();
+  pdl_wait();
   const int lane = threadIdx.x & 31;
   const long long wid = (blockIdx.x * 256ll + threadIdx.x) >> 5;
   const int heads = Hq + 2 * Hk;
@@ -520,15 +527,16 @@ extern "C" int mb_rmsnorm_fwd(const void* x, const void* residual, const void* w
   if (T == 0) return 0;
   if (H % 8) return -1;
   auto X = reinterpret_cast<const __nv_bfloat16*>(x);
+  typedef const __nv_bfloat16* cbf;
+  typedef __nv_bfloat16* bf;
+  cudaError_t e;
   if (residual != nullptr)
-    rmsnorm_fwd_kernel<true><<<static_cast<unsigned>(T), 256, 0, s>>>(X, reinterpret_cast<const __nv_bfloat16*>(residual),
-                                                                       reinterpret_cast<const __nv_bfloat16*>(w),
-                                                                       reinterpret_cast<__nv_bfloat16*>(y),
-                                                                       reinterpret_cast<__nv_bfloat16*>(res_out), rstd, H, eps);
+    e = launch_pdl(rmsnorm_fwd_kernel<true>, dim3(static_cast<unsigned>(T)), dim3(256), 0, s, X, (cbf)residual, (cbf)w, (bf)y, (bf)res_out,
+                   rstd, H, eps);
   else
-    rmsnorm_fwd_kernel<false><<<static_cast<unsigned>(T), 256, 0, s>>>(X, nullptr, reinterpret_cast<const __nv_bfloat16*>(w),
-                                                                        reinterpret_cast<__nv_bfloat16*>(y), nullptr, rstd, H, eps);
-  return static_cast<int>(cudaGetLastError());
+    e = launch_pdl(rmsnorm_fwd_kernel<false>, dim3(static_cast<unsigned>(T)), dim3(256), 0, s, X, (cbf) nullptr, (cbf)w, (bf)y,
+                   (bf) nullptr, rstd, H, eps);
+  return static_cast<int>(e);
 }
 
 // dw_partial must hold mb_rmsnorm_bwd_blocks(T) × H floats; dw_out receives the reduced weight gradient.
@@ -555,9 +563,8 @@ extern "C" int mb_colsum(const float* partial, void* out, int R, int C, int out_
 extern "C" int mb_swiglu_fwd(const void* in, void* out, long long T, int F, const int* rows_ptr, cudaStream_t s) {
   if (T == 0) return 0;
   if (F % 8) return -1;
-  swiglu_fwd_kernel<<<grid_for(T * (F / 8), 256), 256, 0, s>>>(reinterpret_cast<const __nv_bfloat16*>(in),
-                                                                reinterpret_cast<__nv_bfloat16*>(out), T, F, rows_ptr);
-  return static_cast<int>(cudaGetLastError());
+  return static_cast<int>(launch_pdl(swiglu_fwd_kernel, dim3(grid_for(T * (F / 8), 256)), dim3(256), 0, s,
+                                     reinterpret_cast<const __nv_bfloat16*>(in), reinterpret_cast<__nv_bfloat16*>(out), T, F, rows_ptr));
 }
 
 extern "C" int mb_swiglu_bwd(const void* in, const void* dout, void* din, long long T, int F, const int* rows_ptr, cudaStream_t s) {
@@ -602,14 +609,12 @@ extern "C" int mb_qk_norm_rope_cache(const void* q, const void* k, const void* v
   typedef const __nv_bfloat16* cbf;
   typedef __nv_bfloat16* bf;
   if (D == 128)
-    qk_norm_rope_cache_kernel<128><<<blocks, 256, 0, s>>>((cbf)q, (cbf)k, (cbf)v, q_stride, k_stride, v_stride, (cbf)qw, (cbf)kw, positions,
-                                                          (bf)qo, (bf)ko, (bf)kc, (bf)vc, slots, T, Hq, Hk, l2t, eps);
-  else if (D == 64)
-    qk_norm_rope_cache_kernel<64><<<blocks, 256, 0, s>>>((cbf)q, (cbf)k, (cbf)v, q_stride, k_stride, v_stride, (cbf)qw, (cbf)kw, positions,
-                                                         (bf)qo, (bf)ko, (bf)kc, (bf)vc, slots, T, Hq, Hk, l2t, eps);
-  else
-    return -1;
-  return static_cast<int>(cudaGetLastError());
+    return static_cast<int>(launch_pdl(qk_norm_rope_cache_kernel<128>, dim3(blocks), dim3(256), 0, s, (cbf)q, (cbf)k, (cbf)v, q_stride, k_stride,
+                                       v_stride, (cbf)qw, (cbf)kw, positions, (bf)qo, (bf)ko, (bf)kc, (bf)vc, slots, T, Hq, Hk, l2t, eps));
+  if (D == 64)
+    return static_cast<int>(launch_pdl(qk_norm_rope_cache_kernel<64>, dim3(blocks), dim3(256), 0, s, (cbf)q, (cbf)k, (cbf)v, q_stride, k_stride,
+                                       v_stride, (cbf)qw, (cbf)kw, positions, (bf)qo, (bf)ko, (bf)kc, (bf)vc, slots, T, Hq, Hk, l2t, eps));
+  return -1;
 }
 
 extern "C" int mb_qk_norm_rope_bwd_blocks(long long T, int Hn) { return grid_for(T * Hn, 8, 148 * 4); }

@@ -16,6 +16,7 @@
 // Every mbarrier wait is bounded; on timeout the kernel raises `*error_flag`, drains and frees TMEM, and returns.
 #include "ptx.cuh"
 #include "launch.h"
+#include "pdl.cuh"
 
 namespace mb {
 
@@ -100,6 +101,9 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *tmem_base_ptr;
+  // everything above (barrier init, TMEM allocation, descriptor prefetch) may overlap the tail of the previous kernel
+  pdl_trigger();
+  pdl_wait();
 
   auto k_range = [&](int group, int& k0, int& k_blocks) {
     if (MODE == kGroupedWgrad) {
@@ -444,8 +448,7 @@ static int launch_one(const CUtensorMap& ta, const CUtensorMap& tb, const GemmPa
   }
   int grid = total_tiles < num_sms() ? total_tiles : num_sms();
   if (grid <= 0) return 0;
-  kern<<<grid, 192, L::kTotal, stream>>>(ta, tb, p);
-  return static_cast<int>(cudaGetLastError());
+  return static_cast<int>(launch_pdl(kern, dim3(grid), dim3(192), L::kTotal, stream, ta, tb, p));
 }
 
 template <int A_MN, int B_MN, int MODE>

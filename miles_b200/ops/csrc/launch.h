@@ -10,6 +10,8 @@ extern "C" {
 // ---- counter.cpp ----
 void mb_count_launch(int n);
 long long mb_launch_count();
+int mb_pdl_enabled(void);      // programmatic dependent launch for the kernels that support it (pdl.cuh); MILES_PDL=0 disables
+void mb_set_pdl(int on);
 
 // ---- gemm.cu ----
 int mb_gemm_bf16(const void* A, const void* B, void* C, int M, int N, int K, long long lda, long long ldb, long long ldc,

@@ -6,6 +6,7 @@
 #include <stdint.h>
 
 #include "launch.h"
+#include "pdl.cuh"
 
 namespace mb {
 
@@ -38,6 +39,8 @@ __global__ void __launch_bounds__(1024) sample_logprob_kernel(const float* __res
                                                               float* __restrict__ logprobs, int V) {
   __shared__ float sh_m[32], sh_s[32], sh_best[32];
   __shared__ int sh_idx[32];
+  pdl_trigger();
+  pdl_wait();
   const int row = blockIdx.x;
   const float* x = logits + static_cast<long long>(row) * V;
   const float it = 1.f / temperature[row];
@@ -182,8 +185,8 @@ using namespace mb;
 extern "C" int mb_sample_logprob(const float* logits, const float* temperature, const uint8_t* greedy, const long long* seeds,
                                  long long step, long long* tokens, float* logprobs, int B, int V, cudaStream_t s) {
   if (B == 0) return 0;
-  sample_logprob_kernel<<<B, 1024, 0, s>>>(logits, temperature, greedy, seeds, step, tokens, logprobs, V);
-  return static_cast<int>(cudaGetLastError());
+  return static_cast<int>(launch_pdl(sample_logprob_kernel, dim3(B), dim3(1024), 0, s, logits, temperature, greedy, seeds, step, tokens,
+                                     logprobs, V));
 }
 
 extern "C" int mb_logit_stats(const float* logits, long long ld, const long long* targets, float* stats, long long R, int Vc, int v0,

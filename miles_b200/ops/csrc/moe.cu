@@ -10,6 +10,7 @@
 #include <stdint.h>
 
 #include "launch.h"
+#include "pdl.cuh"
 
 namespace mb {
 
@@ -32,6 +33,8 @@ template <int EPL>  // experts per lane = E / 32
 __global__ void __launch_bounds__(256) router_topk_kernel(const float* __restrict__ logits, float* __restrict__ probs,
                                                           float* __restrict__ topk_w, int* __restrict__ topk_idx, long long T, int E,
                                                           int K, int normalize) {
+  pdl_trigger();
+  pdl_wait();
   const long long t = (blockIdx.x * 256ll + threadIdx.x) >> 5;
   const int lane = threadIdx.x & 31;
   if (t >= T) return;
@@ -93,6 +96,8 @@ __global__ void __launch_bounds__(1024) moe_align_kernel(const int* __restrict__
                                                          int expert_offset, int* __restrict__ seg_offsets, int* __restrict__ tile_expert,
                                                          int* __restrict__ row_src, int* __restrict__ dst_row, int max_rows) {
   extern __shared__ int sh[];  // counts[E], cursor[E], seg[E+1]
+  pdl_trigger();
+  pdl_wait();
   if (n_ptr != nullptr) n = min(n, *n_ptr);   // device-side entry count (expert-parallel receive buffers)
   int* counts = sh;
   int* cursor = sh + E;
@@ -146,6 +151,8 @@ __global__ void __launch_bounds__(1024) moe_align_kernel(const int* __restrict__
 __global__ void __launch_bounds__(256) moe_gather_kernel(const bf16* __restrict__ x, bf16* __restrict__ x_perm,
                                                          const int* __restrict__ row_src, const int* __restrict__ seg_offsets, int E,
                                                          int k, int H, int max_rows) {
+  pdl_trigger();
+  pdl_wait();
   const int total = seg_offsets[E];
   const int nvec = H / 8;
   for (int row = blockIdx.x; row < total && row < max_rows; row += gridDim.x) {
@@ -164,6 +171,8 @@ __global__ void __launch_bounds__(256) moe_gather_kernel(const bf16* __restrict_
 __global__ void __launch_bounds__(256) moe_combine_kernel(const bf16* __restrict__ y_perm, const float* __restrict__ w,
                                                           const int* __restrict__ dst_row, bf16* __restrict__ out, long long T, int k,
                                                           int H) {
+  pdl_trigger();
+  pdl_wait();
   const int nvec = H / 8;
   for (long long t = blockIdx.x; t < T; t += gridDim.x) {
     for (int v = threadIdx.x; v < nvec; v += 256) {
@@ -251,19 +260,19 @@ extern "C" int mb_router_topk(const float* logits, float* probs, float* topk_w, 
   if (E > 256 || K > 32) return -1;
   const unsigned blocks = static_cast<unsigned>((T + 7) / 8);
   const int epl = (E + 31) / 32;
-  if (epl <= 1) router_topk_kernel<1><<<blocks, 256, 0, s>>>(logits, probs, topk_w, topk_idx, T, E, K, normalize);
-  else if (epl <= 2) router_topk_kernel<2><<<blocks, 256, 0, s>>>(logits, probs, topk_w, topk_idx, T, E, K, normalize);
-  else if (epl <= 4) router_topk_kernel<4><<<blocks, 256, 0, s>>>(logits, probs, topk_w, topk_idx, T, E, K, normalize);
-  else router_topk_kernel<8><<<blocks, 256, 0, s>>>(logits, probs, topk_w, topk_idx, T, E, K, normalize);
-  return static_cast<int>(cudaGetLastError());
+  cudaError_t e;
+  if (epl <= 1) e = launch_pdl(router_topk_kernel<1>, dim3(blocks), dim3(256), 0, s, logits, probs, topk_w, topk_idx, T, E, K, normalize);
+  else if (epl <= 2) e = launch_pdl(router_topk_kernel<2>, dim3(blocks), dim3(256), 0, s, logits, probs, topk_w, topk_idx, T, E, K, normalize);
+  else if (epl <= 4) e = launch_pdl(router_topk_kernel<4>, dim3(blocks), dim3(256), 0, s, logits, probs, topk_w, topk_idx, T, E, K, normalize);
+  else e = launch_pdl(router_topk_kernel<8>, dim3(blocks), dim3(256), 0, s, logits, probs, topk_w, topk_idx, T, E, K, normalize);
+  return static_cast<int>(e);
 }
 
 extern "C" int mb_moe_align(const int* idx, int n, const int* n_ptr, int E, int expert_offset, int* seg_offsets, int* tile_expert,
                             int* row_src, int* dst_row, int max_rows, cudaStream_t s) {
   if (E > 2048) return -1;
-  moe_align_kernel<<<1, 1024, (3 * E + 1) * sizeof(int), s>>>(idx, n, n_ptr, E, expert_offset, seg_offsets, tile_expert, row_src,
-                                                              dst_row, max_rows);
-  return static_cast<int>(cudaGetLastError());
+  return static_cast<int>(launch_pdl(moe_align_kernel, dim3(1), dim3(1024), (3 * E + 1) * sizeof(int), s, idx, n, n_ptr, E, expert_offset,
+                                     seg_offsets, tile_expert, row_src, dst_row, max_rows));
 }
 
 extern "C" int mb_moe_gather(const void* x, void* x_perm, const int* row_src, const int* seg_offsets, int E, int k, int H,
@@ -271,9 +280,8 @@ extern "C" int mb_moe_gather(const void* x, void* x_perm, const int* row_src, co
   if (max_rows == 0) return 0;
   if (H % 8) return -1;
   const int blocks = max_rows < 148 * 16 ? max_rows : 148 * 16;
-  moe_gather_kernel<<<blocks, 256, 0, s>>>(reinterpret_cast<const bf16*>(x), reinterpret_cast<bf16*>(x_perm), row_src, seg_offsets, E,
-                                           k, H, max_rows);
-  return static_cast<int>(cudaGetLastError());
+  return static_cast<int>(launch_pdl(moe_gather_kernel, dim3(blocks), dim3(256), 0, s, reinterpret_cast<const bf16*>(x),
+                                     reinterpret_cast<bf16*>(x_perm), row_src, seg_offsets, E, k, H, max_rows));
 }
 
 extern "C" int mb_moe_combine(const void* y_perm, const float* w, const int* dst_row, void* out, long long T, int k, int H,
@@ -281,8 +289,8 @@ extern "C" int mb_moe_combine(const void* y_perm, const float* w, const int* dst
   if (T == 0) return 0;
   if (H % 8) return -1;
   const int blocks = T < 148 * 16 ? static_cast<int>(T) : 148 * 16;
-  moe_combine_kernel<<<blocks, 256, 0, s>>>(reinterpret_cast<const bf16*>(y_perm), w, dst_row, reinterpret_cast<bf16*>(out), T, k, H);
-  return static_cast<int>(cudaGetLastError());
+  return static_cast<int>(launch_pdl(moe_combine_kernel, dim3(blocks), dim3(256), 0, s, reinterpret_cast<const bf16*>(y_perm), w, dst_row,
+                                     reinterpret_cast<bf16*>(out), T, k, H));
 }
 
 extern "C" int mb_moe_combine_bwd(const void* dout, const void* y_perm, const float* w, const int* row_src, const int* seg_offsets,

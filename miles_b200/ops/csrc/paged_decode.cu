@@ -11,6 +11,7 @@
 #include <stdint.h>
 
 #include "launch.h"
+#include "pdl.cuh"
 
 namespace mbpd {
 
@@ -57,6 +58,8 @@ __global__ void __launch_bounds__(128) paged_decode_mma_kernel(const bf16* __res
   float* sM = reinterpret_cast<float*>(sV + 2 * TK * D);  // [4][8] max, [4][8] sum
   float* sL = sM + 32;
   float* sO = sL + 32;                            // [4][8][D]
+  mb::pdl_trigger();
+  mb::pdl_wait();
   const int req = blockIdx.z, hk = blockIdx.y, split = blockIdx.x;
   const int L = seq_lens[req];
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -199,6 +202,8 @@ __global__ void __launch_bounds__(128) paged_decode_mma_kernel(const bf16* __res
 template <int D>
 __global__ void paged_merge_kernel2(const float* __restrict__ part_o, const float* __restrict__ part_ml, bf16* __restrict__ out,
                                     int num_splits) {
+  mb::pdl_trigger();
+  mb::pdl_wait();
   const long long rh = blockIdx.x;
   const int d = threadIdx.x;
   float mm = -INFINITY;
@@ -239,9 +244,12 @@ extern "C" int mb_paged_decode(const void* q, const void* kc, const void* vc, co
       if (e != cudaSuccess) return static_cast<int>(e);
       once = true;
     }
-    paged_decode_mma_kernel<128><<<grid, 128, smem_bytes<128>(), s>>>(Q, KC, VC, block_table, seq_lens, part_o, part_ml, max_blocks,
-                                                                     block_size, Hq, Hkv, group, scale, num_splits);
-    paged_merge_kernel2<128><<<batch * Hq, 128, 0, s>>>(part_o, part_ml, reinterpret_cast<bf16*>(out), num_splits);
+    cudaError_t e = mb::launch_pdl(paged_decode_mma_kernel<128>, grid, dim3(128), smem_bytes<128>(), s, Q, KC, VC, block_table, seq_lens, part_o,
+                               part_ml, max_blocks, block_size, Hq, Hkv, group, scale, num_splits);
+    if (e != cudaSuccess) return static_cast<int>(e);
+    e = mb::launch_pdl(paged_merge_kernel2<128>, dim3(batch * Hq), dim3(128), 0, s, static_cast<const float*>(part_o),
+                   static_cast<const float*>(part_ml), reinterpret_cast<bf16*>(out), num_splits);
+    if (e != cudaSuccess) return static_cast<int>(e);
   } else if (D == 64) {
     static bool once = false;
     if (!once) {
@@ -250,9 +258,12 @@ extern "C" int mb_paged_decode(const void* q, const void* kc, const void* vc, co
       if (e != cudaSuccess) return static_cast<int>(e);
       once = true;
     }
-    paged_decode_mma_kernel<64><<<grid, 128, smem_bytes<64>(), s>>>(Q, KC, VC, block_table, seq_lens, part_o, part_ml, max_blocks,
-                                                                   block_size, Hq, Hkv, group, scale, num_splits);
-    paged_merge_kernel2<64><<<batch * Hq, 64, 0, s>>>(part_o, part_ml, reinterpret_cast<bf16*>(out), num_splits);
+    cudaError_t e = mb::launch_pdl(paged_decode_mma_kernel<64>, grid, dim3(128), smem_bytes<64>(), s, Q, KC, VC, block_table, seq_lens, part_o,
+                               part_ml, max_blocks, block_size, Hq, Hkv, group, scale, num_splits);
+    if (e != cudaSuccess) return static_cast<int>(e);
+    e = mb::launch_pdl(paged_merge_kernel2<64>, dim3(batch * Hq), dim3(64), 0, s, static_cast<const float*>(part_o),
+                   static_cast<const float*>(part_ml), reinterpret_cast<bf16*>(out), num_splits);
+    if (e != cudaSuccess) return static_cast<int>(e);
   } else {
     return -1;
   }

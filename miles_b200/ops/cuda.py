@@ -136,9 +136,39 @@ class _Linear(torch.autograd.Function):
         return gx, gw, gb
 
 
+class _LinearMXFP8(torch.autograd.Function):
+    """y = MXFP8(x)·MXFP8(W)ᵀ on the block-scaled tensor-core path; gradients use the bf16 GEMMs on the unquantised
+    operands (straight-through), the `--fp8-recipe mxfp8` forward of the reference's TE recipe."""
+
+    @staticmethod
+    def forward(ctx, x, w, bias):
+        from . import extra
+
+        shp = x.shape
+        x2 = x.reshape(-1, shp[-1])
+        ctx.save_for_backward(x2, w)
+        ctx.has_bias, ctx.shp = bias is not None, shp
+        xq, xs = mxfp8_quant(x2)                   # noqa: F821  (defined in cuda_more, imported at the end of this module)
+        wq, ws = mxfp8_quant(w)                    # noqa: F821
+        y = extra.gemm_mxfp8(xq, xs, wq, ws)
+        if bias is not None:
+            y = y + bias
+        return y.view(*shp[:-1], w.shape[0])
+
+    @staticmethod
+    def backward(ctx, gy):
+        return _Linear.backward(ctx, gy)
+
+
+# `--fp8-recipe mxfp8` (or MILES_MXFP8_LINEAR=1): projections whose K is a multiple of 128 run their forward in MXFP8
+MXFP8_LINEAR = os.environ.get("MILES_MXFP8_LINEAR", "0") == "1"
+
+
 def linear(x, w, bias=None):
     if x.dtype != BF16:
         return torch.nn.functional.linear(x, w.to(x.dtype), bias)
+    if MXFP8_LINEAR and w.dim() == 2 and w.shape[1] % 128 == 0 and w.shape[0] >= 128:
+        return _LinearMXFP8.apply(x, w, bias)
     return _Linear.apply(x, w, bias)
 
 

@@ -67,7 +67,8 @@ def paged_attention(q, k_cache, v_cache, block_table, seq_lens, q_lens=None, max
         return ref.paged_attention(q, k_cache, v_cache, block_table, seq_lens)
     q = _c(q)
     out = torch.empty_like(q)
-    splits = _DECODE_SPLITS
+    # enough (request, kv head, split) CTAs for two waves of the 148 SMs, never more splits than that needs
+    splits = max(1, min(_DECODE_SPLITS, -(-296 // (B * k_cache.shape[2]))))
     part_o = torch.empty(B * Hq * splits * D, dtype=torch.float32, device=q.device)
     part_ml = torch.empty(B * Hq * splits * 2, dtype=torch.float32, device=q.device)
     C.paged_decode(q, k_cache, v_cache, block_table, seq_lens, out, part_o, part_ml, 1.0 / math.sqrt(D), splits)

@@ -89,6 +89,10 @@ class TrainActor:
         self.cfg = cfg or model_config_from_args(args)
         dtype = torch.float32 if getattr(args, "fp32", False) or not getattr(args, "bf16", True) else torch.bfloat16
         torch.manual_seed(args.seed)
+        if getattr(args, "fp8_recipe", None) == "mxfp8" and self.device.type == "cuda":
+            from ..ops import cuda as _cuda_ops
+
+            _cuda_ops.MXFP8_LINEAR = True       # projections run their forward on the block-scaled MXFP8 tensor-core path
         provider = getattr(args, "custom_model_provider_path", None)
         if provider:
             from ..utils.misc import load_function

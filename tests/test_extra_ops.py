@@ -147,6 +147,25 @@ def test_mxfp8_block_scaled_gemm(M, N, K):
 
 
 @pytest.mark.gpu
+def test_mxfp8_linear_autograd(monkeypatch):
+    """`--fp8-recipe mxfp8`: forward on the MXFP8 path (close to bf16), backward the exact bf16 gradients."""
+    from miles_b200.ops import cuda as K_
+
+    torch.manual_seed(7)
+    x = torch.randn(300, 512, device="cuda").bfloat16().requires_grad_()
+    w = (torch.randn(384, 512, device="cuda") * 0.05).bfloat16().requires_grad_()
+    y0 = K_.linear(x, w)
+    g = torch.randn_like(y0)
+    gx0, gw0 = torch.autograd.grad(y0, (x, w), g)
+    monkeypatch.setattr(K_, "MXFP8_LINEAR", True)
+    y1 = K_.linear(x, w)
+    gx1, gw1 = torch.autograd.grad(y1, (x, w), g)
+    rel = ((y1.float() - y0.float()).norm() / y0.float().norm()).item()
+    assert 0 < rel < 0.06, rel
+    assert torch.equal(gx0, gx1) and torch.equal(gw0, gw1)
+
+
+@pytest.mark.gpu
 def test_quant_tool_kernels_and_host_gather():
     torch.manual_seed(5)
     x = (torch.randn(300, 512, device="cuda") * 2).bfloat16()
