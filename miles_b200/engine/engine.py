@@ -497,6 +497,29 @@ class Engine:
             return None
         return torch.full((n_tokens,), int(self.lora_slot), dtype=torch.long, device=self.device)
 
+    def enable_mxfp8_serving(self) -> int:
+        """Serve the dense projections from MXFP8 copies (e4m3 payload + e8m0 scales per 1×32 block): allocates the
+        quantised buffers, fills them from the current weights and registers them with the linear op.  Weight updates
+        refresh them in one fused quantisation launch per bucket (`weight_update` with the engine's `quant_buffers`).
+        Returns the number of bytes of quantised weights."""
+        from ..ops import cuda as K
+        from ..parallel.weight_sync import _skip_quant, fused_weight_sync
+
+        assert self.device.type == "cuda", "MXFP8 serving needs the CUDA block-scaled GEMM"
+        self.quant_buffers = {}
+        total = 0
+        for n, p in self.model.named_parameters():
+            if p.dim() != 2 or p.dtype != torch.bfloat16 or _skip_quant(n, p) or p.shape[1] % 128 or p.shape[0] < 128:
+                continue
+            payload = torch.empty(p.numel(), dtype=torch.uint8, device=p.device)
+            scales = torch.empty(p.numel() // 32, dtype=torch.uint8, device=p.device)
+            self.quant_buffers[n] = (payload, scales)
+            K.register_mxfp8_weight(p.data, payload, scales)
+            total += payload.numel() + scales.numel()
+        fused_weight_sync(type("A", (), {"model": self.model, "args": type("Args", (), {"update_weight_buffer_size": 512 << 20})()})(),
+                          self, quant="mxfp8")
+        return total
+
     def _run_prefill(self, batch: list[Request]):
         toks, pos, slots, cu = [], [], [], [0]
         for r in batch:

@@ -53,6 +53,27 @@ void gemm_splitk(const at::Tensor& A, const at::Tensor& B, at::Tensor& C, int64_
         "mb_gemm_bf16_splitk");
 }
 
+// C[tokens, N] = X[tokens, K] · W[N, K]ᵀ with the weight rows on the 128-row MMA side (decode-sized token counts)
+void gemm_small(const at::Tensor& X, const at::Tensor& W, at::Tensor& C, int64_t tokens, int64_t N, int64_t K, int64_t ldc,
+                const c10::optional<at::Tensor>& bias, int64_t bt, int64_t split_k, const c10::optional<at::Tensor>& ws,
+                const c10::optional<at::Tensor>& counters) {
+  c10::cuda::CUDAGuard g(X.device());
+  int* ef = error_flag_for(X.device()).data_ptr<int>();
+  check(mb_gemm_small(X.data_ptr(), W.data_ptr(), C.data_ptr(), tokens, N, K, K, K, ldc, C.scalar_type() == at::kFloat, cptr(bias), bt,
+                      split_k, ws.has_value() && ws->defined() ? ws->data_ptr<float>() : nullptr,
+                      counters.has_value() && counters->defined() ? counters->data_ptr<int>() : nullptr, ef, cur_stream()),
+        "mb_gemm_small");
+}
+
+void gemm_small_grouped(const at::Tensor& X, const at::Tensor& W, at::Tensor& C, int64_t rows, int64_t N, int64_t K, int64_t E,
+                        const at::Tensor& tile_expert, const c10::optional<at::Tensor>& used_rows, int64_t bt) {
+  c10::cuda::CUDAGuard g(X.device());
+  int* ef = error_flag_for(X.device()).data_ptr<int>();
+  check(mb_gemm_small_grouped(X.data_ptr(), W.data_ptr(), C.data_ptr(), rows, N, K, E, tile_expert.data_ptr<int>(),
+                              used_rows.has_value() && used_rows->defined() ? used_rows->data_ptr<int>() : nullptr, bt, ef, cur_stream()),
+        "mb_gemm_small_grouped");
+}
+
 void gemm_grouped(const at::Tensor& A, const at::Tensor& B, at::Tensor& C, int64_t M_pad, int64_t N, int64_t K, int64_t E,
                   const at::Tensor& tile_expert, bool b_mn, int64_t force_bn) {
   c10::cuda::CUDAGuard g(A.device());
@@ -188,6 +209,8 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("gemm", &gemm);
   m.def("gemm_splitk", &gemm_splitk);
   m.def("gemm_grouped", &gemm_grouped);
+  m.def("gemm_small", &gemm_small);
+  m.def("gemm_small_grouped", &gemm_small_grouped);
   m.def("gemm_grouped_wgrad", &gemm_grouped_wgrad);
   m.def("rmsnorm_fwd", &rmsnorm_fwd);
   m.def("rmsnorm_bwd", &rmsnorm_bwd);

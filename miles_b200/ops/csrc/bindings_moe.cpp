@@ -34,19 +34,20 @@ std::vector<at::Tensor> router_topk(const at::Tensor& logits, int64_t K, bool no
   return {w, idx, probs};
 }
 
-// idx int32 [n] global expert ids → seg_offsets [E+1], tile_expert [max_rows/128], row_src [max_rows], dst_row [n]
+// idx int32 [n] global expert ids → seg_offsets [E+1], tile_expert [max_rows/pad], row_src [max_rows], dst_row [n]
 std::vector<at::Tensor> moe_align(const at::Tensor& idx, int64_t E, int64_t expert_offset, int64_t max_rows,
-                                  const c10::optional<at::Tensor>& n_dev) {
+                                  const c10::optional<at::Tensor>& n_dev, int64_t pad) {
   c10::cuda::CUDAGuard g(idx.device());
   const int64_t n = idx.numel();
   const int* n_ptr = n_dev.has_value() && n_dev->defined() ? n_dev->data_ptr<int>() : nullptr;
   auto opt = idx.options().dtype(at::kInt);
   auto seg = at::empty({E + 1}, opt);
-  auto tile = at::empty({max_rows / 128}, opt);
+  TORCH_CHECK(pad > 0 && max_rows % pad == 0, "moe_align: max_rows must be a multiple of pad");
+  auto tile = at::empty({max_rows / pad}, opt);
   auto row_src = at::empty({max_rows}, opt);
   auto dst_row = at::empty({n}, opt);
-  check(mb_moe_align(idx.data_ptr<int>(), n, n_ptr, E, expert_offset, seg.data_ptr<int>(), tile.data_ptr<int>(), row_src.data_ptr<int>(),
-                     dst_row.data_ptr<int>(), max_rows, cur_stream()),
+  check(mb_moe_align_pad(idx.data_ptr<int>(), n, n_ptr, E, expert_offset, seg.data_ptr<int>(), tile.data_ptr<int>(),
+                         row_src.data_ptr<int>(), dst_row.data_ptr<int>(), max_rows, pad, cur_stream()),
         "mb_moe_align");
   return {seg, tile, row_src, dst_row};
 }
@@ -78,7 +79,8 @@ void moe_combine_bwd(const at::Tensor& dout, const at::Tensor& y_perm, const at:
 
 void register_moe(pybind11::module& m) {
   m.def("router_topk", &router_topk);
-  m.def("moe_align", &moe_align);
+  m.def("moe_align", &moe_align, py::arg("idx"), py::arg("E"), py::arg("expert_offset"), py::arg("max_rows"), py::arg("n_dev"),
+        py::arg("pad") = 128);
   m.def("moe_gather", &moe_gather);
   m.def("moe_combine", &moe_combine);
   m.def("moe_combine_bwd", &moe_combine_bwd);

@@ -22,6 +22,11 @@ int mb_gemm_bf16_splitk(const void* A, const void* B, void* C, int M, int N, int
                         cudaStream_t stream);
 int mb_gemm_bf16_grouped(const void* A, const void* B, void* C, int M_pad, int N, int K, int num_experts,
                          const int* tile_expert, int b_mn, int out_fp32, int force_bn, int* error_flag, cudaStream_t stream);
+// ---- gemm_small.cu: weights on the 128-row MMA side, tokens in tiles of bt ∈ {16, 32, 64} ----
+int mb_gemm_small(const void* X, const void* W, void* C, int tokens, int N, int K, long long ldx, long long ldw, long long ldc,
+                  int out_fp32, const void* bias, int bt, int split_k, float* ws, int* counters, int* error_flag, cudaStream_t stream);
+int mb_gemm_small_grouped(const void* X, const void* W, void* C, int rows, int N, int K, int num_experts, const int* tile_expert,
+                          const int* used_rows, int bt, int* error_flag, cudaStream_t stream);
 int mb_gemm_bf16_grouped_wgrad(const void* dY, const void* X, void* dW, int M_pad, int N, int K, int num_experts,
                                const int* seg_offsets, int out_fp32, int accumulate, int force_bn, int* error_flag,
                                cudaStream_t stream);
@@ -90,6 +95,8 @@ int mb_router_topk(const float* logits, float* probs, float* topk_w, int* topk_i
                    cudaStream_t s);
 int mb_moe_align(const int* idx, int n, const int* n_ptr, int E, int expert_offset, int* seg_offsets, int* tile_expert, int* row_src,
                  int* dst_row, int max_rows, cudaStream_t s);
+int mb_moe_align_pad(const int* idx, int n, const int* n_ptr, int E, int expert_offset, int* seg_offsets, int* tile_expert,
+                     int* row_src, int* dst_row, int max_rows, int pad, cudaStream_t s);
 int mb_moe_gather(const void* x, void* x_perm, const int* row_src, const int* seg_offsets, int E, int k, int H, int max_rows,
                   cudaStream_t s);
 int mb_moe_combine(const void* y_perm, const float* w, const int* dst_row, void* out, long long T, int k, int H, cudaStream_t s);

@@ -91,10 +91,10 @@ __global__ void __launch_bounds__(256) router_topk_kernel(const float* __restric
 
 // ---------------------------------------------------------------------------------------------
 // Single-CTA counting sort.  idx[n] holds global expert ids; local expert = id − expert_offset, others skipped.
-// Outputs: seg_offsets[E+1] (padded to 128), tile_expert[max_tiles], row_src[max_rows], dst_row[n].
+// Outputs: seg_offsets[E+1] (segments padded to `pad` rows), tile_expert[max_rows / pad], row_src[max_rows], dst_row[n].
 __global__ void __launch_bounds__(1024) moe_align_kernel(const int* __restrict__ idx, int n, const int* __restrict__ n_ptr, int E,
                                                          int expert_offset, int* __restrict__ seg_offsets, int* __restrict__ tile_expert,
-                                                         int* __restrict__ row_src, int* __restrict__ dst_row, int max_rows) {
+                                                         int* __restrict__ row_src, int* __restrict__ dst_row, int max_rows, int pad) {
   extern __shared__ int sh[];  // counts[E], cursor[E], seg[E+1]
   pdl_trigger();
   pdl_wait();
@@ -113,15 +113,15 @@ __global__ void __launch_bounds__(1024) moe_align_kernel(const int* __restrict__
     int off = 0;
     for (int e = 0; e < E; ++e) {
       seg[e] = off;
-      off += (counts[e] + kPad - 1) / kPad * kPad;
+      off += (counts[e] + pad - 1) / pad * pad;
     }
     seg[E] = off;
   }
   __syncthreads();
   for (int e = threadIdx.x; e <= E; e += blockDim.x) seg_offsets[e] = seg[e];
-  const int max_tiles = max_rows / kPad;
+  const int max_tiles = max_rows / pad;
   for (int t = threadIdx.x; t < max_tiles; t += blockDim.x) {
-    const int row = t * kPad;
+    const int row = t * pad;
     int ex = -1;
     if (row < seg[E]) {
       int lo = 0, hi = E;   // last e with seg[e] <= row
@@ -268,11 +268,17 @@ extern "C" int mb_router_topk(const float* logits, float* probs, float* topk_w, 
   return static_cast<int>(e);
 }
 
+// pad: rows every expert segment is rounded up to (128 for the training GEMMs, 16/32/64 for the decode-sized grouped GEMM)
+extern "C" int mb_moe_align_pad(const int* idx, int n, const int* n_ptr, int E, int expert_offset, int* seg_offsets, int* tile_expert,
+                                int* row_src, int* dst_row, int max_rows, int pad, cudaStream_t s) {
+  if (E > 2048 || pad <= 0) return -1;
+  return static_cast<int>(launch_pdl(moe_align_kernel, dim3(1), dim3(1024), (3 * E + 1) * sizeof(int), s, idx, n, n_ptr, E, expert_offset,
+                                     seg_offsets, tile_expert, row_src, dst_row, max_rows, pad));
+}
+
 extern "C" int mb_moe_align(const int* idx, int n, const int* n_ptr, int E, int expert_offset, int* seg_offsets, int* tile_expert,
                             int* row_src, int* dst_row, int max_rows, cudaStream_t s) {
-  if (E > 2048) return -1;
-  return static_cast<int>(launch_pdl(moe_align_kernel, dim3(1), dim3(1024), (3 * E + 1) * sizeof(int), s, idx, n, n_ptr, E, expert_offset,
-                                     seg_offsets, tile_expert, row_src, dst_row, max_rows));
+  return mb_moe_align_pad(idx, n, n_ptr, E, expert_offset, seg_offsets, tile_expert, row_src, dst_row, max_rows, kPad, s);
 }
 
 extern "C" int mb_moe_gather(const void* x, void* x_perm, const int* row_src, const int* seg_offsets, int E, int k, int H,

@@ -49,6 +49,8 @@ def gemm_nt(a: torch.Tensor, b: torch.Tensor, out: torch.Tensor | None = None, *
     if out is None:
         out = torch.empty(M, N, dtype=out_dtype or BF16, device=a.device)
     if M and N:
+        if M <= SMALL_M and not accumulate and not force_bn and K >= 256:
+            return _gemm_small(a, b, out, bias, M, N, K)
         split = _pick_split_k(M, N, K) if not force_bn and SPLIT_K else 1
         if split > 1:
             ws, counters = _splitk_workspace(a.device)
@@ -82,6 +84,41 @@ def _splitk_workspace(device):
         _splitk_ws[key] = (torch.empty(148 * 128 * 64, dtype=torch.float32, device=device),
                            torch.zeros(4 * _SPLITK_MAX_TILES * 2, dtype=torch.int32, device=device))
     return _splitk_ws[key]
+
+
+# Decode-sized token counts: the weight rows go on the 128-row side of the MMA and the tokens on the N side in tiles of
+# 16/32/64 (gemm_small.cu), so no pipeline byte is spent on padding rows; split-K fills the SMs.  0 turns the path off.
+SMALL_M = int(os.environ.get("MILES_SMALL_M", "64"))
+_SMALL_WS_FLOATS, _SMALL_MAX_TILES = 4 << 20, 4096
+_small_ws: dict = {}
+
+
+def small_bt(rows: int) -> int:
+    return 16 if rows <= 16 else 32 if rows <= 32 else 64
+
+
+def _small_split(M: int, N: int, K: int, bt: int) -> int:
+    out_tiles = ((N + 127) // 128) * ((M + bt - 1) // bt)
+    kblocks = (K + 63) // 64
+    split = max(1, min(round(148 / out_tiles), kblocks // 2, 32))
+    if split > 1 and (out_tiles > _SMALL_MAX_TILES or split * M * N > _SMALL_WS_FLOATS):
+        return 1
+    per = -(-kblocks // split)
+    return -(-kblocks // per)          # every slice gets at least one K block
+
+
+def _gemm_small(a, b, out, bias, M, N, K):
+    bt = small_bt(M)
+    split = _small_split(M, N, K, bt)
+    ws = counters = None
+    if split > 1:
+        key = a.device.index if a.device.index is not None else torch.cuda.current_device()
+        if key not in _small_ws:
+            _small_ws[key] = (torch.empty(_SMALL_WS_FLOATS, dtype=torch.float32, device=a.device),
+                              torch.zeros(4 * _SMALL_MAX_TILES, dtype=torch.int32, device=a.device))
+        ws, counters = _small_ws[key]
+    C.gemm_small(a, b, out, M, N, K, out.stride(0), bias, bt, split, ws, counters)
+    return out
 
 
 def gemm_nn(a: torch.Tensor, b: torch.Tensor, out: torch.Tensor | None = None, *, out_dtype=None, force_bn: int = 0):
@@ -164,9 +201,31 @@ class _LinearMXFP8(torch.autograd.Function):
 MXFP8_LINEAR = os.environ.get("MILES_MXFP8_LINEAR", "0") == "1"
 
 
+# Inference with pre-quantised weights: the rollout engine registers (payload, scales) for a projection weight; calls
+# made without autograd then skip the bf16 weight entirely (half the weight bytes per decode step).
+_MXFP8_WEIGHTS: dict[int, tuple[torch.Tensor, torch.Tensor]] = {}
+MXFP8_MIN_ROWS = 256
+
+
+def register_mxfp8_weight(w: torch.Tensor, payload: torch.Tensor, scales: torch.Tensor):
+    _MXFP8_WEIGHTS[w.data_ptr()] = (payload, scales)
+
+
+def clear_mxfp8_weights():
+    _MXFP8_WEIGHTS.clear()
+
+
 def linear(x, w, bias=None):
     if x.dtype != BF16:
         return torch.nn.functional.linear(x, w.to(x.dtype), bias)
+    if _MXFP8_WEIGHTS and not torch.is_grad_enabled():
+        reg = _MXFP8_WEIGHTS.get(w.data_ptr())
+        # the block-scaled kernel works on 128×128 tiles: decode-sized batches stay on the split-K bf16 path
+        if reg is not None and x.numel() // x.shape[-1] >= MXFP8_MIN_ROWS:
+            from . import extra
+
+            y = extra.linear_mxfp8(x, reg[0].view(w.shape), reg[1].view(w.shape[0], -1))
+            return y if bias is None else y + bias
     if MXFP8_LINEAR and w.dim() == 2 and w.shape[1] % 128 == 0 and w.shape[0] >= 128:
         return _LinearMXFP8.apply(x, w, bias)
     return _Linear.apply(x, w, bias)

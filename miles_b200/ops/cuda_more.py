@@ -122,17 +122,57 @@ def moe_max_rows(n_pairs: int, num_experts: int) -> int:
     return (n_pairs + num_experts * 127 + 127) // 128 * 128
 
 
-def experts_forward(x_perm, w13, w2, seg, tile):
-    """Grouped expert FFN on expert-sorted, 128-padded rows. Returns (h1 pre-activation, y_perm)."""
+# Inference with few tokens per expert (decode): segments are padded to 16/32/64 rows instead of 128 and the grouped
+# GEMMs run with the expert weights on the 128-row MMA side (gemm_small.cu).  MILES_SMALL_MOE=0 turns the path off.
+SMALL_MOE_AVG = float(os.environ.get("MILES_SMALL_MOE_AVG", "32")) if os.environ.get("MILES_SMALL_MOE", "1") != "0" else 0.0
+
+
+def small_moe_bt(n_pairs: int, num_experts: int, w13, w2) -> int:
+    """Row granularity for an inference MoE call: 128 (general path) or a decode-sized tile."""
+    if SMALL_MOE_AVG <= 0 or torch.is_grad_enabled() or w13.shape[1] % 128 or w2.shape[1] % 128:
+        return 128
+    avg = n_pairs / max(num_experts, 1)
+    if avg > SMALL_MOE_AVG:
+        return 128
+    return 16 if avg <= 6 else 32 if avg <= 16 else 64
+
+
+def moe_max_rows_pad(n_pairs: int, num_experts: int, pad: int) -> int:
+    return (n_pairs + num_experts * (pad - 1) + pad - 1) // pad * pad
+
+
+def experts_forward(x_perm, w13, w2, seg, tile, bt: int = 128):
+    """Grouped expert FFN on expert-sorted rows whose segments are padded to `bt`. Returns (h1 pre-activation, y_perm)."""
     max_rows, H = x_perm.shape
     E, F2, _ = w13.shape
     h1 = torch.empty(max_rows, F2, dtype=x_perm.dtype, device=x_perm.device)
-    C.gemm_grouped(x_perm, w13, h1, max_rows, F2, H, E, tile, False, 0)
     act = torch.empty(max_rows, F2 // 2, dtype=x_perm.dtype, device=x_perm.device)
-    C.swiglu_fwd(h1, act, seg[-1:])
     y_perm = torch.empty(max_rows, H, dtype=x_perm.dtype, device=x_perm.device)
+    if bt != 128:
+        C.gemm_small_grouped(x_perm, w13, h1, max_rows, F2, H, E, tile, seg[-1:], bt)
+        C.swiglu_fwd(h1, act, seg[-1:])
+        C.gemm_small_grouped(act, w2, y_perm, max_rows, H, F2 // 2, E, tile, seg[-1:], bt)
+        return h1, y_perm
+    C.gemm_grouped(x_perm, w13, h1, max_rows, F2, H, E, tile, False, 0)
+    C.swiglu_fwd(h1, act, seg[-1:])
     C.gemm_grouped(act, w2, y_perm, max_rows, H, F2 // 2, E, tile, False, 0)
     return h1, y_perm
+
+
+def _moe_ffn_small(x, w13, w2, topk_w, topk_idx, expert_offset, bt):
+    T, H = x.shape
+    E = w13.shape[0]
+    k = topk_idx.shape[1]
+    x = _c(x)
+    idx32 = _c(topk_idx.to(torch.int32)).view(-1)
+    max_rows = moe_max_rows_pad(T * k, E, bt)
+    seg, tile, row_src, dst_row = C.moe_align(idx32, E, expert_offset, max_rows, None, bt)
+    x_perm = torch.empty(max_rows, H, dtype=x.dtype, device=x.device)
+    C.moe_gather(x, x_perm, row_src, seg, k)
+    _, y_perm = experts_forward(x_perm, _c(w13), _c(w2), seg, tile, bt)
+    out = torch.empty(T, H, dtype=x.dtype, device=x.device)
+    C.moe_combine(y_perm, _c(topk_w.float()), dst_row, out, k)
+    return out
 
 
 def experts_backward(dy_perm, x_perm, h1, w13, w2, seg, tile):
@@ -219,6 +259,9 @@ class _MoEFFN(torch.autograd.Function):
 def moe_ffn(x, w13, w2, topk_w, topk_idx, expert_offset: int = 0):
     if x.dtype != BF16:
         return ref.moe_ffn(x, w13, w2, topk_w, topk_idx)
+    bt = small_moe_bt(topk_idx.numel(), w13.shape[0], w13, w2)
+    if bt != 128 and x.shape[0]:
+        return _moe_ffn_small(x, w13, w2, topk_w, topk_idx, int(expert_offset), bt)
     return _MoEFFN.apply(x, w13, w2, topk_w, topk_idx, int(expert_offset))
 
 

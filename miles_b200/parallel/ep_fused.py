@@ -15,7 +15,7 @@ from __future__ import annotations
 
 import torch
 
-from ..ops.cuda_more import experts_backward, experts_forward, moe_max_rows
+from ..ops.cuda_more import experts_backward, experts_forward, moe_max_rows_pad, small_moe_bt
 from .fabric import CH_EP, CH_EP2
 
 CAPACITY_FACTOR = 2.0       # receive rows per rank = factor × max_tokens × k (uniform routing gives 1.0)
@@ -69,12 +69,14 @@ class _FusedMoE(torch.autograd.Function):
         fab.barrier(ranks, CH_EP)
         C.recv_expert_ids(b.recv_meta, b.counter, b.cap, b.expert_ids, b.n_recv)
         b.counter.zero_()
-        max_rows = moe_max_rows(b.cap, e_local)
-        seg, tile, row_src, _ = C.moe_align(b.expert_ids, e_local, 0, max_rows, b.n_recv)
+        need_bwd = any(ctx.needs_input_grad[:4])
+        # decode-sized calls (about n_pairs rows arrive when the routing is balanced): pad segments to 16/32/64 rows
+        bt = 128 if need_bwd else small_moe_bt(n_pairs, e_local, w13, w2)
+        max_rows = moe_max_rows_pad(b.cap, e_local, bt)
+        seg, tile, row_src, _ = C.moe_align(b.expert_ids, e_local, 0, max_rows, b.n_recv, bt)
         x_perm = torch.empty(max_rows, H, dtype=x.dtype, device=x.device)
         C.moe_gather(b.recv_x.view(b.cap, H), x_perm, row_src, seg, 1)
-        h1, y_perm = experts_forward(x_perm, w13, w2, seg, tile)
-        need_bwd = any(ctx.needs_input_grad[:4])
+        h1, y_perm = experts_forward(x_perm, w13, w2, seg, tile, bt)
         meta = b.recv_meta.clone() if need_bwd else b.recv_meta   # the shared buffer is overwritten by the next layer
         C.moe_return(y_perm, row_src, b.recv_meta, seg, b.ret_ptrs, ep)
         fab.barrier(ranks, CH_EP2)

@@ -100,6 +100,11 @@ def fused_weight_sync(actor, engine, quant: str | None = None, bucket_bytes: int
                 dptr = dst_ptrs[n] if dst_ptrs is not None else d.data_ptr()
                 nbytes = p.numel() * p.element_size()
                 if quant in ("mxfp8", "mxfp8_qdq") and not _skip_quant(n, p) and p.dtype == torch.bfloat16:
+                    if quant == "mxfp8" and n not in getattr(engine, "quant_buffers", {}):
+                        if p.data_ptr() != dptr:            # not served in MXFP8 (e.g. stacked expert weights): plain copy
+                            copies.append((p.data_ptr(), dptr, nbytes, 0))
+                            total += nbytes
+                        continue
                     if quant == "mxfp8":
                         payload, scales = engine.quant_buffers[n]
                         quants.append((p.data_ptr(), payload.data_ptr(), p.numel(), scales.data_ptr()))
@@ -107,7 +112,7 @@ def fused_weight_sync(actor, engine, quant: str | None = None, bucket_bytes: int
                     else:
                         quants.append((p.data_ptr(), dptr, p.numel(), 0))
                         total += nbytes
-                else:
+                elif p.data_ptr() != dptr:                 # aliased tensors (engine built on the trainer's model) need no copy
                     assert d.dtype == p.dtype, f"dtype mismatch for {n}"
                     copies.append((p.data_ptr(), dptr, nbytes, 0))
                     total += nbytes

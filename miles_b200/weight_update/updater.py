@@ -83,7 +83,13 @@ class WeightUpdater:
 
     # ---- protocols -----------------------------------------------------------------------
     def _send_alias(self) -> int:
-        return 0
+        n = 0
+        for e in self.engines:                         # engines that serve MXFP8 copies of the shared bf16 weights
+            if getattr(e, "quant_buffers", None):
+                from ..parallel import weight_sync
+
+                n += weight_sync.fused_weight_sync(self.actor, e, quant="mxfp8")
+        return n
 
     def _send_nvlink(self) -> int:
         from ..parallel import weight_sync

@@ -121,10 +121,12 @@ def _dist_hist(tmp_path, extra, world=2):
     "--model-name tiny-moe --expert-model-parallel-size 2",                 # dp2 × ep2
     "--context-parallel-size 2 --cp-comm-type a2a",                         # cp2 (Ulysses), dp1
     "--pipeline-model-parallel-size 2 --micro-batch-size 8",                # pp2, 4 micro-batches per step
+    # the tiny plumbing config: 16 prompts of length 32 per step, groups of 4, 32 new tokens, lr 1e-5, 3 steps
+    "--rollout-batch-size 16 --synthetic-prompt-len 32 32 --rollout-max-response-len 32 --lr 1e-5 --num-rollout 3 --kl-coef 0",
 ])
 def test_grpo_two_ranks(tmp_path, extra):
     rows = _dist_hist(tmp_path, extra)
-    assert len(rows) == 2
+    assert len(rows) == (3 if "--num-rollout 3" in extra else 2)
     assert max(r["train/train_rollout_logprob_abs_diff"] for r in rows) < 1e-5
     assert abs(rows[0]["train/ppo_kl"]) < 1e-6
     assert all(r["train/grad_norm"] > 0 for r in rows)

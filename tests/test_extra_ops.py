@@ -147,6 +147,41 @@ def test_mxfp8_block_scaled_gemm(M, N, K):
 
 
 @pytest.mark.gpu
+def test_engine_mxfp8_serving_refreshes_with_weights():
+    from types import SimpleNamespace
+
+    from miles_b200.engine.engine import Engine
+    from miles_b200.models.config import PRESETS
+    from miles_b200.ops import cuda as K_
+    from miles_b200.weight_update.updater import WeightUpdater
+
+    eng = Engine(PRESETS["tiny"], device="cuda", dtype=torch.bfloat16, seed=0, num_blocks=64, block_size=64, use_cuda_graph=False)
+    prompt = list(range(5, 305))                              # 300 tokens: the prefill runs on the MXFP8 path
+    sp = {"temperature": 0.0, "max_new_tokens": 1}
+    base = eng.generate(prompt, sp)["meta_info"]["output_token_logprobs"][0]
+    try:
+        nbytes = eng.enable_mxfp8_serving()
+        assert nbytes > 0 and "layers.0.attn.wqkv" in eng.quant_buffers and "layers.0.ln1" not in eng.quant_buffers
+        q = eng.generate(prompt, sp)["meta_info"]["output_token_logprobs"][0]
+        assert abs(q[0] - base[0]) < 0.25 and q[0] != base[0]  # quantised projections: close, not identical
+        # weights change (alias mode: same tensors) → the update refreshes the quantised copies
+        w = eng.model.layers[0].attn.wqkv
+        before = eng.quant_buffers["layers.0.attn.wqkv"][0].clone()
+        with torch.no_grad():
+            w.mul_(1.5)
+        actor = SimpleNamespace(model=eng.model, args=SimpleNamespace(update_weight_buffer_size=1 << 20), weight_version=1,
+                                device=torch.device("cuda"))
+        info = WeightUpdater(actor.args, actor, [eng]).update_weights()
+        assert info["mode"] == "alias" and info["bytes"] > 0
+        qd, sc = ref.mxfp8_quant(w.detach().cpu())
+        got_payload, got_scales = eng.quant_buffers["layers.0.attn.wqkv"]
+        assert torch.equal(got_payload.cpu().view(torch.float8_e4m3fn).float().view(-1), qd.float().view(-1))
+        assert torch.equal(got_scales.cpu().view(-1), sc.view(-1)) and not torch.equal(got_payload, before)
+    finally:
+        K_.clear_mxfp8_weights()
+
+
+@pytest.mark.gpu
 def test_mxfp8_linear_autograd(monkeypatch):
     """`--fp8-recipe mxfp8`: forward on the MXFP8 path (close to bf16), backward the exact bf16 gradients."""
     from miles_b200.ops import cuda as K_
