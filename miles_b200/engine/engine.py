@@ -144,7 +144,10 @@ class Engine:
         self.local_done = True
         self.global_done = True
         self.runner = None
-        if self.device.type == "cuda" and dtype == torch.bfloat16:
+        # models whose mixers keep no paged KV (latent / linear attention of the other families) are served by scoring the
+        # whole sequence again every step: correct for any block, quadratic in length — the functional path for those families
+        self.stateless = not getattr(self.model, "supports_kv_cache", True)
+        if self.device.type == "cuda" and dtype == torch.bfloat16 and not self.stateless:
             from .decode_runner import DecodeRunner
 
             # expert-parallel dispatch over NCCL synchronises with the host, so it cannot be captured
@@ -534,7 +537,8 @@ class Engine:
             positions=torch.tensor(pos, dtype=torch.int32, device=dev),
             cu_seqlens=torch.tensor(cu, dtype=torch.int32, device=dev),
             max_seqlen=max((len(r.all_ids) for r in batch), default=0),
-            kv_cache=self.kv.layers, slot_mapping=torch.tensor(slots, dtype=torch.int64, device=dev),
+            kv_cache=None if self.stateless else self.kv.layers,
+            slot_mapping=None if self.stateless else torch.tensor(slots, dtype=torch.int64, device=dev),
             record_topk=record, lora_slots=self._lora_slots(len(toks)))
         hidden = self.model(torch.tensor(toks, dtype=torch.int32, device=dev), meta)
         if not batch:
@@ -563,12 +567,19 @@ class Engine:
             r.num_cached = len(r.all_ids)
         self._sample_and_append(batch, logits)
         for r in batch:
-            if not r.finished:
+            if not r.finished and r not in self.running:
                 self.running.append(r)
                 if self.runner is not None:
                     self.runner.attach(r)
 
     def _run_decode(self):
+        if self.stateless:
+            reqs = list(self.running)
+            self.stats["decode_tokens"] += len(reqs)
+            self._run_prefill(reqs)                       # scores every sequence from its first token; appends one token each
+            self.stats["prefill_tokens"] -= sum(len(r.all_ids) - 1 for r in reqs)
+            self.running = [r for r in self.running if not r.finished]
+            return
         if self.runner is not None:
             return self._run_decode_static()
         reqs = self.running

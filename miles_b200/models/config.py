@@ -182,6 +182,8 @@ PRESETS: dict[str, ModelConfig] = {
 
 
 def get_config(name_or_path: str) -> ModelConfig:
+    if name_or_path not in PRESETS and not os.path.exists(name_or_path):
+        from . import families  # noqa: F401  (registers the presets of the other model families)
     if name_or_path in PRESETS:
         return PRESETS[name_or_path]
     if os.path.exists(name_or_path):

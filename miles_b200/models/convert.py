@@ -18,8 +18,13 @@ from .config import ModelConfig
 
 # ---- ours → HF -------------------------------------------------------------------------------
 
-def to_hf(name: str, tensor: torch.Tensor, cfg: ModelConfig, *, expert_offset: int = 0) -> list[tuple[str, torch.Tensor]]:
+def to_hf(name: str, tensor: torch.Tensor, cfg: ModelConfig, *, expert_offset: int = 0, _plain: bool = False
+          ) -> list[tuple[str, torch.Tensor]]:
     """Convert one *full* (un-sharded along TP) tensor of this package's layout into HF tensors."""
+    if not _plain and getattr(cfg, "family", "qwen3") != "qwen3":
+        from . import bridges           # latent / linear attention, shared experts, … of the other families
+
+        return bridges.to_hf(name, tensor, cfg, expert_offset=expert_offset)
     if name == "embed":
         return [("model.embed_tokens.weight", tensor)]
     if name == "lm_head":
@@ -68,8 +73,12 @@ def to_hf(name: str, tensor: torch.Tensor, cfg: ModelConfig, *, expert_offset: i
     raise KeyError(f"no HF mapping for {name}")
 
 
-def hf_state_to_ours(hf: dict[str, torch.Tensor], cfg: ModelConfig) -> dict[str, torch.Tensor]:
+def hf_state_to_ours(hf: dict[str, torch.Tensor], cfg: ModelConfig, _plain: bool = False) -> dict[str, torch.Tensor]:
     """Assemble full tensors of this package's layout from an HF state dict."""
+    if not _plain and getattr(cfg, "family", "qwen3") != "qwen3":
+        from . import bridges
+
+        return bridges.from_hf(hf, cfg)
     out: dict[str, torch.Tensor] = {}
     out["embed"] = hf["model.embed_tokens.weight"]
     if "lm_head.weight" in hf and not cfg.tie_embeddings:
@@ -81,11 +90,13 @@ def hf_state_to_ours(hf: dict[str, torch.Tensor], cfg: ModelConfig) -> dict[str,
             continue
         out[f"{o}.ln1"] = hf[f"{pre}.input_layernorm.weight"]
         out[f"{o}.ln2"] = hf[f"{pre}.post_attention_layernorm.weight"]
-        out[f"{o}.attn.wqkv"] = torch.cat([hf[f"{pre}.self_attn.{x}_proj.weight"] for x in "qkv"], 0)
-        if cfg.qkv_bias:
-            out[f"{o}.attn.bqkv"] = torch.cat([hf[f"{pre}.self_attn.{x}_proj.bias"] for x in "qkv"], 0)
-        out[f"{o}.attn.wo"] = hf[f"{pre}.self_attn.o_proj.weight"]
-        if cfg.qk_norm:
+        if f"{pre}.self_attn.k_proj.weight" in hf:          # absent for latent / linear attention layers of other families
+            out[f"{o}.attn.wqkv"] = torch.cat([hf[f"{pre}.self_attn.{x}_proj.weight"] for x in "qkv"], 0)
+            if cfg.qkv_bias:
+                out[f"{o}.attn.bqkv"] = torch.cat([hf[f"{pre}.self_attn.{x}_proj.bias"] for x in "qkv"], 0)
+        if f"{pre}.self_attn.o_proj.weight" in hf:
+            out[f"{o}.attn.wo"] = hf[f"{pre}.self_attn.o_proj.weight"]
+        if cfg.qk_norm and f"{pre}.self_attn.q_norm.weight" in hf:
             out[f"{o}.attn.q_norm"] = hf[f"{pre}.self_attn.q_norm.weight"]
             out[f"{o}.attn.k_norm"] = hf[f"{pre}.self_attn.k_norm.weight"]
         if cfg.layer_is_moe(L):

@@ -92,12 +92,13 @@ class Attention(nn.Module):
         else:
             self.q_norm = self.k_norm = None
 
-    def forward(self, x: torch.Tensor, meta: ForwardMeta, layer: int) -> torch.Tensor:
+    def forward(self, x: torch.Tensor, meta: ForwardMeta, layer: int, qkv: torch.Tensor | None = None) -> torch.Tensor:
         cfg = self.cfg
-        qkv = self.ps.column_linear(x, self.wqkv, self.bqkv)          # SP all-gather fused on GPU
         lora = getattr(self, "lora", None)
-        if lora is not None and "wqkv" in lora:
-            qkv = qkv + lora["wqkv"](x, meta)
+        if qkv is None:                                                   # else: computed by the caller's fused norm + projection
+            qkv = self.ps.column_linear(x, self.wqkv, self.bqkv)          # SP all-gather fused on GPU
+            if lora is not None and "wqkv" in lora:
+                qkv = qkv + lora["wqkv"](x, meta)
         T = qkv.shape[0]
         q, k, v = qkv.split([self.hq * self.d, self.hkv * self.d, self.hkv * self.d], dim=-1)
         q, k, v = q.view(T, self.hq, self.d), k.view(T, self.hkv, self.d), v.view(T, self.hkv, self.d)
@@ -170,9 +171,10 @@ class MoEFFN(nn.Module):
             w2[e - lo].copy_(gen(f"{tag}.e{e}.w2", (H, F), cfg.init_std, dtype, device))
         self.w13, self.w2 = nn.Parameter(w13), nn.Parameter(w2)
 
-    def forward(self, x, meta: ForwardMeta, layer: int):
+    def forward(self, x, meta: ForwardMeta, layer: int, logits: torch.Tensor | None = None):
         # with sequence parallelism each TP rank routes its own token slice (expert-TP is 1)
-        logits = ops.linear_fp32(x, self.router)      # router scores stay fp32 (no bf16 rounding, no cast kernel)
+        if logits is None:
+            logits = ops.linear_fp32(x, self.router)  # router scores stay fp32 (no bf16 rounding, no cast kernel)
         k, norm = self.cfg.moe_topk, self.cfg.moe_norm_topk_prob
         if meta.replay_topk is not None:
             # R3: recorded indices replace top-k, weights come from the current scores so the gate
@@ -203,8 +205,23 @@ class DecoderLayer(nn.Module):
         self.mlp = (MoEFFN(cfg, ps, dtype, device, gen, tag, moe_index) if cfg.layer_is_moe(layer)
                     else DenseFFN(cfg, ps, dtype, device, gen, tag))
 
+    def _forward_few_tokens(self, x, residual, meta: ForwardMeta):
+        """Decode with a handful of rows: each norm is fused into the matrix-vector projection that consumes it."""
+        attn, mlp = self.attn, self.mlp
+        qkv, residual, _ = ops.add_rmsnorm_linear(x, residual, self.ln1, self.eps, attn.wqkv, attn.bqkv)
+        h = attn(None, meta, self.layer, qkv=qkv)
+        if isinstance(mlp, MoEFFN):
+            logits, residual, hn = ops.add_rmsnorm_linear(h, residual, self.ln2, self.eps, mlp.router, want_normed=True,
+                                                          out_fp32=True)
+            return mlp(hn, meta, self.layer, logits=logits), residual
+        h13, residual, _ = ops.add_rmsnorm_linear(h, residual, self.ln2, self.eps, mlp.w13)
+        return ops.linear(ops.swiglu(h13), mlp.w2), residual
+
     def forward(self, x, residual, meta: ForwardMeta):
         # `x` is the previous block's output still to be added to `residual`
+        if (self.attn.ps.tp_size == 1 and ops.few_token_decode(x, self.attn.wqkv) and getattr(self.attn, "lora", None) is None
+                and getattr(self.mlp, "lora", None) is None):
+            return self._forward_few_tokens(x, residual, meta)
         h, residual = ops.add_rmsnorm(x, residual, self.ln1, self.eps)
         h = self.attn(h, meta, self.layer)
         h, residual = ops.add_rmsnorm(h, residual, self.ln2, self.eps)
@@ -320,6 +337,10 @@ def unshard_qkv(parts: list[torch.Tensor], cfg: ModelConfig) -> torch.Tensor:
 def build_model(cfg: ModelConfig, ps: ParallelState | None = None, dtype=torch.bfloat16, device="cpu",
                 seed: int = 0) -> Qwen3Model:
     ps = ps or ParallelState.single()
+    if getattr(cfg, "family", "qwen3") != "qwen3":
+        from .families import build_family_model      # latent / sparse / linear attention, shared experts, hyper-connections
+
+        return build_family_model(cfg, ps, dtype=dtype, device=device, seed=seed)
     layer_range = None
     if ps.pp_size > 1:
         per = math.ceil(cfg.num_layers / ps.pp_size)

@@ -72,6 +72,18 @@ def rmsnorm(x, w, eps=1e-6):
     return ref.rmsnorm(x, w, eps)
 
 
+def few_token_decode(x, w) -> bool:
+    """True when the matrix-vector decode kernels apply to `x · wᵀ`: CUDA bf16, no autograd, a handful of rows."""
+    return x.is_cuda and _k().gemv_ok(x, w)
+
+
+def add_rmsnorm_linear(x, residual, norm_w, eps, w, bias=None, want_normed=False, out_fp32=False):
+    """rmsnorm(x + residual) · wᵀ in one kernel (only where `few_token_decode` holds).
+    Returns (y, x + residual, normalised activations or None)."""
+    y, res, xn = _k().add_rmsnorm_linear(x, residual, norm_w, eps, w, bias, want_normed, out_fp32)
+    return y, (x if res is None else res), xn
+
+
 def add_rmsnorm(x, residual, w, eps=1e-6):
     """(x + residual) → (rmsnorm(sum), sum); residual None means x starts the stream."""
     if residual is None:

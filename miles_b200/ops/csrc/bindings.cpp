@@ -65,6 +65,27 @@ void gemm_small(const at::Tensor& X, const at::Tensor& W, at::Tensor& C, int64_t
         "mb_gemm_small");
 }
 
+// y[M, N] = norm?(x (+ residual)) · Wᵀ (+ bias) for M ≤ 16; two kernel launches are counted by the MoE variant below
+void gemv(const at::Tensor& x, const c10::optional<at::Tensor>& residual, const c10::optional<at::Tensor>& norm_w, double eps,
+          const at::Tensor& W, const c10::optional<at::Tensor>& bias, at::Tensor& y, const c10::optional<at::Tensor>& res_out,
+          const c10::optional<at::Tensor>& xn_out, bool static_w) {
+  c10::cuda::CUDAGuard g(x.device());
+  const int64_t K = x.size(-1), M = x.numel() / K, N = W.size(0);
+  check(mb_gemv(x.data_ptr(), cptr(residual), cptr(norm_w), eps, W.data_ptr(), cptr(bias), y.data_ptr(), y.stride(0),
+                y.scalar_type() == at::kFloat, mptr(res_out), mptr(xn_out), M, N, K, static_w, cur_stream()),
+        "mb_gemv");
+}
+
+void moe_gemv(const at::Tensor& x, const at::Tensor& w13, const at::Tensor& w2, const at::Tensor& topk_idx, const at::Tensor& topk_w,
+              at::Tensor& act, at::Tensor& out, int64_t expert_offset) {
+  c10::cuda::CUDAGuard g(x.device());
+  const int64_t T = x.size(0), H = x.size(1), k = topk_idx.size(1), E = w13.size(0), F = w13.size(1) / 2;
+  mb_count_launch(1);
+  check(mb_moe_gemv(x.data_ptr(), w13.data_ptr(), w2.data_ptr(), topk_idx.data_ptr<int>(), topk_w.data_ptr<float>(), act.data_ptr(),
+                    out.data_ptr(), T, k, E, expert_offset, H, F, cur_stream()),
+        "mb_moe_gemv");
+}
+
 void gemm_small_grouped(const at::Tensor& X, const at::Tensor& W, at::Tensor& C, int64_t rows, int64_t N, int64_t K, int64_t E,
                         const at::Tensor& tile_expert, const c10::optional<at::Tensor>& used_rows, int64_t bt) {
   c10::cuda::CUDAGuard g(X.device());
@@ -210,6 +231,8 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("gemm_splitk", &gemm_splitk);
   m.def("gemm_grouped", &gemm_grouped);
   m.def("gemm_small", &gemm_small);
+  m.def("gemv", &gemv);
+  m.def("moe_gemv", &moe_gemv);
   m.def("gemm_small_grouped", &gemm_small_grouped);
   m.def("gemm_grouped_wgrad", &gemm_grouped_wgrad);
   m.def("rmsnorm_fwd", &rmsnorm_fwd);

@@ -223,15 +223,21 @@ gemm_small_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_const
         if (n_ok) {
           const float b = p.bias != nullptr ? __bfloat162float(p.bias[n]) : 0.f;
           const long long plane_sz = static_cast<long long>(p.tokens) * p.N;
-#pragma unroll 4
+          // one slice at a time with all BT loads of the slice in flight (the loads of a token are independent)
+#pragma unroll
+          for (int i = 0; i < BT; ++i) v[i] = b;
+          for (int sl = 0; sl < split_k; ++sl) {
+            const float* src = p.ws + sl * plane_sz + static_cast<long long>(tok0) * p.N + n;
+#pragma unroll
+            for (int i = 0; i < BT; ++i)
+              if (tok0 + i < p.tokens) v[i] += __ldcg(src + static_cast<long long>(i) * p.N);
+          }
+#pragma unroll
           for (int i = 0; i < BT; ++i) {
             const int tok = tok0 + i;
             if (tok >= p.tokens) break;
-            const float* src = p.ws + static_cast<long long>(tok) * p.N + n;
-            float s = b;
-            for (int sl = 0; sl < split_k; ++sl) s += __ldcg(src + sl * plane_sz);
-            if (p.out_fp32) reinterpret_cast<float*>(p.C)[static_cast<long long>(tok) * p.ldc + n] = s;
-            else reinterpret_cast<__nv_bfloat16*>(p.C)[static_cast<long long>(tok) * p.ldc + n] = __float2bfloat16(s);
+            if (p.out_fp32) reinterpret_cast<float*>(p.C)[static_cast<long long>(tok) * p.ldc + n] = v[i];
+            else reinterpret_cast<__nv_bfloat16*>(p.C)[static_cast<long long>(tok) * p.ldc + n] = __float2bfloat16(v[i]);
           }
         }
         __syncwarp();

@@ -27,6 +27,11 @@ int mb_gemm_small(const void* X, const void* W, void* C, int tokens, int N, int 
                   int out_fp32, const void* bias, int bt, int split_k, float* ws, int* counters, int* error_flag, cudaStream_t stream);
 int mb_gemm_small_grouped(const void* X, const void* W, void* C, int rows, int N, int K, int num_experts, const int* tile_expert,
                           const int* used_rows, int bt, int* error_flag, cudaStream_t stream);
+// ---- gemv.cu: ≤ 16 tokens (dense) / ≤ 8 tokens (MoE), no pipeline set-up ----
+int mb_gemv(const void* x, const void* residual, const void* norm_w, float eps, const void* W, const void* bias, void* y, long long ldy,
+            int out_fp32, void* res_out, void* xn_out, int M, int N, int K, int static_w, cudaStream_t s);
+int mb_moe_gemv(const void* x, const void* w13, const void* w2, const int* topk_idx, const float* topk_w, void* act, void* out, int T, int k,
+                int E, int expert_offset, int H, int F, cudaStream_t s);
 int mb_gemm_bf16_grouped_wgrad(const void* dY, const void* X, void* dW, int M_pad, int N, int K, int num_experts,
                                const int* seg_offsets, int out_fp32, int accumulate, int force_bn, int* error_flag,
                                cudaStream_t stream);

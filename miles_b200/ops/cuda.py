@@ -49,7 +49,13 @@ def gemm_nt(a: torch.Tensor, b: torch.Tensor, out: torch.Tensor | None = None, *
     if out is None:
         out = torch.empty(M, N, dtype=out_dtype or BF16, device=a.device)
     if M and N:
-        if M <= SMALL_M and not accumulate and not force_bn and K >= 256:
+        plain = not accumulate and not force_bn
+        if plain and M <= GEMV_M and K % 32 == 0 and N <= GEMV_MAX_N:
+            C.gemv(a, None, None, 0.0, b, bias, out, None, None, bool(b.is_leaf and b.requires_grad))
+            return out
+        # measured: the operand-swapped kernel wins where its tiles fill the GPU without split-K (wide outputs such as the
+        # LM head); with split-K its reduction costs more than the padding rows of the general kernel
+        if plain and M <= SMALL_M and K >= 256 and (SMALL_SPLIT or _small_split(M, N, K, small_bt(M)) == 1):
             return _gemm_small(a, b, out, bias, M, N, K)
         split = _pick_split_k(M, N, K) if not force_bn and SPLIT_K else 1
         if split > 1:
@@ -86,9 +92,38 @@ def _splitk_workspace(device):
     return _splitk_ws[key]
 
 
+# A handful of tokens (decode with a nearly drained batch): matrix-vector kernels without pipeline set-up (gemv.cu).
+# Up to 16 rows are supported; 0 turns the path off.
+GEMV_M = min(16, int(os.environ.get("MILES_GEMV_M", "8")))
+GEMV_MAX_N = int(os.environ.get("MILES_GEMV_MAX_N", "32768"))
+
+
+def add_rmsnorm_linear(x, residual, norm_w, eps, w, bias=None, want_normed: bool = False, out_fp32: bool = False):
+    """Inference only, ≤ GEMV_M rows: y = rmsnorm(x + residual) · wᵀ in one kernel.
+    Returns (y, x + residual or None, normalised activations or None)."""
+    K = x.shape[-1]
+    x2 = _c(x.reshape(-1, K))
+    r2 = _c(residual.reshape(-1, K)) if residual is not None else None
+    M, N = x2.shape[0], w.shape[0]
+    y = torch.empty(M, N, dtype=torch.float32 if out_fp32 else BF16, device=x.device)
+    res_out = torch.empty_like(x2) if r2 is not None else None
+    xn = torch.empty_like(x2) if want_normed else None
+    C.gemv(x2, r2, norm_w, float(eps), w, bias, y, res_out, xn, bool(w.is_leaf and w.requires_grad))
+    shp = x.shape[:-1]
+    return (y.view(*shp, N), res_out.view(x.shape) if res_out is not None else None, xn.view(x.shape) if xn is not None else None)
+
+
+def gemv_ok(x, w) -> bool:
+    """True when `add_rmsnorm_linear` applies: bf16, no autograd, few rows, K a multiple of 32."""
+    K = x.shape[-1]
+    return (GEMV_M > 0 and x.dtype == BF16 and w.dtype == BF16 and not torch.is_grad_enabled() and K % 32 == 0
+            and 0 < x.numel() // K <= GEMV_M and w.is_contiguous())
+
+
 # Decode-sized token counts: the weight rows go on the 128-row side of the MMA and the tokens on the N side in tiles of
 # 16/32/64 (gemm_small.cu), so no pipeline byte is spent on padding rows; split-K fills the SMs.  0 turns the path off.
 SMALL_M = int(os.environ.get("MILES_SMALL_M", "64"))
+SMALL_SPLIT = os.environ.get("MILES_SMALL_SPLIT", "0") == "1"     # also use it where it needs split-K
 _SMALL_WS_FLOATS, _SMALL_MAX_TILES = 4 << 20, 4096
 _small_ws: dict = {}
 

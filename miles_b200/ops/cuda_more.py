@@ -127,6 +127,9 @@ def moe_max_rows(n_pairs: int, num_experts: int) -> int:
 SMALL_MOE_AVG = float(os.environ.get("MILES_SMALL_MOE_AVG", "32")) if os.environ.get("MILES_SMALL_MOE", "1") != "0" else 0.0
 
 
+MOE_GEMV_T = min(8, int(os.environ.get("MILES_MOE_GEMV_T", "8")))
+
+
 def small_moe_bt(n_pairs: int, num_experts: int, w13, w2) -> int:
     """Row granularity for an inference MoE call: 128 (general path) or a decode-sized tile."""
     if SMALL_MOE_AVG <= 0 or torch.is_grad_enabled() or w13.shape[1] % 128 or w2.shape[1] % 128:
@@ -134,7 +137,7 @@ def small_moe_bt(n_pairs: int, num_experts: int, w13, w2) -> int:
     avg = n_pairs / max(num_experts, 1)
     if avg > SMALL_MOE_AVG:
         return 128
-    return 16 if avg <= 6 else 32 if avg <= 16 else 64
+    return 16 if avg <= 16 else 32          # measured: the finest tile wins (weight re-reads hit L2, padding rows do not)
 
 
 def moe_max_rows_pad(n_pairs: int, num_experts: int, pad: int) -> int:
@@ -259,6 +262,14 @@ class _MoEFFN(torch.autograd.Function):
 def moe_ffn(x, w13, w2, topk_w, topk_idx, expert_offset: int = 0):
     if x.dtype != BF16:
         return ref.moe_ffn(x, w13, w2, topk_w, topk_idx)
+    T, k = topk_idx.shape
+    if (0 < T <= MOE_GEMV_T and T * k <= 64 and not torch.is_grad_enabled() and x.shape[1] % 32 == 0
+            and w13.shape[1] % 64 == 0):
+        # a handful of tokens: two matrix-vector kernels, no sort / gather / combine (gemv.cu)
+        act = torch.empty(T * k, w13.shape[1] // 2, dtype=x.dtype, device=x.device)
+        out = torch.empty_like(x)
+        C.moe_gemv(_c(x), _c(w13), _c(w2), _c(topk_idx.to(torch.int32)), _c(topk_w.float()), act, out, int(expert_offset))
+        return out
     bt = small_moe_bt(topk_idx.numel(), w13.shape[0], w13, w2)
     if bt != 128 and x.shape[0]:
         return _moe_ffn_small(x, w13, w2, topk_w, topk_idx, int(expert_offset), bt)

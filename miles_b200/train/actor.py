@@ -358,6 +358,12 @@ class TrainActor:
                 continue
             loss, m, count = loss_function(self._loss_args(), lb, out, ent, global_batch_size=gbs,
                                            global_num_tokens=gtok)
+            aux = getattr(self.model, "aux_losses", None)
+            if aux is not None and self.role == "actor":
+                # model-side objectives of other families (the sparse-attention indexer's KL), weighted like one micro-batch
+                for name, term in aux().items():
+                    loss = loss + getattr(args, "aux_loss_coef", 1.0) * term / max(1, len(mbs))
+                    m[name] = term.detach() * count
             if io is not None:
                 pipelined.append((loss, io))
             else:

@@ -53,6 +53,52 @@ def test_gemm_small_every_split_and_tile():
     assert K_.check_error_flag(x) == 0
 
 
+@pytest.mark.parametrize("M", [1, 5, 8, 9, 16])
+@pytest.mark.parametrize("N,K", [(128, 2048), (5120, 2048), (2048, 4096), (1000, 96)])
+def test_gemv_matches_fp32(M, N, K):
+    K_ = _k()
+    torch.manual_seed(M * 7 + N)
+    x = torch.randn(M, K, device="cuda", dtype=torch.bfloat16)
+    w = torch.randn(N, K, device="cuda", dtype=torch.bfloat16) * 0.05
+    bias = torch.randn(N, device="cuda", dtype=torch.bfloat16)
+    expect = x.float() @ w.float().t() + bias.float()
+    for static_w in (False, True):
+        y = torch.empty(M, N, device="cuda", dtype=torch.float32)
+        K_.C.gemv(x, None, None, 0.0, w, bias, y, None, None, static_w)
+        assert _rel(y, expect) < 1e-4
+    yb = torch.empty(M, N, device="cuda", dtype=torch.bfloat16)
+    K_.C.gemv(x, None, None, 0.0, w, None, yb, None, None, False)
+    assert _rel(yb, expect - bias.float()) < 5e-3
+
+
+@pytest.mark.parametrize("M", [1, 8, 13])
+@pytest.mark.parametrize("with_residual", [False, True])
+def test_add_rmsnorm_linear_matches_unfused(M, with_residual):
+    K_ = _k()
+    torch.manual_seed(M)
+    K, N, eps = 2048, 640, 1e-6
+    x = torch.randn(M, K, device="cuda", dtype=torch.bfloat16)
+    r = torch.randn(M, K, device="cuda", dtype=torch.bfloat16) if with_residual else None
+    nw = (1 + 0.1 * torch.randn(K, device="cuda")).to(torch.bfloat16)
+    w = torch.randn(N, K, device="cuda", dtype=torch.bfloat16) * 0.05
+    old = K_.GEMV_M
+    K_.GEMV_M = 16
+    try:
+        with torch.no_grad():
+            assert K_.gemv_ok(x, w)
+            y, res, xn = K_.add_rmsnorm_linear(x, r, nw, eps, w, want_normed=True)
+    finally:
+        K_.GEMV_M = old
+    h = (x.float() + r.float()).to(torch.bfloat16).float() if with_residual else x.float()
+    xn_ref = h * torch.rsqrt(h.pow(2).mean(-1, keepdim=True) + eps) * nw.float()
+    assert _rel(xn, xn_ref) < 5e-3
+    assert _rel(y, xn_ref @ w.float().t()) < 1e-2
+    if with_residual:
+        assert torch.equal(res.float(), h)
+    else:
+        assert res is None
+
+
 def test_gemm_small_strided_output():
     K_ = _k()
     x = torch.randn(5, 512, device="cuda", dtype=torch.bfloat16)
@@ -85,6 +131,28 @@ def test_moe_ffn_small_tiles_match_fp32(T, E, K, H, F):
     y_train = cuda_more.moe_ffn(x.requires_grad_(), w13, w2, tw, ti)        # autograd on: the 128-row path
     assert _rel(y, y_train) < 1e-2
     assert _k().check_error_flag(x) == 0
+
+
+@pytest.mark.parametrize("T,E,K,H,F", [(1, 128, 8, 2048, 768), (8, 128, 8, 2048, 768), (5, 4, 4, 256, 96), (3, 16, 2, 128, 32)])
+def test_moe_gemv_matches_fp32(T, E, K, H, F):
+    from miles_b200.ops import cuda_more
+
+    torch.manual_seed(T + E)
+    x = torch.randn(T, H, device="cuda", dtype=torch.bfloat16)
+    w13 = torch.randn(E, 2 * F, H, device="cuda", dtype=torch.bfloat16) * 0.03
+    w2 = torch.randn(E, H, F, device="cuda", dtype=torch.bfloat16) * 0.03
+    tw, ti = torch.randn(T, E, device="cuda").softmax(-1).topk(K, dim=-1)
+    expect = ref.moe_ffn(x.float(), w13.float(), w2.float(), tw, ti)
+    n0 = _k().launch_count()
+    with torch.no_grad():
+        y = cuda_more.moe_ffn(x, w13, w2, tw, ti)
+    assert _k().launch_count() - n0 == 2                     # the two matrix-vector kernels, nothing else
+    assert _rel(y, expect) < 2e-2
+    # experts split over two "ranks": the halves add up
+    with torch.no_grad():
+        lo = cuda_more.moe_ffn(x, w13[: E // 2], w2[: E // 2], tw, ti, 0)
+        hi = cuda_more.moe_ffn(x, w13[E // 2:], w2[E // 2:], tw, ti, E // 2)
+    assert _rel(lo.float() + hi.float(), expect) < 2e-2
 
 
 def test_moe_ffn_small_expert_offset():
