@@ -110,7 +110,12 @@ class Attention(nn.Module):
             q, k = ops.qk_norm_rope(q, k, self.q_norm, self.k_norm, meta.positions, cfg.rope_theta, cfg.rms_eps)
         if meta.cu_seqlens is not None:
             # training, or an engine prefill that starts from an empty cache: attend within the new tokens
-            if self.ps.cp_size > 1:
+            if self.ps.cp_size > 1 and not self.ps.is_ulysses_cp:
+                # ring (zigzag pieces, K/V travel round the group) or all-gather context parallelism
+                from ..parallel import cp_ring as _ring
+                fn = _ring.allgather_attention if self.ps.cp_comm_type == "allgather" else _ring.ring_attention
+                o = fn(q, k, v, meta.cu_seqlens, self.ps)
+            elif self.ps.cp_size > 1:
                 # context parallel (Ulysses): tokens are sharded in contiguous chunks; swap to a head sharding for the
                 # kernel (cu_seqlens describe the whole packed batch) and back
                 from ..parallel import cp as _cp

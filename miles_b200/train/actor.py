@@ -191,16 +191,21 @@ class TrainActor:
         """Context-parallel forward: this rank runs tokens [lo, hi) of the packed batch, scores the response tokens whose
         predicting row falls in that chunk, and the per-token results are assembled over the CP group (every rank ends
         with the full vectors, so sequence-level losses need no further communication)."""
-        from ..parallel import cp
+        from ..parallel import cp, cp_ring
 
         ps = self.ps
-        lo, hi = cp.chunk_bounds(pb.tokens.numel(), ps.cp_size, ps.cp_rank)
+        T = pb.tokens.numel()
+        # the tokens this rank runs: a contiguous chunk (Ulysses, all-gather CP) or two zigzag pieces (ring CP)
+        own = cp_ring.token_index(T, ps, pb.tokens.device)
+        local_row = torch.full((T,), -1, dtype=torch.long, device=own.device)
+        local_row[own] = torch.arange(own.numel(), device=own.device)
         rec = getattr(self.args, "recompute_granularity", None) == "full"
-        meta = ForwardMeta(positions=pb.positions[lo:hi], cu_seqlens=pb.cu_seqlens, max_seqlen=pb.max_seqlen,
-                           replay_topk=pb.replay_topk[lo:hi] if (replay and pb.replay_topk is not None) else None, recompute=rec)
-        hidden = ps.sp_gather(self.model(pb.tokens[lo:hi], meta))
-        mine = (pb.gather_index >= lo) & (pb.gather_index < hi)
-        h = hidden[pb.gather_index[mine] - lo]
+        meta = ForwardMeta(positions=pb.positions[own], cu_seqlens=pb.cu_seqlens, max_seqlen=pb.max_seqlen,
+                           replay_topk=pb.replay_topk[own] if (replay and pb.replay_topk is not None) else None, recompute=rec)
+        hidden = ps.sp_gather(self.model(pb.tokens[own], meta))
+        rows = local_row[pb.gather_index]
+        mine = rows >= 0
+        h = hidden[rows[mine]]
         R = pb.gather_index.numel()
         if self.role == "critic":
             return cp.gather_from_cp(self.model.value_head(h.float()).squeeze(-1), mine, R, ps), None
@@ -239,7 +244,8 @@ class TrainActor:
         return [out[i] for i in sorted(out)]
 
     def _pad_multiple(self) -> int:
-        return max(1, self.ps.tp_size) * max(1, self.ps.cp_size) * (128 if self.device.type == "cuda" else 1)
+        zigzag = 2 if (self.ps.cp_size > 1 and self.ps.cp_comm_type == "p2p") else 1     # ring CP: two pieces per rank
+        return max(1, self.ps.tp_size) * max(1, self.ps.cp_size) * zigzag * (128 if self.device.type == "cuda" else 1)
 
     # ---------------------------------------------------------------------------------------
     # train
