@@ -88,6 +88,8 @@ def build_parser() -> argparse.ArgumentParser:
     g.add_argument("--tensor-model-parallel-size", type=int, default=1)
     g.add_argument("--pipeline-model-parallel-size", type=int, default=1)
     g.add_argument("--virtual-pipeline-model-parallel-size", type=int, default=None)
+    g.add_argument("--pp-schedule", choices=["1f1b", "gpipe"], default="1f1b",
+                   help="pipeline order of the micro-batches of an optimizer step")
     g.add_argument("--context-parallel-size", type=int, default=1)
     g.add_argument("--expert-model-parallel-size", type=int, default=1)
     g.add_argument("--expert-tensor-parallel-size", type=int, default=1)

@@ -5,11 +5,11 @@ The reference takes Megatron's pipeline schedules (1F1B / interleaved, miles/bac
 boundary, small next to TP/EP traffic, so it stays on NCCL here as well.  A stage is a `Qwen3Model` built with a
 `layer_range` (`models/qwen3.py`): the first stage embeds tokens, the last applies the final norm and head.
 
-Schedule: all-forward-then-all-backward over the micro-batches of an optimizer step (GPipe order).  Activations of
-a stage live only at its boundaries plus what autograd keeps; with `--recompute-granularity full` that is one
-`[tokens, hidden]` tensor per layer per micro-batch.  Sends are posted asynchronously (`isend`) and completed before
-the next use of the buffer, receives block: with every stage walking the micro-batches in the same order the
-schedule cannot deadlock.
+Schedules (`--pp-schedule`): `1f1b` (default, `PipeStage.run_1f1b`) is Megatron's non-interleaved order — `pp − rank − 1`
+warm-up forwards, then one forward and one backward per step with the two directions exchanged in ONE grouped p2p call,
+then the remaining backwards — so a stage keeps at most `pp − rank` micro-batches of activations; `gpipe` runs all
+forwards and then all backwards (`recv_forward` / `send_forward` / `backward`), with sends posted asynchronously and
+completed before the next send.  Interleaved (virtual-stage) 1F1B is not built.
 """
 from __future__ import annotations
 
@@ -84,6 +84,79 @@ class PipeStage:
 
     def finish(self):
         self._flush()
+
+    # ---- one-forward-one-backward schedule ---------------------------------------------------------
+    def _exchange(self, send: tuple | None, recv: tuple | None):
+        """One grouped p2p call: (tensor, peer) to send and (buffer, peer) to receive.  Grouping the two directions is
+        what keeps neighbouring stages from waiting on each other's sends (NCCL matches the whole group at once)."""
+        ops = []
+        if send is not None:
+            ops.append(dist.P2POp(dist.isend, send[0], send[1]))
+        if recv is not None:
+            ops.append(dist.P2POp(dist.irecv, recv[0], recv[1]))
+        if ops:
+            for w in dist.batch_isend_irecv(ops):
+                w.wait()
+
+    def run_1f1b(self, n_micro: int, num_tokens_of, forward_step):
+        """Megatron's non-interleaved 1F1B order: `pp − rank − 1` warm-up forwards, then one forward and one backward per
+        step, then the remaining backwards — at most `pp − rank` micro-batches of activations are alive on a stage.
+        forward_step(i, hidden_in) → (hidden_out, loss): hidden_out is None on the last stage, loss None elsewhere."""
+        self._flush()
+        warm = min(self.ps.pp_size - self.ps.pp_rank - 1, n_micro)
+        rem = n_micro - warm
+        alive: list[tuple] = []
+
+        def buf(i):
+            return torch.empty(self._rows(num_tokens_of(i)), self.hidden, dtype=self.dtype, device=self.device)
+
+        def backward(entry, g):
+            hidden_in, hidden_out, loss = entry
+            if self.is_last:
+                loss.backward()
+            else:
+                hidden_out.backward(g)
+            if self.is_first:
+                return None
+            return (hidden_in.grad if hidden_in.grad is not None else torch.zeros_like(hidden_in)).contiguous()
+
+        grad_on = torch.is_grad_enabled()
+        x = None
+        for i in range(warm):
+            if not self.is_first:
+                x = buf(i)
+                self._exchange(None, (x, self.prev))
+                x.requires_grad_(grad_on)
+            out, loss = forward_step(i, x)
+            self._exchange((out.detach().contiguous(), self.next), None)
+            alive.append((x, out, loss))
+        if rem > 0 and not self.is_first:
+            x = buf(warm)
+            self._exchange(None, (x, self.prev))
+            x.requires_grad_(grad_on)
+        for i in range(rem):
+            out, loss = forward_step(warm + i, x)
+            alive.append((x, out, loss))
+            g = None
+            if not self.is_last:
+                g = torch.empty_like(alive[0][1])            # the gradient coming back belongs to the oldest micro-batch alive
+                self._exchange((out.detach().contiguous(), self.next), (g, self.next))
+            gin = backward(alive.pop(0), g)
+            nxt = None
+            if i + 1 < rem and not self.is_first:
+                nxt = buf(warm + i + 1)
+            if not self.is_first:
+                self._exchange((gin, self.prev), (nxt, self.prev) if nxt is not None else None)
+                if nxt is not None:
+                    nxt.requires_grad_(grad_on)
+            x = nxt
+        for _ in range(warm):
+            entry = alive.pop(0)
+            g = torch.empty_like(entry[1])
+            self._exchange(None, (g, self.next))
+            gin = backward(entry, g)
+            if not self.is_first:
+                self._exchange((gin, self.prev), None)
 
 
 def broadcast_from_last_stage(t: torch.Tensor, ps) -> torch.Tensor:

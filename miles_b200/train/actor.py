@@ -180,12 +180,16 @@ class TrainActor:
         if not stage.is_last:
             stage.send_forward(hidden)
             return None, None, StageIO(hidden_in, hidden if grad else None)
+        lp, ent = self._score_hidden(pb, hidden, with_entropy)
+        return lp, ent, StageIO(hidden_in, None)
+
+    def _score_hidden(self, pb: PackedBatch, hidden: torch.Tensor, with_entropy: bool):
+        """Log-probs (+ entropy) of the response tokens, or values for the critic, from final hidden states."""
         h = self.ps.sp_gather(hidden)[pb.gather_index]
         if self.role == "critic":
-            return self.model.value_head(h.float()).squeeze(-1), None, StageIO(hidden_in, None)
+            return self.model.value_head(h.float()).squeeze(-1), None
         temp = getattr(self.args, "rollout_temperature", 1.0)
-        lp, ent = self.ps.vocab_parallel_logprob(h, self.model.head_weight(), pb.targets, temp, with_entropy, self.cfg.vocab_size)
-        return lp, ent, StageIO(hidden_in, None)
+        return self.ps.vocab_parallel_logprob(h, self.model.head_weight(), pb.targets, temp, with_entropy, self.cfg.vocab_size)
 
     def _forward_logprobs_cp(self, pb: PackedBatch, with_entropy: bool, replay: bool):
         """Context-parallel forward: this rank runs tokens [lo, hi) of the packed batch, scores the response tokens whose
@@ -335,17 +339,13 @@ class TrainActor:
         sums: dict[str, torch.Tensor] = {}
         count_sum = torch.zeros((), device=dev)
         want_entropy = getattr(args, "entropy_coef", 0.0) != 0 or getattr(args, "log_entropy", True)
-        pipelined: list = []          # pp > 1: (loss | None, StageIO) per micro-batch, backward runs after all forwards
-        for idx in mbs:
-            pb = pack_micro_batch(shard, idx, dev, pad_multiple=self._pad_multiple(), with_replay=replay)
-            io = None
-            if ps.pp_size > 1:
-                out, ent, io = self._forward_logprobs_pp(pb, want_entropy and self.role == "actor", replay)
-                if out is None:       # not the last stage: nothing to score here
-                    pipelined.append((None, io))
-                    continue
-            else:
-                out, ent = self._forward_logprobs(pb, want_entropy and self.role == "actor", replay)
+        want_ent = want_entropy and self.role == "actor"
+
+        def score(pb, idx, out, ent):
+            """Loss of one micro-batch from its log-probs (values for the critic); adds its metrics to the step's sums."""
+            nonlocal count_sum
+            if not idx:                # empty micro-batch keeps collectives aligned across DP ranks
+                return out.sum() * 0.0
             lb = LossBatch(
                 response_lengths=pb.response_lengths, loss_mask=pb.loss_mask, seq_ids=pb.seq_ids,
                 advantages=_cat(shard.get("advantages"), idx, dev), returns=_cat(shard.get("returns"), idx, dev),
@@ -355,13 +355,6 @@ class TrainActor:
                 old_values=_cat(shard.get("values"), idx, dev) if self.role == "critic" else None,
                 denominators=torch.tensor([shard["rollout_mask_sums"][i] for i in idx], device=dev, dtype=torch.float32)
                 if "rollout_mask_sums" in shard else None)
-            if not idx:  # empty micro-batch keeps collectives aligned across DP ranks
-                loss = out.sum() * 0.0
-                if io is not None:
-                    pipelined.append((loss, io))
-                else:
-                    loss.backward()
-                continue
             loss, m, count = loss_function(self._loss_args(), lb, out, ent, global_batch_size=gbs,
                                            global_num_tokens=gtok)
             aux = getattr(self.model, "aux_losses", None)
@@ -370,18 +363,50 @@ class TrainActor:
                 for name, term in aux().items():
                     loss = loss + getattr(args, "aux_loss_coef", 1.0) * term / max(1, len(mbs))
                     m[name] = term.detach() * count
-            if io is not None:
-                pipelined.append((loss, io))
-            else:
-                loss.backward()
             for k, v in m.items():
                 sums[k] = sums.get(k, 0) + v.detach().float()
             count_sum = count_sum + count
-        if ps.pp_size > 1:
+            return loss
+
+        def pack(idx):
+            return pack_micro_batch(shard, idx, dev, pad_multiple=self._pad_multiple(), with_replay=replay)
+
+        if ps.pp_size > 1 and getattr(args, "pp_schedule", "1f1b") == "1f1b":
+            stage = self._pipe()
+            packed: dict[int, PackedBatch] = {}
+
+            def get(i):
+                if i not in packed:
+                    packed[i] = pack(mbs[i])
+                return packed[i]
+
+            def forward_step(i, hidden_in):
+                pb = get(i)
+                hidden = self.model(pb.tokens, self._meta(pb, replay), hidden_in=hidden_in)
+                if not stage.is_last:
+                    packed.pop(i, None)
+                    return hidden, None
+                out, ent = self._score_hidden(pb, hidden, want_ent)
+                packed.pop(i, None)
+                return None, score(pb, mbs[i], out, ent)
+
+            stage.run_1f1b(len(mbs), lambda i: get(i).tokens.numel(), forward_step)
+        elif ps.pp_size > 1:
+            # all forwards, then all backwards (GPipe order)
+            pipelined: list = []
+            for idx in mbs:
+                pb = pack(idx)
+                out, ent, io = self._forward_logprobs_pp(pb, want_ent, replay)
+                pipelined.append((score(pb, idx, out, ent) if out is not None else None, io))
             stage = self._pipe()
             for loss, io in pipelined:            # same micro-batch order on every stage
                 stage.backward(io, loss)
             stage.finish()
+        else:
+            for idx in mbs:
+                pb = pack(idx)
+                out, ent = self._forward_logprobs(pb, want_ent, replay)
+                score(pb, idx, out, ent).backward()
         self._finalize_grads()
         lr = self.scheduler.get()
         stats = self.optimizer.step(lr)

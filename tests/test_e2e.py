@@ -122,7 +122,8 @@ def _dist_hist(tmp_path, extra, world=2):
     "--context-parallel-size 2 --cp-comm-type a2a",                         # cp2 (Ulysses), dp1
     "--context-parallel-size 2",                                            # cp2, ring attention over zigzag pieces
     "--context-parallel-size 2 --allgather-cp",                             # cp2, K/V all-gathered
-    "--pipeline-model-parallel-size 2 --micro-batch-size 8",                # pp2, 4 micro-batches per step
+    "--pipeline-model-parallel-size 2 --micro-batch-size 8",                # pp2, 4 micro-batches per step, 1F1B order
+    "--pipeline-model-parallel-size 2 --micro-batch-size 8 --pp-schedule gpipe",
     # the tiny plumbing config: 16 prompts of length 32 per step, groups of 4, 32 new tokens, lr 1e-5, 3 steps
     "--rollout-batch-size 16 --synthetic-prompt-len 32 32 --rollout-max-response-len 32 --lr 1e-5 --num-rollout 3 --kl-coef 0",
 ])
