@@ -27,6 +27,21 @@ std::vector<at::Tensor> sample_logprob(const at::Tensor& logits, const at::Tenso
   const int64_t B = logits.size(0), V = logits.size(1);
   auto tok = at::empty({B}, logits.options().dtype(at::kLong));
   auto lp = at::empty({B}, logits.options());
+  const long long* seed_ptr =
+      seeds.has_value() && seeds->defined() ? reinterpret_cast<const long long*>(seeds->data_ptr<int64_t>()) : nullptr;
+  // few rows: several CTAs per row (one CTA per row would leave a 150k-entry vocabulary to a single SM)
+  const int64_t parts = std::min<int64_t>(32, 296 / std::max<int64_t>(B, 1));
+  if (parts >= 2 && B <= 4096) {
+    static std::vector<at::Tensor> counters(64);
+    auto& cnt = counters[logits.device().index()];
+    if (!cnt.defined()) cnt = at::zeros({4096}, logits.options().dtype(at::kInt));
+    auto ws = at::empty({B * parts * 4}, logits.options());
+    check(mb_sample_logprob_split(logits.data_ptr<float>(), temperature.data_ptr<float>(), greedy.data_ptr<uint8_t>(), seed_ptr, step,
+                                  reinterpret_cast<long long*>(tok.data_ptr<int64_t>()), lp.data_ptr<float>(), B, V, parts,
+                                  ws.data_ptr<float>(), cnt.data_ptr<int>(), cur_stream()),
+          "mb_sample_logprob_split");
+    return {tok, lp};
+  }
   check(mb_sample_logprob(logits.data_ptr<float>(), temperature.data_ptr<float>(), greedy.data_ptr<uint8_t>(),
                           seeds.has_value() && seeds->defined() ? reinterpret_cast<const long long*>(seeds->data_ptr<int64_t>()) : nullptr,
                           step, reinterpret_cast<long long*>(tok.data_ptr<int64_t>()), lp.data_ptr<float>(), B, V, cur_stream()),

@@ -2,14 +2,17 @@
 //
 // With a handful of tokens every projection is a matrix-vector product: the time is the weight bytes over HBM bandwidth plus
 // fixed latency, and the latency of a TMA/TMEM pipeline (barrier set-up, TMEM allocation, tile hand-offs, split-K
-// reduction) is several times the streaming time.  These kernels have no prologue: every warp starts streaming weight
-// rows with 16-byte read-only loads at once, eight loads in flight per lane.
+// reduction) is several times the streaming time.  These kernels have no such prologue:
 //
-// The arithmetic still runs on the tensor cores (`mma.sync.m16n8k16`, bf16 → fp32): 16 weight rows are the A operand, the
-// ≤ 8 tokens are the B operand's 8 columns.  Because a dot product does not care about the order of its terms, a lane
-// loads 8 CONSECUTIVE k of one row (one 16-byte load) and feeds register pairs to two MMAs; the activations are loaded
-// with the same permutation of k, so no shuffle or shared-memory staging is needed.
-//   lane = 4·g + t: A rows g and g+8, k ∈ [32c + 8t, 32c + 8t + 8); B column (token) g, same k
+//   * every thread streams ITS OWN 16-byte pieces of the weight rows through a private ring in shared memory with
+//     `cp.async` (S stages of two pieces in flight per thread, no registers held, no barrier: a thread only ever reads
+//     back what it copied itself), so each SM keeps 64–96 KB of weight loads in flight from the first instruction on;
+//   * the activations (≤ 16 rows) are staged once per CTA in shared memory while the first weight loads fly — with the
+//     residual add, the RMSNorm statistics and the norm weight applied on the way when the norm is fused;
+//   * the arithmetic runs on the tensor cores (`mma.sync.m16n8k16`, bf16 → fp32): 16 weight rows are the A operand, the
+//     ≤ 8 tokens the B operand's 8 columns.  A dot product does not care about the order of its terms, so a lane loads 8
+//     CONSECUTIVE k of a row (one 16-byte piece) and feeds register pairs to two MMAs; the activations use the same
+//     permutation of k.   lane = 4·g + t: A rows g and g+8, k ∈ [32c + 8t, 32c + 8t + 8); B column (token) g, same k.
 //
 //   gemv            y[M, N] = norm?(x (+ residual)) · W[N, K]ᵀ (+ bias)       M ≤ 16; optional fused add + RMSNorm prologue
 //   moe_gemv_up     act[pair, F] = silu(W13[e][:F] x) · (W13[e][F:] x)        per distinct expert of the step, T ≤ 8 tokens
@@ -26,10 +29,23 @@ using bf16 = __nv_bfloat16;
 static constexpr int kWarps = 8;
 static constexpr int kThreads = kWarps * 32;
 
-__device__ __forceinline__ uint4 ld_stream(const void* p) {
+__device__ __forceinline__ uint32_t smem_addr(const void* p) { return static_cast<uint32_t>(__cvta_generic_to_shared(p)); }
+__device__ __forceinline__ void cp16(uint32_t dst, const void* src) {
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst), "l"(src) : "memory");
+}
+__device__ __forceinline__ void cp_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N>
+__device__ __forceinline__ void cp_wait() {
+  asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory");
+}
+__device__ __forceinline__ uint4 lds16(uint32_t addr) {
   uint4 v;
-  asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p));
+  asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(addr) : "memory");
   return v;
+}
+// the calling thread's slot of the weight ring: [stage][row g | row g+8][thread] × 16 bytes (conflict-free both ways)
+__device__ __forceinline__ uint32_t ring_slot(uint32_t ring, int stage, int which) {
+  return ring + (((((stage << 1) + which) * kThreads) + threadIdx.x) << 4);
 }
 
 __device__ __forceinline__ void mma_bf16(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0, uint32_t b1) {
@@ -37,38 +53,18 @@ __device__ __forceinline__ void mma_bf16(float (&c)[4], uint32_t a0, uint32_t a1
                : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
                : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
 }
-
 // rows wa (row g) and wb (row g+8), activations xv: two MMAs cover the lane's 8 k
 __device__ __forceinline__ void mma_pair(float (&c)[4], const uint4& wa, const uint4& wb, const uint4& xv) {
   mma_bf16(c, wa.x, wb.x, wa.y, wb.y, xv.x, xv.y);
   mma_bf16(c, wa.z, wb.z, wa.w, wb.w, xv.z, xv.w);
 }
 
-__device__ __forceinline__ float2 unpack2(uint32_t v) {
-  return make_float2(__uint_as_float(v << 16), __uint_as_float(v & 0xffff0000u));
-}
+__device__ __forceinline__ float2 unpack2(uint32_t v) { return make_float2(__uint_as_float(v << 16), __uint_as_float(v & 0xffff0000u)); }
 __device__ __forceinline__ uint32_t pack2(float lo, float hi) {
   __nv_bfloat162 h = __floats2bfloat162_rn(lo, hi);
   return *reinterpret_cast<uint32_t*>(&h);
 }
-
-struct GemvParams {
-  const bf16* x;          // [M, K]
-  const bf16* residual;   // [M, K] or null (NORM only)
-  const bf16* norm_w;     // [K] (NORM only)
-  float eps;
-  const bf16* W;          // [N, K]
-  const bf16* bias;       // [N] or null
-  void* y;                // [M, ldy] bf16 or fp32
-  long long ldy;
-  int out_fp32;
-  bf16* res_out;          // [M, K] or null: bf16(x + residual), written by block 0
-  bf16* xn_out;           // [M, K] or null: the normalised activations, written by block 0
-  int M, N, K;
-  int static_w;           // W is not written by a kernel that may still run: its first loads go before the dependency wait
-};
-
-// h = bf16(x + residual) for the lane's 8 k of one token; returns Σ h²
+// h = bf16(x + residual) for 8 elements; returns Σ h²
 __device__ __forceinline__ float add_residual(uint4& xv, const uint4& rv) {
   float ss = 0.f;
   uint32_t* xs = &xv.x;
@@ -104,14 +100,95 @@ __device__ __forceinline__ uint4 scale8(const uint4& xv, const uint4& wv, float 
   }
   return o;
 }
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  return v;
+}
 
-// NT: groups of 8 tokens (1 or 2).  One CTA = 16 output rows; its 8 warps take the 32-wide k chunks round-robin.
-template <int NT, bool NORM>
+// Row stride of activations staged in shared memory: ≡ 64 (mod 128) bytes, so the two token rows a quarter-warp reads
+// (8 lanes × 16 bytes) fall on disjoint banks.
+__host__ __device__ inline int staged_stride(int K) { return K * 2 + 64; }
+
+// Stage rows [0, rows) of a [*, K] bf16 matrix into shared memory (rows ≥ valid are zero); warp w takes rows w, w+8, ….
+// NORM: h = bf16(x + residual) (block 0 also writes it to res_out), Σh² → rstd[row], the staged value is bf16(h · norm_w).
+template <bool NORM>
+__device__ __forceinline__ void stage_rows(uint8_t* xs, int rows, int valid, int K, const bf16* __restrict__ x,
+                                           const bf16* __restrict__ residual, const bf16* __restrict__ norm_w, float eps,
+                                           bf16* res_out, float* rstd) {
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int nv = K / 8, stride = staged_stride(K);
+  constexpr int B = 4;
+  for (int r = warp; r < rows; r += kWarps) {
+    uint8_t* row = xs + r * stride;
+    float ss = 0.f;
+    if (r < valid) {
+      const bf16* xr = x + static_cast<long long>(r) * K;
+      for (int v0 = lane; v0 < nv; v0 += 32 * B) {
+        uint4 xb[B], rb[B], nb[B];
+#pragma unroll
+        for (int u = 0; u < B; ++u) {
+          const int v = v0 + 32 * u;
+          if (v < nv) {
+            xb[u] = *reinterpret_cast<const uint4*>(xr + v * 8);
+            if (NORM) {
+              if (residual != nullptr) rb[u] = *reinterpret_cast<const uint4*>(residual + static_cast<long long>(r) * K + v * 8);
+              nb[u] = *reinterpret_cast<const uint4*>(norm_w + v * 8);
+            }
+          }
+        }
+#pragma unroll
+        for (int u = 0; u < B; ++u) {
+          const int v = v0 + 32 * u;
+          if (v < nv) {
+            if (NORM) {
+              if (residual != nullptr) {
+                ss += add_residual(xb[u], rb[u]);
+                if (res_out != nullptr && blockIdx.x == 0) *reinterpret_cast<uint4*>(res_out + static_cast<long long>(r) * K + v * 8) = xb[u];
+              } else {
+                ss += sumsq8(xb[u]);
+              }
+              xb[u] = scale8(xb[u], nb[u], 1.f);
+            }
+            *reinterpret_cast<uint4*>(row + v * 16) = xb[u];
+          }
+        }
+      }
+    } else {
+      for (int v = lane; v < nv; v += 32) *reinterpret_cast<uint4*>(row + v * 16) = make_uint4(0, 0, 0, 0);
+    }
+    if (NORM) {
+      ss = warp_sum(ss);
+      if (lane == 0) rstd[r] = rsqrtf(ss / K + eps);
+    }
+  }
+}
+
+struct GemvParams {
+  const bf16* x;          // [M, K]
+  const bf16* residual;   // [M, K] or null (NORM only)
+  const bf16* norm_w;     // [K] (NORM only)
+  float eps;
+  const bf16* W;          // [N, K]
+  const bf16* bias;       // [N] or null
+  void* y;                // [M, ldy] bf16 or fp32
+  long long ldy;
+  int out_fp32;
+  bf16* res_out;          // [M, K] or null: bf16(x + residual), written by block 0
+  bf16* xn_out;           // [M, K] or null: the normalised activations, written by block 0
+  int M, N, K;
+  int static_w;           // W is not written by a kernel that may still run: its first loads go before the dependency wait
+};
+
+// NT: groups of 8 tokens (1 or 2); S: ring stages.  One CTA = 16 output rows; its 8 warps take the 32-wide k chunks round-robin.
+template <int NT, bool NORM, int S>
 __global__ void __launch_bounds__(kThreads) gemv_kernel(GemvParams p) {
+  extern __shared__ __align__(128) uint8_t smem[];
   __shared__ float red[kWarps][NT][16][8];
-  __shared__ float ssq[kWarps][NT][8];
-  __shared__ float rstd_s[NT][8];
+  __shared__ float rstd_s[NT * 8];
   pdl_trigger();
+  const uint32_t ring = smem_addr(smem);
+  uint8_t* xs = smem + S * 2 * kThreads * 16;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int g = lane >> 2, t = lane & 3;
   const int n0 = blockIdx.x * 16;
@@ -119,84 +196,43 @@ __global__ void __launch_bounds__(kThreads) gemv_kernel(GemvParams p) {
   const bf16* wa_ptr = p.W + static_cast<long long>(ra) * p.K + t * 8;
   const bf16* wb_ptr = p.W + static_cast<long long>(rb) * p.K + t * 8;
   const int chunks = p.K / 32;
-  float c[NT][4] = {};
-  float ss[NT] = {};
-  bool tok_ok[NT];
-  const bf16* x_ptr[NT];
-  const bf16* r_ptr[NT];
-#pragma unroll
-  for (int j = 0; j < NT; ++j) {
-    const int tok = g + 8 * j;
-    tok_ok[j] = tok < p.M;
-    x_ptr[j] = p.x + static_cast<long long>(tok_ok[j] ? tok : 0) * p.K + t * 8;
-    r_ptr[j] = (NORM && p.residual != nullptr) ? p.residual + static_cast<long long>(tok_ok[j] ? tok : 0) * p.K + t * 8 : nullptr;
-  }
-  // static weights do not depend on the previous kernel: their first loads are issued before the dependency wait
-  constexpr int U = 8;
+  const int n_i = chunks > warp ? (chunks - warp + kWarps - 1) / kWarps : 0;   // this warp's chunks: warp, warp + 8, …
+  auto issue = [&](int i) {
+    if (i < n_i) {
+      const int ch = warp + i * kWarps;
+      cp16(ring_slot(ring, i & (S - 1), 0), wa_ptr + ch * 32);
+      cp16(ring_slot(ring, i & (S - 1), 1), wb_ptr + ch * 32);
+    }
+    cp_commit();
+  };
   if (!p.static_w) pdl_wait();
-  for (int c0 = warp; c0 < chunks; c0 += kWarps * U) {
-    uint4 wa[U], wb[U];
 #pragma unroll
-    for (int u = 0; u < U; ++u) {
-      const int ch = c0 + u * kWarps;
-      if (ch < chunks) {
-        wa[u] = ld_stream(wa_ptr + ch * 32);
-        wb[u] = ld_stream(wb_ptr + ch * 32);
-      }
+  for (int i = 0; i < S; ++i) issue(i);
+  if (p.static_w) pdl_wait();          // static weights: their first loads are already in flight
+  stage_rows<NORM>(xs, NT * 8, p.M, p.K, p.x, p.residual, p.norm_w, p.eps, p.res_out, rstd_s);
+  __syncthreads();
+  const int stride = staged_stride(p.K);
+  float c[NT][4] = {};
+  for (int i = 0; i < n_i; ++i) {
+    cp_wait<S - 1>();
+    const int st = i & (S - 1), ch = warp + i * kWarps;
+    const uint4 wa = lds16(ring_slot(ring, st, 0)), wb = lds16(ring_slot(ring, st, 1));
+#pragma unroll
+    for (int j = 0; j < NT; ++j) {
+      const uint4 xv = *reinterpret_cast<const uint4*>(xs + (g + 8 * j) * stride + ch * 64 + t * 16);
+      mma_pair(c[j], wa, wb, xv);
     }
-    if (c0 == warp && p.static_w) pdl_wait();
-#pragma unroll
-    for (int u = 0; u < U; ++u) {
-      const int ch = c0 + u * kWarps;
-      if (ch < chunks) {
-#pragma unroll
-        for (int j = 0; j < NT; ++j) {
-          uint4 xv = make_uint4(0, 0, 0, 0);
-          if (tok_ok[j]) {
-            xv = *reinterpret_cast<const uint4*>(x_ptr[j] + ch * 32);
-            if (NORM) {
-              if (r_ptr[j] != nullptr) {
-                const uint4 rv = *reinterpret_cast<const uint4*>(r_ptr[j] + ch * 32);
-                ss[j] += add_residual(xv, rv);
-                if (p.res_out != nullptr && blockIdx.x == 0)
-                  *reinterpret_cast<uint4*>(p.res_out + static_cast<long long>(g + 8 * j) * p.K + ch * 32 + t * 8) = xv;
-              } else {
-                ss[j] += sumsq8(xv);
-              }
-              const uint4 nw = *reinterpret_cast<const uint4*>(p.norm_w + ch * 32 + t * 8);
-              xv = scale8(xv, nw, 1.f);
-            }
-          }
-          mma_pair(c[j], wa[u], wb[u], xv);
-        }
-      }
-    }
+    issue(i + S);
   }
-  if (chunks <= warp && p.static_w) pdl_wait();
+  cp_wait<0>();
 #pragma unroll
   for (int j = 0; j < NT; ++j) {
     red[warp][j][g][2 * t] = c[j][0];
     red[warp][j][g][2 * t + 1] = c[j][1];
     red[warp][j][g + 8][2 * t] = c[j][2];
     red[warp][j][g + 8][2 * t + 1] = c[j][3];
-    if (NORM) {
-      float s = ss[j];
-      s += __shfl_xor_sync(0xffffffffu, s, 1);
-      s += __shfl_xor_sync(0xffffffffu, s, 2);
-      if (t == 0) ssq[warp][j][g] = s;
-    }
   }
   __syncthreads();
-  if (NORM) {
-    if (threadIdx.x < NT * 8) {
-      const int j = threadIdx.x >> 3, tk = threadIdx.x & 7;
-      float s = 0.f;
-#pragma unroll
-      for (int w = 0; w < kWarps; ++w) s += ssq[w][j][tk];
-      rstd_s[j][tk] = rsqrtf(s / p.K + p.eps);
-    }
-    __syncthreads();
-  }
   for (int i = threadIdx.x; i < NT * 128; i += kThreads) {
     const int j = i >> 7, tk = (i >> 4) & 7, row = i & 15;
     const int tok = tk + 8 * j, n = n0 + row;
@@ -204,7 +240,7 @@ __global__ void __launch_bounds__(kThreads) gemv_kernel(GemvParams p) {
       float s = 0.f;
 #pragma unroll
       for (int w = 0; w < kWarps; ++w) s += red[w][j][row][tk];
-      if (NORM) s *= rstd_s[j][tk];
+      if (NORM) s *= rstd_s[tok];
       if (p.bias != nullptr) s += __bfloat162float(p.bias[n]);
       if (p.out_fp32) reinterpret_cast<float*>(p.y)[tok * p.ldy + n] = s;
       else reinterpret_cast<bf16*>(p.y)[tok * p.ldy + n] = __float2bfloat16(s);
@@ -220,7 +256,7 @@ __global__ void __launch_bounds__(kThreads) gemv_kernel(GemvParams p) {
         add_residual(xv, rv);
       }
       const uint4 nw = *reinterpret_cast<const uint4*>(p.norm_w + kv);
-      *reinterpret_cast<uint4*>(p.xn_out + static_cast<long long>(tok) * p.K + kv) = scale8(xv, nw, rstd_s[tok >> 3][tok & 7]);
+      *reinterpret_cast<uint4*>(p.xn_out + static_cast<long long>(tok) * p.K + kv) = scale8(xv, nw, rstd_s[tok]);
     }
   }
 }
@@ -231,6 +267,7 @@ __global__ void __launch_bounds__(kThreads) gemv_kernel(GemvParams p) {
 // with ballots.
 // ---------------------------------------------------------------------------------------------
 static constexpr int kMaxPairs = 64;
+static constexpr int kMoeStages = 8;
 
 struct PairIdx { int lo, hi; };   // local expert of pairs `lane` and `lane + 32`; −1: no pair, or an expert of another rank
 
@@ -259,142 +296,182 @@ __device__ __forceinline__ int pair_of(unsigned long long mask, int tok, int k) 
 }
 
 // Persistent grid over (distinct expert, block of 8 features): an item computes gate rows f0..f0+7 and up rows F+f0..F+f0+7
-// of the expert for all tokens and stores silu(gate) · up for the tokens routed to it.
+// of the expert for all tokens and stores silu(gate) · up for the tokens routed to it.  A warp's weight stream runs
+// across its items without a break (the ring keeps filling while the CTA reduces and stores an item).
 __global__ void __launch_bounds__(kThreads) moe_gemv_up_kernel(const bf16* __restrict__ x, const bf16* __restrict__ w13,
                                                                const int* __restrict__ topk_idx, bf16* __restrict__ act, int T, int k,
                                                                int E, int offset, int H, int F) {
+  constexpr int S = kMoeStages;
+  extern __shared__ __align__(128) uint8_t smem[];
   __shared__ float red[kWarps][16][8];
+  __shared__ int slot_e[kMaxPairs];
+  __shared__ unsigned long long slot_mask[kMaxPairs];
+  __shared__ int n_slots_s;
   pdl_trigger();
   pdl_wait();
+  const uint32_t ring = smem_addr(smem);
+  uint8_t* xs = smem + S * 2 * kThreads * 16;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int g = lane >> 2, t = lane & 3;
   const int n_pairs = T * k;
-  const PairIdx pi = load_pairs(topk_idx, n_pairs, E, offset);
-  // bit p of `firsts`: pair p is the first pair of its (local) expert — one bit per distinct expert of the step
-  unsigned long long firsts = 0ull;
-  for (int p = 0; p < n_pairs; ++p) {
-    const int e = expert_of(pi, p);
-    if (e >= 0 && is_first(match_mask(pi, e), p)) firsts |= 1ull << p;
-  }
-  const int nfb = F / 8;
-  const int n_items = __popcll(firsts) * nfb;
-  const bool tok_ok = g < T;
-  const bf16* x_ptr = x + static_cast<long long>(tok_ok ? g : 0) * H + t * 8;
-  const int chunks = H / 32;
-  constexpr int U = 8;
-  // work item = (distinct expert s, block of 8 features); consecutive CTAs take consecutive feature blocks of one expert
-  for (int item = blockIdx.x; item < n_items; item += gridDim.x) {
-  const int s = item / nfb;
-  unsigned long long rest = firsts;
-  for (int i = 0; i < s; ++i) rest &= rest - 1ull;
-  const int p = __ffsll(static_cast<long long>(rest)) - 1;
-  const int e = expert_of(pi, p);
-  const unsigned long long mask = match_mask(pi, e);
-  const int f0 = (item % nfb) * 8;
-  const bf16* base = w13 + static_cast<long long>(e) * 2 * F * H;
-  const bf16* wa_ptr = base + static_cast<long long>(f0 + g) * H + t * 8;
-  const bf16* wb_ptr = base + static_cast<long long>(F + f0 + g) * H + t * 8;
-  float c[4] = {};
-  for (int c0 = warp; c0 < chunks; c0 += kWarps * U) {
-    uint4 wa[U], wb[U];
-#pragma unroll
-    for (int u = 0; u < U; ++u) {
-      const int ch = c0 + u * kWarps;
-      if (ch < chunks) {
-        wa[u] = ld_stream(wa_ptr + ch * 32);
-        wb[u] = ld_stream(wb_ptr + ch * 32);
-      }
+  if (warp == 0) {
+    // the distinct experts of the step, in order of first appearance
+    const PairIdx pi = load_pairs(topk_idx, n_pairs, E, offset);
+    int cnt = 0;
+    for (int p = 0; p < n_pairs; ++p) {
+      const int e = expert_of(pi, p);
+      if (e < 0) continue;
+      const unsigned long long m = match_mask(pi, e);
+      if (!is_first(m, p)) continue;
+      if (lane == 0) { slot_e[cnt] = e; slot_mask[cnt] = m; }
+      ++cnt;
     }
-#pragma unroll
-    for (int u = 0; u < U; ++u) {
-      const int ch = c0 + u * kWarps;
-      if (ch < chunks) {
-        const uint4 xv = tok_ok ? *reinterpret_cast<const uint4*>(x_ptr + ch * 32) : make_uint4(0, 0, 0, 0);
-        mma_pair(c, wa[u], wb[u], xv);
-      }
-    }
+    if (lane == 0) n_slots_s = cnt;
   }
-  red[warp][g][2 * t] = c[0];
-  red[warp][g][2 * t + 1] = c[1];
-  red[warp][g + 8][2 * t] = c[2];
-  red[warp][g + 8][2 * t + 1] = c[3];
+  stage_rows<false>(xs, 8, T, H, x, nullptr, nullptr, 0.f, nullptr, nullptr);
   __syncthreads();
-  if (threadIdx.x < 64) {
-    const int f = threadIdx.x & 7, tok = threadIdx.x >> 3;
-    const int pair = tok < T ? pair_of(mask, tok, k) : -1;
-    if (pair >= 0) {
-      float gate = 0.f, up = 0.f;
-#pragma unroll
-      for (int w = 0; w < kWarps; ++w) {
-        gate += red[w][f][tok];
-        up += red[w][f + 8][tok];
-      }
-      // the two halves are rounded to bf16 first, like the stored pre-activation of the general path
-      gate = __bfloat162float(__float2bfloat16(gate));
-      up = __bfloat162float(__float2bfloat16(up));
-      const float a = gate / (1.f + __expf(-gate)) * up;
-      act[static_cast<long long>(pair) * F + f0 + f] = __float2bfloat16(a);
+  const int nfb = F / 8;
+  const int n_items = n_slots_s * nfb;
+  const int n_mine = n_items > static_cast<int>(blockIdx.x) ? (n_items - blockIdx.x + gridDim.x - 1) / gridDim.x : 0;
+  const int chunks = H / 32;
+  const int cpw = chunks > warp ? (chunks - warp + kWarps - 1) / kWarps : 0;     // chunks of an item taken by this warp
+  const int total = n_mine * cpw;
+  const int stride = staged_stride(H);
+  auto issue = [&](int q) {
+    if (q < total) {
+      const int j = q / cpw, u = q - j * cpw;
+      const int item = blockIdx.x + j * gridDim.x;
+      const int e = slot_e[item / nfb], f0 = (item % nfb) * 8, ch = warp + u * kWarps;
+      const bf16* base = w13 + static_cast<long long>(e) * 2 * F * H + ch * 32 + t * 8;
+      cp16(ring_slot(ring, q & (S - 1), 0), base + static_cast<long long>(f0 + g) * H);
+      cp16(ring_slot(ring, q & (S - 1), 1), base + static_cast<long long>(F + f0 + g) * H);
     }
+    cp_commit();
+  };
+#pragma unroll
+  for (int q = 0; q < S; ++q) issue(q);
+  int q = 0;
+  for (int j = 0; j < n_mine; ++j) {
+    const int item = blockIdx.x + j * gridDim.x;
+    const int s = item / nfb, f0 = (item % nfb) * 8;
+    float c[4] = {};
+    for (int u = 0; u < cpw; ++u, ++q) {
+      cp_wait<S - 1>();
+      const int st = q & (S - 1), ch = warp + u * kWarps;
+      const uint4 wa = lds16(ring_slot(ring, st, 0)), wb = lds16(ring_slot(ring, st, 1));
+      const uint4 xv = *reinterpret_cast<const uint4*>(xs + g * stride + ch * 64 + t * 16);
+      mma_pair(c, wa, wb, xv);
+      issue(q + S);
+    }
+    red[warp][g][2 * t] = c[0];
+    red[warp][g][2 * t + 1] = c[1];
+    red[warp][g + 8][2 * t] = c[2];
+    red[warp][g + 8][2 * t + 1] = c[3];
+    __syncthreads();
+    if (threadIdx.x < 64) {
+      const int f = threadIdx.x & 7, tok = threadIdx.x >> 3;
+      const int pair = tok < T ? pair_of(slot_mask[s], tok, k) : -1;
+      if (pair >= 0) {
+        float gate = 0.f, up = 0.f;
+#pragma unroll
+        for (int w = 0; w < kWarps; ++w) {
+          gate += red[w][f][tok];
+          up += red[w][f + 8][tok];
+        }
+        // the two halves are rounded to bf16 first, like the stored pre-activation of the general path
+        gate = __bfloat162float(__float2bfloat16(gate));
+        up = __bfloat162float(__float2bfloat16(up));
+        const float a = gate / (1.f + __expf(-gate)) * up;
+        act[static_cast<long long>(pair) * F + f0 + f] = __float2bfloat16(a);
+      }
+    }
+    __syncthreads();   // `red` is reused by the next item
   }
-  __syncthreads();   // `red` is reused by the next item
-  }
+  cp_wait<0>();
 }
 
-// grid (H/16): CTA hb accumulates rows h0..h0+15 of the output over all experts of the step; warp w looks at pairs w, w+8, …
-// and works on those that are the first pair of their expert.
+// grid (H/16): CTA hb accumulates rows h0..h0+15 of the output over all distinct experts of the step; its 8 warps take
+// the 32-wide k chunks of EVERY expert round-robin (equal work per warp whatever the routing), a warp's weight stream runs
+// across the experts without a break.
 // out[t, h] = Σ_experts gate_w(t, e) · (W2[e][h, :] · act[pair(t, e), :])
 __global__ void __launch_bounds__(kThreads) moe_gemv_down_kernel(const bf16* __restrict__ act, const bf16* __restrict__ w2,
                                                                  const int* __restrict__ topk_idx, const float* __restrict__ topk_w,
                                                                  bf16* __restrict__ out, int T, int k, int E, int offset, int H, int F) {
+  constexpr int S = kMoeStages;
+  extern __shared__ __align__(128) uint8_t smem[];
   __shared__ float red[kWarps][16][8];
+  __shared__ int sl_e[kMaxPairs];
+  __shared__ signed char sl_pair[kMaxPairs][8];
+  __shared__ float sl_gw[kMaxPairs][8];
+  __shared__ int n_slots_s;
   pdl_trigger();
   pdl_wait();
+  const uint32_t ring = smem_addr(smem);
+  uint8_t* as = smem + S * 2 * kThreads * 16;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int g = lane >> 2, t = lane & 3;
   const int h0 = blockIdx.x * 16;
   const int chunks = F / 32;
   const int n_pairs = T * k;
-  const PairIdx pi = load_pairs(topk_idx, n_pairs, E, offset);
-  float c[4] = {};
-  constexpr int U = 8;
-  for (int p = warp; p < n_pairs; p += kWarps) {
-    const int e = expert_of(pi, p);
-    if (e < 0) continue;
-    const unsigned long long mask = match_mask(pi, e);
-    if (!is_first(mask, p)) continue;
-    const int pair = g < T ? pair_of(mask, g, k) : -1;
-    const float gw = pair >= 0 ? topk_w[pair] : 0.f;
-    const bf16* base = w2 + static_cast<long long>(e) * H * F;
-    const bf16* wa_ptr = base + static_cast<long long>(h0 + g) * F + t * 8;
-    const bf16* wb_ptr = base + static_cast<long long>(h0 + g + 8) * F + t * 8;
-    const bf16* a_ptr = act + static_cast<long long>(pair >= 0 ? pair : 0) * F + t * 8;
-    float cs[4] = {};
-    for (int c0 = 0; c0 < chunks; c0 += U) {
-      uint4 wa[U], wb[U];
-#pragma unroll
-      for (int u = 0; u < U; ++u) {
-        if (c0 + u < chunks) {
-          wa[u] = ld_stream(wa_ptr + (c0 + u) * 32);
-          wb[u] = ld_stream(wb_ptr + (c0 + u) * 32);
-        }
+  if (warp == 0) {
+    // the distinct experts of the step with, per token, the pair routed to them and its gate weight
+    const PairIdx pi = load_pairs(topk_idx, n_pairs, E, offset);
+    int cnt = 0;
+    for (int p = 0; p < n_pairs; ++p) {
+      const int e = expert_of(pi, p);
+      if (e < 0) continue;
+      const unsigned long long mask = match_mask(pi, e);
+      if (!is_first(mask, p)) continue;
+      if (lane < 8) {
+        const int pair = lane < T ? pair_of(mask, lane, k) : -1;
+        sl_pair[cnt][lane] = static_cast<signed char>(pair);
+        sl_gw[cnt][lane] = pair >= 0 ? topk_w[pair] : 0.f;
       }
-#pragma unroll
-      for (int u = 0; u < U; ++u) {
-        if (c0 + u < chunks) {
-          const uint4 xv = pair >= 0 ? *reinterpret_cast<const uint4*>(a_ptr + (c0 + u) * 32) : make_uint4(0, 0, 0, 0);
-          mma_pair(cs, wa[u], wb[u], xv);
-        }
-      }
+      if (lane == 0) sl_e[cnt] = e;
+      ++cnt;
     }
-    // accumulator columns 2t and 2t+1 are other tokens than this lane's B column: fetch their gate weights from the
-    // lanes that own those tokens
-    const float gw0 = __shfl_sync(0xffffffffu, gw, (2 * t) * 4);
-    const float gw1 = __shfl_sync(0xffffffffu, gw, (2 * t + 1) * 4);
+    if (lane == 0) n_slots_s = cnt;
+  }
+  // all pair rows of the activations → shared memory (rows of other ranks' experts are never read)
+  stage_rows<false>(as, n_pairs, n_pairs, F, act, nullptr, nullptr, 0.f, nullptr, nullptr);
+  __syncthreads();
+  const int cnt = n_slots_s;
+  const int cpw = chunks > warp ? (chunks - warp + kWarps - 1) / kWarps : 0;      // chunks of an expert taken by this warp
+  const int total = cnt * cpw;
+  auto issue = [&](int q) {
+    if (q < total) {
+      const int j = q / cpw, u = q - j * cpw;
+      const bf16* base = w2 + static_cast<long long>(sl_e[j]) * H * F + (warp + u * kWarps) * 32 + t * 8;
+      cp16(ring_slot(ring, q & (S - 1), 0), base + static_cast<long long>(h0 + g) * F);
+      cp16(ring_slot(ring, q & (S - 1), 1), base + static_cast<long long>(h0 + g + 8) * F);
+    }
+    cp_commit();
+  };
+#pragma unroll
+  for (int q = 0; q < S; ++q) issue(q);
+  const int stride = staged_stride(F);
+  float c[4] = {};
+  int q = 0;
+  for (int j = 0; j < cnt; ++j) {
+    const int pair = sl_pair[j][g];
+    const uint8_t* arow = as + (pair >= 0 ? pair : 0) * stride + t * 16;
+    float cs[4] = {};
+    for (int u = 0; u < cpw; ++u, ++q) {
+      cp_wait<S - 1>();
+      const int st = q & (S - 1);
+      const uint4 wa = lds16(ring_slot(ring, st, 0)), wb = lds16(ring_slot(ring, st, 1));
+      const uint4 xv = pair >= 0 ? *reinterpret_cast<const uint4*>(arow + (warp + u * kWarps) * 64) : make_uint4(0, 0, 0, 0);
+      mma_pair(cs, wa, wb, xv);
+      issue(q + S);
+    }
+    // accumulator columns 2t and 2t+1 are tokens 2t and 2t+1
+    const float gw0 = sl_gw[j][2 * t], gw1 = sl_gw[j][2 * t + 1];
     c[0] += gw0 * cs[0];
     c[1] += gw1 * cs[1];
     c[2] += gw0 * cs[2];
     c[3] += gw1 * cs[3];
   }
+  cp_wait<0>();
   red[warp][g][2 * t] = c[0];
   red[warp][g][2 * t + 1] = c[1];
   red[warp][g + 8][2 * t] = c[2];
@@ -411,13 +488,33 @@ __global__ void __launch_bounds__(kThreads) moe_gemv_down_kernel(const bf16* __r
   }
 }
 
+template <typename K>
+static cudaError_t set_smem(K kernel, int bytes) {
+  return cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes);
+}
+
+static constexpr int kDenseStages = 4;
+static constexpr int kMaxSmem = 200 * 1024;
+
+template <int NT, bool NORM>
+static cudaError_t launch_gemv(const GemvParams& p, cudaStream_t s) {
+  const int bytes = kDenseStages * 2 * kThreads * 16 + NT * 8 * staged_stride(p.K);
+  static int configured = 0;
+  if (configured < bytes) {
+    cudaError_t e = set_smem(gemv_kernel<NT, NORM, kDenseStages>, kMaxSmem);
+    if (e != cudaSuccess) return e;
+    configured = kMaxSmem;
+  }
+  return launch_pdl(gemv_kernel<NT, NORM, kDenseStages>, dim3((p.N + 15) / 16), dim3(kThreads), bytes, s, p);
+}
+
 }  // namespace gv
 }  // namespace mb
 
 using namespace mb;
 using namespace mb::gv;
 
-// y[M, N] = norm?(x (+ residual)) · Wᵀ (+ bias).  M ≤ 16, K a multiple of 32, 16-byte aligned rows.
+// y[M, N] = norm?(x (+ residual)) · Wᵀ (+ bias).  M ≤ 16, K a multiple of 32 (≤ 8192 for M ≤ 8, ≤ 4096 above), 16-byte aligned rows.
 // norm_w != null: RMSNorm over K with weight norm_w (after adding `residual` when given) is applied to x first; res_out / xn_out
 // (optional) receive bf16(x + residual) and the normalised activations.  static_w: W is a parameter (not produced by a kernel that
 // may still be running), so its loads may start before the previous kernel has finished.
@@ -425,6 +522,8 @@ extern "C" int mb_gemv(const void* x, const void* residual, const void* norm_w, 
                        long long ldy, int out_fp32, void* res_out, void* xn_out, int M, int N, int K, int static_w, cudaStream_t s) {
   if (M <= 0 || N <= 0) return 0;
   if (M > 16 || K % 32 || K <= 0) return -1;
+  const int nt = M <= 8 ? 1 : 2;
+  if (kDenseStages * 2 * kThreads * 16 + nt * 8 * staged_stride(K) > kMaxSmem) return -2;
   GemvParams p{};
   p.x = reinterpret_cast<const bf16*>(x);
   p.residual = reinterpret_cast<const bf16*>(residual);
@@ -436,24 +535,34 @@ extern "C" int mb_gemv(const void* x, const void* residual, const void* norm_w, 
   p.res_out = reinterpret_cast<bf16*>(res_out);
   p.xn_out = reinterpret_cast<bf16*>(xn_out);
   p.M = M; p.N = N; p.K = K; p.static_w = static_w;
-  const dim3 grid((N + 15) / 16), block(kThreads);
   cudaError_t e;
-  if (norm_w != nullptr) e = M <= 8 ? launch_pdl(gemv_kernel<1, true>, grid, block, 0, s, p) : launch_pdl(gemv_kernel<2, true>, grid, block, 0, s, p);
-  else e = M <= 8 ? launch_pdl(gemv_kernel<1, false>, grid, block, 0, s, p) : launch_pdl(gemv_kernel<2, false>, grid, block, 0, s, p);
+  if (norm_w != nullptr) e = nt == 1 ? launch_gemv<1, true>(p, s) : launch_gemv<2, true>(p, s);
+  else e = nt == 1 ? launch_gemv<1, false>(p, s) : launch_gemv<2, false>(p, s);
   return static_cast<int>(e);
 }
 
-// MoE FFN for T ≤ 8 tokens (T·k ≤ 64): act [T·k, F] scratch, out [T, H].  F a multiple of 32 (and of 8), H a multiple of 32.
+// MoE FFN for T ≤ 8 tokens (T·k ≤ 64): act [T·k, F] scratch, out [T, H].  H and F multiples of 32, H a multiple of 16.
 extern "C" int mb_moe_gemv(const void* x, const void* w13, const void* w2, const int* topk_idx, const float* topk_w, void* act, void* out,
                            int T, int k, int E, int expert_offset, int H, int F, cudaStream_t s) {
   if (T <= 0) return 0;
   if (T > 8 || T * k > kMaxPairs || H % 32 || F % 32) return -1;
+  const int ring_bytes = kMoeStages * 2 * kThreads * 16;
+  const int up_bytes = ring_bytes + 8 * staged_stride(H);
+  const int down_bytes = ring_bytes + T * k * staged_stride(F);
+  if (up_bytes > kMaxSmem || down_bytes > kMaxSmem) return -2;
+  static bool configured = false;
+  if (!configured) {
+    cudaError_t e = set_smem(moe_gemv_up_kernel, kMaxSmem);
+    if (e == cudaSuccess) e = set_smem(moe_gemv_down_kernel, kMaxSmem);
+    if (e != cudaSuccess) return static_cast<int>(e);
+    configured = true;
+  }
   const int max_items = (T * k < E ? T * k : E) * (F / 8);
   const int up_grid = max_items < 2 * 148 ? max_items : 2 * 148;
-  cudaError_t e = launch_pdl(moe_gemv_up_kernel, dim3(up_grid), dim3(kThreads), 0, s, reinterpret_cast<const bf16*>(x),
+  cudaError_t e = launch_pdl(moe_gemv_up_kernel, dim3(up_grid), dim3(kThreads), up_bytes, s, reinterpret_cast<const bf16*>(x),
                              reinterpret_cast<const bf16*>(w13), topk_idx, reinterpret_cast<bf16*>(act), T, k, E, expert_offset, H, F);
   if (e != cudaSuccess) return static_cast<int>(e);
-  e = launch_pdl(moe_gemv_down_kernel, dim3(H / 16), dim3(kThreads), 0, s, reinterpret_cast<const bf16*>(act),
+  e = launch_pdl(moe_gemv_down_kernel, dim3(H / 16), dim3(kThreads), down_bytes, s, reinterpret_cast<const bf16*>(act),
                  reinterpret_cast<const bf16*>(w2), topk_idx, topk_w, reinterpret_cast<bf16*>(out), T, k, E, expert_offset, H, F);
   return static_cast<int>(e);
 }

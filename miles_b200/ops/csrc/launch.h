@@ -109,6 +109,8 @@ int mb_moe_combine_bwd(const void* dout, const void* y_perm, const float* w, con
                        void* dy_perm, float* dw, int k, int H, int max_rows, cudaStream_t s);
 
 // ---- misc.cu ----
+int mb_sample_logprob_split(const float* logits, const float* temperature, const uint8_t* greedy, const long long* seeds, long long step,
+                            long long* tokens, float* logprobs, int B, int V, int parts, float* ws, int* counters, cudaStream_t s);
 int mb_sample_logprob(const float* logits, const float* temperature, const uint8_t* greedy, const long long* seeds, long long step,
                       long long* tokens, float* logprobs, int B, int V, cudaStream_t s);
 int mb_logit_stats(const float* logits, long long ld, const long long* targets, float* stats, long long R, int Vc, int v0,

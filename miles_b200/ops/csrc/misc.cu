@@ -87,6 +87,75 @@ __global__ void __launch_bounds__(1024) sample_logprob_kernel(const float* __res
   }
 }
 
+// The same for few rows: `parts` CTAs per row each take a slice of the vocabulary and leave (max, Σexp, best score, best
+// index) in `ws`; the last CTA of a row to arrive (counter) merges the slices.  counters[row] is zero on entry and on exit.
+__global__ void __launch_bounds__(256) sample_logprob_split_kernel(const float* __restrict__ logits, const float* __restrict__ temperature,
+                                                                   const uint8_t* __restrict__ greedy, const long long* __restrict__ seeds,
+                                                                   long long step, long long* __restrict__ tokens,
+                                                                   float* __restrict__ logprobs, int V, int parts, float4* __restrict__ ws,
+                                                                   int* __restrict__ counters) {
+  __shared__ float sh_m[8], sh_s[8], sh_best[8];
+  __shared__ int sh_idx[8];
+  __shared__ int sh_last;
+  pdl_trigger();
+  pdl_wait();
+  const int row = blockIdx.x / parts, part = blockIdx.x % parts;
+  const float* x = logits + static_cast<long long>(row) * V;
+  const float it = 1.f / temperature[row];
+  const bool gr = greedy[row] != 0;
+  const uint64_t seed = static_cast<uint64_t>(seeds ? seeds[row] : row);
+  const int per = (V + parts - 1) / parts;
+  const int lo = part * per, hi = min(V, lo + per);
+  MS ms{-INFINITY, 0.f};
+  float best = -INFINITY;
+  int best_i = 0x7fffffff;
+  for (int i = lo + threadIdx.x; i < hi; i += 256) {
+    const float z = x[i] * it;
+    ms = ms_merge(ms, MS{z, 1.f});
+    float score = z;
+    if (!gr) score += -__logf(-__logf(uniform01(seed, static_cast<uint64_t>(step), static_cast<uint64_t>(i))));
+    if (score > best) { best = score; best_i = i; }
+  }
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  auto warp_merge = [&]() {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+      MS other{__shfl_xor_sync(0xffffffffu, ms.m, o), __shfl_xor_sync(0xffffffffu, ms.s, o)};
+      ms = ms_merge(ms, other);
+      const float ob = __shfl_xor_sync(0xffffffffu, best, o);
+      const int oi = __shfl_xor_sync(0xffffffffu, best_i, o);
+      if (ob > best || (ob == best && oi < best_i)) { best = ob; best_i = oi; }
+    }
+  };
+  warp_merge();
+  if (lane == 0) { sh_m[warp] = ms.m; sh_s[warp] = ms.s; sh_best[warp] = best; sh_idx[warp] = best_i; }
+  __syncthreads();
+  if (warp == 0) {
+    ms = (lane < 8) ? MS{sh_m[lane], sh_s[lane]} : MS{-INFINITY, 0.f};
+    best = (lane < 8) ? sh_best[lane] : -INFINITY;
+    best_i = (lane < 8) ? sh_idx[lane] : 0x7fffffff;
+    warp_merge();
+    if (lane == 0) {
+      __stcg(&ws[row * parts + part], make_float4(ms.m, ms.s, best, __int_as_float(best_i)));
+      __threadfence();
+      sh_last = atomicAdd(&counters[row], 1) == parts - 1;
+    }
+  }
+  __syncthreads();
+  if (!sh_last || warp != 0) return;
+  __threadfence();
+  float4 v = lane < parts ? __ldcg(&ws[row * parts + lane]) : make_float4(-INFINITY, 0.f, -INFINITY, __int_as_float(0x7fffffff));
+  ms = MS{v.x, v.y};
+  best = v.z;
+  best_i = __float_as_int(v.w);
+  warp_merge();
+  if (lane == 0) {
+    tokens[row] = best_i;
+    logprobs[row] = x[best_i] * it - (ms.m + __logf(ms.s));
+    counters[row] = 0;
+  }
+}
+
 // Streaming statistics over one vocabulary chunk.  stats[r] = {m, s, e, t}:
 //   m running max of z = logit·inv_temp, s = Σ exp(z − m), e = Σ exp(z − m)·z, t = z[target] (if in this chunk).
 __global__ void __launch_bounds__(256) logit_stats_kernel(const float* __restrict__ logits, long long ld, const long long* __restrict__ targets,
@@ -187,6 +256,16 @@ extern "C" int mb_sample_logprob(const float* logits, const float* temperature, 
   if (B == 0) return 0;
   return static_cast<int>(launch_pdl(sample_logprob_kernel, dim3(B), dim3(1024), 0, s, logits, temperature, greedy, seeds, step, tokens,
                                      logprobs, V));
+}
+
+// parts CTAs per row (2…32); ws: 4·B·parts floats; counters: B ints, zero on entry (and again on exit)
+extern "C" int mb_sample_logprob_split(const float* logits, const float* temperature, const uint8_t* greedy, const long long* seeds,
+                                       long long step, long long* tokens, float* logprobs, int B, int V, int parts, float* ws,
+                                       int* counters, cudaStream_t s) {
+  if (B == 0) return 0;
+  if (parts < 1 || parts > 32) return -1;
+  return static_cast<int>(launch_pdl(sample_logprob_split_kernel, dim3(B * parts), dim3(256), 0, s, logits, temperature, greedy, seeds, step,
+                                     tokens, logprobs, V, parts, reinterpret_cast<float4*>(ws), counters));
 }
 
 extern "C" int mb_logit_stats(const float* logits, long long ld, const long long* targets, float* stats, long long R, int Vc, int v0,

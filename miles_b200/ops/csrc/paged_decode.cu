@@ -50,7 +50,8 @@ __global__ void __launch_bounds__(128) paged_decode_mma_kernel(const bf16* __res
                                                                const bf16* __restrict__ vc, const int* __restrict__ block_table,
                                                                const int* __restrict__ seq_lens, float* __restrict__ part_o,
                                                                float* __restrict__ part_ml, int max_blocks, int block_size, int Hq,
-                                                               int Hkv, int group, float scale, int num_splits) {
+                                                               int Hkv, int group, float scale, int num_splits, bf16* __restrict__ out,
+                                                               int* __restrict__ counters) {
   extern __shared__ __align__(128) uint8_t smem_raw[];
   bf16* sQ = reinterpret_cast<bf16*>(smem_raw);   // 16 × D
   bf16* sK = sQ + 16 * D;                         // 2 × TK × D
@@ -193,9 +194,37 @@ __global__ void __launch_bounds__(128) paged_decode_mma_kernel(const bf16* __res
       oo += sO[(w * 8 + g) * D + d] * a;
     }
     const long long base = (static_cast<long long>(req) * Hq + hk * group + g) * num_splits + split;
-    part_o[base * D + d] = oo;
-    if (d == 0) { part_ml[base * 2] = (mm == -INFINITY) ? -INFINITY : mm * sl2; part_ml[base * 2 + 1] = ll; }
+    if (counters != nullptr && num_splits == 1) {          // a single split: normalise and write the result directly
+      out[(static_cast<long long>(req) * Hq + hk * group + g) * D + d] = __float2bfloat16(ll > 0.f ? oo / ll : 0.f);
+      continue;
+    }
+    __stcg(&part_o[base * D + d], oo);
+    if (d == 0) { __stcg(&part_ml[base * 2], (mm == -INFINITY) ? -INFINITY : mm * sl2); __stcg(&part_ml[base * 2 + 1], ll); }
   }
+  if (counters == nullptr || num_splits == 1) return;      // merged by paged_merge_kernel2 / nothing to merge
+  // the last split of this (request, kv head) to arrive merges all of them: no second kernel
+  __shared__ int s_last;
+  __threadfence();
+  __syncthreads();
+  if (threadIdx.x == 0) s_last = atomicAdd(&counters[req * Hkv + hk], 1) == num_splits - 1;
+  __syncthreads();
+  if (!s_last) return;
+  __threadfence();
+  for (int i = threadIdx.x; i < group * D; i += 128) {
+    const int g = i / D, d = i % D;
+    const long long rh = static_cast<long long>(req) * Hq + hk * group + g;
+    float mm = -INFINITY;
+    for (int sp = 0; sp < num_splits; ++sp) mm = fmaxf(mm, __ldcg(&part_ml[(rh * num_splits + sp) * 2]));
+    float ll = 0.f, oo = 0.f;
+    for (int sp = 0; sp < num_splits; ++sp) {
+      const float ms = __ldcg(&part_ml[(rh * num_splits + sp) * 2]);
+      const float a = (ms == -INFINITY) ? 0.f : exp2f(ms - mm);
+      ll += __ldcg(&part_ml[(rh * num_splits + sp) * 2 + 1]) * a;
+      oo += __ldcg(&part_o[(rh * num_splits + sp) * D + d]) * a;
+    }
+    out[rh * D + d] = __float2bfloat16(ll > 0.f ? oo / ll : 0.f);
+  }
+  if (threadIdx.x == 0) counters[req * Hkv + hk] = 0;
 }
 
 // partial maxima are stored pre-multiplied by scale·log2(e)
@@ -233,6 +262,29 @@ extern "C" int mb_paged_decode(const void* q, const void* kc, const void* vc, co
   const int group = Hq / Hkv;
   if (group > 8 || group * Hkv != Hq) return -2;
   dim3 grid(num_splits, Hkv, batch);
+  // arrival counters for the in-kernel merge: one per (request, kv head), zero between calls; allocated on first use
+  // outside stream capture (a call that arrives first during a capture keeps the separate merge kernel)
+  static int* counter_buf[64] = {};
+  static int counter_cap[64] = {};
+  int dev = 0;
+  cudaGetDevice(&dev);
+  int* counters = nullptr;
+  if (dev < 64) {
+    if (counter_cap[dev] < batch * Hkv) {
+      cudaStreamCaptureStatus st = cudaStreamCaptureStatusNone;
+      cudaStreamIsCapturing(s, &st);
+      if (st == cudaStreamCaptureStatusNone) {
+        const int cap = batch * Hkv > 16384 ? batch * Hkv : 16384;
+        int* fresh = nullptr;
+        if (cudaMalloc(&fresh, cap * sizeof(int)) == cudaSuccess && cudaMemset(fresh, 0, cap * sizeof(int)) == cudaSuccess) {
+          counter_buf[dev] = fresh;      // an older, smaller buffer may still be referenced by captured graphs: it is kept
+          counter_cap[dev] = cap;
+        }
+      }
+    }
+    if (counter_cap[dev] >= batch * Hkv) counters = counter_buf[dev];
+  }
+  bf16* O = reinterpret_cast<bf16*>(out);
   auto Q = reinterpret_cast<const bf16*>(q);
   auto KC = reinterpret_cast<const bf16*>(kc);
   auto VC = reinterpret_cast<const bf16*>(vc);
@@ -245,9 +297,9 @@ extern "C" int mb_paged_decode(const void* q, const void* kc, const void* vc, co
       once = true;
     }
     cudaError_t e = mb::launch_pdl(paged_decode_mma_kernel<128>, grid, dim3(128), smem_bytes<128>(), s, Q, KC, VC, block_table, seq_lens, part_o,
-                               part_ml, max_blocks, block_size, Hq, Hkv, group, scale, num_splits);
+                               part_ml, max_blocks, block_size, Hq, Hkv, group, scale, num_splits, O, counters);
     if (e != cudaSuccess) return static_cast<int>(e);
-    e = mb::launch_pdl(paged_merge_kernel2<128>, dim3(batch * Hq), dim3(128), 0, s, static_cast<const float*>(part_o),
+    if (counters == nullptr) e = mb::launch_pdl(paged_merge_kernel2<128>, dim3(batch * Hq), dim3(128), 0, s, static_cast<const float*>(part_o),
                    static_cast<const float*>(part_ml), reinterpret_cast<bf16*>(out), num_splits);
     if (e != cudaSuccess) return static_cast<int>(e);
   } else if (D == 64) {
@@ -259,9 +311,9 @@ extern "C" int mb_paged_decode(const void* q, const void* kc, const void* vc, co
       once = true;
     }
     cudaError_t e = mb::launch_pdl(paged_decode_mma_kernel<64>, grid, dim3(128), smem_bytes<64>(), s, Q, KC, VC, block_table, seq_lens, part_o,
-                               part_ml, max_blocks, block_size, Hq, Hkv, group, scale, num_splits);
+                               part_ml, max_blocks, block_size, Hq, Hkv, group, scale, num_splits, O, counters);
     if (e != cudaSuccess) return static_cast<int>(e);
-    e = mb::launch_pdl(paged_merge_kernel2<64>, dim3(batch * Hq), dim3(64), 0, s, static_cast<const float*>(part_o),
+    if (counters == nullptr) e = mb::launch_pdl(paged_merge_kernel2<64>, dim3(batch * Hq), dim3(64), 0, s, static_cast<const float*>(part_o),
                    static_cast<const float*>(part_ml), reinterpret_cast<bf16*>(out), num_splits);
     if (e != cudaSuccess) return static_cast<int>(e);
   } else {

@@ -50,7 +50,7 @@ def gemm_nt(a: torch.Tensor, b: torch.Tensor, out: torch.Tensor | None = None, *
         out = torch.empty(M, N, dtype=out_dtype or BF16, device=a.device)
     if M and N:
         plain = not accumulate and not force_bn
-        if plain and M <= GEMV_M and K % 32 == 0 and N <= GEMV_MAX_N:
+        if plain and M <= GEMV_M and _gemv_k_ok(M, K) and N <= GEMV_MAX_N:
             C.gemv(a, None, None, 0.0, b, bias, out, None, None, bool(b.is_leaf and b.requires_grad))
             return out
         # measured: the operand-swapped kernel wins where its tiles fill the GPU without split-K (wide outputs such as the
@@ -98,6 +98,11 @@ GEMV_M = min(16, int(os.environ.get("MILES_GEMV_M", "8")))
 GEMV_MAX_N = int(os.environ.get("MILES_GEMV_MAX_N", "32768"))
 
 
+def _gemv_k_ok(rows: int, K: int) -> bool:
+    """The kernel stages the activation rows in shared memory: 8 (or 16) rows of K bf16 next to a 32 KB weight ring."""
+    return K % 32 == 0 and (8 if rows <= 8 else 16) * (2 * K + 64) + 32768 <= 200 * 1024
+
+
 def add_rmsnorm_linear(x, residual, norm_w, eps, w, bias=None, want_normed: bool = False, out_fp32: bool = False):
     """Inference only, ≤ GEMV_M rows: y = rmsnorm(x + residual) · wᵀ in one kernel.
     Returns (y, x + residual or None, normalised activations or None)."""
@@ -116,7 +121,7 @@ def add_rmsnorm_linear(x, residual, norm_w, eps, w, bias=None, want_normed: bool
 def gemv_ok(x, w) -> bool:
     """True when `add_rmsnorm_linear` applies: bf16, no autograd, few rows, K a multiple of 32."""
     K = x.shape[-1]
-    return (GEMV_M > 0 and x.dtype == BF16 and w.dtype == BF16 and not torch.is_grad_enabled() and K % 32 == 0
+    return (GEMV_M > 0 and x.dtype == BF16 and w.dtype == BF16 and not torch.is_grad_enabled() and _gemv_k_ok(x.numel() // K, K)
             and 0 < x.numel() // K <= GEMV_M and w.is_contiguous())
 
 

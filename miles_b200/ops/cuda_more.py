@@ -264,7 +264,9 @@ def moe_ffn(x, w13, w2, topk_w, topk_idx, expert_offset: int = 0):
         return ref.moe_ffn(x, w13, w2, topk_w, topk_idx)
     T, k = topk_idx.shape
     if (0 < T <= MOE_GEMV_T and T * k <= 64 and not torch.is_grad_enabled() and x.shape[1] % 32 == 0
-            and w13.shape[1] % 64 == 0):
+            and w13.shape[1] % 64 == 0
+            # both kernels keep their activations in shared memory next to a 64 KB weight ring
+            and 65536 + max(8 * (2 * x.shape[1] + 64), T * k * (w13.shape[1] + 64)) <= 200 * 1024):
         # a handful of tokens: two matrix-vector kernels, no sort / gather / combine (gemv.cu)
         act = torch.empty(T * k, w13.shape[1] // 2, dtype=x.dtype, device=x.device)
         out = torch.empty_like(x)
