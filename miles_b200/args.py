@@ -97,6 +97,10 @@ def build_parser() -> argparse.ArgumentParser:
     g.add_argument("--cp-comm-type", choices=["p2p", "a2a", "allgather"], default="p2p")
     _bool_flag(g, "--allgather-cp")
     _bool_flag(g, "--indep-dp")
+    g.add_argument("--indep-dp-num-cells", type=int, default=1, help="independent training worlds (cells) averaging gradients")
+    g.add_argument("--indep-dp-cell-id", type=int, default=0)
+    g.add_argument("--indep-dp-store", default="127.0.0.1:29650", help="host:port of the cross-cell store (cell 0 serves it)")
+    g.add_argument("--indep-dp-timeout", type=float, default=30.0, help="seconds before a cross-cell collective gives up")
     g.add_argument("--fsdp-dp-replicate", type=int, default=1)
     _bool_flag(g, "--use-distributed-optimizer", default=True)
     _bool_flag(g, "--overlap-grad-reduce", default=True)

@@ -109,9 +109,10 @@ def create_rollout_components(args, ps: ParallelState, actor=None, tracker=None)
     ex = RolloutExecutor(args, data_source, client, ps=ps, rollout_dp_size=rollout_dp, rollout_dp_rank=rollout_dp_rank,
                          tracker=tracker)
     ex.is_leader = ps.tp_rank == 0
-    # distinct prompts per rollout-DP rank: advance the data source by rank-dependent seeds
+    # distinct prompts per rollout-DP rank (and per independent-DP cell): advance the data source by rank-dependent seeds
     if hasattr(data_source, "gen"):
-        data_source.gen.manual_seed(args.rollout_seed * 9973 + rollout_dp_rank)
+        cell = getattr(args, "indep_dp_cell_id", 0)
+        data_source.gen.manual_seed(args.rollout_seed * 9973 + rollout_dp_rank + 7919 * cell)
     return RolloutComponents(engines=engines, client=client, executor=ex, data_source=data_source)
 
 

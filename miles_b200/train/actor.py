@@ -117,6 +117,7 @@ class TrainActor:
         self.scheduler = LRScheduler(self.optimizer.lr, args.min_lr, args.lr_warmup_iters, args.lr_decay_iters,
                                      args.lr_decay_style)
         self.backuper = TensorBackuper(self.model)
+        self.indep_dp = self._make_indep_dp()
         # checkpoints
         from ..checkpoint import manager as ckpt
         loaded_iter = ckpt.load_into_actor(self, args)
@@ -132,6 +133,35 @@ class TrainActor:
             else:
                 self.backuper.backup("ref")
         return self.start_rollout_id
+
+    def _make_indep_dp(self):
+        """`--indep-dp`: this training world is one cell of several; gradients are averaged across the cells through a
+        group that survives the loss of a cell (ft/indep_dp.py).  Rank r of every cell forms one cross-cell group."""
+        args = self.args
+        n_cells = getattr(args, "indep_dp_num_cells", 1)
+        if not getattr(args, "indep_dp", False) or n_cells <= 1:
+            return None
+        from ..ft.indep_dp import IndepDP
+
+        host, port = args.indep_dp_store.rsplit(":", 1)
+        rank = dist.get_rank() if dist.is_initialized() else 0
+        cell = args.indep_dp_cell_id
+        idp = IndepDP(cell, host, int(port) + rank, backend="nccl" if self.device.type == "cuda" else "gloo",
+                      timeout_s=getattr(args, "indep_dp_timeout", 30.0), is_store_master=cell == 0, expected_cells=n_cells)
+        if cell == 0:
+            idp.members.publish(0, list(range(n_cells)))
+        idp.follow_membership()
+        return idp
+
+    def _exchange_across_cells(self) -> bool:
+        """Average the gradient buffers over the live cells; False when the cells agreed to discard this step."""
+        if self.indep_dp is None:
+            return True
+        buckets = [d.grad_buf for d in self.optimizer.domains]
+        finite = all(bool(torch.isfinite(b).all()) for b in buckets)
+        committed, cells = self.indep_dp.step(buckets, local_ok=finite)
+        self.last_cells = cells
+        return committed
 
     def _symmetric_allocator(self):
         """Flat param/grad buffers come from the fabric's symmetric heap so peers can address them."""
@@ -409,9 +439,14 @@ class TrainActor:
                 score(pb, idx, out, ent).backward()
         self._finalize_grads()
         lr = self.scheduler.get()
-        stats = self.optimizer.step(lr)
-        self.scheduler.step()
-        self.global_step += 1
+        if self._exchange_across_cells():
+            stats = self.optimizer.step(lr)
+            self.scheduler.step()
+            self.global_step += 1
+        else:
+            # the cells agreed to discard this step (some cell saw a non-finite gradient): nothing is applied anywhere
+            self.optimizer.zero_grad()
+            stats = {"grad_norm": float("nan")}
         # metrics: Σ over micro-batches and DP ranks of reduced values / global count
         keys = sorted(sums)
         if ps.dp_size > 1 and ps.dp_group is not None:

@@ -82,6 +82,7 @@ def train(args):
             metrics.update(rollout.executor.eval(rollout_id))
         tracker.log(metrics, rollout_id)
     tracker.finish()
+    tracker.actor = actor          # programmatic callers (tests, notebooks) reach the trained model through the tracker
     return tracker
 
 
