@@ -173,7 +173,11 @@ def load_named_into_model(model, named_tensors: Iterable[tuple[str, torch.Tensor
         if tuple(t.shape) != tuple(p.shape):
             t = shard_for_rank(n, t, cfg, ps)
         assert tuple(t.shape) == tuple(p.shape), f"{n}: got {tuple(t.shape)}, model has {tuple(p.shape)}"
-        if t.data_ptr() != p.data.data_ptr():
+        if type(p.data) is not torch.Tensor:           # an FSDP-sharded parameter takes its slice of the full tensor
+            from ..train.fsdp import copy_into
+
+            copy_into(p, t)
+        elif t.data_ptr() != p.data.data_ptr():
             p.data.copy_(t)
 
 

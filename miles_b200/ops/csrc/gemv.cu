@@ -164,6 +164,20 @@ __device__ __forceinline__ void stage_rows(uint8_t* xs, int rows, int valid, int
   }
 }
 
+// Plain copy of rows [0, valid) of a [*, K] bf16 matrix into shared memory with cp.async (every piece in flight at once, no
+// registers); rows [valid, rows) are zeroed.  The caller commits the group and waits for it before the CTA barrier.
+__device__ __forceinline__ void stage_rows_async(uint8_t* xs, int rows, int valid, int K, const bf16* __restrict__ x) {
+  const int nv = K / 8, stride = staged_stride(K);
+  for (int i = threadIdx.x; i < valid * nv; i += kThreads) {
+    const int r = i / nv, v = i - r * nv;
+    cp16(smem_addr(xs + r * stride + v * 16), x + static_cast<long long>(r) * K + v * 8);
+  }
+  for (int i = threadIdx.x; i < (rows - valid) * nv; i += kThreads) {
+    const int r = valid + i / nv, v = i % nv;
+    *reinterpret_cast<uint4*>(xs + r * stride + v * 16) = make_uint4(0, 0, 0, 0);
+  }
+}
+
 struct GemvParams {
   const bf16* x;          // [M, K]
   const bf16* residual;   // [M, K] or null (NORM only)
@@ -209,7 +223,13 @@ __global__ void __launch_bounds__(kThreads) gemv_kernel(GemvParams p) {
 #pragma unroll
   for (int i = 0; i < S; ++i) issue(i);
   if (p.static_w) pdl_wait();          // static weights: their first loads are already in flight
-  stage_rows<NORM>(xs, NT * 8, p.M, p.K, p.x, p.residual, p.norm_w, p.eps, p.res_out, rstd_s);
+  if (NORM) {
+    stage_rows<true>(xs, NT * 8, p.M, p.K, p.x, p.residual, p.norm_w, p.eps, p.res_out, rstd_s);
+  } else {
+    stage_rows_async(xs, NT * 8, p.M, p.K, p.x);
+    cp_commit();
+    cp_wait<0>();
+  }
   __syncthreads();
   const int stride = staged_stride(p.K);
   float c[NT][4] = {};
@@ -328,7 +348,9 @@ __global__ void __launch_bounds__(kThreads) moe_gemv_up_kernel(const bf16* __res
     }
     if (lane == 0) n_slots_s = cnt;
   }
-  stage_rows<false>(xs, 8, T, H, x, nullptr, nullptr, 0.f, nullptr, nullptr);
+  stage_rows_async(xs, 8, T, H, x);
+  cp_commit();
+  cp_wait<0>();
   __syncthreads();
   const int nfb = F / 8;
   const int n_items = n_slots_s * nfb;
@@ -413,6 +435,10 @@ __global__ void __launch_bounds__(kThreads) moe_gemv_down_kernel(const bf16* __r
   const int h0 = blockIdx.x * 16;
   const int chunks = F / 32;
   const int n_pairs = T * k;
+  // all pair rows of the activations → shared memory, in flight while warp 0 builds the expert table (rows of other
+  // ranks' experts are copied too and never read)
+  stage_rows_async(as, n_pairs, n_pairs, F, act);
+  cp_commit();
   if (warp == 0) {
     // the distinct experts of the step with, per token, the pair routed to them and its gate weight
     const PairIdx pi = load_pairs(topk_idx, n_pairs, E, offset);
@@ -432,8 +458,6 @@ __global__ void __launch_bounds__(kThreads) moe_gemv_down_kernel(const bf16* __r
     }
     if (lane == 0) n_slots_s = cnt;
   }
-  // all pair rows of the activations → shared memory (rows of other ranks' experts are never read)
-  stage_rows<false>(as, n_pairs, n_pairs, F, act, nullptr, nullptr, 0.f, nullptr, nullptr);
   __syncthreads();
   const int cnt = n_slots_s;
   const int cpw = chunks > warp ? (chunks - warp + kWarps - 1) / kWarps : 0;      // chunks of an expert taken by this warp
@@ -449,6 +473,8 @@ __global__ void __launch_bounds__(kThreads) moe_gemv_down_kernel(const bf16* __r
   };
 #pragma unroll
   for (int q = 0; q < S; ++q) issue(q);
+  cp_wait<S>();          // the activation rows (the oldest group) have landed; the weight ring keeps filling
+  __syncthreads();
   const int stride = staged_stride(F);
   float c[4] = {};
   int q = 0;

@@ -10,6 +10,8 @@
 #include <cuda_runtime.h>
 #include <stdint.h>
 
+#include <cstdlib>
+
 #include "launch.h"
 #include "pdl.cuh"
 
@@ -262,14 +264,17 @@ extern "C" int mb_paged_decode(const void* q, const void* kc, const void* vc, co
   const int group = Hq / Hkv;
   if (group > 8 || group * Hkv != Hq) return -2;
   dim3 grid(num_splits, Hkv, batch);
-  // arrival counters for the in-kernel merge: one per (request, kv head), zero between calls; allocated on first use
-  // outside stream capture (a call that arrives first during a capture keeps the separate merge kernel)
+  // Optional in-kernel merge (MILES_DECODE_FUSED_MERGE=1): the last split of a (request, kv head) to arrive merges them,
+  // which saves the merge launch but leaves the whole GQA group to one CTA; measured slower than the separate merge
+  // kernel at the batch sizes of the rollout (21 µs against 11 + 4 µs at batch 8), so it is off by default.
+  // Arrival counters: one per (request, kv head), zero between calls; allocated on first use outside stream capture.
+  static const bool fused_merge = [] { const char* e = getenv("MILES_DECODE_FUSED_MERGE"); return e != nullptr && e[0] == '1'; }();
   static int* counter_buf[64] = {};
   static int counter_cap[64] = {};
   int dev = 0;
   cudaGetDevice(&dev);
   int* counters = nullptr;
-  if (dev < 64) {
+  if (fused_merge && dev < 64) {
     if (counter_cap[dev] < batch * Hkv) {
       cudaStreamCaptureStatus st = cudaStreamCaptureStatusNone;
       cudaStreamIsCapturing(s, &st);

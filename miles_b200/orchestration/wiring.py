@@ -83,10 +83,13 @@ def create_rollout_components(args, ps: ParallelState, actor=None, tracker=None)
     else:
         ek = dict(getattr(args, "engine_kwargs", {}) or {})
         device = actor.device if actor is not None else ("cuda" if torch.cuda.is_available() else "cpu")
-        dtype = next(actor.model.parameters()).dtype if actor is not None else torch.bfloat16
+        dtype = (getattr(actor, "compute_dtype", None) or next(actor.model.parameters()).dtype) if actor is not None else torch.bfloat16
         share = actor is not None and getattr(args, "colocate", False) and not ek.get("own_weights", False)
         eos = ek.get("eos_token_ids") or ([tok.eos_token_id] if tok is not None and tok.eos_token_id is not None else [])
         engine_ps = ps
+        if getattr(actor, "fsdp", False):
+            # FSDP keeps parameters sharded between uses: the engine holds a copy of its own, fed by the named tensor stream
+            share = False
         if ps.pp_size > 1:
             # a pipeline stage holds a slice of the layers: the in-process engine then keeps a full copy of its own
             # (every rank serves requests data-parallel) and receives weights through the HF-named tensor stream

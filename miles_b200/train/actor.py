@@ -42,20 +42,25 @@ class TensorBackuper:
 
     def backup(self, tag: str):
         store = self.tags.setdefault(tag, {})
+        from .fsdp import local_data
+
         for n, p in self.model.named_parameters():
+            src = local_data(p)                 # the shard of an FSDP parameter, the tensor itself otherwise
             if n not in store:
-                t = torch.empty(p.shape, dtype=p.dtype, device="cpu")
+                t = torch.empty(src.shape, dtype=src.dtype, device="cpu")
                 if torch.cuda.is_available():
                     t = t.pin_memory()
                 store[n] = t
-            store[n].copy_(p.data, non_blocking=True)
+            store[n].copy_(src, non_blocking=True)
         if torch.cuda.is_available():
             torch.cuda.current_stream().synchronize()
 
     def restore(self, tag: str):
+        from .fsdp import local_data
+
         store = self.tags[tag]
         for n, p in self.model.named_parameters():
-            p.data.copy_(store[n], non_blocking=True)
+            local_data(p).copy_(store[n], non_blocking=True)
         if torch.cuda.is_available():
             torch.cuda.current_stream().synchronize()
 
@@ -93,6 +98,10 @@ class TrainActor:
             from ..ops import cuda as _cuda_ops
 
             _cuda_ops.MXFP8_LINEAR = True       # projections run their forward on the block-scaled MXFP8 tensor-core path
+        self.fsdp = getattr(args, "train_backend", "native") == "fsdp" and dist.is_initialized() and dist.get_world_size() > 1
+        compute_dtype = self.compute_dtype = dtype
+        if self.fsdp:
+            dtype = torch.float32               # FSDP keeps fp32 shards (the master weights) and computes in `compute_dtype`
         provider = getattr(args, "custom_model_provider_path", None)
         if provider:
             from ..utils.misc import load_function
@@ -106,11 +115,22 @@ class TrainActor:
             from .critic import attach_value_head
             attach_value_head(self.model, self.cfg, dtype, self.device)
         mark_expert_params(self.model)
+        lr0 = args.lr if self.role == "actor" else args.critic_lr
+        if self.fsdp:
+            # parameters sharded per decoder layer (PyTorch FSDP2), AdamW on the shards; see train/fsdp.py
+            from .fsdp import FsdpOptimizer, shard_model
+
+            shard_model(self.model, self.ps, self.device, dp_replicate=getattr(args, "fsdp_dp_replicate", 1),
+                        compute_dtype=compute_dtype)
         named = [(n, p) for n, p in self.model.named_parameters() if p.requires_grad]   # LoRA / critic freeze the rest
-        self.optimizer = DistributedAdam(
-            named, lr=args.lr if self.role == "actor" else args.critic_lr, betas=(args.adam_beta1, args.adam_beta2),
-            eps=args.adam_eps, weight_decay=args.weight_decay, clip_grad=args.clip_grad, ps=self.ps,
-            allocator=self._symmetric_allocator())
+        if self.fsdp:
+            self.optimizer = FsdpOptimizer(named, lr=lr0, betas=(args.adam_beta1, args.adam_beta2), eps=args.adam_eps,
+                                           weight_decay=args.weight_decay, clip_grad=args.clip_grad)
+        else:
+            self.optimizer = DistributedAdam(
+                named, lr=lr0, betas=(args.adam_beta1, args.adam_beta2),
+                eps=args.adam_eps, weight_decay=args.weight_decay, clip_grad=args.clip_grad, ps=self.ps,
+                allocator=self._symmetric_allocator())
         self.tp_replicated = {n for n, p in named if _tp_replicated(n)}
         if self.ps.tp_size > 1:
             self.optimizer.mark_tp_replicated(self.tp_replicated, named)
@@ -536,7 +556,12 @@ class TrainActor:
         self.asleep = False
 
     def named_weights(self):
-        """This rank's shard, named by our layout (for checkpointing and weight sync)."""
+        """This rank's shard, named by our layout (for checkpointing and weight sync).  With the FSDP backend every
+        parameter is gathered in full, one at a time (collective: all ranks iterate together)."""
+        if getattr(self, "fsdp", False):
+            from .fsdp import full_data
+
+            return ((n, full_data(p)) for n, p in self.model.named_parameters_global())
         return [(n, p.data) for n, p in self.model.named_parameters_global()]
 
 

@@ -120,6 +120,7 @@ def _dist_hist(tmp_path, extra, world=2):
     "--tensor-model-parallel-size 2 --sequence-parallel",                   # tp2 + sp
     "--model-name tiny-moe --expert-model-parallel-size 2",                 # dp2 × ep2
     "--context-parallel-size 2 --cp-comm-type a2a",                         # cp2 (Ulysses), dp1
+    "--train-backend fsdp",                                                 # dp2, parameters sharded per layer (FSDP2)
     "--context-parallel-size 2",                                            # cp2, ring attention over zigzag pieces
     "--context-parallel-size 2 --allgather-cp",                             # cp2, K/V all-gathered
     "--pipeline-model-parallel-size 2 --micro-batch-size 8",                # pp2, 4 micro-batches per step, 1F1B order
@@ -133,6 +134,16 @@ def test_grpo_two_ranks(tmp_path, extra):
     assert max(r["train/train_rollout_logprob_abs_diff"] for r in rows) < 1e-5
     assert abs(rows[0]["train/ppo_kl"]) < 1e-6
     assert all(r["train/grad_norm"] > 0 for r in rows)
+
+
+def test_fsdp_checkpoint_save_and_resume(tmp_path):
+    d = str(tmp_path / "ckpt")
+    (tmp_path / "a").mkdir()
+    (tmp_path / "b").mkdir()
+    rows1 = _dist_hist(tmp_path / "a", f"--train-backend fsdp --save {d} --save-interval 1 --num-rollout 2")
+    rows2 = _dist_hist(tmp_path / "b", f"--train-backend fsdp --save {d} --load {d} --save-interval 1 --num-rollout 3")
+    assert len(rows1) == 2 and [r["rollout/step"] for r in rows2] == [2]            # resumed after two saved rollouts
+    assert rows2[0]["train/train_rollout_logprob_abs_diff"] < 1e-5                  # the reloaded shards feed the engine
 
 
 # ---- asynchronous loops --------------------------------------------------------------------------------------------
