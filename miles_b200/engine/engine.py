@@ -621,6 +621,10 @@ class Engine:
         self.running = [r for r in reqs if not r.finished]
 
     def _append_token(self, r: Request, t: int, l: float):
+        if not (0 <= t < self.cfg.vocab_size) or l != l:
+            # a non-finite hidden state; stop here rather than feed the id to the next step's embedding lookup
+            raise RuntimeError(f"engine step {self._step_count}: request {r.rid} sampled id {t} with log-prob {l} "
+                               f"(context {len(r.all_ids)} tokens, {len(self.running)} running)")
         r.output_ids.append(t)
         r.output_logprobs.append(l)
         if r.weight_versions and r.weight_versions[-1][0] == self.weight_version:

@@ -63,15 +63,6 @@ gemm_small_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_const
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_base_ptr + 1);
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
 
-  const int n_tiles = (p.N + BMW - 1) / BMW;
-  int t_tiles = (p.tokens + BT - 1) / BT;
-  if (p.grouped && p.used_rows != nullptr) t_tiles = min(t_tiles, (__ldg(p.used_rows) + BT - 1) / BT);
-  const int out_tiles = n_tiles * t_tiles;
-  const int split_k = p.split_k > 1 ? p.split_k : 1;
-  const int total = out_tiles * split_k;
-  const int total_kb = (p.K + BK - 1) / BK;
-  const int kb_per = (total_kb + split_k - 1) / split_k;
-
   if (threadIdx.x == 0) {
     for (int s = 0; s < kStages; ++s) { mbar_init(&full_bar[s], 1); mbar_init(&empty_bar[s], 1); }
     for (int b = 0; b < 2; ++b) { mbar_init(&tmem_full[b], 1); mbar_init(&tmem_empty[b], 4); }
@@ -90,6 +81,16 @@ gemm_small_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_const
   const uint32_t tmem_base = *tmem_base_ptr;
   pdl_trigger();
   pdl_wait();
+
+  const int n_tiles = (p.N + BMW - 1) / BMW;
+  // `used_rows` is written by a preceding kernel of the stream: read it only after the dependency wait
+  int t_tiles = (p.tokens + BT - 1) / BT;
+  if (p.grouped && p.used_rows != nullptr) t_tiles = min(t_tiles, (*p.used_rows + BT - 1) / BT);
+  const int out_tiles = n_tiles * t_tiles;
+  const int split_k = p.split_k > 1 ? p.split_k : 1;
+  const int total = out_tiles * split_k;
+  const int total_kb = (p.K + BK - 1) / BK;
+  const int kb_per = (total_kb + split_k - 1) / split_k;
 
   // tile id → (feature tile, token tile, K slice); consecutive CTAs take different feature tiles of the same tokens
   auto decode = [&](int t, int& n_blk, int& t_blk, int& slice) {

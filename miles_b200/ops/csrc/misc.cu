@@ -108,7 +108,7 @@ __global__ void __launch_bounds__(256) sample_logprob_split_kernel(const float* 
   const int lo = part * per, hi = min(V, lo + per);
   MS ms{-INFINITY, 0.f};
   float best = -INFINITY;
-  int best_i = 0x7fffffff;
+  int best_i = 0x7fffffff;   // "no candidate": loses every tie; clamped into the vocabulary before it is used as an index
   for (int i = lo + threadIdx.x; i < hi; i += 256) {
     const float z = x[i] * it;
     ms = ms_merge(ms, MS{z, 1.f});
@@ -150,6 +150,8 @@ __global__ void __launch_bounds__(256) sample_logprob_split_kernel(const float* 
   best_i = __float_as_int(v.w);
   warp_merge();
   if (lane == 0) {
+    // a row whose logits are all NaN has no candidate: report token 0 with a NaN log-prob instead of indexing out of range
+    if (best_i < 0 || best_i >= V) best_i = 0;
     tokens[row] = best_i;
     logprobs[row] = x[best_i] * it - (ms.m + __logf(ms.s));
     counters[row] = 0;
