@@ -228,6 +228,7 @@ def main():
         counters["h2d"] += engine.stats.get("h2d_bytes", 0) + sum(len(t) for t in shard["tokens"]) * 4 * 3
         counters["d2h"] += engine.stats.get("d2h_bytes", 0) + 4 * len(metrics)
         engine.stats["h2d_bytes"] = engine.stats["d2h_bytes"] = 0
+        counters["engine"] = {k: (round(v, 3) if isinstance(v, float) else v) for k, v in engine.stats.items()}
         return metrics
 
     for i in range(a.warmup):
@@ -238,6 +239,8 @@ def main():
                   file=sys.stderr, flush=True)
     for k in counters:
         counters[k] = 0
+    for k in list(engine.stats):
+        engine.stats[k] = type(engine.stats[k])()
     launches0 = K.launch_count()
     sampler = ClockSampler(local)
     if world > 1:
@@ -292,6 +295,7 @@ def main():
             "breakdown_s_per_step": {"rollout": counters["rollout_s"] / a.steps, "train": counters["train_s"] / a.steps,
                                      "weight_sync": counters["sync_s"] / a.steps},
             "tokens_per_step": total_tokens // a.steps, "kernel_error_flag": err,
+            "engine_stats_rank0": counters.get("engine"),
         }
         print(json.dumps(out))
     if world > 1:

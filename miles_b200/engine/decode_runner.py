@@ -11,6 +11,7 @@ graph launch instead of ~25 launches per layer.
 """
 from __future__ import annotations
 
+import time
 import zlib
 
 import numpy as np
@@ -118,7 +119,21 @@ class DecodeRunner:
                 return min(b, self.max_rows)
         return self.max_rows
 
+    def bucket_needed(self) -> int:
+        return self._bucket(max(self.high, 1))
+
     def _forward(self, B: int, record: bool):
+        e = self.e
+        uniform = e.lockstep_group is not None      # lockstep ranks run every decode step with the same row count
+        if uniform:
+            e.ps.moe_uniform_tokens = True
+        try:
+            self._forward_impl(B, record)
+        finally:
+            if uniform:
+                e.ps.moe_uniform_tokens = False
+
+    def _forward_impl(self, B: int, record: bool):
         e = self.e
         R, MB = self.max_rows, self.max_blocks
         tokens = self.d_i32[0:B]
@@ -137,7 +152,7 @@ class DecodeRunner:
         if record and meta.record_topk:
             self.o_routed[:B].copy_(torch.stack(meta.record_topk, dim=1))
 
-    def step(self, reqs: list, step_no: int):
+    def step(self, reqs: list, step_no: int, min_bucket: int = 0):
         """Run one decode step for the attached requests; returns (tokens, logprobs, routed | None) as numpy views
         indexed by row."""
         e = self.e
@@ -156,7 +171,7 @@ class DecodeRunner:
             self.len_np[row] = n
             self.slot_np[row] = r.blocks[pos // bs] * bs + pos % bs
             self.seed_np[row] = (r.seed * 1000003 + n) & 0x7FFFFFFFFFFFFFFF
-        B = self._bucket(max(self.high, 1))
+        B = min(max(self._bucket(max(self.high, 1)), int(min_bucket)), self.max_rows)
         record = self.n_moe > 0 and any(r.return_routed_experts for r in reqs)
         self.d_i32.copy_(self.h_i32, non_blocking=True)
         self.d_i64.copy_(self.h_i64, non_blocking=True)
@@ -180,12 +195,16 @@ class DecodeRunner:
             self.h_routed[:B].copy_(self.o_routed[:B], non_blocking=True)
             nbytes += self.h_routed[:B].numel() * 4
         e.stats["d2h_bytes"] = e.stats.get("d2h_bytes", 0) + nbytes
+        t0 = time.perf_counter()
         torch.cuda.current_stream().synchronize()
+        e.stats["decode_wait_s"] = e.stats.get("decode_wait_s", 0.0) + time.perf_counter() - t0   # host idle, GPU busy
         return self.h_tok.numpy(), self.h_lp.numpy(), (self.h_routed.numpy() if record else None)
 
+    @torch.no_grad()
     def warmup(self):
         """One eager decode step on padding rows only (no KV writes): initialises per-kernel attributes before any
-        graph capture.  Expert-parallel ranks call this together (every MoE layer is a collective)."""
+        graph capture.  Expert-parallel ranks call this together (every MoE layer is a collective).  Runs without autograd:
+        a recorded forward would keep every layer's worst-case-sized dispatch buffers alive until the step ends."""
         if getattr(self, "_warm", False):
             return
         self.d_i32.copy_(self.h_i32)

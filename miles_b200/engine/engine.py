@@ -144,6 +144,7 @@ class Engine:
         self.local_done = True
         self.global_done = True
         self.runner = None
+        self._agreed_bucket = 0
         # models whose mixers keep no paged KV (latent / linear attention of the other families) are served by scoring the
         # whole sequence again every step: correct for any block, quadratic in length — the functional path for those families
         self.stateless = not getattr(self.model, "supports_kv_cache", True)
@@ -395,13 +396,20 @@ class Engine:
                 return self._step_lockstep()
             if self.paused or not self.kv.allocated:
                 return False
+            t0 = time.perf_counter()
             batch = self._schedule_prefill()
             if batch:
                 self._run_prefill(batch)
+                self.stats["prefill_s"] = self.stats.get("prefill_s", 0.0) + time.perf_counter() - t0
             elif self.running:
                 if not self._ensure_decode_blocks():
                     return True
+                n = len(self.running)
                 self._run_decode()
+                # wall time of decode steps by batch-size class (host bookkeeping included): where a rollout's time goes
+                key = "decode_s_le8" if n <= 8 else "decode_s_le32" if n <= 32 else "decode_s_gt32"
+                self.stats[key] = self.stats.get(key, 0.0) + time.perf_counter() - t0
+                self.stats[key.replace("_s_", "_n_")] = self.stats.get(key.replace("_s_", "_n_"), 0) + 1
             else:
                 return False
             self.stats["steps"] += 1
@@ -418,15 +426,24 @@ class Engine:
         want_decode = bool(self.running) and not self.paused and not batch
         if want_decode and not self._ensure_decode_blocks():
             want_decode = False
-        flags = torch.tensor([int(bool(batch)), int(want_decode), int(not self.local_done)], dtype=torch.int32,
+        # the decode batch bucket is agreed too (the largest any rank needs): with the same row count on every rank the
+        # expert-parallel layers can bound what each rank receives by ep · rows · k instead of the buffer capacity
+        bucket = self.runner.bucket_needed() if (self.runner is not None and want_decode) else 0
+        flags = torch.tensor([int(bool(batch)), int(want_decode), int(not self.local_done), bucket], dtype=torch.int32,
                              device=self.device if self.device.type == "cuda" else "cpu")
         dist.all_reduce(flags, op=dist.ReduceOp.MAX, group=self.lockstep_group)
-        any_prefill, any_decode, any_active = (int(v) for v in flags.tolist())
+        any_prefill, any_decode, any_active, self._agreed_bucket = (int(v) for v in flags.tolist())
         self.global_done = not any_active and not any_prefill and not any_decode
+        t0 = time.perf_counter()
         if any_prefill:
             self._run_prefill(batch)
+            self.stats["prefill_s"] = self.stats.get("prefill_s", 0.0) + time.perf_counter() - t0
         elif any_decode:
+            n = len(self.running)
             self._run_decode()
+            key = "decode_s_le8" if n <= 8 else "decode_s_le32" if n <= 32 else "decode_s_gt32"
+            self.stats[key] = self.stats.get(key, 0.0) + time.perf_counter() - t0
+            self.stats[key.replace("_s_", "_n_")] = self.stats.get(key.replace("_s_", "_n_"), 0) + 1
         else:
             return False
         self.stats["steps"] += 1
@@ -611,7 +628,8 @@ class Engine:
     def _run_decode_static(self):
         """CUDA path: static buffers + (optionally) a CUDA graph per batch bucket; see `decode_runner`."""
         reqs = self.running
-        tok, lp, routed = self.runner.step(reqs, self._step_count)
+        tok, lp, routed = self.runner.step(reqs, self._step_count,
+                                           min_bucket=self._agreed_bucket if self.lockstep_group is not None else 0)
         self.stats["decode_tokens"] += len(reqs)
         for r in reqs:
             row = r.row

@@ -36,6 +36,8 @@ class _Buffers:
         self.ret_ptrs = fab.peer_ptrs(self.ret, ranks)
         self.expert_ids = torch.empty(self.cap, dtype=torch.int32, device=fab.device)
         self.n_recv = torch.zeros(1, dtype=torch.int32, device=fab.device)
+        self.pair_ids = torch.arange(self.max_pairs, dtype=torch.int32, device=fab.device)
+        self.minus_one = torch.full((), -1, dtype=torch.int32, device=fab.device)
 
 
 def _buffers(fab, H, k, ps, T) -> _Buffers:
@@ -51,7 +53,7 @@ def _buffers(fab, H, k, ps, T) -> _Buffers:
 
 class _FusedMoE(torch.autograd.Function):
     @staticmethod
-    def forward(ctx, x, w13, w2, topk_w, topk_idx, fab, ps, num_experts):
+    def forward(ctx, x, w13, w2, topk_w, topk_idx, fab, ps, num_experts, grad_mode=True):
         C = fab.C
         T, H = x.shape
         k = topk_idx.shape[1]
@@ -67,13 +69,22 @@ class _FusedMoE(torch.autograd.Function):
         if n_pairs:
             C.moe_dispatch(x, idx32, k, e_local, me, b.recv_x_ptrs, b.recv_meta_ptrs, b.counter_ptrs, ep, b.cap, sent_row, fab.err)
         fab.barrier(ranks, CH_EP)
-        C.recv_expert_ids(b.recv_meta, b.counter, b.cap, b.expert_ids, b.n_recv)
+        # `needs_input_grad` follows the inputs' requires_grad flags even under no_grad (the engine serves the trainer's
+        # parameters): without the caller's grad mode inference would take the 128-row training tiles and clone what
+        # backward needs.  (Inside `forward` grad mode is always off, so the wrapper samples it.)
+        need_bwd = grad_mode and any(ctx.needs_input_grad[:4])
+        # Rows that can arrive here: the buffer capacity in general; ep · T · k when every rank of the group runs this call
+        # with the same T (the engine's decode steps agree on one batch bucket).  Everything sized by this bound — the
+        # expert-id scan, the tile table, the padded row space — then shrinks from ~300k rows to a few hundred.
+        cap = b.cap
+        if getattr(ps, "moe_uniform_tokens", False) and not need_bwd:
+            cap = min(cap, (ep * max(n_pairs, 1) + 127) // 128 * 128)
+        C.recv_expert_ids(b.recv_meta, b.counter, cap, b.expert_ids[:cap], b.n_recv)
         b.counter.zero_()
-        need_bwd = any(ctx.needs_input_grad[:4])
         # decode-sized calls (about n_pairs rows arrive when the routing is balanced): pad segments to 16/32/64 rows
         bt = 128 if need_bwd else small_moe_bt(n_pairs, e_local, w13, w2)
-        max_rows = moe_max_rows_pad(b.cap, e_local, bt)
-        seg, tile, row_src, _ = C.moe_align(b.expert_ids, e_local, 0, max_rows, b.n_recv, bt)
+        max_rows = moe_max_rows_pad(cap, e_local, bt)
+        seg, tile, row_src, _ = C.moe_align(b.expert_ids[:cap], e_local, 0, max_rows, b.n_recv, bt)
         x_perm = torch.empty(max_rows, H, dtype=x.dtype, device=x.device)
         C.moe_gather(b.recv_x.view(b.cap, H), x_perm, row_src, seg, 1)
         h1, y_perm = experts_forward(x_perm, w13, w2, seg, tile, bt)
@@ -81,8 +92,7 @@ class _FusedMoE(torch.autograd.Function):
         C.moe_return(y_perm, row_src, b.recv_meta, seg, b.ret_ptrs, ep)
         fab.barrier(ranks, CH_EP2)
         out = torch.empty(T, H, dtype=x.dtype, device=x.device)
-        ar = torch.arange(max(n_pairs, 1), dtype=torch.int32, device=x.device)
-        dst_row = torch.where(sent_row >= 0, ar, torch.full_like(ar, -1))
+        dst_row = torch.where(sent_row >= 0, b.pair_ids[:max(n_pairs, 1)], b.minus_one)
         if T:
             C.moe_combine(b.ret.view(b.max_pairs, H), wf, dst_row, out, k)
         if need_bwd:
@@ -118,8 +128,8 @@ class _FusedMoE(torch.autograd.Function):
         dx = torch.empty(T, H, dtype=dout.dtype, device=dev)
         if T:
             C.moe_combine(b.ret.view(b.max_pairs, H), None, dst_row, dx, k)
-        return dx, dw13, dw2, dw_flat[:n_pairs].view(T, k), None, None, None, None
+        return dx, dw13, dw2, dw_flat[:n_pairs].view(T, k), None, None, None, None, None
 
 
 def fused_moe(fab, x, w13, w2, topk_w, topk_idx, num_experts, ps):
-    return _FusedMoE.apply(x, w13, w2, topk_w, topk_idx, fab, ps, num_experts)
+    return _FusedMoE.apply(x, w13, w2, topk_w, topk_idx, fab, ps, num_experts, torch.is_grad_enabled())

@@ -139,6 +139,24 @@ def _case_fused_moe(rank, world):
             assert _rel(got[4], twf.grad) < 3e-2, ("dw_topk", T)
         assert _rel(got[2], gw13[rank * e_local:(rank + 1) * e_local]) < 3e-2, ("dw13", T)
         assert _rel(got[3], gw2[rank * e_local:(rank + 1) * e_local]) < 3e-2, ("dw2", T)
+    # inference with the same row count on every rank (the engine's agreed decode bucket): the receive side is sized by
+    # ep · T · k instead of the buffer capacity; several calls in a row reuse the buffers as consecutive layers do
+    ps.moe_uniform_tokens = True
+    try:
+        with torch.no_grad():
+            for T in (1, 8, 24, 64):
+                for rep in range(3):
+                    gr = torch.Generator(device="cuda").manual_seed(1000 * T + 10 * rep + rank)
+                    x = (0.5 * torch.randn(T, H, device="cuda", generator=gr)).to(torch.bfloat16)
+                    tw, ti, _ = ref.router_topk(torch.randn(T, E, device="cuda", generator=gr), K, True)
+                    w13 = w13_all[rank * e_local:(rank + 1) * e_local].contiguous()
+                    w2 = w2_all[rank * e_local:(rank + 1) * e_local].contiguous()
+                    y = ps.moe_ffn(x, w13, w2, tw, ti, E)
+                    ps.fabric.check()
+                    yf = ref.moe_ffn(x.float(), w13_all.float(), w2_all.float(), tw.float(), ti)
+                    assert _rel(y, yf) < 2e-2, ("uniform", T, rep, _rel(y, yf))
+    finally:
+        ps.moe_uniform_tokens = False
 
 
 def _case_fused_optimizer(rank, world):
