@@ -119,10 +119,11 @@ void moe_return(const at::Tensor& y_perm, const at::Tensor& row_src, const at::T
         "mb_moe_return");
 }
 
-void recv_expert_ids(const at::Tensor& meta, const at::Tensor& counter, int64_t capacity, at::Tensor& expert_ids, at::Tensor& n_out) {
+void recv_expert_ids(const at::Tensor& meta, at::Tensor& counter, int64_t capacity, at::Tensor& expert_ids, at::Tensor& n_out,
+                     bool clear_counter) {
   c10::cuda::CUDAGuard g(meta.device());
   check(mb_recv_expert_ids(meta.data_ptr(), counter.data_ptr<int>(), capacity, expert_ids.data_ptr<int>(), n_out.data_ptr<int>(),
-                           cur_stream()),
+                           clear_counter ? 1 : 0, cur_stream()),
         "mb_recv_expert_ids");
 }
 
@@ -191,6 +192,7 @@ void register_fabric(pybind11::module& m) {
   m.def("moe_dispatch", &moe_dispatch);
   m.def("moe_scatter_known", &moe_scatter_known);
   m.def("moe_return", &moe_return);
-  m.def("recv_expert_ids", &recv_expert_ids);
+  m.def("recv_expert_ids", &recv_expert_ids, pybind11::arg("meta"), pybind11::arg("counter"), pybind11::arg("capacity"),
+        pybind11::arg("expert_ids"), pybind11::arg("n_out"), pybind11::arg("clear_counter") = false);
   m.def("stats_merge", &stats_merge);
 }

@@ -59,10 +59,11 @@ void moe_gather(const at::Tensor& x, at::Tensor& x_perm, const at::Tensor& row_s
         "mb_moe_gather");
 }
 
-void moe_combine(const at::Tensor& y_perm, const c10::optional<at::Tensor>& w, const at::Tensor& dst_row, at::Tensor& out, int64_t k) {
+void moe_combine(const at::Tensor& y_perm, const c10::optional<at::Tensor>& w, const at::Tensor& dst_row, at::Tensor& out, int64_t k,
+                 bool identity_rows) {
   c10::cuda::CUDAGuard g(out.device());
   check(mb_moe_combine(y_perm.data_ptr(), w.has_value() && w->defined() ? w->data_ptr<float>() : nullptr, dst_row.data_ptr<int>(),
-                       out.data_ptr(), out.size(0), k, out.size(-1), cur_stream()),
+                       out.data_ptr(), out.size(0), k, out.size(-1), identity_rows ? 1 : 0, cur_stream()),
         "mb_moe_combine");
 }
 
@@ -82,6 +83,7 @@ void register_moe(pybind11::module& m) {
   m.def("moe_align", &moe_align, py::arg("idx"), py::arg("E"), py::arg("expert_offset"), py::arg("max_rows"), py::arg("n_dev"),
         py::arg("pad") = 128);
   m.def("moe_gather", &moe_gather);
-  m.def("moe_combine", &moe_combine);
+  m.def("moe_combine", &moe_combine, pybind11::arg("y_perm"), pybind11::arg("w"), pybind11::arg("dst_row"), pybind11::arg("out"),
+        pybind11::arg("k"), pybind11::arg("identity_rows") = false);
   m.def("moe_combine_bwd", &moe_combine_bwd);
 }

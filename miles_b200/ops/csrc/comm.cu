@@ -241,10 +241,18 @@ __global__ void __launch_bounds__(256) moe_return_kernel(const bf16* __restrict_
 }
 
 // Local expert id per received row (for the counting sort), from the metadata; n is read from the device counter.
-__global__ void recv_expert_ids_kernel(const int4* __restrict__ meta, const int* __restrict__ counter, int capacity,
-                                       int* __restrict__ expert_ids, int* __restrict__ n_out) {
-  const int n = min(*counter, capacity);
-  if (blockIdx.x == 0 && threadIdx.x == 0) *n_out = n;
+// clear_counter (single-block launches only): the receive counter is reset here, after every thread has its copy of n,
+// instead of by a separate memset; peers only add to it again after the next cross-rank barrier of the stream.
+__global__ void recv_expert_ids_kernel(const int4* __restrict__ meta, int* __restrict__ counter, int capacity,
+                                       int* __restrict__ expert_ids, int* __restrict__ n_out, int clear_counter) {
+  __shared__ int n_sh;
+  if (threadIdx.x == 0) n_sh = min(*counter, capacity);
+  __syncthreads();
+  const int n = n_sh;
+  if (blockIdx.x == 0 && threadIdx.x == 0) {
+    *n_out = n;
+    if (clear_counter) *counter = 0;
+  }
   for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < capacity; i += gridDim.x * blockDim.x)
     expert_ids[i] = (i < n) ? meta[i].z : -1;
 }
@@ -377,9 +385,15 @@ extern "C" int mb_moe_return(const void* y_perm, const int* row_src, const void*
   return static_cast<int>(cudaGetLastError());
 }
 
-extern "C" int mb_recv_expert_ids(const void* meta, const int* counter, int capacity, int* expert_ids, int* n_out, cudaStream_t s) {
-  recv_expert_ids_kernel<<<blocks_for(capacity, 256, 64), 256, 0, s>>>(reinterpret_cast<const int4*>(meta), counter, capacity,
-                                                                      expert_ids, n_out);
+extern "C" int mb_recv_expert_ids(const void* meta, int* counter, int capacity, int* expert_ids, int* n_out, int clear_counter,
+                                  cudaStream_t s) {
+  if (clear_counter) {
+    if (capacity > 16384) return -1;    // one block only: the reset must follow every read of the counter
+    recv_expert_ids_kernel<<<1, 1024, 0, s>>>(reinterpret_cast<const int4*>(meta), counter, capacity, expert_ids, n_out, 1);
+  } else {
+    recv_expert_ids_kernel<<<blocks_for(capacity, 256, 64), 256, 0, s>>>(reinterpret_cast<const int4*>(meta), counter, capacity,
+                                                                        expert_ids, n_out, 0);
+  }
   return static_cast<int>(cudaGetLastError());
 }
 

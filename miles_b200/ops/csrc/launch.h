@@ -104,7 +104,8 @@ int mb_moe_align_pad(const int* idx, int n, const int* n_ptr, int E, int expert_
                      int* row_src, int* dst_row, int max_rows, int pad, cudaStream_t s);
 int mb_moe_gather(const void* x, void* x_perm, const int* row_src, const int* seg_offsets, int E, int k, int H, int max_rows,
                   cudaStream_t s);
-int mb_moe_combine(const void* y_perm, const float* w, const int* dst_row, void* out, long long T, int k, int H, cudaStream_t s);
+int mb_moe_combine(const void* y_perm, const float* w, const int* dst_row, void* out, long long T, int k, int H, int identity_rows,
+                   cudaStream_t s);
 int mb_moe_combine_bwd(const void* dout, const void* y_perm, const float* w, const int* row_src, const int* seg_offsets, int E,
                        void* dy_perm, float* dw, int k, int H, int max_rows, cudaStream_t s);
 
@@ -142,7 +143,7 @@ int mb_moe_scatter_known(const void* rows_in, int src_by_pair, const int* topk_i
                          int H, int e_local, const long long* recv_x_ptrs, int world, cudaStream_t s);
 int mb_moe_return(const void* y_perm, const int* row_src, const void* meta, const int* seg_offsets, int E, int H, int max_rows,
                   const long long* ret_ptrs, int world, cudaStream_t s);
-int mb_recv_expert_ids(const void* meta, const int* counter, int capacity, int* expert_ids, int* n_out, cudaStream_t s);
+int mb_recv_expert_ids(const void* meta, int* counter, int capacity, int* expert_ids, int* n_out, int clear_counter, cudaStream_t s);
 int mb_sum_rows(const long long* src_ptrs, int world, void* out, long long numel, cudaStream_t s);
 int mb_gather_rows(const long long* src_ptrs, int world, void* out, long long bytes_per_rank, cudaStream_t s);
 int mb_stats_merge(const long long* stats_ptrs, int world, long long R, float* logp, float* ent, float* lse, cudaStream_t s);

@@ -168,9 +168,10 @@ __global__ void __launch_bounds__(256) moe_gather_kernel(const bf16* __restrict_
 }
 
 // out[t, :] = Σ_j w[t,j] · y_perm[dst_row[t·k+j], :]   (w == nullptr → weights 1)
+// identity_rows: dst_row only says whether pair p took part (≥ 0); its row is p itself (per-pair return buffers).
 __global__ void __launch_bounds__(256) moe_combine_kernel(const bf16* __restrict__ y_perm, const float* __restrict__ w,
                                                           const int* __restrict__ dst_row, bf16* __restrict__ out, long long T, int k,
-                                                          int H) {
+                                                          int H, int identity_rows) {
   pdl_trigger();
   pdl_wait();
   const int nvec = H / 8;
@@ -178,8 +179,9 @@ __global__ void __launch_bounds__(256) moe_combine_kernel(const bf16* __restrict
     for (int v = threadIdx.x; v < nvec; v += 256) {
       float acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
       for (int j = 0; j < k; ++j) {
-        const int row = dst_row[t * k + j];
+        int row = dst_row[t * k + j];
         if (row < 0) continue;
+        if (identity_rows) row = static_cast<int>(t * k + j);
         const float wj = w ? w[t * k + j] : 1.f;
         const uint4 raw = *reinterpret_cast<const uint4*>(y_perm + static_cast<long long>(row) * H + v * 8);
         const __nv_bfloat162* p = reinterpret_cast<const __nv_bfloat162*>(&raw);
@@ -291,12 +293,12 @@ extern "C" int mb_moe_gather(const void* x, void* x_perm, const int* row_src, co
 }
 
 extern "C" int mb_moe_combine(const void* y_perm, const float* w, const int* dst_row, void* out, long long T, int k, int H,
-                              cudaStream_t s) {
+                              int identity_rows, cudaStream_t s) {
   if (T == 0) return 0;
   if (H % 8) return -1;
   const int blocks = T < 148 * 16 ? static_cast<int>(T) : 148 * 16;
   return static_cast<int>(launch_pdl(moe_combine_kernel, dim3(blocks), dim3(256), 0, s, reinterpret_cast<const bf16*>(y_perm), w, dst_row,
-                                     reinterpret_cast<bf16*>(out), T, k, H));
+                                     reinterpret_cast<bf16*>(out), T, k, H, identity_rows));
 }
 
 extern "C" int mb_moe_combine_bwd(const void* dout, const void* y_perm, const float* w, const int* row_src, const int* seg_offsets,

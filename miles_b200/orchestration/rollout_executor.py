@@ -64,17 +64,29 @@ class RolloutExecutor:
         else:
             out = self._call(self.rollout_fn, RolloutFnTrainInput(rollout_id))
             groups, metrics = out.samples, dict(out.metrics)
-        groups = self._exchange(groups)
+        dp = self.ps.dp_size if self.ps is not None else 1
+        # one engine per data-parallel rank: the rank may keep what it generated (prompt groups are never split, so group
+        # normalisation is unaffected) instead of pickling every sample — routed experts included — to every rank
+        local = (getattr(args, "rollout_data_exchange", "gather") == "local" and self.rollout_dp_size > 1
+                 and dp == self.rollout_dp_size and dist.is_initialized() and self._is_rollout_leader())
+        t_gen = time.time() - t0
+        if not local:
+            groups = self._exchange(groups)
         if getattr(args, "save_debug_rollout_data", None) and (not dist.is_initialized() or dist.get_rank() == 0):
             path = args.save_debug_rollout_data.format(rollout_id=rollout_id)
             os.makedirs(os.path.dirname(path) or ".", exist_ok=True)
             torch.save({"rollout_id": rollout_id, "samples": [[s.to_dict() for s in g] for g in groups]}, path)
         data = convert_samples_to_train_data(args, groups)
         metrics.update(self._rollout_metrics(groups, data, time.time() - t0))
-        dp = self.ps.dp_size if self.ps is not None else 1
-        shards = split_train_data_by_dp(args, data, dp)
-        mine = self.ps.dp_rank if self.ps is not None else 0
-        ref = object_store.put(shards[mine])
+        metrics["perf/generate_time"] = t_gen
+        if local:
+            metrics = self._reduce_metrics(metrics, len(data["tokens"]), sum(data["response_lengths"]))
+            shard = dict(data)
+            shard["partition"] = list(range(len(data["tokens"])))
+        else:
+            shards = split_train_data_by_dp(args, data, dp)
+            shard = shards[self.ps.dp_rank if self.ps is not None else 0]
+        ref = object_store.put(shard)
         return RolloutDataPack(rollout_id=rollout_id, sample_indices=data["sample_indices"], data_ref=ref, metrics=metrics)
 
     def eval(self, rollout_id: int) -> dict:
@@ -103,6 +115,32 @@ class RolloutExecutor:
             if part:
                 out.extend([[Sample.from_dict(d) for d in g] for g in part])
         out.sort(key=lambda g: g[0].index if g[0].index is not None else 0)
+        return out
+
+    def _reduce_metrics(self, m: dict, n_samples: int, n_resp: int) -> dict:
+        """Whole-job values of the per-rank rollout metrics (local exchange mode): means are re-weighted by their own
+        denominators (samples, or response tokens for the log-prob mean), totals summed, extrema reduced."""
+        by_sample = ["rollout/raw_reward", "rollout/response_len/mean", "rollout/truncated_ratio"]
+        dev = "cuda" if dist.get_backend(self.gather_group) == "nccl" else "cpu"
+        sums = torch.tensor([float(n_samples), float(n_resp), m.get("rollout/total_tokens", 0.0),
+                             m.get("rollout/log_probs", 0.0) * n_resp] + [m.get(k, 0.0) * n_samples for k in by_sample],
+                            dtype=torch.float64, device=dev)
+        ext = torch.tensor([m.get("rollout/response_len/max", 0.0), -m.get("rollout/response_len/min", 0.0),
+                            m.get("perf/rollout_time", 0.0), m.get("perf/generate_time", 0.0)], dtype=torch.float64, device=dev)
+        dist.all_reduce(sums, group=self.gather_group)
+        dist.all_reduce(ext, op=dist.ReduceOp.MAX, group=self.gather_group)
+        sums, ext = sums.tolist(), ext.tolist()
+        n, r = max(sums[0], 1.0), max(sums[1], 1.0)
+        out = dict(m)
+        out["rollout/total_tokens"] = sums[2]
+        if "rollout/log_probs" in m:
+            out["rollout/log_probs"] = sums[3] / r
+        for i, k in enumerate(by_sample):
+            out[k] = sums[4 + i] / n
+        out["rollout/response_len/max"], out["rollout/response_len/min"] = ext[0], -ext[1]
+        out["perf/rollout_time"], out["perf/generate_time"] = ext[2], ext[3]
+        gpus = max(1, getattr(self.args, "rollout_num_gpus", 1) or 1)
+        out["perf/tokens_per_gpu_per_sec"] = sums[1] / max(ext[2], 1e-9) / gpus
         return out
 
     def _is_rollout_leader(self) -> bool:

@@ -79,8 +79,10 @@ class _FusedMoE(torch.autograd.Function):
         cap = b.cap
         if getattr(ps, "moe_uniform_tokens", False) and not need_bwd:
             cap = min(cap, (ep * max(n_pairs, 1) + 127) // 128 * 128)
-        C.recv_expert_ids(b.recv_meta, b.counter, cap, b.expert_ids[:cap], b.n_recv)
-        b.counter.zero_()
+        small = cap <= 16384                # one-block scan that also resets the receive counter (no separate memset)
+        C.recv_expert_ids(b.recv_meta, b.counter, cap, b.expert_ids[:cap], b.n_recv, small)
+        if not small:
+            b.counter.zero_()
         # decode-sized calls (about n_pairs rows arrive when the routing is balanced): pad segments to 16/32/64 rows
         bt = 128 if need_bwd else small_moe_bt(n_pairs, e_local, w13, w2)
         max_rows = moe_max_rows_pad(cap, e_local, bt)
@@ -92,9 +94,13 @@ class _FusedMoE(torch.autograd.Function):
         C.moe_return(y_perm, row_src, b.recv_meta, seg, b.ret_ptrs, ep)
         fab.barrier(ranks, CH_EP2)
         out = torch.empty(T, H, dtype=x.dtype, device=x.device)
-        dst_row = torch.where(sent_row >= 0, b.pair_ids[:max(n_pairs, 1)], b.minus_one)
-        if T:
-            C.moe_combine(b.ret.view(b.max_pairs, H), wf, dst_row, out, k)
+        if need_bwd:
+            dst_row = torch.where(sent_row >= 0, b.pair_ids[:max(n_pairs, 1)], b.minus_one)
+            if T:
+                C.moe_combine(b.ret.view(b.max_pairs, H), wf, dst_row, out, k)
+        elif T:
+            # the return buffer is indexed by pair: `sent_row` only has to say which pairs took part
+            C.moe_combine(b.ret.view(b.max_pairs, H), wf, sent_row, out, k, True)
         if need_bwd:
             ret_saved = b.ret.view(b.max_pairs, H)[:max(n_pairs, 1)].clone()
             ctx.save_for_backward(w13, w2, wf, idx32, sent_row, dst_row, seg, tile, row_src, meta, h1, x_perm, ret_saved)

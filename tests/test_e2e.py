@@ -119,6 +119,8 @@ def _dist_hist(tmp_path, extra, world=2):
     "",                                                                     # dp2
     "--tensor-model-parallel-size 2 --sequence-parallel",                   # tp2 + sp
     "--model-name tiny-moe --expert-model-parallel-size 2",                 # dp2 × ep2
+    "--rollout-data-exchange local",                                        # dp2, every rank trains on what it generated
+    "--model-name tiny-moe --expert-model-parallel-size 2 --use-rollout-routing-replay --rollout-data-exchange local",
     "--context-parallel-size 2 --cp-comm-type a2a",                         # cp2 (Ulysses), dp1
     "--train-backend fsdp",                                                 # dp2, parameters sharded per layer (FSDP2)
     "--context-parallel-size 2",                                            # cp2, ring attention over zigzag pieces
