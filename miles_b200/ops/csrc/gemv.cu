@@ -338,13 +338,24 @@ __global__ void __launch_bounds__(kThreads) moe_gemv_up_kernel(const bf16* __res
     // the distinct experts of the step, in order of first appearance
     const PairIdx pi = load_pairs(topk_idx, n_pairs, E, offset);
     int cnt = 0;
-    for (int p = 0; p < n_pairs; ++p) {
-      const int e = expert_of(pi, p);
-      if (e < 0) continue;
-      const unsigned long long m = match_mask(pi, e);
-      if (!is_first(m, p)) continue;
-      if (lane == 0) { slot_e[cnt] = e; slot_mask[cnt] = m; }
-      ++cnt;
+    if (E <= n_pairs) {
+      // few local experts: one ballot pair per expert instead of a shuffle + ballot round per pair (the other warps wait
+      // for this table; slots are then in expert order, which only changes which CTA takes which item)
+      for (int e = 0; e < E; ++e) {
+        const unsigned long long m = match_mask(pi, e);
+        if (m == 0ull) continue;
+        if (lane == 0) { slot_e[cnt] = e; slot_mask[cnt] = m; }
+        ++cnt;
+      }
+    } else {
+      for (int p = 0; p < n_pairs; ++p) {
+        const int e = expert_of(pi, p);
+        if (e < 0) continue;
+        const unsigned long long m = match_mask(pi, e);
+        if (!is_first(m, p)) continue;
+        if (lane == 0) { slot_e[cnt] = e; slot_mask[cnt] = m; }
+        ++cnt;
+      }
     }
     if (lane == 0) n_slots_s = cnt;
   }
@@ -359,14 +370,21 @@ __global__ void __launch_bounds__(kThreads) moe_gemv_up_kernel(const bf16* __res
   const int cpw = chunks > warp ? (chunks - warp + kWarps - 1) / kWarps : 0;     // chunks of an item taken by this warp
   const int total = n_mine * cpw;
   const int stride = staged_stride(H);
+  // the copies are issued in stream order, so the (item, chunk) cursor advances incrementally: no division per copy
+  int i_u = 0, i_item = blockIdx.x;
+  const long long up_off = static_cast<long long>(F) * H;
+  const bf16* i_base = nullptr;
+  auto set_item = [&]() {
+    if (i_item < n_items)
+      i_base = w13 + static_cast<long long>(slot_e[i_item / nfb]) * 2 * F * H + static_cast<long long>((i_item % nfb) * 8 + g) * H + t * 8;
+  };
+  set_item();
   auto issue = [&](int q) {
     if (q < total) {
-      const int j = q / cpw, u = q - j * cpw;
-      const int item = blockIdx.x + j * gridDim.x;
-      const int e = slot_e[item / nfb], f0 = (item % nfb) * 8, ch = warp + u * kWarps;
-      const bf16* base = w13 + static_cast<long long>(e) * 2 * F * H + ch * 32 + t * 8;
-      cp16(ring_slot(ring, q & (S - 1), 0), base + static_cast<long long>(f0 + g) * H);
-      cp16(ring_slot(ring, q & (S - 1), 1), base + static_cast<long long>(F + f0 + g) * H);
+      const bf16* pa = i_base + (warp + i_u * kWarps) * 32;
+      cp16(ring_slot(ring, q & (S - 1), 0), pa);
+      cp16(ring_slot(ring, q & (S - 1), 1), pa + up_off);
+      if (++i_u == cpw) { i_u = 0; i_item += gridDim.x; set_item(); }
     }
     cp_commit();
   };
@@ -443,11 +461,7 @@ __global__ void __launch_bounds__(kThreads) moe_gemv_down_kernel(const bf16* __r
     // the distinct experts of the step with, per token, the pair routed to them and its gate weight
     const PairIdx pi = load_pairs(topk_idx, n_pairs, E, offset);
     int cnt = 0;
-    for (int p = 0; p < n_pairs; ++p) {
-      const int e = expert_of(pi, p);
-      if (e < 0) continue;
-      const unsigned long long mask = match_mask(pi, e);
-      if (!is_first(mask, p)) continue;
+    auto add_slot = [&](int e, unsigned long long mask) {
       if (lane < 8) {
         const int pair = lane < T ? pair_of(mask, lane, k) : -1;
         sl_pair[cnt][lane] = static_cast<signed char>(pair);
@@ -455,6 +469,19 @@ __global__ void __launch_bounds__(kThreads) moe_gemv_down_kernel(const bf16* __r
       }
       if (lane == 0) sl_e[cnt] = e;
       ++cnt;
+    };
+    if (E <= n_pairs) {                      // few local experts: a ballot pair per expert (see moe_gemv_up_kernel)
+      for (int e = 0; e < E; ++e) {
+        const unsigned long long mask = match_mask(pi, e);
+        if (mask != 0ull) add_slot(e, mask);
+      }
+    } else {
+      for (int p = 0; p < n_pairs; ++p) {
+        const int e = expert_of(pi, p);
+        if (e < 0) continue;
+        const unsigned long long mask = match_mask(pi, e);
+        if (is_first(mask, p)) add_slot(e, mask);
+      }
     }
     if (lane == 0) n_slots_s = cnt;
   }
@@ -462,12 +489,18 @@ __global__ void __launch_bounds__(kThreads) moe_gemv_down_kernel(const bf16* __r
   const int cnt = n_slots_s;
   const int cpw = chunks > warp ? (chunks - warp + kWarps - 1) / kWarps : 0;      // chunks of an expert taken by this warp
   const int total = cnt * cpw;
+  int i_u = 0, i_j = 0;                                         // issue cursor: (expert slot, chunk), advanced in stream order
+  const long long row_off = static_cast<long long>(h0 + g) * F + t * 8;
+  const bf16* i_base = cnt > 0 ? w2 + static_cast<long long>(sl_e[0]) * H * F + row_off : nullptr;
   auto issue = [&](int q) {
     if (q < total) {
-      const int j = q / cpw, u = q - j * cpw;
-      const bf16* base = w2 + static_cast<long long>(sl_e[j]) * H * F + (warp + u * kWarps) * 32 + t * 8;
-      cp16(ring_slot(ring, q & (S - 1), 0), base + static_cast<long long>(h0 + g) * F);
-      cp16(ring_slot(ring, q & (S - 1), 1), base + static_cast<long long>(h0 + g + 8) * F);
+      const bf16* pa = i_base + (warp + i_u * kWarps) * 32;
+      cp16(ring_slot(ring, q & (S - 1), 0), pa);
+      cp16(ring_slot(ring, q & (S - 1), 1), pa + 8 * F);
+      if (++i_u == cpw) {
+        i_u = 0;
+        if (++i_j < cnt) i_base = w2 + static_cast<long long>(sl_e[i_j]) * H * F + row_off;
+      }
     }
     cp_commit();
   };
