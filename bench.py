@@ -44,6 +44,9 @@ def parse():
     p.add_argument("--mean-response-len", type=int, default=512,
                    help="stop-token set sized so that a random-init policy stops after this many tokens on average")
     p.add_argument("--max-tokens-per-gpu", type=int, default=16384)
+    p.add_argument("--mem-fraction-static", type=float, default=0.75,
+                   help="share of device memory for weights + optimizer state + KV cache; the rest (45 GB at 0.75) stays free for "
+                        "training activations. Too small a KV cache caps how many of the 64 requests decode at once.")
     p.add_argument("--no-fused", action="store_true", help="NCCL + separate GEMM baseline instead of the fused kernels")
     p.add_argument("--no-cuda-graph", action="store_true")
     p.add_argument("--quiet", action="store_true")
@@ -181,9 +184,12 @@ def main():
 
     from miles_b200.engine.engine import Engine
 
-    engine = Engine(cfg, model=actor.model, ps=ps, device=dev, dtype=torch.bfloat16, mem_fraction_static=0.55,
+    engine = Engine(cfg, model=actor.model, ps=ps, device=dev, dtype=torch.bfloat16, mem_fraction_static=a.mem_fraction_static,
                     max_running_requests=a.prompts_per_gpu * a.samples_per_prompt, max_prefill_tokens=16384,
                     max_context_len=a.prompt_len_max + a.max_new_tokens, seed=1234 + rank, use_cuda_graph=not a.no_cuda_graph)
+    if rank == 0 and not a.quiet:
+        print(f"[engine] KV cache: {engine.allocator.num_free} blocks x {engine.block_size} tokens = "
+              f"{engine.allocator.num_free * engine.block_size} tokens", file=sys.stderr, flush=True)
     client = InProcEngineClient([engine])
     source = SyntheticPromptSource(args, V - n_stop, a.prompt_len_min, a.prompt_len_max, seed=1000 + rank)
     executor = RolloutExecutor(args, source, client, ps=ps, rollout_dp_size=world, rollout_dp_rank=rank)

@@ -173,9 +173,42 @@ def bench_mxfp8(a):
     return out
 
 
+def bench_moe_gemv(a):
+    """Decode-time MoE FFN for a handful of tokens (matrix-vector kernels, gemv.cu): 16 local experts of the Qwen3-30B-A3B
+    shape, top-8 routing; three weight sets are rotated so that no call finds its 151 MB of weights in L2."""
+    from . import cuda as K
+    from . import reference as ref
+
+    hbm, _, tag = peaks()
+    T, k, E, H, F = max(1, min(a.batch, 8)), 8, 16, 2048, 768
+    torch.manual_seed(0)
+    sets = [((0.02 * torch.randn(E, 2 * F, H, device="cuda")).bfloat16(), (0.02 * torch.randn(E, H, F, device="cuda")).bfloat16())
+            for _ in range(3)]
+    x = torch.randn(T, H, device="cuda").bfloat16()
+    tw, ti, _ = ref.router_topk(torch.randn(T, E, device="cuda"), k, True)
+    ti32, twf = ti.to(torch.int32).contiguous(), tw.float().contiguous()
+    act = torch.empty(T * k, F, dtype=torch.bfloat16, device="cuda")
+    out = torch.empty_like(x)
+    state = {"i": 0}
+
+    def run():
+        w13, w2 = sets[state["i"] % 3]
+        state["i"] += 1
+        K.C.moe_gemv(x, w13, w2, ti32, twf, act, out, 0)
+
+    ms = timeit(run, iters=a.iters, flush=False)
+    w13, w2 = sets[(state["i"] - 1) % 3]
+    want = ref.moe_ffn(x.float(), w13.float(), w2.float(), tw.float(), ti)
+    rel = ((out.float() - want).norm() / want.norm()).item()
+    touched = int(torch.unique(ti).numel())
+    gb = touched * 3 * F * H * 2 / 1e9
+    return [{"op": "moe_gemv up+down", "tokens": T, "experts_touched": touched, "us": ms * 1e3, "weight_MB": gb * 1e3,
+             "GBps": gb / (ms * 1e-3), "frac_hbm": gb / (ms * 1e-3) / hbm, "peak": tag, "rel_err_vs_fp32": rel}]
+
+
 def main():
     p = argparse.ArgumentParser()
-    p.add_argument("what", choices=["gemm", "mxfp8", "attention", "decode", "elementwise", "all"])
+    p.add_argument("what", choices=["gemm", "mxfp8", "attention", "decode", "elementwise", "moe_gemv", "all"])
     p.add_argument("--m", type=int, default=0)
     p.add_argument("--n", type=int, default=8192)
     p.add_argument("--k", type=int, default=8192)
@@ -199,6 +232,8 @@ def main():
         rows += bench_decode(a2)
     if a.what in ("elementwise", "all"):
         rows += bench_elementwise(a)
+    if a.what in ("moe_gemv", "all"):
+        rows += bench_moe_gemv(a)
     for r in rows:
         print(json.dumps({k: (round(v, 4) if isinstance(v, float) else v) for k, v in r.items()}))
     if a.json:
