@@ -116,6 +116,9 @@ class Engine:
         hkv = cfg.num_kv_heads // self.ps.tp_size
         if num_blocks is None:
             if self.device.type == "cuda":
+                # blocks the caching allocator holds but no tensor uses (temporaries of the trainer's set-up) count as
+                # used in mem_get_info: hand them back first, or the cache is sized from a fraction of what is really free
+                torch.cuda.empty_cache()
                 free, total = torch.cuda.mem_get_info(self.device)
                 budget = int(free - (1.0 - mem_fraction_static) * total)
                 budget = max(budget, 1 << 30)
