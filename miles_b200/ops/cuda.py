@@ -94,7 +94,7 @@ def _splitk_workspace(device):
 
 # A handful of tokens (decode with a nearly drained batch): matrix-vector kernels without pipeline set-up (gemv.cu).
 # Up to 16 rows are supported; 0 turns the path off.
-GEMV_M = min(16, int(os.environ.get("MILES_GEMV_M", "8")))
+GEMV_M = min(16, int(os.environ.get("MILES_GEMV_M", "16")))
 GEMV_MAX_N = int(os.environ.get("MILES_GEMV_MAX_N", "32768"))
 
 
