@@ -271,10 +271,12 @@ class Qwen3Model(nn.Module):
         tp = self.ps.tp_size
         return self.embed if tp == 1 else self.embed.chunk(tp, 0)[self.ps.tp_rank]
 
-    def forward(self, tokens: torch.Tensor, meta: ForwardMeta, hidden_in: torch.Tensor | None = None):
-        """tokens int [T] → final-norm hidden states [T(/tp with SP), H] (last stage) or raw hidden."""
+    def forward(self, tokens: torch.Tensor, meta: ForwardMeta, hidden_in: torch.Tensor | None = None,
+                inputs_embeds: torch.Tensor | None = None):
+        """tokens int [T] → final-norm hidden states [T(/tp with SP), H] (last stage) or raw hidden.
+        `inputs_embeds` [T, H] replaces the embedding look-up (vision-language: image features merged in)."""
         if self.has_embed:
-            x = ops.embedding(tokens, self.embed)
+            x = inputs_embeds if inputs_embeds is not None else ops.embedding(tokens, self.embed)
             x = self.ps.sp_scatter(x)
         else:
             x = hidden_in
