@@ -162,7 +162,11 @@ def main():
         if ps.fused:
             from miles_b200.parallel.fabric import Fabric
 
-            ps.fabric = Fabric.create(ps)
+            try:
+                ps.fabric = Fabric.create(ps)
+            except Exception as e:      # peer mapping refused on this box: run the NCCL path and say so in `fused_comm`
+                print(f"[bench] fabric unavailable ({type(e).__name__}: {e}); falling back to NCCL collectives", file=sys.stderr)
+                ps.fused, ps.fabric = False, None
     else:
         ps = ParallelState.single()
 

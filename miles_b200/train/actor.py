@@ -201,7 +201,9 @@ class TrainActor:
     def _forward_logprobs(self, pb: PackedBatch, with_entropy: bool, replay: bool):
         if self.ps.cp_size > 1:
             return self._forward_logprobs_cp(pb, with_entropy, replay)
-        hidden = self.model(pb.tokens, self._meta(pb, replay))
+        # vision-language policies take the images of the packed samples next to the token stream
+        hidden = (self.model(pb.tokens, self._meta(pb, replay), **pb.mm_inputs) if pb.mm_inputs
+                  else self.model(pb.tokens, self._meta(pb, replay)))
         if self.role == "critic":
             h = self.ps.sp_gather(hidden)
             return self.model.value_head(h[pb.gather_index].float()).squeeze(-1), None

@@ -76,6 +76,8 @@ def convert_samples_to_train_data(args, samples: list[Sample] | list[list[Sample
         data["opd_reverse_kl"] = [list(s.opd_reverse_kl) for s in flat]
     if any(s.weight_versions for s in flat):
         data["weight_versions"] = [s.oldest_weight_version for s in flat]
+    if any(getattr(s, "multimodal_train_inputs", None) for s in flat):
+        data["multimodal_train_inputs"] = [s.multimodal_train_inputs for s in flat]
     # per-rollout mask sums: siblings of one rollout (same rollout_id) share a denominator
     sums: dict[Any, int] = {}
     for rid, lm in zip(data["rollout_ids"], data["loss_masks"]):
@@ -86,7 +88,8 @@ def convert_samples_to_train_data(args, samples: list[Sample] | list[list[Sample
 
 _PER_SAMPLE_KEYS = ("tokens", "response_lengths", "total_lengths", "rewards", "raw_reward", "truncated", "loss_masks",
                     "sample_indices", "rollout_ids", "rollout_log_probs", "rollout_routed_experts",
-                    "teacher_log_probs", "opd_reverse_kl", "weight_versions", "rollout_mask_sums", "advantages")
+                    "teacher_log_probs", "opd_reverse_kl", "weight_versions", "rollout_mask_sums", "advantages",
+                    "multimodal_train_inputs")
 
 
 def karmarkar_karp(lengths: list[int], k: int, equal_size: bool = True) -> list[list[int]]:
@@ -192,6 +195,7 @@ class PackedBatch:
     sample_index: list[int] = field(default_factory=list)   # indices into the rank-local shard
     replay_topk: torch.Tensor | None = None  # int32 [T_pad, L_moe, k]
     num_real_tokens: int = 0
+    mm_inputs: dict | None = None   # vision-language: {"patches": [N, patch_dim], "grid_thw": [n_images, 3]} of the packed samples
 
 
 def pack_micro_batch(shard: dict[str, Any], idx: list[int], device, *, pad_multiple: int = PAD_MULTIPLE,
@@ -239,7 +243,16 @@ def pack_micro_batch(shard: dict[str, Any], idx: list[int], device, *, pad_multi
             if pad:
                 body = torch.cat([body, torch.full((pad,) + tuple(body.shape[1:]), -1, dtype=torch.int32)], 0)
             replay = body.to(device)
+    mm = None
+    if shard.get("multimodal_train_inputs") is not None:
+        # per-sample {"patches", "grid_thw"} in sample order = the order of the image placeholder tokens in the packed stream
+        parts = [shard["multimodal_train_inputs"][i] for i in idx]
+        parts = [p for p in parts if p and p.get("patches") is not None and len(p["patches"])]
+        if parts:
+            mm = {"patches": torch.cat([torch.as_tensor(p["patches"]) for p in parts], 0).to(device),
+                  "grid_thw": torch.cat([torch.as_tensor(p["grid_thw"]).view(-1, 3) for p in parts], 0).to(device)}
     return PackedBatch(
+        mm_inputs=mm,
         tokens=torch.tensor(toks, dtype=torch.int32, device=device),
         positions=torch.tensor(pos, dtype=torch.int32, device=device),
         cu_seqlens=torch.tensor(cu, dtype=torch.int32, device=device),

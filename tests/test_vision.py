@@ -61,3 +61,35 @@ def test_merge_and_gradients_through_language_model():
     plain = torch.tensor([5, 6, 7, 8], dtype=torch.int32)
     m2 = ForwardMeta(positions=torch.arange(4, dtype=torch.int32), cu_seqlens=torch.tensor([0, 4], dtype=torch.int32), max_seqlen=4)
     assert torch.equal(vlm(plain, m2), lm(plain, m2))
+
+
+def test_packed_batch_carries_images_in_sample_order():
+    from miles_b200.train.data import pack_micro_batch
+
+    lm_cfg = PRESETS["tiny"]
+    lm = build_model(lm_cfg, dtype=torch.float32, device="cpu", seed=0)
+    cfg, tower = _tower(lm_cfg.hidden_size)
+    image_id = lm_cfg.vocab_size - 1
+    vlm = VisionLanguageModel(lm, tower, image_id)
+    g = torch.Generator().manual_seed(3)
+    img_a = {"patches": torch.randn(16, cfg.patch_dim, generator=g), "grid_thw": torch.tensor([[1, 4, 4]])}
+    img_b = {"patches": torch.randn(8, cfg.patch_dim, generator=g), "grid_thw": torch.tensor([[1, 2, 4]])}
+    shard = {
+        "tokens": [[4, image_id, image_id, image_id, image_id, 9, 10, 11], [5, 6, 7, 8], [3, image_id, image_id, 12, 13]],
+        "response_lengths": [3, 2, 2],
+        "loss_masks": [[1, 1, 1], [1, 1], [1, 1]],
+        "multimodal_train_inputs": [img_a, None, img_b],
+    }
+    pb = pack_micro_batch(shard, [0, 1, 2], "cpu", pad_multiple=1)
+    assert pb.mm_inputs["patches"].shape[0] == 24 and pb.mm_inputs["grid_thw"].tolist() == [[1, 4, 4], [1, 2, 4]]
+    meta = ForwardMeta(positions=pb.positions, cu_seqlens=pb.cu_seqlens, max_seqlen=pb.max_seqlen)
+    h = vlm(pb.tokens, meta, **pb.mm_inputs)
+    # the text-only sample in the middle is unaffected by the images around it
+    solo = pack_micro_batch(shard, [1], "cpu", pad_multiple=1)
+    h_solo = vlm(solo.tokens, ForwardMeta(positions=solo.positions, cu_seqlens=solo.cu_seqlens, max_seqlen=solo.max_seqlen))
+    assert solo.mm_inputs is None and torch.allclose(h[8:12], h_solo, atol=1e-5)
+    # order: swapping which image goes with which sample changes the first sample's hidden states
+    pb2 = pack_micro_batch(dict(shard, multimodal_train_inputs=[img_a, None, {"patches": img_b["patches"] + 1, "grid_thw": img_b["grid_thw"]}]),
+                           [0, 1, 2], "cpu", pad_multiple=1)
+    h2 = vlm(pb2.tokens, meta, **pb2.mm_inputs)
+    assert torch.allclose(h[:8], h2[:8], atol=1e-5) and not torch.allclose(h[12:], h2[12:], atol=1e-4)
