@@ -12,7 +12,7 @@ sys.path.insert(0, ROOT)
 
 BASE = ("--model-name tiny --fp32 --rollout-batch-size 4 --n-samples-per-prompt 2 --rollout-max-response-len 8 "
         "--rm-type even_fraction --lr 1e-3 --colocate --advantage-estimator grpo "
-        "--data-source-path miles_b200.rollout.data_source.SyntheticSource --synthetic-prompt-len 6 10 --indep-dp-timeout 5")
+        "--data-source-path miles_b200.rollout.data_source.SyntheticSource --synthetic-prompt-len 6 10")
 
 
 def _free_port() -> int:
@@ -32,7 +32,9 @@ def _cell(cell, n_cells, store_port, world_port, num_rollout, out_dir, leave_aft
     import train as T
     from miles_b200.args import parse_args
 
-    extra = f" --num-rollout {num_rollout}"
+    # a short group timeout only where a cell is meant to go missing; otherwise a loaded machine (parallel test workers)
+    # must not turn a slow peer into a lost one
+    extra = f" --num-rollout {num_rollout} --indep-dp-timeout {5 if leave_after is not None else 60}"
     if n_cells > 1:
         extra += f" --indep-dp --indep-dp-num-cells {n_cells} --indep-dp-cell-id {cell} --indep-dp-store 127.0.0.1:{store_port}"
     args = parse_args((BASE + extra).split())
