@@ -159,7 +159,8 @@ def build_parser() -> argparse.ArgumentParser:
     g.add_argument("--num-rollout", type=int, default=None)
     g.add_argument("--num-epoch", type=int, default=None)
     g.add_argument("--update-weight-buffer-size", type=int, default=512 * 1024 * 1024)
-    g.add_argument("--update-weight-transfer-mode", choices=["auto", "broadcast", "broadcast_packed", "cuda_ipc", "p2p", "delta", "nvlink"], default="auto")
+    g.add_argument("--update-weight-transfer-mode", choices=["auto", "alias", "nvlink", "tensor", "broadcast", "broadcast_packed", "cuda_ipc", "p2p", "disk", "delta"],
+                   default="auto")
     g.add_argument("--update-weights-interval", type=int, default=1)
     _bool_flag(g, "--fully-async")
     g.add_argument("--max-weight-staleness", type=int, default=1)

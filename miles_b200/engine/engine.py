@@ -266,12 +266,25 @@ class Engine:
         return {"success": True}
 
     def update_weights_from_disk(self, model_path: str, weight_version: int | None = None):
-        """Load an HF safetensors directory (full tensors, HF names) into this rank's shard."""
+        """Load an HF safetensors directory (full tensors, HF names) into this rank's shard.  A version directory of the
+        delta protocol (`v{N}/manifest.json` under a delta root) is followed with a `DeltaReader` instead."""
+        import os
+
         from ..checkpoint import hf_io
         from ..models.convert import load_named_into_model
 
         with self.lock:
-            load_named_into_model(self.model, hf_io.load_hf_dir(model_path).items(), self.cfg, self.ps)
+            if os.path.exists(os.path.join(model_path, "manifest.json")):
+                from ..weight_update.delta import DeltaReader
+
+                root, leaf = os.path.split(os.path.normpath(model_path))
+                rd = getattr(self, "_delta_reader", None)
+                if rd is None or rd.root != root:
+                    rd = self._delta_reader = DeltaReader(root)
+                named = rd.update_to(int(leaf.lstrip("v"))).items()
+            else:
+                named = hf_io.load_hf_dir(model_path).items()
+            load_named_into_model(self.model, named, self.cfg, self.ps)
             if weight_version is not None:
                 self.weight_version = int(weight_version)
         return {"success": True}

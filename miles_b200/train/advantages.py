@@ -20,6 +20,19 @@ def compute_kl_for_advantages(args, log_probs, ref_log_probs):
     return mu.compute_approx_kl(log_probs, ref_log_probs, getattr(args, "kl_loss_type", "k1"))
 
 
+def last_trainable_index(loss_mask: torch.Tensor, seq_ids: torch.Tensor, num_seqs: int):
+    """Flat index of the last token with loss_mask > 0 of every sequence, and which sequences have one.  The terminal
+    reward is credited there (a response may end in masked tokens: tool or environment output of a multi-turn rollout),
+    as in the reference (loss/hub/math_utils.py get_reinforce_plus_plus_returns, get_advantages_and_returns_batch)."""
+    R = loss_mask.numel()
+    idx = torch.arange(R, device=loss_mask.device)
+    cand = torch.where(loss_mask > 0, idx, torch.full_like(idx, -1))
+    last = torch.full((num_seqs,), -1, dtype=idx.dtype, device=loss_mask.device)
+    last = last.scatter_reduce(0, seq_ids, cand, reduce="amax", include_self=True)
+    has = last >= 0
+    return last.clamp_min(0), has
+
+
 def compute_advantages_and_returns(args, *, rewards: torch.Tensor, response_lengths: list[int],
                                    loss_mask: torch.Tensor, log_probs: torch.Tensor | None = None,
                                    ref_log_probs: torch.Tensor | None = None,
@@ -43,17 +56,17 @@ def compute_advantages_and_returns(args, *, rewards: torch.Tensor, response_leng
         ret = adv.clone()
     elif est == "ppo":
         assert values is not None, "PPO needs critic values"
-        lens = torch.as_tensor(response_lengths, device=device)
-        last = torch.cumsum(lens, 0) - 1
+        last, has = last_trainable_index(loss_mask, seq_ids, S)
         tok_r = -kl_coef * kl
-        tok_r = tok_r.index_add(0, last, rewards.float().to(device))
+        tok_r = tok_r.index_add(0, last[has], rewards.float().to(device)[has])
         adv, ret = mu.masked_gae(tok_r, values.float(), loss_mask, response_lengths, args.gamma, args.lambd)
     elif est == "reinforce_plus_plus":
-        lens = torch.as_tensor(response_lengths, device=device)
-        last = torch.cumsum(lens, 0) - 1
-        tok_r = (-kl_coef * kl) * loss_mask
-        tok_r = tok_r.index_add(0, last, rewards.float().to(device))
+        last, has = last_trainable_index(loss_mask, seq_ids, S)
+        tok_r = -kl_coef * kl
+        tok_r = tok_r.index_add(0, last[has], rewards.float().to(device)[has])
         ret = mu.discounted_returns(tok_r, response_lengths, args.gamma)
+        # a fully masked sequence has no trainable token to carry the reward: it contributes nothing
+        ret = ret * has[seq_ids]
         adv = ret.clone()
     elif est == "reinforce_plus_plus_baseline":
         adv = r_tok - kl_coef * kl

@@ -40,18 +40,14 @@ def convert_samples_to_train_data(args, samples: list[Sample] | list[list[Sample
         flat = list(samples)
         n = getattr(args, "n_samples_per_prompt", 1)
         group_sizes = [n] * (len(flat) // n) + ([len(flat) % n] if len(flat) % n else [])
-    flat = [s for s in flat if not s.remove_sample] if any(s.remove_sample for s in flat) else flat
+    # samples marked remove_sample stay in the batch (their reward still counts in the group statistics and the batch and
+    # shard sizes stay fixed); only their loss mask is zeroed below
     raw = torch.tensor([s.get_reward_value(getattr(args, "reward_key", None)) for s in flat], dtype=torch.float32)
     post = getattr(args, "custom_reward_post_process_path", None)
     if post:
         rewards = torch.as_tensor(load_function(post)(args, flat), dtype=torch.float32)
     else:
-        if sum(group_sizes) != len(flat):  # removed samples broke the grouping: regroup by group_index
-            by: dict[Any, int] = {}
-            for s in flat:
-                by[s.group_index] = by.get(s.group_index, 0) + 1
-            group_sizes = list(by.values())
-        rewards = normalize_group_rewards(args, raw, group_sizes)
+        rewards = normalize_rewards_by_rollout(args, flat, raw, group_sizes)
     data: dict[str, Any] = {
         "tokens": [list(s.tokens) for s in flat],
         "response_lengths": [s.response_length for s in flat],
@@ -59,12 +55,15 @@ def convert_samples_to_train_data(args, samples: list[Sample] | list[list[Sample
         "rewards": rewards.tolist(),
         "raw_reward": raw.tolist(),
         "truncated": [1 if s.status == Status.TRUNCATED else 0 for s in flat],
-        "loss_masks": [list(s.loss_mask) if s.loss_mask is not None else [1] * s.response_length for s in flat],
+        "loss_masks": [[0] * s.response_length if s.remove_sample else
+                       (list(s.loss_mask) if s.loss_mask is not None else [1] * s.response_length) for s in flat],
         "sample_indices": [s.index for s in flat],
         "rollout_ids": [s.rollout_id if s.rollout_id is not None else s.index for s in flat],
         "prompt_group_sizes": group_sizes,
     }
     for s, lm in zip(flat, data["loss_masks"]):
+        assert s.loss_mask is None or len(s.loss_mask) == s.response_length, \
+            f"loss_mask length {len(s.loss_mask)} != response_length {s.response_length}"
         assert len(lm) == s.response_length, f"loss_mask length {len(lm)} != response_length {s.response_length}"
     if all(s.rollout_log_probs is not None for s in flat) and flat:
         data["rollout_log_probs"] = [list(s.rollout_log_probs) for s in flat]
@@ -84,6 +83,36 @@ def convert_samples_to_train_data(args, samples: list[Sample] | list[list[Sample
         sums[rid] = sums.get(rid, 0) + int(sum(lm))
     data["rollout_mask_sums"] = [sums[rid] for rid in data["rollout_ids"]]
     return data
+
+
+def normalize_rewards_by_rollout(args, flat: list[Sample], raw: torch.Tensor, group_sizes: list[int]) -> torch.Tensor:
+    """Group normalisation with one vote per rollout: segments of one rollout (same `rollout_id`, e.g. the turns of a
+    multi-turn trajectory split into several training rows) carry one shared reward, which enters the prompt group's
+    mean / std once and is broadcast back to every segment; siblings with different rewards are an error
+    (reference: miles/ray/rollout/train_data_conversion.py:275-322)."""
+    est = args.advantage_estimator
+    if est not in ("grpo", "gspo", "reinforce_plus_plus_baseline") or not getattr(args, "rewards_normalization", True):
+        return raw.float()
+    out = torch.empty(len(flat), dtype=torch.float32)
+    off = 0
+    for n in group_sizes:
+        keys: dict[Any, list[int]] = {}
+        for i in range(off, off + n):
+            s = flat[i]
+            key = s.rollout_id if s.rollout_id is not None else (s.index if s.index is not None else ("row", i))
+            keys.setdefault(key, []).append(i)
+        shared = []
+        for key, rows in keys.items():
+            vals = [float(raw[i]) for i in rows]
+            if any(v != vals[0] for v in vals[1:]):
+                raise ValueError(f"all samples of rollout {key!r} must share one reward; rows {rows} have rewards {vals}")
+            shared.append(vals[0])
+        normed = normalize_group_rewards(args, torch.tensor(shared, dtype=torch.float32), [len(shared)])
+        for (key, rows), v in zip(keys.items(), normed.tolist()):
+            for i in rows:
+                out[i] = v
+        off += n
+    return out
 
 
 _PER_SAMPLE_KEYS = ("tokens", "response_lengths", "total_lengths", "rewards", "raw_reward", "truncated", "loss_masks",
@@ -166,15 +195,18 @@ def make_micro_batches(args, total_lengths: list[int], *, dp_group=None, cp_size
         num = int(t.item())
     if vpp_multiple > 1:
         num = (num + vpp_multiple - 1) // vpp_multiple * vpp_multiple
-    num = min(num, max(n, 1)) if not getattr(args, "use_dynamic_batch_size", False) else num
+    # every DP rank returns exactly `num` parts (never fewer than the reduced count: layers with collectives inside the
+    # forward must run the same number of times everywhere); a rank with too few samples pads with empty parts
+    if n == 0:
+        return [[] for _ in range(num)]
     if getattr(args, "use_dynamic_batch_size", False):
         parts = karmarkar_karp(total_lengths, num, equal_size=False)
         parts = [sorted(p) for p in parts]
     else:
         mbs = (n + num - 1) // num
         parts = [list(range(i, min(n, i + mbs))) for i in range(0, n, mbs)]
-        while len(parts) < num:
-            parts.append([])
+    while len(parts) < num:
+        parts.append([])
     return parts
 
 

@@ -154,7 +154,7 @@ def policy_loss_function(args, batch: LossBatch, log_probs: torch.Tensor, entrop
         assert batch.ref_log_probs is not None, "--use-kl-loss needs reference log-probs"
         ratio = None
         if getattr(args, "use_unbiased_kl", False):
-            ratio = torch.exp((log_probs - old).clamp(-20, 20)).detach()
+            ratio = torch.exp((log_probs - old).clamp(-20, 20))     # live: its gradient is part of the estimator
         kl = mu.compute_approx_kl(log_probs, batch.ref_log_probs, args.kl_loss_type, ratio)
         kl_loss = red(kl)
         metrics["kl_loss"] = kl_loss.detach()

@@ -35,7 +35,8 @@ def lengths_to_seq_ids(lengths, device) -> torch.Tensor:
 
 def compute_approx_kl(log_probs, log_probs_base, kl_loss_type: str = "k1", importance_ratio=None):
     """Schulman's estimators with d = logp − logp_base: k1 d; k2 d²/2; k3 exp(−d) − 1 + d;
-    low_var_kl = k3 clamped to [−10, 10] with a guarded exponent. Optionally × importance ratio."""
+    low_var_kl = k3 with a guarded exponent, clamped to [−10, 10] AFTER the optional × importance ratio
+    (reference: loss/hub/math_utils.py:139-180)."""
     d = log_probs.float() - log_probs_base.float()
     if kl_loss_type == "k1":
         kl = d
@@ -44,12 +45,14 @@ def compute_approx_kl(log_probs, log_probs_base, kl_loss_type: str = "k1", impor
     elif kl_loss_type == "k3":
         kl = torch.exp(-d) - 1.0 + d
     elif kl_loss_type == "low_var_kl":
-        nd = torch.clamp(-d, min=-20.0, max=20.0)
-        kl = torch.clamp(torch.exp(nd) - 1.0 - nd, min=-10.0, max=10.0)
+        nd = torch.clamp(torch.nan_to_num(-d, nan=0.0, posinf=20.0, neginf=-20.0), min=-20.0, max=20.0)
+        kl = torch.exp(nd) - 1.0 - nd
     else:
         raise ValueError(f"unknown kl_loss_type {kl_loss_type}")
     if importance_ratio is not None:
         kl = kl * importance_ratio
+    if kl_loss_type == "low_var_kl":
+        kl = torch.clamp(kl, min=-10.0, max=10.0)
     return kl
 
 
@@ -59,14 +62,16 @@ def compute_gspo_kl(log_probs, old_log_probs, mask, seq_ids, num_seqs):
 
 
 def compute_opsm_mask(log_probs, old_log_probs, advantages, mask, seq_ids, num_seqs, delta: float):
-    """Off-policy sequence masking: drop a whole sequence when A<0 and its mean KL(old‖new) > delta.
+    """Off-policy sequence masking: a token is dropped when ITS advantage is negative and the mean KL(old‖new) of its
+    sequence exceeds delta (per-token test on the advantage, per-sequence test on the KL; with GRPO's constant advantage
+    that drops whole sequences, with GAE advantages only the negative tokens — reference: loss/hub/math_utils.py:183-222).
 
-    Returns (keep mask [R] float, fraction of sequences clipped)."""
-    seq_kl = segment_sum((old_log_probs.float() - log_probs.float()) * mask, seq_ids, num_seqs) / \
-        segment_sum(mask, seq_ids, num_seqs).clamp_min(1.0)
-    seq_adv = segment_sum(advantages.float() * mask, seq_ids, num_seqs)
-    drop = (seq_kl > delta) & (seq_adv < 0)
-    return (~drop).float()[seq_ids], drop.float().mean()
+    Returns (keep mask [R] float, Σ over sequences of the dropped-token fraction ÷ number of sequences)."""
+    n_tok = segment_sum(mask, seq_ids, num_seqs).clamp_min(1.0)
+    seq_kl = segment_sum((old_log_probs.float() - log_probs.float()) * mask, seq_ids, num_seqs) / n_tok
+    drop = ((advantages.float() < 0) & (seq_kl > delta)[seq_ids]).float()
+    frac = (segment_sum(drop, seq_ids, num_seqs) / n_tok).sum() / max(num_seqs, 1)
+    return 1.0 - drop, frac
 
 
 def compute_policy_loss(ppo_kl, advantages, eps_clip: float, eps_clip_high: float, eps_clip_c: float | None = None):

@@ -183,7 +183,7 @@ def connect(updater, host: str = "127.0.0.1", port: int = 29600, backend: str | 
 def broadcast_buckets(updater, group_name: str = "weight_sync") -> int:
     """Stream every bucket: all trainer ranks take part in the shard gathers, rank 0 alone talks to the engines."""
     args = updater.args
-    packed = getattr(args, "update_weight_transfer_mode", "") == "broadcast_packed" or getattr(args, "broadcast_packed", False)
+    packed = getattr(updater, "packed", False) or getattr(args, "broadcast_packed", False)
     leader = updater._is_leader()
     pg = get_group(group_name)
     if leader and pg is None:

@@ -16,8 +16,14 @@ Transfer protocols (`--update-weight-transfer-mode`):
 * `broadcast` HF-named buckets broadcast from trainer rank 0 over a process group that includes remote
             engine processes (reference protocols/broadcast.py:21-208); HTTP engines are told names,
             dtypes and shapes first.
-* `disk`    HF safetensors snapshot + `update_weights_from_disk` (reference protocols/delta.py, simplified
-            to full snapshots; deltas are computed by `miles_b200.weight_update.delta`).
+* `disk`    HF safetensors snapshot + `update_weights_from_disk`.
+* `delta`   per-version XOR deltas on shared storage written by `weight_update.delta.DeltaWriter`; in-process engines
+            follow with a `DeltaReader`, remote ones load the version directory (reference protocols/delta.py:69-470).
+
+Command-line names (`--update-weight-transfer-mode`) map onto these: `broadcast_packed` = `broadcast` with flattened
+buckets, `cuda_ipc` = `tensor` (same-process hand-off of device tensors: no handle serialisation is needed), `p2p` =
+`nvlink` (peer-memory stores are the point-to-point transfer engine of one NVSwitch box; engines in other processes or on
+other boxes are refused with a message that names `broadcast`), `delta` = `delta`.
 """
 from __future__ import annotations
 
@@ -43,8 +49,21 @@ class WeightUpdater:
                 mode = "nvlink"
             else:
                 mode = "tensor"
-        self.mode = mode
+        self.packed = bool(getattr(args, "broadcast_packed", False))
+        if mode not in CLI_MODES:
+            raise ValueError(f"unknown weight transfer mode {mode!r}; choose one of {sorted(CLI_MODES)}")
+        impl = CLI_MODES[mode]
+        if mode == "broadcast_packed":
+            self.packed = True
+        if mode == "p2p" and not all(hasattr(e, "model") for e in self.engines):
+            raise ValueError("--update-weight-transfer-mode p2p writes into the engine's buffers through peer memory and needs "
+                             "the engine in this process; use broadcast for engines behind HTTP")
+        assert hasattr(self, f"_send_{impl}"), impl
+        self.cli_mode = mode
+        self.mode = impl
         self.quant = quant
+        self._delta_writer = None
+        self._delta_readers: dict[int, Any] = {}
         self.last_seconds = 0.0
         self.connected_engines_hash = None
 
@@ -64,9 +83,17 @@ class WeightUpdater:
             e.flush_cache()
         self._barrier()
         t1 = time.perf_counter()
-        nbytes = getattr(self, f"_send_{self.mode}")()
-        if self.actor.device.type == "cuda":
-            torch.cuda.synchronize()
+        ok = False
+        try:
+            nbytes = getattr(self, f"_send_{self.mode}")()
+            if self.actor.device.type == "cuda":
+                torch.cuda.synchronize()
+            ok = True
+        finally:
+            # a failed transfer must not leave the engines paused: they resume on the version they hold
+            if not ok:
+                for e in self.engines:
+                    e.continue_generation()
         self._barrier()
         t2 = time.perf_counter()
         for e in self.engines:
@@ -128,6 +155,34 @@ class WeightUpdater:
             e.update_weights_from_disk(d)
         return sum(p.numel() * p.element_size() for p in self.actor.model.parameters())
 
+    def _send_delta(self) -> int:
+        import os
+        import tempfile
+
+        from .delta import DeltaReader, DeltaWriter
+
+        root = getattr(self.args, "update_weight_disk_dir", None) or getattr(self, "_delta_root", None)
+        if root is None:
+            root = self._delta_root = tempfile.mkdtemp(prefix="miles_delta_")
+        version = self.actor.weight_version
+        named = ((n, t) for bucket in iter_hf_weights(self.actor, bucket_bytes=None, quant=self.quant) for n, t in bucket)
+        nbytes = 0
+        if self._is_leader():
+            if self._delta_writer is None:
+                self._delta_writer = DeltaWriter(root, full_every=getattr(self.args, "update_weight_delta_full_every", 10))
+            nbytes = self._delta_writer.publish(version, named).get("stored_bytes", 0)
+        else:
+            for _ in named:           # the shard gathers inside the iterator are collective
+                pass
+        self._barrier()
+        for i, e in enumerate(self.engines):
+            if hasattr(e, "model"):
+                rd = self._delta_readers.setdefault(i, DeltaReader(root))
+                e.update_weights_from_tensor(list(rd.update_to(version).items()))
+            else:
+                e.update_weights_from_disk(os.path.join(root, f"v{version}"))
+        return nbytes
+
     # ---- verification --------------------------------------------------------------------
     def check_equal(self):
         """Engine-side tensor compare (`--check-weight-update-equal`)."""
@@ -138,6 +193,11 @@ class WeightUpdater:
             for n, p in e.model.named_parameters():
                 if n in mine and not torch.equal(p.data, mine[n].data):
                     raise AssertionError(f"weight {n} differs between trainer and engine after update")
+
+
+# command-line name → protocol implemented here
+CLI_MODES = {"alias": "alias", "nvlink": "nvlink", "tensor": "tensor", "broadcast": "broadcast", "disk": "disk", "delta": "delta",
+             "broadcast_packed": "broadcast", "cuda_ipc": "tensor", "p2p": "nvlink"}
 
 
 def _same_layout(engine, actor) -> bool:
