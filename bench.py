@@ -203,7 +203,8 @@ def main():
         engines = [engine]
 
     Rollout.executor = executor
-    counters = {"tokens": 0, "h2d": 0, "d2h": 0, "sync_s": 0.0, "rollout_s": 0.0, "train_s": 0.0}
+    counters = {"tokens": 0, "gen_tokens": 0, "h2d": 0, "d2h": 0, "sync_s": 0.0, "rollout_s": 0.0, "train_s": 0.0}
+    from miles_b200.train import data as train_data
 
     stall_s = int(os.environ.get("MILES_STALL_DUMP_S", "0"))
 
@@ -231,13 +232,17 @@ def main():
         info = update_weights(args, actor, Rollout, updater)
         t3 = time.perf_counter()
         counters["tokens"] += int(pack.metrics["rollout/total_tokens"])
+        counters["gen_tokens"] += int(pack.metrics.get("rollout/response_tokens", 0))
         counters["rollout_s"] += t1 - t0
         counters["train_s"] += t2 - t1
         counters["sync_s"] += t3 - t2
-        # host→device: prompt ids + per-step decode inputs; device→host: sampled ids/log-probs + loss metrics
-        counters["h2d"] += engine.stats.get("h2d_bytes", 0) + sum(len(t) for t in shard["tokens"]) * 4 * 3
+        # counted where the copies are made: the engine's prefill inputs, per-decode-step row state and sampled ids /
+        # log-probs / routed experts (pinned buffers of the decode runner); the trainer's packed micro-batches (pinned
+        # staging, `train/data.to_device`); the loss metrics read back at the end of the step
+        counters["h2d"] += engine.stats.get("h2d_bytes", 0) + train_data.TRANSFER["h2d_bytes"]
         counters["d2h"] += engine.stats.get("d2h_bytes", 0) + 4 * len(metrics)
         engine.stats["h2d_bytes"] = engine.stats["d2h_bytes"] = 0
+        train_data.TRANSFER["h2d_bytes"] = 0
         counters["engine"] = {k: (round(v, 3) if isinstance(v, float) else v) for k, v in engine.stats.items()}
         return metrics
 
@@ -277,6 +282,7 @@ def main():
     dev_ms, wall_ms = float(t[0]), float(t[1])
     # executor.get gathers all ranks' samples, so `tokens` already counts the whole job
     total_tokens = counters["tokens"]
+    gen_tokens = counters["gen_tokens"]
     err = K.check_error_flag()
     if rank == 0:
         value = total_tokens / (dev_ms / 1e3)
@@ -305,6 +311,8 @@ def main():
             "breakdown_s_per_step": {"rollout": counters["rollout_s"] / a.steps, "train": counters["train_s"] / a.steps,
                                      "weight_sync": counters["sync_s"] / a.steps},
             "tokens_per_step": total_tokens // a.steps, "kernel_error_flag": err,
+            # the reference's perf/tokens_per_gpu_per_sec counts response tokens only: the same quantity for the whole job
+            "generated_tokens_per_s": gen_tokens / (dev_ms / 1e3), "generated_tokens_per_step": gen_tokens // a.steps,
             "engine_stats_rank0": counters.get("engine"),
         }
         print(json.dumps(out))

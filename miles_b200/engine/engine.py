@@ -58,6 +58,8 @@ class Request:
     bt_len: int = 0
     logprob_start_len: int = -1    # ≥ 0: also return log-probs of the input tokens from this position on (scoring)
     input_logprobs: list[float] | None = None
+    leader: Any = None             # request of the same prefill batch with identical tokens whose prompt KV this one shares
+    cached_tokens: int = 0         # prompt tokens whose KV was shared instead of recomputed
 
     @property
     def all_ids(self) -> list[int]:
@@ -73,7 +75,7 @@ class Request:
             "finish_reason": self.finish_reason,
             "prompt_tokens": len(self.input_ids),
             "completion_tokens": len(self.output_ids),
-            "cached_tokens": 0,
+            "cached_tokens": self.cached_tokens,
             "weight_version": str(self.weight_versions[-1][0]) if self.weight_versions else str(engine.weight_version),
             "weight_version_spans": self.weight_versions,
         }
@@ -98,7 +100,8 @@ class Engine:
                  device="cpu", dtype=torch.bfloat16, num_blocks: int | None = None, block_size: int | None = None,
                  mem_fraction_static: float = 0.7, max_running_requests: int = 512, max_prefill_tokens: int = 16384,
                  max_context_len: int | None = None, eos_token_ids: list[int] | None = None, tokenizer=None,
-                 seed: int = 0, use_cuda_graph: bool = True, record_routing: bool | None = None):
+                 seed: int = 0, use_cuda_graph: bool = True, record_routing: bool | None = None,
+                 share_prompt_kv: bool = True):
         self.cfg = cfg
         self.ps = ps or ParallelState.single()
         self.device = torch.device(device)
@@ -112,6 +115,9 @@ class Engine:
         self.eos_token_ids = set(eos_token_ids or [])
         self.tokenizer = tokenizer
         self.mem_fraction_static = mem_fraction_static
+        # requests of one prefill batch with identical tokens (the n samples of a prompt) run the prompt once: the full KV
+        # blocks are shared by reference count, the partial last block is copied, the first token is sampled per request
+        self.share_prompt_kv = share_prompt_kv
         self.use_cuda_graph = use_cuda_graph and self.device.type == "cuda"
         hkv = cfg.num_kv_heads // self.ps.tp_size
         if num_blocks is None:
@@ -466,27 +472,48 @@ class Engine:
         self._step_count += 1
         return True
 
+    def check_fabric(self):
+        """Raise if a peer-memory kernel of this process gave up a bounded wait (the step that followed is garbage)."""
+        fab = getattr(self.ps, "fabric", None)
+        if fab is not None:
+            fab.check()
+
     def begin_rollout(self):
         self.local_done = False
         self.global_done = False
+        fab = getattr(self.ps, "fabric", None)
+        if fab is not None:
+            fab.phase_barrier(self.lockstep_group)      # host skew is absorbed here, not in a kernel's bounded wait
         if self.runner is not None and self.lockstep_group is not None and self.kv.allocated:
             self.runner.warmup()
 
     def finish_rollout(self):
+        if not self.local_done:
+            self.check_fabric()
         self.local_done = True
 
     def _schedule_prefill(self) -> list[Request]:
         batch, tokens = [], 0
+        leaders: dict[tuple, Request] = {}
+        share = self.share_prompt_kv and not self.stateless
         while self.waiting and len(self.running) + len(batch) < self.max_running:
             r = self.waiting[0]
             n = len(r.all_ids)
-            if batch and tokens + n > self.max_prefill_tokens:
-                break
+            key = None
+            lead = None
+            if share and r.logprob_start_len < 0:
+                key = (n, hash(tuple(r.all_ids)))
+                lead = leaders.get(key)
+                if lead is not None and lead.all_ids != r.all_ids:
+                    lead = None
             need = self._blocks_needed(n + 1)
-            # keep headroom so running requests can still grow by one block each
-            if need + len(self.running) > self.allocator.num_free and (self.running or batch):
+            shared = (n // self.block_size) if lead is not None else 0      # full blocks of the leader's prompt
+            if lead is None and batch and tokens + n > self.max_prefill_tokens:
                 break
-            blocks = self.allocator.alloc(need)
+            # keep headroom so running requests can still grow by one block each
+            if (need - shared) + len(self.running) > self.allocator.num_free and (self.running or batch):
+                break
+            blocks = self.allocator.alloc(need - shared)
             if blocks is None:
                 if not self.running and not batch:
                     self.waiting.popleft()
@@ -494,9 +521,18 @@ class Engine:
                     continue
                 break
             self.waiting.popleft()
-            r.blocks = blocks
+            if lead is not None:
+                self.allocator.share(lead.blocks[:shared])
+                r.blocks = lead.blocks[:shared] + blocks
+                r.leader = lead
+                r.cached_tokens = n
+            else:
+                r.blocks = blocks
+                r.leader = None
+                tokens += n
+                if key is not None:
+                    leaders[key] = r
             batch.append(r)
-            tokens += n
         return batch
 
     def _ensure_decode_blocks(self) -> bool:
@@ -557,8 +593,11 @@ class Engine:
         return total
 
     def _run_prefill(self, batch: list[Request]):
+        """Prefill the unique sequences of the batch; followers (identical tokens, see `_schedule_prefill`) take their
+        leader's prompt KV — shared full blocks, a copy of the partial last block — and its last-position logits."""
+        lead_reqs = [r for r in batch if r.leader is None]
         toks, pos, slots, cu = [], [], [], [0]
-        for r in batch:
+        for r in lead_reqs:
             ids = r.all_ids
             toks += ids
             pos += list(range(len(ids)))
@@ -569,10 +608,11 @@ class Engine:
         meta = ForwardMeta(
             positions=torch.tensor(pos, dtype=torch.int32, device=dev),
             cu_seqlens=torch.tensor(cu, dtype=torch.int32, device=dev),
-            max_seqlen=max((len(r.all_ids) for r in batch), default=0),
+            max_seqlen=max((len(r.all_ids) for r in lead_reqs), default=0),
             kv_cache=None if self.stateless else self.kv.layers,
             slot_mapping=None if self.stateless else torch.tensor(slots, dtype=torch.int64, device=dev),
             record_topk=record, lora_slots=self._lora_slots(len(toks)))
+        self.stats["h2d_bytes"] = self.stats.get("h2d_bytes", 0) + 4 * len(toks) * 2 + 4 * len(cu) + 8 * len(slots)
         hidden = self.model(torch.tensor(toks, dtype=torch.int32, device=dev), meta)
         if not batch:
             return
@@ -580,7 +620,9 @@ class Engine:
         last = torch.tensor([c - 1 for c in cu[1:]], dtype=torch.int64, device=dev)
         logits = self.model.logits(hidden[last])
         self.stats["prefill_tokens"] += len(toks)
-        for r, a, b in zip(batch, cu[:-1], cu[1:]):
+        span = {id(r): (a, b) for r, a, b in zip(lead_reqs, cu[:-1], cu[1:])}
+        lead_row = {id(r): i for i, r in enumerate(lead_reqs)}
+        for r, a, b in zip(lead_reqs, cu[:-1], cu[1:]):
             if r.logprob_start_len >= 0 and r.input_logprobs is None and r.retractions == 0:
                 # score the prompt: row p predicts token p+1 (temperature 1, the teacher / reference distribution)
                 n_in = len(r.input_ids)
@@ -589,21 +631,50 @@ class Engine:
                 tgt = torch.tensor(r.input_ids[lo + 1:n_in], dtype=torch.int64, device=dev)
                 lp, _ = self.model.log_probs(hidden[rows], tgt) if len(tgt) else (torch.empty(0), None)
                 r.input_logprobs = [float(x) for x in lp.float().tolist()]
+        followers = [r for r in batch if r.leader is not None]
+        if followers:
+            self._copy_tail_blocks(followers)
+            self.stats["shared_prompt_tokens"] = self.stats.get("shared_prompt_tokens", 0) + sum(r.cached_tokens for r in followers)
         if record is not None:
             rec = torch.stack(record, dim=1).cpu().numpy().astype(np.int32)  # [T, L_moe, k]
-            for r, a, b in zip(batch, cu[:-1], cu[1:]):
+            self.stats["d2h_bytes"] = self.stats.get("d2h_bytes", 0) + rec.nbytes
+            for r in batch:
                 if r.return_routed_experts:
+                    a, b = span[id(r.leader if r.leader is not None else r)]
                     # after a retraction the request already holds rows for its first num-recorded tokens
                     have = sum(x.shape[0] for x in r.routed)
                     r.routed.append(rec[a + have:b])
         for r in batch:
             r.num_cached = len(r.all_ids)
+        if followers:
+            rows = torch.tensor([lead_row[id(r.leader if r.leader is not None else r)] for r in batch], dtype=torch.int64, device=dev)
+            logits = logits[rows]
+        for r in batch:
+            r.leader = None
         self._sample_and_append(batch, logits)
         for r in batch:
             if not r.finished and r not in self.running:
                 self.running.append(r)
                 if self.runner is not None:
                     self.runner.attach(r)
+
+    def _copy_tail_blocks(self, followers: list[Request]):
+        """Followers own their last (partial) prompt block: copy the leader's partial block into it, all followers and
+        all layers' K and V in one indexed copy per tensor."""
+        bs = self.block_size
+        src, dst = [], []
+        for r in followers:
+            n = len(r.all_ids)
+            if n % bs:
+                src.append(r.leader.blocks[n // bs])
+                dst.append(r.blocks[n // bs])
+        if not src:
+            return
+        s_idx = torch.tensor(src, dtype=torch.int64, device=self.device)
+        d_idx = torch.tensor(dst, dtype=torch.int64, device=self.device)
+        for kc, vc in self.kv.layers.values():
+            kc[d_idx] = kc[s_idx]
+            vc[d_idx] = vc[s_idx]
 
     def _run_decode(self):
         if self.stateless:
@@ -680,5 +751,7 @@ class Engine:
                              device=dev)
         tok, lp = sample(logits.float(), temp, top_p, top_k, seeds=seeds, step=0)
         tok_l, lp_l = tok.tolist(), lp.tolist()
+        self.stats["h2d_bytes"] = self.stats.get("h2d_bytes", 0) + 24 * len(reqs)
+        self.stats["d2h_bytes"] = self.stats.get("d2h_bytes", 0) + 12 * len(reqs)
         for r, t, l in zip(reqs, tok_l, lp_l):
             self._append_token(r, int(t), float(l))

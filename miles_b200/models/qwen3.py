@@ -128,6 +128,8 @@ class Attention(nn.Module):
             o = ops.paged_attention(q, kc, vc, meta.block_table, meta.seq_lens, q_lens=meta.q_lens,
                                     max_q_len=meta.max_seqlen)
         o = o.reshape(T, self.hq * self.d)
+        if lora is None and self.ps.defer_allreduce(o):
+            return self.ps.row_linear_partial(o, self.wo)             # reduced inside the next add + RMSNorm kernel
         out = self.ps.row_linear(o, self.wo)                          # reduce-scatter fused on GPU
         if lora is not None and "wo" in lora:
             out = out + lora["wo"](o, meta)
@@ -151,6 +153,8 @@ class DenseFFN(nn.Module):
         if lora is not None and "w13" in lora:
             h13 = h13 + lora["w13"](x, meta)
         h = ops.swiglu(h13)
+        if lora is None and self.ps.defer_allreduce(h):
+            return self.ps.row_linear_partial(h, self.w2)             # reduced inside the next add + RMSNorm kernel
         out = self.ps.row_linear(h, self.w2)
         if lora is not None and "w2" in lora:
             out = out + lora["w2"](h, meta)
@@ -198,6 +202,14 @@ class MoEFFN(nn.Module):
         return self.ps.moe_ffn(x, self.w13, self.w2, w, idx, self.cfg.num_experts)
 
 
+def add_rmsnorm_reducing(ps, x, residual, w, eps):
+    """add + RMSNorm; when `x` is a tensor-parallel partial sum (see `ParallelState.defer_allreduce`) the all-reduce over
+    the TP ranks happens inside the same kernel, reading the peers' partial rows over NVLink."""
+    if getattr(x, "_tp_partial", False):
+        return ps.allreduce_add_rmsnorm(x, residual, w, eps)
+    return ops.add_rmsnorm(x, residual, w, eps)
+
+
 class DecoderLayer(nn.Module):
     def __init__(self, cfg, ps, dtype, device, gen, layer: int, moe_index: int):
         super().__init__()
@@ -227,9 +239,9 @@ class DecoderLayer(nn.Module):
         if (self.attn.ps.tp_size == 1 and ops.few_token_decode(x, self.attn.wqkv) and getattr(self.attn, "lora", None) is None
                 and getattr(self.mlp, "lora", None) is None):
             return self._forward_few_tokens(x, residual, meta)
-        h, residual = ops.add_rmsnorm(x, residual, self.ln1, self.eps)
+        h, residual = add_rmsnorm_reducing(self.attn.ps, x, residual, self.ln1, self.eps)
         h = self.attn(h, meta, self.layer)
-        h, residual = ops.add_rmsnorm(h, residual, self.ln2, self.eps)
+        h, residual = add_rmsnorm_reducing(self.attn.ps, h, residual, self.ln2, self.eps)
         h = self.mlp(h, meta, self.layer)
         return h, residual
 
@@ -287,8 +299,11 @@ class Qwen3Model(nn.Module):
             else:
                 x, residual = layer(x, residual, meta)
         if not self.has_head:
+            if getattr(x, "_tp_partial", False):       # a pipeline stage boundary needs the reduced value
+                x = self.ps.allreduce_add_rmsnorm(x, residual, self.layers[-1].ln2, self.cfg.rms_eps)[1]
+                return x
             return x if residual is None else x + residual
-        h, _ = ops.add_rmsnorm(x, residual, self.norm, self.cfg.rms_eps)
+        h, _ = add_rmsnorm_reducing(self.ps, x, residual, self.norm, self.cfg.rms_eps)
         return h
 
     def global_name(self, name: str) -> str:

@@ -147,12 +147,20 @@ void gather_rows(const at::Tensor& src_ptrs, int64_t world, at::Tensor& out) {
         "mb_gather_rows");
 }
 
-void ag_gemm(const at::Tensor& x_ptrs, const at::Tensor& W, at::Tensor& Y, int64_t rows_per_rank, int64_t rank, int64_t world,
-             const at::Tensor& flag_ptrs, int64_t channel, int64_t epoch, at::Tensor& err) {
+void ag_gemm(const at::Tensor& xg_ptrs, const at::Tensor& W, at::Tensor& Y, at::Tensor& block_counters, int64_t rows_per_rank,
+             int64_t rank, int64_t world, const at::Tensor& flag_ptrs, int64_t channel, int64_t epoch, at::Tensor& err) {
   c10::cuda::CUDAGuard g(Y.device());
-  check(mb_ag_gemm(lptr(x_ptrs), W.data_ptr(), Y.data_ptr(), rows_per_rank, W.size(0), W.size(1), rank, world, lptr(flag_ptrs), channel,
-                   epoch, err.data_ptr<int>(), cur_stream()),
+  TORCH_CHECK(block_counters.numel() * 128 >= rows_per_rank * world, "block_counters too small");
+  check(mb_ag_gemm(lptr(xg_ptrs), W.data_ptr(), Y.data_ptr(), block_counters.data_ptr<int>(), rows_per_rank, W.size(0), W.size(1), rank,
+                   world, lptr(flag_ptrs), channel, epoch, err.data_ptr<int>(), cur_stream()),
         "mb_ag_gemm");
+}
+
+// error flag address + peer wait limit for the kernels that talk to peers (0 keeps the current limit)
+void fabric_configure(at::Tensor& err, int64_t wait_ns) {
+  c10::cuda::CUDAGuard g(err.device());
+  check(mb_comm_configure(err.data_ptr<int>(), static_cast<unsigned long long>(wait_ns)), "mb_comm_configure");
+  check(mb_gemm_comm_configure(err.data_ptr<int>(), static_cast<unsigned long long>(wait_ns)), "mb_gemm_comm_configure");
 }
 
 void gemm_rs(const at::Tensor& X, const at::Tensor& W, const at::Tensor& partial_ptrs, at::Tensor& out, at::Tensor& counters,
@@ -180,6 +188,7 @@ void register_fabric(pybind11::module& m) {
   m.def("multi_copy", &multi_copy);
   m.def("multi_mxfp8", &multi_mxfp8);
   m.def("ag_gemm", &ag_gemm);
+  m.def("fabric_configure", &fabric_configure);
   m.def("gemm_rs", &gemm_rs);
   m.def("sum_rows", &sum_rows);
   m.def("gather_rows", &gather_rows);

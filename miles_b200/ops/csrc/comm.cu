@@ -63,6 +63,7 @@ __device__ __forceinline__ uint4 pack8(const float (&f)[8]) {
 __global__ void __launch_bounds__(256) ar_add_rmsnorm_kernel(PeerPtrs partials, int world, const bf16* __restrict__ residual,
                                                              const bf16* __restrict__ w, bf16* __restrict__ y, bf16* __restrict__ res_out,
                                                              int H, float eps) {
+  if (fabric_poisoned()) return;
   __shared__ float sh[8];
   const long long row = blockIdx.x;
   const int nvec = H / 8;
@@ -114,6 +115,7 @@ __global__ void __launch_bounds__(256) ar_add_rmsnorm_kernel(PeerPtrs partials, 
 // rank also counts, e.g. tensor-parallel replicas; nullptr → 1)
 __global__ void __launch_bounds__(256) rs_reduce_sqnorm_kernel(PeerPtrs grads, int world, int rank, long long lo, long long hi,
                                                                const float* __restrict__ norm_weight, float* __restrict__ sqnorm) {
+  if (fabric_poisoned()) return;
   __shared__ float sh[8];
   float ss = 0.f;
   float* mine = reinterpret_cast<float*>(grads.p[rank]);
@@ -139,6 +141,7 @@ __global__ void __launch_bounds__(256) adam_allgather_kernel(float* __restrict__
                                                              const float* __restrict__ decay_mask, const float* __restrict__ sqnorm,
                                                              float clip, PeerPtrs params, int world, long long lo, long long n, float lr,
                                                              float b1, float b2, float eps, float wd, float bc1, float bc2) {
+  if (fabric_poisoned()) return;
   float scale = 1.f;
   if (clip > 0.f && sqnorm != nullptr) scale = fminf(1.f, clip / (sqrtf(*sqnorm) + 1e-6f));
   for (long long i = (blockIdx.x * 256ll + threadIdx.x) * 4; i < n; i += static_cast<long long>(gridDim.x) * 1024) {
@@ -178,6 +181,7 @@ __global__ void __launch_bounds__(256) adam_allgather_kernel(float* __restrict__
 __global__ void __launch_bounds__(256) moe_dispatch_kernel(const bf16* __restrict__ x, const int* __restrict__ topk_idx, long long n_pairs,
                                                            int k, int H, int e_local, int rank, PeerPtrs recv_x, PeerPtrs recv_meta,
                                                            PeerPtrs counters, int capacity, int* __restrict__ sent_row, int* err) {
+  if (fabric_poisoned()) return;
   const int lane = threadIdx.x & 31;
   const int nvec = H / 8;
   for (long long pair = (blockIdx.x * 256ll + threadIdx.x) >> 5; pair < n_pairs; pair += (static_cast<long long>(gridDim.x) * 256) >> 5) {
@@ -210,6 +214,7 @@ __global__ void __launch_bounds__(256) moe_dispatch_kernel(const bf16* __restric
 __global__ void __launch_bounds__(256) moe_scatter_known_kernel(const bf16* __restrict__ rows_in, int src_by_pair,
                                                                 const int* __restrict__ topk_idx, const int* __restrict__ sent_row,
                                                                 long long n_pairs, int k, int H, int e_local, PeerPtrs recv_x) {
+  if (fabric_poisoned()) return;
   const int lane = threadIdx.x & 31;
   const int nvec = H / 8;
   for (long long pair = (blockIdx.x * 256ll + threadIdx.x) >> 5; pair < n_pairs; pair += (static_cast<long long>(gridDim.x) * 256) >> 5) {
@@ -227,6 +232,7 @@ __global__ void __launch_bounds__(256) moe_scatter_known_kernel(const bf16* __re
 __global__ void __launch_bounds__(256) moe_return_kernel(const bf16* __restrict__ y_perm, const int* __restrict__ row_src,
                                                          const int4* __restrict__ meta, const int* __restrict__ seg_offsets, int E,
                                                          int H, int max_rows, PeerPtrs ret) {
+  if (fabric_poisoned()) return;
   const int lane = threadIdx.x & 31;
   const int nvec = H / 8;
   const int total = min(seg_offsets[E], max_rows);
@@ -262,6 +268,7 @@ __global__ void recv_expert_ids_kernel(const int4* __restrict__ meta, int* __res
 // A rank whose vocabulary shard does not contain the target leaves t = 0 and contributes nothing to it.
 __global__ void stats_merge_kernel(PeerPtrs stats, int world, long long R, float* __restrict__ logp, float* __restrict__ ent,
                                    float* __restrict__ lse) {
+  if (fabric_poisoned()) return;
   const long long r = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x;
   if (r >= R) return;
   float M = -INFINITY, S = 0.f, Es = 0.f, T = 0.f;
@@ -282,6 +289,7 @@ __global__ void stats_merge_kernel(PeerPtrs stats, int world, long long R, float
 
 // out[i] = Σ_r src_r[i] (bf16, fp32 accumulate): every rank reads the same-shaped block from each peer.
 __global__ void __launch_bounds__(256) sum_rows_kernel(PeerPtrs src, int world, bf16* __restrict__ out, long long nvec) {
+  if (fabric_poisoned()) return;
   for (long long v = blockIdx.x * 256ll + threadIdx.x; v < nvec; v += static_cast<long long>(gridDim.x) * 256) {
     float acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
     for (int r = 0; r < world; ++r) {
@@ -296,6 +304,7 @@ __global__ void __launch_bounds__(256) sum_rows_kernel(PeerPtrs src, int world, 
 
 // out[r·n + i] = src_r[i]: all-gather by peer loads (16-byte vectors), n = elements per rank / 8.
 __global__ void __launch_bounds__(256) gather_rows_kernel(PeerPtrs src, int world, uint4* __restrict__ out, long long nvec_per_rank) {
+  if (fabric_poisoned()) return;
   const long long total = nvec_per_rank * world;
   for (long long v = blockIdx.x * 256ll + threadIdx.x; v < total; v += static_cast<long long>(gridDim.x) * 256) {
     const int r = static_cast<int>(v / nvec_per_rank);
@@ -319,6 +328,8 @@ static int blocks_for(long long items, int per_block, int cap = 148 * 4) {
 }  // namespace mb
 
 using namespace mb;
+
+MB_DEFINE_FABRIC_CONFIGURE(mb_comm_configure)
 
 extern "C" int mb_barrier(const long long* flag_ptrs, int rank, int world, int channel, int* epochs, int* err, cudaStream_t s) {
   if (world > kMaxRanks) return -1;

@@ -8,7 +8,18 @@
 namespace mb {
 
 static constexpr int kMaxRanks = 8;
-static constexpr unsigned long long kPeerWaitLimitNs = 1000000000ull;  // 1 s, then give up and raise the error flag
+// How long a wait on a peer may poll before it gives up and raises the error flag, and where that flag lives.  Both are
+// per translation unit (every .cu that includes this header has its own copy) and are set from the host with the unit's
+// `*_configure` call; the default suits tests, production sets a few seconds (`Fabric.configure`).
+static __device__ unsigned long long g_peer_wait_limit_ns = 2000000000ull;
+static __device__ int* g_fabric_err = nullptr;
+
+// True once any kernel of this process raised the error flag: kernels that would consume what a timed-out wait was
+// guarding return at once instead (their outputs are then undefined; the host raises when it polls the flag).
+__device__ __forceinline__ bool fabric_poisoned() {
+  int* e = g_fabric_err;
+  return e != nullptr && *reinterpret_cast<volatile int*>(e) != 0;
+}
 
 struct PeerPtrs {
   void* p[kMaxRanks];
@@ -34,15 +45,16 @@ __device__ __forceinline__ int ld_relaxed_sys(const int* addr) {
   return v;
 }
 
-// Wait until *addr >= target (acquire).  Returns false after kPeerWaitLimitNs.
+// Wait until *addr >= target (acquire).  Returns false after g_peer_wait_limit_ns.
 __device__ __forceinline__ bool wait_flag_ge(const int* addr, int target) {
   unsigned long long t0 = 0;
+  const unsigned long long limit = g_peer_wait_limit_ns;
   for (unsigned i = 0;; ++i) {
     if (ld_acquire_sys(addr) >= target) return true;
     if ((i & 255u) == 255u) {
       const unsigned long long now = gtimer_ns();
       if (t0 == 0) t0 = now;
-      else if (now - t0 > kPeerWaitLimitNs) return false;
+      else if (now - t0 > limit) return false;
     }
   }
 }
@@ -60,10 +72,20 @@ __device__ __forceinline__ bool cross_rank_barrier(const PeerPtrs& flags, int ra
     int* remote = reinterpret_cast<int*>(flags.p[threadIdx.x]) + channel * kMaxRanks + rank;
     st_release_sys(remote, epoch);
     const int* mine = reinterpret_cast<const int*>(flags.p[rank]) + channel * kMaxRanks + threadIdx.x;
-    if (!wait_flag_ge(mine, epoch)) ok_sh = 0;
+    // a poisoned process still publishes its epoch (peers are not made to wait for it) but waits for nobody
+    if (!fabric_poisoned() && !wait_flag_ge(mine, epoch)) ok_sh = 0;
   }
   __syncthreads();
   return ok_sh != 0;
 }
+
+// Host side of the two settings above for the including translation unit.
+#define MB_DEFINE_FABRIC_CONFIGURE(fn_name)                                                                        \
+  extern "C" int fn_name(int* err, unsigned long long wait_ns) {                                                  \
+    cudaError_t e = cudaMemcpyToSymbol(mb::g_fabric_err, &err, sizeof(err));                                      \
+    if (e != cudaSuccess) return static_cast<int>(e);                                                             \
+    if (wait_ns) e = cudaMemcpyToSymbol(mb::g_peer_wait_limit_ns, &wait_ns, sizeof(wait_ns));                     \
+    return static_cast<int>(e);                                                                                   \
+  }
 
 }  // namespace mb

@@ -1,17 +1,21 @@
 // Tensor-parallel GEMMs fused with their sequence-parallel collective, one kernel each (tcgen05 + TMA + NVLink peers):
 //
-//  all-gather → GEMM   y[T, N] = gather_r(x_r[T/w, K]) · Wᵀ.  The A operand has one tensor map per rank over that rank's
-//      staged x (peer memory for r ≠ rank).  Tiles are visited owner by owner starting with this rank, the TMA producer
-//      waits (bounded) for the owner's "staged" flag the first time it needs that owner, then loads the tile straight from
-//      the peer's memory into shared memory — no gathered copy of x is ever written.  (Plain TMA loads, no multicast.)
+//  all-gather → GEMM   y[T, N] = gather_r(x_r[T/w, K]) · Wᵀ.  Every rank keeps a symmetric [T, K] buffer whose own row
+//      block holds its x.  Four copy warps per CTA bring each remote row block over NVLink ONCE into the same rows of the
+//      local buffer (16-byte peer loads, several in flight per thread) after the owner's "staged" flag arrived, and count
+//      finished pieces per 128-row block; the TMA producer visits this rank's blocks first, waits (bounded) for a remote
+//      block's count, then loads its tiles from LOCAL memory for every N tile.  The remote bytes cross NVLink once, not
+//      once per N tile, and later tiles hit this GPU's L2.  (Plain TMA loads from local memory, no multicast.)
 //
-//  GEMM → reduce-scatter   out[T/w, N] = Σ_r (x_r[T, K/w] · W_rᵀ)[rows of this rank].  Every rank writes its partial tiles
-//      into its own symmetric buffer, visiting destination row blocks starting with the *next* rank so that the blocks
-//      other ranks wait for are finished first; when the last tile of a destination is stored the epilogue publishes a
-//      flag to that rank.  After its tiles each CTA joins the reduction of this rank's row block, reading the partial
-//      rows of every peer with 16-byte loads once their flags have arrived.
+//  GEMM → reduce-scatter   out[T/w, N] = Σ_r (x_r[T, K/w] · W_rᵀ)[rows of this rank].  Every rank owns a symmetric buffer
+//      of `world` slots [T/w, N]; the epilogue PUSHES each finished partial tile straight into slot `rank` of the
+//      destination rank's buffer (peer stores from the registers that hold the tile), visiting destinations starting with
+//      the next rank; when the last tile for a destination is stored a flag is published to it.  After its tiles each
+//      CTA joins the reduction of this rank's row block, now a sum over LOCAL slots.  No full [T, N] partial is written
+//      locally and nothing is pulled.
 //
-// Pipeline and warp roles are those of gemm.cu (warp 0 TMA, warp 1 MMA, warps 2-5 epilogue, double-buffered TMEM).
+// Pipeline and warp roles are those of gemm.cu (warp 0 TMA, warp 1 MMA, warps 2-5 epilogue, double-buffered TMEM);
+// warps 6-9 exist only in the all-gather kernel (the copy warps).
 #include "comm.cuh"
 #include "launch.h"
 #include "ptx.cuh"
@@ -29,14 +33,14 @@ struct TmapArray {
 
 struct CommGemmParams {
   int M, N, K;
-  void* C;              // AG: y [M, N];  RS: this rank's partial buffer [M, N]
+  void* C;              // AG: y [M, N]
   long long ldc;
   int rank, world, rows_per_rank;
   PeerPtrs flags;
   int channel, epoch;
-  PeerPtrs partials;    // RS: every rank's partial buffer
+  PeerPtrs partials;    // RS: every rank's slot buffer [world, rows_per_rank, N];  AG: every rank's gathered buffer [M, K]
   void* out;            // RS: [rows_per_rank, N]
-  int* dest_counters;   // RS: [world], zero on entry
+  int* dest_counters;   // RS: [world], zero on entry;  AG: [M / 128] pieces copied per row block, zero on entry
   int* error_flag;
 };
 
@@ -50,9 +54,23 @@ struct CSmem {
 };
 
 __device__ __forceinline__ void epi_bar_sync() { asm volatile("bar.sync 1, 128;" ::: "memory"); }
+__device__ __forceinline__ void copy_bar_sync() { asm volatile("bar.sync 2, 128;" ::: "memory"); }
+__device__ __forceinline__ void fence_proxy_async_all() { asm volatile("fence.proxy.async;" ::: "memory"); }
+__device__ __forceinline__ int ld_acquire_gpu(const int* addr) {
+  int v;
+  asm volatile("ld.acquire.gpu.global.s32 %0, [%1];" : "=r"(v) : "l"(addr) : "memory");
+  return v;
+}
+__device__ __forceinline__ uint4 ld_peer16(const uint4* p) {
+  uint4 v;
+  asm volatile("ld.global.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p));
+  return v;
+}
+static constexpr int kCopyPieces = 8;        // a 128-row block is copied in 8 pieces of 16 rows
+static constexpr int kCopyThreads = 128;
 
 template <int BN, int MODE>
-__global__ void __launch_bounds__(192, 1)
+__global__ void __launch_bounds__(MODE == kAllGather ? 320 : 192, 1)
 gemm_comm_kernel(const __grid_constant__ TmapArray tmaps_a, const __grid_constant__ CUtensorMap tmap_b, CommGemmParams p) {
   using L = CSmem<BN>;
   constexpr int kStages = L::kStages;
@@ -67,6 +85,7 @@ gemm_comm_kernel(const __grid_constant__ TmapArray tmaps_a, const __grid_constan
   uint64_t* tmem_empty = tmem_full + 2;
   uint32_t* tmem_base_ptr = reinterpret_cast<uint32_t*>(tmem_empty + 2);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_base_ptr + 1);
+  volatile int* copy_go = abort_flag + 1;     // the copy warps' shared decision for the current piece
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int mb_per_rank = p.rows_per_rank / CBM;
@@ -108,19 +127,30 @@ gemm_comm_kernel(const __grid_constant__ TmapArray tmaps_a, const __grid_constan
     if (elect_one()) {
       int stage = 0;
       uint32_t phase = 0;
-      int ready_owner = p.rank;   // owners are visited in order; each needs one flag wait
+      int ready_blk = -1;         // a CTA meets the tiles of one row block consecutively (m fastest): one wait per block
       for (int t = blockIdx.x; t < total_tiles && !*abort_flag; t += gridDim.x) {
         int owner, m_blk, n_blk;
         decode(t, owner, m_blk, n_blk);
-        if (MODE == kAllGather && owner != p.rank && owner != ready_owner) {
-          if (!wait_flag_ge(my_flags + owner, p.epoch)) { *abort_flag = 1; atomicExch(p.error_flag, 11); break; }
-          fence_proxy_async();
-          ready_owner = owner;
+        if (MODE == kAllGather && owner != p.rank && m_blk != ready_blk) {
+          // the copy warps of the whole grid bring this block in; wait until all its pieces are in local memory
+          const unsigned long long limit = g_peer_wait_limit_ns + kWaitLimitNs;
+          unsigned long long t0 = 0;
+          bool ok = true;
+          for (unsigned i = 0; ld_acquire_gpu(p.dest_counters + m_blk) < kCopyPieces; ++i) {
+            if ((i & 255u) == 255u) {
+              const unsigned long long now = gtimer_ns();
+              if (t0 == 0) t0 = now;
+              else if (now - t0 > limit || *abort_flag) { ok = false; break; }
+            }
+          }
+          if (!ok) { *abort_flag = 1; atomicCAS(p.error_flag, 0, 11); break; }
+          fence_proxy_async_all();
+          ready_blk = m_blk;
         }
-        const CUtensorMap* ta = (MODE == kAllGather) ? &tmaps_a.m[owner] : &tmaps_a.m[0];
-        const int a_row = (MODE == kAllGather) ? (m_blk - owner * mb_per_rank) * CBM : m_blk * CBM;
+        const CUtensorMap* ta = &tmaps_a.m[0];
+        const int a_row = m_blk * CBM;
         for (int kb = 0; kb < k_blocks; ++kb) {
-          if (!mbar_wait(&empty_bar[stage], phase ^ 1)) { *abort_flag = 1; atomicExch(p.error_flag, 12); break; }
+          if (!mbar_wait(&empty_bar[stage], phase ^ 1)) { *abort_flag = 1; atomicCAS(p.error_flag, 0, 12); break; }
           mbar_expect_tx(&full_bar[stage], L::kStageBytes);
           tma_load_2d(smem_a + stage * L::kABytes, ta, &full_bar[stage], kb * CBK, a_row);
           tma_load_2d(smem_b + stage * L::kBBytes, &tmap_b, &full_bar[stage], kb * CBK, n_blk * BN);
@@ -134,12 +164,12 @@ gemm_comm_kernel(const __grid_constant__ TmapArray tmaps_a, const __grid_constan
       int stage = 0, acc = 0;
       uint32_t phase = 0, acc_phase = 0;
       for (int t = blockIdx.x; t < total_tiles && !*abort_flag; t += gridDim.x) {
-        if (!mbar_wait(&tmem_empty[acc], acc_phase ^ 1)) { *abort_flag = 1; atomicExch(p.error_flag, 13); break; }
+        if (!mbar_wait(&tmem_empty[acc], acc_phase ^ 1)) { *abort_flag = 1; atomicCAS(p.error_flag, 0, 13); break; }
         tc_fence_after();
         const uint32_t d_tmem = tmem_base + acc * BN;
         bool ok = true;
         for (int kb = 0; kb < k_blocks; ++kb) {
-          if (!mbar_wait(&full_bar[stage], phase)) { *abort_flag = 1; atomicExch(p.error_flag, 14); ok = false; break; }
+          if (!mbar_wait(&full_bar[stage], phase)) { *abort_flag = 1; atomicCAS(p.error_flag, 0, 14); ok = false; break; }
           tc_fence_after();
           const uint32_t a_addr = smem_u32(smem_a + stage * L::kABytes);
           const uint32_t b_addr = smem_u32(smem_b + stage * L::kBBytes);
@@ -156,6 +186,51 @@ gemm_comm_kernel(const __grid_constant__ TmapArray tmaps_a, const __grid_constan
         if (++acc == 2) { acc = 0; acc_phase ^= 1; }
       }
     }
+  } else if (MODE == kAllGather && warp >= 6) {
+    // copy warps: remote row blocks → the same rows of the local gathered buffer, owner by owner in the order the tiles
+    // need them; pieces are dealt round-robin over the grid so that every block is finished by many CTAs at once
+    const int ctid = threadIdx.x - 192;
+    const long long row_vecs = p.K / 8;                                  // 16-byte vectors per row
+    const long long piece_vecs = (CBM / kCopyPieces) * row_vecs;
+    uint4* local = reinterpret_cast<uint4*>(p.partials.p[p.rank]);
+    const int pieces_per_owner = mb_per_rank * kCopyPieces;
+    const int total_pieces = pieces_per_owner * (p.world - 1);
+    int ready_owner = -1;
+    for (int pc = blockIdx.x; pc < total_pieces; pc += gridDim.x) {
+      const int owner = (p.rank + 1 + pc / pieces_per_owner) % p.world;
+      const int rem = pc % pieces_per_owner;
+      const int m_blk = owner * mb_per_rank + rem / kCopyPieces;
+      // one thread decides for all 128 (waits for the owner's flag when a new owner starts); the others learn it behind a
+      // barrier, so that no thread can leave the loop while another still heads for a barrier
+      if (ctid == 0) {
+        bool go = !*abort_flag;
+        if (go && owner != ready_owner && !wait_flag_ge(my_flags + owner, p.epoch)) {
+          *abort_flag = 1;
+          atomicCAS(p.error_flag, 0, 17);
+          go = false;
+        }
+        *copy_go = go ? 1 : 0;
+      }
+      ready_owner = owner;
+      copy_bar_sync();
+      if (!*copy_go) break;
+      const long long base = (static_cast<long long>(m_blk) * kCopyPieces + rem % kCopyPieces) * piece_vecs;
+      const uint4* src = reinterpret_cast<const uint4*>(p.partials.p[owner]) + base;
+      uint4* dst = local + base;
+      long long v = ctid;
+      for (; v + 7 * kCopyThreads < piece_vecs; v += 8 * kCopyThreads) {
+        uint4 r[8];
+#pragma unroll
+        for (int u = 0; u < 8; ++u) r[u] = ld_peer16(src + v + u * kCopyThreads);
+#pragma unroll
+        for (int u = 0; u < 8; ++u) dst[v + u * kCopyThreads] = r[u];
+      }
+      for (; v < piece_vecs; v += kCopyThreads) dst[v] = ld_peer16(src + v);
+      fence_proxy_async_all();
+      __threadfence();
+      copy_bar_sync();
+      if (ctid == 0) atomicAdd(p.dest_counters + m_blk, 1);
+    }
   } else {
     const int q = warp & 3;
     const int etid = threadIdx.x - 64;   // 0..127 within the epilogue group
@@ -164,11 +239,15 @@ gemm_comm_kernel(const __grid_constant__ TmapArray tmaps_a, const __grid_constan
     for (int t = blockIdx.x; t < total_tiles && !*abort_flag; t += gridDim.x) {
       int owner, m_blk, n_blk;
       decode(t, owner, m_blk, n_blk);
-      if (!mbar_wait(&tmem_full[acc], acc_phase)) { *abort_flag = 1; atomicExch(p.error_flag, 15); break; }
+      if (!mbar_wait(&tmem_full[acc], acc_phase)) { *abort_flag = 1; atomicCAS(p.error_flag, 0, 15); break; }
       tc_fence_after();
       const int row = m_blk * CBM + q * 32 + lane;
       const uint32_t t_row = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + acc * BN;
-      __nv_bfloat16* c_row = reinterpret_cast<__nv_bfloat16*>(p.C) + static_cast<long long>(row) * p.ldc;
+      // RS: the tile goes into slot `rank` of the destination's buffer (peer memory unless owner == rank)
+      __nv_bfloat16* c_row = (MODE == kAllGather)
+          ? reinterpret_cast<__nv_bfloat16*>(p.C) + static_cast<long long>(row) * p.ldc
+          : reinterpret_cast<__nv_bfloat16*>(p.partials.p[owner]) +
+                (static_cast<long long>(p.rank) * p.rows_per_rank + (row - owner * p.rows_per_rank)) * p.ldc;
 #pragma unroll 1
       for (int c = 0; c < BN / 32; ++c) {
         uint32_t r[32];
@@ -212,14 +291,14 @@ gemm_comm_kernel(const __grid_constant__ TmapArray tmaps_a, const __grid_constan
       bool ok = true;
       for (int r = 0; r < p.world && ok; ++r) ok = wait_flag_ge(my_flags + r, p.epoch);
       if (!ok) {
-        atomicExch(p.error_flag, 16);
+        atomicCAS(p.error_flag, 0, 16);
       } else {
         const long long nvec = static_cast<long long>(p.rows_per_rank) * p.N / 8;
-        const long long base = static_cast<long long>(p.rank) * p.rows_per_rank * p.N / 8;
+        const uint4* slots = reinterpret_cast<const uint4*>(p.partials.p[p.rank]);
         for (long long v = blockIdx.x * 128ll + etid; v < nvec; v += static_cast<long long>(gridDim.x) * 128) {
           float accv[8] = {0, 0, 0, 0, 0, 0, 0, 0};
           for (int r = 0; r < p.world; ++r) {
-            const uint4 raw = reinterpret_cast<const uint4*>(p.partials.p[r])[base + v];
+            const uint4 raw = slots[r * nvec + v];
             const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&raw);
 #pragma unroll
             for (int i = 0; i < 4; ++i) {
@@ -268,7 +347,7 @@ static int launch_comm(const TmapArray& ta, const CUtensorMap& tb, const CommGem
     configured = true;
   }
   const int grid = tiles < sm_count() ? tiles : sm_count();
-  kern<<<grid, 192, L::kTotal, s>>>(ta, tb, p);
+  kern<<<grid, MODE == kAllGather ? 320 : 192, L::kTotal, s>>>(ta, tb, p);
   return static_cast<int>(cudaGetLastError());
 }
 
@@ -276,30 +355,37 @@ static int launch_comm(const TmapArray& ta, const CUtensorMap& tb, const CommGem
 
 using namespace mb;
 
-// x_ptrs[r]: rank r's staged x [rows_per_rank, K] (bf16, row-major) as mapped in this process.
-extern "C" int mb_ag_gemm(const long long* x_ptrs, const void* W, void* Y, int rows_per_rank, int N, int K, int rank, int world,
-                          const long long* flag_ptrs, int channel, int epoch, int* error_flag, cudaStream_t s) {
+MB_DEFINE_FABRIC_CONFIGURE(mb_gemm_comm_configure)
+
+// xg_ptrs[r]: rank r's symmetric gathered buffer [rows_per_rank·world, K] (bf16, row-major) as mapped in this process;
+// rank r has written its own x into rows [r·rows_per_rank, (r+1)·rows_per_rank) of its buffer before this launch.
+// block_counters: [rows_per_rank·world / 128] ints (zeroed here).
+extern "C" int mb_ag_gemm(const long long* xg_ptrs, const void* W, void* Y, int* block_counters, int rows_per_rank, int N, int K,
+                          int rank, int world, const long long* flag_ptrs, int channel, int epoch, int* error_flag, cudaStream_t s) {
   if (world > kMaxRanks || rows_per_rank % CBM || K % 8) return -1;
-  TmapArray ta;
-  for (int r = 0; r < world; ++r) {
-    const int rc = make_tmap_bf16_2d(&ta.m[r], reinterpret_cast<const void*>(x_ptrs[r]), rows_per_rank, K, K, CBM, CBK);
-    if (rc) return 1000 + rc;
-  }
-  for (int r = world; r < kMaxRanks; ++r) ta.m[r] = ta.m[0];
   const int M = rows_per_rank * world;
+  TmapArray ta;
+  const int rc0 = make_tmap_bf16_2d(&ta.m[0], reinterpret_cast<const void*>(xg_ptrs[rank]), M, K, K, CBM, CBK);   // LOCAL memory only
+  if (rc0) return 1000 + rc0;
+  for (int r = 1; r < kMaxRanks; ++r) ta.m[r] = ta.m[0];
   const int bn = ((M / CBM) * ((N + 255) / 256) >= sm_count()) ? 256 : 128;
   CUtensorMap tb;
   int rc = make_tmap_bf16_2d(&tb, W, N, K, K, bn, CBK);
   if (rc) return 2000 + rc;
+  cudaError_t e = cudaMemsetAsync(block_counters, 0, sizeof(int) * (M / CBM), s);
+  if (e != cudaSuccess) return static_cast<int>(e);
   CommGemmParams p{};
   p.M = M; p.N = N; p.K = K; p.C = Y; p.ldc = N; p.rank = rank; p.world = world; p.rows_per_rank = rows_per_rank;
-  for (int r = 0; r < kMaxRanks; ++r) p.flags.p[r] = (r < world) ? reinterpret_cast<void*>(flag_ptrs[r]) : nullptr;
-  p.channel = channel; p.epoch = epoch; p.error_flag = error_flag;
+  for (int r = 0; r < kMaxRanks; ++r) {
+    p.flags.p[r] = (r < world) ? reinterpret_cast<void*>(flag_ptrs[r]) : nullptr;
+    p.partials.p[r] = (r < world) ? reinterpret_cast<void*>(xg_ptrs[r]) : nullptr;
+  }
+  p.channel = channel; p.epoch = epoch; p.error_flag = error_flag; p.dest_counters = block_counters;
   const int tiles = (M / CBM) * ((N + bn - 1) / bn);
   return bn == 256 ? launch_comm<256, kAllGather>(ta, tb, p, tiles, s) : launch_comm<128, kAllGather>(ta, tb, p, tiles, s);
 }
 
-// X [T, K] local; W [N, K]; partial_ptrs[r]: rank r's partial buffer [T, N] bf16; out [T/world, N]; counters [world] ints.
+// X [T, K] local; W [N, K]; partial_ptrs[r]: rank r's slot buffer [world, T/world, N] bf16; out [T/world, N]; counters [world] ints.
 extern "C" int mb_gemm_rs(const void* X, const void* W, const long long* partial_ptrs, void* out, int* counters, int T, int N, int K,
                           int rank, int world, const long long* flag_ptrs, int channel, int epoch, int* error_flag, cudaStream_t s) {
   if (world > kMaxRanks || T % (CBM * world) || K % 8 || N % 8) return -1;
@@ -315,7 +401,7 @@ extern "C" int mb_gemm_rs(const void* X, const void* W, const long long* partial
   cudaError_t e = cudaMemsetAsync(counters, 0, sizeof(int) * world, s);
   if (e != cudaSuccess) return static_cast<int>(e);
   CommGemmParams p{};
-  p.M = T; p.N = N; p.K = K; p.C = reinterpret_cast<void*>(partial_ptrs[rank]); p.ldc = N; p.rank = rank; p.world = world;
+  p.M = T; p.N = N; p.K = K; p.C = nullptr; p.ldc = N; p.rank = rank; p.world = world;
   p.rows_per_rank = rows_per_rank;
   for (int r = 0; r < kMaxRanks; ++r) {
     p.flags.p[r] = (r < world) ? reinterpret_cast<void*>(flag_ptrs[r]) : nullptr;

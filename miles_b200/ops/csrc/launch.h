@@ -174,8 +174,10 @@ int mb_multi_copy(const long long* table, const long long* prefix, int n, long l
 int mb_multi_mxfp8(const long long* table, const long long* prefix, int n, long long total_chunks, int qdq, cudaStream_t s);
 
 // ---- gemm_comm.cu ----
-int mb_ag_gemm(const long long* x_ptrs, const void* W, void* Y, int rows_per_rank, int N, int K, int rank, int world,
-               const long long* flag_ptrs, int channel, int epoch, int* error_flag, cudaStream_t s);
+int mb_ag_gemm(const long long* xg_ptrs, const void* W, void* Y, int* block_counters, int rows_per_rank, int N, int K, int rank,
+               int world, const long long* flag_ptrs, int channel, int epoch, int* error_flag, cudaStream_t s);
+int mb_comm_configure(int* err, unsigned long long wait_ns);
+int mb_gemm_comm_configure(int* err, unsigned long long wait_ns);
 int mb_gemm_rs(const void* X, const void* W, const long long* partial_ptrs, void* out, int* counters, int T, int N, int K, int rank,
                int world, const long long* flag_ptrs, int channel, int epoch, int* error_flag, cudaStream_t s);
 

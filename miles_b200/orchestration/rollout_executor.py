@@ -133,6 +133,7 @@ class RolloutExecutor:
         n, r = max(sums[0], 1.0), max(sums[1], 1.0)
         out = dict(m)
         out["rollout/total_tokens"] = sums[2]
+        out["rollout/response_tokens"] = sums[1]
         if "rollout/log_probs" in m:
             out["rollout/log_probs"] = sums[3] / r
         for i, k in enumerate(by_sample):
@@ -159,6 +160,7 @@ class RolloutExecutor:
             "rollout/response_len/min": min(resp),
             "rollout/truncated_ratio": sum(data["truncated"]) / len(flat),
             "rollout/total_tokens": float(sum(data["total_lengths"])),
+            "rollout/response_tokens": float(sum(resp)),
             "perf/rollout_time": dt,
             "perf/tokens_per_gpu_per_sec": sum(resp) / max(dt, 1e-9) / max(1, getattr(self.args, "rollout_num_gpus", 1) or 1),
         }

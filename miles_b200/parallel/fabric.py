@@ -55,6 +55,29 @@ class Fabric:
         self._flag_ptrs: dict[tuple, torch.Tensor] = {}
         self._moe: dict[tuple, Any] = {}
         self._scratch: dict[str, Any] = {}
+        self.configure()
+
+    def configure(self, wait_ns: int | None = None):
+        """Tell the peer-memory kernels where the error flag lives (so that, once it is raised, they return instead of
+        consuming what a timed-out wait was guarding) and how long a wait on a peer may poll.  The limit defaults to
+        `MILES_PEER_WAIT_MS` (5000 ms): long enough for host skew between ranks inside a phase, short enough that a lost
+        peer ends the step with an error instead of a hang."""
+        import os
+
+        if wait_ns is None:
+            wait_ns = int(float(os.environ.get("MILES_PEER_WAIT_MS", "5000")) * 1e6)
+        self.wait_ns = int(wait_ns)
+        self.C.fabric_configure(self.err, self.wait_ns)
+
+    def phase_barrier(self, group=None):
+        """Host-side rendezvous (NCCL / gloo) at a phase boundary — start of a rollout, of a train step, of a weight
+        update — so that rank skew accumulated on the host (data conversion, garbage collection, checkpoint writes) is
+        absorbed here, where waiting is unbounded and cheap, and not inside a kernel's bounded wait."""
+        if dist.is_initialized() and dist.get_world_size(group) > 1:
+            dist.barrier(group=group)
+
+    def clear_error(self):
+        self.err.zero_()
 
     @staticmethod
     def create(ps) -> "Fabric":

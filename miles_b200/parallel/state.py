@@ -163,6 +163,23 @@ class ParallelState:
         from . import tp
         return tp.row_parallel_linear(x, w, self)
 
+    def defer_allreduce(self, x) -> bool:
+        """True where a row-parallel projection may hand on its UNREDUCED partial sums because the next op is the fused
+        all-reduce + residual add + RMSNorm kernel over peer memory: tensor-parallel inference (replicated activations,
+        no autograd) on CUDA with the NVLink fabric up — the rollout engine's prefill and decode."""
+        return (self.tp_size > 1 and not self.sequence_parallel and self.fabric is not None and self.fused and x.is_cuda
+                and x.dtype == torch.bfloat16 and not torch.is_grad_enabled())
+
+    def row_linear_partial(self, x, w):
+        """This rank's partial sums of a row-parallel projection, marked so that the consumer reduces them."""
+        y = ops.linear(x, w)
+        y._tp_partial = True
+        return y
+
+    def allreduce_add_rmsnorm(self, partial, residual, w, eps):
+        """(rmsnorm(Σ_ranks partial + residual)·w, Σ_ranks partial + residual) in the fused peer-memory kernel(s)."""
+        return self.fabric.allreduce_add_rmsnorm(partial, residual, w, eps, self)
+
     def sp_gather(self, x):
         if self.tp_size == 1 or not self.sequence_parallel:
             return x

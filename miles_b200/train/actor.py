@@ -316,6 +316,8 @@ class TrainActor:
         dev = self.device
         ps = self.ps
         dp_group = ps.dp_group
+        if ps.fabric is not None:
+            ps.fabric.phase_barrier()       # absorb host skew between ranks before the first kernel that waits on a peer
         with self.timer.span("data_preprocess"):
             mbs = make_micro_batches(args, shard["total_lengths"], dp_group=dp_group, cp_size=ps.cp_size)
         metrics: dict[str, float] = {}
@@ -374,6 +376,8 @@ class TrainActor:
         metrics["perf/actor_train_tok_per_s"] = tok / max(metrics["perf/train_time"], 1e-9)
         for k, v in self.timer.pop_all().items():
             metrics[f"perf/{k}_time"] = v
+        if ps.fabric is not None:
+            ps.fabric.check()               # a bounded wait on a peer ran out somewhere in this step: fail it loudly
         self.weight_version += 1
         return metrics
 

@@ -26,6 +26,19 @@ from .advantages import normalize_group_rewards
 
 PAD_MULTIPLE = 128
 
+# bytes this module moved between host and device (what a step's end-to-end accounting reads)
+TRANSFER = {"h2d_bytes": 0}
+
+
+def to_device(values, dtype, device) -> torch.Tensor:
+    """Host list / array → device tensor.  On CUDA the staging tensor is pinned (the caching host allocator reuses the
+    pages) and the copy is asynchronous on the current stream."""
+    t = values if isinstance(values, torch.Tensor) else torch.tensor(values, dtype=dtype)
+    if torch.device(device).type != "cuda":
+        return t.to(device)
+    TRANSFER["h2d_bytes"] += t.numel() * t.element_size()
+    return t.pin_memory().to(device, non_blocking=True)
+
 
 # ---- samples → train data ----------------------------------------------------------------------
 
@@ -274,7 +287,7 @@ def pack_micro_batch(shard: dict[str, Any], idx: list[int], device, *, pad_multi
             body = torch.cat(rows, 0)
             if pad:
                 body = torch.cat([body, torch.full((pad,) + tuple(body.shape[1:]), -1, dtype=torch.int32)], 0)
-            replay = body.to(device)
+            replay = to_device(body, torch.int32, device)
     mm = None
     if shard.get("multimodal_train_inputs") is not None:
         # per-sample {"patches", "grid_thw"} in sample order = the order of the image placeholder tokens in the packed stream
@@ -285,16 +298,16 @@ def pack_micro_batch(shard: dict[str, Any], idx: list[int], device, *, pad_multi
                   "grid_thw": torch.cat([torch.as_tensor(p["grid_thw"]).view(-1, 3) for p in parts], 0).to(device)}
     return PackedBatch(
         mm_inputs=mm,
-        tokens=torch.tensor(toks, dtype=torch.int32, device=device),
-        positions=torch.tensor(pos, dtype=torch.int32, device=device),
-        cu_seqlens=torch.tensor(cu, dtype=torch.int32, device=device),
+        tokens=to_device(toks, torch.int32, device),
+        positions=to_device(pos, torch.int32, device),
+        cu_seqlens=to_device(cu, torch.int32, device),
         max_seqlen=max_len,
         total_lengths=total_lengths,
         response_lengths=response_lengths,
-        gather_index=torch.tensor(gather, dtype=torch.int64, device=device),
-        targets=torch.tensor(targets, dtype=torch.int64, device=device),
-        loss_mask=torch.tensor(mask, dtype=torch.float32, device=device),
-        seq_ids=torch.tensor(seq_ids, dtype=torch.int64, device=device),
+        gather_index=to_device(gather, torch.int64, device),
+        targets=to_device(targets, torch.int64, device),
+        loss_mask=to_device(mask, torch.float32, device),
+        seq_ids=to_device(seq_ids, torch.int64, device),
         sample_index=list(idx),
         replay_topk=replay,
         num_real_tokens=real,
@@ -307,4 +320,4 @@ def flat_per_token(shard: dict[str, Any], key: str, idx: list[int], device, dtyp
     vals: list = []
     for i in idx:
         vals.extend(shard[key][i])
-    return torch.tensor(vals, dtype=dtype, device=device)
+    return to_device(vals, dtype, device)

@@ -88,6 +88,9 @@ class WeightUpdater:
             nbytes = getattr(self, f"_send_{self.mode}")()
             if self.actor.device.type == "cuda":
                 torch.cuda.synchronize()
+            fab = getattr(getattr(self.actor, "ps", None), "fabric", None)
+            if fab is not None:
+                fab.check()
             ok = True
         finally:
             # a failed transfer must not leave the engines paused: they resume on the version they hold

@@ -158,3 +158,33 @@ def test_http_server_and_router_roundtrip():
         rsrv.should_exit = True
         eng._stop_loop = True
         time.sleep(0.1)
+
+
+@pytest.mark.parametrize("name,plen", [("tiny", 10), ("tiny", 12), ("tiny-moe", 7)])
+def test_samples_of_one_prompt_share_prompt_kv(name, plen):
+    """The n samples of a prompt prefill it once: same tokens and log-probs as without sharing under fixed seeds, an
+    n-th of the prefill tokens, fewer blocks in use, and the routed experts of the shared prompt reach every sample."""
+    prompts = [[5 + i for i in range(plen)]] * 4 + [[40, 41, 42]] * 2 + [[9, 8, 7, 6, 5]]
+    sps = [{"temperature": 1.0, "max_new_tokens": 6, "seed": 100 + i} for i in range(len(prompts))]
+    res = {}
+    for share in (True, False):
+        eng = _engine(name, share_prompt_kv=share)
+        free0 = eng.allocator.num_free
+        reqs = [eng.add_request(p, dict(sp), True, name == "tiny-moe") for p, sp in zip(prompts, sps)]
+        eng.step()                                             # the prefill step
+        used_after_prefill = free0 - eng.allocator.num_free
+        while not all(r.done.is_set() for r in reqs):
+            eng.step()
+        res[share] = ([r.to_response(eng) for r in reqs], eng.stats["prefill_tokens"], used_after_prefill)
+        assert eng.allocator.num_free == free0                 # every reference was released
+    (a, tok_a, used_a), (b, tok_b, used_b) = res[True], res[False]
+    assert tok_a == plen + 3 + 5 and tok_b == 4 * plen + 2 * 3 + 5
+    assert used_a < used_b
+    for x, y in zip(a, b):
+        assert x["output_ids"] == y["output_ids"]
+        for (l1, t1, _), (l2, t2, _) in zip(x["meta_info"]["output_token_logprobs"], y["meta_info"]["output_token_logprobs"]):
+            assert t1 == t2 and abs(l1 - l2) < 1e-5
+        assert x["meta_info"].get("routed_experts") == y["meta_info"].get("routed_experts")
+    assert a[1]["meta_info"]["cached_tokens"] == plen and a[0]["meta_info"]["cached_tokens"] == 0
+    # siblings really diverge (different seeds), so the shared blocks were not written by anyone's decode steps
+    assert len({tuple(x["output_ids"]) for x in a[:4]}) > 1

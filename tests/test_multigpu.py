@@ -216,6 +216,17 @@ def _case_allreduce_rmsnorm(rank, world):
     dist.all_reduce(tot)
     yr, rr = ref.add_rmsnorm(tot.bfloat16(), res, w, 1e-6)
     assert _rel(y, yr) < 2e-2 and _rel(r, rr) < 2e-2
+    # prefill-sized input: at 4+ ranks this takes the two-shot schedule (sum own row block, gather the reduced blocks)
+    T = 512 * world
+    partial = torch.randn(T, H, device="cuda", generator=g).bfloat16()
+    res = torch.randn(T, H, device="cuda").bfloat16()
+    for _ in range(2):
+        y, r = ps.fabric.allreduce_add_rmsnorm(partial, res, w, 1e-6, ps)
+    ps.fabric.check()
+    tot = partial.float().clone()
+    dist.all_reduce(tot)
+    yr, rr = ref.add_rmsnorm(tot.bfloat16(), res, w, 1e-6)
+    assert _rel(y, yr) < 2e-2 and _rel(r, rr) < 2e-2
 
 
 def _case_tp_fused_linears(rank, world):
@@ -290,28 +301,67 @@ def _case_vocab_logprob(rank, world):
     assert _rel(w.grad, wf.grad[rank * vl:(rank + 1) * vl]) < 3e-2
 
 
+def _case_engine_tp_fused_allreduce(rank, world):
+    """The rollout engine under tensor parallelism: attention-out and MLP-down hand on partial sums and the all-reduce
+    runs inside the add + RMSNorm kernel; tokens and log-probs must match the NCCL all-reduce path."""
+    from miles_b200.engine.engine import Engine
+    from miles_b200.models.config import ModelConfig
+    from miles_b200.parallel.fabric import Fabric
+    from miles_b200.parallel.state import ParallelState
+
+    cfg = ModelConfig(name="tp-dense", vocab_size=4096, hidden_size=1024, num_layers=3, num_heads=16, num_kv_heads=8, head_dim=128, ffn_hidden_size=2048)
+    ps = ParallelState.build(tp=world, sequence_parallel=True)
+    ps.fabric = Fabric.create(ps)
+    eng = Engine(cfg, ps=ps, device=f"cuda:{rank}", num_blocks=64, block_size=64, use_cuda_graph=False, seed=0)
+    prompts = [list(range(5 + i, 5 + i + 40 + 7 * i)) for i in range(3)]
+    long_prompt = [list(range(3, 3 + 1024))]               # prefill-sized: takes the two-shot schedule at tp >= 4
+    sp = {"temperature": 0.0, "max_new_tokens": 6}
+    outs = {}
+    for fused in (True, False):
+        ps.fused = fused
+        res = eng.generate(prompts + long_prompt, sp)
+        outs[fused] = [[(t, lp) for lp, t, _ in r["meta_info"]["output_token_logprobs"]] for r in res]
+    ps.fabric.check()
+    for a, b in zip(outs[True], outs[False]):
+        assert [t for t, _ in a] == [t for t, _ in b], (a, b)
+        assert max(abs(x[1] - y[1]) for x, y in zip(a, b)) < 5e-2
+
+
 # ---- pytest entry points -----------------------------------------------------------------------------------
-
-def test_tp_fused_ag_gemm_and_gemm_rs():
-    _run("_case_tp_fused_linears")
-
-
-def test_fused_vocab_parallel_logprob():
-    _run("_case_vocab_logprob")
+# every case runs at 2, 4 and 8 ranks where the box has that many GPUs (skipped otherwise)
+WORLDS = [2, 4, 8]
 
 
-
-def test_fabric_barrier_and_symmetric_memory():
-    _run("_case_barrier_and_symmetric")
-
-
-def test_fused_moe_dispatch_combine_matches_oracle():
-    _run("_case_fused_moe")
+@pytest.mark.parametrize("world", WORLDS)
+def test_tp_fused_ag_gemm_and_gemm_rs(world):
+    _run("_case_tp_fused_linears", world)
 
 
-def test_fused_optimizer_step_matches_collective_path():
-    _run("_case_fused_optimizer")
+@pytest.mark.parametrize("world", WORLDS)
+def test_fused_vocab_parallel_logprob(world):
+    _run("_case_vocab_logprob", world)
 
 
-def test_allreduce_add_rmsnorm():
-    _run("_case_allreduce_rmsnorm")
+@pytest.mark.parametrize("world", WORLDS)
+def test_fabric_barrier_and_symmetric_memory(world):
+    _run("_case_barrier_and_symmetric", world)
+
+
+@pytest.mark.parametrize("world", WORLDS)
+def test_fused_moe_dispatch_combine_matches_oracle(world):
+    _run("_case_fused_moe", world)
+
+
+@pytest.mark.parametrize("world", WORLDS)
+def test_fused_optimizer_step_matches_collective_path(world):
+    _run("_case_fused_optimizer", world)
+
+
+@pytest.mark.parametrize("world", WORLDS)
+def test_allreduce_add_rmsnorm(world):
+    _run("_case_allreduce_rmsnorm", world)
+
+
+@pytest.mark.parametrize("world", WORLDS)
+def test_engine_tp_allreduce_fused_into_rmsnorm(world):
+    _run("_case_engine_tp_fused_allreduce", world, timeout=240)

@@ -51,12 +51,24 @@ def _run_both(lib, x, w, dy, dres, rstd, dw_fp32):
     rc = lib.mb_rmsnorm_bwd(p(x), p(w), p(dy), p(dres), p(rstd), p(dx_a), p(partial), p(dw_a), int(dw_fp32), T, H, stream)
     assert rc == 0
     torch.cuda.synchronize()
+    if not _run_both.primed:
+        # the first call on a device resolves the scratch array's address (documented one-time set-up); measure after it
+        rc = lib.mb_rmsnorm_bwd_static(p(x), p(w), p(dy), p(dres), p(rstd), p(dx_b), p(dw_b), int(dw_fp32), T, H, stream)
+        assert rc == 0, lib.mb_rmsnorm_bwd_static_strerror(rc)
+        torch.cuda.synchronize()
+        _run_both.primed = True
     before = torch.cuda.memory_stats()["allocation.all.allocated"]
+    free_before, _ = torch.cuda.mem_get_info()       # the driver's own count: a raw cudaMalloc would show here
     rc = lib.mb_rmsnorm_bwd_static(p(x), p(w), p(dy), p(dres), p(rstd), p(dx_b), p(dw_b), int(dw_fp32), T, H, stream)
     assert rc == 0, lib.mb_rmsnorm_bwd_static_strerror(rc)
     torch.cuda.synchronize()
+    free_after, _ = torch.cuda.mem_get_info()
     assert torch.cuda.memory_stats()["allocation.all.allocated"] == before
+    assert free_after == free_before, f"device memory in use changed by {free_before - free_after} bytes across the call"
     return (dx_a, dw_a), (dx_b, dw_b)
+
+
+_run_both.primed = False
 
 
 def test_static_matches_existing_on_consecutive_calls():
