@@ -203,6 +203,7 @@ def main():
         engines = [engine]
 
     Rollout.executor = executor
+    phases: dict = {}
     counters = {"tokens": 0, "gen_tokens": 0, "h2d": 0, "d2h": 0, "sync_s": 0.0, "rollout_s": 0.0, "train_s": 0.0}
     from miles_b200.train import data as train_data
 
@@ -244,6 +245,9 @@ def main():
         engine.stats["h2d_bytes"] = engine.stats["d2h_bytes"] = 0
         train_data.TRANSFER["h2d_bytes"] = 0
         counters["engine"] = {k: (round(v, 3) if isinstance(v, float) else v) for k, v in engine.stats.items()}
+        for k, v in metrics.items():                       # the trainer's own phase timers (seconds, this rank)
+            if k.startswith("perf/") and k.endswith("_time"):
+                phases[k[5:-5]] = phases.get(k[5:-5], 0.0) + float(v)
         return metrics
 
     for i in range(a.warmup):
@@ -254,6 +258,7 @@ def main():
                   file=sys.stderr, flush=True)
     for k in counters:
         counters[k] = 0
+    phases.clear()
     for k in list(engine.stats):
         engine.stats[k] = type(engine.stats[k])()
     launches0 = K.launch_count()
@@ -310,6 +315,7 @@ def main():
             "gpu_launches": int(launches),
             "breakdown_s_per_step": {"rollout": counters["rollout_s"] / a.steps, "train": counters["train_s"] / a.steps,
                                      "weight_sync": counters["sync_s"] / a.steps},
+            "train_phases_s_per_step_rank0": {k: round(v / a.steps, 3) for k, v in sorted(phases.items())},
             "tokens_per_step": total_tokens // a.steps, "kernel_error_flag": err,
             # the reference's perf/tokens_per_gpu_per_sec counts response tokens only: the same quantity for the whole job
             "generated_tokens_per_s": gen_tokens / (dev_ms / 1e3), "generated_tokens_per_step": gen_tokens // a.steps,

@@ -688,6 +688,17 @@ extern "C" int mb_flash_fwd(const void* q, const void* k, const void* v, void* o
   return static_cast<int>(cudaGetLastError());
 }
 
+// delta[h, t] = Σ_d dO[t, h, d] · O[t, h, d] (the backward's pre-pass, shared by both backward implementations)
+extern "C" int mb_attn_delta(const void* o, const void* dout, float* delta, int total_tokens, int Hq, int D, cudaStream_t s) {
+  if (total_tokens == 0) return 0;
+  const long long warps = static_cast<long long>(total_tokens) * Hq;
+  const unsigned blocks = static_cast<unsigned>((warps + 7) / 8);
+  if (D == 128) attn_delta_kernel<128><<<blocks, 256, 0, s>>>(reinterpret_cast<const bf16*>(o), reinterpret_cast<const bf16*>(dout), delta, total_tokens, Hq);
+  else if (D == 64) attn_delta_kernel<64><<<blocks, 256, 0, s>>>(reinterpret_cast<const bf16*>(o), reinterpret_cast<const bf16*>(dout), delta, total_tokens, Hq);
+  else return -1;
+  return static_cast<int>(cudaGetLastError());
+}
+
 extern "C" int mb_flash_bwd(const void* q, const void* k, const void* v, const void* o, const void* dout, const float* lse,
                             float* delta, void* dq, void* dk, void* dv, const int* cu_seqlens, int batch, int max_seqlen,
                             int total_tokens, long long q_stride, long long k_stride, long long v_stride, int Hq, int Hkv, int D,

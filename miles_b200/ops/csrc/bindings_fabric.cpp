@@ -103,6 +103,45 @@ void moe_dispatch(const at::Tensor& x, const at::Tensor& topk_idx, int64_t k, in
         "mb_moe_dispatch");
 }
 
+void moe_dispatch_signal(const at::Tensor& x, const at::Tensor& topk_idx, int64_t k, int64_t e_local, int64_t rank,
+                         const at::Tensor& recv_x_ptrs, const at::Tensor& recv_meta_ptrs, const at::Tensor& counter_ptrs, int64_t world,
+                         int64_t capacity, at::Tensor& sent_row, at::Tensor& err, const at::Tensor& flag_ptrs, int64_t channel,
+                         at::Tensor& epochs, at::Tensor& ticket) {
+  c10::cuda::CUDAGuard g(x.device());
+  check(mb_moe_dispatch_signal(x.data_ptr(), topk_idx.data_ptr<int>(), topk_idx.numel(), k, x.size(-1), e_local, rank, lptr(recv_x_ptrs),
+                               lptr(recv_meta_ptrs), lptr(counter_ptrs), world, capacity, sent_row.data_ptr<int>(), err.data_ptr<int>(),
+                               lptr(flag_ptrs), channel, epochs.data_ptr<int>(), ticket.data_ptr<int>(), cur_stream()),
+        "mb_moe_dispatch_signal");
+}
+
+void moe_recv_align(const at::Tensor& meta, at::Tensor& counter, int64_t capacity, int64_t E, at::Tensor& seg, at::Tensor& tile,
+                    at::Tensor& row_src, int64_t pad, const at::Tensor& flag_ptrs, int64_t rank, int64_t world, int64_t channel,
+                    const at::Tensor& epochs, at::Tensor& err) {
+  c10::cuda::CUDAGuard g(meta.device());
+  check(mb_moe_recv_align(meta.data_ptr(), counter.data_ptr<int>(), capacity, E, seg.data_ptr<int>(), tile.data_ptr<int>(),
+                          row_src.data_ptr<int>(), row_src.numel(), pad, lptr(flag_ptrs), rank, world, channel, epochs.data_ptr<int>(),
+                          err.data_ptr<int>(), cur_stream()),
+        "mb_moe_recv_align");
+}
+
+void moe_return_signal(const at::Tensor& y_perm, const at::Tensor& row_src, const at::Tensor& meta, const at::Tensor& seg,
+                       const at::Tensor& ret_ptrs, int64_t world, const at::Tensor& flag_ptrs, int64_t rank, int64_t channel,
+                       at::Tensor& epochs, at::Tensor& ticket) {
+  c10::cuda::CUDAGuard g(y_perm.device());
+  check(mb_moe_return_signal(y_perm.data_ptr(), row_src.data_ptr<int>(), meta.data_ptr(), seg.data_ptr<int>(), seg.numel() - 1,
+                             y_perm.size(-1), y_perm.size(0), lptr(ret_ptrs), world, lptr(flag_ptrs), rank, channel,
+                             epochs.data_ptr<int>(), ticket.data_ptr<int>(), cur_stream()),
+        "mb_moe_return_signal");
+}
+
+void moe_combine_wait(const at::Tensor& ret, const at::Tensor& w, const at::Tensor& sent_row, at::Tensor& out, int64_t k,
+                      const at::Tensor& flag_ptrs, int64_t rank, int64_t world, int64_t channel, const at::Tensor& epochs, at::Tensor& err) {
+  c10::cuda::CUDAGuard g(out.device());
+  check(mb_moe_combine_wait(ret.data_ptr(), w.data_ptr<float>(), sent_row.data_ptr<int>(), out.data_ptr(), out.size(0), k, out.size(-1),
+                            lptr(flag_ptrs), rank, world, channel, epochs.data_ptr<int>(), err.data_ptr<int>(), cur_stream()),
+        "mb_moe_combine_wait");
+}
+
 void moe_scatter_known(const at::Tensor& rows_in, bool src_by_pair, const at::Tensor& topk_idx, const at::Tensor& sent_row, int64_t k,
                        int64_t e_local, const at::Tensor& recv_x_ptrs, int64_t world) {
   c10::cuda::CUDAGuard g(rows_in.device());
@@ -200,6 +239,10 @@ void register_fabric(pybind11::module& m) {
   m.def("adam_allgather", &adam_allgather);
   m.def("moe_dispatch", &moe_dispatch);
   m.def("moe_scatter_known", &moe_scatter_known);
+  m.def("moe_dispatch_signal", &moe_dispatch_signal);
+  m.def("moe_recv_align", &moe_recv_align);
+  m.def("moe_return_signal", &moe_return_signal);
+  m.def("moe_combine_wait", &moe_combine_wait);
   m.def("moe_return", &moe_return);
   m.def("recv_expert_ids", &recv_expert_ids, pybind11::arg("meta"), pybind11::arg("counter"), pybind11::arg("capacity"),
         pybind11::arg("expert_ids"), pybind11::arg("n_out"), pybind11::arg("clear_counter") = false);

@@ -75,6 +75,21 @@ void flash_bwd(const at::Tensor& q, const at::Tensor& k, const at::Tensor& v, co
         "mb_flash_bwd");
 }
 
+// tcgen05 backward (head_dim 128): delta pre-pass + dK/dV kernel + dQ kernel
+void flash_bwd_tc(const at::Tensor& q, const at::Tensor& k, const at::Tensor& v, const at::Tensor& o, const at::Tensor& dout,
+                  const at::Tensor& lse, at::Tensor& delta, at::Tensor& dq, at::Tensor& dk, at::Tensor& dv, const at::Tensor& cu_seqlens,
+                  int64_t max_seqlen, double scale, bool causal, at::Tensor& err) {
+  c10::cuda::CUDAGuard g(q.device());
+  const int64_t T = q.size(0), Hq = q.size(1), D = q.size(2), Hkv = k.size(1);
+  TORCH_CHECK(D == 128, "flash_bwd_tc serves head_dim 128");
+  check(mb_attn_delta(o.data_ptr(), dout.data_ptr(), delta.data_ptr<float>(), T, Hq, D, cur_stream()), "mb_attn_delta");
+  mb_count_launch(2);
+  check(mb_flash_bwd_tc(q.data_ptr(), k.data_ptr(), v.data_ptr(), dout.data_ptr(), lse.data_ptr<float>(), delta.data_ptr<float>(),
+                        dq.data_ptr(), dk.data_ptr(), dv.data_ptr(), cu_seqlens.data_ptr<int>(), cu_seqlens.numel() - 1, max_seqlen, T,
+                        q.stride(0), k.stride(0), v.stride(0), Hq, Hkv, scale, causal, err.data_ptr<int>(), cur_stream()),
+        "mb_flash_bwd_tc");
+}
+
 void paged_decode(const at::Tensor& q, const at::Tensor& kc, const at::Tensor& vc, const at::Tensor& block_table,
                   const at::Tensor& seq_lens, at::Tensor& out, at::Tensor& part_o, at::Tensor& part_ml, double scale,
                   int64_t num_splits) {
@@ -99,6 +114,7 @@ void register_more(pybind11::module& m) {
   m.def("flash_fwd_tc", &flash_fwd_tc);
   m.def("flash_fwd_tc_ctas_per_sm", []() { return mb_flash_fwd_tc_ctas_per_sm(); });
   m.def("flash_bwd", &flash_bwd);
+  m.def("flash_bwd_tc", &flash_bwd_tc);
   m.def("paged_decode", &paged_decode);
   register_moe(m);
   register_misc(m);

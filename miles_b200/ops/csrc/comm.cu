@@ -13,6 +13,7 @@
 
 #include "comm.cuh"
 #include "launch.h"
+#include "pdl.cuh"
 
 namespace mb {
 
@@ -209,6 +210,161 @@ __global__ void __launch_bounds__(256) moe_dispatch_kernel(const bf16* __restric
   }
 }
 
+// Decode-time expert parallelism with the barriers folded into the kernels on either side of them (inference, at most
+// 16384 receivable rows): `moe_dispatch_signal` = dispatch + publish from its last block; `moe_recv_align` = wait for every
+// peer's publish, read and reset the receive counter, counting-sort the received rows by local expert;
+// `moe_return_signal` = return + publish; `moe_combine_wait` = wait + weighted sum.  Four launches where the general path
+// takes eight (dispatch, barrier, expert-id scan, align, …, return, barrier, combine).
+__global__ void __launch_bounds__(256) moe_dispatch_signal_kernel(const bf16* __restrict__ x, const int* __restrict__ topk_idx,
+                                                                  long long n_pairs, int k, int H, int e_local, int rank,
+                                                                  PeerPtrs recv_x, PeerPtrs recv_meta, PeerPtrs counters, int capacity,
+                                                                  int* __restrict__ sent_row, int* err, PeerPtrs flags, int world,
+                                                                  int channel, int* epochs, int* ticket) {
+  // programmatic dependent launch: the successor may be scheduled at once (it waits for this grid's completion before it
+  // reads anything), and nothing a predecessor wrote is read here before the wait
+  pdl_trigger();
+  pdl_wait();
+  if (!fabric_poisoned()) {
+    const int lane = threadIdx.x & 31;
+    const int nvec = H / 8;
+    for (long long pair = (blockIdx.x * 256ll + threadIdx.x) >> 5; pair < n_pairs; pair += (static_cast<long long>(gridDim.x) * 256) >> 5) {
+      const int e = topk_idx[pair];
+      if (e < 0) {
+        if (lane == 0) sent_row[pair] = -1;
+        continue;
+      }
+      const int dest = e / e_local;
+      int row = 0;
+      if (lane == 0) row = atomicAdd(reinterpret_cast<int*>(counters.p[dest]), 1);
+      row = __shfl_sync(0xffffffffu, row, 0);
+      if (row >= capacity) {
+        if (lane == 0) { atomicCAS(err, 0, 200); sent_row[pair] = -1; }
+        continue;
+      }
+      const uint4* src = reinterpret_cast<const uint4*>(x + (pair / k) * H);
+      uint4* dst = reinterpret_cast<uint4*>(reinterpret_cast<bf16*>(recv_x.p[dest]) + static_cast<long long>(row) * H);
+      for (int v = lane; v < nvec; v += 32) dst[v] = src[v];
+      if (lane == 0) {
+        reinterpret_cast<int4*>(recv_meta.p[dest])[row] = make_int4(rank, static_cast<int>(pair), e - dest * e_local, 0);
+        sent_row[pair] = row;
+      }
+    }
+  }
+  publish_when_grid_done(flags, rank, world, channel, epochs, ticket);
+}
+
+// One block.  Outputs as `moe_align`: seg_offsets[E+1] (segments padded to `pad`), tile_expert[max_rows / pad], row_src[max_rows].
+__global__ void __launch_bounds__(1024) moe_recv_align_kernel(const int4* __restrict__ meta, int* __restrict__ counter, int capacity, int E,
+                                                              int* __restrict__ seg_offsets, int* __restrict__ tile_expert,
+                                                              int* __restrict__ row_src, int max_rows, int pad, PeerPtrs flags, int rank,
+                                                              int world, int channel, const int* epochs, int* err) {
+  extern __shared__ int sh[];   // counts[E], cursor[E], seg[E+1], n
+  int* counts = sh;
+  int* cursor = sh + E;
+  int* seg = sh + 2 * E;
+  int* n_sh = sh + 3 * E + 1;
+  pdl_trigger();
+  pdl_wait();
+  const bool ok = wait_peers(flags, rank, world, channel, epochs);
+  if (!ok && threadIdx.x == 0) atomicCAS(err, 0, 100 + channel);
+  if (threadIdx.x == 0) *n_sh = ok ? min(*counter, capacity) : 0;
+  for (int e = threadIdx.x; e < E; e += blockDim.x) { counts[e] = 0; cursor[e] = 0; }
+  __syncthreads();
+  const int n = *n_sh;
+  if (threadIdx.x == 0) *counter = 0;      // peers add to it again only after the next publish of this rank's stream
+  for (int i = threadIdx.x; i < n; i += blockDim.x) {
+    const int e = meta[i].z;
+    if (e >= 0 && e < E) atomicAdd(&counts[e], 1);
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    int off = 0;
+    for (int e = 0; e < E; ++e) {
+      seg[e] = off;
+      off += (counts[e] + pad - 1) / pad * pad;
+    }
+    seg[E] = off;
+  }
+  __syncthreads();
+  for (int e = threadIdx.x; e <= E; e += blockDim.x) seg_offsets[e] = seg[e];
+  const int max_tiles = max_rows / pad;
+  for (int t = threadIdx.x; t < max_tiles; t += blockDim.x) {
+    const int row = t * pad;
+    int ex = -1;
+    if (row < seg[E]) {
+      int lo = 0, hi = E;
+      while (hi - lo > 1) {
+        const int mid = (lo + hi) >> 1;
+        if (seg[mid] <= row) lo = mid; else hi = mid;
+      }
+      ex = lo;
+    }
+    tile_expert[t] = ex;
+  }
+  for (int r = threadIdx.x; r < seg[E] && r < max_rows; r += blockDim.x) row_src[r] = -1;
+  __syncthreads();
+  for (int i = threadIdx.x; i < n; i += blockDim.x) {
+    const int e = meta[i].z;
+    if (e >= 0 && e < E) {
+      const int row = seg[e] + atomicAdd(&cursor[e], 1);
+      if (row < max_rows) row_src[row] = i;
+    }
+  }
+}
+
+__global__ void __launch_bounds__(256) moe_return_signal_kernel(const bf16* __restrict__ y_perm, const int* __restrict__ row_src,
+                                                                const int4* __restrict__ meta, const int* __restrict__ seg_offsets, int E,
+                                                                int H, int max_rows, PeerPtrs ret, PeerPtrs flags, int rank, int world,
+                                                                int channel, int* epochs, int* ticket) {
+  pdl_trigger();
+  pdl_wait();
+  if (!fabric_poisoned()) {
+    const int lane = threadIdx.x & 31;
+    const int nvec = H / 8;
+    const int total = min(seg_offsets[E], max_rows);
+    for (int p = (blockIdx.x * 256 + threadIdx.x) >> 5; p < total; p += (gridDim.x * 256) >> 5) {
+      const int r = row_src[p];
+      if (r < 0) continue;
+      const int4 mt = meta[r];
+      const uint4* src = reinterpret_cast<const uint4*>(y_perm + static_cast<long long>(p) * H);
+      uint4* dst = reinterpret_cast<uint4*>(reinterpret_cast<bf16*>(ret.p[mt.x]) + static_cast<long long>(mt.y) * H);
+      for (int v = lane; v < nvec; v += 32) dst[v] = src[v];
+    }
+  }
+  publish_when_grid_done(flags, rank, world, channel, epochs, ticket);
+}
+
+// out[t, :] = Σ_j w[t, j] · ret[t·k + j, :] over the pairs that took part (sent_row ≥ 0), after every peer's publish arrived
+__global__ void __launch_bounds__(256) moe_combine_wait_kernel(const bf16* __restrict__ ret, const float* __restrict__ w,
+                                                               const int* __restrict__ sent_row, bf16* __restrict__ out, long long T, int k,
+                                                               int H, PeerPtrs flags, int rank, int world, int channel, const int* epochs,
+                                                               int* err) {
+  // the next kernel of the stream (the following layer's fused norm + projection) is released at once: it streams its
+  // weights while this grid still waits for the peers' results
+  pdl_trigger();
+  pdl_wait();
+  if (!wait_peers(flags, rank, world, channel, epochs)) {
+    if (threadIdx.x == 0) atomicCAS(err, 0, 100 + channel);
+    return;
+  }
+  if (fabric_poisoned()) return;
+  const int nvec = H / 8;
+  for (long long t = blockIdx.x; t < T; t += gridDim.x) {
+    for (int v = threadIdx.x; v < nvec; v += 256) {
+      float acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+      for (int j = 0; j < k; ++j) {
+        if (sent_row[t * k + j] < 0) continue;
+        const float wj = w[t * k + j];
+        float f[8];
+        unpack8(*reinterpret_cast<const uint4*>(ret + (t * k + j) * H + v * 8), f);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) acc[i] += wj * f[i];
+      }
+      *reinterpret_cast<uint4*>(out + t * H + v * 8) = pack8(acc);
+    }
+  }
+}
+
 // Rows pushed to remote rows that are already known: dst rank = topk_idx / e_local, dst row = sent_row[pair].
 // rows_in is indexed by pair (src_by_pair = 1) or by token (pair / k).
 __global__ void __launch_bounds__(256) moe_scatter_known_kernel(const bf16* __restrict__ rows_in, int src_by_pair,
@@ -377,6 +533,46 @@ extern "C" int mb_moe_dispatch(const void* x, const int* topk_idx, long long n_p
                                                              make_ptrs(recv_x_ptrs, world), make_ptrs(recv_meta_ptrs, world),
                                                              make_ptrs(counter_ptrs, world), capacity, sent_row, err);
   return static_cast<int>(cudaGetLastError());
+}
+
+extern "C" int mb_moe_dispatch_signal(const void* x, const int* topk_idx, long long n_pairs, int k, int H, int e_local, int rank,
+                                      const long long* recv_x_ptrs, const long long* recv_meta_ptrs, const long long* counter_ptrs,
+                                      int world, int capacity, int* sent_row, int* err, const long long* flag_ptrs, int channel,
+                                      int* epochs, int* ticket, cudaStream_t s) {
+  if (H % 8 || world > kMaxRanks) return -1;
+  return static_cast<int>(launch_pdl(moe_dispatch_signal_kernel, dim3(blocks_for(n_pairs > 0 ? n_pairs : 1, 8)), dim3(256), 0, s,
+                                     reinterpret_cast<const bf16*>(x), topk_idx, n_pairs, k, H, e_local, rank,
+                                     make_ptrs(recv_x_ptrs, world), make_ptrs(recv_meta_ptrs, world), make_ptrs(counter_ptrs, world),
+                                     capacity, sent_row, err, make_ptrs(flag_ptrs, world), world, channel, epochs, ticket));
+}
+
+extern "C" int mb_moe_recv_align(const void* meta, int* counter, int capacity, int E, int* seg_offsets, int* tile_expert, int* row_src,
+                                 int max_rows, int pad, const long long* flag_ptrs, int rank, int world, int channel, const int* epochs,
+                                 int* err, cudaStream_t s) {
+  if (capacity > 16384 || world > kMaxRanks || pad <= 0 || max_rows % pad) return -1;
+  return static_cast<int>(launch_pdl(moe_recv_align_kernel, dim3(1), dim3(1024), (3 * E + 2) * sizeof(int), s,
+                                     reinterpret_cast<const int4*>(meta), counter, capacity, E, seg_offsets, tile_expert, row_src,
+                                     max_rows, pad, make_ptrs(flag_ptrs, world), rank, world, channel, epochs, err));
+}
+
+extern "C" int mb_moe_return_signal(const void* y_perm, const int* row_src, const void* meta, const int* seg_offsets, int E, int H,
+                                    int max_rows, const long long* ret_ptrs, int world, const long long* flag_ptrs, int rank, int channel,
+                                    int* epochs, int* ticket, cudaStream_t s) {
+  if (world > kMaxRanks) return -1;
+  return static_cast<int>(launch_pdl(moe_return_signal_kernel, dim3(blocks_for(max_rows > 0 ? max_rows : 1, 8)), dim3(256), 0, s,
+                                     reinterpret_cast<const bf16*>(y_perm), row_src, reinterpret_cast<const int4*>(meta), seg_offsets,
+                                     E, H, max_rows, make_ptrs(ret_ptrs, world), make_ptrs(flag_ptrs, world), rank, world, channel,
+                                     epochs, ticket));
+}
+
+extern "C" int mb_moe_combine_wait(const void* ret, const float* w, const int* sent_row, void* out, long long T, int k, int H,
+                                   const long long* flag_ptrs, int rank, int world, int channel, const int* epochs, int* err,
+                                   cudaStream_t s) {
+  if (H % 8 || world > kMaxRanks) return -1;
+  const int blocks = T < 1 ? 1 : (T < 148 * 16 ? static_cast<int>(T) : 148 * 16);
+  return static_cast<int>(launch_pdl(moe_combine_wait_kernel, dim3(blocks), dim3(256), 0, s, reinterpret_cast<const bf16*>(ret), w,
+                                     sent_row, reinterpret_cast<bf16*>(out), T, k, H, make_ptrs(flag_ptrs, world), rank, world,
+                                     channel, epochs, err));
 }
 
 extern "C" int mb_moe_scatter_known(const void* rows_in, int src_by_pair, const int* topk_idx, const int* sent_row, long long n_pairs,

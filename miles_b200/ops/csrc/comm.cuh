@@ -79,6 +79,46 @@ __device__ __forceinline__ bool cross_rank_barrier(const PeerPtrs& flags, int ra
   return ok_sh != 0;
 }
 
+// ---- split barrier: the producer kernel signals from its last block, the consumer kernel waits in its prologue -------------
+// `publish_when_grid_done`: call with ALL threads of every block after the block's last global write that peers will read.
+// The block that takes the last ticket advances the device-side epoch of `channel` and publishes it to every peer
+// (release at system scope); `ticket` is one int that is zero between kernels (the last block resets it).
+__device__ __forceinline__ void publish_when_grid_done(const PeerPtrs& flags, int rank, int world, int channel, int* epochs,
+                                                       int* ticket) {
+  __shared__ int last_sh, epoch_sh;
+  __threadfence_system();
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    const int t = atomicAdd(ticket, 1);
+    last_sh = (t == static_cast<int>(gridDim.x) - 1);
+    if (last_sh) {
+      __threadfence();                    // the other blocks' writes (ordered before their tickets) are visible here
+      *ticket = 0;
+      epoch_sh = ++epochs[channel];
+    }
+  }
+  __syncthreads();
+  if (last_sh && static_cast<int>(threadIdx.x) < world) {
+    __threadfence_system();
+    st_release_sys(reinterpret_cast<int*>(flags.p[threadIdx.x]) + channel * kMaxRanks + rank, epoch_sh);
+  }
+}
+
+// `wait_peers`: every block of the consumer waits (bounded) until all peers published the current epoch of `channel`.
+// The epoch is read from device memory: the producer kernel of THIS rank advanced it earlier on the same stream.
+__device__ __forceinline__ bool wait_peers(const PeerPtrs& flags, int rank, int world, int channel, const int* epochs) {
+  __shared__ int ok_sh;
+  if (threadIdx.x == 0) ok_sh = 1;
+  __syncthreads();
+  if (static_cast<int>(threadIdx.x) < world) {
+    const int epoch = *reinterpret_cast<const volatile int*>(epochs + channel);
+    const int* mine = reinterpret_cast<const int*>(flags.p[rank]) + channel * kMaxRanks + threadIdx.x;
+    if (!fabric_poisoned() && !wait_flag_ge(mine, epoch)) ok_sh = 0;
+  }
+  __syncthreads();
+  return ok_sh != 0;
+}
+
 // Host side of the two settings above for the including translation unit.
 #define MB_DEFINE_FABRIC_CONFIGURE(fn_name)                                                                        \
   extern "C" int fn_name(int* err, unsigned long long wait_ns) {                                                  \

@@ -54,7 +54,8 @@ struct SmemLayout {
   static constexpr int kStageBytes = kABytes + kBBytes;
   static constexpr int kStages = (BN >= 256) ? 4 : (BN >= 128 ? 6 : 8);
   static constexpr int kBarrierBytes = 256;
-  static constexpr int kTotal = kStages * kStageBytes + kBarrierBytes + 1024;  // + alignment slack
+  static constexpr int kStagingBytes = 4 * 4096;   // epilogue: one 32-row × 128-byte transposition tile per warp
+  static constexpr int kTotal = kStages * kStageBytes + kBarrierBytes + kStagingBytes + 1024;  // + alignment slack
 };
 
 template <int BN, int A_MN, int B_MN, int MODE>
@@ -73,6 +74,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
   uint64_t* tmem_empty = tmem_full + 2;        // [2]
   uint32_t* tmem_base_ptr = reinterpret_cast<uint32_t*>(tmem_empty + 2);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_base_ptr + 1);
+  uint8_t* smem_stage = smem + kStages * L::kStageBytes + L::kBarrierBytes;
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
@@ -314,6 +316,95 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
           __syncwarp();
           if (lane == 0) p.counters[tt * 4 + q] = 0;
         }
+        continue;
+      }
+      // Coalesced path: the accumulator arrives one row per thread, but whole 128-byte lines are what the memory system
+      // wants.  Each warp turns 128 bytes of output per row at a time (64 bf16 or 32 fp32 columns) through its staging tile
+      // (16-byte units, XOR-swizzled against bank conflicts): written row-per-lane, read back with 8 lanes covering one
+      // row, so every store instruction writes four full lines.  Needs 16-byte aligned rows; otherwise the plain path below.
+      const int esz = p.out_fp32 ? 4 : 2;
+      const int cols_per_round = 128 / esz;
+      if ((((p.ldc * esz) | (p.group_stride_c * esz) | static_cast<long long>(reinterpret_cast<uintptr_t>(p.C))) & 15) == 0 &&
+          (p.N * esz) % 16 == 0) {
+        const int row0 = m_blk * BM + q * 32;
+        uint8_t* stage = smem_stage + q * 4096;
+        uint8_t* c_tile = reinterpret_cast<uint8_t*>(p.C) +
+                          (static_cast<long long>(group) * p.group_stride_c + static_cast<long long>(row0) * p.ldc) * esz;
+#pragma unroll 1
+        for (int c2 = 0; c2 < BN / cols_per_round; ++c2) {
+          const int colr = n_blk * BN + c2 * cols_per_round;
+          if (colr >= p.N) break;                                  // uniform over the warp
+          if (p.out_fp32) {
+            uint32_t r[32];
+            tmem_ld_32x32(t_row + c2 * 32, r);
+            tmem_ld_wait();
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+              float4 o;
+              o.x = (k_blocks == 0) ? 0.f : __uint_as_float(r[4 * i]);
+              o.y = (k_blocks == 0) ? 0.f : __uint_as_float(r[4 * i + 1]);
+              o.z = (k_blocks == 0) ? 0.f : __uint_as_float(r[4 * i + 2]);
+              o.w = (k_blocks == 0) ? 0.f : __uint_as_float(r[4 * i + 3]);
+              *reinterpret_cast<float4*>(stage + lane * 128 + ((i ^ (lane & 7)) << 4)) = o;
+            }
+          } else {
+#pragma unroll
+            for (int half = 0; half < 2; ++half) {
+              uint32_t r[32];
+              tmem_ld_32x32(t_row + c2 * 64 + half * 32, r);
+              tmem_ld_wait();
+              if (k_blocks == 0) {
+#pragma unroll
+                for (int i = 0; i < 32; ++i) r[i] = 0u;
+              }
+              if (p.bias != nullptr) {
+#pragma unroll
+                for (int i = 0; i < 32; ++i) {
+                  const int col = colr + half * 32 + i;
+                  if (col < p.N) r[i] = __float_as_uint(__uint_as_float(r[i]) + __bfloat162float(p.bias[col]));
+                }
+              }
+#pragma unroll
+              for (int i = 0; i < 4; ++i) {
+                uint4 o;
+                o.x = pack_bf16x2(__uint_as_float(r[8 * i]), __uint_as_float(r[8 * i + 1]));
+                o.y = pack_bf16x2(__uint_as_float(r[8 * i + 2]), __uint_as_float(r[8 * i + 3]));
+                o.z = pack_bf16x2(__uint_as_float(r[8 * i + 4]), __uint_as_float(r[8 * i + 5]));
+                o.w = pack_bf16x2(__uint_as_float(r[8 * i + 6]), __uint_as_float(r[8 * i + 7]));
+                *reinterpret_cast<uint4*>(stage + lane * 128 + (((half * 4 + i) ^ (lane & 7)) << 4)) = o;
+              }
+            }
+          }
+          __syncwarp();
+          const int unit = lane & 7;
+          const int col = colr + unit * (16 / esz);
+#pragma unroll
+          for (int k = 0; k < 8; ++k) {
+            const int rr = k * 4 + (lane >> 3);
+            if (row0 + rr < p.M && col < p.N) {
+              uint8_t* dst = c_tile + (static_cast<long long>(rr) * p.ldc + col) * esz;
+              if (p.out_fp32) {
+                float4 o = *reinterpret_cast<const float4*>(stage + rr * 128 + ((unit ^ (rr & 7)) << 4));
+                if (p.bias != nullptr) {
+                  o.x += __bfloat162float(p.bias[col]); o.y += __bfloat162float(p.bias[col + 1]);
+                  o.z += __bfloat162float(p.bias[col + 2]); o.w += __bfloat162float(p.bias[col + 3]);
+                }
+                if (p.accumulate) {
+                  const float4 old = *reinterpret_cast<const float4*>(dst);
+                  o.x += old.x; o.y += old.y; o.z += old.z; o.w += old.w;
+                }
+                *reinterpret_cast<float4*>(dst) = o;
+              } else {
+                *reinterpret_cast<uint4*>(dst) = *reinterpret_cast<const uint4*>(stage + rr * 128 + ((unit ^ (rr & 7)) << 4));
+              }
+            }
+          }
+          __syncwarp();
+        }
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&tmem_empty[acc]);
+        if (++acc == 2) { acc = 0; acc_phase ^= 1; }
         continue;
       }
       uint8_t* c_base = reinterpret_cast<uint8_t*>(p.C) +

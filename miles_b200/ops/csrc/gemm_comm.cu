@@ -50,7 +50,7 @@ struct CSmem {
   static constexpr int kBBytes = BN * CBK * 2;
   static constexpr int kStageBytes = kABytes + kBBytes;
   static constexpr int kStages = (BN >= 256) ? 4 : 6;
-  static constexpr int kTotal = kStages * kStageBytes + 256 + 1024;
+  static constexpr int kTotal = kStages * kStageBytes + 256 + 4 * 4096 + 1024;
 };
 
 __device__ __forceinline__ void epi_bar_sync() { asm volatile("bar.sync 1, 128;" ::: "memory"); }
@@ -86,6 +86,7 @@ gemm_comm_kernel(const __grid_constant__ TmapArray tmaps_a, const __grid_constan
   uint32_t* tmem_base_ptr = reinterpret_cast<uint32_t*>(tmem_empty + 2);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_base_ptr + 1);
   volatile int* copy_go = abort_flag + 1;     // the copy warps' shared decision for the current piece
+  uint8_t* smem_stage = smem + kStages * L::kStageBytes + 256;   // 4 epilogue warps × 4 KB
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int mb_per_rank = p.rows_per_rank / CBM;
@@ -241,35 +242,45 @@ gemm_comm_kernel(const __grid_constant__ TmapArray tmaps_a, const __grid_constan
       decode(t, owner, m_blk, n_blk);
       if (!mbar_wait(&tmem_full[acc], acc_phase)) { *abort_flag = 1; atomicCAS(p.error_flag, 0, 15); break; }
       tc_fence_after();
-      const int row = m_blk * CBM + q * 32 + lane;
       const uint32_t t_row = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + acc * BN;
+      // The accumulator arrives one ROW per thread; global (and above all peer) stores want whole 128-byte lines.  Each warp
+      // turns 64 columns at a time through its 4 KB staging tile (16-byte units, XOR-swizzled against bank conflicts):
+      // written row-per-lane, read back with 8 lanes covering one row's 128 bytes, so that every store instruction
+      // writes four full lines.
+      const int row0 = m_blk * CBM + q * 32;                      // first row of this warp's 32
+      uint8_t* stage = smem_stage + q * 4096;
       // RS: the tile goes into slot `rank` of the destination's buffer (peer memory unless owner == rank)
-      __nv_bfloat16* c_row = (MODE == kAllGather)
-          ? reinterpret_cast<__nv_bfloat16*>(p.C) + static_cast<long long>(row) * p.ldc
+      __nv_bfloat16* c_base = (MODE == kAllGather)
+          ? reinterpret_cast<__nv_bfloat16*>(p.C) + static_cast<long long>(row0) * p.ldc
           : reinterpret_cast<__nv_bfloat16*>(p.partials.p[owner]) +
-                (static_cast<long long>(p.rank) * p.rows_per_rank + (row - owner * p.rows_per_rank)) * p.ldc;
+                (static_cast<long long>(p.rank) * p.rows_per_rank + (row0 - owner * p.rows_per_rank)) * p.ldc;
 #pragma unroll 1
-      for (int c = 0; c < BN / 32; ++c) {
-        uint32_t r[32];
-        tmem_ld_32x32(t_row + c * 32, r);
-        tmem_ld_wait();
-        const int col0 = n_blk * BN + c * 32;
-        if (row < p.M && col0 < p.N) {
-          __nv_bfloat16* dst = c_row + col0;
-          if (col0 + 32 <= p.N) {
+      for (int c2 = 0; c2 < BN / 64; ++c2) {
 #pragma unroll
-            for (int i = 0; i < 32; i += 8) {
-              uint4 o;
-              o.x = pack_bf16x2(__uint_as_float(r[i]), __uint_as_float(r[i + 1]));
-              o.y = pack_bf16x2(__uint_as_float(r[i + 2]), __uint_as_float(r[i + 3]));
-              o.z = pack_bf16x2(__uint_as_float(r[i + 4]), __uint_as_float(r[i + 5]));
-              o.w = pack_bf16x2(__uint_as_float(r[i + 6]), __uint_as_float(r[i + 7]));
-              *reinterpret_cast<uint4*>(dst + i) = o;
-            }
-          } else {
-            for (int i = 0; i < 32 && col0 + i < p.N; ++i) dst[i] = __float2bfloat16(__uint_as_float(r[i]));
+        for (int half = 0; half < 2; ++half) {
+          uint32_t r[32];
+          tmem_ld_32x32(t_row + c2 * 64 + half * 32, r);
+          tmem_ld_wait();
+#pragma unroll
+          for (int i = 0; i < 4; ++i) {
+            uint4 o;
+            o.x = pack_bf16x2(__uint_as_float(r[8 * i]), __uint_as_float(r[8 * i + 1]));
+            o.y = pack_bf16x2(__uint_as_float(r[8 * i + 2]), __uint_as_float(r[8 * i + 3]));
+            o.z = pack_bf16x2(__uint_as_float(r[8 * i + 4]), __uint_as_float(r[8 * i + 5]));
+            o.w = pack_bf16x2(__uint_as_float(r[8 * i + 6]), __uint_as_float(r[8 * i + 7]));
+            *reinterpret_cast<uint4*>(stage + lane * 128 + (((half * 4 + i) ^ (lane & 7)) << 4)) = o;
           }
         }
+        __syncwarp();
+        const int unit = lane & 7;
+        const int col = n_blk * BN + c2 * 64 + unit * 8;
+#pragma unroll
+        for (int k = 0; k < 8; ++k) {
+          const int rr = k * 4 + (lane >> 3);
+          const uint4 o = *reinterpret_cast<const uint4*>(stage + rr * 128 + ((unit ^ (rr & 7)) << 4));
+          if (row0 + rr < p.M && col < p.N) *reinterpret_cast<uint4*>(c_base + static_cast<long long>(rr) * p.ldc + col) = o;
+        }
+        __syncwarp();
       }
       tc_fence_before();
       __syncwarp();
@@ -362,7 +373,7 @@ MB_DEFINE_FABRIC_CONFIGURE(mb_gemm_comm_configure)
 // block_counters: [rows_per_rank·world / 128] ints (zeroed here).
 extern "C" int mb_ag_gemm(const long long* xg_ptrs, const void* W, void* Y, int* block_counters, int rows_per_rank, int N, int K,
                           int rank, int world, const long long* flag_ptrs, int channel, int epoch, int* error_flag, cudaStream_t s) {
-  if (world > kMaxRanks || rows_per_rank % CBM || K % 8) return -1;
+  if (world > kMaxRanks || rows_per_rank % CBM || K % 8 || N % 8) return -1;
   const int M = rows_per_rank * world;
   TmapArray ta;
   const int rc0 = make_tmap_bf16_2d(&ta.m[0], reinterpret_cast<const void*>(xg_ptrs[rank]), M, K, K, CBM, CBK);   // LOCAL memory only

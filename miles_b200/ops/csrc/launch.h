@@ -82,6 +82,10 @@ int mb_adamw(float* master, const float* grad, float* m, float* v, const float* 
 int mb_flash_fwd(const void* q, const void* k, const void* v, void* o, float* lse, const int* cu_seqlens, int batch, int max_seqlen,
                  int total_tokens, long long q_stride, long long k_stride, long long v_stride, int Hq, int Hkv, int D, float scale,
                  int causal, cudaStream_t s);
+int mb_flash_bwd_tc(const void* q, const void* k, const void* v, const void* dout, const float* lse, const float* delta, void* dq,
+                    void* dk, void* dv, const int* cu_seqlens, int batch, int max_seqlen, int total_tokens, long long q_stride,
+                    long long k_stride, long long v_stride, int Hq, int Hkv, float scale, int causal, int* error_flag, cudaStream_t s);
+int mb_attn_delta(const void* o, const void* dout, float* delta, int total_tokens, int Hq, int D, cudaStream_t s);
 int mb_flash_bwd(const void* q, const void* k, const void* v, const void* o, const void* dout, const float* lse, float* delta,
                  void* dq, void* dk, void* dv, const int* cu_seqlens, int batch, int max_seqlen, int total_tokens, long long q_stride,
                  long long k_stride, long long v_stride, int Hq, int Hkv, int D, float scale, int causal, cudaStream_t s);
@@ -139,6 +143,17 @@ int mb_adam_allgather(float* master, const float* grad_shard, float* m, float* v
 int mb_moe_dispatch(const void* x, const int* topk_idx, long long n_pairs, int k, int H, int e_local, int rank,
                     const long long* recv_x_ptrs, const long long* recv_meta_ptrs, const long long* counter_ptrs, int world,
                     int capacity, int* sent_row, int* err, cudaStream_t s);
+int mb_moe_dispatch_signal(const void* x, const int* topk_idx, long long n_pairs, int k, int H, int e_local, int rank,
+                           const long long* recv_x_ptrs, const long long* recv_meta_ptrs, const long long* counter_ptrs, int world,
+                           int capacity, int* sent_row, int* err, const long long* flag_ptrs, int channel, int* epochs, int* ticket,
+                           cudaStream_t s);
+int mb_moe_recv_align(const void* meta, int* counter, int capacity, int E, int* seg_offsets, int* tile_expert, int* row_src, int max_rows,
+                      int pad, const long long* flag_ptrs, int rank, int world, int channel, const int* epochs, int* err, cudaStream_t s);
+int mb_moe_return_signal(const void* y_perm, const int* row_src, const void* meta, const int* seg_offsets, int E, int H, int max_rows,
+                         const long long* ret_ptrs, int world, const long long* flag_ptrs, int rank, int channel, int* epochs, int* ticket,
+                         cudaStream_t s);
+int mb_moe_combine_wait(const void* ret, const float* w, const int* sent_row, void* out, long long T, int k, int H,
+                        const long long* flag_ptrs, int rank, int world, int channel, const int* epochs, int* err, cudaStream_t s);
 int mb_moe_scatter_known(const void* rows_in, int src_by_pair, const int* topk_idx, const int* sent_row, long long n_pairs, int k,
                          int H, int e_local, const long long* recv_x_ptrs, int world, cudaStream_t s);
 int mb_moe_return(const void* y_perm, const int* row_src, const void* meta, const int* seg_offsets, int E, int H, int max_rows,

@@ -15,6 +15,7 @@ from .cuda import BF16, C, _c, gemm_nn, gemm_nt, gemm_tn
 
 
 USE_TC_ATTENTION = os.environ.get("MILES_TC_ATTENTION", "1") != "0"
+USE_TC_ATTENTION_BWD = os.environ.get("MILES_TC_ATTENTION_BWD", "1") != "0"
 
 
 class _FlashAttn(torch.autograd.Function):
@@ -45,7 +46,13 @@ class _FlashAttn(torch.autograd.Function):
         dk = torch.empty(k.shape, dtype=k.dtype, device=k.device)
         dv = torch.empty(v.shape, dtype=v.dtype, device=v.device)
         delta = torch.empty_like(lse)
-        C.flash_bwd(q, k, v, o, do, lse, delta, dq, dk, dv, cu, ctx.max_seqlen, ctx.scale, ctx.causal)
+        D = q.shape[-1]
+        if (D == 128 and USE_TC_ATTENTION_BWD and q.stride(0) % 8 == 0 and k.stride(0) % 8 == 0 and v.stride(0) % 8 == 0
+                and q.stride(1) == D and k.stride(1) == D and v.stride(1) == D):
+            # tcgen05 backward: Sᵀ/dPᵀ and the dK, dV, dQ accumulators live in tensor memory
+            C.flash_bwd_tc(q, k, v, o, do, lse, delta, dq, dk, dv, cu, ctx.max_seqlen, ctx.scale, ctx.causal, C.error_flag(q))
+        else:
+            C.flash_bwd(q, k, v, o, do, lse, delta, dq, dk, dv, cu, ctx.max_seqlen, ctx.scale, ctx.causal)
         return dq, dk, dv, None, None, None
 
 

@@ -24,6 +24,7 @@ class RolloutComponents:
     client: Any
     executor: Any
     data_source: Any
+    controller: Any = None          # InferenceController over `engines`: memory hand-over, weight-update framing, health
 
 
 def create_parallel_state(args) -> ParallelState:
@@ -116,15 +117,40 @@ def create_rollout_components(args, ps: ParallelState, actor=None, tracker=None)
     if hasattr(data_source, "gen"):
         cell = getattr(args, "indep_dp_cell_id", 0)
         data_source.gen.manual_seed(args.rollout_seed * 9973 + rollout_dp_rank + 7919 * cell)
-    return RolloutComponents(engines=engines, client=client, executor=ex, data_source=data_source)
+    controller = None
+    if engines:
+        from .inference_controller import InferenceController, ServerCell, ServerGroup
+
+        group = ServerGroup("regular", max(1, ps.tp_size), max(1, ps.tp_size))
+        controller = InferenceController([ServerCell(e, "default", group) for e in engines],
+                                         probe=lambda e: e.health().get("status") == "ok")
+    return RolloutComponents(engines=engines, client=client, executor=ex, data_source=data_source, controller=controller)
 
 
 def update_weights(args, actor, rollout: RolloutComponents, updater=None) -> dict:
-    """start → actor.update_weights → end; publishes the new weight version to the executor."""
+    """start_update_weights (pause + flush under the controller's lock) → actor.update_weights → end_update_weights
+    (version label + resume; engines resume on their old version when the transfer failed), then the new weight version is
+    published to the executor (reference: miles/ray/placement_group.py:371-404)."""
     from ..weight_update.updater import WeightUpdater
 
     updater = updater or WeightUpdater(args, actor, rollout.engines)
-    info = actor.update_weights(updater)
+    ctl = getattr(rollout, "controller", None)
+    if ctl is None:
+        info = actor.update_weights(updater)
+    else:
+        ctl.tick()                                         # quarantine engines that stopped answering before talking to them
+        targets = ctl.start_update_weights()
+        ok = False
+        try:
+            updater.framed = True                          # the controller owns pause / flush / resume for this transfer
+            updater.engines = list(targets) or updater.engines
+            info = actor.update_weights(updater)
+            ok = True
+        finally:
+            updater.framed = False
+            ctl.end_update_weights(actor.weight_version, ok=ok)
+        for e in ctl.stale_engines():                      # re-admitted engines that missed updates are now in line
+            ctl.mark_synced(e)
     rollout.executor.set_weight_version(actor.weight_version)
     if getattr(args, "audit_dir", None):
         _audit_weights(args, actor, rollout, info)

@@ -38,6 +38,11 @@ class _Buffers:
         self.n_recv = torch.zeros(1, dtype=torch.int32, device=fab.device)
         self.pair_ids = torch.arange(self.max_pairs, dtype=torch.int32, device=fab.device)
         self.minus_one = torch.full((), -1, dtype=torch.int32, device=fab.device)
+        self.tickets = torch.zeros(2, dtype=torch.int32, device=fab.device)     # last-block tickets of the signalling kernels
+        key = (tuple(ranks), "raw")
+        if key not in fab._flag_ptrs:
+            fab._flag_ptrs[key] = fab.flags.ptrs(ranks)
+        self.flag_ptrs = fab._flag_ptrs[key]
 
 
 def _buffers(fab, H, k, ps, T) -> _Buffers:
@@ -49,6 +54,34 @@ def _buffers(fab, H, k, ps, T) -> _Buffers:
         fab._moe[key] = b
     assert T * k <= b.max_pairs, f"{T} tokens exceed the fabric's MoE buffers (set fabric.moe_max_tokens before first use)"
     return b
+
+
+import os
+
+# decode path: cross-rank barriers folded into the kernels on either side of them (MILES_EP_FOLDED=0 keeps the barrier kernels)
+FOLDED_BARRIERS = os.environ.get("MILES_EP_FOLDED", "1") != "0"
+
+
+def _decode_path(C, fab, b, x, w13, w2, wf, idx32, sent_row, cap, T, H, k, e_local, ep, me):
+    """Inference with the same row count on every rank (the engine's agreed decode bucket): 8 launches per layer —
+    dispatch+signal, wait+count+sort, gather, W13, SwiGLU, W2, return+signal, wait+combine."""
+    n_pairs = T * k
+    dev = x.device
+    C.moe_dispatch_signal(x, idx32, k, e_local, me, b.recv_x_ptrs, b.recv_meta_ptrs, b.counter_ptrs, ep, b.cap, sent_row, fab.err,
+                          b.flag_ptrs, CH_EP, fab.epochs, b.tickets[0:1])
+    bt = small_moe_bt(n_pairs, e_local, w13, w2)
+    max_rows = moe_max_rows_pad(cap, e_local, bt)
+    seg = torch.empty(e_local + 1, dtype=torch.int32, device=dev)
+    tile = torch.empty(max_rows // bt, dtype=torch.int32, device=dev)
+    row_src = torch.empty(max_rows, dtype=torch.int32, device=dev)
+    C.moe_recv_align(b.recv_meta, b.counter, cap, e_local, seg, tile, row_src, bt, b.flag_ptrs, me, ep, CH_EP, fab.epochs, fab.err)
+    x_perm = torch.empty(max_rows, H, dtype=x.dtype, device=dev)
+    C.moe_gather(b.recv_x.view(b.cap, H), x_perm, row_src, seg, 1)
+    _, y_perm = experts_forward(x_perm, w13, w2, seg, tile, bt)
+    C.moe_return_signal(y_perm, row_src, b.recv_meta, seg, b.ret_ptrs, ep, b.flag_ptrs, me, CH_EP2, fab.epochs, b.tickets[1:2])
+    out = torch.empty(T, H, dtype=x.dtype, device=dev)
+    C.moe_combine_wait(b.ret.view(b.max_pairs, H), wf, sent_row, out, k, b.flag_ptrs, me, ep, CH_EP2, fab.epochs, fab.err)
+    return out
 
 
 class _FusedMoE(torch.autograd.Function):
@@ -66,6 +99,10 @@ class _FusedMoE(torch.autograd.Function):
         wf = topk_w.float().contiguous()
         n_pairs = T * k
         sent_row = torch.empty(max(n_pairs, 1), dtype=torch.int32, device=x.device)
+        if not grad_mode and getattr(ps, "moe_uniform_tokens", False):
+            small_cap = min(b.cap, (ep * max(n_pairs, 1) + 127) // 128 * 128)
+            if small_cap <= 16384 and FOLDED_BARRIERS:
+                return _decode_path(C, fab, b, x, w13, w2, wf, idx32, sent_row, small_cap, T, H, k, e_local, ep, me)
         if n_pairs:
             C.moe_dispatch(x, idx32, k, e_local, me, b.recv_x_ptrs, b.recv_meta_ptrs, b.counter_ptrs, ep, b.cap, sent_row, fab.err)
         fab.barrier(ranks, CH_EP)

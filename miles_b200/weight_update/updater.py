@@ -62,6 +62,7 @@ class WeightUpdater:
         self.cli_mode = mode
         self.mode = impl
         self.quant = quant
+        self.framed = False          # True while a controller frames the transfer (it pauses, flushes and resumes the engines)
         self._delta_writer = None
         self._delta_readers: dict[int, Any] = {}
         self.last_seconds = 0.0
@@ -78,9 +79,10 @@ class WeightUpdater:
     def update_weights(self) -> dict:
         t0 = time.perf_counter()
         version = self.actor.weight_version
-        for e in self.engines:
-            e.pause_generation("retract")
-            e.flush_cache()
+        if not self.framed:
+            for e in self.engines:
+                e.pause_generation("retract")
+                e.flush_cache()
         self._barrier()
         t1 = time.perf_counter()
         ok = False
@@ -94,15 +96,16 @@ class WeightUpdater:
             ok = True
         finally:
             # a failed transfer must not leave the engines paused: they resume on the version they hold
-            if not ok:
+            if not ok and not self.framed:
                 for e in self.engines:
                     e.continue_generation()
         self._barrier()
         t2 = time.perf_counter()
-        for e in self.engines:
-            e.update_weight_version(version)
-            e.continue_generation()
-        if getattr(self.args, "ci_test", False):
+        if not self.framed:
+            for e in self.engines:
+                e.update_weight_version(version)
+                e.continue_generation()
+        if getattr(self.args, "ci_test", False) and not self.framed:
             for e in self.engines:
                 assert e.get_weight_version() == version, "engine weight version differs from the trainer's"
         if getattr(self.args, "check_weight_update_equal", False):

@@ -45,6 +45,44 @@ def test_flash_attention_fwd_bwd(D, lens, heads):
     assert _rel(qkv.grad, xf.grad) < 3e-2, _rel(qkv.grad, xf.grad)
 
 
+@pytest.mark.parametrize("causal", [True, False])
+@pytest.mark.parametrize("lens", [[1], [127], [128], [129], [4096], [300, 1, 129, 64, 1000]])
+@pytest.mark.parametrize("heads", [(8, 1), (4, 4)])
+def test_flash_attention_bwd_tcgen05_vs_fp32(lens, heads, causal):
+    """The tcgen05 backward (head_dim 128) against fp32 autograd, and against the mma.sync backward it replaces."""
+    from miles_b200.ops import cuda_more
+
+    torch.manual_seed(1)
+    Hq, Hkv = heads
+    D, T = 128, sum(lens)
+    cu = torch.tensor([0] + list(torch.tensor(lens).cumsum(0)), dtype=torch.int32, device="cuda")
+    grads = {}
+    for tc in (True, False):
+        cuda_more.USE_TC_ATTENTION_BWD = tc
+        try:
+            qkv = (0.5 * torch.randn(T, (Hq + 2 * Hkv) * D, device="cuda", generator=torch.Generator(device="cuda").manual_seed(3))
+                   ).to(torch.bfloat16).requires_grad_()
+            q, k, v = qkv.split([Hq * D, Hkv * D, Hkv * D], dim=-1)
+            o = cuda_more._FlashAttn.apply(q.view(T, Hq, D), k.view(T, Hkv, D), v.view(T, Hkv, D), cu, max(lens), causal)
+            g = torch.randn(o.shape, device="cuda", generator=torch.Generator(device="cuda").manual_seed(4)).to(torch.bfloat16)
+            o.backward(g)
+            grads[tc] = qkv.grad.clone()
+        finally:
+            cuda_more.USE_TC_ATTENTION_BWD = True
+    assert _k().check_error_flag() == 0
+    xf = qkv.detach().float().requires_grad_()
+    qf, kf, vf = xf.split([Hq * D, Hkv * D, Hkv * D], dim=-1)
+    of = _attn_ref(qf.view(T, Hq, D), kf.view(T, Hkv, D), vf.view(T, Hkv, D), cu, causal)
+    of.backward(g.float())
+    for name, lo, hi in (("dq", 0, Hq * D), ("dk", Hq * D, (Hq + Hkv) * D), ("dv", (Hq + Hkv) * D, (Hq + 2 * Hkv) * D)):
+        want = xf.grad[:, lo:hi]
+        if want.norm() < 1e-4:         # a single-key softmax has no gradient towards q and k: only rounding noise may remain
+            assert grads[True][:, lo:hi].float().abs().max() < 1e-4, name
+            continue
+        assert _rel(grads[True][:, lo:hi], want) < 3e-2, (name, _rel(grads[True][:, lo:hi], want))
+        assert _rel(grads[True][:, lo:hi], grads[False][:, lo:hi]) < 3e-2, (name, "vs mma.sync")
+
+
 @pytest.mark.parametrize("D,Hq,Hkv", [(128, 32, 4), (128, 8, 8), (64, 4, 2)])
 def test_paged_decode(D, Hq, Hkv):
     torch.manual_seed(1)

@@ -47,9 +47,7 @@ def train(args):
             tracker.log(pack.metrics, rollout_id)
             continue
         if args.colocate and args.offload_rollout:
-            for e in rollout.engines:
-                e.pause_generation("retract")
-                e.release_memory_occupation(["kv_cache", "cuda_graph"])
+            rollout.controller.offload(("kv_cache", "cuda_graph"))
         shard = object_store.get(pack.data_ref)
         metrics = dict(pack.metrics)
         if critic is not None:
@@ -68,16 +66,11 @@ def train(args):
 
         if args.offload_train:
             actor.sleep()
-        if args.colocate and args.offload_rollout:
-            for e in rollout.engines:
-                e.resume_memory_occupation(["weights"])
         if _should(args.update_weights_interval, rollout_id):
             info = update_weights(args, actor, rollout)
             metrics["perf/update_weights_time"] = info["seconds"]
         if args.colocate and args.offload_rollout:
-            for e in rollout.engines:
-                e.resume_memory_occupation(["kv_cache", "cuda_graph"])
-                e.continue_generation()
+            rollout.controller.onload(("weights", "kv_cache", "cuda_graph"))
         if _should(args.eval_interval, rollout_id):
             metrics.update(rollout.executor.eval(rollout_id))
         tracker.log(metrics, rollout_id)
