@@ -216,6 +216,13 @@ void multi_copy(const at::Tensor& table, const at::Tensor& prefix, int64_t total
   check(mb_multi_copy(lptr(table), lptr(prefix), table.size(0), total_chunks, cur_stream()), "mb_multi_copy");
 }
 
+// rectangles {src, dst, rows, row_bytes, src_pitch, dst_pitch}: the resharding copy (dst may be a peer GPU's buffer)
+void multi_copy2d(const at::Tensor& table, const at::Tensor& prefix, int64_t total_items, bool qdq) {
+  c10::cuda::CUDAGuard g(table.device());
+  TORCH_CHECK(table.dim() == 2 && table.size(1) == 6, "multi_copy2d: table must be [n, 6]");
+  check(mb_multi_copy2d(lptr(table), lptr(prefix), table.size(0), total_items, qdq ? 1 : 0, cur_stream()), "mb_multi_copy2d");
+}
+
 void multi_mxfp8(const at::Tensor& table, const at::Tensor& prefix, int64_t total_chunks, bool qdq) {
   c10::cuda::CUDAGuard g(table.device());
   check(mb_multi_mxfp8(lptr(table), lptr(prefix), table.size(0), total_chunks, qdq, cur_stream()), "mb_multi_mxfp8");
@@ -226,6 +233,7 @@ void multi_mxfp8(const at::Tensor& table, const at::Tensor& prefix, int64_t tota
 void register_fabric(pybind11::module& m) {
   m.def("multi_copy", &multi_copy);
   m.def("multi_mxfp8", &multi_mxfp8);
+  m.def("multi_copy2d", &multi_copy2d);
   m.def("ag_gemm", &ag_gemm);
   m.def("fabric_configure", &fabric_configure);
   m.def("gemm_rs", &gemm_rs);

@@ -186,6 +186,7 @@ int mb_sparse_attention_fwd(const void* q, const void* k, const void* v, const i
 
 // ---- weight_sync.cu (one launch per bucket of tensors; dst may be peer memory) ----
 int mb_multi_copy(const long long* table, const long long* prefix, int n, long long total_chunks, cudaStream_t s);
+int mb_multi_copy2d(const long long* table, const long long* prefix, int n, long long total_items, int qdq, cudaStream_t s);
 int mb_multi_mxfp8(const long long* table, const long long* prefix, int n, long long total_chunks, int qdq, cudaStream_t s);
 
 // ---- gemm_comm.cu ----

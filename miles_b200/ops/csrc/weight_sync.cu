@@ -125,6 +125,80 @@ __global__ void __launch_bounds__(256) multi_mxfp8_kernel(const Desc* __restrict
   }
 }
 
+// ---- resharding copy: rectangles between tensors of different row pitch ---------------------------------------------------
+// One descriptor = one rectangle of a 2-D view: `rows` rows of `row_bytes` bytes, source rows `src_pitch` bytes apart,
+// destination rows `dst_pitch` apart.  A tensor-parallel shard that becomes part of a differently sharded (or unsharded)
+// tensor is one or a few such rectangles: a dim-0 shard is a block of whole rows, a dim-1 shard a column band of every
+// row, a [q; k; v] or [gate; up] stacking three or two row blocks.  A work item is a group of rows of about 16 KB.
+// QDQ: bf16 rows go through MXFP8 (1×32 blocks along the row, e8m0 scale) on the way, so the destination holds the values
+// the block-quantised model would compute with; row_bytes must then be a multiple of 64.
+struct Desc2 {
+  long long src, dst, rows, row_bytes, src_pitch, dst_pitch;
+};
+
+__device__ __forceinline__ long long rows_per_item(long long row_bytes) {
+  const long long r = kChunkBytes / (row_bytes > 0 ? row_bytes : 1);
+  return r > 0 ? r : 1;
+}
+
+template <bool QDQ>
+__global__ void __launch_bounds__(256) multi_copy2d_kernel(const Desc2* __restrict__ table, const long long* __restrict__ prefix, int n) {
+  const long long total = prefix[n];
+  for (long long c = blockIdx.x; c < total; c += gridDim.x) {
+    const int d = find_desc(prefix, n, c);
+    const Desc2 t = table[d];
+    const long long rpi = rows_per_item(t.row_bytes);
+    const long long r0 = (c - prefix[d]) * rpi;
+    const long long r1 = min(t.rows, r0 + rpi);
+    const bool vec = ((t.src | t.dst | t.row_bytes | t.src_pitch | t.dst_pitch) & 15) == 0;
+    if (QDQ) {
+      const long long blocks_per_row = t.row_bytes / 64;                 // 32 bf16 per block
+      const long long items = (r1 - r0) * blocks_per_row;
+      for (long long i = threadIdx.x; i < items; i += 256) {
+        const long long r = r0 + i / blocks_per_row, b = i % blocks_per_row;
+        const bf16* x = reinterpret_cast<const bf16*>(reinterpret_cast<const char*>(t.src) + r * t.src_pitch) + b * 32;
+        bf16* y = reinterpret_cast<bf16*>(reinterpret_cast<char*>(t.dst) + r * t.dst_pitch) + b * 32;
+        float v[32];
+#pragma unroll
+        for (int k = 0; k < 4; ++k) ld8(x + k * 8, v + k * 8);
+        float amax = 0.f;
+#pragma unroll
+        for (int k = 0; k < 32; ++k) amax = fmaxf(amax, fabsf(v[k]));
+        const int e = e8m0_for(amax);
+        const float inv_scale = __uint_as_float(static_cast<uint32_t>(254 - e) << 23);
+        const float scale = __uint_as_float(static_cast<uint32_t>(max(e, 1)) << 23);
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+          __nv_bfloat162 o[4];
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            const __nv_fp8x2_storage_t pair = __nv_cvt_float2_to_fp8x2(
+                make_float2(v[8 * k + 2 * j] * inv_scale, v[8 * k + 2 * j + 1] * inv_scale), __NV_SATFINITE, __NV_E4M3);
+            const __half2_raw hr = __nv_cvt_fp8x2_to_halfraw2(pair, __NV_E4M3);
+            const float2 f = __half22float2(*reinterpret_cast<const __half2*>(&hr));
+            o[j] = __floats2bfloat162_rn(f.x * scale, f.y * scale);
+          }
+          reinterpret_cast<uint4*>(y)[k] = *reinterpret_cast<const uint4*>(o);
+        }
+      }
+    } else if (vec) {
+      const long long vpr = t.row_bytes >> 4;
+      const long long items = (r1 - r0) * vpr;
+      for (long long i = threadIdx.x; i < items; i += 256) {
+        const long long r = r0 + i / vpr, v = i % vpr;
+        reinterpret_cast<uint4*>(reinterpret_cast<char*>(t.dst) + r * t.dst_pitch)[v] =
+            reinterpret_cast<const uint4*>(reinterpret_cast<const char*>(t.src) + r * t.src_pitch)[v];
+      }
+    } else {
+      const long long items = (r1 - r0) * t.row_bytes;
+      for (long long i = threadIdx.x; i < items; i += 256) {
+        const long long r = r0 + i / t.row_bytes, b = i % t.row_bytes;
+        (reinterpret_cast<char*>(t.dst) + r * t.dst_pitch)[b] = (reinterpret_cast<const char*>(t.src) + r * t.src_pitch)[b];
+      }
+    }
+  }
+}
+
 int grid_for(long long total) { return static_cast<int>(total < 148 * 8 ? (total > 0 ? total : 1) : 148 * 8); }
 
 }  // namespace
@@ -146,5 +220,16 @@ extern "C" int mb_multi_mxfp8(const long long* table, const long long* prefix, i
     mb::multi_mxfp8_kernel<true><<<mb::grid_for(total_chunks), 256, 0, s>>>(reinterpret_cast<const mb::Desc*>(table), prefix, n);
   else
     mb::multi_mxfp8_kernel<false><<<mb::grid_for(total_chunks), 256, 0, s>>>(reinterpret_cast<const mb::Desc*>(table), prefix, n);
+  return static_cast<int>(cudaGetLastError());
+}
+
+// table: device int64 [n, 6] = {src, dst, rows, row_bytes, src_pitch, dst_pitch}; prefix: device int64 [n+1] offsets of work items
+// (a work item = max(1, 16384 / row_bytes) rows); qdq: rows go through MXFP8 on the way (bf16 in, bf16 out)
+extern "C" int mb_multi_copy2d(const long long* table, const long long* prefix, int n, long long total_items, int qdq, cudaStream_t s) {
+  if (n == 0 || total_items == 0) return 0;
+  if (qdq)
+    mb::multi_copy2d_kernel<true><<<mb::grid_for(total_items), 256, 0, s>>>(reinterpret_cast<const mb::Desc2*>(table), prefix, n);
+  else
+    mb::multi_copy2d_kernel<false><<<mb::grid_for(total_items), 256, 0, s>>>(reinterpret_cast<const mb::Desc2*>(table), prefix, n);
   return static_cast<int>(cudaGetLastError());
 }

@@ -58,8 +58,11 @@ def _buffers(fab, H, k, ps, T) -> _Buffers:
 
 import os
 
-# decode path: cross-rank barriers folded into the kernels on either side of them (MILES_EP_FOLDED=0 keeps the barrier kernels)
-FOLDED_BARRIERS = os.environ.get("MILES_EP_FOLDED", "1") != "0"
+# Decode path variant with the cross-rank barriers folded into the kernels on either side of them (8 launches per layer
+# instead of 11).  Measured on 2 GPUs it is 4 % SLOWER than the separate one-block barrier kernels (1.63 vs 1.57 ms for 12
+# layers at 8 rows per rank: the signalling epilogue and the in-kernel wait lengthen kernels on the critical path by more
+# than the three launches they remove), so it is off unless MILES_EP_FOLDED=1.
+FOLDED_BARRIERS = os.environ.get("MILES_EP_FOLDED", "0") == "1"
 
 
 def _decode_path(C, fab, b, x, w13, w2, wf, idx32, sent_row, cap, T, H, k, e_local, ep, me):

@@ -45,7 +45,7 @@ class WeightUpdater:
             if all(getattr(e, "model", None) is actor.model for e in self.engines):
                 mode = "alias"
             elif all(hasattr(e, "model") for e in self.engines) and actor.device.type == "cuda" and \
-                    all(_same_layout(e, actor) for e in self.engines):
+                    all(_same_layout(e, actor) or _can_reshard(e, actor) for e in self.engines):
                 mode = "nvlink"
             else:
                 mode = "tensor"
@@ -63,6 +63,7 @@ class WeightUpdater:
         self.mode = impl
         self.quant = quant
         self.framed = False          # True while a controller frames the transfer (it pauses, flushes and resumes the engines)
+        self._reshard_plans: dict[int, Any] = {}
         self._delta_writer = None
         self._delta_readers: dict[int, Any] = {}
         self.last_seconds = 0.0
@@ -128,8 +129,19 @@ class WeightUpdater:
         from ..parallel import weight_sync
 
         n = 0
-        for e in self.engines:
-            n += weight_sync.fused_weight_sync(self.actor, e, quant=self.quant)
+        for i, e in enumerate(self.engines):
+            if _same_layout(e, self.actor):
+                n += weight_sync.fused_weight_sync(self.actor, e, quant=self.quant)
+                continue
+            # different TP / EP layout: every trainer rank stores the rectangles of its shards straight into the shards of
+            # every engine rank (peer memory), one kernel per transfer, no gathered full tensors
+            assert _can_reshard(e, self.actor), "resharding sync needs the NVLink fabric and an in-process engine on every rank"
+            plan = self._reshard_plans.get(i)
+            if plan is None:
+                from ..parallel.reshard import ReshardPlan
+
+                plan = self._reshard_plans[i] = ReshardPlan(self.actor, e, self.actor.ps.fabric, quant=self.quant)
+            n += plan.run()
         return n
 
     def _send_tensor(self) -> int:
@@ -204,6 +216,12 @@ class WeightUpdater:
 # command-line name → protocol implemented here
 CLI_MODES = {"alias": "alias", "nvlink": "nvlink", "tensor": "tensor", "broadcast": "broadcast", "disk": "disk", "delta": "delta",
              "broadcast_packed": "broadcast", "cuda_ipc": "tensor", "p2p": "nvlink"}
+
+
+def _can_reshard(engine, actor) -> bool:
+    ps = getattr(actor, "ps", None)
+    return (ps is not None and getattr(ps, "fabric", None) is not None and hasattr(engine, "model")
+            and engine.model is not actor.model and ps.pp_size == 1 and getattr(engine.ps, "pp_size", 1) == 1)
 
 
 def _same_layout(engine, actor) -> bool:

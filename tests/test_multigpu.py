@@ -365,3 +365,9 @@ def test_allreduce_add_rmsnorm(world):
 @pytest.mark.parametrize("world", WORLDS)
 def test_engine_tp_allreduce_fused_into_rmsnorm(world):
     _run("_case_engine_tp_fused_allreduce", world, timeout=240)
+
+
+def _case_reshard_proxy(rank, world):
+    import test_reshard
+
+    test_reshard._case_reshard(rank, world)
