@@ -37,6 +37,9 @@ def build_parser() -> argparse.ArgumentParser:
     _bool_flag(g, "--colocate", help="trainer and rollout engine share the same GPUs")
     _bool_flag(g, "--offload-train")
     _bool_flag(g, "--offload-rollout")
+    g.add_argument("--offload-train-mode", choices=["vmm", "move"], default="vmm",
+                   help="vmm: optimizer state in a CUDA-VMM arena whose pages are released at stable addresses (falls back to "
+                        "move where the native runtime or the driver's VMM is missing); move: copy tensors to pinned host memory")
     _bool_flag(g, "--offload", help="shorthand for --offload-train --offload-rollout")
     g.add_argument("--worker-comm-backend", choices=["inproc", "rpc"], default="inproc")
 
@@ -308,6 +311,15 @@ def build_parser() -> argparse.ArgumentParser:
     _bool_flag(g, "--check-weight-update-equal")
     _bool_flag(g, "--debug-deterministic-collective")
     _bool_flag(g, "--ci-test")
+    g.add_argument("--ft-max-attempts", type=int, default=30, help="retries of a failed trainer call under --use-fault-tolerance")
+    g.add_argument("--ft-heartbeat-timeout", type=float, default=60.0)
+    _bool_flag(g, "--true-on-policy-mode", help="pin every source of train / rollout numeric divergence (see utils/true_on_policy)")
+    g.add_argument("--snapshot-dir", type=str, default=None,
+                   help="publish a full HF safetensors snapshot of the policy here every --snapshot-interval weight updates")
+    g.add_argument("--snapshot-interval", type=int, default=1)
+    g.add_argument("--snapshot-keep", type=int, default=2)
+    g.add_argument("--optimizer-nvme-dir", type=str, default=None,
+                   help="stream fp32 master weights and Adam moments from files in this directory (state larger than HBM + host)")
     g.add_argument("--audit-dir", type=str, default=None,
                    help="write the audit event log here (weight checksums per version; analyse with miles_b200.audit.events)")
     g.add_argument("--ci-save-grad-norm", type=str, default=None)
@@ -395,6 +407,10 @@ def validate_args(args) -> None:
         args.eps_clip_high = args.eps_clip
     if args.use_fault_tolerance:
         args.indep_dp = args.indep_dp or "train" in (args.ft_components or [])
+    if getattr(args, "true_on_policy_mode", False):
+        from .utils import true_on_policy
+
+        args.true_on_policy_contracts = true_on_policy.apply(args)
     args.rewards_normalization = not args.disable_rewards_normalization
     args.grpo_std_normalization = not args.disable_grpo_std_normalization
     if args.use_rollout_routing_replay:

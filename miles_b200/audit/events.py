@@ -78,8 +78,11 @@ class DataWitness:
         self.logger = logger
         self._next = 0
 
-    def allocate(self, rollout_id: int, n: int) -> list[int]:
-        ids = list(range(self._next, self._next + n))
+    def allocate(self, rollout_id: int, n: int, namespace: int = 0) -> list[int]:
+        """`namespace` keeps ids of allocators that run side by side apart (one per rollout rank when every rank trains on
+        what it generated)."""
+        base = (int(namespace) << 40) + self._next
+        ids = list(range(base, base + n))
         self._next += n
         self.logger.log("witness_allocated", rollout_id=rollout_id, ids=ids)
         return ids

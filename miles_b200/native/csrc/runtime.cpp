@@ -110,6 +110,8 @@ struct Driver {
   CUresult (*cuMemcpyDtoH)(void*, CUdeviceptr, size_t) = nullptr;
   CUresult (*cuMemcpyHtoD)(CUdeviceptr, const void*, size_t) = nullptr;
   CUresult (*cuCtxSynchronize)() = nullptr;
+  CUresult (*cuMemHostAlloc)(void**, size_t, unsigned) = nullptr;
+  CUresult (*cuMemFreeHost)(void*) = nullptr;
   bool ok = false;
 };
 
@@ -132,6 +134,8 @@ static Driver& driver() {
     LOAD(cuMemcpyDtoH, "cuMemcpyDtoH_v2");
     LOAD(cuMemcpyHtoD, "cuMemcpyHtoD_v2");
     LOAD(cuCtxSynchronize, "cuCtxSynchronize");
+    LOAD(cuMemHostAlloc, "cuMemHostAlloc");
+    LOAD(cuMemFreeHost, "cuMemFreeHost");
 #undef LOAD
     d.ok = d.cuInit && d.cuMemCreate && d.cuMemMap && d.cuMemAddressReserve && d.cuMemSetAccess && d.cuMemUnmap &&
            d.cuMemRelease && d.cuMemGetAllocationGranularity && d.cuMemcpyDtoH && d.cuMemcpyHtoD;
@@ -152,7 +156,26 @@ struct Region {
   bool mapped = false;
   std::string tag;
   void* host_copy = nullptr;
+  bool host_pinned = false;      // the saved copy lives in page-locked memory (copies run at PCIe rate)
 };
+
+static void* host_alloc(Region& r) {
+  Driver& d = driver();
+  void* p = nullptr;
+  if (d.cuMemHostAlloc && d.cuMemFreeHost && d.cuMemHostAlloc(&p, r.size, 0) == 0 && p) {
+    r.host_pinned = true;
+    return p;
+  }
+  r.host_pinned = false;
+  return malloc(r.size);
+}
+
+static void host_free(Region& r) {
+  if (!r.host_copy) return;
+  if (r.host_pinned) driver().cuMemFreeHost(r.host_copy);
+  else free(r.host_copy);
+  r.host_copy = nullptr;
+}
 
 struct VmmArena {
   int device = 0;
@@ -223,7 +246,7 @@ int32_t mbrt_arena_free(void* h, uint64_t ptr) {
     d.cuMemRelease(r.handle);
     a->mapped_bytes -= r.size;
   }
-  if (r.host_copy) free(r.host_copy);
+  host_free(r);
   d.cuMemAddressFree(r.va, r.size);
   a->regions.erase(it);
   return 0;
@@ -241,7 +264,7 @@ int64_t mbrt_arena_pause(void* h, const char* tag, int32_t keep_contents) {
     Region& r = kv.second;
     if (!r.mapped || (tag && tag[0] && r.tag != tag)) continue;
     if (keep_contents) {
-      r.host_copy = malloc(r.size);
+      r.host_copy = host_alloc(r);
       if (!r.host_copy || d.cuMemcpyDtoH(r.host_copy, r.va, r.size) != 0) return -1;
     }
     d.cuMemUnmap(r.va, r.size);
@@ -264,8 +287,7 @@ int64_t mbrt_arena_resume(void* h, const char* tag) {
     if (map_region(a, r) != 0) return -1;
     if (r.host_copy) {
       if (d.cuMemcpyHtoD(r.va, r.host_copy, r.size) != 0) return -2;
-      free(r.host_copy);
-      r.host_copy = nullptr;
+      host_free(r);
     }
     restored += static_cast<int64_t>(r.size);
   }

@@ -76,7 +76,17 @@ class RolloutExecutor:
             path = args.save_debug_rollout_data.format(rollout_id=rollout_id)
             os.makedirs(os.path.dirname(path) or ".", exist_ok=True)
             torch.save({"rollout_id": rollout_id, "samples": [[s.to_dict() for s in g] for g in groups]}, path)
+        witness = getattr(self, "witness", None)
+        if witness is None and getattr(args, "audit_dir", None):
+            from ..audit.events import DataWitness, EventLogger
+
+            rank = dist.get_rank() if dist.is_initialized() else 0
+            witness = self.witness = DataWitness(EventLogger(args.audit_dir, "rollout", rank))
         data = convert_samples_to_train_data(args, groups)
+        if witness is not None:
+            # every sample of the batch gets an id here and the trainer reports the ids it consumed: the audit analyser
+            # then proves that no sample was dropped or trained on twice
+            data["witness_ids"] = witness.allocate(rollout_id, len(data["tokens"]), namespace=self.rollout_dp_rank if local else 0)
         metrics.update(self._rollout_metrics(groups, data, time.time() - t0))
         metrics["perf/generate_time"] = t_gen
         if local:

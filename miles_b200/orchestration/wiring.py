@@ -66,6 +66,80 @@ def create_training_models(args, ps: ParallelState):
     return actor, critic, start
 
 
+class TrainerController:
+    """Driver-side handle of the trainer (reference: `TrainerController`, miles/ray/train/group.py:52-685).  Without
+    `--use-fault-tolerance` calls go straight to this rank's `TrainActor`.  With it the actor is a `Cell` of a
+    `CellController`: a call that raises is retried (`--ft-max-attempts`, the reference retries 30 times) after the
+    cell's state was rolled back by `recover`, the membership epoch is published, and every step leaves a heartbeat in
+    the job's store when one is configured (`--indep-dp-store`), which is what the health checker of the other cells and of
+    an external supervisor read."""
+
+    def __init__(self, args, actor):
+        self.args, self.actor = args, actor
+        self.cells = None
+        self.monitor = None
+        if getattr(args, "use_fault_tolerance", False):
+            from ..ft.controller import Cell, CellController, HeartbeatMonitor
+
+            cell_id = getattr(args, "indep_dp_cell_id", 0) or 0
+            self.cells = CellController([Cell(cell_id, [_RetryableActor(actor)])], min_quorum=1,
+                                        max_attempts=getattr(args, "ft_max_attempts", 30) or 30)
+            store = getattr(actor, "cell_store", None)
+            if store is not None:
+                self.monitor = HeartbeatMonitor(store, timeout_s=getattr(args, "ft_heartbeat_timeout", 60.0) or 60.0)
+            self.worker_id = f"cell{cell_id}/rank{actor.ps.rank}"
+
+    def train(self, rollout_id: int, shard: dict) -> dict:
+        if self.cells is None:
+            return self.actor.train(rollout_id, shard)
+        if self.monitor is not None:
+            self.monitor.beat(self.worker_id)
+        # one local cell: a failed attempt fences it (min_quorum = 1 makes `execute` give up at once); the worker is this very
+        # process, still alive after a host-side exception, so it is re-admitted (`heal`) and the step is tried again
+        last = None
+        for _ in range(self.cells.max_attempts):
+            try:
+                out = self.cells.execute("train", rollout_id, shard)
+                return next(iter(out.values()))[0]
+            except RuntimeError as e:
+                last = e
+                dead = [c for c in self.cells.cells.values() if c not in self.cells.alive()]
+                if not dead:
+                    raise
+                for c in dead:
+                    self.cells.heal(c.cell_id, [_RetryableActor(self.actor)])
+        raise RuntimeError(f"train did not succeed in {self.cells.max_attempts} attempts") from last
+
+    def __getattr__(self, name):
+        return getattr(self.actor, name)
+
+
+class _RetryableActor:
+    """A worker handle whose failed call leaves the trainer where it was: gradients cleared, nothing half applied."""
+
+    def __init__(self, actor):
+        self.actor = actor
+
+    def init(self, *a, **kw):
+        return None            # the actor of this process is initialised by `create_training_models`
+
+    def train(self, rollout_id, shard):
+        try:
+            return self.actor.train(rollout_id, shard)
+        except BaseException:
+            self.actor.optimizer.zero_grad()
+            shard.pop("advantages", None)
+            shard.pop("returns", None)
+            raise
+
+    def kill(self):
+        return None            # fencing a cell of ONE process means not calling it again; the controller does that
+
+
+def create_trainer_controller(args, actor) -> TrainerController:
+    return TrainerController(args, actor)
+
+
 def create_rollout_components(args, ps: ParallelState, actor=None, tracker=None) -> RolloutComponents:
     from ..engine.engine import Engine
     from ..rollout.client import HttpEngineClient, InProcEngineClient
@@ -154,7 +228,27 @@ def update_weights(args, actor, rollout: RolloutComponents, updater=None) -> dic
     rollout.executor.set_weight_version(actor.weight_version)
     if getattr(args, "audit_dir", None):
         _audit_weights(args, actor, rollout, info)
+    if getattr(args, "snapshot_dir", None):
+        info["snapshot"] = _publish_snapshot(args, actor)
     return info
+
+
+_SNAPSHOTS = {}
+
+
+def _publish_snapshot(args, actor):
+    """Periodic full HF export next to the weight push (engines outside the job follow `latest`); every trainer rank drives
+    the HF-named bucket iterator (its shard gathers are collective), rank 0 writes."""
+    from ..weight_update.delta import SnapshotPublisher
+    from ..weight_update.hf_iterator import iter_hf_weights
+
+    pub = _SNAPSHOTS.get(args.snapshot_dir)
+    if pub is None:
+        pub = _SNAPSHOTS[args.snapshot_dir] = SnapshotPublisher(args.snapshot_dir, actor.cfg, every=args.snapshot_interval,
+                                                                keep=args.snapshot_keep, src_dir=getattr(args, "hf_checkpoint", None))
+    rank0 = not dist.is_initialized() or dist.get_rank() == 0
+    return pub.maybe_publish(actor.weight_version, iter_hf_weights(actor, bucket_bytes=getattr(args, "update_weight_buffer_size", 512 << 20)),
+                             write=rank0)
 
 
 _AUDIT = {}

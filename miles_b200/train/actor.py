@@ -127,10 +127,20 @@ class TrainActor:
             self.optimizer = FsdpOptimizer(named, lr=lr0, betas=(args.adam_beta1, args.adam_beta2), eps=args.adam_eps,
                                            weight_decay=args.weight_decay, clip_grad=args.clip_grad)
         else:
+            # --offload-train: optimizer state lives in a VMM arena; sleep() releases its physical pages (contents kept in
+            # pinned host memory), wake_up() maps them back at the same addresses
+            self.arena = None
+            state_alloc = None
+            if getattr(args, "offload_train", False) and getattr(args, "offload_train_mode", "vmm") == "vmm":
+                from ..utils.memory import make_arena
+
+                self.arena = make_arena(self.device)
+                if self.arena is not None:
+                    state_alloc = lambda n, dt, dev, tag: self.arena.empty((n,), dt, tag="optimizer")  # noqa: E731
             self.optimizer = DistributedAdam(
                 named, lr=lr0, betas=(args.adam_beta1, args.adam_beta2),
                 eps=args.adam_eps, weight_decay=args.weight_decay, clip_grad=args.clip_grad, ps=self.ps,
-                allocator=self._symmetric_allocator())
+                allocator=self._symmetric_allocator(), state_allocator=state_alloc)
         self.tp_replicated = {n for n, p in named if _tp_replicated(n)}
         if self.ps.tp_size > 1:
             self.optimizer.mark_tp_replicated(self.tp_replicated, named)
@@ -378,6 +388,12 @@ class TrainActor:
             metrics[f"perf/{k}_time"] = v
         if ps.fabric is not None:
             ps.fabric.check()               # a bounded wait on a peer ran out somewhere in this step: fail it loudly
+        if "witness_ids" in shard and getattr(args, "audit_dir", None):
+            from ..audit.events import DataWitness
+            from ..orchestration.wiring import audit_logger
+
+            DataWitness(audit_logger(args, "trainer", ps.rank)).consumed(rollout_id, self.global_step, shard["witness_ids"],
+                                                                        dp_rank=ps.dp_rank)
         self.weight_version += 1
         return metrics
 
@@ -546,7 +562,10 @@ class TrainActor:
         groups = self.optimizer.tensors_by_tag()
         self._offloaded = {}
         if "optimizer" in tags:
-            self._offloaded["optimizer"] = offload_tensors(groups["optimizer"])
+            if getattr(self, "arena", None) is not None:
+                self._arena_released = self.arena.pause("optimizer", keep_contents=True)
+            else:
+                self._offloaded["optimizer"] = offload_tensors(groups["optimizer"])
         if "grad" in tags:
             self.optimizer.release_grads()
         self.asleep = True
@@ -555,6 +574,9 @@ class TrainActor:
         from ..utils.memory import onload_tensors
         if not self.asleep:
             return
+        if getattr(self, "arena", None) is not None and getattr(self, "_arena_released", 0):
+            self.arena.resume("optimizer")
+            self._arena_released = 0
         for t, saved in self._offloaded.items():
             onload_tensors(saved)
         self._offloaded = {}

@@ -131,7 +131,7 @@ def normalize_rewards_by_rollout(args, flat: list[Sample], raw: torch.Tensor, gr
 _PER_SAMPLE_KEYS = ("tokens", "response_lengths", "total_lengths", "rewards", "raw_reward", "truncated", "loss_masks",
                     "sample_indices", "rollout_ids", "rollout_log_probs", "rollout_routed_experts",
                     "teacher_log_probs", "opd_reverse_kl", "weight_versions", "rollout_mask_sums", "advantages",
-                    "multimodal_train_inputs")
+                    "multimodal_train_inputs", "witness_ids")
 
 
 def karmarkar_karp(lengths: list[int], k: int, equal_size: bool = True) -> list[list[int]]:

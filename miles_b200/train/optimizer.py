@@ -48,11 +48,14 @@ class _Domain:
 class DistributedAdam:
     def __init__(self, named_params: Iterable[tuple[str, torch.nn.Parameter]], *, lr: float, betas=(0.9, 0.98),
                  eps: float = 1e-8, weight_decay: float = 0.0, clip_grad: float = 1.0, ps=None,
-                 allocator=None, moments_dtype=torch.float32):
+                 allocator=None, moments_dtype=torch.float32, state_allocator=None):
         self.lr, self.betas, self.eps, self.weight_decay, self.clip_grad = lr, betas, eps, weight_decay, clip_grad
         self.ps = ps
         self.step_count = 0
         self.allocator = allocator
+        # where the fp32 master weights and the Adam moments live: None → ordinary tensors; a callable (n, dtype, device, tag)
+        # → e.g. the VMM arena, whose physical pages can be released for the rollout phase at stable addresses
+        self.state_allocator = state_allocator
         named = [(n, p) for n, p in named_params if p.requires_grad]
         dense = [(n, p) for n, p in named if not _is_expert(n)]
         expert = [(n, p) for n, p in named if _is_expert(n)]
@@ -96,9 +99,15 @@ class DistributedAdam:
                 decay[o:o + p.numel()] = 1.0
         s = n_pad // gsize
         d.shard = (grank * s, (grank + 1) * s)
-        d.master = d.param_buf[d.shard[0]:d.shard[1]].float().clone()
-        d.exp_avg = torch.zeros(s, dtype=moments_dtype, device=device)
-        d.exp_avg_sq = torch.zeros(s, dtype=moments_dtype, device=device)
+        if self.state_allocator is not None:
+            d.master = self.state_allocator(s, torch.float32, device, f"{name}.master")
+            d.master.copy_(d.param_buf[d.shard[0]:d.shard[1]])
+            d.exp_avg = self.state_allocator(s, moments_dtype, device, f"{name}.exp_avg").zero_()
+            d.exp_avg_sq = self.state_allocator(s, moments_dtype, device, f"{name}.exp_avg_sq").zero_()
+        else:
+            d.master = d.param_buf[d.shard[0]:d.shard[1]].float().clone()
+            d.exp_avg = torch.zeros(s, dtype=moments_dtype, device=device)
+            d.exp_avg_sq = torch.zeros(s, dtype=moments_dtype, device=device)
         d.decay_mask = decay[d.shard[0]:d.shard[1]].clone()
         return d
 

@@ -4,9 +4,10 @@ Two mechanisms:
 * `offload_tensors` / `onload_tensors`: keep the python tensor objects, swap their storage for a
   pinned host copy (the torch-native `offload.py` of the reference,
   miles/backends/training_utils/torch_native/offload.py:1-29).
-* `miles_b200.native.vmm_arena.VmmArena`: a C++ CUDA-VMM arena with tagged pause/resume that frees
+* `miles_b200.native.runtime.VmmArena`: a C++ CUDA-VMM arena with tagged pause/resume that frees
   the physical pages but keeps virtual addresses stable (the role `torch_memory_saver` plays for the
-  reference), so CUDA graphs and peer mappings survive a sleep/wake cycle.
+  reference), so CUDA graphs and peer mappings survive a sleep/wake cycle.  `make_arena` gives the trainer one when
+  `--offload-train` is on and the native runtime is built; optimizer state then lives in it under the tag "optimizer".
 """
 from __future__ import annotations
 
@@ -40,6 +41,21 @@ def onload_tensors(saved: list[tuple[torch.Tensor, torch.Tensor]]):
         t.data = host.to(t._offload_device, non_blocking=True)
     if torch.cuda.is_available():
         torch.cuda.synchronize()
+
+
+def make_arena(device) -> "object | None":
+    """A VMM arena on `device`, or None where it cannot exist (CPU, native runtime not built, driver without VMM)."""
+    dev = torch.device(device)
+    if dev.type != "cuda" or not torch.cuda.is_available():
+        return None
+    try:
+        from ..native import runtime as rt
+
+        if not rt.available():
+            return None
+        return rt.VmmArena(dev.index if dev.index is not None else torch.cuda.current_device())
+    except Exception:
+        return None
 
 
 def gpu_memory_report(device=None) -> dict:

@@ -120,3 +120,23 @@ def test_convert_tool_chain(tmp_path):
     assert i4.dtype == torch.bfloat16 and i4.float().view(-1, 32).unique(dim=1).shape[1] <= 32
     tool.main(["hf-to-nvfp4-qdq", "--hf", hf_dir, "--out", str(tmp_path / "n4")])
     assert hf_io.load_hf_dir(str(tmp_path / "n4"))[name].shape == a[name].shape
+
+
+def test_run_with_audit_dir_allocates_and_consumes_every_witness(tmp_path, tiny_args):
+    """`train.py --audit-dir`: the rollout executor gives every sample a witness id, the trainer reports the ids it
+    consumed, and the analyser finds every sample trained on exactly once; `--snapshot-dir` leaves an HF snapshot."""
+    import train as train_entry
+    from test_e2e import BASE
+    from miles_b200.args import parse_args
+    from miles_b200.audit import events
+
+    args = parse_args((BASE + f" --audit-dir {tmp_path / 'audit'} --num-rollout 2 --snapshot-dir {tmp_path / 'snap'} "
+                       "--true-on-policy-mode").split())
+    assert args.true_on_policy_contracts and args.rollout_top_p == 1.0
+    train_entry.train(args)
+    ev = events.read_events(str(tmp_path / "audit"))
+    kinds = {e["kind"] for e in ev}
+    assert {"witness_allocated", "witness_consumed", "weights_published"} <= kinds
+    assert events.rule_witness(ev) == []
+    latest = (tmp_path / "snap" / "latest").read_text().strip()
+    assert (tmp_path / "snap" / latest / "config.json").exists()

@@ -222,3 +222,27 @@ def _indep_dp_body(rank, world, port):
 
 def test_indep_dp_reconfigures_when_a_cell_leaves():
     run_distributed(_indep_dp_body, 3, (_free_port(),), timeout=120)
+
+
+def test_train_py_retries_a_failed_trainer_call_under_fault_tolerance(monkeypatch):
+    """`--use-fault-tolerance`: the driver's trainer handle is a CellController; a step that raises once is retried and the
+    run completes with the same number of optimizer steps."""
+    import train as train_entry
+    from test_e2e import BASE
+    from miles_b200.args import parse_args
+    from miles_b200.train.actor import TrainActor
+
+    calls = {"n": 0}
+    real = TrainActor.train
+
+    def flaky(self, rollout_id, shard):
+        calls["n"] += 1
+        if calls["n"] == 2:
+            raise RuntimeError("injected host-side failure")
+        return real(self, rollout_id, shard)
+
+    monkeypatch.setattr(TrainActor, "train", flaky)
+    args = parse_args((BASE + " --use-fault-tolerance --num-rollout 2").split())
+    tr = train_entry.train(args)
+    assert calls["n"] == 3 and len(tr.history.rows) == 2
+    assert tr.actor.global_step == 2

@@ -63,3 +63,58 @@ def test_decode_while_batch_drains(engine):
         assert len(o["output_ids"]) == sp["max_new_tokens"]
         assert all(0 <= t < cfg.vocab_size for t in o["output_ids"])
         assert all(lp == lp and lp <= 0.0 for lp, _, _ in o["meta_info"]["output_token_logprobs"])
+
+
+@pytest.mark.gpu
+def test_vmm_arena_pause_releases_memory_and_resume_restores_contents():
+    """The trainer's sleep / wake-up mechanism: tagged arena regions give their physical pages back (device memory in use
+    drops), keep their addresses, and come back with their contents."""
+    from miles_b200.native import runtime as rt
+
+    if not rt.available():
+        pytest.skip("native runtime not built")
+    arena = rt.VmmArena(torch.cuda.current_device())
+    try:
+        a = arena.empty((64 << 20,), torch.float32, tag="optimizer")        # 256 MB
+        b = arena.empty((1 << 20,), torch.bfloat16, tag="other")
+        a.copy_(torch.arange(a.numel(), device="cuda", dtype=torch.float32))
+        b.fill_(3.0)
+        torch.cuda.synchronize()
+        ptr = a.data_ptr()
+        free0, _ = torch.cuda.mem_get_info()
+        released = arena.pause("optimizer", keep_contents=True)
+        free1, _ = torch.cuda.mem_get_info()
+        assert released >= a.numel() * 4 and free1 - free0 >= (200 << 20), (released, free1 - free0)
+        assert float(b.float().sum()) == 3.0 * b.numel()                   # other tags stay mapped
+        arena.resume("optimizer")
+        free2, _ = torch.cuda.mem_get_info()
+        assert free2 <= free1 - (200 << 20) and a.data_ptr() == ptr
+        assert torch.equal(a[:1000], torch.arange(1000, device="cuda", dtype=torch.float32))
+        assert float(a[-1]) == float(a.numel() - 1)
+    finally:
+        arena.close()
+
+
+@pytest.mark.gpu
+def test_trainer_sleep_uses_the_arena_and_training_continues():
+    from miles_b200.args import parse_args
+    from miles_b200.models.config import ModelConfig
+    from miles_b200.native import runtime as rt
+    from miles_b200.train.actor import TrainActor
+
+    if not rt.available():
+        pytest.skip("native runtime not built")
+    cfg = ModelConfig(name="sleepy", vocab_size=1024, hidden_size=256, num_layers=2, num_heads=4, num_kv_heads=2, head_dim=64,
+                      ffn_hidden_size=512)
+    args = parse_args("--rollout-batch-size 2 --n-samples-per-prompt 2 --num-rollout 1 --lr 1e-3 --colocate --offload-train".split())
+    actor = TrainActor(args, device="cuda:0")
+    actor.init(cfg)
+    assert actor.arena is not None
+    d = actor.optimizer.domains[0]
+    before = d.master.clone()
+    free0, _ = torch.cuda.mem_get_info()
+    actor.sleep()
+    free1, _ = torch.cuda.mem_get_info()
+    assert free1 > free0
+    actor.wake_up()
+    assert torch.equal(d.master, before)

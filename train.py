@@ -12,8 +12,8 @@ from __future__ import annotations
 import os
 
 from miles_b200.args import parse_args
-from miles_b200.orchestration.wiring import (create_parallel_state, create_rollout_components, create_training_models,
-                                             update_weights)
+from miles_b200.orchestration.wiring import (create_parallel_state, create_rollout_components, create_trainer_controller,
+                                             create_training_models, update_weights)
 from miles_b200.utils import object_store
 from miles_b200.utils.tracking import Tracker
 
@@ -28,6 +28,7 @@ def train(args):
     ps = create_parallel_state(args)
     tracker = Tracker(args, stdout=ps.rank == 0)
     actor, critic, start_rollout_id = create_training_models(args, ps)
+    trainer = create_trainer_controller(args, actor)     # retries / heartbeats under --use-fault-tolerance, else a pass-through
     rollout = create_rollout_components(args, ps, actor, tracker)
     rollout.executor.load(start_rollout_id - 1 if start_rollout_id > 0 else None)
     if args.num_rollout is None:
@@ -54,7 +55,7 @@ def train(args):
             cm = critic.train(rollout_id, shard)
             metrics.update({k.replace("train/", "train/critic-"): v for k, v in cm.items()})
         if critic is None or rollout_id >= args.num_critic_only_steps:
-            metrics.update(actor.train(rollout_id, shard))
+            metrics.update(trainer.train(rollout_id, shard))
         object_store.remove(pack.data_ref)
 
         sentinel = args.save_trigger_sentinel and os.path.exists(args.save_trigger_sentinel)
