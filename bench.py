@@ -43,7 +43,7 @@ def parse():
     p.add_argument("--max-new-tokens", type=int, default=8192)
     p.add_argument("--mean-response-len", type=int, default=512,
                    help="stop-token set sized so that a random-init policy stops after this many tokens on average")
-    p.add_argument("--max-tokens-per-gpu", type=int, default=16384)
+    p.add_argument("--max-tokens-per-gpu", type=int, default=32768, help="token budget of a micro-batch (the reference recipe's value)")
     p.add_argument("--mem-fraction-static", type=float, default=0.75,
                    help="share of device memory for weights + optimizer state + KV cache; the rest (45 GB at 0.75) stays free for "
                         "training activations. Too small a KV cache caps how many of the 64 requests decode at once.")
@@ -164,6 +164,8 @@ def main():
 
             try:
                 ps.fabric = Fabric.create(ps)
+                # dispatch / return buffers are sized from the largest micro-batch (or prefill batch) a rank can see
+                ps.fabric.moe_max_tokens = max(a.max_tokens_per_gpu, 16384) + 2048
             except Exception as e:      # peer mapping refused on this box: run the NCCL path and say so in `fused_comm`
                 print(f"[bench] fabric unavailable ({type(e).__name__}: {e}); falling back to NCCL collectives", file=sys.stderr)
                 ps.fused, ps.fabric = False, None

@@ -8,6 +8,12 @@ sampled ids / log-probs (and routed experts) back with one device→host copy.  
 
 The graph contains the whole model forward, the LM head, and the fused sample+log-prob kernel, so a decode step is one
 graph launch instead of ~25 launches per layer.
+
+Several steps per host round trip (`steps > 1`): the graph is replayed `steps` times back to back; between replays a few
+device-side ops feed the sampled token back (token ← sample, position / length + 1, cache slot from the block table,
+random seed + 1) and append the step's outputs to a history buffer.  The host then reads all `steps` tokens of every
+row at once and drops what a row produced after its stop token or length limit.  Per-step host work, the lockstep
+agreement of expert-parallel ranks and the skew between their hosts are then paid once per `steps` steps.
 """
 from __future__ import annotations
 
@@ -60,6 +66,15 @@ class DecodeRunner:
         self.h_tok = torch.zeros(R, dtype=torch.int64).pin_memory()
         self.h_lp = torch.zeros(R, dtype=torch.float32).pin_memory()
         self.h_routed = torch.zeros(R, max(self.n_moe, 1), max(self.topk, 1), dtype=torch.int32).pin_memory()
+        # histories of a multi-step call: [step, row]
+        self.max_steps = 8
+        S = self.max_steps
+        self.hist_tok = torch.zeros(S, R, dtype=torch.int64, device=self.dev)
+        self.hist_lp = torch.zeros(S, R, dtype=torch.float32, device=self.dev)
+        self.hist_routed = torch.zeros(S, R, max(self.n_moe, 1), max(self.topk, 1), dtype=torch.int32, device=self.dev)
+        self.hh_tok = torch.zeros(S, R, dtype=torch.int64).pin_memory()
+        self.hh_lp = torch.zeros(S, R, dtype=torch.float32).pin_memory()
+        self.hh_routed = torch.zeros(S, R, max(self.n_moe, 1), max(self.topk, 1), dtype=torch.int32).pin_memory()
         self.rows: list = [None] * R          # row → Request
         self.free_rows = list(range(R - 1, -1, -1))
         self.high = 0                         # 1 + highest occupied row
@@ -152,9 +167,29 @@ class DecodeRunner:
         if record and meta.record_topk:
             self.o_routed[:B].copy_(torch.stack(meta.record_topk, dim=1))
 
-    def step(self, reqs: list, step_no: int, min_bucket: int = 0):
-        """Run one decode step for the attached requests; returns (tokens, logprobs, routed | None) as numpy views
-        indexed by row."""
+    def _advance(self, B: int, k: int, record: bool):
+        """Device-side hand-over between two replays of one multi-step call (rows with length 0 are padding)."""
+        R, MB = self.max_rows, self.max_blocks
+        bs = self.e.block_size
+        self.hist_tok[k, :B].copy_(self.o_tok[:B])
+        self.hist_lp[k, :B].copy_(self.o_lp[:B])
+        if record:
+            self.hist_routed[k, :B].copy_(self.o_routed[:B])
+        tok, pos, ln = self.d_i32[0:B], self.d_i32[R:R + B], self.d_i32[2 * R:2 * R + B]
+        active = ln > 0
+        tok.copy_(self.o_tok[:B])
+        inc = active.to(torch.int32)
+        pos.add_(inc)
+        ln.add_(inc)
+        p64 = pos.long()
+        blk = self.d_i32[3 * R:].view(R, MB)[:B].gather(1, (p64 // bs).clamp_(max=MB - 1).unsqueeze(1)).squeeze(1).long()
+        self.d_i64[0:B].copy_(torch.where(active, blk * bs + p64 % bs, torch.full_like(p64, -1)))
+        self.d_i64[R:R + B].add_(1).bitwise_and_(0x7FFFFFFFFFFFFFFF)
+
+    def step(self, reqs: list, step_no: int, min_bucket: int = 0, steps: int = 1):
+        """Run `steps` decode steps for the attached requests (every request must own cache blocks for `steps` more
+        tokens).  Returns (tokens, logprobs, routed | None) as numpy views indexed [row] for one step and [step, row] for
+        several."""
         e = self.e
         bs = e.block_size
         if len(self.free_rows) and (self.high - len(reqs)) > max(8, len(reqs) // 4):
@@ -179,15 +214,31 @@ class DecodeRunner:
         self.d_u8.copy_(self.h_u8, non_blocking=True)
         e.stats["h2d_bytes"] = e.stats.get("h2d_bytes", 0) + self.h_i32.numel() * 4 + self.h_i64.numel() * 8 + 5 * self.max_rows
         key = (B, record)
-        if self.use_graph:
-            if key not in self.graphs:
-                self._capture(key)
-            self.graphs[key].replay()
-            from .. import ops
+        steps = max(1, min(int(steps), self.max_steps))
+        for k in range(steps):
+            if self.use_graph:
+                if key not in self.graphs:
+                    self._capture(key)
+                self.graphs[key].replay()
+                from .. import ops
 
-            ops._k().C.count_launches(self.launches_per_graph[key])
-        else:
-            self._forward(B, record)
+                ops._k().C.count_launches(self.launches_per_graph[key])
+            else:
+                self._forward(B, record)
+            if steps > 1:
+                self._advance(B, k, record)
+        if steps > 1:
+            self.hh_tok[:steps, :B].copy_(self.hist_tok[:steps, :B], non_blocking=True)
+            self.hh_lp[:steps, :B].copy_(self.hist_lp[:steps, :B], non_blocking=True)
+            nbytes = 12 * B * steps
+            if record:
+                self.hh_routed[:steps, :B].copy_(self.hist_routed[:steps, :B], non_blocking=True)
+                nbytes += self.hh_routed[:steps, :B].numel() * 4
+            e.stats["d2h_bytes"] = e.stats.get("d2h_bytes", 0) + nbytes
+            t0 = time.perf_counter()
+            torch.cuda.current_stream().synchronize()
+            e.stats["decode_wait_s"] = e.stats.get("decode_wait_s", 0.0) + time.perf_counter() - t0
+            return self.hh_tok.numpy(), self.hh_lp.numpy(), (self.hh_routed.numpy() if record else None)
         self.h_tok[:B].copy_(self.o_tok[:B], non_blocking=True)
         self.h_lp[:B].copy_(self.o_lp[:B], non_blocking=True)
         nbytes = 12 * B

@@ -101,7 +101,7 @@ class Engine:
                  mem_fraction_static: float = 0.7, max_running_requests: int = 512, max_prefill_tokens: int = 16384,
                  max_context_len: int | None = None, eos_token_ids: list[int] | None = None, tokenizer=None,
                  seed: int = 0, use_cuda_graph: bool = True, record_routing: bool | None = None,
-                 share_prompt_kv: bool = True):
+                 share_prompt_kv: bool = True, decode_steps_per_sync: int = 4):
         self.cfg = cfg
         self.ps = ps or ParallelState.single()
         self.device = torch.device(device)
@@ -118,6 +118,10 @@ class Engine:
         # requests of one prefill batch with identical tokens (the n samples of a prompt) run the prompt once: the full KV
         # blocks are shared by reference count, the partial last block is copied, the first token is sampled per request
         self.share_prompt_kv = share_prompt_kv
+        # decode steps per host round trip on the CUDA runner (see `decode_runner`): a finished request may run up to
+        # steps − 1 extra positions whose tokens are dropped; nothing waits on the host in between
+        self.decode_steps_per_sync = max(1, int(decode_steps_per_sync))
+        self._agreed_steps = 1
         self.use_cuda_graph = use_cuda_graph and self.device.type == "cuda"
         hkv = cfg.num_kv_heads // self.ps.tp_size
         if num_blocks is None:
@@ -424,14 +428,16 @@ class Engine:
                 self._run_prefill(batch)
                 self.stats["prefill_s"] = self.stats.get("prefill_s", 0.0) + time.perf_counter() - t0
             elif self.running:
-                if not self._ensure_decode_blocks():
+                k = self._decode_lookahead()
+                if not self._ensure_decode_blocks(k):
                     return True
                 n = len(self.running)
+                self._agreed_steps = k
                 self._run_decode()
                 # wall time of decode steps by batch-size class (host bookkeeping included): where a rollout's time goes
                 key = "decode_s_le8" if n <= 8 else "decode_s_le32" if n <= 32 else "decode_s_gt32"
                 self.stats[key] = self.stats.get(key, 0.0) + time.perf_counter() - t0
-                self.stats[key.replace("_s_", "_n_")] = self.stats.get(key.replace("_s_", "_n_"), 0) + 1
+                self.stats[key.replace("_s_", "_n_")] = self.stats.get(key.replace("_s_", "_n_"), 0) + self._agreed_steps
             else:
                 return False
             self.stats["steps"] += 1
@@ -446,15 +452,18 @@ class Engine:
 
         batch = [] if self.paused else self._schedule_prefill()
         want_decode = bool(self.running) and not self.paused and not batch
-        if want_decode and not self._ensure_decode_blocks():
+        k = self._decode_lookahead() if want_decode else self.decode_steps_per_sync
+        if want_decode and not self._ensure_decode_blocks(k):
             want_decode = False
         # the decode batch bucket is agreed too (the largest any rank needs): with the same row count on every rank the
         # expert-parallel layers can bound what each rank receives by ep · rows · k instead of the buffer capacity
         bucket = self.runner.bucket_needed() if (self.runner is not None and want_decode) else 0
-        flags = torch.tensor([int(bool(batch)), int(want_decode), int(not self.local_done), bucket], dtype=torch.int32,
+        # the number of steps per round trip is agreed as well: the smallest any rank can take (−k under MAX)
+        flags = torch.tensor([int(bool(batch)), int(want_decode), int(not self.local_done), bucket, -k], dtype=torch.int32,
                              device=self.device if self.device.type == "cuda" else "cpu")
         dist.all_reduce(flags, op=dist.ReduceOp.MAX, group=self.lockstep_group)
-        any_prefill, any_decode, any_active, self._agreed_bucket = (int(v) for v in flags.tolist())
+        any_prefill, any_decode, any_active, self._agreed_bucket, neg_k = (int(v) for v in flags.tolist())
+        self._agreed_steps = max(1, -neg_k)
         self.global_done = not any_active and not any_prefill and not any_decode
         t0 = time.perf_counter()
         if any_prefill:
@@ -465,7 +474,7 @@ class Engine:
             self._run_decode()
             key = "decode_s_le8" if n <= 8 else "decode_s_le32" if n <= 32 else "decode_s_gt32"
             self.stats[key] = self.stats.get(key, 0.0) + time.perf_counter() - t0
-            self.stats[key.replace("_s_", "_n_")] = self.stats.get(key.replace("_s_", "_n_"), 0) + 1
+            self.stats[key.replace("_s_", "_n_")] = self.stats.get(key.replace("_s_", "_n_"), 0) + self._agreed_steps
         else:
             return False
         self.stats["steps"] += 1
@@ -479,6 +488,11 @@ class Engine:
             fab.check()
 
     def begin_rollout(self):
+        import gc
+
+        # lockstep ranks wait for the slowest host at every agreement: a cyclic-GC pause on one rank stalls all of them
+        gc.collect()
+        gc.disable()
         self.local_done = False
         self.global_done = False
         fab = getattr(self.ps, "fabric", None)
@@ -489,6 +503,9 @@ class Engine:
 
     def finish_rollout(self):
         if not self.local_done:
+            import gc
+
+            gc.enable()
             self.check_fabric()
         self.local_done = True
 
@@ -535,13 +552,25 @@ class Engine:
             batch.append(r)
         return batch
 
-    def _ensure_decode_blocks(self) -> bool:
-        """Every running request needs a slot for its next token; retract the youngest on shortage."""
+    def _decode_lookahead(self) -> int:
+        """Decode steps the next round trip may take: the configured count, bounded by what every running request may still
+        generate and by the context limit (positions beyond either are never written)."""
+        if self.runner is None or self.stateless or self.decode_steps_per_sync <= 1 or not self.running:
+            return 1
+        k = self.decode_steps_per_sync
+        for r in self.running:
+            k = min(k, r.sampling.max_new_tokens - len(r.output_ids), self.max_context_len - len(r.all_ids))
+        return max(1, k)
+
+    def _ensure_decode_blocks(self, lookahead: int = 1) -> bool:
+        """Every running request needs slots for its next `lookahead` tokens; retract the youngest on shortage."""
+        bs = self.block_size
         while True:
-            short = [r for r in self.running if len(r.all_ids) + 1 > len(r.blocks) * self.block_size]
-            if len(short) <= self.allocator.num_free:
-                for r in short:
-                    r.blocks += self.allocator.alloc(1)
+            need = {id(r): max(0, self._blocks_needed(len(r.all_ids) + lookahead) - len(r.blocks)) for r in self.running}
+            if sum(need.values()) <= self.allocator.num_free:
+                for r in self.running:
+                    if need[id(r)]:
+                        r.blocks += self.allocator.alloc(need[id(r)])
                 return True
             victim = max(self.running, key=lambda r: r.arrival)
             self._retract(victim)
@@ -715,14 +744,27 @@ class Engine:
     def _run_decode_static(self):
         """CUDA path: static buffers + (optionally) a CUDA graph per batch bucket; see `decode_runner`."""
         reqs = self.running
+        steps = self._agreed_steps
         tok, lp, routed = self.runner.step(reqs, self._step_count,
-                                           min_bucket=self._agreed_bucket if self.lockstep_group is not None else 0)
-        self.stats["decode_tokens"] += len(reqs)
-        for r in reqs:
-            row = r.row
-            if routed is not None and r.return_routed_experts:
-                r.routed.append(routed[row:row + 1].copy())
-            self._append_token(r, int(tok[row]), float(lp[row]))
+                                           min_bucket=self._agreed_bucket if self.lockstep_group is not None else 0, steps=steps)
+        if steps == 1:
+            self.stats["decode_tokens"] += len(reqs)
+            for r in reqs:
+                row = r.row
+                if routed is not None and r.return_routed_experts:
+                    r.routed.append(routed[row:row + 1].copy())
+                self._append_token(r, int(tok[row]), float(lp[row]))
+        else:
+            rows = [(r, r.row) for r in reqs]      # `_finish` detaches the row; keep it for the remaining sub-steps
+            for k in range(steps):
+                for r, row in rows:
+                    if r.finished:
+                        continue                   # what a row produced after its stop token / limit is dropped
+                    self.stats["decode_tokens"] += 1
+                    if routed is not None and r.return_routed_experts:
+                        r.routed.append(routed[k, row:row + 1].copy())
+                    self._append_token(r, int(tok[k, row]), float(lp[k, row]))
+            self.stats["decode_extra_steps"] = self.stats.get("decode_extra_steps", 0) + steps - 1
         self.running = [r for r in reqs if not r.finished]
 
     def _append_token(self, r: Request, t: int, l: float):
