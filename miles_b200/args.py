@@ -330,6 +330,11 @@ def build_parser() -> argparse.ArgumentParser:
     g.add_argument("--profile-step-end", type=int, default=12)
     g.add_argument("--tensorboard-dir", type=str, default=None)
     _bool_flag(g, "--record-memory-history")
+    g.add_argument("--memory-snapshot-dir", type=str, default=".")
+    g.add_argument("--memory-snapshot-path", type=str, default="snapshot.pickle")
+    g.add_argument("--memory-snapshot-num-steps", type=int, default=None)
+    g.add_argument("--memory-recorder", choices=["torch"], default="torch")
+    _bool_flag(g, "--nvtx", help="NVTX ranges around the trainer's phases")
 
     g = p.add_argument_group("user functions")
     g.add_argument("--custom-megatron-init-path", type=str, default=None)

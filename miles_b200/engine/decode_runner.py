@@ -170,21 +170,12 @@ class DecodeRunner:
     def _advance(self, B: int, k: int, record: bool):
         """Device-side hand-over between two replays of one multi-step call (rows with length 0 are padding)."""
         R, MB = self.max_rows, self.max_blocks
-        bs = self.e.block_size
-        self.hist_tok[k, :B].copy_(self.o_tok[:B])
-        self.hist_lp[k, :B].copy_(self.o_lp[:B])
-        if record:
-            self.hist_routed[k, :B].copy_(self.o_routed[:B])
-        tok, pos, ln = self.d_i32[0:B], self.d_i32[R:R + B], self.d_i32[2 * R:2 * R + B]
-        active = ln > 0
-        tok.copy_(self.o_tok[:B])
-        inc = active.to(torch.int32)
-        pos.add_(inc)
-        ln.add_(inc)
-        p64 = pos.long()
-        blk = self.d_i32[3 * R:].view(R, MB)[:B].gather(1, (p64 // bs).clamp_(max=MB - 1).unsqueeze(1)).squeeze(1).long()
-        self.d_i64[0:B].copy_(torch.where(active, blk * bs + p64 % bs, torch.full_like(p64, -1)))
-        self.d_i64[R:R + B].add_(1).bitwise_and_(0x7FFFFFFFFFFFFFFF)
+        from .. import ops
+
+        C = ops._k().C
+        C.decode_advance(self.o_tok[:B], self.o_lp[:B], self.o_routed[:B] if record else None, self.hist_tok[k, :B], self.hist_lp[k, :B],
+                         self.hist_routed[k, :B] if record else None, self.d_i32[0:B], self.d_i32[R:R + B], self.d_i32[2 * R:2 * R + B],
+                         self.d_i32[3 * R:].view(R, MB)[:B], self.e.block_size, self.d_i64[0:B], self.d_i64[R:R + B])
 
     def step(self, reqs: list, step_no: int, min_bucket: int = 0, steps: int = 1):
         """Run `steps` decode steps for the attached requests (every request must own cache blocks for `steps` more

@@ -101,7 +101,7 @@ class Engine:
                  mem_fraction_static: float = 0.7, max_running_requests: int = 512, max_prefill_tokens: int = 16384,
                  max_context_len: int | None = None, eos_token_ids: list[int] | None = None, tokenizer=None,
                  seed: int = 0, use_cuda_graph: bool = True, record_routing: bool | None = None,
-                 share_prompt_kv: bool = True, decode_steps_per_sync: int = 4):
+                 share_prompt_kv: bool = True, decode_steps_per_sync: int = 8):
         self.cfg = cfg
         self.ps = ps or ParallelState.single()
         self.device = torch.device(device)

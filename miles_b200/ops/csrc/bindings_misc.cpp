@@ -21,6 +21,23 @@ inline void check(int rc, const char* what) {
   throw std::runtime_error(buf);
 }
 
+// device-side hand-over between two decode steps of one host round trip (see decode_advance_kernel)
+void decode_advance(const at::Tensor& o_tok, const at::Tensor& o_lp, const c10::optional<at::Tensor>& o_routed, at::Tensor& h_tok,
+                    at::Tensor& h_lp, const c10::optional<at::Tensor>& h_routed, at::Tensor& tok, at::Tensor& pos, at::Tensor& len,
+                    const at::Tensor& block_table, int64_t block_size, at::Tensor& slot, at::Tensor& seed) {
+  c10::cuda::CUDAGuard g(o_tok.device());
+  const int64_t B = tok.numel();
+  const bool rec = o_routed.has_value() && o_routed->defined() && h_routed.has_value() && h_routed->defined();
+  const int64_t per = rec ? o_routed->numel() / std::max<int64_t>(o_routed->size(0), 1) : 0;
+  check(mb_decode_advance(reinterpret_cast<const long long*>(o_tok.data_ptr<int64_t>()), o_lp.data_ptr<float>(),
+                          rec ? o_routed->data_ptr<int>() : nullptr, reinterpret_cast<long long*>(h_tok.data_ptr<int64_t>()),
+                          h_lp.data_ptr<float>(), rec ? h_routed->data_ptr<int>() : nullptr, per, tok.data_ptr<int>(), pos.data_ptr<int>(),
+                          len.data_ptr<int>(), block_table.data_ptr<int>(), block_table.size(1), block_size,
+                          reinterpret_cast<long long*>(slot.data_ptr<int64_t>()), reinterpret_cast<long long*>(seed.data_ptr<int64_t>()), B,
+                          cur_stream()),
+        "mb_decode_advance");
+}
+
 std::vector<at::Tensor> sample_logprob(const at::Tensor& logits, const at::Tensor& temperature, const at::Tensor& greedy,
                                        const c10::optional<at::Tensor>& seeds, int64_t step) {
   c10::cuda::CUDAGuard g(logits.device());
@@ -119,6 +136,7 @@ at::Tensor nvfp4_qdq(const at::Tensor& x, const at::Tensor& global_amax) {
 }  // namespace
 
 void register_misc(pybind11::module& m) {
+  m.def("decode_advance", &decode_advance);
   m.def("sample_logprob", &sample_logprob);
   m.def("logit_stats", &logit_stats);
   m.def("logit_stats_finish", &logit_stats_finish);

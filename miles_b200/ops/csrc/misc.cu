@@ -251,7 +251,47 @@ __global__ void __launch_bounds__(256) logit_grad_kernel(const float* __restrict
 
 }  // namespace mb
 
+namespace mb {
+// Hand-over between two decode steps of one host round trip, one thread per row: record the step's outputs, feed the
+// sampled token back, advance position and length of live rows (length 0 = padding row), look the new cache slot up in
+// the block table, advance the random seed.
+__global__ void decode_advance_kernel(const long long* __restrict__ o_tok, const float* __restrict__ o_lp, const int* __restrict__ o_routed,
+                                      long long* __restrict__ h_tok, float* __restrict__ h_lp, int* __restrict__ h_routed,
+                                      int routed_per_row, int* __restrict__ tok, int* __restrict__ pos, int* __restrict__ len,
+                                      const int* __restrict__ block_table, int max_blocks, int block_size,
+                                      long long* __restrict__ slot, long long* __restrict__ seed, int B) {
+  pdl_trigger();
+  pdl_wait();
+  const int r = blockIdx.x * blockDim.x + threadIdx.x;
+  if (r >= B) return;
+  const long long t = o_tok[r];
+  h_tok[r] = t;
+  h_lp[r] = o_lp[r];
+  if (h_routed != nullptr)
+    for (int i = 0; i < routed_per_row; ++i) h_routed[static_cast<long long>(r) * routed_per_row + i] = o_routed[static_cast<long long>(r) * routed_per_row + i];
+  tok[r] = static_cast<int>(t);
+  if (len[r] > 0) {
+    const int p = pos[r] + 1;
+    pos[r] = p;
+    len[r] += 1;
+    const int b = min(p / block_size, max_blocks - 1);
+    slot[r] = static_cast<long long>(block_table[static_cast<long long>(r) * max_blocks + b]) * block_size + p % block_size;
+  } else {
+    slot[r] = -1;
+  }
+  seed[r] = (seed[r] + 1) & 0x7FFFFFFFFFFFFFFFll;
+}
+}  // namespace mb
+
 using namespace mb;
+
+extern "C" int mb_decode_advance(const long long* o_tok, const float* o_lp, const int* o_routed, long long* h_tok, float* h_lp,
+                                 int* h_routed, int routed_per_row, int* tok, int* pos, int* len, const int* block_table, int max_blocks,
+                                 int block_size, long long* slot, long long* seed, int B, cudaStream_t s) {
+  if (B == 0) return 0;
+  return static_cast<int>(launch_pdl(decode_advance_kernel, dim3((B + 127) / 128), dim3(128), 0, s, o_tok, o_lp, o_routed, h_tok, h_lp,
+                                     h_routed, routed_per_row, tok, pos, len, block_table, max_blocks, block_size, slot, seed, B));
+}
 
 extern "C" int mb_sample_logprob(const float* logits, const float* temperature, const uint8_t* greedy, const long long* seeds,
                                  long long step, long long* tokens, float* logprobs, int B, int V, cudaStream_t s) {

@@ -146,6 +146,10 @@ class TrainActor:
             self.optimizer.mark_tp_replicated(self.tp_replicated, named)
         self.scheduler = LRScheduler(self.optimizer.lr, args.min_lr, args.lr_warmup_iters, args.lr_decay_iters,
                                      args.lr_decay_style)
+        from ..utils.profiling import TrainProfiler
+
+        self.profiler = TrainProfiler(args)
+        self.profiler.on_init_end()
         self.backuper = TensorBackuper(self.model)
         self.indep_dp = self._make_indep_dp()
         # checkpoints
@@ -290,7 +294,7 @@ class TrainActor:
         out: dict[int, torch.Tensor] = {}
         replay = getattr(self.args, "use_routing_replay", False)
         self.model.eval()
-        for idx in micro_batches:
+        for idx in (self.profiler.iterate("train_log_probs", micro_batches) if hasattr(self, "profiler") else micro_batches):
             pb = pack_micro_batch(shard, idx, self.device, pad_multiple=self._pad_multiple(), with_replay=replay)
             if self.ps.pp_size > 1:
                 from ..parallel.pp import broadcast_from_last_stage
@@ -338,7 +342,7 @@ class TrainActor:
                 with self.timer.span("ref_log_probs"):
                     ref_lp = self.compute_log_probs(shard, mbs, tag="ref")
             if not getattr(args, "skip_actor_forward_only", False) and not getattr(args, "use_rollout_logprobs", False):
-                with self.timer.span("log_probs"):
+                with self.timer.span("log_probs"), self.profiler.range("log_probs"):
                     old_lp = self.compute_log_probs(shard, mbs, tag=None)
             elif getattr(args, "use_rollout_logprobs", False):
                 assert "rollout_log_probs" in shard, "--use-rollout-logprobs needs engine log-probs"
@@ -373,9 +377,9 @@ class TrainActor:
         steps = max(1, getattr(args, "num_steps_per_rollout", 1) or 1)
         self.model.train()
         agg: dict[str, list] = {}
-        with self.timer.span("actor_train" if self.role == "actor" else "critic_train"):
+        with self.timer.span("actor_train" if self.role == "actor" else "critic_train"), self.profiler.range("actor_train"):
             per_step = _split_steps(mbs, steps)
-            for step_mbs in per_step:
+            for step_mbs in self.profiler.iterate("train_actor", per_step):
                 step_metrics = self._train_one_step(shard, step_mbs, old_lp, ref_lp)
                 for k, v in step_metrics.items():
                     agg.setdefault(k, []).append(v)
@@ -388,6 +392,7 @@ class TrainActor:
             metrics[f"perf/{k}_time"] = v
         if ps.fabric is not None:
             ps.fabric.check()               # a bounded wait on a peer ran out somewhere in this step: fail it loudly
+        self.profiler.step(rollout_id)
         if "witness_ids" in shard and getattr(args, "audit_dir", None):
             from ..audit.events import DataWitness
             from ..orchestration.wiring import audit_logger

@@ -140,3 +140,19 @@ def test_run_with_audit_dir_allocates_and_consumes_every_witness(tmp_path, tiny_
     assert events.rule_witness(ev) == []
     latest = (tmp_path / "snap" / "latest").read_text().strip()
     assert (tmp_path / "snap" / latest / "config.json").exists()
+
+
+def test_train_profiler_writes_traces_for_the_selected_window(tmp_path):
+    """`--use-pytorch-profiler --profile-target train_overall train_actor`: one trace per target for the step window."""
+    import glob
+
+    import train as train_entry
+    from test_e2e import BASE
+    from miles_b200.args import parse_args
+
+    for target in ("train_overall", "train_log_probs"):
+        args = parse_args((BASE + f" --num-rollout 3 --use-pytorch-profiler --profile-target {target} "
+                           f"--profile-step-start 1 --profile-step-end 2 --tensorboard-dir {tmp_path}").split())
+        train_entry.train(args)
+        names = [p.rsplit("/", 1)[-1] for p in glob.glob(str(tmp_path / "*.json*"))]
+        assert any(n.startswith(f"{target}_rank_0") for n in names), (target, names)
