@@ -343,6 +343,9 @@ def build_parser() -> argparse.ArgumentParser:
     g.add_argument("--custom-rollout-log-function-path", type=str, default=None)
     g.add_argument("--custom-eval-rollout-log-function-path", type=str, default=None)
     g.add_argument("--custom-config-path", type=str, default=None)
+    from .args_compat import add_compat_arguments
+
+    add_compat_arguments(p)       # every remaining flag name of the reference's parser
     return p
 
 
@@ -412,6 +415,8 @@ def validate_args(args) -> None:
         args.eps_clip_high = args.eps_clip
     if args.use_fault_tolerance:
         args.indep_dp = args.indep_dp or "train" in (args.ft_components or [])
+    if getattr(args, "enable_witness", False) and not args.audit_dir:
+        args.audit_dir = "audit"            # witnesses are events of the audit log
     if getattr(args, "true_on_policy_mode", False):
         from .utils import true_on_policy
 

@@ -172,6 +172,8 @@ class InferenceController:
                     c.state = "alive"
 
     # ---- weight update framing -----------------------------------------------------------------------
+    pause_mode = "retract"          # how engines stop for an update (`--pause-generation-mode`: abort | retract | in_place)
+
     def start_update_weights(self, model: str | None = None) -> list:
         """pause → flush on every engine that follows the trainer; returns those engines."""
         self.lock._lock.acquire()
@@ -179,7 +181,7 @@ class InferenceController:
         self.updating = True
         targets = self.engines(model)
         for e in targets:
-            e.pause_generation("retract")
+            e.pause_generation(self.pause_mode)
             e.flush_cache()
         return targets
 

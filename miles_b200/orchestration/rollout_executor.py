@@ -76,6 +76,9 @@ class RolloutExecutor:
             path = args.save_debug_rollout_data.format(rollout_id=rollout_id)
             os.makedirs(os.path.dirname(path) or ".", exist_ok=True)
             torch.save({"rollout_id": rollout_id, "samples": [[s.to_dict() for s in g] for g in groups]}, path)
+        post = getattr(args, "rollout_all_samples_process_path", None)
+        if post:
+            load_function(post)(args, groups)
         witness = getattr(self, "witness", None)
         if witness is None and getattr(args, "audit_dir", None):
             from ..audit.events import DataWitness, EventLogger
@@ -87,6 +90,8 @@ class RolloutExecutor:
             # every sample of the batch gets an id here and the trainer reports the ids it consumed: the audit analyser
             # then proves that no sample was dropped or trained on twice
             data["witness_ids"] = witness.allocate(rollout_id, len(data["tokens"]), namespace=self.rollout_dp_rank if local else 0)
+        if getattr(args, "rollout_data_postprocess_path", None):
+            load_function(args.rollout_data_postprocess_path)(args, data)
         metrics.update(self._rollout_metrics(groups, data, time.time() - t0))
         metrics["perf/generate_time"] = t_gen
         if local:

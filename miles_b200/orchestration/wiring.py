@@ -28,7 +28,8 @@ class RolloutComponents:
 
 
 def create_parallel_state(args) -> ParallelState:
-    rank, world, local = init_distributed()
+    rank, world, local = init_distributed(backend=getattr(args, "distributed_backend", None),
+                                          timeout_s=60.0 * (getattr(args, "distributed_timeout_minutes", 30) or 30))
     if world == 1:
         return ParallelState.single()
     ps = ParallelState.build(
@@ -197,7 +198,9 @@ def create_rollout_components(args, ps: ParallelState, actor=None, tracker=None)
 
         group = ServerGroup("regular", max(1, ps.tp_size), max(1, ps.tp_size))
         controller = InferenceController([ServerCell(e, "default", group) for e in engines],
-                                         probe=lambda e: e.health().get("status") == "ok")
+                                         probe=lambda e: e.health().get("status") == "ok",
+                                         health_threshold=getattr(args, "miles_router_health_check_failure_threshold", 3) or 3)
+        controller.pause_mode = getattr(args, "pause_generation_mode", None) or "retract"
     return RolloutComponents(engines=engines, client=client, executor=ex, data_source=data_source, controller=controller)
 
 

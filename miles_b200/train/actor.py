@@ -157,6 +157,12 @@ class TrainActor:
         loaded_iter = ckpt.load_into_actor(self, args)
         if loaded_iter is not None:
             self.start_rollout_id = loaded_iter + 1
+            if getattr(args, "reset_optimizer_states", False):
+                self.optimizer.reset_state()           # keep the weights, restart Adam (a new task on an old checkpoint)
+            if getattr(args, "rematerialize_param_from_master_weight", False) or getattr(args, "check_rematerialize_param_from_master_weight", False):
+                self._rematerialize(check=getattr(args, "check_rematerialize_param_from_master_weight", False))
+        if getattr(args, "start_rollout_id", None) is not None:
+            self.start_rollout_id = int(args.start_rollout_id)
         need_ref = getattr(args, "need_ref", False) if with_ref is None else with_ref
         if need_ref and self.role == "actor":
             if getattr(args, "ref_load", None) and args.ref_load != getattr(args, "hf_checkpoint", None):
@@ -167,6 +173,29 @@ class TrainActor:
             else:
                 self.backuper.backup("ref")
         return self.start_rollout_id
+
+    def _rematerialize(self, check: bool = False):
+        """Rewrite the compute-dtype parameters of this rank's optimizer shards from the fp32 master copy (a checkpoint's
+        bf16 weights and master weights can disagree by one rounding after a dtype or layout change); with `check` the
+        rewrite must be a no-op (reference: megatron_utils/rematerialize_utils.py)."""
+        opt = self.optimizer
+        for d in getattr(opt, "domains", []):
+            lo, hi = d.shard
+            fresh = d.master.to(d.param_buf.dtype)
+            if check and not torch.equal(fresh, d.param_buf[lo:hi]):
+                bad = (fresh != d.param_buf[lo:hi]).sum().item()
+                raise AssertionError(f"{d.name}: {bad} parameters differ from their fp32 master copy")
+            d.param_buf[lo:hi].copy_(fresh)
+        if hasattr(opt, "_all_gather"):
+            for d in opt.domains:
+                opt._all_gather(d)
+
+    def _hook(self, flag: str, *a):
+        path = getattr(self.args, flag, None)
+        if path:
+            from ..utils.misc import load_function
+
+            load_function(path)(self.args, self, *a)
 
     def _make_indep_dp(self):
         """`--indep-dp`: this training world is one cell of several; gradients are averaged across the cells through a
@@ -315,7 +344,8 @@ class TrainActor:
 
     def _pad_multiple(self) -> int:
         zigzag = 2 if (self.ps.cp_size > 1 and self.ps.cp_comm_type == "p2p") else 1     # ring CP: two pieces per rank
-        return max(1, self.ps.tp_size) * max(1, self.ps.cp_size) * zigzag * (128 if self.device.type == "cuda" else 1)
+        mult = int(getattr(self.args, "data_pad_size_multiplier", 128) or 128)
+        return max(1, self.ps.tp_size) * max(1, self.ps.cp_size) * zigzag * (mult if self.device.type == "cuda" else 1)
 
     # ---------------------------------------------------------------------------------------
     # train
@@ -342,6 +372,7 @@ class TrainActor:
                 with self.timer.span("ref_log_probs"):
                     ref_lp = self.compute_log_probs(shard, mbs, tag="ref")
             if not getattr(args, "skip_actor_forward_only", False) and not getattr(args, "use_rollout_logprobs", False):
+                self._hook("custom_megatron_before_log_prob_hook_path", rollout_id)
                 with self.timer.span("log_probs"), self.profiler.range("log_probs"):
                     old_lp = self.compute_log_probs(shard, mbs, tag=None)
             elif getattr(args, "use_rollout_logprobs", False):
@@ -380,6 +411,7 @@ class TrainActor:
         with self.timer.span("actor_train" if self.role == "actor" else "critic_train"), self.profiler.range("actor_train"):
             per_step = _split_steps(mbs, steps)
             for step_mbs in self.profiler.iterate("train_actor", per_step):
+                self._hook("custom_megatron_before_train_step_hook_path", rollout_id)
                 step_metrics = self._train_one_step(shard, step_mbs, old_lp, ref_lp)
                 for k, v in step_metrics.items():
                     agg.setdefault(k, []).append(v)
@@ -415,7 +447,8 @@ class TrainActor:
         gbs, gtok = max(1.0, counts[0].item()), max(1.0, counts[1].item())
         sums: dict[str, torch.Tensor] = {}
         count_sum = torch.zeros((), device=dev)
-        want_entropy = getattr(args, "entropy_coef", 0.0) != 0 or getattr(args, "log_entropy", True)
+        want_entropy = (getattr(args, "entropy_coef", 0.0) != 0 or getattr(args, "log_entropy", True)
+                        or getattr(args, "observe_training_entropy", False))
         want_ent = want_entropy and self.role == "actor"
 
         def score(pb, idx, out, ent):
@@ -486,7 +519,10 @@ class TrainActor:
                 score(pb, idx, out, ent).backward()
         self._finalize_grads()
         lr = self.scheduler.get()
-        if self._exchange_across_cells():
+        if getattr(args, "debug_disable_optimizer", False):
+            self.optimizer.zero_grad()
+            stats = {"grad_norm": 0.0}
+        elif self._exchange_across_cells():
             stats = self.optimizer.step(lr)
             self.scheduler.step()
             self.global_step += 1
@@ -557,6 +593,16 @@ class TrainActor:
     def save_model(self, iteration: int, with_optimizer: bool = True):
         from ..checkpoint import manager as ckpt
         ckpt.save_from_actor(self, self.args, iteration, with_optimizer)
+        if getattr(self.args, "save_local_weight_checksum", False):
+            from ..audit.events import combined_checksum, model_checksums
+            import json
+            import os
+
+            sums = model_checksums(self.named_weights())
+            d = ckpt.iter_dir(self.args.save, iteration)
+            with open(os.path.join(d, f"weight_checksum_rank{self.ps.rank:05d}.json"), "w") as f:
+                json.dump({"combined": combined_checksum(sums), "tensors": sums}, f)
+        self._hook("custom_megatron_post_save_hook_path", iteration)
 
     def sleep(self, tags=("optimizer", "grad")):
         """Release trainer memory for the rollout phase (colocated mode): optimizer shards move to

@@ -72,7 +72,20 @@ class WandbBackend(_Backend):
         import wandb
 
         self.wandb = wandb
-        wandb.init(project=args.wandb_project, group=args.wandb_group, mode=args.wandb_mode, config=vars(args))
+        import os as _os
+
+        if getattr(args, "wandb_key", None):
+            _os.environ.setdefault("WANDB_API_KEY", args.wandb_key)
+        if getattr(args, "wandb_host", None):
+            _os.environ.setdefault("WANDB_BASE_URL", args.wandb_host)
+        name = getattr(args, "wandb_run_name", None) or getattr(args, "wandb_group", None)
+        if name and getattr(args, "wandb_random_suffix", True):
+            import uuid as _uuid
+
+            name = f"{name}-{_uuid.uuid4().hex[:6]}"
+        wandb.init(project=args.wandb_project, group=args.wandb_group, mode=args.wandb_mode, config=vars(args), name=name,
+                   entity=getattr(args, "wandb_team", None), dir=getattr(args, "wandb_dir", None),
+                   id=getattr(args, "wandb_run_id", None), resume="allow" if getattr(args, "wandb_run_id", None) else None)
 
     def log(self, metrics, step, step_key):
         self.wandb.log({**metrics, step_key: step})
@@ -86,7 +99,11 @@ class MlflowBackend(_Backend):
         import mlflow
 
         self.mlflow = mlflow
-        mlflow.start_run()
+        if getattr(args, "mlflow_tracking_uri", None):
+            mlflow.set_tracking_uri(args.mlflow_tracking_uri)
+        if getattr(args, "mlflow_experiment_name", None):
+            mlflow.set_experiment(args.mlflow_experiment_name)
+        mlflow.start_run(run_id=getattr(args, "mlflow_run_id", None), run_name=getattr(args, "mlflow_run_name", None))
 
     def log(self, metrics, step, step_key):
         self.mlflow.log_metrics({k.replace("/", "."): v for k, v in metrics.items() if isinstance(v, (int, float))}, step=step)

@@ -156,3 +156,30 @@ def test_train_profiler_writes_traces_for_the_selected_window(tmp_path):
         train_entry.train(args)
         names = [p.rsplit("/", 1)[-1] for p in glob.glob(str(tmp_path / "*.json*"))]
         assert any(n.startswith(f"{target}_rank_0") for n in names), (target, names)
+
+
+def test_reference_flag_surface_parses_and_wired_flags_act(tmp_path):
+    """Every flag name of the reference's own parser is accepted; a handful of the wired ones are checked for effect."""
+    import re
+
+    import train as train_entry
+    from test_e2e import BASE
+    from miles_b200.args import build_parser, parse_args
+
+    have = {s for a in build_parser()._actions for s in a.option_strings}
+    for must in ("--start-rollout-id", "--eval-top-k", "--dumper-enable", "--opd-teacher-urls", "--mlflow-tracking-uri",
+                 "--pause-generation-mode", "--session-server-port", "--ci-metric-checker-key", "--offload-train-target"):
+        assert must in have, must
+    # behaviour: stop after rollout 1 of 5, no optimizer updates, checkpoint with per-rank checksums, audit analysis at the end
+    args = parse_args((BASE + f" --num-rollout 5 --debug-exit-after-rollout 1 --debug-disable-optimizer --save {tmp_path / 'ck'} "
+                       f"--save-interval 1 --save-local-weight-checksum --enable-witness --audit-dir {tmp_path / 'au'} "
+                       "--enable-event-analyzer").split())
+    tr = train_entry.train(args)
+    assert len(tr.history.rows) == 2 and tr.actor.global_step == 0
+    assert all(g == 0.0 for g in tr.history.series("train/grad_norm"))
+    assert list((tmp_path / "ck").rglob("weight_checksum_rank00000.json"))
+    assert tr.findings == []
+    # --start-rollout-id overrides the resume point; --reset-optimizer-states restarts Adam on the loaded weights
+    args = parse_args((BASE + f" --num-rollout 4 --load {tmp_path / 'ck'} --start-rollout-id 3 --reset-optimizer-states").split())
+    tr = train_entry.train(args)
+    assert [r["rollout/step"] for r in tr.history.rows] == [3]

@@ -35,7 +35,7 @@ def train(args):
         assert args.num_epoch and len(rollout.data_source), "--num-rollout or --num-epoch (with --prompt-data) required"
         args.num_rollout = args.num_epoch * len(rollout.data_source) // args.rollout_batch_size
 
-    if not args.debug_train_only:
+    if not args.debug_train_only and not args.debug_skip_weight_update:
         update_weights(args, actor, rollout)           # initial push (and consistency check)
     if args.offload_train and not args.debug_rollout_only:
         actor.sleep()
@@ -67,7 +67,7 @@ def train(args):
 
         if args.offload_train:
             actor.sleep()
-        if _should(args.update_weights_interval, rollout_id):
+        if _should(args.update_weights_interval, rollout_id) and not args.debug_skip_weight_update:
             info = update_weights(args, actor, rollout)
             metrics["perf/update_weights_time"] = info["seconds"]
         if args.colocate and args.offload_rollout:
@@ -75,6 +75,15 @@ def train(args):
         if _should(args.eval_interval, rollout_id):
             metrics.update(rollout.executor.eval(rollout_id))
         tracker.log(metrics, rollout_id)
+        if args.debug_exit_after_rollout is not None and rollout_id >= args.debug_exit_after_rollout:
+            break
+    if args.enable_event_analyzer and args.audit_dir and ps.rank == 0:
+        from miles_b200.audit import events
+
+        findings = events.analyze(args.audit_dir)
+        tracker.findings = findings
+        if findings:
+            print(f"[audit] {len(findings)} finding(s): " + "; ".join(str(dict(f)) for f in findings[:5]))
     tracker.finish()
     tracker.actor = actor          # programmatic callers (tests, notebooks) reach the trained model through the tracker
     return tracker
