@@ -55,6 +55,10 @@ def build_parser() -> argparse.ArgumentParser:
     g.add_argument("--load", type=str, default=None)
     g.add_argument("--save", type=str, default=None)
     g.add_argument("--save-interval", type=int, default=None)
+    g.add_argument("--ckpt-format", choices=["torch_dist", "native"], default="torch_dist",
+                   help="torch_dist: one DCP store per iteration with Megatron-named entries and the optimizer state in "
+                        "model space, reloadable under any parallel layout; native: one file per rank with that rank's shards")
+    g.add_argument("--no-load-rng", action="store_true", help="do not restore the RNG state from a checkpoint")
     _bool_flag(g, "--save-hf")
     g.add_argument("--save-trigger-sentinel", type=str, default=None)
     _bool_flag(g, "--no-save-optim")

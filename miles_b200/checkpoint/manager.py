@@ -4,8 +4,11 @@ Directory layout is the reference's (miles/backends/megatron_utils/checkpoint.py
 tracker miles/backends/training_utils/checkpoint/tracker.py:5-19):
 
     <save>/latest_checkpointed_iteration.txt
-    <save>/iter_{N:07d}/model_rank{R:05d}.pt            this package's sharded format (weights by our names)
-    <save>/iter_{N:07d}/optim_rank{R:05d}.pt            optimizer shard + scheduler
+    <save>/iter_{N:07d}/.metadata, __R_0.distcp, common.pt   --ckpt-format torch_dist (default): Megatron-named entries,
+                                                        chunks written by their owners, optimizer state in model space
+                                                        (checkpoint/sharded.py); reloadable under any parallel layout
+    <save>/iter_{N:07d}/model_rank{R:05d}.pt            --ckpt-format native: this rank's shards by our names
+    <save>/iter_{N:07d}/optim_rank{R:05d}.pt            … its optimizer shard + scheduler
     <save>/iter_{N:07d}/hf/…                            optional HF safetensors export (--save-hf)
     <save>/iter_{N:07d}/.complete                       written last, after every rank finished
     <save>/rollout/global_dataset_state_dict_{N}.pt     data-source state (written by the data source)
@@ -84,6 +87,29 @@ def save_from_actor(actor, args, iteration: int, with_optimizer: bool = True):
     rank, world = _rank_world()
     d = iter_dir(root, iteration)
 
+    fmt = getattr(args, "ckpt_format", "torch_dist")
+    from . import sharded
+
+    use_dist = (fmt == "torch_dist" and not getattr(actor, "fsdp", False) and sharded.supported(actor.cfg, actor.ps)
+                and hasattr(actor.model, "named_parameters_global"))
+    with_opt = with_optimizer and not getattr(args, "no_save_optim", False)
+
+    def write_dist(directory):
+        meta = {"iteration": iteration, "cfg": actor.cfg.asdict(), "world_size": world, "checkpoint_version": 3.0,
+                "weight_version": actor.weight_version, "global_step": actor.global_step,
+                "optimizer": {"step_count": actor.optimizer.step_count}, "scheduler": actor.scheduler.state_dict(),
+                "args": {k: v for k, v in vars(args).items() if isinstance(v, (int, float, str, bool, type(None), list, tuple))}}
+        sharded.save(actor, directory, with_optimizer=with_opt, common=meta)
+        torch.save({"rng": torch.get_rng_state()}, os.path.join(directory, f"rng_rank{rank:05d}.pt"))
+        _save_hf(directory)
+
+    def _save_hf(directory):
+        if getattr(args, "save_hf", False):
+            from ..weight_update.hf_iterator import iter_hf_weights
+
+            hf_io.save_hf_sharded(os.path.join(directory, "hf"), iter_hf_weights(actor, bucket_bytes=None), actor.cfg,
+                                  write=(rank == 0), src_dir=getattr(args, "hf_checkpoint", None))
+
     def write(directory):
         state = {n: t.detach().cpu() for n, t in actor.named_weights()}       # model-wide names (pipeline stages too)
         meta = {"iteration": iteration, "cfg": actor.cfg.asdict(), "world_size": world,
@@ -91,16 +117,21 @@ def save_from_actor(actor, args, iteration: int, with_optimizer: bool = True):
                 "tp_rank": actor.ps.tp_rank, "pp_rank": actor.ps.pp_rank, "ep_rank": actor.ps.ep_rank,
                 "dp_rank": actor.ps.dp_rank, "weight_version": actor.weight_version, "global_step": actor.global_step}
         torch.save({"model": state, "meta": meta}, os.path.join(directory, f"model_rank{rank:05d}.pt"))
-        if with_optimizer and not getattr(args, "no_save_optim", False):
+        if with_opt:
             torch.save({"optimizer": actor.optimizer.state_dict(), "scheduler": actor.scheduler.state_dict(),
                         "rng": torch.get_rng_state()}, os.path.join(directory, f"optim_rank{rank:05d}.pt"))
-        if getattr(args, "save_hf", False):
-            from ..weight_update.hf_iterator import iter_hf_weights
+        _save_hf(directory)
 
-            hf_io.save_hf_sharded(os.path.join(directory, "hf"), iter_hf_weights(actor, bucket_bytes=None), actor.cfg,
-                                  write=(rank == 0), src_dir=getattr(args, "hf_checkpoint", None))
+    def write_fsdp(directory):
+        from . import fsdp_dcp
 
-    collective_write(d, write)
+        fsdp_dcp.save(actor, directory, iteration, with_optimizer=with_opt)
+        _save_hf(directory)
+
+    if fmt == "torch_dist" and getattr(actor, "fsdp", False):
+        collective_write(d, write_fsdp)
+    else:
+        collective_write(d, write_dist if use_dist else write)
     if rank == 0:
         write_tracker(root, iteration)
 
@@ -122,11 +153,21 @@ def load_weights_only(actor, path: str):
         blob = torch.load(mine, map_location="cpu", weights_only=False)
         load_named_into_model(actor.model, blob["model"].items(), actor.cfg, actor.ps)
         return blob["meta"]
-    from . import torch_dist
+    from . import fsdp_dcp, torch_dist
 
+    if fsdp_dcp.is_fsdp_dir(d):
+        assert getattr(actor, "fsdp", False), f"{d} holds an FSDP-backend checkpoint; load it with --train-backend fsdp"
+        meta = fsdp_dcp.load_model(actor, d)
+        return {"iteration": meta.get("iteration", 0), "weight_version": meta.get("weight_version", 0),
+                "global_step": meta.get("global_step", 0), "optimizer": {"step_count": meta.get("optimizer_steps", 0)}}
     if torch_dist.is_torch_dist_dir(d):
         from ..models.convert import megatron_to_ours
+        from . import sharded
 
+        if sharded.supported(actor.cfg, actor.ps) and hasattr(actor.model, "named_parameters_global") and \
+                not getattr(actor, "fsdp", False) and torch_dist.has_per_layer_names(d):
+            common = sharded.load(actor, d, with_optimizer=False)
+            return common or {"iteration": it if isinstance(it, int) else 0}
         full = megatron_to_ours(torch_dist.load_state(d), actor.cfg)
         load_named_into_model(actor.model, full.items(), actor.cfg, actor.ps)
         return {"iteration": it if isinstance(it, int) else 0}
@@ -141,9 +182,24 @@ def load_into_actor(actor, args) -> int | None:
         it = read_tracker(load)
         actor.optimizer.reload_master_from_params()
         rank, _ = _rank_world()
-        opt_path = os.path.join(iter_dir(load, it) if isinstance(it, int) else os.path.join(load, "release"),
-                                f"optim_rank{rank:05d}.pt")
-        if os.path.exists(opt_path) and not getattr(args, "no_load_optim", False) and not getattr(args, "finetune", False):
+        d = iter_dir(load, it) if isinstance(it, int) else os.path.join(load, "release")
+        opt_path = os.path.join(d, f"optim_rank{rank:05d}.pt")
+        want_opt = not getattr(args, "no_load_optim", False) and not getattr(args, "finetune", False)
+        from . import fsdp_dcp, sharded, torch_dist
+
+        if want_opt and fsdp_dcp.is_fsdp_dir(d) and getattr(actor, "fsdp", False):
+            if fsdp_dcp.load_optimizer(actor, d, load_rng=not getattr(args, "no_load_rng", False)) and meta:
+                actor.optimizer.step_count = meta.get("optimizer", {}).get("step_count", 0)
+        elif want_opt and not os.path.exists(opt_path) and torch_dist.is_torch_dist_dir(d) and sharded.has_optimizer(d) \
+                and hasattr(actor.optimizer, "domains"):
+            sharded.load_optimizer(actor, d)
+            if meta and "scheduler" in meta:
+                actor.scheduler.load_state_dict(meta["scheduler"])
+                actor.optimizer.step_count = meta.get("optimizer", {}).get("step_count", 0)
+            rng = os.path.join(d, f"rng_rank{rank:05d}.pt")
+            if os.path.exists(rng) and not getattr(args, "no_load_rng", False):
+                torch.set_rng_state(torch.load(rng, weights_only=False)["rng"])
+        elif os.path.exists(opt_path) and want_opt:
             blob = torch.load(opt_path, map_location="cpu", weights_only=False)
             actor.optimizer.load_state_dict(blob["optimizer"])
             actor.scheduler.load_state_dict(blob["scheduler"])

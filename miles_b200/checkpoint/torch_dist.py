@@ -18,6 +18,18 @@ def is_torch_dist_dir(d: str) -> bool:
     return os.path.isdir(d) and os.path.exists(os.path.join(d, ".metadata"))
 
 
+def has_per_layer_names(d: str) -> bool:
+    """True when the store names decoder layers one by one (`decoder.layers.<i>.…`); Megatron-core may instead stack all
+    layers of a block under one entry with a leading layer axis, which `load_state` unstacks."""
+    import re
+
+    import torch.distributed.checkpoint as dcp
+
+    keys = dcp.FileSystemReader(d).read_metadata().state_dict_metadata.keys()
+    layered = [k for k in keys if ".layers." in k and "optimizer" not in k]
+    return all(re.search(r"\.layers\.\d+\.", k) for k in layered)
+
+
 def find_iteration_dir(root: str) -> str:
     """`root` may be the iteration directory itself or a Megatron checkpoint root with
     `latest_checkpointed_iteration.txt`."""
@@ -48,11 +60,23 @@ def load_state(d: str, prefix_filter: tuple[str, ...] = ("optimizer", "rng", "_e
             continue
         sd[name] = torch.empty(m.size, dtype=m.properties.dtype)
     dcp.load(sd, storage_reader=reader, no_dist=True)
+    import re
+
     out = {}
     for k, v in sd.items():
         k = k[len("model."):] if k.startswith("model.") else k      # Megatron nests weights under "model."
         k = k[len("module.module."):] if k.startswith("module.module.") else k
-        out[k] = v
+        # Megatron-core may store all layers of a block as ONE entry with a leading layer axis, and grouped experts as
+        # one entry with a leading expert axis: split both into the per-layer / per-expert names
+        layered = [(k, v)]
+        if ".layers." in k and not re.search(r"\.layers\.\d+\.", k):
+            layered = [(k.replace(".layers.", f".layers.{i}."), v[i]) for i in range(v.shape[0])]
+        for k2, v2 in layered:
+            if ".experts.experts." in k2 and not re.search(r"\.weight\d+$", k2):
+                for e in range(v2.shape[0]):
+                    out[k2.replace(".experts.experts.", ".experts.") + str(e)] = v2[e]
+            else:
+                out[k2] = v2
     return out
 
 

@@ -43,6 +43,8 @@ class _Domain:
     shard: tuple[int, int] = (0, 0)
     numel: int = 0
     decay_mask: torch.Tensor | None = None  # fp32 shard, 1 where weight decay applies
+    names: list[str] = None             # parameter names, in buffer order
+    offsets: list[int] = None           # element offset of each parameter in the flat buffers
 
 
 class DistributedAdam:
@@ -86,7 +88,7 @@ class DistributedAdam:
             total += (p.numel() + ALIGN - 1) // ALIGN * ALIGN
         unit = ALIGN * gsize
         n_pad = (total + unit - 1) // unit * unit
-        d = _Domain(name, params, group, gsize, grank, numel=n_pad)
+        d = _Domain(name, params, group, gsize, grank, numel=n_pad, names=[n for n, _ in named], offsets=offs)
         d.param_buf = self._alloc(n_pad, dtype, device, f"{name}.param")
         d.grad_buf = self._alloc(n_pad, torch.float32, device, f"{name}.grad")
         decay = torch.zeros(n_pad, dtype=torch.float32, device=device)

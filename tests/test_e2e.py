@@ -146,6 +146,13 @@ def test_fsdp_checkpoint_save_and_resume(tmp_path):
     rows2 = _dist_hist(tmp_path / "b", f"--train-backend fsdp --save {d} --load {d} --save-interval 1 --num-rollout 3")
     assert len(rows1) == 2 and [r["rollout/step"] for r in rows2] == [2]            # resumed after two saved rollouts
     assert rows2[0]["train/train_rollout_logprob_abs_diff"] < 1e-5                  # the reloaded shards feed the engine
+    it = os.path.join(d, "iter_0000001")                                            # one DCP store per kind of state
+    for sub in ("model/.metadata", "optimizer/.metadata", "lr_scheduler/.metadata", "rng.pt", "meta.json"):
+        assert os.path.exists(os.path.join(it, sub)), sub
+    import torch.distributed.checkpoint as dcp
+
+    keys = dcp.FileSystemReader(os.path.join(it, "optimizer")).read_metadata().state_dict_metadata
+    assert "optim_state.optim.state.layers.0.attn.wo.exp_avg" in keys
 
 
 # ---- asynchronous loops --------------------------------------------------------------------------------------------
