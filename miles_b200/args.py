@@ -33,6 +33,15 @@ def build_parser() -> argparse.ArgumentParser:
     g.add_argument("--critic-num-gpus-per-node", type=int, default=None)
     g.add_argument("--rollout-num-gpus", type=int, default=None)
     g.add_argument("--rollout-num-gpus-per-engine", type=int, default=1)
+    g.add_argument("--worker-provider", choices=["none", "local", "static", "registration"], default="none",
+                   help="with --rollout-engine http: where engine servers come from. local: launched, watched and restarted "
+                        "by this job; static: already running at --rollout-engine-addrs; registration: they announce "
+                        "themselves to the hub at --registration-hub-port; none: only a router URL is given (--engine-router-url)")
+    g.add_argument("--rollout-num-engines", type=int, default=1, help="engine servers to launch with --worker-provider local")
+    g.add_argument("--rollout-engine-addrs", nargs="*", default=None, help="host:port of running engine servers (static provider)")
+    g.add_argument("--registration-hub-port", type=int, default=None)
+    g.add_argument("--registration-ttl", type=float, default=30.0)
+    g.add_argument("--worker-log-dir", type=str, default=None)
     g.add_argument("--num-gpus-per-node", type=int, default=8)
     _bool_flag(g, "--colocate", help="trainer and rollout engine share the same GPUs")
     _bool_flag(g, "--offload-train")

@@ -58,7 +58,7 @@ def _rank_world():
     return 0, 1
 
 
-def collective_write(directory: str, write_fn) -> None:
+def collective_write(directory: str, write_fn, group=None) -> None:
     """Run `write_fn(directory)` on every rank; raise everywhere if anyone failed; mark complete."""
     rank, world = _rank_world()
     os.makedirs(directory, exist_ok=True)
@@ -69,7 +69,7 @@ def collective_write(directory: str, write_fn) -> None:
         err = f"rank {rank}: {type(e).__name__}: {e}"
     if world > 1:
         errs: list = [None] * world
-        dist.all_gather_object(errs, err)
+        dist.all_gather_object(errs, err, group=group)
     else:
         errs = [err]
     bad = [e for e in errs if e]
@@ -78,7 +78,55 @@ def collective_write(directory: str, write_fn) -> None:
     if rank == 0:
         open(os.path.join(directory, ".complete"), "w").close()
     if world > 1:
-        dist.barrier()
+        dist.barrier(group=group)
+
+
+class _AsyncSave:
+    """`--async-save`: the training thread stages this rank's chunks in host memory, a writer thread plans and writes the
+    store over its OWN gloo process group (so its collectives never interleave with the trainer's), then marks the
+    directory complete and moves the tracker.  At most one save is in flight: the next save, `finalize_async_save()` and
+    interpreter exit wait for it and re-raise its error (the reference: `--async-save`,
+    miles/backends/megatron_utils/checkpoint.py, Megatron's async strategy)."""
+
+    def __init__(self):
+        self.thread = None
+        self.error: BaseException | None = None
+        self.group = None
+
+    def ensure_group(self):
+        if self.group is None and dist.is_initialized() and dist.get_world_size() > 1:
+            self.group = dist.new_group(backend="gloo")              # collective: every rank takes this path together
+        return self.group
+
+    def wait(self):
+        t, self.thread = self.thread, None
+        if t is not None:
+            t.join()
+        if self.error is not None:
+            e, self.error = self.error, None
+            raise RuntimeError(f"asynchronous checkpoint save failed: {e}") from e
+
+    def start(self, fn):
+        import threading
+
+        self.wait()
+
+        def run():
+            try:
+                fn()
+            except BaseException as e:  # surfaced by the next wait()
+                self.error = e
+
+        self.thread = threading.Thread(target=run, name="ckpt-writer", daemon=False)
+        self.thread.start()
+
+
+_ASYNC = _AsyncSave()
+
+
+def finalize_async_save():
+    """Block until the checkpoint in flight (if any) is on disk; raises if it failed."""
+    _ASYNC.wait()
 
 
 def save_from_actor(actor, args, iteration: int, with_optimizer: bool = True):
@@ -128,6 +176,26 @@ def save_from_actor(actor, args, iteration: int, with_optimizer: bool = True):
         fsdp_dcp.save(actor, directory, iteration, with_optimizer=with_opt)
         _save_hf(directory)
 
+    if use_dist and getattr(args, "async_save", False):
+        group = _ASYNC.ensure_group()
+        _ASYNC.wait()
+        staged = sharded.stage(actor, with_optimizer=with_opt, to_host=True)
+        meta = {"iteration": iteration, "cfg": actor.cfg.asdict(), "world_size": world, "checkpoint_version": 3.0,
+                "weight_version": actor.weight_version, "global_step": actor.global_step,
+                "optimizer": {"step_count": actor.optimizer.step_count}, "scheduler": actor.scheduler.state_dict()}
+        rng = torch.get_rng_state()
+
+        def job():
+            def w(directory):
+                sharded.write_staged(staged, directory, common=meta, process_group=group)
+                torch.save({"rng": rng}, os.path.join(directory, f"rng_rank{rank:05d}.pt"))
+
+            collective_write(d, w, group=group)
+            if rank == 0:
+                write_tracker(root, iteration)
+
+        _ASYNC.start(job)
+        return
     if fmt == "torch_dist" and getattr(actor, "fsdp", False):
         collective_write(d, write_fsdp)
     else:

@@ -225,9 +225,12 @@ def _build_state(named, cfg, ps, names, prefix: str, for_load: bool):
 
 def save(actor, directory: str, *, with_optimizer: bool = True, common: dict | None = None) -> None:
     """Collective: write this rank's chunks of the model (and optimizer) into the DCP store at `directory`."""
-    import torch.distributed.checkpoint as dcp
+    write_staged(stage(actor, with_optimizer=with_optimizer, to_host=False), directory, common=common)
 
-    Save, _ = _planners()
+
+def stage(actor, *, with_optimizer: bool = True, to_host: bool = True) -> dict:
+    """Collective (the optimizer shards are gathered): this rank's chunks, copied to host memory when `to_host` so that
+    training may go on while another thread writes them."""
     cfg, ps = actor.cfg, actor.ps
     names = megatron_name_map(cfg)
     state, _ = _build_state(_model_items(actor), cfg, ps, names, "", for_load=False)
@@ -240,10 +243,21 @@ def save(actor, directory: str, *, with_optimizer: bool = True, common: dict | N
                 ch.parts = [(off, t.cpu()) for off, t in ch.parts]
             state.update(st)
             del items, flats
+    if to_host:
+        for ch in state.values():
+            ch.parts = [(off, t.cpu().clone() if t.device.type == "cpu" else t.cpu()) for off, t in ch.parts]
+    return state
+
+
+def write_staged(state: dict, directory: str, *, common: dict | None = None, process_group=None) -> None:
+    """Collective over `process_group` (default: the world): plan and write the staged chunks."""
+    import torch.distributed.checkpoint as dcp
+
+    Save, _ = _planners()
     world = dist.is_initialized() and dist.get_world_size() > 1
     os.makedirs(directory, exist_ok=True)
     dcp.save(state, storage_writer=dcp.FileSystemWriter(directory, single_file_per_rank=True, thread_count=1),
-             planner=Save(), no_dist=not world)
+             planner=Save(), no_dist=not world, process_group=process_group if world else None)
     if (not dist.is_initialized() or dist.get_rank() == 0) and common is not None:
         torch.save(common, os.path.join(directory, COMMON))
 

@@ -87,6 +87,11 @@ def build_app(engine, tokenizer=None):
         engine.continue_generation()
         return {"success": True}
 
+    @app.post("/flush_cache")
+    async def flush_cache():
+        engine.flush_cache()
+        return {"success": True}
+
     @app.post("/abort_request")
     async def abort(request: Request):
         body = await _json(request)

@@ -25,6 +25,7 @@ class RolloutComponents:
     executor: Any
     data_source: Any
     controller: Any = None          # InferenceController over `engines`: memory hand-over, weight-update framing, health
+    fleet: Any = None               # workers.fleet.Fleet when engine servers run as supervised processes (HTTP engines)
 
 
 def create_parallel_state(args) -> ParallelState:
@@ -153,8 +154,24 @@ def create_rollout_components(args, ps: ParallelState, actor=None, tracker=None)
     data_source = ds_cls(args, tok)
     kind = getattr(args, "rollout_engine", "native")
     engines: list = []
+    fleet = None
     if kind == "http":
-        client = HttpEngineClient(args.engine_kwargs["router_url"], tokenizer=tok,
+        router_url = (getattr(args, "engine_kwargs", None) or {}).get("router_url")
+        worker_urls = None
+        if getattr(args, "worker_provider", "none") != "none":
+            # engine servers + router as supervised worker processes (or adopted from elsewhere): rank 0 owns the fleet,
+            # the other ranks only learn the router's address
+            from .workers.fleet import launch_fleet
+
+            if ps.rank == 0:
+                fleet = launch_fleet(args, log_dir=getattr(args, "worker_log_dir", None))
+                engines = list(fleet.engines.values())
+                router_url, worker_urls = fleet.router_url, [e.url for e in engines]
+            if ps.world_size > 1:
+                box = [router_url, worker_urls]
+                torch.distributed.broadcast_object_list(box, src=0)
+                router_url, worker_urls = box
+        client = HttpEngineClient(router_url, tokenizer=tok, worker_urls=worker_urls,
                                   num_moe_layers=sum(cfg.layer_is_moe(l) for l in range(cfg.num_layers)), moe_topk=cfg.moe_topk)
     else:
         ek = dict(getattr(args, "engine_kwargs", {}) or {})
@@ -201,7 +218,11 @@ def create_rollout_components(args, ps: ParallelState, actor=None, tracker=None)
                                          probe=lambda e: e.health().get("status") == "ok",
                                          health_threshold=getattr(args, "miles_router_health_check_failure_threshold", 3) or 3)
         controller.pause_mode = getattr(args, "pause_generation_mode", None) or "retract"
-    return RolloutComponents(engines=engines, client=client, executor=ex, data_source=data_source, controller=controller)
+        if fleet is not None:
+            # a cell restarted by the fleet watcher comes back with fresh weights: stale until the updater has re-sent them
+            fleet.on_restart = lambda e: setattr(controller._cell_of(e), "state", "stale")
+    return RolloutComponents(engines=engines, client=client, executor=ex, data_source=data_source, controller=controller,
+                             fleet=fleet)
 
 
 def update_weights(args, actor, rollout: RolloutComponents, updater=None) -> dict:

@@ -159,7 +159,7 @@ class HttpEngineClient:
         await self.start()
 
     async def finish(self):
-        pass
+        await self.close()            # the session belongs to the event loop of this rollout; the next one opens its own
 
     async def call_all(self, endpoint: str, body: dict | None = None) -> list:
         targets = self.worker_urls or [self.base_url]

@@ -43,13 +43,21 @@ def _full_ours(preset):
     return {n: p.detach().clone() for n, p in m.named_parameters()}
 
 
-def _save_body(rank, world, preset, ps_kw, root):
+def _save_body(rank, world, preset, ps_kw, root, extra=""):
     sys.path.insert(0, ROOT)
     from miles_b200.checkpoint import manager
 
-    actor, args = _actor(preset, f"--save {root} --seed 5", ps_kw)
+    actor, args = _actor(preset, f"--save {root} --seed 5 {extra}", ps_kw)
     _fake_step(actor, 0)
     manager.save_from_actor(actor, args, 3)
+    if extra:
+        # the writer thread works from host copies: training may overwrite parameters and state straight away
+        for p in actor.model.parameters():
+            p.data.zero_()
+        for d in actor.optimizer.domains:
+            d.exp_avg.zero_()
+        manager.finalize_async_save()
+        assert os.path.exists(os.path.join(root, "iter_0000003", ".complete"))
 
 
 def _load_body(rank, world, preset, ps_kw, root, out):
@@ -103,6 +111,24 @@ def test_store_round_trips_across_layouts(tmp_path, preset, src, dst):
         ps = ParallelState.build(**dst, rank=r, world_size=2, create_groups=False)
         for n, t in got.items():
             assert torch.equal(t, shard_for_rank(n, want[n], cfg, ps)), (n, r)
+
+
+def test_async_save_writes_the_staged_state(tmp_path):
+    from miles_b200.checkpoint import torch_dist
+    from miles_b200.models.config import PRESETS
+    from miles_b200.models.convert import megatron_to_ours
+
+    root = str(tmp_path / "ckpt")
+    run_distributed(_save_body, 2, ("tiny", dict(tp=2), root, "--async-save"))
+    d = os.path.join(root, "iter_0000003")
+    full = megatron_to_ours(torch_dist.load_state(d), PRESETS["tiny"])
+    want = _full_ours("tiny")
+    for n in want:
+        assert torch.equal(full[n], want[n]), n
+    opt = torch_dist.load_state(d, prefix_filter=("rng", "_extra_state"))
+    k = "optimizer.state.exp_avg.decoder.layers.1.mlp.linear_fc2.weight"
+    assert torch.equal(opt[k], want["layers.1.mlp.w2"] * 0.5 + 0.25)
+    assert open(os.path.join(root, "latest_checkpointed_iteration.txt")).read().strip() == "3"
 
 
 def test_stacked_layer_entries_are_unstacked(tmp_path):

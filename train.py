@@ -84,6 +84,11 @@ def train(args):
         tracker.findings = findings
         if findings:
             print(f"[audit] {len(findings)} finding(s): " + "; ".join(str(dict(f)) for f in findings[:5]))
+    from miles_b200.checkpoint.manager import finalize_async_save
+
+    finalize_async_save()                 # --async-save: the last checkpoint is on disk before the run ends
+    if getattr(rollout, "fleet", None) is not None:
+        rollout.fleet.shutdown()          # engine servers and router launched by this job
     tracker.finish()
     tracker.actor = actor          # programmatic callers (tests, notebooks) reach the trained model through the tracker
     return tracker

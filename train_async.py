@@ -76,6 +76,11 @@ def train(args):
     finally:
         rollout.executor.shutdown()
         pool.shutdown(wait=True)
+    from miles_b200.checkpoint.manager import finalize_async_save
+
+    finalize_async_save()                 # --async-save: the last checkpoint is on disk before the run ends
+    if getattr(rollout, "fleet", None) is not None:
+        rollout.fleet.shutdown()          # engine servers and router launched by this job
     tracker.finish()
     return tracker
 
