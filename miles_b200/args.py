@@ -64,6 +64,10 @@ def build_parser() -> argparse.ArgumentParser:
     g.add_argument("--load", type=str, default=None)
     g.add_argument("--save", type=str, default=None)
     g.add_argument("--save-interval", type=int, default=None)
+    g.add_argument("--offload-train-release-process-groups", action="store_true",
+                   help="with --offload-train: also destroy the trainer's communicators while it sleeps (their device buffers "
+                        "are freed) and re-create them on wake-up; only when the rollout engines do not share them "
+                        "(--rollout-engine http, or in-process engines with tp = ep = 1)")
     g.add_argument("--ckpt-format", choices=["torch_dist", "native"], default="torch_dist",
                    help="torch_dist: one DCP store per iteration with Megatron-named entries and the optimizer state in "
                         "model space, reloadable under any parallel layout; native: one file per rank with that rank's shards")

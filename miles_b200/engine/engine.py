@@ -154,6 +154,10 @@ class Engine:
         self._graphs: dict[int, Any] = {}
         # expert-parallel engines step in lockstep over the EP group (see `_step_lockstep`)
         self.lockstep_group = self.ps.ep_group if (self.ps.ep_size > 1 and cfg.is_moe) else None
+        if self.lockstep_group is not None:
+            from ..parallel.reloadable import REGISTRY
+
+            REGISTRY.bind(self, "lockstep_group")
         self.local_done = True
         self.global_done = True
         self.runner = None

@@ -126,7 +126,10 @@ class _RetryableActor:
         return None            # the actor of this process is initialised by `create_training_models`
 
     def train(self, rollout_id, shard):
+        from ..testing import fault_injector
+
         try:
+            fault_injector.GLOBAL.at("train", step=rollout_id)    # host-side injection point, before anything is launched
             return self.actor.train(rollout_id, shard)
         except BaseException:
             self.actor.optimizer.zero_grad()

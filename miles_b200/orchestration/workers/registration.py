@@ -11,6 +11,12 @@ reporter.py:28-146 (debounced interval trigger, snapshot), models.py.
 """
 from __future__ import annotations
 
+try:  # module level: route signatures are resolved against module globals
+    from fastapi import FastAPI, HTTPException, Request
+    from fastapi.responses import JSONResponse
+except ImportError:  # the HTTP surface is optional
+    FastAPI = HTTPException = Request = JSONResponse = None
+
 import asyncio
 import json
 import time
@@ -67,8 +73,6 @@ class RegistrationHub(BaseWorkerProvider):
 
     # ---- HTTP surface ------------------------------------------------------------------------------------------
     def build_app(self):
-        from fastapi import FastAPI, HTTPException, Request
-
         app = FastAPI(title="miles_b200 registration hub")
 
         @app.post("/register")

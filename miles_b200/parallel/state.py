@@ -132,19 +132,36 @@ class ParallelState:
             "ep": [[p_ * block + g * ep + i for i in range(ep)] for p_ in range(pp) for g in range(block // ep)],
             "edp": [[p_ * block + g * ep + i for g in range(block // ep)] for p_ in range(pp) for i in range(ep)],
         }
+        from .reloadable import REGISTRY
+
         for name, lists in groups.items():
             for ranks in lists:
                 ranks_sorted = list(ranks)
                 handle = None
                 if create_groups and dist.is_initialized() and len(ranks_sorted) > 1:
-                    handle = dist.new_group(ranks_sorted)
+                    handle = REGISTRY.new_group(ranks_sorted)      # recorded: `release_groups` / `reload_groups` below
                 if rank in ranks_sorted:
                     setattr(ps, f"{name}_group", handle)
+                    REGISTRY.bind(ps, f"{name}_group")
                     if name in ("tp", "ep", "dp", "pp", "cp"):
                         setattr(ps, f"{name}_ranks", ranks_sorted)
         if dist.is_initialized():
             ps.world_group = dist.group.WORLD
         return ps
+
+    @staticmethod
+    def release_groups() -> int:
+        """Destroy every communicator made by `build` (their device buffers go back to the allocator); every rank calls
+        this at the same point.  Collectives are unavailable until `reload_groups`."""
+        from .reloadable import REGISTRY
+
+        return REGISTRY.destroy_all() if dist.is_initialized() else 0
+
+    @staticmethod
+    def reload_groups() -> int:
+        from .reloadable import REGISTRY
+
+        return REGISTRY.reload_all() if dist.is_initialized() else 0
 
     # ---------------------------------------------------------------------------------------
     # entry points used by the model

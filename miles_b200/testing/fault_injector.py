@@ -95,3 +95,11 @@ def parse_rules(spec: str) -> list[Rule]:
                           step=int(kv["step"]) if "step" in kv else None, point=kv.get("point"),
                           arg=float(kv.get("arg", 0.0)), once=kv.get("once", "1") != "0"))
     return rules
+
+
+GLOBAL = FaultInjector()          # the process-wide injector: product code calls `GLOBAL.at(point)` at a few host-side points
+
+
+def arm(point: str, error: BaseException | None = None, step: int | None = None) -> Rule:
+    """Make the next pass through `point` in this process raise (used by the cell API's inject-fault)."""
+    return GLOBAL.inject("raise", point=point, step=step, rank=GLOBAL.rank)

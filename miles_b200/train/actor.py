@@ -581,6 +581,8 @@ class TrainActor:
 
         upd = engine_or_updater if isinstance(engine_or_updater, WeightUpdater) else \
             WeightUpdater(self.args, self, engine_or_updater)
+        temporary = getattr(self, "_groups_released", False)     # asleep with released groups: bring them back for the transfer
+        self.ensure_groups()
         with self.timer.span("update_weights"):
             if getattr(self.model, "lora_adapters", None) and upd.mode != "alias":
                 from .lora import merged
@@ -588,10 +590,13 @@ class TrainActor:
                     info = upd.update_weights()
             else:
                 info = upd.update_weights()
+        if temporary:
+            self._groups_released = self.ps.release_groups() > 0
         return info
 
     def save_model(self, iteration: int, with_optimizer: bool = True):
         from ..checkpoint import manager as ckpt
+        self.ensure_groups()
         ckpt.save_from_actor(self, self.args, iteration, with_optimizer)
         if getattr(self.args, "save_local_weight_checksum", False):
             from ..audit.events import combined_checksum, model_checksums
@@ -619,12 +624,17 @@ class TrainActor:
                 self._offloaded["optimizer"] = offload_tensors(groups["optimizer"])
         if "grad" in tags:
             self.optimizer.release_grads()
+        if getattr(self.args, "offload_train_release_process_groups", False):
+            # communicators pin device memory too; with engines in other processes nothing here needs them until wake-up
+            self._groups_released = self.ps.release_groups() > 0
         self.asleep = True
 
     def wake_up(self):
         from ..utils.memory import onload_tensors
         if not self.asleep:
+            self.ensure_groups()
             return
+        self.ensure_groups()
         if getattr(self, "arena", None) is not None and getattr(self, "_arena_released", 0):
             self.arena.resume("optimizer")
             self._arena_released = 0
@@ -633,6 +643,12 @@ class TrainActor:
         self._offloaded = {}
         self.optimizer.restore_grads()
         self.asleep = False
+
+    def ensure_groups(self):
+        """Re-create the process groups released by `sleep` (collective; a no-op when they are alive)."""
+        if getattr(self, "_groups_released", False):
+            self.ps.reload_groups()
+            self._groups_released = False
 
     def named_weights(self):
         """This rank's shard, named by our layout (for checkpointing and weight sync).  With the FSDP backend every

@@ -111,6 +111,10 @@ class DistributedAdam:
             d.exp_avg = torch.zeros(s, dtype=moments_dtype, device=device)
             d.exp_avg_sq = torch.zeros(s, dtype=moments_dtype, device=device)
         d.decay_mask = decay[d.shard[0]:d.shard[1]].clone()
+        if group is not None:
+            from ..parallel.reloadable import REGISTRY
+
+            REGISTRY.bind(d, "group")                  # the handle follows a release / reload of the process groups
         return d
 
     # ---- step ----------------------------------------------------------------------------

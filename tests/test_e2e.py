@@ -123,6 +123,7 @@ def _dist_hist(tmp_path, extra, world=2):
     "--model-name tiny-moe --expert-model-parallel-size 2 --use-rollout-routing-replay --rollout-data-exchange local",
     "--context-parallel-size 2 --cp-comm-type a2a",                         # cp2 (Ulysses), dp1
     "--train-backend fsdp",                                                 # dp2, parameters sharded per layer (FSDP2)
+    "--offload-train --offload-train-release-process-groups",               # dp2, communicators destroyed while asleep
     "--context-parallel-size 2",                                            # cp2, ring attention over zigzag pieces
     "--context-parallel-size 2 --allgather-cp",                             # cp2, K/V all-gathered
     "--pipeline-model-parallel-size 2 --micro-batch-size 8",                # pp2, 4 micro-batches per step, 1F1B order

@@ -246,3 +246,148 @@ def test_train_py_retries_a_failed_trainer_call_under_fault_tolerance(monkeypatc
     tr = train_entry.train(args)
     assert calls["n"] == 3 and len(tr.history.rows) == 2
     assert tr.actor.global_step == 2
+
+
+# ---- cell REST API + the in-job controller loop ---------------------------------------------------------------------
+
+def _free_port():
+    import socket
+
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        return s.getsockname()[1]
+
+
+def test_cell_api_lists_fences_and_heals():
+    import types
+
+    import requests
+
+    from miles_b200.ft.api_server import MiniFTController, http_cell_client, start_api_server
+    from miles_b200.ft.controller import Cell, CellController
+    from miles_b200.orchestration.inference_controller import InferenceController, ServerCell, ServerGroup
+
+    class W:
+        def __init__(self):
+            self.fail = False
+
+        def init(self):
+            return "ok"
+
+        def train(self, step):
+            if self.fail:
+                raise RuntimeError("host-side failure")
+            return step
+
+    class Eng:
+        def __init__(self):
+            self.ok, self.version, self.paused = True, 0, False
+
+        def pause_generation(self, mode="retract"):
+            self.paused = True
+
+        def continue_generation(self):
+            self.paused = False
+
+        def get_weight_version(self):
+            return self.version
+
+    workers = [W(), W()]
+    cells = CellController([Cell(0, [workers[0]]), Cell(1, [workers[1]])], min_quorum=1)
+    cells.execute("init")
+    trainer = types.SimpleNamespace(cells=cells)
+    engines = [Eng(), Eng()]
+    group = ServerGroup("regular", 1, 1)
+    ictl = InferenceController([ServerCell(e, "default", group) for e in engines], probe=lambda e: e.ok, health_threshold=1)
+    rollout = types.SimpleNamespace(controller=ictl, fleet=None)
+    port = _free_port()
+    server, thread, _ = start_api_server(types.SimpleNamespace(api_server_port=port, api_server_host="127.0.0.1"), trainer, rollout)
+    base = f"http://127.0.0.1:{port}/api/v1"
+    try:
+        assert requests.get(f"{base}/health").json() == {"status": "ok"}
+        items = requests.get(f"{base}/cells").json()["items"]
+        assert [c["metadata"]["name"] for c in items] == ["trainer-0", "trainer-1", "rollout-0", "rollout-1"]
+        assert all(c["status"]["phase"] == "Running" for c in items)
+        r = requests.get(f"{base}/cells/nope")
+        assert r.status_code == 404 and r.json()["reason"] == "NotFound" and r.json()["kind"] == "Status"
+        assert requests.patch(f"{base}/cells/trainer-1", json={"spec": {"pause": True}}).status_code == 400
+        # a trainer cell fails on the host → the API shows it, the controller loop fences and later heals it
+        workers[1].fail = True
+        cells.execute("train", 1)                                  # retried on the quorum (cell 0)
+        c1 = requests.get(f"{base}/cells/trainer-1").json()
+        assert c1["status"]["phase"] == "Failed" and c1["status"]["conditions"][1]["status"] == "False"
+        now = [0.0]
+        get_cells, patch = http_cell_client(f"http://127.0.0.1:{port}")
+        ft = MiniFTController(get_cells, patch, resume_delay=5.0, clock=lambda: now[0])
+        ft.poll_and_heal()
+        assert ft.log == [("suspended", "trainer-1", 5.0)]
+        assert requests.get(f"{base}/cells/trainer-1").json()["spec"]["suspend"] is True
+        now[0] = 4.0
+        ft.poll_and_heal()                                         # still fenced: the delay has not passed
+        assert len(ft.log) == 1
+        workers[1].fail = False
+        now[0] = 5.5
+        ft.poll_and_heal()
+        assert ft.log[-1] == ("resumed", "trainer-1")
+        c1 = requests.get(f"{base}/cells/trainer-1").json()
+        assert c1["status"]["phase"] == "Running" and c1["status"]["generation"] == 1 and not c1["spec"]["suspend"]
+        assert sorted(cells.execute("train", 2)) == [0, 1]
+        # rollout cells: a failed probe shows as unhealthy; suspend pauses the engine; resume re-admits it as stale when it
+        # missed a weight update
+        engines[0].ok = False
+        ictl.tick()
+        assert requests.get(f"{base}/cells/rollout-0").json()["status"]["phase"] == "Failed"
+        ictl.weight_version = 3
+        engines[0].ok = True
+        requests.patch(f"{base}/cells/rollout-0", json={"spec": {"suspend": True}})
+        assert engines[0].paused
+        out = requests.patch(f"{base}/cells/rollout-0", json={"spec": {"suspend": False}}).json()
+        assert out["status"]["phase"] == "Running" and not engines[0].paused and ictl.stale_engines() == [engines[0]]
+        # fault injection is refused where there is no process of ours to signal
+        r = requests.post(f"{base}/cells/rollout-1/inject-fault", json={"mode": "kill"})
+        assert r.status_code == 400 and r.json()["reason"] == "BadRequest"
+        # second consecutive failure of the same cell doubles the fence time
+        workers[1].fail = True
+        cells.execute("train", 3)
+        ft.poll_and_heal()
+        assert ft.log[-1] == ("suspended", "trainer-1", 10.0)
+    finally:
+        server.should_exit = True
+        thread.join(5)
+
+
+def test_api_fault_injection_makes_the_next_train_call_raise_and_retry(tmp_path):
+    """inject-fault (mode raise) on the trainer cell of this process: the next train call raises on the host before any
+    launch, the fault-tolerant handle rolls back and retries, the step completes."""
+    import sys
+
+    sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+    import requests
+
+    from test_e2e import BASE
+    from miles_b200.args import parse_args
+    from miles_b200.ft.api_server import start_api_server
+    from miles_b200.orchestration.wiring import (create_parallel_state, create_rollout_components, create_trainer_controller,
+                                                 create_training_models)
+    from miles_b200.testing import fault_injector
+    from miles_b200.utils import object_store
+
+    port = _free_port()
+    args = parse_args((BASE + f" --use-fault-tolerance --api-server-port {port}").split())
+    ps = create_parallel_state(args)
+    actor, _, _ = create_training_models(args, ps)
+    trainer = create_trainer_controller(args, actor)
+    rollout = create_rollout_components(args, ps, actor)
+    server, thread, _ = start_api_server(args, trainer, rollout)
+    try:
+        r = requests.post(f"http://127.0.0.1:{port}/api/v1/cells/trainer-0/inject-fault", json={"mode": "raise"})
+        assert r.status_code == 200
+        pack = rollout.executor.get(0)
+        out = trainer.train(0, object_store.get(pack.data_ref))
+        assert out["train/grad_norm"] > 0
+        assert ("raise", "train", 0) in fault_injector.GLOBAL.log
+        kinds = [k for k, _ in trainer.cells.log]
+        assert "cell_failed" in kinds and "healed" in kinds
+    finally:
+        server.should_exit = True
+        thread.join(5)

@@ -117,3 +117,42 @@ def test_perf_and_rollout_stats(tmp_path):
     except AssertionError:
         pass
     M.check_kl_zero_at_step0(torch.zeros(3), torch.zeros(3))
+
+
+# ---- reloadable process groups ----------------------------------------------------------------------------------------
+
+def _reload_body(rank, world):
+    import torch
+    import torch.distributed as dist
+
+    from miles_b200.parallel.reloadable import REGISTRY
+    from miles_b200.parallel.state import ParallelState
+
+    ps = ParallelState.build(tp=2)                 # world 4: tp groups {0,1},{2,3}; dp groups {0,2},{1,3}
+
+    class Holder:
+        pass
+
+    h = Holder()
+    h.group = ps.dp_group
+    assert REGISTRY.bind(h, "group") and not REGISTRY.bind(h, "missing")
+    x = torch.ones(1) * (rank + 1)
+    dist.all_reduce(x, group=ps.tp_group)
+    assert x.item() == (3 if rank < 2 else 7)
+    n = ps.release_groups()
+    assert n > 0 and ps.tp_group is None and ps.dp_group is None and h.group is None and REGISTRY.released
+    y = torch.ones(1)
+    dist.all_reduce(y)                              # the world group stays
+    assert y.item() == world
+    assert ps.reload_groups() == n and not REGISTRY.released
+    assert ps.tp_group is not None and h.group is ps.dp_group
+    z = torch.ones(1) * (rank + 1)
+    dist.all_reduce(z, group=h.group)
+    assert z.item() == (4 if rank % 2 == 0 else 6)
+    assert ps.reload_groups() == 0                  # nothing left to re-create
+
+
+def test_process_groups_release_and_reload():
+    from dist_utils import run_distributed
+
+    run_distributed(_reload_body, 4)

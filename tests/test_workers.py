@@ -223,3 +223,29 @@ def test_engine_fleet_survives_a_lost_engine(tmp_path):
         assert len(object_store.get(pack.data_ref)["tokens"]) == 8
     finally:
         fleet.shutdown()
+
+
+def test_registration_hub_over_http():
+    import socket
+
+    import requests
+
+    from miles_b200.orchestration.workers.registration import http_poster
+
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        port = s.getsockname()[1]
+    hub = RegistrationHub(ttl=30.0)
+    server, thread = hub.serve(port=port)
+    try:
+        w = WorkerInfo("engine-c0-w0", "engine", "engine-c0", 0, 0, "127.0.0.1", (("port", 30000),))
+        snap = {"reporter_id": "node-a", "seq": 1, "cells": [cell_to_json(CellInfo("engine-c0", "engine", 0, True, (w,)))]}
+        out = asyncio.run(http_poster(f"http://127.0.0.1:{port}")(snap))
+        assert out == {"accepted": True, "reporters": 1}
+        cells = requests.get(f"http://127.0.0.1:{port}/cells").json()["cells"]
+        assert cells[0]["workers"][0]["name"] == "engine-c0-w0"
+        bad = {"reporter_id": "node-b", "seq": 1, "cells": [dict(snap["cells"][0])]}
+        assert requests.post(f"http://127.0.0.1:{port}/register", json=bad).status_code == 422     # the cell has a reporter already
+    finally:
+        server.should_exit = True
+        thread.join(5)

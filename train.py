@@ -35,6 +35,10 @@ def train(args):
         assert args.num_epoch and len(rollout.data_source), "--num-rollout or --num-epoch (with --prompt-data) required"
         args.num_rollout = args.num_epoch * len(rollout.data_source) // args.rollout_batch_size
 
+    from miles_b200.ft.api_server import maybe_start_mini_ft_controller, start_api_server
+
+    api = start_api_server(args, trainer, rollout) if ps.rank == 0 else None     # --api-server-port: cells over REST
+    maybe_start_mini_ft_controller(args) if api else None
     if not args.debug_train_only and not args.debug_skip_weight_update:
         update_weights(args, actor, rollout)           # initial push (and consistency check)
     if args.offload_train and not args.debug_rollout_only:
