@@ -491,6 +491,25 @@ class Engine:
         if fab is not None:
             fab.check()
 
+    dumper = None               # utils.dumper.DumperSwitch with the "inference" phase on (`attach_dumper`)
+
+    def attach_dumper(self, switch):
+        """Dump this engine's forwards under the inference phase; graphs cannot run Python hooks, so decode goes eager."""
+        if switch is None or not switch.enabled("inference"):
+            return
+        self.dumper = switch
+        switch.register(self.model)
+        self.runner = None
+        self.use_cuda_graph = False
+
+    def _dumped_forward(self, toks, meta):
+        if self.dumper is None:
+            return self.model(toks, meta)
+        with self.dumper.phase("inference"):
+            hidden = self.model(toks, meta)
+            self.dumper.step()
+        return hidden
+
     def begin_rollout(self):
         import gc
 
@@ -646,7 +665,7 @@ class Engine:
             slot_mapping=None if self.stateless else torch.tensor(slots, dtype=torch.int64, device=dev),
             record_topk=record, lora_slots=self._lora_slots(len(toks)))
         self.stats["h2d_bytes"] = self.stats.get("h2d_bytes", 0) + 4 * len(toks) * 2 + 4 * len(cu) + 8 * len(slots)
-        hidden = self.model(torch.tensor(toks, dtype=torch.int32, device=dev), meta)
+        hidden = self._dumped_forward(torch.tensor(toks, dtype=torch.int32, device=dev), meta)
         if not batch:
             return
         hidden = self.ps.sp_gather(hidden)
@@ -731,7 +750,7 @@ class Engine:
             seq_lens=torch.tensor([p + 1 for p in pos], dtype=torch.int32, device=dev),
             slot_mapping=torch.tensor(slots, dtype=torch.int64, device=dev), record_topk=record,
             lora_slots=self._lora_slots(len(toks)))
-        hidden = self.model(torch.tensor(toks, dtype=torch.int32, device=dev), meta)
+        hidden = self._dumped_forward(torch.tensor(toks, dtype=torch.int32, device=dev), meta)
         if not reqs:
             return
         hidden = self.ps.sp_gather(hidden)

@@ -198,6 +198,7 @@ def create_rollout_components(args, ps: ParallelState, actor=None, tracker=None)
                         max_prefill_tokens=ek.get("max_prefill_tokens", 16384),
                         max_context_len=getattr(args, "rollout_max_context_len", None), eos_token_ids=eos, tokenizer=tok,
                         seed=args.rollout_seed, use_cuda_graph=not ek.get("disable_cuda_graph", False))
+        engine.attach_dumper(getattr(actor, "dumper", None))
         engines = [engine]
         client = InProcEngineClient(engines, tokenizer=tok, policy=getattr(args, "router_policy", "least_active"))
     # rollout data parallelism: one engine group per (tp × ep-within-dp) block; groups take disjoint prompts

@@ -151,6 +151,11 @@ class TrainActor:
         self.profiler = TrainProfiler(args)
         self.profiler.on_init_end()
         self.backuper = TensorBackuper(self.model)
+        from ..utils.dumper import DumperSwitch
+
+        self.dumper = DumperSwitch.from_args(args, self.ps.rank)       # --dumper-enable + per-phase lists; None when off
+        if self.dumper is not None:
+            self.dumper.register(self.model)
         self.indep_dp = self._make_indep_dp()
         # checkpoints
         from ..checkpoint import manager as ckpt
@@ -332,6 +337,11 @@ class TrainActor:
                 if lp is None:
                     lp = torch.zeros(pb.gather_index.numel(), device=self.device)
                 lp = broadcast_from_last_stage(lp.float().contiguous(), self.ps)     # every stage keeps the same record
+            elif self.dumper is not None:
+                with self.dumper.phase("fwd_only"):
+                    lp, _ = self._forward_logprobs(pb, False, replay)
+                    self.dumper.dump("log_probs", lp)
+                    self.dumper.step()
             else:
                 lp, _ = self._forward_logprobs(pb, False, replay)
             for i, piece in zip(idx, lp.float().split(pb.response_lengths)):
@@ -515,9 +525,20 @@ class TrainActor:
         else:
             for idx in mbs:
                 pb = pack(idx)
+                if self.dumper is not None:
+                    with self.dumper.phase("fwd_bwd"):
+                        out, ent = self._forward_logprobs(pb, want_ent, replay)
+                        self.dumper.dump("log_probs", out)
+                    score(pb, idx, out, ent).backward()
+                    continue
                 out, ent = self._forward_logprobs(pb, want_ent, replay)
                 score(pb, idx, out, ent).backward()
         self._finalize_grads()
+        if self.dumper is not None:
+            with self.dumper.phase("fwd_bwd") as d:
+                if d is not None:
+                    d.dump_model(self.model)                 # parameters and the reduced gradients of this optimizer step
+                    d.step()
         lr = self.scheduler.get()
         if getattr(args, "debug_disable_optimizer", False):
             self.optimizer.zero_grad()

@@ -183,3 +183,40 @@ def test_reference_flag_surface_parses_and_wired_flags_act(tmp_path):
     args = parse_args((BASE + f" --num-rollout 4 --load {tmp_path / 'ck'} --start-rollout-id 3 --reset-optimizer-states").split())
     tr = train_entry.train(args)
     assert [r["rollout/step"] for r in tr.history.rows] == [3]
+
+
+def test_dumper_phases_and_compare(tmp_path):
+    """--dumper-enable with the three phase lists: trainer log-prob passes, train passes (with parameters and gradients)
+    and the engine's forwards land in their own trees; the compare tool matches a tree with itself and flags a change."""
+    import torch
+
+    from test_e2e import BASE, _run
+    from miles_b200.utils import dumper as D
+
+    d = str(tmp_path / "dump")
+    _run(f"--num-rollout 1 --dumper-enable --dumper-dir {d} --dumper-inference steps=2 --dumper-fwd-only filter=layers.0.|log_probs "
+         f"--dumper-fwd-bwd max_numel=64")
+    assert sorted(os.listdir(d)) == ["fwd_bwd", "fwd_only", "inference"]
+    inf = os.path.join(d, "inference")
+    assert sorted(os.listdir(inf)) == ["step00000", "step00001"]                       # steps=2
+    names = {f.split("___", 1)[1] for f in os.listdir(os.path.join(d, "fwd_only", "step00000", "rank000"))}
+    assert names == {"layers.0.out.pt", "layers.0.attn.out.pt", "layers.0.mlp.out.pt", "log_probs.pt"}
+    fb = os.path.join(d, "fwd_bwd", "step00000", "rank000")
+    files = os.listdir(fb)
+    assert any("___grad.layers.0.attn.wqkv" in f for f in files) and any("___param.embed" in f for f in files)
+    big = torch.load(os.path.join(fb, next(f for f in files if "___param.embed" in f)), weights_only=False)
+    assert big["meta"]["sampled"] and big["value"].numel() <= 64 and big["meta"]["norm"] > 0
+    assert all(r["status"] == "ok" for r in D.compare(inf, inf))
+    # perturb one tensor of a copy
+    import shutil
+
+    other = str(tmp_path / "other")
+    shutil.copytree(inf, other)
+    victim = os.path.join(other, "step00001", "rank000", sorted(os.listdir(os.path.join(other, "step00001", "rank000")))[0])
+    blob = torch.load(victim, weights_only=False)
+    blob["value"] = blob["value"] * 1.5
+    torch.save(blob, victim)
+    rows = D.compare(inf, other)
+    assert [r["status"] for r in rows].count("diff") == 1
+    assert D.main(["compare", inf, other]) == 1 and D.main(["compare", inf, inf]) == 0
+    assert D.DumperConfig.kv_to_dict(["max-numel=8", "enable=false"]) == {"max_numel": 8, "enable": False}
