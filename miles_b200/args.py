@@ -68,6 +68,15 @@ def build_parser() -> argparse.ArgumentParser:
                    help="with --offload-train: also destroy the trainer's communicators while it sleeps (their device buffers "
                         "are freed) and re-create them on wake-up; only when the rollout engines do not share them "
                         "(--rollout-engine http, or in-process engines with tp = ep = 1)")
+    g.add_argument("--export-quant", choices=["none", "fp8", "mxfp8", "nvfp4", "int4"], default="none",
+                   help="quantise HF-named tensors on export: --save-hf snapshots and the tensor / broadcast / disk weight sync")
+    g.add_argument("--export-quant-ignore", nargs="*", default=None, help="module names (or re:<regex>) kept in high precision")
+    g.add_argument("--export-quant-all-linears", action="store_true", help="nvfp4: also the attention and dense-MLP projections (default: routed experts only)")
+    g.add_argument("--nvfp4-four-over-six", action="store_true", help="per block, map the maximum to 4 or to 6, whichever quantises with less error")
+    g.add_argument("--num-layers-at-start-in-bf16", type=int, default=0)
+    g.add_argument("--num-layers-at-end-in-bf16", type=int, default=0)
+    g.add_argument("--int4-group-size", type=int, default=32)
+    g.add_argument("--int4-asymmetric", action="store_true")
     g.add_argument("--ckpt-format", choices=["torch_dist", "native"], default="torch_dist",
                    help="torch_dist: one DCP store per iteration with Megatron-named entries and the optimizer state in "
                         "model space, reloadable under any parallel layout; native: one file per rank with that rank's shards")

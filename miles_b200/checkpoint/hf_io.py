@@ -49,7 +49,7 @@ def save_safetensors(path: str, tensors: dict[str, torch.Tensor], metadata: dict
         f.write(hjson)
         for n in order:
             t = tensors[n].detach().contiguous().cpu()
-            f.write(t.view(torch.uint8).reshape(-1).numpy().tobytes() if t.numel() else b"")
+            f.write(t.reshape(-1).view(torch.uint8).numpy().tobytes() if t.numel() else b"")   # reshape first: a scalar has no last dim to reinterpret
     os.replace(tmp, path)
 
 

@@ -29,6 +29,7 @@ import torch.distributed as dist
 
 from ..models.convert import hf_state_to_ours, load_named_into_model
 from . import hf_io
+from ..weight_update.quantize import hf_quant_config
 
 TRACKER = "latest_checkpointed_iteration.txt"
 
@@ -129,6 +130,11 @@ def finalize_async_save():
     _ASYNC.wait()
 
 
+def _export_quant(args):
+    q = getattr(args, "export_quant", None)
+    return None if q in (None, "none") else q
+
+
 def save_from_actor(actor, args, iteration: int, with_optimizer: bool = True):
     root = args.save
     assert root, "--save is required to save checkpoints"
@@ -155,8 +161,9 @@ def save_from_actor(actor, args, iteration: int, with_optimizer: bool = True):
         if getattr(args, "save_hf", False):
             from ..weight_update.hf_iterator import iter_hf_weights
 
-            hf_io.save_hf_sharded(os.path.join(directory, "hf"), iter_hf_weights(actor, bucket_bytes=None), actor.cfg,
-                                  write=(rank == 0), src_dir=getattr(args, "hf_checkpoint", None))
+            hf_io.save_hf_sharded(os.path.join(directory, "hf"), iter_hf_weights(actor, bucket_bytes=None, quant=_export_quant(args)), actor.cfg,
+                                  write=(rank == 0), src_dir=getattr(args, "hf_checkpoint", None),
+                                  extra_config=hf_quant_config(_export_quant(args)) if _export_quant(args) else None)
 
     def write(directory):
         state = {n: t.detach().cpu() for n, t in actor.named_weights()}       # model-wide names (pipeline stages too)

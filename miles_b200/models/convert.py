@@ -165,6 +165,10 @@ def load_named_into_model(model, named_tensors: Iterable[tuple[str, torch.Tensor
     named = list(named_tensors)
     params = dict(model.named_parameters_global() if hasattr(model, "named_parameters_global") else model.named_parameters())
     if named and (named[0][0].startswith("model.") or named[0][0].startswith("lm_head")):
+        from ..weight_update.quant_export import dequantize_named, is_quantized_stream
+
+        if is_quantized_stream(named):              # fp8 / mxfp8 / nvfp4 / int4 export formats decode on arrival
+            named = dequantize_named(named, next(iter(params.values())).dtype)
         named = list(hf_state_to_ours(dict(named), cfg).items())
     for n, t in named:
         if n not in params:

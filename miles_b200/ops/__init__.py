@@ -213,5 +213,5 @@ def int4_fake_quant(x, block_m=1, block_n=32, symmetric=True):
     return ref.int4_fake_quant(x, block_m, block_n, symmetric)
 
 
-def nvfp4_qdq(x, global_amax=None):
-    return _k().nvfp4_qdq(x, global_amax) if x.is_cuda else ref.nvfp4_qdq(x, global_amax)
+def nvfp4_qdq(x, global_amax=None, four_over_six=False):
+    return _k().nvfp4_qdq(x, global_amax, four_over_six) if x.is_cuda else ref.nvfp4_qdq(x, global_amax, four_over_six=four_over_six)

@@ -126,10 +126,10 @@ at::Tensor absmax(const at::Tensor& x) {
   return out;
 }
 
-at::Tensor nvfp4_qdq(const at::Tensor& x, const at::Tensor& global_amax) {
+at::Tensor nvfp4_qdq(const at::Tensor& x, const at::Tensor& global_amax, bool four_over_six) {
   c10::cuda::CUDAGuard g(x.device());
   auto y = at::empty_like(x);
-  check(mb_nvfp4_qdq(x.data_ptr(), y.data_ptr(), global_amax.data_ptr<float>(), x.numel(), cur_stream()), "mb_nvfp4_qdq");
+  check(mb_nvfp4_qdq(x.data_ptr(), y.data_ptr(), global_amax.data_ptr<float>(), x.numel(), four_over_six ? 1 : 0, cur_stream()), "mb_nvfp4_qdq");
   return y;
 }
 

@@ -153,12 +153,11 @@ __global__ void __launch_bounds__(256) int4_fake_quant_kernel(const bf16* __rest
   }
 }
 
-// ---- NVFP4 quantise→dequantise: one thread per 16-element block -----------------------------------------
-__device__ __forceinline__ float e2m1_value(uint32_t code) {   // 4-bit sign|exp(2)|mant(1)
-  const float mag[8] = {0.f, 0.5f, 1.f, 1.5f, 2.f, 3.f, 4.f, 6.f};
-  const float v = mag[code & 7];
-  return (code & 8) ? -v : v;
-}
+// ---- NVFP4 quantise→dequantise ---------------------------------------------------------------------------
+// Two adjacent lanes share one 1×16 block: each loads and stores 16 bytes (every warp access is one contiguous 512-byte
+// run), the block maximum and the candidates' errors meet through one shuffle.  FOS ("four over six"): the block is
+// quantised twice, with its maximum mapped to 6 and to 4 (finer steps when the values crowd the upper half of the e2m1
+// grid), and the candidate with the smaller squared error is kept.
 __device__ __forceinline__ uint32_t cvt_e2m1x2(float lo, float hi) {
   uint32_t r;
   asm volatile(
@@ -169,40 +168,69 @@ __device__ __forceinline__ uint32_t cvt_e2m1x2(float lo, float hi) {
       : "f"(lo), "f"(hi));
   return r;  // low nibble = lo, high nibble = hi
 }
+__device__ __forceinline__ float2 e2m1x2_to_float2(uint32_t code) {
+  uint32_t h2;
+  asm volatile(
+      "{\n\t.reg .b8 t;\n\t"
+      "cvt.u8.u32 t, %1;\n\t"
+      "cvt.rn.f16x2.e2m1x2 %0, t;\n\t}\n"
+      : "=r"(h2)
+      : "r"(code));
+  return __half22float2(*reinterpret_cast<__half2*>(&h2));
+}
 
-__global__ void __launch_bounds__(256) nvfp4_qdq_kernel(const bf16* __restrict__ x, bf16* __restrict__ y, const float* __restrict__ global_amax,
-                                                        long long nblocks) {
-  const long long b = blockIdx.x * 256ll + threadIdx.x;
-  if (b >= nblocks) return;
-  float v[16];
-  ld8(x + b * 16, *reinterpret_cast<float(*)[8]>(&v[0]));
-  ld8(x + b * 16 + 8, *reinterpret_cast<float(*)[8]>(&v[8]));
-  float amax = 0.f;
-#pragma unroll
-  for (int i = 0; i < 16; ++i) amax = fmaxf(amax, fabsf(v[i]));
-  const float gscale = (448.f * 6.f) / fmaxf(*global_amax, 1e-12f);
-  const float sb_f = fminf(amax / 6.f * gscale, 448.f);
+__device__ __forceinline__ float nvfp4_candidate(const float (&v)[8], float amax, float gscale, float target, float (&o)[8]) {
+  const float sb_f = fminf(amax / target * gscale, 448.f);
   const __nv_fp8_storage_t sb8 = __nv_cvt_float_to_fp8(sb_f, __NV_SATFINITE, __NV_E4M3);
   const float sb = __half2float(__half(__nv_cvt_fp8_to_halfraw(sb8, __NV_E4M3)));
   const float dec = sb / gscale;
   const float enc = dec > 0.f ? 1.f / dec : 0.f;
-  float o[16];
+  float err = 0.f;
 #pragma unroll
-  for (int i = 0; i < 16; i += 2) {
-    const uint32_t code = cvt_e2m1x2(v[i] * enc, v[i + 1] * enc);
-    o[i] = e2m1_value(code & 0xf) * dec;
-    o[i + 1] = e2m1_value((code >> 4) & 0xf) * dec;
+  for (int i = 0; i < 8; i += 2) {
+    const float2 q = e2m1x2_to_float2(cvt_e2m1x2(v[i] * enc, v[i + 1] * enc));
+    o[i] = q.x * dec;
+    o[i + 1] = q.y * dec;
+    err += (o[i] - v[i]) * (o[i] - v[i]) + (o[i + 1] - v[i + 1]) * (o[i + 1] - v[i + 1]);
   }
-  uint4 w0, w1;
-  __nv_bfloat162* p0 = reinterpret_cast<__nv_bfloat162*>(&w0);
-  __nv_bfloat162* p1 = reinterpret_cast<__nv_bfloat162*>(&w1);
+  return err;
+}
+
+template <bool FOS>
+__global__ void __launch_bounds__(256) nvfp4_qdq_kernel(const bf16* __restrict__ x, bf16* __restrict__ y, const float* __restrict__ global_amax,
+                                                        long long npieces) {   // pieces of 8 elements; even, so partner lanes live or die together
+  const long long i = blockIdx.x * 256ll + threadIdx.x;
+  const bool live = i < npieces;
+  float v[8];
+  if (live) {
+    ld8(x + i * 8, v);
+  } else {
 #pragma unroll
-  for (int i = 0; i < 4; ++i) {
-    p0[i] = __floats2bfloat162_rn(o[2 * i], o[2 * i + 1]);
-    p1[i] = __floats2bfloat162_rn(o[8 + 2 * i], o[8 + 2 * i + 1]);
+    for (int k = 0; k < 8; ++k) v[k] = 0.f;
   }
-  *reinterpret_cast<uint4*>(y + b * 16) = w0;
-  *reinterpret_cast<uint4*>(y + b * 16 + 8) = w1;
+  float amax = 0.f;
+#pragma unroll
+  for (int k = 0; k < 8; ++k) amax = fmaxf(amax, fabsf(v[k]));
+  amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 1));
+  const float gscale = (448.f * 6.f) / fmaxf(__ldg(global_amax), 1e-12f);
+  float o[8];
+  float e6 = nvfp4_candidate(v, amax, gscale, 6.f, o);
+  if (FOS) {
+    float o4[8];
+    float e4 = nvfp4_candidate(v, amax, gscale, 4.f, o4);
+    e6 += __shfl_xor_sync(0xffffffffu, e6, 1);
+    e4 += __shfl_xor_sync(0xffffffffu, e4, 1);
+    if (e4 < e6) {
+#pragma unroll
+      for (int k = 0; k < 8; ++k) o[k] = o4[k];
+    }
+  }
+  if (!live) return;
+  uint4 w;
+  __nv_bfloat162* p = reinterpret_cast<__nv_bfloat162*>(&w);
+#pragma unroll
+  for (int k = 0; k < 4; ++k) p[k] = __floats2bfloat162_rn(o[2 * k], o[2 * k + 1]);
+  *reinterpret_cast<uint4*>(y + i * 8) = w;
 }
 
 __global__ void __launch_bounds__(256) absmax_kernel(const bf16* __restrict__ x, float* __restrict__ out, long long n) {
@@ -249,12 +277,15 @@ extern "C" int mb_int4_fake_quant(const void* x, void* y, float* scales, int M, 
   return static_cast<int>(cudaGetLastError());
 }
 
-extern "C" int mb_nvfp4_qdq(const void* x, void* y, const float* global_amax, long long numel, cudaStream_t s) {
+extern "C" int mb_nvfp4_qdq(const void* x, void* y, const float* global_amax, long long numel, int four_over_six, cudaStream_t s) {
   if (numel == 0) return 0;
   if (numel % 16) return -1;
-  const long long nb = numel / 16;
-  nvfp4_qdq_kernel<<<static_cast<unsigned>((nb + 255) / 256), 256, 0, s>>>(reinterpret_cast<const bf16*>(x), reinterpret_cast<bf16*>(y),
-                                                                          global_amax, nb);
+  const long long np = numel / 8;
+  const unsigned grid = static_cast<unsigned>((np + 255) / 256);
+  if (four_over_six)
+    nvfp4_qdq_kernel<true><<<grid, 256, 0, s>>>(reinterpret_cast<const bf16*>(x), reinterpret_cast<bf16*>(y), global_amax, np);
+  else
+    nvfp4_qdq_kernel<false><<<grid, 256, 0, s>>>(reinterpret_cast<const bf16*>(x), reinterpret_cast<bf16*>(y), global_amax, np);
   return static_cast<int>(cudaGetLastError());
 }
 

@@ -393,9 +393,9 @@ def absmax(x):
     return C.absmax(_c(x))
 
 
-def nvfp4_qdq(x, global_amax=None):
+def nvfp4_qdq(x, global_amax=None, four_over_six=False):
     assert x.dtype == BF16 and x.numel() % 16 == 0
     x = _c(x)
     if global_amax is None:
         global_amax = C.absmax(x)
-    return C.nvfp4_qdq(x, global_amax.reshape(1).float())
+    return C.nvfp4_qdq(x, global_amax.reshape(1).float(), bool(four_over_six))

@@ -300,17 +300,27 @@ def _round_e2m1(v: torch.Tensor) -> torch.Tensor:
     return r * v.sign()
 
 
-def nvfp4_qdq(x: torch.Tensor, global_amax: torch.Tensor | None = None, block: int = 16):
-    """NVFP4 quantise→dequantise: 1×16 blocks, e4m3 block scale, fp32 per-tensor scale."""
+def nvfp4_qdq(x: torch.Tensor, global_amax: torch.Tensor | None = None, block: int = 16, four_over_six: bool = False):
+    """NVFP4 quantise→dequantise: 1×16 blocks, e4m3 block scale, fp32 per-tensor scale.  `four_over_six`: per block the
+    maximum is mapped to 6 or to 4, whichever gives the smaller squared error."""
     shp = x.shape
     xf = x.float().reshape(-1, block)
     gamax = x.float().abs().max() if global_amax is None else global_amax.float()
     gscale = (FP8_E4M3_MAX * FP4_E2M1_MAX) / gamax.clamp_min(1e-12)  # encode scale
     amax = xf.abs().amax(-1, keepdim=True)
-    sb = (amax / FP4_E2M1_MAX * gscale).clamp(max=FP8_E4M3_MAX).to(torch.float8_e4m3fn).float()
-    dec = sb / gscale  # decode multiplier per block
-    q = _round_e2m1(torch.where(dec > 0, xf / dec, torch.zeros_like(xf)))
-    return (q * dec).reshape(shp).to(x.dtype)
+
+    def candidate(target):
+        sb = (amax / target * gscale).clamp(max=FP8_E4M3_MAX).to(torch.float8_e4m3fn).float()
+        dec = sb / gscale  # decode multiplier per block
+        enc = torch.where(dec > 0, 1.0 / dec, torch.zeros_like(dec))
+        return _round_e2m1(xf * enc) * dec
+
+    y = candidate(FP4_E2M1_MAX)
+    if four_over_six:
+        y4 = candidate(4.0)
+        better = ((y4 - xf) ** 2).sum(-1, keepdim=True) < ((y - xf) ** 2).sum(-1, keepdim=True)
+        y = torch.where(better, y4, y)
+    return y.reshape(shp).to(x.dtype)
 
 
 # --------------------------------------------------------------------------------------------

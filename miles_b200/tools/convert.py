@@ -4,6 +4,8 @@
     python -m miles_b200.tools.convert torch-dist-to-hf  --load DIR --out DIR --hf-config DIR|--model-name NAME
     python -m miles_b200.tools.convert hf-to-fp8         --hf DIR --out DIR        (128×128 block e4m3 + weight_scale_inv)
     python -m miles_b200.tools.convert hf-to-mxfp8       --hf DIR --out DIR        (1×32 block e4m3 + ue8m0 scales)
+    python -m miles_b200.tools.convert hf-to-nvfp4       --hf DIR --out DIR [--four-over-six] [--all-linears] [--ignore …]   (packed e2m1 + scales)
+    python -m miles_b200.tools.convert hf-to-int4        --hf DIR --out DIR [--group-size 32] [--asymmetric]                 (compressed-tensors)
     python -m miles_b200.tools.convert hf-to-nvfp4-qdq   --hf DIR --out DIR        (bf16 values that went through NVFP4)
     python -m miles_b200.tools.convert hf-to-int4-qdq    --hf DIR --out DIR [--block 1 32] [--asymmetric]
     python -m miles_b200.tools.convert fp8-to-bf16       --hf DIR --out DIR        (dequantise block-scaled FP8 weights)
@@ -118,6 +120,25 @@ def hf_to_quant(args, mode: str):
     return _map_shards(args, fn, hf_quant_config(mode))
 
 
+def hf_to_packed(args, mode: str):
+    """Packed NVFP4 (ModelOpt layout) / compressed-tensors int4 export of an HF directory."""
+    from ..weight_update import quant_export as qe
+
+    dev = _dev()
+    if mode == "nvfp4":
+        opts = dict(ignore=args.ignore, four_over_six=args.four_over_six, all_linears=args.all_linears, pair_strict=False)
+        cfg = qe.quant_config("nvfp4", ignore=args.ignore, four_over_six=args.four_over_six)
+    else:
+        opts = dict(ignore=args.ignore, group_size=args.group_size, symmetric=not args.asymmetric)
+        cfg = qe.quant_config("int4", group_size=args.group_size, symmetric=not args.asymmetric, ignore=args.ignore)
+
+    def fn(named):
+        named = [(n, t.to(dev) if t.dim() == 2 else t) for n, t in named]
+        return [(n, t.cpu()) for n, t in quantize_hf_tensors(named, mode, **opts)]
+
+    return _map_shards(args, fn, cfg)
+
+
 def hf_to_nvfp4_qdq(args):
     dev = _dev()
 
@@ -188,6 +209,18 @@ def main(argv=None):
         if name == "hf-to-int4-qdq":
             s.add_argument("--block", type=int, nargs=2, default=[1, 32])
             s.add_argument("--asymmetric", action="store_true")
+    for name in ("hf-to-nvfp4", "hf-to-int4"):
+        s = sub.add_parser(name)
+        s.add_argument("--hf", required=True)
+        s.add_argument("--out", required=True)
+        s.add_argument("--model-name", default=None)
+        s.add_argument("--ignore", nargs="*", default=[])
+        if name == "hf-to-nvfp4":
+            s.add_argument("--four-over-six", action="store_true")
+            s.add_argument("--all-linears", action="store_true")
+        else:
+            s.add_argument("--group-size", type=int, default=32)
+            s.add_argument("--asymmetric", action="store_true")
     s = sub.add_parser("torch-dist-to-hf")
     s.add_argument("--load", required=True)
     s.add_argument("--out", required=True)
@@ -196,6 +229,7 @@ def main(argv=None):
     a = p.parse_args(argv)
     return {"hf-to-torch-dist": hf_to_torch_dist, "torch-dist-to-hf": torch_dist_to_hf,
             "hf-to-fp8": lambda x: hf_to_quant(x, "fp8"), "hf-to-mxfp8": lambda x: hf_to_quant(x, "mxfp8"),
+            "hf-to-nvfp4": lambda x: hf_to_packed(x, "nvfp4"), "hf-to-int4": lambda x: hf_to_packed(x, "int4"),
             "hf-to-nvfp4-qdq": hf_to_nvfp4_qdq, "hf-to-int4-qdq": hf_to_int4_qdq, "fp8-to-bf16": fp8_to_bf16}[a.cmd](a)
 
 

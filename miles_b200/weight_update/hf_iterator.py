@@ -71,16 +71,31 @@ def iter_full_tensors(actor) -> Iterator[tuple[str, torch.Tensor]]:
             yield name, unshard_tp(name, _all_gather_tp(t, ps), cfg)
 
 
+def quant_options_from_args(args, quant: str | None, cfg) -> dict:
+    """Options of the packed export formats taken from the command line."""
+    if quant == "nvfp4":
+        return {"ignore": list(getattr(args, "export_quant_ignore", None) or []) + list(getattr(args, "extra_high_precision_layers_hf", None) or []),
+                "four_over_six": bool(getattr(args, "nvfp4_four_over_six", False)), "num_layers": cfg.num_layers,
+                "bf16_head": int(getattr(args, "num_layers_at_start_in_bf16", 0) or 0),
+                "bf16_tail": int(getattr(args, "num_layers_at_end_in_bf16", 0) or 0),
+                "all_linears": bool(getattr(args, "export_quant_all_linears", False))}
+    if quant == "int4":
+        return {"ignore": list(getattr(args, "export_quant_ignore", None) or []), "group_size": int(getattr(args, "int4_group_size", 32) or 32),
+                "symmetric": not getattr(args, "int4_asymmetric", False)}
+    return {}
+
+
 def iter_hf_weights(actor, bucket_bytes: int | None = 512 << 20, quant: str | None = None
                     ) -> Iterator[list[tuple[str, torch.Tensor]]]:
-    """Buckets of (hf_name, tensor). `quant` ∈ {None, 'fp8', 'mxfp8'}."""
+    """Buckets of (hf_name, tensor). `quant` ∈ {None, 'fp8', 'mxfp8', 'nvfp4', 'int4'}."""
+    qopts = quant_options_from_args(getattr(actor, "args", None), quant, actor.cfg)
     cfg = actor.cfg
     bucket: list[tuple[str, torch.Tensor]] = []
     size = 0
     for name, full in iter_full_tensors(actor):
         group = to_hf(name, full, cfg)
         if quant:
-            group = quantize_hf_tensors(group, quant)
+            group = quantize_hf_tensors(group, quant, **qopts)
         nb = sum(t.numel() * t.element_size() for _, t in group)
         if bucket_bytes is not None and bucket and size + nb > bucket_bytes:
             yield bucket

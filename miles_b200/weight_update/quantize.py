@@ -4,6 +4,7 @@
   kernel miles/kernels/quant/fp8_blockwise.py:24-79).
 * `mxfp8`: 1×32-block e4m3 with uint8 e8m0 `weight_scale_inv`
   (reference: processors/quantizer_mxfp8.py:6-114, miles/utils/mxfp8.py:48-78).
+* `nvfp4`, `int4`: packed export formats, see `quant_export.py`.
 Only 2-D projection weights are quantised; embeddings, norms, the router gate and the LM head stay in
 bf16 (the reference's skip list, miles/utils/mxfp8.py:7-20).
 """
@@ -22,7 +23,11 @@ def should_quantize(name: str, t: torch.Tensor) -> bool:
     return not any(s in name for s in SKIP_SUBSTRINGS)
 
 
-def quantize_hf_tensors(named: list[tuple[str, torch.Tensor]], mode: str) -> list[tuple[str, torch.Tensor]]:
+def quantize_hf_tensors(named: list[tuple[str, torch.Tensor]], mode: str, **options) -> list[tuple[str, torch.Tensor]]:
+    if mode in ("nvfp4", "int4"):                    # packed export formats with their own eligibility rules
+        from . import quant_export
+
+        return (quant_export.export_nvfp4 if mode == "nvfp4" else quant_export.export_int4)(list(named), **options)
     out: list[tuple[str, torch.Tensor]] = []
     for n, t in named:
         if not should_quantize(n, t):
@@ -49,4 +54,8 @@ def hf_quant_config(mode: str) -> dict:
     if mode == "mxfp8":
         return {"quantization_config": {"quant_method": "mxfp8", "fmt": "e4m3", "weight_block_size": [1, 32],
                                         "scale_fmt": "ue8m0"}}
+    if mode in ("nvfp4", "int4"):
+        from . import quant_export
+
+        return quant_export.quant_config(mode)
     return {}

@@ -61,7 +61,9 @@ class WeightUpdater:
         assert hasattr(self, f"_send_{impl}"), impl
         self.cli_mode = mode
         self.mode = impl
-        self.quant = quant
+        self.quant = quant or (getattr(args, "export_quant", None) if impl in ("disk", "delta", "broadcast", "tensor") else None)
+        if self.quant == "none":
+            self.quant = None
         self.framed = False          # True while a controller frames the transfer (it pauses, flushes and resumes the engines)
         self._reshard_plans: dict[int, Any] = {}
         self._delta_writer = None
@@ -166,8 +168,10 @@ class WeightUpdater:
 
         d = getattr(self.args, "update_weight_disk_dir", None) or tempfile.mkdtemp(prefix="miles_sync_")
         d = os.path.join(d, f"v{self.actor.weight_version}")
+        from .quantize import hf_quant_config
+
         hf_io.save_hf_sharded(d, iter_hf_weights(self.actor, bucket_bytes=None, quant=self.quant), self.actor.cfg,
-                              write=self._is_leader())
+                              write=self._is_leader(), extra_config=hf_quant_config(self.quant) if self.quant else None)
         self._barrier()
         for e in self.engines:
             e.update_weights_from_disk(d)

@@ -208,6 +208,18 @@ def test_quant_kernels_match_reference():
     y = _k().nvfp4_qdq(x)
     yr = ref.nvfp4_qdq(x)
     assert _rel(y, yr) < 2e-2, _rel(y, yr)
+    assert (y != yr).float().mean() < 1e-3                       # same grid points except rare ties of the reciprocal
+    # four-over-six: per block the better of "max → 6" and "max → 4"; never worse than the plain rule
+    y46 = _k().nvfp4_qdq(x, None, True)
+    yr46 = ref.nvfp4_qdq(x, four_over_six=True)
+    assert (y46 != yr46).float().mean() < 1e-3
+    e, e46 = (y.float() - x.float()).pow(2).sum(), (y46.float() - x.float()).pow(2).sum()
+    assert e46 < e
+    # the packed export decodes to the same values
+    from miles_b200.weight_update import quant_export as qe
+
+    x2 = x.reshape(-1, 64)
+    assert (qe.nvfp4_dequantize(*qe.nvfp4_quantize(x2, four_over_six=True)) != y46.reshape(-1, 64)).float().mean() < 1e-3
 
 
 def test_fused_weight_sync_kernels():

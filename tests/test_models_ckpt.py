@@ -221,3 +221,90 @@ def test_nvme_stream_adam_matches_adamw_and_resumes(tmp_path):
         ref_opt.step()
     torch.testing.assert_close(flat, ref_p.detach(), atol=1e-6, rtol=1e-5)
     opt2.close()
+
+
+def test_packed_nvfp4_and_int4_export_decode_to_the_fake_quant_values(tmp_path):
+    """What the exporters pack must decode to exactly what fake-quantised training computes."""
+    from miles_b200 import ops
+    from miles_b200.ops import reference as R
+    from miles_b200.weight_update import quant_export as qe
+
+    g = torch.Generator().manual_seed(0)
+    w = (torch.randn(48, 64, generator=g) * torch.rand(48, 1, generator=g) * 3).bfloat16()
+    q, sb, s2 = qe.nvfp4_quantize(w)
+    assert q.dtype == torch.uint8 and q.shape == (48, 32) and sb.dtype == torch.float8_e4m3fn and sb.shape == (48, 4)
+    assert torch.equal(qe.nvfp4_dequantize(q, sb, s2), R.nvfp4_qdq(w))
+    # ties and saturation of the e2m1 rounding
+    probe = torch.tensor([0.25, 0.75, 1.25, 1.75, 2.5, 3.5, 5.0, 7.0, 0.0, 0.26])
+    assert qe.e2m1_codes(probe).tolist() == [0, 2, 2, 4, 4, 6, 6, 7, 0, 1]
+    # four-over-six never loses to the plain rule, and wins on blocks whose values sit between the coarse upper steps
+    x = torch.full((1, 16), 4.2)
+    x[0, 0] = 5.0
+    big = torch.cat([x, torch.full((1, 16), 448.0 * 6)], 0).float()           # second row pins the tensor scale to 1
+    plain = qe.nvfp4_dequantize(*qe.nvfp4_quantize(big), dtype=torch.float32)
+    fos = qe.nvfp4_dequantize(*qe.nvfp4_quantize(big, four_over_six=True), dtype=torch.float32)
+    assert ((fos - big) ** 2).sum() < ((plain - big) ** 2).sum()
+    e_plain = ((qe.nvfp4_dequantize(q, sb, s2).float() - w.float()) ** 2).sum()
+    e_fos = ((qe.nvfp4_dequantize(*qe.nvfp4_quantize(w, four_over_six=True)).float() - w.float()) ** 2).sum()
+    assert e_fos <= e_plain
+    # naming, pairing and eligibility
+    named = [("model.layers.0.mlp.experts.3.gate_proj.weight", w), ("model.layers.0.mlp.experts.3.up_proj.weight", w * 2),
+             ("model.layers.0.mlp.experts.3.down_proj.weight", w), ("model.layers.0.self_attn.q_proj.weight", w),
+             ("model.layers.1.mlp.experts.0.down_proj.weight", w), ("model.norm.weight", torch.ones(64))]
+    out = dict(qe.export_nvfp4(named, ignore=["model.layers.1.mlp.experts"], num_layers=2))
+    gate, up = "model.layers.0.mlp.experts.3.gate_proj", "model.layers.0.mlp.experts.3.up_proj"
+    assert out[gate + ".weight"].dtype == torch.uint8 and torch.equal(out[gate + ".weight_scale_2"], out[up + ".weight_scale_2"])
+    assert out["model.layers.0.self_attn.q_proj.weight"].dtype == torch.bfloat16           # experts only by default
+    assert out["model.layers.1.mlp.experts.0.down_proj.weight"].dtype == torch.bfloat16    # ignore rule
+    assert torch.equal(qe.nvfp4_dequantize(out[up + ".weight"], out[up + ".weight_scale"], out[up + ".weight_scale_2"]),
+                       R.nvfp4_qdq(w * 2, global_amax=(w * 2).float().abs().max()))
+    with pytest.raises(ValueError):
+        qe.export_nvfp4(named[:1], num_layers=2)                                           # a gate without its up
+    assert qe.is_ignored("a.b.c.weight", ["a.b"]) and qe.is_ignored("a.b.weight", ["re:a\\..*"]) and not qe.is_ignored("a.bc.weight", ["a.b"])
+    # int4: symmetric and asymmetric, packing order, decode = fake quant
+    parts = qe.int4_quantize(w, 32, True)
+    assert parts["weight_packed"].dtype == torch.int32 and parts["weight_packed"].shape == (48, 8) and parts["weight_shape"].tolist() == [48, 64]
+    want, _ = ops.int4_fake_quant(w, 1, 32, True)
+    assert torch.allclose(qe.int4_dequantize(parts).float(), want.float(), atol=1e-2, rtol=1e-2)
+    codes = torch.arange(16, dtype=torch.uint8).reshape(1, 16)
+    packed = qe.pack_int32(codes)
+    assert packed.tolist() == [[0x76543210, 0xFEDCBA98 - (1 << 32)]] and torch.equal(qe.unpack_int32(packed, 16), codes.long())
+    asym = qe.int4_quantize(w, 32, False)
+    assert asym["weight_zero_point"].shape == (6, 2)                                      # [M/8, K/g]: packed along M
+    assert (qe.int4_dequantize(asym).float() - w.float()).abs().max() < (w.float().abs().max() / 7)
+    out4 = dict(qe.export_int4([("model.layers.0.self_attn.q_proj.weight", w), ("lm_head.weight", w)], group_size=32))
+    assert "model.layers.0.self_attn.q_proj.weight_packed" in out4 and "lm_head.weight" in out4
+    assert qe.quant_config("int4")["quantization_config"]["format"] == "pack-quantized"
+    assert qe.quant_config("nvfp4")["quantization_config"]["quant_algo"] == "NVFP4"
+
+
+@pytest.mark.parametrize("mode,preset", [("nvfp4", "tiny-moe"), ("int4", "tiny")])
+def test_quantised_disk_sync_reaches_the_engine_as_the_quantised_values(tmp_path, mode, preset):
+    """--export-quant through the disk protocol: the engine ends up with decode(quantise(trainer weights))."""
+    from test_e2e import BASE
+    from miles_b200.args import parse_args
+    from miles_b200.engine.engine import Engine
+    from miles_b200.models.convert import hf_state_to_ours, to_hf
+    from miles_b200.orchestration.wiring import create_parallel_state, create_training_models
+    from miles_b200.weight_update import quant_export as qe
+    from miles_b200.weight_update.updater import WeightUpdater
+
+    args = parse_args((BASE.replace("--model-name tiny", f"--model-name {preset}") + f" --export-quant {mode} --export-quant-all-linears "
+                       f"--update-weight-transfer-mode disk --update-weight-disk-dir {tmp_path}").split())
+    ps = create_parallel_state(args)
+    actor, _, _ = create_training_models(args, ps)
+    eng = Engine(actor.cfg, ps=ps, device="cpu", dtype=torch.float32, num_blocks=8, block_size=16, seed=99)
+    WeightUpdater(args, actor, [eng]).update_weights()
+    import json
+
+    cfgj = json.load(open(next(os.path.join(r, "config.json") for r, _, f in os.walk(tmp_path) if "config.json" in f)))
+    assert cfgj["quantization_config"]["quant_method"] in ("modelopt", "compressed-tensors")
+    got = dict(eng.model.named_parameters())
+    hf = [x for n, p in actor.model.named_parameters() for x in to_hf(n, p.data, actor.cfg)]
+    packed = qe.export_nvfp4(hf, all_linears=True, num_layers=actor.cfg.num_layers) if mode == "nvfp4" else qe.export_int4(hf)
+    want = hf_state_to_ours(dict(qe.dequantize_named(packed, torch.float32)), actor.cfg)
+    changed = 0
+    for n, p in actor.model.named_parameters():
+        assert torch.allclose(got[n].data, want[n].float(), atol=1e-6), n
+        changed += int(not torch.equal(want[n].float(), p.data.float()))
+    assert changed > 0                                                         # something really was quantised
