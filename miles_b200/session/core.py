@@ -104,7 +104,7 @@ class SessionManager:
             ids = self.tito.start(messages, tools)
             s.tokens, s.prompt_length = list(ids), len(ids)
         else:
-            ids = self.tito.extend(s.messages, new, tools)
+            ids = self.tito.extend(s.messages, new, tools, pretokenized=s.tokens)
             s.tokens += ids
             s.loss_mask += [0] * len(ids)
             s.log_probs += [0.0] * len(ids)
@@ -126,7 +126,7 @@ class SessionManager:
         s.log_probs += [0.0] * len(close)
         for span in meta.get("weight_version_spans") or []:
             s.weight_versions.append(list(span))
-        text = out.get("text") or self.tito.decode([t for t in gen if t not in self.tito.encode(self.tito.end_of_turn)[:1]])
+        text = out.get("text") or self.tito.decode(self.tito.strip_turn_end(gen))
         s.messages.append({"role": "assistant", "content": text})
         marks.append(len(s.tokens))
         fr = (meta.get("finish_reason") or {}).get("type", "stop")
@@ -186,3 +186,73 @@ def build_app(manager: SessionManager):
         return {"status": "ok", "sessions": len(manager.sessions)}
 
     return app
+
+
+# ---- picking what to train on ---------------------------------------------------------------------------------------
+
+def drop_same_prompt_retries(samples: list) -> list:
+    """Default `--session-sample-picker-path`: an agent that retries a call leaves several samples with the same prompt
+    ids in one session; only the last attempt of each prompt is trained on (the earlier ones were discarded by the agent).
+    The prompt of a multi-turn sample is everything before its last sampled turn."""
+    last: dict[tuple, int] = {}
+    for i, s in enumerate(samples):
+        n = len(s.tokens) - s.response_length
+        mask = list(s.loss_mask or [])
+        if mask and any(mask):                       # multi-turn: the context ends where the LAST sampled run begins
+            j = len(mask) - 1
+            while j >= 0 and not mask[j]:
+                j -= 1
+            while j >= 0 and mask[j]:
+                j -= 1
+            n += j + 1
+        last[tuple(s.tokens[:n])] = i
+    keep = set(last.values())
+    return [s for i, s in enumerate(samples) if i in keep]
+
+
+def default_postprocess(samples: list) -> list:
+    """Default `--session-sample-postprocessor-path`: samples pass through unchanged."""
+    return samples
+
+
+def session_samples(manager: SessionManager, root_sid: str, args=None) -> list:
+    """Training samples of a session tree: every branch is a complete trajectory from the first message on (a fork copies
+    the shared turns' ids), so each session of the tree gives one sample; the configured picker then drops what should not
+    be trained on and the post-processor has the last word."""
+    from ..utils.misc import load_function
+
+    children: dict[str, list[str]] = {}
+    for sid, s in manager.sessions.items():
+        if s.parent is not None:
+            children.setdefault(s.parent, []).append(sid)
+    members, stack = [], [root_sid]
+    while stack:
+        sid = stack.pop()
+        members.append(sid)
+        stack.extend(children.get(sid, []))
+    samples = [manager.to_sample(sid) for sid in sorted(members) if manager.sessions[sid].tokens]
+    pick = load_function(getattr(args, "session_sample_picker_path", None) or "miles_b200.session.core.drop_same_prompt_retries")
+    post = load_function(getattr(args, "session_sample_postprocessor_path", None) or "miles_b200.session.core.default_postprocess")
+    return post(pick(samples))
+
+
+def start_session_server(args, tokenizer, generate, in_thread: bool = True):
+    """Serve sessions on `--session-server-ip` : `--session-server-port` with the `--tito-model` family.  Returns
+    (manager, server, thread)."""
+    import threading
+
+    import uvicorn
+
+    family = getattr(args, "tito_model", None) or "auto"
+    manager = SessionManager(tokenizer, generate, family="auto" if family == "default" else family)
+    host = getattr(args, "session_server_ip", None) or "127.0.0.1"
+    port = int(getattr(args, "session_server_port", None) or 30300)
+    server = uvicorn.Server(uvicorn.Config(build_app(manager), host=host, port=port, log_level="warning"))
+    if not in_thread:
+        server.run()
+        return manager, server, None
+    t = threading.Thread(target=server.run, daemon=True, name=f"session-server-{port}")
+    t.start()
+    while not server.started:
+        time.sleep(0.01)
+    return manager, server, t

@@ -218,3 +218,100 @@ def test_delta_writer_reader_and_snapshots(tmp_path):
     from miles_b200.checkpoint import hf_io
 
     assert "model.embed_tokens.weight" in hf_io.load_hf_dir(str(tmp_path / "snap" / "step_4"))
+
+
+# ---- chat families of the token-in-token-out tokenizer --------------------------------------------------------------
+
+FAMILY_SPECIALS = {
+    "qwen3": ["<|im_start|>", "<|im_end|>", "<|endoftext|>"],
+    "glm47": ["[gMASK]", "<sop>", "<|system|>", "<|user|>", "<|assistant|>", "<|observation|>", "<|endoftext|>"],
+    "deepseek": ["<｜begin▁of▁sentence｜>", "<｜User｜>", "<｜Assistant｜>", "<｜tool▁output▁begin｜>", "<｜tool▁output▁end｜>", "<｜end▁of▁sentence｜>"],
+    "kimi": ["<|im_system|>", "<|im_user|>", "<|im_assistant|>", "<|im_middle|>", "<|im_end|>"],
+    "llama": ["<|begin_of_text|>", "<|start_header_id|>", "<|end_header_id|>", "<|eot_id|>"],
+    "gemma": ["<bos>", "<start_of_turn>", "<end_of_turn>"],
+}
+
+
+@pytest.mark.parametrize("family", sorted(FAMILY_SPECIALS))
+def test_tito_family_trajectory_equals_full_render(family):
+    """For every family: start → model turn (ends the way that family's models end a turn) → appended tool + user
+    messages → the kept trajectory equals the tokenisation of the fully rendered conversation, the model's ids untouched."""
+    from miles_b200.session.tito import ByteChatTokenizer, TitoTokenizer
+    from miles_b200.session.tito_families import guess_family
+
+    tok = ByteChatTokenizer(FAMILY_SPECIALS[family])
+    assert guess_family(tok) == family
+    tito = TitoTokenizer(tok, family)
+    msgs = [{"role": "system", "content": "be brief"}, {"role": "user", "content": "2+2?"}]
+    ids = tito.start(msgs)
+    assert ids == tito.encode(tito.render(msgs, add_generation_prompt=True))
+    answer = tito.encode("it is 4")
+    if family == "glm47":
+        gen = answer + tito.encode("<|observation|>")        # GLM ends its turn by sampling the next role tag
+    else:
+        gen = answer + tito.encode(tito.spec.eot)
+    traj = ids + gen + tito.close_assistant_turn(gen)
+    history = msgs + [{"role": "assistant", "content": "it is 4"}]
+    new = [{"role": "tool", "content": "calc says 4"}, {"role": "user", "content": "thanks, and 3+3?"}]
+    traj = traj + tito.extend(history, new, pretokenized=traj)
+    want = tito.encode(tito.render(history + new, add_generation_prompt=True))
+    assert traj == want, (tito.decode(traj), tito.decode(want))
+    assert traj[len(ids):len(ids) + len(answer)] == answer
+    rep = tito.check_against_fresh(history + new, traj[:-len(tito.encode(tito.spec.generation_prompt))])
+    assert rep["special_equal"] and rep["equal"]
+    with pytest.raises(ValueError):
+        tito.extend(history, [{"role": "assistant", "content": "x"}])          # an assistant message cannot be injected
+
+
+def test_tito_qwen_tools_thinking_and_grouped_tool_results():
+    from miles_b200.session.tito import ByteChatTokenizer, TitoTokenizer
+    from miles_b200.session.tito_families import QWEN3, QWEN35, compare_token_sequences
+
+    tools = [{"type": "function", "function": {"name": "add", "parameters": {"type": "object"}}}]
+    msgs = [{"role": "user", "content": "add"},
+            {"role": "assistant", "content": "", "reasoning_content": "need the tool",
+             "tool_calls": [{"function": {"name": "add", "arguments": "{\"a\": 1}"}}]},
+            {"role": "tool", "content": "1"}, {"role": "tool", "content": "2"}]
+    text = QWEN3.render(msgs, add_generation_prompt=True, tools=tools, enable_thinking=False)
+    assert "<tools>\n" + '{"type": "function"' in text and "# Tools" in text
+    assert '<think>\nneed the tool</think>\n<tool_call>\n{"name": "add", "arguments": {"a": 1}}\n</tool_call><|im_end|>' in text
+    assert "<|im_start|>user\n<tool_response>\n1\n</tool_response>\n<tool_response>\n2\n</tool_response><|im_end|>" in text   # one turn
+    assert text.endswith("<|im_start|>assistant\n<think>\n\n</think>\n\n")
+    assert "<function=add>\n<parameter=a>\n1\n</parameter>" in QWEN35.render(msgs)
+    t = TitoTokenizer(ByteChatTokenizer(), "qwen3")
+    assert (t.reasoning_parser, t.tool_call_parser) == ("qwen3", "qwen25")
+    rep = compare_token_sequences([1, 256, 5, 257, 10], [1, 256, 6, 7, 257], {256, 257}, {10})
+    assert not rep["equal"] and rep["special_equal"] and rep["first_diff"] == 2
+    assert not compare_token_sequences([256, 257], [256], {256, 257})["special_equal"]
+
+
+def test_session_server_with_family_and_sample_picking():
+    import asyncio
+    import types
+
+    from miles_b200.session.core import SessionManager, drop_same_prompt_retries, session_samples
+    from miles_b200.session.tito import ByteChatTokenizer
+    from miles_b200.types import Sample
+
+    tok = ByteChatTokenizer(FAMILY_SPECIALS["glm47"])
+
+    async def generate(payload):
+        reply = list(b"ok") + [tok.SPECIALS["<|user|>"]]
+        return {"text": "", "meta_info": {"output_token_logprobs": [[-0.5, t] for t in reply], "finish_reason": {"type": "stop"}}}
+
+    m = SessionManager(tok, generate, family="glm47")
+    s = m.create("a")
+    out = asyncio.run(m.chat("a", [{"role": "user", "content": "hi"}]))
+    assert out["choices"][0]["message"]["content"] == "ok"
+    asyncio.run(m.chat("a", [{"role": "user", "content": "hi"}, {"role": "assistant", "content": "ok"}, {"role": "user", "content": "more"}]))
+    text = tok.decode(m.get("a").tokens)
+    assert text == "[gMASK]<sop><|user|>\nhi<|assistant|>\nok<|user|>\nmore<|assistant|>\nok<|user|>"      # no doubled role tag
+    # a diverging request forks a branch; samples come from the leaves only
+    asyncio.run(m.chat("a", [{"role": "user", "content": "hi"}, {"role": "assistant", "content": "ok"}, {"role": "user", "content": "other"}]))
+    got = session_samples(m, "a", types.SimpleNamespace())
+    assert len(got) == 2 and all(isinstance(x, Sample) for x in got)
+    a = Sample(tokens=[1, 2, 3, 9], response_length=1)
+    b = Sample(tokens=[1, 2, 3, 8], response_length=1)
+    c = Sample(tokens=[1, 2, 4, 8], response_length=1)
+    assert drop_same_prompt_retries([a, b, c]) == [b, c]
+    del s
