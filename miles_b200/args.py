@@ -346,6 +346,7 @@ def build_parser() -> argparse.ArgumentParser:
     g.add_argument("--snapshot-keep", type=int, default=2)
     g.add_argument("--optimizer-nvme-dir", type=str, default=None,
                    help="stream fp32 master weights and Adam moments from files in this directory (state larger than HBM + host)")
+    g.add_argument("--optimizer-nvme-bucket-numel", type=int, default=64 << 20, help="floats per streamed bucket (three such buffers on the device)")
     g.add_argument("--audit-dir", type=str, default=None,
                    help="write the audit event log here (weight checksums per version; analyse with miles_b200.audit.events)")
     g.add_argument("--ci-save-grad-norm", type=str, default=None)

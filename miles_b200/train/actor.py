@@ -140,7 +140,8 @@ class TrainActor:
             self.optimizer = DistributedAdam(
                 named, lr=lr0, betas=(args.adam_beta1, args.adam_beta2),
                 eps=args.adam_eps, weight_decay=args.weight_decay, clip_grad=args.clip_grad, ps=self.ps,
-                allocator=self._symmetric_allocator(), state_allocator=state_alloc)
+                allocator=self._symmetric_allocator(), state_allocator=state_alloc,
+                nvme_dir=self._nvme_dir(), nvme_bucket_numel=int(getattr(args, "optimizer_nvme_bucket_numel", 64 << 20) or (64 << 20)))
         self.tp_replicated = {n for n, p in named if _tp_replicated(n)}
         if self.ps.tp_size > 1:
             self.optimizer.mark_tp_replicated(self.tp_replicated, named)
@@ -664,6 +665,16 @@ class TrainActor:
         self._offloaded = {}
         self.optimizer.restore_grads()
         self.asleep = False
+
+    def _nvme_dir(self):
+        """`--optimizer-nvme-dir DIR` (or `--stream-optimizer-state-to-disk`, which defaults DIR to <save>/optimizer_stream)."""
+        d = getattr(self.args, "optimizer_nvme_dir", None)
+        if d is None and getattr(self.args, "stream_optimizer_state_to_disk", False):
+            import tempfile
+
+            base = getattr(self.args, "save", None) or tempfile.gettempdir()
+            d = os.path.join(base, "optimizer_stream")
+        return os.path.join(d, self.role) if d else None
 
     def ensure_groups(self):
         """Re-create the process groups released by `sleep` (collective; a no-op when they are alive)."""

@@ -27,9 +27,11 @@ FILES = ("master", "exp_avg", "exp_avg_sq")
 
 class NvmeStreamAdam:
     def __init__(self, flat_param: torch.Tensor, directory: str, *, lr=1e-3, betas=(0.9, 0.999), eps=1e-8, weight_decay=0.0,
-                 bucket_numel: int = 64 << 20, rank: int = 0):
-        """`flat_param`: the flat (bf16 or fp32) parameter buffer this optimizer updates in place."""
+                 bucket_numel: int = 64 << 20, rank: int = 0, decay_mask: torch.Tensor | None = None):
+        """`flat_param`: the flat (bf16 or fp32) parameter buffer this optimizer updates in place.  `decay_mask` (fp32, same
+        length, on the parameters' device): weight decay applies only where it is 1."""
         self.param = flat_param
+        self.decay_mask = decay_mask
         self.n = flat_param.numel()
         self.lr, self.betas, self.eps, self.wd = lr, betas, eps, weight_decay
         self.bucket = min(bucket_numel, self.n)
@@ -102,8 +104,19 @@ class NvmeStreamAdam:
                     d[k].copy_(h[k][:m], non_blocking=True)
             else:
                 d = {k: h[k][:m] for k in FILES}
-            ops.adamw_step(d["master"], flat_grad[lo:hi], d["exp_avg"], d["exp_avg_sq"], lr=lr, beta1=b1, beta2=b2, eps=self.eps,
-                           weight_decay=self.wd, step=self.step_count, grad_scale=grad_scale, param_out=self.param[lo:hi])
+            if self.decay_mask is None:
+                ops.adamw_step(d["master"], flat_grad[lo:hi], d["exp_avg"], d["exp_avg_sq"], lr=lr, beta1=b1, beta2=b2, eps=self.eps,
+                               weight_decay=self.wd, step=self.step_count, grad_scale=grad_scale, param_out=self.param[lo:hi])
+            elif self.dev is not None:
+                ops._k().adamw_step_masked(d["master"], flat_grad[lo:hi], d["exp_avg"], d["exp_avg_sq"], self.decay_mask[lo:hi], lr, b1, b2,
+                                           self.eps, self.wd, self.step_count, grad_scale, self.param[lo:hi])
+            else:
+                gs = flat_grad[lo:hi].float() * grad_scale
+                d["exp_avg"].mul_(b1).add_(gs, alpha=1 - b1)
+                d["exp_avg_sq"].mul_(b2).addcmul_(gs, gs, value=1 - b2)
+                denom = (d["exp_avg_sq"] / (1 - b2 ** self.step_count)).sqrt_().add_(self.eps)
+                d["master"].mul_(1 - lr * self.wd * self.decay_mask[lo:hi]).addcdiv_(d["exp_avg"] / (1 - b1 ** self.step_count), denom, value=-lr)
+                self.param[lo:hi].copy_(d["master"])
             if self.dev is not None:
                 for k in FILES:
                     h[k][:m].copy_(d[k], non_blocking=True)
@@ -113,6 +126,16 @@ class NvmeStreamAdam:
             pending_write = self.io.submit(self._write, slot, lo, hi)
         if pending_write is not None:
             pending_write.result()
+
+    def tensor(self, key: str) -> torch.Tensor:
+        """The whole state file as a CPU tensor that SHARES the mapping (reads and writes go to the file)."""
+        return torch.from_numpy(self.maps[key])
+
+    def reload_master(self):
+        """Rewrite the master file from the current parameters (after loading weights); the moments stay."""
+        for lo in range(0, self.n, self.bucket):
+            hi = min(self.n, lo + self.bucket)
+            self.maps["master"][lo:hi] = self.param[lo:hi].detach().float().cpu().numpy()
 
     def flush(self):
         for m in self.maps.values():

@@ -17,6 +17,7 @@ buffer.  On CPU (gloo) and in the baseline mode the stages are separate collecti
 from __future__ import annotations
 
 import math
+import os
 from dataclasses import dataclass
 from typing import Any, Iterable
 
@@ -43,6 +44,7 @@ class _Domain:
     shard: tuple[int, int] = (0, 0)
     numel: int = 0
     decay_mask: torch.Tensor | None = None  # fp32 shard, 1 where weight decay applies
+    nvme: Any = None                    # NvmeStreamAdam holding this shard's state in files (then master / moments are file-backed views)
     names: list[str] = None             # parameter names, in buffer order
     offsets: list[int] = None           # element offset of each parameter in the flat buffers
 
@@ -50,7 +52,8 @@ class _Domain:
 class DistributedAdam:
     def __init__(self, named_params: Iterable[tuple[str, torch.nn.Parameter]], *, lr: float, betas=(0.9, 0.98),
                  eps: float = 1e-8, weight_decay: float = 0.0, clip_grad: float = 1.0, ps=None,
-                 allocator=None, moments_dtype=torch.float32, state_allocator=None):
+                 allocator=None, moments_dtype=torch.float32, state_allocator=None, nvme_dir: str | None = None,
+                 nvme_bucket_numel: int = 64 << 20):
         self.lr, self.betas, self.eps, self.weight_decay, self.clip_grad = lr, betas, eps, weight_decay, clip_grad
         self.ps = ps
         self.step_count = 0
@@ -58,6 +61,9 @@ class DistributedAdam:
         # where the fp32 master weights and the Adam moments live: None → ordinary tensors; a callable (n, dtype, device, tag)
         # → e.g. the VMM arena, whose physical pages can be released for the rollout phase at stable addresses
         self.state_allocator = state_allocator
+        # fp32 master weights and Adam moments of this rank's shards in FILES under this directory, streamed through the
+        # device bucket by bucket at every step (train/nvme_stream.py): for state that fits neither HBM nor host memory
+        self.nvme_dir, self.nvme_bucket_numel = nvme_dir, nvme_bucket_numel
         named = [(n, p) for n, p in named_params if p.requires_grad]
         dense = [(n, p) for n, p in named if not _is_expert(n)]
         expert = [(n, p) for n, p in named if _is_expert(n)]
@@ -101,7 +107,17 @@ class DistributedAdam:
                 decay[o:o + p.numel()] = 1.0
         s = n_pad // gsize
         d.shard = (grank * s, (grank + 1) * s)
-        if self.state_allocator is not None:
+        d.decay_mask = decay[d.shard[0]:d.shard[1]].clone()
+        if self.nvme_dir is not None:
+            from .nvme_stream import NvmeStreamAdam
+
+            rank = dist.get_rank() if dist.is_initialized() else 0
+            d.nvme = NvmeStreamAdam(d.param_buf[d.shard[0]:d.shard[1]], os.path.join(self.nvme_dir, name), lr=self.lr, betas=self.betas,
+                                    eps=self.eps, weight_decay=self.weight_decay, bucket_numel=self.nvme_bucket_numel, rank=rank,
+                                    decay_mask=d.decay_mask)
+            # file-backed views: everything that reads or writes the optimizer state (checkpoints, resets) goes to the files
+            d.master, d.exp_avg, d.exp_avg_sq = d.nvme.tensor("master"), d.nvme.tensor("exp_avg"), d.nvme.tensor("exp_avg_sq")
+        elif self.state_allocator is not None:
             d.master = self.state_allocator(s, torch.float32, device, f"{name}.master")
             d.master.copy_(d.param_buf[d.shard[0]:d.shard[1]])
             d.exp_avg = self.state_allocator(s, moments_dtype, device, f"{name}.exp_avg").zero_()
@@ -110,7 +126,6 @@ class DistributedAdam:
             d.master = d.param_buf[d.shard[0]:d.shard[1]].float().clone()
             d.exp_avg = torch.zeros(s, dtype=moments_dtype, device=device)
             d.exp_avg_sq = torch.zeros(s, dtype=moments_dtype, device=device)
-        d.decay_mask = decay[d.shard[0]:d.shard[1]].clone()
         if group is not None:
             from ..parallel.reloadable import REGISTRY
 
@@ -193,13 +208,17 @@ class DistributedAdam:
         b1, b2 = self.betas
         for d, g in zip(self.domains, shards):
             lo, hi = d.shard
-            _adam_shard(d, g, lr, b1, b2, self.eps, self.weight_decay, self.step_count, scale, d.param_buf[lo:hi])
+            if d.nvme is not None:
+                d.nvme.step_count = self.step_count - 1
+                d.nvme.step(g, grad_scale=float(scale), lr=lr)
+            else:
+                _adam_shard(d, g, lr, b1, b2, self.eps, self.weight_decay, self.step_count, scale, d.param_buf[lo:hi])
             self._all_gather(d)
         return {"grad_norm": float(norm)}
 
     def _try_fused_step(self, lr):
         ps = self.ps
-        if ps is None or ps.fabric is None or not ps.fused:
+        if ps is None or ps.fabric is None or not ps.fused or self.nvme_dir is not None:
             return None
         from ..parallel import dp as dp_fused
         return dp_fused.fused_step(self, lr)
@@ -224,6 +243,9 @@ class DistributedAdam:
     def reload_master_from_params(self):
         """After loading model weights: refresh fp32 master from the (new) parameter buffer."""
         for d in self.domains:
+            if d.nvme is not None:
+                d.nvme.reload_master()
+                continue
             d.master.copy_(d.param_buf[d.shard[0]:d.shard[1]].float())
 
     def reset_state(self):
@@ -255,7 +277,8 @@ class DistributedAdam:
     def tensors_by_tag(self) -> dict[str, list[torch.Tensor]]:
         out = {"optimizer": [], "grad": [], "param": []}
         for d in self.domains:
-            out["optimizer"] += [d.master, d.exp_avg, d.exp_avg_sq]
+            if d.nvme is None:                       # file-backed state occupies no device memory: nothing to move on sleep
+                out["optimizer"] += [d.master, d.exp_avg, d.exp_avg_sq]
             out["grad"].append(d.grad_buf)
             out["param"].append(d.param_buf)
         return out

@@ -308,3 +308,29 @@ def test_quantised_disk_sync_reaches_the_engine_as_the_quantised_values(tmp_path
         assert torch.allclose(got[n].data, want[n].float(), atol=1e-6), n
         changed += int(not torch.equal(want[n].float(), p.data.float()))
     assert changed > 0                                                         # something really was quantised
+
+
+def test_nvme_streamed_optimizer_in_the_trainer_matches_the_resident_one(tmp_path):
+    """--optimizer-nvme-dir: the trainer's distributed Adam keeps master weights and moments in files; two GRPO steps give the
+    same weights as the resident optimizer, the sharded checkpoint reads the state through the file-backed views."""
+    from test_e2e import BASE, _run
+    from miles_b200.args import parse_args
+    from miles_b200.orchestration.wiring import create_parallel_state, create_training_models
+
+    h_ref = _run("--weight-decay 0.1")
+    h_nv = _run(f"--weight-decay 0.1 --optimizer-nvme-dir {tmp_path}/nv --optimizer-nvme-bucket-numel 4096")
+    for k in ("train/grad_norm", "train/loss", "rollout/raw_reward"):
+        for a, b in zip(h_ref.series(k), h_nv.series(k)):
+            assert abs(a - b) <= 1e-5 * max(1.0, abs(a)), (k, a, b)
+    assert os.path.exists(os.path.join(tmp_path, "nv", "actor", "dense", "rank0", "exp_avg.bin"))
+    args = parse_args((BASE + f" --optimizer-nvme-dir {tmp_path}/nv2 --save {tmp_path}/ck").split())
+    actor, _, _ = create_training_models(args, create_parallel_state(args))
+    d = actor.optimizer.domains[0]
+    assert d.nvme is not None and d.master.device.type == "cpu" and torch.equal(d.master, d.param_buf[d.shard[0]:d.shard[1]].float().cpu())
+    d.exp_avg.fill_(0.25)                                   # through the view, into the file
+    assert float(torch.from_numpy(d.nvme.maps["exp_avg"][:4].copy()).sum()) == 1.0
+    actor.save_model(0)
+    from miles_b200.checkpoint import torch_dist
+
+    opt = torch_dist.load_state(os.path.join(tmp_path, "ck", "iter_0000000"), prefix_filter=("rng", "_extra_state"))
+    assert float(opt["optimizer.state.exp_avg.decoder.layers.0.self_attention.linear_proj.weight"].mean()) == 0.25
