@@ -77,6 +77,9 @@ def build_parser() -> argparse.ArgumentParser:
     g.add_argument("--num-layers-at-end-in-bf16", type=int, default=0)
     g.add_argument("--int4-group-size", type=int, default=32)
     g.add_argument("--int4-asymmetric", action="store_true")
+    g.add_argument("--custom-step-runner-path", type=str, default=None,
+                   help="module:factory(actor) → an object with forward_only_step / forward_backward_step / zero_grad / apply_step "
+                        "(train/step_runner.py) replacing the built-in linear / GPipe / 1F1B schedules")
     g.add_argument("--ckpt-format", choices=["torch_dist", "native"], default="torch_dist",
                    help="torch_dist: one DCP store per iteration with Megatron-named entries and the optimizer state in "
                         "model space, reloadable under any parallel layout; native: one file per rank with that rank's shards")

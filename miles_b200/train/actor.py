@@ -329,26 +329,16 @@ class TrainActor:
         out: dict[int, torch.Tensor] = {}
         replay = getattr(self.args, "use_routing_replay", False)
         self.model.eval()
-        for idx in (self.profiler.iterate("train_log_probs", micro_batches) if hasattr(self, "profiler") else micro_batches):
-            pb = pack_micro_batch(shard, idx, self.device, pad_multiple=self._pad_multiple(), with_replay=replay)
-            if self.ps.pp_size > 1:
-                from ..parallel.pp import broadcast_from_last_stage
 
-                lp, _, _io = self._forward_logprobs_pp(pb, False, replay)
-                if lp is None:
-                    lp = torch.zeros(pb.gather_index.numel(), device=self.device)
-                lp = broadcast_from_last_stage(lp.float().contiguous(), self.ps)     # every stage keeps the same record
-            elif self.dumper is not None:
-                with self.dumper.phase("fwd_only"):
-                    lp, _ = self._forward_logprobs(pb, False, replay)
-                    self.dumper.dump("log_probs", lp)
-                    self.dumper.step()
-            else:
-                lp, _ = self._forward_logprobs(pb, False, replay)
+        def pack(idx):
+            return pack_micro_batch(shard, idx, self.device, pad_multiple=self._pad_multiple(), with_replay=replay)
+
+        def keep(pb, idx, lp):
             for i, piece in zip(idx, lp.float().split(pb.response_lengths)):
                 out[i] = piece
-        if self.ps.pp_size > 1:
-            self._pipe().finish()
+
+        batches = self.profiler.iterate("train_log_probs", micro_batches) if hasattr(self, "profiler") else micro_batches
+        self._step_runner().forward_only_step(batches, pack, keep, replay=replay)
         if tag is not None and tag != "actor":
             self.backuper.restore("actor")
         return [out[i] for i in sorted(out)]
@@ -492,48 +482,10 @@ class TrainActor:
         def pack(idx):
             return pack_micro_batch(shard, idx, dev, pad_multiple=self._pad_multiple(), with_replay=replay)
 
-        if ps.pp_size > 1 and getattr(args, "pp_schedule", "1f1b") == "1f1b":
-            stage = self._pipe()
-            packed: dict[int, PackedBatch] = {}
-
-            def get(i):
-                if i not in packed:
-                    packed[i] = pack(mbs[i])
-                return packed[i]
-
-            def forward_step(i, hidden_in):
-                pb = get(i)
-                hidden = self.model(pb.tokens, self._meta(pb, replay), hidden_in=hidden_in)
-                if not stage.is_last:
-                    packed.pop(i, None)
-                    return hidden, None
-                out, ent = self._score_hidden(pb, hidden, want_ent)
-                packed.pop(i, None)
-                return None, score(pb, mbs[i], out, ent)
-
-            stage.run_1f1b(len(mbs), lambda i: get(i).tokens.numel(), forward_step)
-        elif ps.pp_size > 1:
-            # all forwards, then all backwards (GPipe order)
-            pipelined: list = []
-            for idx in mbs:
-                pb = pack(idx)
-                out, ent, io = self._forward_logprobs_pp(pb, want_ent, replay)
-                pipelined.append((score(pb, idx, out, ent) if out is not None else None, io))
-            stage = self._pipe()
-            for loss, io in pipelined:            # same micro-batch order on every stage
-                stage.backward(io, loss)
-            stage.finish()
-        else:
-            for idx in mbs:
-                pb = pack(idx)
-                if self.dumper is not None:
-                    with self.dumper.phase("fwd_bwd"):
-                        out, ent = self._forward_logprobs(pb, want_ent, replay)
-                        self.dumper.dump("log_probs", out)
-                    score(pb, idx, out, ent).backward()
-                    continue
-                out, ent = self._forward_logprobs(pb, want_ent, replay)
-                score(pb, idx, out, ent).backward()
+        # the schedule of forwards and backwards over the micro-batches belongs to the step runner (linear, GPipe, 1F1B, or
+        # a custom one): this method only says how a micro-batch is packed and how its loss is computed
+        runner = self._step_runner()
+        runner.forward_backward_step(mbs, pack, score, want_ent=want_ent, replay=replay)
         self._finalize_grads()
         if self.dumper is not None:
             with self.dumper.phase("fwd_bwd") as d:
@@ -572,6 +524,16 @@ class TrainActor:
         out_metrics["grad_norm"] = stats["grad_norm"]
         out_metrics["lr-pg_0"] = lr
         return out_metrics
+
+    def _step_runner(self):
+        """The object that runs forwards and backwards over micro-batches (`train/step_runner.py`); `--custom-step-runner-path`
+        plugs another schedule or another backend's model."""
+        r = getattr(self, "_runner", None)
+        if r is None:
+            from .step_runner import build_step_runner
+
+            r = self._runner = build_step_runner(self)
+        return r
 
     def _loss_args(self):
         if self.role != "critic":

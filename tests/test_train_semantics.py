@@ -222,3 +222,38 @@ def test_failed_transfer_leaves_engines_running():
     with pytest.raises(RuntimeError, match="link down"):
         up.update_weights()
     assert eng.paused is False and eng.version == 0
+
+
+def test_custom_step_runner_is_used(tmp_path):
+    """--custom-step-runner-path: the trainer's forwards and backwards go through the plugged runner."""
+    import sys
+    import textwrap
+
+    mod = tmp_path / "my_runner.py"
+    mod.write_text(textwrap.dedent("""
+        from miles_b200.train.step_runner import LinearStepRunner
+
+        CALLS = {"fwd": 0, "fwd_bwd": 0}
+
+        class Counting(LinearStepRunner):
+            def forward_only_step(self, mbs, pack, compute, *, replay=False):
+                CALLS["fwd"] += 1
+                return super().forward_only_step(mbs, pack, compute, replay=replay)
+
+            def forward_backward_step(self, mbs, pack, score, *, want_ent, replay):
+                CALLS["fwd_bwd"] += 1
+                return super().forward_backward_step(mbs, pack, score, want_ent=want_ent, replay=replay)
+
+        def build(actor):
+            return Counting(actor)
+    """))
+    sys.path.insert(0, str(tmp_path))
+    try:
+        from test_e2e import _run
+
+        h = _run("--custom-step-runner-path my_runner.build --num-rollout 1")
+        import my_runner
+
+        assert my_runner.CALLS["fwd"] >= 1 and my_runner.CALLS["fwd_bwd"] >= 1 and h.series("train/grad_norm")[0] > 0
+    finally:
+        sys.path.remove(str(tmp_path))
