@@ -460,6 +460,26 @@ def validate_args(args) -> None:
     if args.fp32:
         args.bf16 = False
 
+    if getattr(args, "use_opd", False):
+        if args.opd_type is None:
+            raise ValueError("--use-opd needs --opd-type sglang (teacher engines) or megatron (teacher weights in the trainer)")
+        if (args.opd_log_prob_top_k or 0) < 0:
+            raise ValueError("--opd-log-prob-top-k must be non-negative")
+        if (args.opd_log_prob_top_k or 0) > 0 and args.opd_type != "sglang":
+            raise ValueError("--opd-log-prob-top-k needs --opd-type sglang")
+        if args.opd_type == "sglang":
+            from .rollout.opd import parse_teacher_urls
+
+            parse_teacher_urls(args.opd_teacher_urls)          # malformed or duplicate entries fail here, not mid-rollout
+            if not (args.opd_teacher_urls or args.opd_teacher_url or getattr(args, "opd_teacher_client", None)):
+                raise ValueError("--opd-type sglang needs --opd-teacher-url or --opd-teacher-urls")
+            if not getattr(args, "custom_rm_path", None):
+                args.custom_rm_path = "miles_b200.rollout.opd.opd_reward"   # scoring rides on the reward hook
+        elif args.opd_type == "megatron":
+            if not args.opd_teacher_load or not os.path.isdir(args.opd_teacher_load):
+                raise ValueError("--opd-type megatron needs --opd-teacher-load pointing at a checkpoint directory")
+        if not args.opd_kl_coef:
+            args.opd_kl_coef = 1.0
     # four-knob invariant: rollout_batch_size × n_samples = global_batch_size × num_steps_per_rollout
     if args.rollout_batch_size is not None:
         total = args.rollout_batch_size * args.n_samples_per_prompt

@@ -58,6 +58,8 @@ class Request:
     bt_len: int = 0
     logprob_start_len: int = -1    # ≥ 0: also return log-probs of the input tokens from this position on (scoring)
     input_logprobs: list[float] | None = None
+    top_logprobs_num: int = 0      # > 0 with scoring: also the k most likely tokens (and their log-probs) at every scored position
+    input_top_logprobs: list | None = None
     leader: Any = None             # request of the same prefill batch with identical tokens whose prompt KV this one shares
     cached_tokens: int = 0         # prompt tokens whose KV was shared instead of recomputed
 
@@ -87,6 +89,8 @@ class Request:
             toks = self.input_ids[start:]
             lps = ([None] if start == 0 else []) + list(self.input_logprobs)
             meta["input_token_logprobs"] = [(lp, t, None) for lp, t in zip(lps, toks)]
+            if self.input_top_logprobs is not None:
+                meta["input_top_logprobs"] = ([None] if start == 0 else []) + self.input_top_logprobs
         if self.return_routed_experts and self.routed:
             arr = np.concatenate(self.routed, axis=0)
             n = len(self.input_ids) + len(self.output_ids) - 1
@@ -177,14 +181,14 @@ class Engine:
     # ---------------------------------------------------------------------------------------
     def add_request(self, input_ids: list[int], sampling_params: dict | SamplingParams | None = None,
                     return_logprob: bool = True, return_routed_experts: bool = False, rid: str | None = None,
-                    on_done=None, logprob_start_len: int = -1) -> Request:
+                    on_done=None, logprob_start_len: int = -1, top_logprobs_num: int = 0) -> Request:
         sp = sampling_params if isinstance(sampling_params, SamplingParams) else SamplingParams.from_dict(sampling_params)
         with self.lock:
             rid = rid or f"req-{next(self._rid)}"
             req = Request(rid=rid, input_ids=list(input_ids), sampling=sp, return_logprob=return_logprob,
                           return_routed_experts=return_routed_experts and self.cfg.is_moe,
                           seed=(sp.seed if sp.seed is not None else (self.seed * 1000003 + zlib.crc32(rid.encode())) % (2 ** 31)),
-                          on_done=on_done, logprob_start_len=int(logprob_start_len))
+                          on_done=on_done, logprob_start_len=int(logprob_start_len), top_logprobs_num=int(top_logprobs_num or 0))
             budget = self.max_context_len - len(input_ids)
             if budget <= 0 or sp.max_new_tokens <= 0:
                 req.finish_reason = {"type": "length", "length": 0}
@@ -683,6 +687,13 @@ class Engine:
                 tgt = torch.tensor(r.input_ids[lo + 1:n_in], dtype=torch.int64, device=dev)
                 lp, _ = self.model.log_probs(hidden[rows], tgt) if len(tgt) else (torch.empty(0), None)
                 r.input_logprobs = [float(x) for x in lp.float().tolist()]
+                if r.top_logprobs_num > 0 and len(tgt):
+                    tops = []
+                    for c0 in range(0, rows.numel(), 512):          # full-vocabulary rows, 512 at a time
+                        lg = torch.log_softmax(self.model.logits(hidden[rows[c0:c0 + 512]]).float(), dim=-1)
+                        v, i = lg.topk(min(r.top_logprobs_num, lg.shape[-1]), dim=-1)
+                        tops += [[(float(a), int(b), None) for a, b in zip(vr, ir)] for vr, ir in zip(v.tolist(), i.tolist())]
+                    r.input_top_logprobs = tops
         followers = [r for r in batch if r.leader is not None]
         if followers:
             self._copy_tail_blocks(followers)

@@ -56,7 +56,8 @@ def build_app(engine, tokenizer=None):
         sps = sp if isinstance(sp, list) else [sp] * len(batch)
         reqs = [engine.add_request(i, dict(s), body.get("return_logprob", False), body.get("return_routed_experts", False),
                                    rid=(body.get("rid") if not batched else None),
-                                   logprob_start_len=body.get("logprob_start_len", -1)) for i, s in zip(batch, sps)]
+                                   logprob_start_len=body.get("logprob_start_len", -1),
+                                   top_logprobs_num=body.get("top_logprobs_num", 0)) for i, s in zip(batch, sps)]
         outs = [await _wait(r) for r in reqs]
         return JSONResponse(outs if batched else outs[0])
 

@@ -124,6 +124,66 @@ __global__ void __launch_bounds__(256) rmsnorm_fwd_kernel(const __nv_bfloat16* _
   }
 }
 
+// The same op with one WARP per row, for rows of 256·VPL elements (VPL 16-byte vectors per lane): every lane has all of its
+// loads in flight at once (2·VPL·16 bytes), the row sum needs shuffles only — no shared memory, no CTA barrier — and the
+// post-add values wait in registers as packed bf16.  Eight rows per CTA.
+template <bool ADD, int VPL>
+__global__ void __launch_bounds__(256) rmsnorm_fwd_warp_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ residual,
+                                                               const __nv_bfloat16* __restrict__ w, __nv_bfloat16* __restrict__ y,
+                                                               __nv_bfloat16* __restrict__ res_out, float* __restrict__ rstd_out,
+                                                               long long T, float eps) {
+  pdl_trigger();
+  pdl_wait();
+  constexpr int H = VPL * 256;
+  const int lane = threadIdx.x & 31;
+  const long long row = blockIdx.x * 8ll + (threadIdx.x >> 5);
+  if (row >= T) return;
+  const bf16x8* xr = reinterpret_cast<const bf16x8*>(x + row * H);
+  bf16x8 v[VPL];
+#pragma unroll
+  for (int i = 0; i < VPL; ++i) v[i] = xr[lane + 32 * i];
+  if (ADD) {
+    const bf16x8* rr = reinterpret_cast<const bf16x8*>(residual + row * H);
+    bf16x8 r[VPL];
+#pragma unroll
+    for (int i = 0; i < VPL; ++i) r[i] = rr[lane + 32 * i];
+    bf16x8* ro = reinterpret_cast<bf16x8*>(res_out + row * H);
+#pragma unroll
+    for (int i = 0; i < VPL; ++i) {
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const float2 a = __bfloat1622float2(v[i].v[j]), b = __bfloat1622float2(r[i].v[j]);
+        v[i].v[j] = __floats2bfloat162_rn(a.x + b.x, a.y + b.y);
+      }
+      ro[lane + 32 * i] = v[i];
+    }
+  }
+  float ss = 0.f;
+#pragma unroll
+  for (int i = 0; i < VPL; ++i)
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const float2 a = __bfloat1622float2(v[i].v[j]);
+      ss += a.x * a.x + a.y * a.y;
+    }
+  ss = warp_sum(ss);
+  const float rstd = rsqrtf(ss / H + eps);
+  if (lane == 0 && rstd_out != nullptr) rstd_out[row] = rstd;
+  const bf16x8* wr = reinterpret_cast<const bf16x8*>(w);
+  bf16x8* yr = reinterpret_cast<bf16x8*>(y + row * H);
+#pragma unroll
+  for (int i = 0; i < VPL; ++i) {
+    const bf16x8 wv = wr[lane + 32 * i];
+    bf16x8 o;
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const float2 a = __bfloat1622float2(v[i].v[j]), b = __bfloat1622float2(wv.v[j]);
+      o.v[j] = __floats2bfloat162_rn(a.x * rstd * b.x, a.y * rstd * b.y);
+    }
+    yr[lane + 32 * i] = o;
+  }
+}
+
 // RMSNorm backward.  x is the normalised input (the post-add residual stream), dy the gradient of y,
 // `dres` an optional extra gradient flowing into x directly (the residual branch).
 //   dx = rstd·(w·dy − x̂·mean(w·dy·x̂)) + dres ;   dw_partial[block] += dy·x̂
@@ -530,6 +590,21 @@ extern "C" int mb_rmsnorm_fwd(const void* x, const void* residual, const void* w
   typedef const __nv_bfloat16* cbf;
   typedef __nv_bfloat16* bf;
   cudaError_t e;
+  const bool add = residual != nullptr;
+  const dim3 wgrid(static_cast<unsigned>((T + 7) / 8));
+  // rows of 1024 / 2048 / 4096 elements with 16-byte aligned pointers: one warp per row (T ≥ 64 so that the grid fills the SMs)
+  const bool aligned = ((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(y) | reinterpret_cast<uintptr_t>(w) |
+                         reinterpret_cast<uintptr_t>(residual) | reinterpret_cast<uintptr_t>(res_out)) & 15) == 0;
+  if (aligned && T >= 64 && (H == 1024 || H == 2048 || H == 4096)) {
+#define MB_RMS_WARP(ADD_, VPL_)                                                                                                    \
+  launch_pdl(rmsnorm_fwd_warp_kernel<ADD_, VPL_>, wgrid, dim3(256), 0, s, X, (cbf)residual, (cbf)w, (bf)y, (bf)res_out, rstd, \
+             static_cast<long long>(T), eps)
+    if (H == 1024) e = add ? MB_RMS_WARP(true, 4) : MB_RMS_WARP(false, 4);
+    else if (H == 2048) e = add ? MB_RMS_WARP(true, 8) : MB_RMS_WARP(false, 8);
+    else e = add ? MB_RMS_WARP(true, 16) : MB_RMS_WARP(false, 16);
+#undef MB_RMS_WARP
+    return static_cast<int>(e);
+  }
   if (residual != nullptr)
     e = launch_pdl(rmsnorm_fwd_kernel<true>, dim3(static_cast<unsigned>(T)), dim3(256), 0, s, X, (cbf)residual, (cbf)w, (bf)y, (bf)res_out,
                    rstd, H, eps);

@@ -97,7 +97,8 @@ class InProcEngineClient:
         try:
             eng.add_request(payload["input_ids"], payload.get("sampling_params"), payload.get("return_logprob", True),
                             payload.get("return_routed_experts", False), on_done=on_done,
-                            logprob_start_len=payload.get("logprob_start_len", -1))
+                            logprob_start_len=payload.get("logprob_start_len", -1),
+                            top_logprobs_num=payload.get("top_logprobs_num", 0))
             await self.start()
             req = await fut
         finally:

@@ -178,6 +178,16 @@ class TrainActor:
                 self.backuper.restore("actor")
             else:
                 self.backuper.backup("ref")
+        if self.role == "actor" and getattr(args, "use_opd", False) and getattr(args, "opd_type", None) == "megatron":
+            load = getattr(args, "opd_teacher_load", None)
+            assert load, "--opd-type megatron needs --opd-teacher-load"
+            step = getattr(args, "opd_teacher_ckpt_step", None)
+            if step is not None:                      # a chosen iteration instead of the tracker's latest
+                load = ckpt.iter_dir(load, int(step))
+            self.backuper.backup("actor")
+            ckpt.load_weights_only(self, load)
+            self.backuper.backup("teacher")
+            self.backuper.restore("actor")
         return self.start_rollout_id
 
     def _rematerialize(self, check: bool = False):
@@ -372,6 +382,10 @@ class TrainActor:
             if getattr(args, "need_ref", False) and self.backuper.has("ref"):
                 with self.timer.span("ref_log_probs"):
                     ref_lp = self.compute_log_probs(shard, mbs, tag="ref")
+            if self.backuper.has("teacher") and "teacher_log_probs" not in shard:
+                # --opd-type megatron: the teacher is a second set of weights of this trainer, scored like the reference policy
+                with self.timer.span("teacher_log_probs"):
+                    shard["teacher_log_probs"] = [t.tolist() for t in self.compute_log_probs(shard, mbs, tag="teacher")]
             if not getattr(args, "skip_actor_forward_only", False) and not getattr(args, "use_rollout_logprobs", False):
                 self._hook("custom_megatron_before_log_prob_hook_path", rollout_id)
                 with self.timer.span("log_probs"), self.profiler.range("log_probs"):

@@ -131,3 +131,62 @@ def test_prompt_logprobs_and_opd_scoring():
     itl = req.to_response(teacher_eng)["meta_info"]["input_token_logprobs"]
     assert len(itl) == T and itl[0][0] is None and abs(itl[5][0] - want[1]) < 1e-4
     assert opd.topk_reverse_kl([[-0.1, -3.0]], [[-0.1, -3.0]])[0] < 1e-9
+
+
+def test_opd_teacher_fleet_topk_strategies_and_trainer_side_teacher(tmp_path):
+    import pytest
+
+    # teacher fleet: routing by the sample's metadata key, default fallback, malformed entries
+    assert opd.parse_teacher_urls(["math=http://h1:1/generate", "http://h3:3"]) == {"math": "http://h1:1/generate", "default": "http://h3:3"}
+    with pytest.raises(ValueError):
+        opd.parse_teacher_urls(["a=http://x", "a=http://y"])
+    e1, t1 = _client(seed=1)
+    e2, t2 = _client(seed=2)
+    s_math = Sample(tokens=[5, 6, 7, 9], metadata={"opd_teacher": "math"})
+    s_other = Sample(tokens=[5, 6, 7, 9], metadata={"opd_teacher": "poetry"})
+    for s in (s_math, s_other):
+        s.append_response([3, 4, 5], [-1.0, -1.0, -1.0])
+
+    async def go(k=0, strategy="only-teacher"):
+        args = _args(opd_teacher_client={"math": t1, "default": t2}, opd_teacher_key="opd_teacher", opd_task_rm_type=None,
+                     opd_log_prob_top_k=k, opd_top_k_strategy=strategy, opd_reward_weight_mode="student_p")
+        for t in (t1, t2):
+            await t.begin()
+        for s in (s_math, s_other):
+            await opd.opd_reward(args, s)
+        for t in (t1, t2):
+            await t.finish()
+
+    asyncio.run(go())
+    assert s_math.teacher_log_probs != s_other.teacher_log_probs                   # two different teachers answered
+    # top-k scoring: the teacher's k most likely tokens per response position, sorted, log-probs of a distribution
+    asyncio.run(go(k=4))
+    req = e1.add_request(s_math.tokens, {"temperature": 0.0, "max_new_tokens": 1}, logprob_start_len=4, top_logprobs_num=4)
+    while not req.done.is_set():
+        e1.step()
+    meta = req.to_response(e1)["meta_info"]
+    tops = meta["input_top_logprobs"]
+    assert len(tops) == 3 and all(len(row) == 4 and row[0][0] >= row[-1][0] for row in tops)
+    assert all(abs(tops[j][0][0]) < 20 and meta["input_token_logprobs"][j][0] <= tops[j][0][0] + 1e-6 for j in range(3))
+    assert len(s_math.opd_reverse_kl) == 3                                          # only-teacher: computed without student lists
+    # strategies on a hand-made position
+    st, te = {1: -0.2, 2: -2.0}, {1: -0.5, 3: -1.0}
+    assert opd.set_reverse_kl(st, te, "intersection") == pytest.approx(0.0)          # one shared token: both renormalise to 1
+    assert opd.set_reverse_kl(st, te, "only-student") > 0 and opd.set_reverse_kl(st, te, "union", "teacher_p") != 0
+    assert opd.set_reverse_kl(st, te, "xor", "none") == pytest.approx(((-2.0 - -1.0) + (-2.0 - -1.0)) / 2)
+    with pytest.raises(ValueError):
+        opd.set_reverse_kl(st, te, "nearest")
+    # --opd-type megatron: the trainer scores with a second set of weights loaded from a checkpoint
+    import os
+    import sys
+
+    sys.path.insert(0, os.path.dirname(os.path.abspath(__file__)))
+    from test_e2e import BASE, _run
+    from miles_b200.args import parse_args
+
+    ck = str(tmp_path / "teacher")
+    _run(f"--num-rollout 1 --save {ck} --save-interval 1 --seed 77")
+    with pytest.raises(ValueError):
+        parse_args((BASE + " --use-opd").split())
+    h = _run(f"--use-opd --opd-type megatron --opd-teacher-load {ck} --opd-teacher-ckpt-step 0 --opd-kl-coef 0.5 --num-rollout 1")
+    assert "perf/teacher_log_probs_time" in h.rows[0] and h.series("train/grad_norm")[0] > 0

@@ -75,7 +75,7 @@ def test_linear_autograd():
     assert _rel(x.grad, xr.grad) < 1e-2 and _rel(w.grad, wr.grad) < 1e-2
 
 
-@pytest.mark.parametrize("T,H", [(1, 1024), (513, 2048), (300, 2560), (64, 5120)])
+@pytest.mark.parametrize("T,H", [(1, 1024), (513, 2048), (300, 2560), (64, 5120), (70, 1024), (65, 4096), (63, 2048)])
 def test_rmsnorm_fwd_bwd(T, H):
     torch.manual_seed(3)
     x = torch.randn(T, H, device="cuda", dtype=torch.bfloat16, requires_grad=True)
