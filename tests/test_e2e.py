@@ -210,3 +210,44 @@ def test_staleness_buffer_policies():
     s = SubmissionScheduler(batch=8, max_inflight=12, target_buffered=8)
     assert s.allowance(inflight=0, buffered=0) == 12 and s.allowance(inflight=4, buffered=8) == 4
     assert s.allowance(inflight=12, buffered=0) == 0
+
+
+# ---- supervised fine-tuning through the same loop ---------------------------------------------------------------------
+
+class ChatSource:
+    """A data source of two-turn conversations over the byte tokenizer."""
+
+    def __init__(self, args, tokenizer=None):
+        from miles_b200.session.tito import ByteChatTokenizer
+
+        self.tokenizer = ByteChatTokenizer()
+        self.i = 0
+
+    def get_samples(self, n):
+        from miles_b200.types import Sample
+
+        out = []
+        for _ in range(n):
+            self.i += 1
+            out.append([Sample(prompt=[{"role": "user", "content": f"say {self.i % 3}"}, {"role": "assistant", "content": "ok " * (1 + self.i % 2)}])])
+        return out
+
+    def add_samples(self, groups):
+        pass
+
+    def save(self, rollout_id):
+        pass
+
+    def load(self, rollout_id=None):
+        pass
+
+    def __len__(self):
+        return 0
+
+
+def test_sft_loss_goes_down():
+    h = _run("--loss-type sft_loss --rollout-function-path miles_b200.rollout.sft_rollout.SftRolloutFn --tito-model qwen3 "
+             "--data-source-path test_e2e.ChatSource --n-samples-per-prompt 1 --rollout-batch-size 8 --global-batch-size 8 "
+             "--disable-compute-advantages-and-returns --lr 3e-3 --num-rollout 6")
+    losses = h.series("train/sft_loss")
+    assert len(losses) == 6 and losses[-1] < 0.6 * losses[0], losses

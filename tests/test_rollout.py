@@ -113,3 +113,71 @@ def test_native_runtime_allocator_and_router_core():
     assert 1 not in {core.pick("round_robin") for _ in range(6)}
     k = core.pick("consistent_hashing", "session-a")
     assert all(core.pick("consistent_hashing", "session-a") == k for _ in range(4))
+
+
+def test_sft_rollout_masks_assistant_turns_only(tmp_path):
+    """Multi-turn conversations → token ids + a loss mask that is 1 exactly on what the assistant produced (content and
+    end-of-turn token), for a ChatML-style family and for one that ends turns with the next role tag."""
+    import json
+    from types import SimpleNamespace
+
+    from miles_b200.rollout.inference_rollout import RolloutFnTrainInput
+    from miles_b200.rollout.sft_rollout import SftRolloutFn, conversation_tokens_and_mask
+    from miles_b200.session.tito import ByteChatTokenizer, TitoTokenizer
+    from miles_b200.types import Sample
+
+    tok = ByteChatTokenizer()
+    tito = TitoTokenizer(tok, "qwen3")
+    msgs = [{"role": "system", "content": "sys"}, {"role": "user", "content": "q1"}, {"role": "assistant", "content": "a1"},
+            {"role": "tool", "content": "t"}, {"role": "assistant", "content": "a2"}]
+    ids, mask = conversation_tokens_and_mask(tito, msgs)
+    assert ids == tito.encode(tito.render(msgs))                              # the pieces add up to the rendered conversation
+    trained = tok.decode([t for t, m in zip(ids, mask) if m])
+    assert trained == "a1<|im_end|>a2<|im_end|>"
+    glm = TitoTokenizer(ByteChatTokenizer(["[gMASK]", "<sop>", "<|system|>", "<|user|>", "<|assistant|>", "<|observation|>"]), "glm47")
+    ids2, mask2 = conversation_tokens_and_mask(glm, msgs[1:3])
+    assert glm.tok.decode([t for t, m in zip(ids2, mask2) if m]) == "a1<|user|>"       # the turn ends by emitting the next role tag
+
+    class Source:
+        tokenizer = tok
+
+        def get_samples(self, n):
+            return [[Sample(prompt=msgs)], [Sample(prompt="what?", label="that")], [Sample(prompt=[{"role": "user", "content": "no answer"}])]][:n]
+
+    fn = SftRolloutFn(SimpleNamespace(rollout_batch_size=3, tito_model="qwen3", rollout_max_context_len=None), Source())
+    out = fn(RolloutFnTrainInput(0))
+    assert len(out.samples) == 2 and out.metrics["rollout/sft_dropped"] == 1.0   # a conversation without an assistant turn trains nothing
+    s = out.samples[0][0]
+    assert len(s.loss_mask) == s.response_length and s.loss_mask[0] == 1 and sum(s.loss_mask) == len(tok("a1<|im_end|>a2<|im_end|>")["input_ids"])
+    s2 = out.samples[1][0]
+    assert tok.decode(s2.tokens[-s2.response_length:]).startswith("that<|im_end|>")
+    del json
+
+
+def test_recipes_build_commands_that_parse():
+    """Every launch recipe yields an argument list the trainer's parser accepts; run.py prints the torchrun command."""
+    import io
+    import os
+    import sys
+    from contextlib import redirect_stdout
+
+    sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+    import run
+    from miles_b200 import recipes
+    from miles_b200.args import parse_args
+
+    for name in recipes.RECIPES:
+        for mode in ("normal", "debug_minimal", "debug_one_sample"):
+            r = recipes.build(name, recipes.Knobs(num_gpus=8, mode=mode, dynamic_sampling=True, use_kl_loss=True))
+            a = parse_args(r.args)
+            assert a.rollout_batch_size >= 1 and os.path.exists(os.path.join(os.path.dirname(run.__file__), r.entry)), name
+    a = parse_args(recipes.build("qwen3-30b-a3b", recipes.Knobs(num_gpus=8, mxfp8=True)).args)
+    assert a.expert_model_parallel_size == 8 and a.fp8_recipe == "mxfp8" and a.max_tokens_per_gpu == 32768 and a.use_rollout_routing_replay
+    buf = io.StringIO()
+    with redirect_stdout(buf):
+        assert run.main(["qwen3-4b", "--num-gpus", "4", "--mode", "debug_minimal", "--dry-run", "--", "--lr", "3e-6"]) == 0
+    cmd = buf.getvalue()
+    assert "--nproc-per-node=4" in cmd and "train.py" in cmd and cmd.rstrip().endswith("--lr 3e-6")
+    with redirect_stdout(io.StringIO()) as b2:
+        run.main(["list"])
+    assert "qwen3-235b-a22b" in b2.getvalue()
