@@ -61,6 +61,9 @@ class Request:
     top_logprobs_num: int = 0      # > 0 with scoring: also the k most likely tokens (and their log-probs) at every scored position
     input_top_logprobs: list | None = None
     leader: Any = None             # request of the same prefill batch with identical tokens whose prompt KV this one shares
+    cache_nodes: list = field(default_factory=list)   # prefix-cache nodes this request pins (their blocks head its block table)
+    prefill_pos: int = 0           # tokens whose KV is in place (cached prefix + chunks already run); < len(all_ids) while prefilling
+    chunk: tuple = (0, 0)          # token range [start, end) the next prefill step computes
     cached_tokens: int = 0         # prompt tokens whose KV was shared instead of recomputed
 
     @property
@@ -105,7 +108,8 @@ class Engine:
                  mem_fraction_static: float = 0.7, max_running_requests: int = 512, max_prefill_tokens: int = 16384,
                  max_context_len: int | None = None, eos_token_ids: list[int] | None = None, tokenizer=None,
                  seed: int = 0, use_cuda_graph: bool = True, record_routing: bool | None = None,
-                 share_prompt_kv: bool = True, decode_steps_per_sync: int = 8):
+                 share_prompt_kv: bool = True, decode_steps_per_sync: int = 8, prefix_cache: bool = True,
+                 chunked_prefill_size: int | None = None):
         self.cfg = cfg
         self.ps = ps or ParallelState.single()
         self.device = torch.device(device)
@@ -143,6 +147,16 @@ class Engine:
         self.kv = KVCache(hi - lo, num_blocks, self.block_size, hkv, cfg.head_dim, dtype, self.device,
                           layer_ids=list(range(lo, hi)))
         self.allocator = make_allocator(num_blocks)
+        self.stateless = not getattr(self.model, "supports_kv_cache", True)
+        # full KV blocks of finished prefills and finished requests stay in a block-granular radix tree: a later prompt that
+        # starts with the same tokens (the next turn of a conversation, another sample of a prompt) computes only the rest
+        from .prefix_cache import PrefixCache
+
+        self.prefix_cache = PrefixCache(self.allocator, self.block_size) if (prefix_cache and not self.stateless) else None
+        # prompts longer than this many new tokens are prefilled in pieces, one per step, each attending to the KV of the
+        # pieces before it through the paged cache (None: a prompt is always one piece)
+        self.chunked_prefill_size = int(chunked_prefill_size) if chunked_prefill_size else None
+        self.prefilling: list[Request] = []          # requests between their first and last prefill piece (they hold blocks)
         self.waiting: deque[Request] = deque()
         self.running: list[Request] = []
         self.requests: dict[str, Request] = {}
@@ -168,7 +182,6 @@ class Engine:
         self._agreed_bucket = 0
         # models whose mixers keep no paged KV (latent / linear attention of the other families) are served by scoring the
         # whole sequence again every step: correct for any block, quadratic in length — the functional path for those families
-        self.stateless = not getattr(self.model, "supports_kv_cache", True)
         if self.device.type == "cuda" and dtype == torch.bfloat16 and not self.stateless:
             from .decode_runner import DecodeRunner
 
@@ -233,7 +246,7 @@ class Engine:
                 if not self.step():
                     if self.paused:
                         time.sleep(0.001)
-                    elif not self.waiting and not self.running:
+                    elif not self.waiting and not self.running and not self.prefilling:
                         break
         else:
             for r in reqs:
@@ -252,7 +265,7 @@ class Engine:
             if mode == "abort":
                 self.abort_request(None)
             elif mode == "retract":
-                for r in list(self.running):
+                for r in list(self.running) + list(self.prefilling):
                     self._retract(r)
 
     def continue_generation(self):
@@ -261,12 +274,36 @@ class Engine:
 
     def flush_cache(self) -> bool:
         with self.lock:
-            if self.running:
+            if self.running or self.prefilling:
                 return False
+            if self.prefix_cache is not None:
+                self.prefix_cache.reset()
             self.allocator.reset()
             return True
 
+    def _cacheable(self, r: "Request") -> bool:
+        """Requests whose prefix KV may come from / go to the prefix cache: plain generation.  Scoring requests need the
+        hidden states of every prompt position, recorded routing needs every position's expert choice — both are computed
+        only by running the whole prompt."""
+        return self.prefix_cache is not None and r.logprob_start_len < 0 and not r.return_routed_experts
+
+    def _invalidate_prefix_cache(self):
+        """Cached KV belongs to the weights that computed it."""
+        if self.prefix_cache is not None:
+            self.prefix_cache.reset()
+
+    def _alloc_blocks(self, n: int):
+        """Allocate, evicting unpinned cached prefixes (least recently used first) when the free list is short."""
+        if n > self.allocator.num_free and self.prefix_cache is not None:
+            self.prefix_cache.evict(n - self.allocator.num_free)
+        return self.allocator.alloc(n) if n > 0 else []
+
+    def _free_blocks(self) -> int:
+        return self.allocator.num_free + (self.prefix_cache.evictable() if self.prefix_cache is not None else 0)
+
     def update_weight_version(self, version: int):
+        if int(version) != self.weight_version:
+            self._invalidate_prefix_cache()
         self.weight_version = int(version)
 
     def get_weight_version(self) -> int:
@@ -279,6 +316,7 @@ class Engine:
 
         with self.lock:
             load_named_into_model(self.model, named_tensors, self.cfg, self.ps)
+            self._invalidate_prefix_cache()
             if weight_version is not None:
                 self.weight_version = int(weight_version)
         return {"success": True}
@@ -303,6 +341,7 @@ class Engine:
             else:
                 named = hf_io.load_hf_dir(model_path).items()
             load_named_into_model(self.model, named, self.cfg, self.ps)
+            self._invalidate_prefix_cache()
             if weight_version is not None:
                 self.weight_version = int(weight_version)
         return {"success": True}
@@ -363,8 +402,9 @@ class Engine:
                 self.kv.allocate()
 
     def health(self) -> dict:
-        return {"status": "ok", "running": len(self.running), "waiting": len(self.waiting),
-                "free_blocks": self.allocator.num_free, "weight_version": self.weight_version, "paused": self.paused}
+        return {"status": "ok", "running": len(self.running), "waiting": len(self.waiting), "prefilling": len(self.prefilling),
+                "free_blocks": self.allocator.num_free, "weight_version": self.weight_version, "paused": self.paused,
+                "cached_blocks": self.prefix_cache.num_nodes if self.prefix_cache is not None else 0}
 
     # ---------------------------------------------------------------------------------------
     # background loop (server mode)
@@ -400,7 +440,18 @@ class Engine:
         r.finish_reason = reason
         if self.runner is not None:
             self.runner.detach(r)
+        if r in self.prefilling:
+            self.prefilling.remove(r)
         if r.blocks:
+            if self.prefix_cache is not None and self._cacheable(r) and reason.get("type") != "abort":
+                # every position but the last sampled token has its KV written: the next turn of this conversation starts here
+                n_kv = len(r.all_ids) - 1 if r.num_cached else r.prefill_pos       # num_cached > 0: the prefill completed
+                full = max(0, n_kv) // self.block_size
+                if full:
+                    self.prefix_cache.insert(r.all_ids[: full * self.block_size], r.blocks[:full])
+            if self.prefix_cache is not None and r.cache_nodes:
+                self.prefix_cache.unpin(r.cache_nodes)
+                r.cache_nodes = []
             self.allocator.release(r.blocks)
             r.blocks = []
         self.requests.pop(r.rid, None)
@@ -410,9 +461,14 @@ class Engine:
 
     def _retract(self, r: Request):
         """Give the blocks back; the request restarts from a prefill of prompt+output."""
+        if self.prefix_cache is not None and r.cache_nodes:
+            self.prefix_cache.unpin(r.cache_nodes)
+            r.cache_nodes = []
         if r.blocks:
             self.allocator.release(r.blocks)
-        r.blocks, r.num_cached = [], 0
+        r.blocks, r.num_cached, r.prefill_pos = [], 0, 0
+        if r in self.prefilling:
+            self.prefilling.remove(r)
         r.retractions += 1
         if self.runner is not None:
             self.runner.detach(r)
@@ -537,7 +593,24 @@ class Engine:
         self.local_done = True
 
     def _schedule_prefill(self) -> list[Request]:
+        """Requests (each with the token range `chunk` it computes this step) for one prefill batch of at most
+        `max_prefill_tokens` new tokens: first the next pieces of prompts that are mid-prefill, then newly admitted ones.
+        A new request takes its longest cached prefix from the prefix cache; identical prompts of one batch share the
+        first one's KV; with chunked prefill a prompt that does not fit the rest of the budget takes what is left."""
         batch, tokens = [], 0
+        bs = self.block_size
+        budget = self.max_prefill_tokens
+        piece = self.chunked_prefill_size
+        for r in self.prefilling:
+            n = len(r.all_ids)
+            take = min(n - r.prefill_pos, piece or n, max(budget - tokens, 0) if batch else (piece or n))
+            if take <= 0:
+                break
+            r.chunk = (r.prefill_pos, r.prefill_pos + take)
+            tokens += take
+            batch.append(r)
+        if len(batch) < len(self.prefilling):
+            return batch                               # no room for newcomers while earlier prompts still wait for their pieces
         leaders: dict[tuple, Request] = {}
         share = self.share_prompt_kv and not self.stateless
         while self.waiting and len(self.running) + len(batch) < self.max_running:
@@ -551,15 +624,26 @@ class Engine:
                 if lead is not None and lead.all_ids != r.all_ids:
                     lead = None
             need = self._blocks_needed(n + 1)
-            shared = (n // self.block_size) if lead is not None else 0      # full blocks of the leader's prompt
-            if lead is None and batch and tokens + n > self.max_prefill_tokens:
-                break
+            shared = (n // bs) if lead is not None else 0                  # full blocks of the leader's prompt
+            hit = self.prefix_cache.match(r.all_ids, (n - 1) // bs) if (lead is None and self._cacheable(r)) else []
+            cached = len(hit) * bs
+            new_tokens = n - cached
+            room = budget - tokens
+            chunkable = piece is not None and lead is None and r.logprob_start_len < 0 and not self.stateless
+            if chunkable:
+                take = min(new_tokens, piece, room) if batch else min(new_tokens, piece)
+                if take < new_tokens and take < bs:
+                    break                              # not worth a piece smaller than a block: next step
+            else:
+                take = new_tokens
+                if lead is None and batch and tokens + new_tokens > budget:
+                    break
             # keep headroom so running requests can still grow by one block each
-            if (need - shared) + len(self.running) > self.allocator.num_free and (self.running or batch):
+            if (need - shared - len(hit)) + len(self.running) > self._free_blocks() and (self.running or batch):
                 break
-            blocks = self.allocator.alloc(need - shared)
+            blocks = self._alloc_blocks(need - shared - len(hit))
             if blocks is None:
-                if not self.running and not batch:
+                if not self.running and not batch and not self.prefilling:
                     self.waiting.popleft()
                     self._finish(r, {"type": "abort", "message": "prompt does not fit in the KV cache"})
                     continue
@@ -570,12 +654,19 @@ class Engine:
                 r.blocks = lead.blocks[:shared] + blocks
                 r.leader = lead
                 r.cached_tokens = n
+                r.chunk = (n, n)
             else:
-                r.blocks = blocks
+                if hit:
+                    r.cache_nodes = self.prefix_cache.acquire(r.all_ids, len(hit))      # pins the nodes, takes this request's references
+                    self.stats["prefix_cache_hit_tokens"] = self.stats.get("prefix_cache_hit_tokens", 0) + cached
+                r.blocks = [nd.block for nd in r.cache_nodes] + blocks
                 r.leader = None
-                tokens += n
-                if key is not None:
-                    leaders[key] = r
+                r.cached_tokens = cached
+                r.prefill_pos = cached
+                r.chunk = (cached, cached + take)
+                tokens += take
+                if key is not None and cached + take == n:
+                    leaders[key] = r                   # only a prompt that completes in this batch can lend its KV
             batch.append(r)
         return batch
 
@@ -594,10 +685,10 @@ class Engine:
         bs = self.block_size
         while True:
             need = {id(r): max(0, self._blocks_needed(len(r.all_ids) + lookahead) - len(r.blocks)) for r in self.running}
-            if sum(need.values()) <= self.allocator.num_free:
+            if sum(need.values()) <= self._free_blocks():
                 for r in self.running:
                     if need[id(r)]:
-                        r.blocks += self.allocator.alloc(need[id(r)])
+                        r.blocks += self._alloc_blocks(need[id(r)])
                 return True
             victim = max(self.running, key=lambda r: r.arrival)
             self._retract(victim)
@@ -649,35 +740,57 @@ class Engine:
         return total
 
     def _run_prefill(self, batch: list[Request]):
-        """Prefill the unique sequences of the batch; followers (identical tokens, see `_schedule_prefill`) take their
-        leader's prompt KV — shared full blocks, a copy of the partial last block — and its last-position logits."""
+        """Run the pieces scheduled by `_schedule_prefill`.  When every piece is a whole prompt starting from an empty cache
+        the batch attends within its own tokens (packed variable-length attention); otherwise (a cached prefix, a later
+        piece of a chunked prompt) the new tokens attend to their request's paged KV, which holds the earlier positions.
+        Followers (identical tokens) take their leader's prompt KV — shared full blocks, a copy of the partial last block —
+        and its last-position logits.  Requests whose prompt is complete after this step sample their first token."""
         lead_reqs = [r for r in batch if r.leader is None]
         toks, pos, slots, cu = [], [], [], [0]
         for r in lead_reqs:
+            a, b = r.chunk
             ids = r.all_ids
-            toks += ids
-            pos += list(range(len(ids)))
-            slots += self._slots(r, 0, len(ids))
-            cu.append(cu[-1] + len(ids))
+            toks += ids[a:b]
+            pos += list(range(a, b))
+            slots += self._slots(r, a, b)
+            cu.append(cu[-1] + (b - a))
         dev = self.device
         record = [] if any(r.return_routed_experts for r in batch) else None
-        meta = ForwardMeta(
-            positions=torch.tensor(pos, dtype=torch.int32, device=dev),
-            cu_seqlens=torch.tensor(cu, dtype=torch.int32, device=dev),
-            max_seqlen=max((len(r.all_ids) for r in lead_reqs), default=0),
-            kv_cache=None if self.stateless else self.kv.layers,
-            slot_mapping=None if self.stateless else torch.tensor(slots, dtype=torch.int64, device=dev),
-            record_topk=record, lora_slots=self._lora_slots(len(toks)))
+        whole = all(r.chunk[0] == 0 for r in lead_reqs)
+        if whole or self.stateless:
+            meta = ForwardMeta(
+                positions=torch.tensor(pos, dtype=torch.int32, device=dev),
+                cu_seqlens=torch.tensor(cu, dtype=torch.int32, device=dev),
+                max_seqlen=max((r.chunk[1] for r in lead_reqs), default=0),
+                kv_cache=None if self.stateless else self.kv.layers,
+                slot_mapping=None if self.stateless else torch.tensor(slots, dtype=torch.int64, device=dev),
+                record_topk=record, lora_slots=self._lora_slots(len(toks)))
+        else:
+            # keys of request i: positions [0, end_i) read from its blocks; queries: its new tokens [start_i, end_i)
+            gather = []
+            cu_k = [0]
+            for r in lead_reqs:
+                gather += self._slots(r, 0, r.chunk[1])
+                cu_k.append(cu_k[-1] + r.chunk[1])
+            meta = ForwardMeta(
+                positions=torch.tensor(pos, dtype=torch.int32, device=dev), cu_seqlens=None,
+                max_seqlen=max((r.chunk[1] - r.chunk[0] for r in lead_reqs), default=0),
+                kv_cache=self.kv.layers, block_table=self._block_table(lead_reqs),
+                seq_lens=torch.tensor([r.chunk[1] for r in lead_reqs], dtype=torch.int32, device=dev),
+                q_lens=torch.tensor([r.chunk[1] - r.chunk[0] for r in lead_reqs], dtype=torch.int32, device=dev),
+                slot_mapping=torch.tensor(slots, dtype=torch.int64, device=dev),
+                record_topk=record, lora_slots=self._lora_slots(len(toks)))
+            meta.extend = {"cu_q": torch.tensor(cu, dtype=torch.int32, device=dev), "cu_k": torch.tensor(cu_k, dtype=torch.int32, device=dev),
+                           "kv_slots": torch.tensor(gather, dtype=torch.int64, device=dev),
+                           "max_k": max((r.chunk[1] for r in lead_reqs), default=0)}
+            self.stats["extend_tokens"] = self.stats.get("extend_tokens", 0) + len(toks)
         self.stats["h2d_bytes"] = self.stats.get("h2d_bytes", 0) + 4 * len(toks) * 2 + 4 * len(cu) + 8 * len(slots)
         hidden = self._dumped_forward(torch.tensor(toks, dtype=torch.int32, device=dev), meta)
         if not batch:
             return
         hidden = self.ps.sp_gather(hidden)
-        last = torch.tensor([c - 1 for c in cu[1:]], dtype=torch.int64, device=dev)
-        logits = self.model.logits(hidden[last])
         self.stats["prefill_tokens"] += len(toks)
         span = {id(r): (a, b) for r, a, b in zip(lead_reqs, cu[:-1], cu[1:])}
-        lead_row = {id(r): i for i, r in enumerate(lead_reqs)}
         for r, a, b in zip(lead_reqs, cu[:-1], cu[1:]):
             if r.logprob_start_len >= 0 and r.input_logprobs is None and r.retractions == 0:
                 # score the prompt: row p predicts token p+1 (temperature 1, the teacher / reference distribution)
@@ -692,7 +805,7 @@ class Engine:
                     for c0 in range(0, rows.numel(), 512):          # full-vocabulary rows, 512 at a time
                         lg = torch.log_softmax(self.model.logits(hidden[rows[c0:c0 + 512]]).float(), dim=-1)
                         v, i = lg.topk(min(r.top_logprobs_num, lg.shape[-1]), dim=-1)
-                        tops += [[(float(a), int(b), None) for a, b in zip(vr, ir)] for vr, ir in zip(v.tolist(), i.tolist())]
+                        tops += [[(float(x), int(y), None) for x, y in zip(vr, ir)] for vr, ir in zip(v.tolist(), i.tolist())]
                     r.input_top_logprobs = tops
         followers = [r for r in batch if r.leader is not None]
         if followers:
@@ -703,19 +816,46 @@ class Engine:
             self.stats["d2h_bytes"] = self.stats.get("d2h_bytes", 0) + rec.nbytes
             for r in batch:
                 if r.return_routed_experts:
-                    a, b = span[id(r.leader if r.leader is not None else r)]
-                    # after a retraction the request already holds rows for its first num-recorded tokens
+                    src = r.leader if r.leader is not None else r
+                    a, b = span[id(src)]
+                    start = src.chunk[0]
+                    # rows [a, b) are tokens [start, end); after a retraction the request already holds its first `have` rows
                     have = sum(x.shape[0] for x in r.routed)
-                    r.routed.append(rec[a + have:b])
-        for r in batch:
+                    r.routed.append(rec[a + max(have - start, 0):b])
+        done, lead_row = [], {}
+        for i, r in enumerate(lead_reqs):
+            r.prefill_pos = r.chunk[1]
+            if r.prefill_pos >= len(r.all_ids):
+                lead_row[id(r)] = len(done)
+                done.append(i)
+                if r in self.prefilling:
+                    self.prefilling.remove(r)
+                if self._cacheable(r):
+                    full = len(r.all_ids) // self.block_size
+                    if full:
+                        # the request goes on using these blocks: pin the nodes that own them until it finishes
+                        held = set(map(id, r.cache_nodes))
+                        fresh = [nd for nd in self.prefix_cache.insert(r.all_ids[: full * self.block_size], r.blocks[:full])
+                                 if id(nd) not in held]
+                        self.prefix_cache.pin(fresh)
+                        r.cache_nodes = r.cache_nodes + fresh
+            elif r not in self.prefilling:
+                self.prefilling.append(r)
+        finished_batch = [r for r in batch if (r.leader if r.leader is not None else r).prefill_pos >= len(r.all_ids)]
+        if not finished_batch:
+            return
+        last = torch.tensor([cu[i + 1] - 1 for i in done], dtype=torch.int64, device=dev)
+        logits = self.model.logits(hidden[last])
+        for r in finished_batch:
             r.num_cached = len(r.all_ids)
-        if followers:
-            rows = torch.tensor([lead_row[id(r.leader if r.leader is not None else r)] for r in batch], dtype=torch.int64, device=dev)
+            r.prefill_pos = len(r.all_ids)
+        if followers or len(done) != len(finished_batch):
+            rows = torch.tensor([lead_row[id(r.leader if r.leader is not None else r)] for r in finished_batch], dtype=torch.int64, device=dev)
             logits = logits[rows]
         for r in batch:
             r.leader = None
-        self._sample_and_append(batch, logits)
-        for r in batch:
+        self._sample_and_append(finished_batch, logits)
+        for r in finished_batch:
             if not r.finished and r not in self.running:
                 self.running.append(r)
                 if self.runner is not None:

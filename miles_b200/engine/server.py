@@ -275,10 +275,13 @@ def main():
     p.add_argument("--mem-fraction-static", type=float, default=0.7)
     p.add_argument("--max-running-requests", type=int, default=256)
     p.add_argument("--device", default="cuda" if torch.cuda.is_available() else "cpu")
+    p.add_argument("--disable-radix-cache", action="store_true", help="do not reuse KV across requests with a common prefix")
+    p.add_argument("--chunked-prefill-size", type=int, default=0, help="prefill long prompts in pieces of this many tokens (0: whole)")
     a = p.parse_args()
     cfg = get_config(a.hf_checkpoint or a.model_name)
     dtype = torch.bfloat16 if a.device.startswith("cuda") else torch.float32
-    eng = Engine(cfg, device=a.device, dtype=dtype, mem_fraction_static=a.mem_fraction_static, max_running_requests=a.max_running_requests)
+    eng = Engine(cfg, device=a.device, dtype=dtype, mem_fraction_static=a.mem_fraction_static, max_running_requests=a.max_running_requests,
+                 prefix_cache=not a.disable_radix_cache, chunked_prefill_size=a.chunked_prefill_size or None)
     if a.hf_checkpoint:
         eng.update_weights_from_disk(a.hf_checkpoint)
     serve(eng, a.host, a.port)

@@ -44,6 +44,9 @@ class ForwardMeta:
     record_topk: "list[torch.Tensor] | None" = None  # filled with int32 [T,k] per MoE layer when not None
     recompute: bool = False                  # activation checkpoint each layer
     lora_slots: torch.Tensor | None = None   # int64 [T] adapter slot per token (None → slot 0; -1 → base model only)
+    # prefill that continues cached KV (a prefix-cache hit, a later piece of a chunked prompt): packed offsets of the new
+    # tokens (cu_q) and of every request's keys (cu_k), flat cache slots of those keys (kv_slots), longest key sequence (max_k)
+    extend: "dict | None" = None
 
 
 class _Init:
@@ -126,7 +129,7 @@ class Attention(nn.Module):
         else:
             kc, vc = meta.kv_cache[layer]
             o = ops.paged_attention(q, kc, vc, meta.block_table, meta.seq_lens, q_lens=meta.q_lens,
-                                    max_q_len=meta.max_seqlen)
+                                    max_q_len=meta.max_seqlen, extend=meta.extend)
         o = o.reshape(T, self.hq * self.d)
         if lora is None and self.ps.defer_allreduce(o):
             return self.ps.row_linear_partial(o, self.wo)             # reduced inside the next add + RMSNorm kernel

@@ -159,9 +159,9 @@ def kv_cache_write(k, v, k_cache, v_cache, slot_mapping):
     vc[slot_mapping.long()] = v.detach().to(vc.dtype)
 
 
-def paged_attention(q, k_cache, v_cache, block_table, seq_lens, q_lens=None, max_q_len=1):
+def paged_attention(q, k_cache, v_cache, block_table, seq_lens, q_lens=None, max_q_len=1, extend=None):
     if q.is_cuda:
-        return _k().paged_attention(q, k_cache, v_cache, block_table, seq_lens, q_lens, max_q_len)
+        return _k().paged_attention(q, k_cache, v_cache, block_table, seq_lens, q_lens, max_q_len, extend)
     return ref.paged_attention(q, k_cache, v_cache, block_table, seq_lens, q_lens=q_lens)
 
 

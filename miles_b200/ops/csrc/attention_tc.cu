@@ -32,6 +32,9 @@ struct Params {
   __nv_bfloat16* o;
   float* lse;
   const int* cu_seqlens;
+  const int* cu_seqlens_k;     // null: keys are the queries' own sequences.  Else sequence b has keys [cu_k[b], cu_k[b+1]) and, under
+                               // the causal mask, query i sees keys ≤ i + (Lk − Lq): the queries are the LAST Lq positions of the keys
+                               // (a prompt continued after a cached prefix, a later chunk of a long prompt)
   int Hq, Hkv, total_tokens;
   float scale;
   int causal;
@@ -71,12 +74,16 @@ flash_fwd_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int b = blockIdx.z, h = blockIdx.y;
   const int seq_start = p.cu_seqlens[b], L = p.cu_seqlens[b + 1] - seq_start;
+  const int k_start = p.cu_seqlens_k != nullptr ? p.cu_seqlens_k[b] : seq_start;
+  const int Lk = p.cu_seqlens_k != nullptr ? p.cu_seqlens_k[b + 1] - k_start : L;
+  const int off = Lk - L;                             // causal diagonal shift (0 when keys and queries coincide)
   const int qb = gridDim.x - 1 - blockIdx.x;          // long (late) query blocks first
   const int q0 = qb * BQ;
   if (q0 >= L) return;
   const int hk = h / (p.Hq / p.Hkv);
-  const int kv_end = p.causal ? min(L, q0 + BQ) : L;
+  const int kv_end = p.causal ? max(0, min(Lk, q0 + BQ + off)) : Lk;
   const int n_blocks = (kv_end + BKV - 1) / BKV;
+  if (n_blocks <= 0) return;                          // only with fewer keys than queries (callers keep Lk ≥ Lq): nothing to attend to
 
   if (threadIdx.x == 0) {
     mbar_init(q_full, 1);
@@ -110,7 +117,7 @@ flash_fwd_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
       tma_load_2d(smem + Smem::q + kQAtom, &tm_q, q_full, h * D + 64, seq_start + q0);
       for (int j = 0; j < n_blocks && !*abort_flag; ++j) {
         const int st = j & 1;
-        const int row = seq_start + j * BKV;
+        const int row = k_start + j * BKV;
         if (!mbar_wait(&k_empty[st], ((j >> 1) & 1) ^ 1)) { *abort_flag = 1; atomicExch(p.error_flag, 21); break; }
         mbar_expect_tx(&k_full[st], kKVBytes);
         uint8_t* sk = smem + Smem::k + st * kKVBytes;
@@ -178,7 +185,7 @@ flash_fwd_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
       if (!mbar_wait(&s_full[st], (j >> 1) & 1)) { ok = false; break; }
       tc_fence_after();
       const int kv0 = j * BKV;
-      const bool need_mask = (kv0 + BKV > L) || (p.causal && kv0 + BKV > q0);
+      const bool need_mask = (kv0 + BKV > Lk) || (p.causal && kv0 + BKV > q0 + off);
       uint32_t s[2][32];
       tmem_ld_32x32(tmem + lane_off + st * BKV, s[0]);
       tmem_ld_32x32(tmem + lane_off + st * BKV + 32, s[1]);
@@ -194,7 +201,7 @@ flash_fwd_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
           float v = __uint_as_float(s[c][i]);
           if (need_mask) {
             const int col = kv0 + c * 32 + i;
-            if (col >= L || (p.causal && col > qpos)) v = -INFINITY;
+            if (col >= Lk || (p.causal && col > qpos + off)) v = -INFINITY;
             s[c][i] = __float_as_uint(v);
           }
           mx4[i & 3] = fmaxf(mx4[i & 3], v);
@@ -306,16 +313,19 @@ extern "C" int mb_flash_fwd_tc_ctas_per_sm() {
 }
 
 // q [T, Hq, 128] (token stride q_stride elements), k/v [T, Hkv, 128]; o [T, Hq, 128] contiguous; lse [Hq, T].
+// cu_seqlens_k / total_k_tokens: optional separate key sequences (null / 0: the queries' own), see Params.
 extern "C" int mb_flash_fwd_tc(const void* q, const void* k, const void* v, void* o, float* lse, const int* cu_seqlens, int batch,
                                int max_seqlen, int total_tokens, long long q_stride, long long k_stride, long long v_stride, int Hq,
-                               int Hkv, float scale, int causal, int* error_flag, cudaStream_t s) {
+                               int Hkv, float scale, int causal, int* error_flag, const int* cu_seqlens_k, int total_k_tokens,
+                               cudaStream_t s) {
   if (batch == 0 || total_tokens == 0 || max_seqlen == 0) return 0;
+  const int tk_rows = cu_seqlens_k != nullptr ? total_k_tokens : total_tokens;
   CUtensorMap tq, tk, tv;
   int rc = make_tmap_bf16_2d(&tq, q, total_tokens, static_cast<long long>(Hq) * fa::D, q_stride, fa::BQ, 64);
   if (rc) return 1000 + rc;
-  rc = make_tmap_bf16_2d(&tk, k, total_tokens, static_cast<long long>(Hkv) * fa::D, k_stride, fa::BKV, 64);
+  rc = make_tmap_bf16_2d(&tk, k, tk_rows, static_cast<long long>(Hkv) * fa::D, k_stride, fa::BKV, 64);
   if (rc) return 2000 + rc;
-  rc = make_tmap_bf16_2d(&tv, v, total_tokens, static_cast<long long>(Hkv) * fa::D, v_stride, fa::BKV, 64);
+  rc = make_tmap_bf16_2d(&tv, v, tk_rows, static_cast<long long>(Hkv) * fa::D, v_stride, fa::BKV, 64);
   if (rc) return 3000 + rc;
   static bool once = false;
   if (!once) {
@@ -326,7 +336,7 @@ extern "C" int mb_flash_fwd_tc(const void* q, const void* k, const void* v, void
     if (e != cudaSuccess) return static_cast<int>(e);
     once = true;
   }
-  fa::Params p{reinterpret_cast<__nv_bfloat16*>(o), lse, cu_seqlens, Hq, Hkv, total_tokens, scale, causal, error_flag};
+  fa::Params p{reinterpret_cast<__nv_bfloat16*>(o), lse, cu_seqlens, cu_seqlens_k, Hq, Hkv, total_tokens, scale, causal, error_flag};
   dim3 grid((max_seqlen + fa::BQ - 1) / fa::BQ, Hq, batch);
   fa::flash_fwd_tc_kernel<<<grid, 192, fa::Smem::total, s>>>(tq, tk, tv, p);
   return static_cast<int>(cudaGetLastError());

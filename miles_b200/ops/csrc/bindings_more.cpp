@@ -54,12 +54,14 @@ void flash_fwd(const at::Tensor& q, const at::Tensor& k, const at::Tensor& v, at
 }
 
 void flash_fwd_tc(const at::Tensor& q, const at::Tensor& k, const at::Tensor& v, at::Tensor& o, const c10::optional<at::Tensor>& lse,
-                  const at::Tensor& cu_seqlens, int64_t max_seqlen, double scale, bool causal, at::Tensor& err) {
+                  const at::Tensor& cu_seqlens, int64_t max_seqlen, double scale, bool causal, at::Tensor& err,
+                  const c10::optional<at::Tensor>& cu_seqlens_k) {
   c10::cuda::CUDAGuard g(q.device());
   const int64_t T = q.size(0), Hq = q.size(1), Hkv = k.size(1);
+  const int* cuk = cu_seqlens_k.has_value() ? cu_seqlens_k->data_ptr<int>() : nullptr;
   check(mb_flash_fwd_tc(q.data_ptr(), k.data_ptr(), v.data_ptr(), o.data_ptr(), fptr(lse), cu_seqlens.data_ptr<int>(),
                         cu_seqlens.numel() - 1, max_seqlen, T, q.stride(0), k.stride(0), v.stride(0), Hq, Hkv, scale, causal,
-                        err.data_ptr<int>(), cur_stream()),
+                        err.data_ptr<int>(), cuk, static_cast<int>(k.size(0)), cur_stream()),
         "mb_flash_fwd_tc");
 }
 

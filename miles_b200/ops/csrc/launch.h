@@ -96,7 +96,7 @@ int mb_paged_decode(const void* q, const void* kc, const void* vc, const int* bl
 // ---- attention_tc.cu (tcgen05 forward, head_dim 128) ----
 int mb_flash_fwd_tc(const void* q, const void* k, const void* v, void* o, float* lse, const int* cu_seqlens, int batch, int max_seqlen,
                     int total_tokens, long long q_stride, long long k_stride, long long v_stride, int Hq, int Hkv, float scale,
-                    int causal, int* error_flag, cudaStream_t s);
+                    int causal, int* error_flag, const int* cu_seqlens_k, int total_k_tokens, cudaStream_t s);
 int mb_flash_fwd_tc_ctas_per_sm(void);
 
 // ---- moe.cu ----

@@ -31,7 +31,7 @@ class _FlashAttn(torch.autograd.Function):
                 max_seqlen = int((cu_seqlens[1:] - cu_seqlens[:-1]).max().item())
             if D == 128 and USE_TC_ATTENTION and q.stride(0) % 8 == 0 and k.stride(0) % 8 == 0 and v.stride(0) % 8 == 0:
                 # tcgen05 forward (TMA-fed, accumulators in tensor memory)
-                C.flash_fwd_tc(q, k, v, o, lse, cu_seqlens, max_seqlen, scale, causal, C.error_flag(q))
+                C.flash_fwd_tc(q, k, v, o, lse, cu_seqlens, max_seqlen, scale, causal, C.error_flag(q), None)
             else:
                 C.flash_fwd(q, k, v, o, lse, cu_seqlens, max_seqlen, scale, causal)
         ctx.save_for_backward(q, k, v, o, lse, cu_seqlens)
@@ -65,9 +65,38 @@ def attention_varlen(q, k, v, cu_seqlens, max_seqlen=0, causal=True):
 _DECODE_SPLITS = int(os.environ.get("MILES_DECODE_SPLITS", "8"))   # KV splits per (request, kv head) in paged decode
 
 
-def paged_attention(q, k_cache, v_cache, block_table, seq_lens, q_lens=None, max_q_len=1):
-    """Decode (one new token per request) over the paged cache. Chunked prefill with a prefix is not a CUDA path."""
-    assert q_lens is None, "paged_attention on CUDA serves decode steps (q_len = 1)"
+def extend_attention(q, k_cache, v_cache, block_table, seq_lens, q_lens, extend=None):
+    """New tokens of each request attend to that request's whole paged KV (which already contains them): the keys and
+    values are gathered from the cache into packed buffers and the tcgen05 forward kernel runs with separate query and key
+    sequences — query i of a request sees keys ≤ i + (Lk − Lq)."""
+    T, Hq, D = q.shape
+    Hkv = k_cache.shape[2]
+    if extend is None:                       # callers outside the engine: build the description here (host round trip)
+        bs = k_cache.shape[1]
+        sl, ql = seq_lens.tolist(), q_lens.tolist()
+        slots = [int(block_table[b, p // bs]) * bs + p % bs for b, L in enumerate(sl) for p in range(L)]
+        cu_q = torch.tensor([0] + list(torch.tensor(ql).cumsum(0).tolist()), dtype=torch.int32, device=q.device)
+        cu_k = torch.tensor([0] + list(torch.tensor(sl).cumsum(0).tolist()), dtype=torch.int32, device=q.device)
+        extend = {"cu_q": cu_q, "cu_k": cu_k, "kv_slots": torch.tensor(slots, dtype=torch.int64, device=q.device), "max_k": max(sl)}
+    kk = k_cache.view(-1, Hkv, D).index_select(0, extend["kv_slots"])
+    vv = v_cache.view(-1, Hkv, D).index_select(0, extend["kv_slots"])
+    max_q = int(q_lens.max().item()) if "max_q" not in extend else extend["max_q"]
+    if q.dtype != BF16 or D != 128 or not USE_TC_ATTENTION:
+        return ref.paged_attention(q, k_cache, v_cache, block_table, seq_lens, q_lens=q_lens)
+    q = _c(q)
+    o = torch.empty(T, Hq, D, dtype=q.dtype, device=q.device)
+    lse = torch.empty(Hq, T, dtype=torch.float32, device=q.device)
+    C.flash_fwd_tc(q, kk, vv, o, lse, extend["cu_q"], max_q, 1.0 / math.sqrt(D), True, C.error_flag(q), extend["cu_k"])
+    return o
+
+
+def paged_attention(q, k_cache, v_cache, block_table, seq_lens, q_lens=None, max_q_len=1, extend=None):
+    """Decode (one new token per request) over the paged cache; with `q_lens` a prefill that continues cached KV
+    (`extend_attention`)."""
+    if q_lens is not None:
+        if extend is not None:
+            extend = dict(extend, max_q=int(max_q_len))
+        return extend_attention(q, k_cache, v_cache, block_table, seq_lens, q_lens, extend)
     B, Hq, D = q.shape
     group = Hq // k_cache.shape[2]
     if q.dtype != BF16 or D not in (64, 128) or group not in (1, 2, 4, 8):

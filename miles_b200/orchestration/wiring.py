@@ -197,7 +197,9 @@ def create_rollout_components(args, ps: ParallelState, actor=None, tracker=None)
                         max_running_requests=ek.get("max_running_requests", 512),
                         max_prefill_tokens=ek.get("max_prefill_tokens", 16384),
                         max_context_len=getattr(args, "rollout_max_context_len", None), eos_token_ids=eos, tokenizer=tok,
-                        seed=args.rollout_seed, use_cuda_graph=not ek.get("disable_cuda_graph", False))
+                        seed=args.rollout_seed, use_cuda_graph=not ek.get("disable_cuda_graph", False),
+                        prefix_cache=not ek.get("disable_radix_cache", False),
+                        chunked_prefill_size=(ek.get("chunked_prefill_size") if (ek.get("chunked_prefill_size") or 0) > 0 else None))
         engine.attach_dumper(getattr(actor, "dumper", None))
         engines = [engine]
         client = InProcEngineClient(engines, tokenizer=tok, policy=getattr(args, "router_policy", "least_active"))

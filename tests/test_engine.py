@@ -58,7 +58,7 @@ def test_continuous_batching_equals_one_by_one():
     solo = [eng.generate(p, sp)["output_ids"] for p in prompts]
     batch = [o["output_ids"] for o in eng.generate(prompts, sp)]
     assert solo == batch
-    assert eng.allocator.num_free == 64                                 # every block returned
+    assert eng._free_blocks() == 64                                     # every block returned (or held by the prefix cache only)
 
 
 def test_stop_tokens_and_eos():
@@ -176,7 +176,7 @@ def test_samples_of_one_prompt_share_prompt_kv(name, plen):
         while not all(r.done.is_set() for r in reqs):
             eng.step()
         res[share] = ([r.to_response(eng) for r in reqs], eng.stats["prefill_tokens"], used_after_prefill)
-        assert eng.allocator.num_free == free0                 # every reference was released
+        assert eng._free_blocks() == free0                     # every reference was released (the prefix cache holds the rest)
     (a, tok_a, used_a), (b, tok_b, used_b) = res[True], res[False]
     assert tok_a == plen + 3 + 5 and tok_b == 4 * plen + 2 * 3 + 5
     assert used_a < used_b
@@ -188,3 +188,88 @@ def test_samples_of_one_prompt_share_prompt_kv(name, plen):
     assert a[1]["meta_info"]["cached_tokens"] == plen and a[0]["meta_info"]["cached_tokens"] == 0
     # siblings really diverge (different seeds), so the shared blocks were not written by anyone's decode steps
     assert len({tuple(x["output_ids"]) for x in a[:4]}) > 1
+
+
+# ---- prefix (radix) cache and chunked prefill --------------------------------------------------------------------------
+
+def test_prefix_cache_tree_pins_and_evicts():
+    from miles_b200.engine.kv_cache import BlockAllocator
+    from miles_b200.engine.prefix_cache import PrefixCache
+
+    al = BlockAllocator(16)
+    pc = PrefixCache(al, 4)
+    a = al.alloc(3)
+    toks = list(range(12))
+    mine = pc.insert(toks, a)
+    assert [n.block for n in mine] == a and pc.num_nodes == 3
+    al.release(a)                                            # the request is gone; the tree keeps the blocks alive
+    assert al.num_free == 13 and pc.evictable() == 3
+    assert [n.block for n in pc.match(toks + [99])] == a
+    assert [n.block for n in pc.match(toks[:8] + [77, 78, 79, 80])] == a[:2]     # diverges in the third block
+    assert pc.match(toks, max_blocks=2)[-1].block == a[1]
+    got = pc.acquire(toks[:8])                               # a request takes the first two blocks
+    assert [n.users for n in got] == [1, 1] and pc.evictable() == 1               # only the unpinned leaf may go
+    b = al.alloc(1)
+    other = pc.insert(toks[:8] + [50, 51, 52, 53], [a[0], a[1], b[0]])            # a sibling branch below the shared prefix
+    assert len(other) == 3 and pc.num_nodes == 4
+    assert pc.evict(10) == 2 and pc.num_nodes == 2           # both leaves; the pinned chain stays
+    pc.unpin(got)
+    al.release([n.block for n in got])
+    al.release(b)
+    assert pc.evictable() == 2 and pc.evict(1) == 1          # leaf first: the tree never loses an inner node before its children
+    assert [n.block for n in pc.match(toks)] == a[:1]
+    assert pc.reset() == 1 and al.num_free == 16
+
+
+def _gen(eng, prompts, sps):
+    outs = eng.generate(prompts, sps)
+    return [(o["output_ids"], [round(x[0], 5) for x in o["meta_info"]["output_token_logprobs"]], o["meta_info"]["cached_tokens"]) for o in outs]
+
+
+@pytest.mark.parametrize("name", ["tiny", "tiny-moe"])
+def test_prefix_cache_and_chunked_prefill_keep_results(name):
+    """Multi-turn style prompts (each extends the previous conversation) through an engine with the prefix cache, and long
+    prompts through chunked prefill: same tokens and log-probs as an engine that recomputes everything in one piece."""
+    base = [3 + (i * 7) % 50 for i in range(37)]
+    turn2 = base + [60, 61, 62, 63, 64]
+    turn3 = turn2 + [70, 71] * 9
+    sp = {"temperature": 0.0, "max_new_tokens": 5}
+    plain = _engine(name, prefix_cache=False)
+    want = [_gen(plain, [p], [dict(sp)])[0] for p in (base, turn2, turn3, base)]
+    assert all(w[2] == 0 for w in want)
+    cached = _engine(name)
+    got = [_gen(cached, [p], [dict(sp)])[0] for p in (base, turn2, turn3, base)]
+    for w, g in zip(want, got):
+        assert w[0] == g[0] and max(abs(x - y) for x, y in zip(w[1], g[1])) < 1e-4
+    bs = cached.block_size
+    assert [g[2] for g in got] == [0, (len(base) // bs) * bs, (len(turn2) // bs) * bs, ((len(base) - 1) // bs) * bs]
+    assert cached.stats["prefix_cache_hit_tokens"] == sum(g[2] for g in got) and cached.stats["extend_tokens"] > 0
+    assert cached._free_blocks() == plain._free_blocks()
+    # generated tokens are cached too: a prompt that continues the model's own answer hits beyond the old prompt
+    cont = base + want[0][0] + [5, 6, 7]
+    assert _gen(cached, [cont], [dict(sp)])[0][2] >= ((len(base) + len(want[0][0]) - 1) // bs) * bs - bs
+    # a weight update invalidates the cache
+    cached.update_weight_version(3)
+    assert cached.prefix_cache.num_nodes == 0 and _gen(cached, [turn2], [dict(sp)])[0][2] == 0
+    # chunked prefill: pieces of 16 tokens, several requests in flight, mixed with short prompts
+    chunked = _engine(name, prefix_cache=False, chunked_prefill_size=16, max_prefill_tokens=24)
+    prompts = [turn3, [9, 8, 7], turn2, base[:20]]
+    sps = [{"temperature": 1.0, "max_new_tokens": 6, "seed": 11 + i} for i in range(4)]
+    w2 = _gen(plain, prompts, [dict(s) for s in sps])
+    g2 = _gen(chunked, prompts, [dict(s) for s in sps])
+    for w, g in zip(w2, g2):
+        assert w[0] == g[0] and max(abs(x - y) for x, y in zip(w[1], g[1])) < 1e-4
+    assert chunked.stats["extend_tokens"] > 0 and chunked._free_blocks() == plain._free_blocks()
+
+
+def test_eviction_under_pressure_keeps_serving():
+    """A cache that fills the pool gives blocks back (least recently used first) instead of failing or retracting."""
+    eng = _engine("tiny", num_blocks=24)
+    sp = {"temperature": 0.0, "max_new_tokens": 4}
+    outs = []
+    for i in range(12):
+        p = [5 + i] * 30 + [40 + i]
+        outs.append(eng.generate(p, dict(sp))["output_ids"])
+    assert eng.prefix_cache.stats["evicted_blocks"] > 0 and eng.stats["retractions"] == 0
+    again = eng.generate([5 + 11] * 30 + [40 + 11], dict(sp))
+    assert again["output_ids"] == outs[11] and again["meta_info"]["cached_tokens"] > 0

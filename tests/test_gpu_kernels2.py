@@ -266,3 +266,33 @@ def test_fused_weight_sync_kernels():
         payload, scales = eng3.quant_buffers[name]
         assert torch.equal(payload.view(torch.float8_e4m3fn).float().view(-1), qd.float().view(-1)), name
         assert torch.equal(scales.view(-1), sc.view(-1)), name
+
+
+@pytest.mark.parametrize("heads", [(8, 1), (4, 4)])
+@pytest.mark.parametrize("case", [[(1, 1)], [(5, 133)], [(128, 128)], [(64, 1000), (1, 65), (200, 200), (129, 4096)]])
+def test_extend_attention_separate_query_and_key_sequences(case, heads):
+    """New tokens attending to their request's paged KV (a cached prefix, an earlier piece of a chunked prompt): the tcgen05
+    forward with separate query and key sequences against the fp32 statement over the paged cache."""
+    torch.manual_seed(5)
+    Hq, Hkv = heads
+    D, bs = 128, 64
+    q_lens = [c[0] for c in case]
+    k_lens = [c[1] for c in case]
+    B = len(case)
+    nb = [(L + bs - 1) // bs for L in k_lens]
+    total_blocks = sum(nb) + 3
+    kc = torch.randn(total_blocks, bs, Hkv, D, device="cuda").mul_(0.5).to(torch.bfloat16)
+    vc = torch.randn(total_blocks, bs, Hkv, D, device="cuda").mul_(0.5).to(torch.bfloat16)
+    perm = torch.randperm(total_blocks)[: sum(nb)].tolist()                 # scattered blocks
+    bt = torch.zeros(B, max(nb), dtype=torch.int32, device="cuda")
+    at = 0
+    for b in range(B):
+        bt[b, : nb[b]] = torch.tensor(perm[at:at + nb[b]], dtype=torch.int32)
+        at += nb[b]
+    q = torch.randn(sum(q_lens), Hq, D, device="cuda").mul_(0.5).to(torch.bfloat16)
+    sl = torch.tensor(k_lens, dtype=torch.int32, device="cuda")
+    ql = torch.tensor(q_lens, dtype=torch.int32, device="cuda")
+    got = _k().paged_attention(q, kc, vc, bt, sl, ql, max(q_lens))
+    want = ref.paged_attention(q.float(), kc.float(), vc.float(), bt, sl, q_lens=ql)
+    assert _k().check_error_flag() == 0
+    assert _rel(got, want) < 2e-2, _rel(got, want)
