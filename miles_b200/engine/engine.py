@@ -376,8 +376,10 @@ class Engine:
     def release_memory_occupation(self, tags: list[str] | None = None):
         tags = tags or ["kv_cache", "weights", "cuda_graph"]
         with self.lock:
-            assert not self.running, "release_memory_occupation with requests in flight; pause (retract) first"
+            assert not self.running and not self.prefilling, "release_memory_occupation with requests in flight; pause (retract) first"
             if "kv_cache" in tags:
+                if self.prefix_cache is not None:
+                    self.prefix_cache.reset()              # the cached KV goes with the cache's memory
                 self.kv.free()
                 self.allocator.reset()
             if "cuda_graph" in tags:

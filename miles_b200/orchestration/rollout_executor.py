@@ -121,14 +121,17 @@ class RolloutExecutor:
     def _exchange(self, groups: list[list[Sample]]) -> list[list[Sample]]:
         if self.rollout_dp_size <= 1 or not dist.is_initialized():
             return groups
+        from ..utils import ragged_codec
+
         world = dist.get_world_size(self.gather_group)
-        payload = [[s.to_dict() for s in g] for g in groups] if self._is_rollout_leader() else None
+        # per-token fields travel as flat typed arrays with offsets (one buffer per field), not as lists of Python numbers
+        payload = ragged_codec.encode_groups(groups) if self._is_rollout_leader() else None
         gathered: list = [None] * world
         dist.all_gather_object(gathered, payload, group=self.gather_group)
         out = []
         for part in gathered:
             if part:
-                out.extend([[Sample.from_dict(d) for d in g] for g in part])
+                out.extend(ragged_codec.decode_groups(part, Sample))
         out.sort(key=lambda g: g[0].index if g[0].index is not None else 0)
         return out
 

@@ -108,3 +108,72 @@ def test_pack_replay_rows_follow_tokens():
     assert b.replay_topk.shape == (8, 2, 2)
     assert torch.equal(b.replay_topk[:4], torch.from_numpy(re0))
     assert (b.replay_topk[4:] == -1).all()
+
+
+def test_ragged_codec_and_object_store_backends(tmp_path):
+    """Samples survive the typed ragged codec bit-exactly (None vs empty kept apart, routed experts with their shape), the
+    encoding is no larger than pickled lists (and is built from a handful of buffers instead of an object per token), and the object store round-trips batches through its three backends."""
+    import pickle
+
+    import numpy as np
+
+    from miles_b200.types import Sample
+    from miles_b200.utils import object_store, ragged_codec
+
+    rng = np.random.default_rng(0)
+    groups = []
+    for g in range(3):
+        grp = []
+        for i in range(4):
+            n = int(rng.integers(5, 400))
+            s = Sample(tokens=rng.integers(0, 150000, n).tolist(), response_length=n // 2, index=g * 4 + i,
+                       metadata={"k": g}, reward=float(i))
+            s.loss_mask = [1] * (n // 2) if i % 2 else None
+            s.rollout_log_probs = (-rng.random(n // 2)).astype(np.float32).tolist() if i != 3 else []
+            s.rollout_routed_experts = rng.integers(0, 128, (n - 1, 2, 8)).astype(np.int32) if i == 0 else None
+            grp.append(s)
+        groups.append(grp)
+    enc = ragged_codec.encode_groups(groups)
+    back = ragged_codec.decode_groups(pickle.loads(pickle.dumps(enc, protocol=5)), Sample)
+    assert [len(g) for g in back] == [4, 4, 4]
+    for ga, gb in zip(groups, back):
+        for a, b in zip(ga, gb):
+            assert a.tokens == b.tokens and a.loss_mask == b.loss_mask and a.index == b.index and a.metadata == b.metadata
+            assert (a.rollout_log_probs is None) == (b.rollout_log_probs is None)
+            assert a.rollout_log_probs == [] if a.rollout_log_probs == [] else np.allclose(a.rollout_log_probs, b.rollout_log_probs)
+            if a.rollout_routed_experts is None:
+                assert b.rollout_routed_experts is None
+            else:
+                assert np.array_equal(a.rollout_routed_experts, b.rollout_routed_experts)
+    naive = len(pickle.dumps([[s.to_dict() for s in g] for g in groups]))
+    assert len(pickle.dumps(enc, protocol=5)) < naive
+    blob = ragged_codec.dumps([s.to_dict() for s in groups[0]], compress=True)
+    assert ragged_codec.loads(blob)[1]["tokens"] == groups[0][1].tokens
+    batch = {"tokens": [s.tokens for s in groups[0]], "loss_masks": [[1, 0, 1], [], [1], [0]], "rewards": [0.5, 1.0, 0.0, 2.0],
+             "rollout_log_probs": [[-0.5, -1.5], [], [-2.0], [-0.25]], "note": "x"}
+
+    class KV:
+        def __init__(self):
+            self.d = {}
+
+        def set(self, k, v):
+            self.d[k] = v
+
+        def get(self, k):
+            return self.d[k]
+
+        def delete_key(self, k):
+            self.d.pop(k)
+
+    try:
+        for conf in ({}, {"directory": str(tmp_path / "store")}, {"store": KV()}):
+            object_store.configure(**conf)
+            key = object_store.put(batch)
+            got = object_store.get(key)
+            assert got["tokens"] == batch["tokens"] and got["loss_masks"] == batch["loss_masks"] and got["note"] == "x"
+            assert got["rollout_log_probs"] == batch["rollout_log_probs"] and got["rewards"] == batch["rewards"]
+            object_store.remove(key)
+            with pytest.raises(Exception):
+                object_store.get(key)
+    finally:
+        object_store.configure()
