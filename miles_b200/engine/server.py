@@ -112,6 +112,19 @@ def build_app(engine, tokenizer=None):
     @app.post("/update_weights_from_tensor")
     async def update_from_tensor(request: Request):
         body = await request.json()
+        if body.get("ipc_bucket") is not None:
+            # one flat bucket: an IPC mapping of the sender's device buffer (or its bytes); copied, then unmapped before
+            # the response — the sender reuses the buffer as soon as it has the answer
+            from ..weight_update import cuda_ipc
+
+            flat, manifest = cuda_ipc.open_bucket(body["ipc_bucket"], engine.device)
+            named = cuda_ipc.split_bucket(flat, manifest)
+            engine.update_weights_from_tensor(named, body.get("weight_version"), body.get("load_format"))
+            n = len(named)
+            if flat.is_cuda:
+                torch.cuda.current_stream(flat.device).synchronize()
+            del named, flat
+            return {"success": True, "num_tensors": n}
         named = []
         for blob in body["serialized_named_tensors"]:
             named += deserialize_named_tensors(blob, engine.device)

@@ -63,6 +63,22 @@ class RemoteEngine:
         except Exception:
             return None                                  # servers without the endpoint flush on weight update
 
+    def update_weights_from_tensor(self, named, weight_version=None, load_format=None):
+        """A bucket of HF-named tensors: device tensors go as ONE CUDA-IPC handle (the server maps the trainer's buffer and
+        copies device to device), host tensors as bytes."""
+        from ...weight_update import cuda_ipc
+
+        named = list(named)
+        if named and named[0][1].is_cuda:
+            need = sum((t.numel() * t.element_size() + cuda_ipc.ALIGN - 1) // cuda_ipc.ALIGN * cuda_ipc.ALIGN for _, t in named)
+            st = getattr(self, "_staging", None)
+            if st is None or st.numel() < need:
+                self._staging = st = torch_empty_u8(need, named[0][1].device)
+        else:
+            st = None
+        return cuda_ipc.send_bucket(lambda body: self._post("update_weights_from_tensor", body), named,
+                                    weight_version=weight_version, staging=st)
+
     def update_weights_from_disk(self, path: str):
         return self._post("update_weights_from_disk", {"model_path": path})
 
@@ -162,6 +178,12 @@ class Fleet:
             self._thread.join(10)
         if self.manager is not None:
             self.manager.stop_all()
+
+
+def torch_empty_u8(n: int, device):
+    import torch
+
+    return torch.empty(n, dtype=torch.uint8, device=device)
 
 
 def wait_healthy(url: str, timeout: float = 180.0):

@@ -172,3 +172,44 @@ def test_prefix_cache_and_chunked_prefill_on_cuda():
         assert max(abs(x - y) for x, y in zip(la[:n], lb[:n])) < 5e-2 and max(abs(x - y) for x, y in zip(la[:n], lc[:n])) < 5e-2
     assert cached.stats["prefix_cache_hit_tokens"] == 256 + 448 and cached.stats["extend_tokens"] > 0
     assert chunked.stats["extend_tokens"] > 0
+
+
+@pytest.mark.gpu
+def test_cuda_ipc_bucket_between_processes(tmp_path):
+    """An engine server in ANOTHER process on this GPU receives a bucket as a CUDA-IPC handle of the sender's flat buffer
+    and ends up with bit-identical weights (no kernel of one process waits on the other: the copy is ordered by the HTTP
+    request / response)."""
+    import socket
+    import subprocess
+    import sys
+
+    from miles_b200.engine.server import weight_checksums
+    from miles_b200.models.config import PRESETS
+    from miles_b200.models.convert import to_hf
+    from miles_b200.models.qwen3 import build_model
+    from miles_b200.orchestration.workers.fleet import RemoteEngine, wait_healthy
+    from miles_b200.parallel.state import ParallelState
+
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        port = s.getsockname()[1]
+    proc = subprocess.Popen([sys.executable, "-m", "miles_b200.engine.server", "--model-name", "tiny", "--port", str(port),
+                             "--mem-fraction-static", "0.05"], stdout=open(tmp_path / "server.log", "wb"), stderr=subprocess.STDOUT)
+    try:
+        wait_healthy(f"http://127.0.0.1:{port}", 240.0)
+        cfg = PRESETS["tiny"]
+        model = build_model(cfg, ParallelState.single(), dtype=torch.bfloat16, device="cuda", seed=123)
+        named = [x for n, p in model.named_parameters() for x in to_hf(n, p.data, cfg)]
+        eng = RemoteEngine(f"http://127.0.0.1:{port}")
+        nbytes = eng.update_weights_from_tensor(named, weight_version=5)
+        assert nbytes >= sum(t.numel() * t.element_size() for _, t in named)
+        out = eng._post("weights_checker", {"action": "compare", "checksums": weight_checksums(model)})
+        assert out == {"success": True, "mismatched": []}, out
+        eng._post("update_weight_version", {"weight_version": 5})
+        assert eng.get_weight_version() == 5
+    finally:
+        proc.terminate()
+        try:
+            proc.wait(timeout=20)
+        except subprocess.TimeoutExpired:
+            proc.kill()

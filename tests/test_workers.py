@@ -219,6 +219,20 @@ def test_engine_fleet_survives_a_lost_engine(tmp_path):
         update_weights(args, actor, rollout)
         assert [e.get_weight_version() for e in rollout.engines] == [actor.weight_version] * 2
         assert rollout.controller.stale_engines() == []
+        # the tensor protocol towards engines in other processes: flat buckets (bytes here; CUDA-IPC handles on a GPU)
+        from miles_b200.weight_update.updater import WeightUpdater
+
+        for p in actor.model.parameters():
+            p.data.add_(0.01)
+        actor.weight_version += 1
+        upd = WeightUpdater(args, actor, rollout.engines, mode="tensor")
+        update_weights(args, actor, rollout, updater=upd)
+        assert [e.get_weight_version() for e in rollout.engines] == [actor.weight_version] * 2
+        from miles_b200.engine.server import weight_checksums
+
+        want = weight_checksums(actor.model)
+        for e in rollout.engines:                                                       # every tensor arrived bit-exactly
+            assert e._post("weights_checker", {"action": "compare", "checksums": want}) == {"success": True, "mismatched": []}
         pack = rollout.executor.get(1)                                                  # both engines serve again
         assert len(object_store.get(pack.data_ref)["tokens"]) == 8
     finally:
