@@ -336,7 +336,13 @@ def build_parser() -> argparse.ArgumentParser:
     _bool_flag(g, "--debug-train-only")
     g.add_argument("--load-debug-rollout-data", type=str, default=None)
     g.add_argument("--save-debug-rollout-data", type=str, default=None)
-    g.add_argument("--dump-details", type=str, default=None)
+    g.add_argument("--dump-details", type=str, default=None,
+                   help="directory for everything a post-mortem needs: rollout dumps (rollout_data/{id}.pt), per-rank train data "
+                        "(train_data/{id}_{rank}.pt) and, with --use-miles-dashboard, metrics and per-rank phase intervals (dashboard/)")
+    g.add_argument("--use-miles-dashboard", action="store_true",
+                   help="record metrics and per-rank phase intervals under <dump-details>/dashboard for `python -m miles_b200.dashboard.server "
+                        "--dump-details DIR`")
+    g.add_argument("--save-debug-train-data", type=str, default=None, help="path pattern ({rollout_id}, {rank}) for per-rank train data")
     _bool_flag(g, "--check-weight-update-equal")
     _bool_flag(g, "--debug-deterministic-collective")
     _bool_flag(g, "--ci-test")
@@ -460,6 +466,14 @@ def validate_args(args) -> None:
     if args.fp32:
         args.bf16 = False
 
+    if getattr(args, "dump_details", None):
+        d = args.dump_details
+        args.save_debug_rollout_data = args.save_debug_rollout_data or os.path.join(d, "rollout_data", "{rollout_id}.pt")
+        args.save_debug_train_data = getattr(args, "save_debug_train_data", None) or os.path.join(d, "train_data", "{rollout_id}_{rank}.pt")
+        if getattr(args, "use_miles_dashboard", False) and not args.jsonl_metrics_path:
+            args.jsonl_metrics_path = os.path.join(d, "dashboard", "metrics.jsonl")
+    elif getattr(args, "use_miles_dashboard", False):
+        raise ValueError("--use-miles-dashboard needs --dump-details DIR")
     if getattr(args, "use_opd", False):
         if args.opd_type is None:
             raise ValueError("--use-opd needs --opd-type sglang (teacher engines) or megatron (teacher weights in the trainer)")

@@ -138,20 +138,47 @@ def scrape_prometheus(text: str) -> dict[str, float]:
 
 PAGE = """<!doctype html><html><head><meta charset="utf-8"><title>miles_b200</title>
 <style>body{font:13px system-ui;margin:16px;background:#111;color:#ddd}canvas{background:#1b1b1b;margin:6px;border-radius:4px}
-input{background:#222;color:#ddd;border:1px solid #444;padding:4px;width:320px}.t{display:inline-block;text-align:center}</style></head>
-<body><h3>miles_b200 run dashboard</h3><input id="f" placeholder="filter (prefix), e.g. train/ or perf/"><div id="g"></div>
+input,select{background:#222;color:#ddd;border:1px solid #444;padding:4px}.t{display:inline-block;text-align:center}
+nav a{margin-right:14px;color:#6cf;cursor:pointer}nav a.on{color:#fff;font-weight:600}table{border-collapse:collapse}
+td,th{border-bottom:1px solid #333;padding:3px 8px;text-align:right}.alarm{color:#f66}.warn{color:#fc6}.info{color:#9c9}
+.tok{display:inline-block;padding:1px 2px;margin:1px;border-radius:2px;background:#222}.tok.r{background:#234}.tok.m{opacity:.45}</style></head>
+<body><h3>miles_b200 run dashboard</h3><nav><a id="n-metrics" class="on">metrics</a><a id="n-timeline">timeline</a><a id="n-advice">advisories</a><a id="n-samples">samples</a></nav>
+<div id="metrics"><input id="f" style="width:320px" placeholder="filter (prefix), e.g. train/ or perf/"><div id="g"></div></div>
+<div id="timeline" hidden><canvas id="tl" width="1200" height="400"></canvas><pre id="util"></pre></div>
+<div id="advice" hidden></div>
+<div id="samples" hidden>rollout <select id="rid"></select> <span id="sum"></span><table id="tab"></table><div id="tv"></div></div>
 <script>
-async function draw(){const p=document.getElementById('f').value;const names=await (await fetch('/api/names?prefix='+encodeURIComponent(p))).json();
-const g=document.getElementById('g');g.innerHTML='';for(const n of names.slice(0,48)){const d=await (await fetch('/api/series?name='+encodeURIComponent(n)+'&last=500')).json();
-const w=document.createElement('div');w.className='t';const c=document.createElement('canvas');c.width=300;c.height=120;w.appendChild(c);
-w.appendChild(document.createElement('br'));w.appendChild(document.createTextNode(n+(d.length?' = '+d[d.length-1][1].toPrecision(5):'')));g.appendChild(w);
-if(!d.length)continue;const x=c.getContext('2d');const ys=d.map(e=>e[1]);const lo=Math.min(...ys),hi=Math.max(...ys);x.strokeStyle='#6cf';x.beginPath();
-d.forEach((e,i)=>{const X=i/(d.length-1||1)*290+5,Y=110-(hi>lo?(e[1]-lo)/(hi-lo):.5)*100;i?x.lineTo(X,Y):x.moveTo(X,Y)});x.stroke();}}
-draw();setInterval(draw,5000);document.getElementById('f').onchange=draw;</script></body></html>"""
+const J=async u=>(await fetch(u)).json();const $=i=>document.getElementById(i);
+for(const t of ['metrics','timeline','advice','samples'])$('n-'+t).onclick=()=>{for(const u of ['metrics','timeline','advice','samples']){$(u).hidden=u!=t;$('n-'+u).className=u==t?'on':''}show[t]()};
+const COL={};const color=n=>COL[n]||(COL[n]='hsl('+(Object.keys(COL).length*67%360)+',60%,55%)');
+const show={async metrics(){const p=$('f').value;const names=await J('/api/names?prefix='+encodeURIComponent(p));const g=$('g');g.innerHTML='';
+for(const n of names.slice(0,48)){const d=await J('/api/series?name='+encodeURIComponent(n)+'&last=500');const w=document.createElement('div');w.className='t';
+const c=document.createElement('canvas');c.width=300;c.height=120;w.appendChild(c);w.appendChild(document.createElement('br'));
+w.appendChild(document.createTextNode(n+(d.length?' = '+d[d.length-1][1].toPrecision(5):'')));g.appendChild(w);if(!d.length)continue;
+const x=c.getContext('2d');const ys=d.map(e=>e[1]);const lo=Math.min(...ys),hi=Math.max(...ys);x.strokeStyle='#6cf';x.beginPath();
+d.forEach((e,i)=>{const X=i/(d.length-1||1)*290+5,Y=110-(hi>lo?(e[1]-lo)/(hi-lo):.5)*100;i?x.lineTo(X,Y):x.moveTo(X,Y)});x.stroke();}},
+async timeline(){const d=await J('/api/phases');const c=$('tl'),x=c.getContext('2d');x.clearRect(0,0,c.width,c.height);const L=Object.keys(d.lanes);
+if(!L.length){x.fillStyle='#888';x.fillText('no phase records (run with --use-miles-dashboard --dump-details DIR)',20,30);return}
+c.height=Math.max(120,L.length*26+50);const W=c.width-140,span=Math.max(d.t1-d.t0,1e-9);L.forEach((l,i)=>{x.fillStyle='#aaa';x.fillText(l,4,i*26+22);
+for(const r of d.lanes[l]){x.fillStyle=color(r.phase);x.fillRect(130+(r.start-d.t0)/span*W,i*26+8,Math.max(1,(r.end-r.start)/span*W),18)}});
+let k=0;for(const n in COL){x.fillStyle=COL[n];x.fillRect(130+k*120,L.length*26+20,10,10);x.fillStyle='#ccc';x.fillText(n,144+k*120,L.length*26+29);k++}
+$('util').textContent=JSON.stringify(d.utilisation,null,1)},
+async advice(){const a=await J('/api/advisories');$('advice').innerHTML=a.length?a.map(r=>'<p class="'+r.severity+'"><b>['+r.severity+'] '+r.title+'</b><br>'+r.detail+'<br><i>'+r.hint+'</i></p>').join(''):'<p>nothing to report</p>'},
+async samples(){const ids=await J('/api/rollouts');const s=$('rid');if(!s.options.length){s.innerHTML=ids.map(i=>'<option>'+i+'</option>').join('');s.onchange=show.samples}
+if(!ids.length){$('sum').textContent='no rollout dumps (run with --dump-details DIR)';return}const id=s.value||ids[ids.length-1];const d=await J('/api/rollout/'+id);
+$('sum').textContent=JSON.stringify(d.summary);$('tab').innerHTML='<tr><th>group</th><th>sample</th><th>prompt</th><th>response</th><th>reward</th><th>status</th><th>mean logp</th></tr>'+
+d.samples.map(r=>'<tr data-g="'+r.group+'" data-s="'+r.sample+'"><td>'+r.group+'</td><td>'+r.sample+'</td><td>'+r.prompt_tokens+'</td><td>'+r.response_tokens+'</td><td>'+r.reward+'</td><td>'+r.status+'</td><td>'+(r.mean_logprob==null?'':r.mean_logprob.toFixed(3))+'</td></tr>').join('');
+for(const tr of $('tab').querySelectorAll('tr[data-g]'))tr.onclick=async()=>{const v=await J('/api/sample/'+id+'/'+tr.dataset.g+'/'+tr.dataset.s);
+$('tv').innerHTML='<p>reward '+v.reward+' · '+v.status+'</p>'+v.tokens.map(t=>'<span class="tok '+(t.part=='response'?'r':'')+(t.trained===false?' m':'')+'" title="'+t.pos+(t.rollout_log_prob!=null?' logp '+t.rollout_log_prob.toFixed(3):'')+'">'+t.text.replace(/</g,'&lt;')+'</span>').join('')}}};
+show.metrics();setInterval(()=>{if(!$('metrics').hidden)show.metrics()},5000);$('f').onchange=show.metrics;</script></body></html>"""
 
 
-def build_app(store: SeriesStore):
+def build_app(store: SeriesStore, dump_dir: str | None = None, tokenizer=None):
+    from . import advisory, phases
+    from .dump_reader import DumpReader
+
     app = FastAPI(title="miles_b200 dashboard")
+    reader = DumpReader(dump_dir, tokenizer) if dump_dir else None
 
     @app.get("/", response_class=HTMLResponse)
     async def index():
@@ -170,6 +197,28 @@ def build_app(store: SeriesStore):
         store.add_many(body.get("metrics", {}), body.get("step", time.time()))
         return {"ok": True}
 
+    @app.get("/api/phases")
+    async def phase_rows():
+        rows = phases.read_phases(dump_dir) if dump_dir else []
+        return {"lanes": phases.lanes(rows), "utilisation": phases.utilisation(rows),
+                "t0": min((r["start"] for r in rows), default=0.0), "t1": max((r["end"] for r in rows), default=0.0)}
+
+    @app.get("/api/advisories")
+    async def advisories(min_gap_s: float = 60.0):
+        return advisory.compute_advisories(store, phases.read_phases(dump_dir) if dump_dir else [], min_gap_s)
+
+    @app.get("/api/rollouts")
+    async def rollouts():
+        return reader.rollout_ids() if reader else []
+
+    @app.get("/api/rollout/{rollout_id}")
+    async def rollout(rollout_id: int):
+        return {"summary": reader.summary(rollout_id), "samples": reader.samples(rollout_id)}
+
+    @app.get("/api/sample/{rollout_id}/{group}/{sample}")
+    async def sample(rollout_id: int, group: int, sample: int):
+        return reader.token_view(rollout_id, group, sample)
+
     return app
 
 
@@ -183,12 +232,17 @@ def main():
     p.add_argument("--host", default="127.0.0.1")
     p.add_argument("--port", type=int, default=8265)
     p.add_argument("--gpu-interval", type=float, default=2.0)
+    p.add_argument("--dump-details", default=None, help="directory given to the run's --dump-details: phase lanes, rollout dumps, metrics")
     a = p.parse_args()
     store = SeriesStore()
+    import os
+
+    if a.dump_details and not a.jsonl and os.path.exists(os.path.join(a.dump_details, "dashboard", "metrics.jsonl")):
+        a.jsonl = os.path.join(a.dump_details, "dashboard", "metrics.jsonl")
     if a.jsonl:
         store.load_jsonl(a.jsonl)
     GpuSampler(store, a.gpu_interval).start()
-    uvicorn.run(build_app(store), host=a.host, port=a.port, log_level="warning")
+    uvicorn.run(build_app(store, a.dump_details), host=a.host, port=a.port, log_level="warning")
 
 
 if __name__ == "__main__":

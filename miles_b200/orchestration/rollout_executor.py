@@ -94,6 +94,15 @@ class RolloutExecutor:
             load_function(args.rollout_data_postprocess_path)(args, data)
         metrics.update(self._rollout_metrics(groups, data, time.time() - t0))
         metrics["perf/generate_time"] = t_gen
+        if getattr(args, "use_miles_dashboard", False) and getattr(args, "dump_details", None):
+            from ..dashboard.phases import PhaseSink
+
+            sink = getattr(self, "_phase_sink", None)
+            if sink is None:
+                sink = self._phase_sink = PhaseSink(args.dump_details, dist.get_rank() if dist.is_initialized() else 0, "rollout")
+            sink.rollout_id = rollout_id
+            sink.write("generate", t0, t0 + t_gen)
+            sink.write("rollout", t0, time.time())
         if local:
             metrics = self._reduce_metrics(metrics, len(data["tokens"]), sum(data["response_lengths"]))
             shard = dict(data)

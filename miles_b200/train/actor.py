@@ -152,6 +152,11 @@ class TrainActor:
         self.profiler = TrainProfiler(args)
         self.profiler.on_init_end()
         self.backuper = TensorBackuper(self.model)
+        if getattr(args, "use_miles_dashboard", False) and getattr(args, "dump_details", None):
+            from ..dashboard.phases import PhaseSink
+
+            self.phase_sink = PhaseSink(args.dump_details, self.ps.rank, self.role)
+            self.timer.sinks.append(self.phase_sink)          # every timed span of this rank becomes a lane interval
         from ..utils.dumper import DumperSwitch
 
         self.dumper = DumperSwitch.from_args(args, self.ps.rank)       # --dumper-enable + per-phase lists; None when off
@@ -373,6 +378,8 @@ class TrainActor:
         dp_group = ps.dp_group
         if ps.fabric is not None:
             ps.fabric.phase_barrier()       # absorb host skew between ranks before the first kernel that waits on a peer
+        if getattr(self, "phase_sink", None) is not None:
+            self.phase_sink.rollout_id = rollout_id
         with self.timer.span("data_preprocess"):
             mbs = make_micro_batches(args, shard["total_lengths"], dp_group=dp_group, cp_size=ps.cp_size)
         metrics: dict[str, float] = {}
@@ -415,6 +422,16 @@ class TrainActor:
                 opd_reverse_kl=flat_per_token(shard, "opd_reverse_kl", order, dev) if "opd_reverse_kl" in shard else None)
             shard["advantages"] = list(adv.split(resp))
             shard["returns"] = list(ret.split(resp))
+        pattern = getattr(args, "save_debug_train_data", None)
+        if pattern:
+            path = pattern.format(rollout_id=rollout_id, rank=ps.rank)
+            os.makedirs(os.path.dirname(path) or ".", exist_ok=True)
+            keep = ("tokens", "response_lengths", "total_lengths", "loss_masks", "rewards", "raw_reward", "rollout_log_probs", "sample_indices")
+            blob = {k: shard[k] for k in keep if k in shard}
+            blob["advantages"] = [a.tolist() for a in shard["advantages"]]
+            blob["log_probs"] = [t.tolist() for t in old_lp] if old_lp else None
+            blob["ref_log_probs"] = [t.tolist() for t in ref_lp] if ref_lp else None
+            torch.save({"rollout_id": rollout_id, "rank": ps.rank, "dp_rank": ps.dp_rank, "data": blob}, path)
         if getattr(args, "ci_test", False) and old_lp is not None and ref_lp is not None and rollout_id == 0 \
                 and not getattr(args, "ref_load", None):
             kl0 = (torch.cat(old_lp) - torch.cat(ref_lp)).abs().max().item()

@@ -220,3 +220,44 @@ def test_dumper_phases_and_compare(tmp_path):
     assert [r["status"] for r in rows].count("diff") == 1
     assert D.main(["compare", inf, other]) == 1 and D.main(["compare", inf, inf]) == 0
     assert D.DumperConfig.kv_to_dict(["max-numel=8", "enable=false"]) == {"max_numel": 8, "enable": False}
+
+
+def test_dashboard_phases_advisories_and_sample_views(tmp_path):
+    """A run with --dump-details --use-miles-dashboard leaves metrics, per-rank phase lanes and rollout dumps; the dashboard
+    serves timeline, advisories and sample / token views from them."""
+    from fastapi.testclient import TestClient
+
+    from test_e2e import _run
+    from miles_b200.dashboard import advisory, phases
+    from miles_b200.dashboard.server import SeriesStore, build_app
+
+    d = str(tmp_path / "dump")
+    _run(f"--dump-details {d} --use-miles-dashboard --num-rollout 2")
+    assert os.path.exists(os.path.join(d, "dashboard", "metrics.jsonl")) and os.path.exists(os.path.join(d, "train_data", "1_0.pt"))
+    rows = phases.read_phases(d)
+    names = {(r["role"], r["phase"]) for r in rows}
+    assert {("actor", "actor_train"), ("actor", "log_probs"), ("rollout", "generate")} <= names
+    util = phases.utilisation(rows)
+    assert 0.0 <= util["actor:0"]["idle"] < 1.0 and util["actor:0"]["phases"]["actor_train"] > 0
+    store = SeriesStore()
+    store.load_jsonl(os.path.join(d, "dashboard", "metrics.jsonl"))
+    app = TestClient(build_app(store, d))
+    tl = app.get("/api/phases").json()
+    assert "actor:0" in tl["lanes"] and tl["t1"] > tl["t0"]
+    assert app.get("/api/rollouts").json() == [0, 1]
+    ro = app.get("/api/rollout/1").json()
+    assert ro["summary"]["samples"] == 32 and len(ro["samples"]) == 32 and ro["summary"]["groups"] == 8
+    tv = app.get("/api/sample/1/0/1").json()
+    assert tv["tokens"][0]["part"] == "prompt" and tv["tokens"][-1]["part"] == "response" and tv["tokens"][-1]["rollout_log_prob"] is not None
+    assert "timeline" in app.get("/").text
+    # advisories from hand-made signals: a stalled lane, uneven ranks, truncation, train / rollout mismatch
+    fake = [{"rank": r, "role": "actor", "phase": "actor_train", "start": 0.0, "end": 10.0 + 10 * r, "rollout_id": 0} for r in (0, 1)]
+    fake.append({"rank": 0, "role": "actor", "phase": "log_probs", "start": 400.0, "end": 410.0, "rollout_id": 1})
+    st = SeriesStore()
+    for i in range(5):
+        st.add_many({"rollout/truncated_ratio": 0.5, "train/train_rollout_logprob_abs_diff": 0.2, "perf/rollout_time": 30.0, "perf/train_time": 5.0}, i)
+    found = advisory.compute_advisories(st, fake, min_gap_s=60.0)
+    titles = " | ".join(a["title"] for a in found)
+    assert found[0]["severity"] == "alarm" and "recorded nothing" in titles and "differs by" in titles and "length limit" in titles
+    assert "disagree on log-probs" in titles and "generation takes" in titles
+    assert advisory.compute_advisories(SeriesStore(), []) == []
