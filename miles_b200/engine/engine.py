@@ -885,6 +885,8 @@ class Engine:
         if self.stateless:
             reqs = list(self.running)
             self.stats["decode_tokens"] += len(reqs)
+            for r in reqs:
+                r.chunk = (0, len(r.all_ids))             # the whole sequence, every step
             self._run_prefill(reqs)                       # scores every sequence from its first token; appends one token each
             self.stats["prefill_tokens"] -= sum(len(r.all_ids) - 1 for r in reqs)
             self.running = [r for r in self.running if not r.finished]

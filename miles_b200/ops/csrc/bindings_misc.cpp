@@ -146,4 +146,20 @@ void register_misc(pybind11::module& m) {
   m.def("int4_fake_quant", &int4_fake_quant);
   m.def("absmax", &absmax);
   m.def("nvfp4_qdq", &nvfp4_qdq);
+  // index checks of the debug build: limits are published per kind of index (0 cache slots, 1 MoE (token, choice) pairs,
+  // 2 cache blocks); the report lists, per translation unit, {count, first code, first index, its limit}
+  m.def("is_debug_build", []() { return mb_elementwise_bounds_set_limit(-1, 0) != -1; });
+  m.def("bounds_set_limit", [](int64_t which, int64_t value) {
+    const int a = mb_elementwise_bounds_set_limit(which, value), b = mb_moe_bounds_set_limit(which, value),
+              c = mb_paged_bounds_set_limit(which, value);
+    return a == 0 && b == 0 && c == 0;
+  });
+  m.def("bounds_report", [](bool clear) {
+    std::vector<std::vector<int64_t>> out;
+    long long r[4];
+    if (mb_elementwise_bounds_read(r, clear) == 0) out.push_back({0, r[0], r[1], r[2], r[3]});
+    if (mb_moe_bounds_read(r, clear) == 0) out.push_back({1, r[0], r[1], r[2], r[3]});
+    if (mb_paged_bounds_read(r, clear) == 0) out.push_back({2, r[0], r[1], r[2], r[3]});
+    return out;
+  });
 }

@@ -7,6 +7,7 @@
 #include <stdint.h>
 
 #include "launch.h"
+#include "debug.cuh"
 #include "pdl.cuh"
 
 namespace mb {
@@ -373,7 +374,8 @@ __global__ void __launch_bounds__(256) qk_norm_rope_cache_kernel(const __nv_bflo
                      nullptr, lane);
     return;
   }
-  const long long slot = slots[t];
+  long long slot = slots[t];
+  if (slot >= 0 && !dbg::in_bounds(dbg::kKvSlots, slot, 101)) slot = -1;   // debug build: a slot outside the cache is recorded, not written
   if (h < Hq + Hk) {
     const int hk = h - Hq;
     norm_rope_row<D>(k + t * k_tok_stride + hk * D, ko + (t * Hk + hk) * D, kw, static_cast<float>(positions[t]), log2_theta, eps,
@@ -503,7 +505,7 @@ __global__ void __launch_bounds__(256) kv_cache_write_kernel(const __nv_bfloat16
     const long long t = i / nvec;
     const int c = static_cast<int>(i % nvec) * 8;
     const long long slot = slots[t];
-    if (slot < 0) continue;
+    if (slot < 0 || !dbg::in_bounds(dbg::kKvSlots, slot, 102)) continue;
     *reinterpret_cast<uint4*>(kc + slot * row_elems + c) = *reinterpret_cast<const uint4*>(k + t * k_stride + c);
     *reinterpret_cast<uint4*>(vc + slot * row_elems + c) = *reinterpret_cast<const uint4*>(v + t * v_stride + c);
   }
@@ -581,6 +583,8 @@ static int grid_for(long long work_items, int per_block, int max_blocks = 148 * 
 }  // namespace mb
 
 using namespace mb;
+
+MB_DEFINE_BOUNDS_API(mb_elementwise_bounds)
 
 extern "C" int mb_rmsnorm_fwd(const void* x, const void* residual, const void* w, void* y, void* res_out, float* rstd, long long T,
                               int H, float eps, cudaStream_t s) {

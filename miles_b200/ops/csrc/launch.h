@@ -99,6 +99,14 @@ int mb_flash_fwd_tc(const void* q, const void* k, const void* v, void* o, float*
                     int causal, int* error_flag, const int* cu_seqlens_k, int total_k_tokens, cudaStream_t s);
 int mb_flash_fwd_tc_ctas_per_sm(void);
 
+// ---- debug.cuh: index checks of the debug build (each returns −1 in a build without them) ----
+int mb_elementwise_bounds_set_limit(int which, long long value);
+int mb_elementwise_bounds_read(long long* out4, int clear);
+int mb_moe_bounds_set_limit(int which, long long value);
+int mb_moe_bounds_read(long long* out4, int clear);
+int mb_paged_bounds_set_limit(int which, long long value);
+int mb_paged_bounds_read(long long* out4, int clear);
+
 // ---- moe.cu ----
 int mb_router_topk(const float* logits, float* probs, float* topk_w, int* topk_idx, long long T, int E, int K, int normalize,
                    cudaStream_t s);

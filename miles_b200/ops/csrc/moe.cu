@@ -10,6 +10,7 @@
 #include <stdint.h>
 
 #include "launch.h"
+#include "debug.cuh"
 #include "pdl.cuh"
 
 namespace mb {
@@ -158,7 +159,7 @@ __global__ void __launch_bounds__(256) moe_gather_kernel(const bf16* __restrict_
   for (int row = blockIdx.x; row < total && row < max_rows; row += gridDim.x) {
     const int src = row_src[row];
     uint4* dst = reinterpret_cast<uint4*>(x_perm + static_cast<long long>(row) * H);
-    if (src >= 0) {
+    if (src >= 0 && dbg::in_bounds(dbg::kMoePairs, src, 201)) {
       const uint4* s = reinterpret_cast<const uint4*>(x + static_cast<long long>(src / k) * H);
       for (int v = threadIdx.x; v < nvec; v += 256) dst[v] = s[v];
     } else {
@@ -255,6 +256,8 @@ __global__ void __launch_bounds__(256) moe_combine_bwd_kernel(const bf16* __rest
 }  // namespace mb
 
 using namespace mb;
+
+MB_DEFINE_BOUNDS_API(mb_moe_bounds)
 
 extern "C" int mb_router_topk(const float* logits, float* probs, float* topk_w, int* topk_idx, long long T, int E, int K,
                               int normalize, cudaStream_t s) {

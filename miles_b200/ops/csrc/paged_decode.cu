@@ -13,6 +13,7 @@
 #include <cstdlib>
 
 #include "launch.h"
+#include "debug.cuh"
 #include "pdl.cuh"
 
 namespace mbpd {
@@ -84,9 +85,11 @@ __global__ void __launch_bounds__(128) paged_decode_mma_kernel(const bf16* __res
     for (int i = threadIdx.x; i < TK * kChunks; i += 128) {
       const int r = i / kChunks, c = i % kChunks;
       const int key = k0 + r;
-      const bool ok = key < k_end;
+      bool ok = key < k_end;
       const int kk = ok ? key : k_begin;
-      const long long slot = static_cast<long long>(bt[kk / block_size]) * block_size + kk % block_size;
+      long long blk = bt[kk / block_size];
+      if (!mb::dbg::in_bounds(mb::dbg::kKvBlocks, blk, 301)) { ok = false; blk = 0; }   // debug build: zero-filled instead of read
+      const long long slot = blk * block_size + kk % block_size;
       const long long off = (slot * Hkv + hk) * D + c * 8;
       cp_async16(sK + st * TK * D + toff<D>(r, c), kc + off, ok);
       cp_async16(sV + st * TK * D + toff<D>(r, c), vc + off, ok);
@@ -255,6 +258,8 @@ static size_t smem_bytes() { return static_cast<size_t>(16 * D + 4 * TK * D) * 2
 }  // namespace mbpd
 
 using namespace mbpd;
+
+MB_DEFINE_BOUNDS_API(mb_paged_bounds)
 
 // part_o: [B·Hq·splits·D] floats, part_ml: [B·Hq·splits·2] floats.  Hq/Hkv ≤ 8.
 extern "C" int mb_paged_decode(const void* q, const void* kc, const void* vc, const int* block_table, const int* seq_lens, void* out,

@@ -16,6 +16,27 @@ from . import reference as ref
 
 C = _build.load()
 
+# the debug build of the extension (MILES_DEBUG_KERNELS=1, csrc/debug.cuh): kernels check the indices they take from tensors
+# against limits published here, record violations and skip the access
+DEBUG_KERNELS = bool(C.is_debug_build()) if hasattr(C, "is_debug_build") else False
+_published: dict[int, int] = {}
+LIMIT_KV_SLOTS, LIMIT_MOE_PAIRS, LIMIT_KV_BLOCKS = 0, 1, 2
+
+
+def publish_limit(which: int, value: int) -> None:
+    if DEBUG_KERNELS and _published.get(which) != int(value):
+        C.bounds_set_limit(int(which), int(value))
+        _published[which] = int(value)
+
+
+def bounds_report(clear: bool = True) -> list[dict]:
+    """Index violations seen by the debug build since the last clearing report: one entry per translation unit that saw any."""
+    if not DEBUG_KERNELS:
+        return []
+    unit = {0: "elementwise.cu", 1: "moe.cu", 2: "paged_decode.cu"}
+    return [{"unit": unit[int(r[0])], "count": int(r[1]), "code": int(r[2]), "index": int(r[3]), "limit": int(r[4])}
+            for r in C.bounds_report(bool(clear)) if r[1] > 0]
+
 BF16 = torch.bfloat16
 
 
@@ -428,6 +449,7 @@ def qk_norm_rope_cache(q, k, v, q_w, k_w, positions, theta, eps, k_cache, v_cach
         return q, k
     qo = torch.empty(T, Hq, D, dtype=q.dtype, device=q.device)
     ko = torch.empty(T, Hk, D, dtype=k.dtype, device=k.device)
+    publish_limit(LIMIT_KV_SLOTS, k_cache.shape[0] * k_cache.shape[1])
     C.qk_norm_rope_cache(q, k, v, q_w, k_w, positions, qo, ko, k_cache, v_cache, slot_mapping, float(theta), float(eps))
     return qo, ko
 
@@ -438,6 +460,7 @@ def rope(x, positions, theta, inverse=False):
 
 def kv_cache_write(k, v, k_cache, v_cache, slot_mapping):
     assert k.stride(2) == 1 and k.stride(1) == k.shape[2]
+    publish_limit(LIMIT_KV_SLOTS, k_cache.shape[0] * k_cache.shape[1])
     C.kv_cache_write(k.detach(), v.detach(), k_cache, v_cache, slot_mapping.to(torch.int64))
 
 

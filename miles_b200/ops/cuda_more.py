@@ -7,7 +7,7 @@ import os
 import torch
 
 from . import reference as ref
-from .cuda import BF16, C, _c, gemm_nn, gemm_nt, gemm_tn
+from .cuda import BF16, LIMIT_KV_BLOCKS, LIMIT_MOE_PAIRS, C, _c, gemm_nn, gemm_nt, gemm_tn, publish_limit
 
 # ---------------------------------------------------------------------------------------------
 # attention
@@ -107,6 +107,7 @@ def paged_attention(q, k_cache, v_cache, block_table, seq_lens, q_lens=None, max
     splits = max(1, min(_DECODE_SPLITS, -(-296 // (B * k_cache.shape[2]))))
     part_o = torch.empty(B * Hq * splits * D, dtype=torch.float32, device=q.device)
     part_ml = torch.empty(B * Hq * splits * 2, dtype=torch.float32, device=q.device)
+    publish_limit(LIMIT_KV_BLOCKS, k_cache.shape[0])
     C.paged_decode(q, k_cache, v_cache, block_table, seq_lens, out, part_o, part_ml, 1.0 / math.sqrt(D), splits)
     return out
 
@@ -207,6 +208,7 @@ def _moe_ffn_small(x, w13, w2, topk_w, topk_idx, expert_offset, bt):
     max_rows = moe_max_rows_pad(T * k, E, bt)
     seg, tile, row_src, dst_row = C.moe_align(idx32, E, expert_offset, max_rows, None, bt)
     x_perm = torch.empty(max_rows, H, dtype=x.dtype, device=x.device)
+    publish_limit(LIMIT_MOE_PAIRS, x.shape[0] * k)
     C.moe_gather(x, x_perm, row_src, seg, k)
     _, y_perm = experts_forward(x_perm, _c(w13), _c(w2), seg, tile, bt)
     out = torch.empty(T, H, dtype=x.dtype, device=x.device)
@@ -250,6 +252,7 @@ class _MoEFFN(torch.autograd.Function):
         max_rows = moe_max_rows(T * k, E)
         seg, tile, row_src, dst_row = C.moe_align(idx32, E, expert_offset, max_rows, None)
         x_perm = torch.empty(max_rows, H, dtype=x.dtype, device=x.device)
+        publish_limit(LIMIT_MOE_PAIRS, x.shape[0] * k)
         C.moe_gather(x, x_perm, row_src, seg, k)
         h1 = torch.empty(max_rows, F2, dtype=x.dtype, device=x.device)
         C.gemm_grouped(x_perm, w13, h1, max_rows, F2, H, E, tile, False, 0)
@@ -285,6 +288,7 @@ class _MoEFFN(torch.autograd.Function):
         dh1 = torch.empty(max_rows, F2, dtype=x.dtype, device=x.device)
         C.swiglu_bwd(h1, dact, dh1, seg[-1:])
         x_perm = torch.empty(max_rows, H, dtype=x.dtype, device=x.device)
+        publish_limit(LIMIT_MOE_PAIRS, x.shape[0] * k)
         C.moe_gather(x, x_perm, row_src, seg, k)
         dw13 = torch.empty_like(w13)
         C.gemm_grouped_wgrad(dh1, x_perm, dw13, max_rows, F2, H, E, seg, False, 0)
