@@ -163,6 +163,15 @@ void qk_norm_rope_fwd(const at::Tensor& q, const at::Tensor& k, const c10::optio
         "mb_qk_norm_rope_fwd");
 }
 
+at::Tensor rope(const at::Tensor& x, const at::Tensor& positions, double theta, bool inverse) {
+  c10::cuda::CUDAGuard g(x.device());
+  auto y = at::empty({x.size(0), x.size(1), x.size(2)}, x.options());
+  check(mb_rope(x.data_ptr(), y.data_ptr(), positions.data_ptr<int>(), x.size(0), x.size(1), x.size(2), x.stride(0), theta, inverse ? 1 : 0,
+                cur_stream()),
+        "mb_rope");
+  return y;
+}
+
 void qk_norm_rope_cache(const at::Tensor& q, const at::Tensor& k, const at::Tensor& v, const c10::optional<at::Tensor>& qw,
                         const c10::optional<at::Tensor>& kw, const at::Tensor& positions, at::Tensor& qo, at::Tensor& ko,
                         at::Tensor& kc, at::Tensor& vc, const at::Tensor& slots, double theta, double eps) {
@@ -239,6 +248,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("rmsnorm_bwd", &rmsnorm_bwd);
   m.def("swiglu_fwd", &swiglu_fwd);
   m.def("swiglu_bwd", &swiglu_bwd);
+  m.def("rope", &rope);
   m.def("qk_norm_rope_fwd", &qk_norm_rope_fwd);
   m.def("qk_norm_rope_bwd", &qk_norm_rope_bwd);
   m.def("qk_norm_rope_cache", &qk_norm_rope_cache);

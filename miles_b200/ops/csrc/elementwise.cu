@@ -493,6 +493,35 @@ __global__ void __launch_bounds__(256) qk_norm_rope_bwd_kernel(const __nv_bfloat
 }
 
 // ---------------------------------------------------------------------------------------------
+// Rotary embedding alone (NeoX pairing: element i rotates with element i + D/2), forward or inverse (= its own backward).
+// One warp per (token, head); x [T, H, D] with token stride `tok_stride`, y contiguous.
+// ---------------------------------------------------------------------------------------------
+template <int D>
+__global__ void __launch_bounds__(256) rope_kernel(const __nv_bfloat16* __restrict__ x, __nv_bfloat16* __restrict__ y,
+                                                   const int* __restrict__ positions, long long T, int H, long long tok_stride,
+                                                   float log2_theta, int inverse) {
+  const int lane = threadIdx.x & 31;
+  const long long wid = (blockIdx.x * 256ll + threadIdx.x) >> 5;
+  if (wid >= T * H) return;
+  const long long t = wid / H;
+  const int h = static_cast<int>(wid % H);
+  const __nv_bfloat16* src = x + t * tok_stride + static_cast<long long>(h) * D;
+  __nv_bfloat16* dst = y + (t * H + h) * D;
+  const float pos = static_cast<float>(positions[t]);
+  constexpr int HALF = D / 2;
+#pragma unroll
+  for (int i = lane; i < HALF; i += 32) {
+    const float inv_freq = exp2f(-log2_theta * (static_cast<float>(2 * i) / D));
+    float sn, cs;
+    sincosf(pos * inv_freq, &sn, &cs);
+    if (inverse) sn = -sn;
+    const float a = __bfloat162float(src[i]), b = __bfloat162float(src[i + HALF]);
+    dst[i] = __float2bfloat16(a * cs - b * sn);
+    dst[i + HALF] = __float2bfloat16(b * cs + a * sn);
+  }
+}
+
+// ---------------------------------------------------------------------------------------------
 // KV cache scatter: rows [T, Hkv·D] → cache[slot, Hkv·D]
 // ---------------------------------------------------------------------------------------------
 __global__ void __launch_bounds__(256) kv_cache_write_kernel(const __nv_bfloat16* __restrict__ k, const __nv_bfloat16* __restrict__ v,
@@ -652,6 +681,18 @@ extern "C" int mb_swiglu_bwd(const void* in, const void* dout, void* din, long l
   swiglu_bwd_kernel<<<grid_for(T * (F / 8), 256), 256, 0, s>>>(reinterpret_cast<const __nv_bfloat16*>(in),
                                                                 reinterpret_cast<const __nv_bfloat16*>(dout),
                                                                 reinterpret_cast<__nv_bfloat16*>(din), T, F, rows_ptr);
+  return static_cast<int>(cudaGetLastError());
+}
+
+extern "C" int mb_rope(const void* x, void* y, const int* positions, long long T, int H, int D, long long tok_stride, float theta,
+                       int inverse, cudaStream_t s) {
+  if (T == 0 || H == 0) return 0;
+  const unsigned blocks = static_cast<unsigned>((T * H + 7) / 8);
+  auto X = reinterpret_cast<const __nv_bfloat16*>(x);
+  auto Y = reinterpret_cast<__nv_bfloat16*>(y);
+  if (D == 128) rope_kernel<128><<<blocks, 256, 0, s>>>(X, Y, positions, T, H, tok_stride, log2f(theta), inverse);
+  else if (D == 64) rope_kernel<64><<<blocks, 256, 0, s>>>(X, Y, positions, T, H, tok_stride, log2f(theta), inverse);
+  else return -1;
   return static_cast<int>(cudaGetLastError());
 }
 

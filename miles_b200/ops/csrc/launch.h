@@ -66,6 +66,8 @@ int mb_swiglu_bwd(const void* in, const void* dout, void* din, long long T, int 
 int mb_qk_norm_rope_fwd(const void* q, const void* k, long long q_stride, long long k_stride, const void* qw, const void* kw,
                         const int* positions, void* qo, void* ko, float* q_rstd, float* k_rstd, long long T, int Hq, int Hk, int D,
                         float theta, float eps, cudaStream_t s);
+int mb_rope(const void* x, void* y, const int* positions, long long T, int H, int D, long long tok_stride, float theta, int inverse,
+            cudaStream_t s);
 int mb_qk_norm_rope_cache(const void* q, const void* k, const void* v, long long q_stride, long long k_stride, long long v_stride,
                           const void* qw, const void* kw, const int* positions, void* qo, void* ko, void* kc, void* vc,
                           const long long* slots, long long T, int Hq, int Hk, int D, float theta, float eps, cudaStream_t s);

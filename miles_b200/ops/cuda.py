@@ -454,8 +454,26 @@ def qk_norm_rope_cache(q, k, v, q_w, k_w, positions, theta, eps, k_cache, v_cach
     return qo, ko
 
 
+class _Rope(torch.autograd.Function):
+    """Rotary embedding alone; the backward is the inverse rotation of the incoming gradient."""
+
+    @staticmethod
+    def forward(ctx, x, positions, theta, inverse):
+        ctx.save_for_backward(positions)
+        ctx.theta, ctx.inverse = theta, inverse
+        return C.rope(x, positions, float(theta), bool(inverse))
+
+    @staticmethod
+    def backward(ctx, g):
+        (positions,) = ctx.saved_tensors
+        g = g if (g.stride(2) == 1 and g.stride(1) == g.shape[2]) else g.contiguous()
+        return C.rope(g, positions, float(ctx.theta), not ctx.inverse), None, None, None
+
+
 def rope(x, positions, theta, inverse=False):
-    return ref.rope(x, positions, theta, inverse)
+    if x.dtype != BF16 or x.dim() != 3 or x.shape[-1] not in (64, 128) or x.stride(2) != 1 or x.stride(1) != x.shape[2]:
+        return ref.rope(x, positions, theta, inverse)
+    return _Rope.apply(x, positions.to(torch.int32), theta, inverse)
 
 
 def kv_cache_write(k, v, k_cache, v_cache, slot_mapping):

@@ -63,6 +63,11 @@ def grouped_rmsnorm(x, w, n: int, eps: float = 1e-6):
 
 def swiglu_fp32(gate_up: torch.Tensor) -> torch.Tensor:
     """silu(gate)·up computed in fp32, rounded once to the input dtype (matches the engine's `silu_and_mul`)."""
+    if gate_up.is_cuda and gate_up.dtype == torch.bfloat16 and gate_up.shape[-1] % 16 == 0:
+        # the SwiGLU kernel reads bf16, computes silu(gate)·up in fp32 registers and rounds once: exactly this contract
+        from .. import ops
+
+        return ops.swiglu(gate_up.reshape(-1, gate_up.shape[-1])).reshape(*gate_up.shape[:-1], gate_up.shape[-1] // 2)
     g, u = gate_up.float().chunk(2, dim=-1)
     return (F.silu(g) * u).to(gate_up.dtype)
 

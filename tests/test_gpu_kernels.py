@@ -214,3 +214,28 @@ def test_qk_norm_rope_cache_matches_separate_ops(D, norm):
     torch.cuda.synchronize()
     assert torch.equal(q1, q2) and torch.equal(k1, k2)
     assert torch.equal(kc1, kc2) and torch.equal(vc1, vc2)
+
+
+@pytest.mark.parametrize("D,H,T", [(128, 8, 300), (64, 3, 17)])
+def test_rope_alone_and_swiglu_fp32(D, H, T):
+    """The stand-alone rotary kernel (forward, inverse, autograd) and the fp32-compute SwiGLU against their fp32 statements."""
+    from miles_b200.ops import extra
+
+    torch.manual_seed(4)
+    x = torch.randn(T, H, D, device="cuda").to(torch.bfloat16).requires_grad_()
+    pos = torch.randint(0, 40000, (T,), device="cuda", dtype=torch.int32)
+    y = _k().rope(x, pos, 1e6)
+    want = ref.rope(x.detach().float(), pos, 1e6)
+    assert _rel(y, want) < 1e-2
+    back = _k().rope(y.detach(), pos, 1e6, inverse=True)
+    assert _rel(back, x.detach().float()) < 2e-2                       # inverse rotation returns the input
+    g = torch.randn_like(y)
+    y.backward(g)
+    xf = x.detach().float().requires_grad_()
+    ref.rope(xf, pos, 1e6).backward(g.float())
+    assert _rel(x.grad, xf.grad) < 1e-2
+    strided = torch.randn(T, H * D + 64, device="cuda").to(torch.bfloat16)[:, : H * D].view(T, H, D)     # token stride ≠ H·D
+    assert _rel(_k().rope(strided, pos, 1e4), ref.rope(strided.float(), pos, 1e4)) < 1e-2
+    gu = torch.randn(T, 2 * 384, device="cuda").to(torch.bfloat16)
+    a, b = gu.float().chunk(2, -1)
+    assert _rel(extra.swiglu_fp32(gu), torch.nn.functional.silu(a) * b) < 1e-2
