@@ -96,10 +96,20 @@ void gemm_mxfp8(const at::Tensor& A, const at::Tensor& sa, const at::Tensor& B, 
         "mb_gemm_mxfp8");
 }
 
+// A [M_pad, K] / sa: expert-sorted rows (segments padded to 128); B [E, N, K] / sb [E, N, K/32]; tile_expert int32 [M_pad/128]
+void gemm_mxfp8_grouped(const at::Tensor& A, const at::Tensor& sa, const at::Tensor& B, const at::Tensor& sb, at::Tensor& C,
+                        const at::Tensor& tile_expert, at::Tensor& err) {
+  c10::cuda::CUDAGuard g(A.device());
+  check(mb_gemm_mxfp8_grouped(A.data_ptr(), sa.data_ptr(), B.data_ptr(), sb.data_ptr(), C.data_ptr(), A.size(0), B.size(1), A.size(1),
+                              B.size(0), tile_expert.data_ptr<int>(), C.stride(0), err.data_ptr<int>(), cur_stream()),
+        "mb_gemm_mxfp8_grouped");
+}
+
 }  // namespace
 
 void register_extra(pybind11::module& m) {
   m.def("gemm_mxfp8", &gemm_mxfp8);
+  m.def("gemm_mxfp8_grouped", &gemm_mxfp8_grouped);
   m.def("sparse_attention_fwd", &sparse_attention_fwd);
   m.def("grouped_rmsnorm", &grouped_rmsnorm);
   m.def("short_conv", &short_conv);

@@ -36,7 +36,17 @@ struct Params {
   int M, N, K;
   long long ldc;
   int* error_flag;
+  // grouped (MoE) form: rows of A are expert-sorted and padded to 128 per expert; tile_expert[m_blk] is the expert of each
+  // row block (−1: a block past the rows in use — computed against expert 0 and not stored, so that every role of the CTA
+  // walks the same tile sequence); B and its scales hold the experts stacked, N rows each.  null: one dense B.
+  const int* tile_expert;
 };
+
+__device__ __forceinline__ int b_row_base(const Params& p, int m_blk) {
+  if (p.tile_expert == nullptr) return 0;
+  const int e = p.tile_expert[m_blk];
+  return (e < 0 ? 0 : e) * p.N;
+}
 
 __global__ void __launch_bounds__(256, 1)
 gemm_mxfp8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b, Params p) {
@@ -82,7 +92,7 @@ gemm_mxfp8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
           if (!mbar_wait(&empty_bar[stage], phase ^ 1)) { *abort_flag = 1; atomicExch(p.error_flag, 31); break; }
           mbar_expect_tx(&full_bar[stage], kABytes + kBBytes);
           tma_load_2d(stage_ptr(stage), &tmap_a, &full_bar[stage], ks * BK, m_blk * BM);
-          tma_load_2d(stage_ptr(stage) + kABytes, &tmap_b, &full_bar[stage], ks * BK, n_blk * BN);
+          tma_load_2d(stage_ptr(stage) + kABytes, &tmap_b, &full_bar[stage], ks * BK, b_row_base(p, m_blk) + n_blk * BN);
           if (++stage == kStages) { stage = 0; phase ^= 1; }
         }
       }
@@ -99,11 +109,12 @@ gemm_mxfp8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
       if (item >= n_items) return;
       const int t = blockIdx.x + static_cast<int>(item / k_stages) * gridDim.x, ks = static_cast<int>(item % k_stages);
       const int blk = is_a ? t % m_tiles : t / m_tiles;
+      const int base = is_a ? 0 : b_row_base(p, t % m_tiles);       // stacked experts: rows of this tile's expert
 #pragma unroll
       for (int m1 = 0; m1 < 4; ++m1) {
         const int r = blk * 128 + m1 * 32 + lane;
         // rows past the matrix edge get scale 2^0: their operand rows are zero-filled, the products stay 0
-        w[m1] = r < limit ? __ldg(src32 + static_cast<long long>(r) * words_per_row + ks) : 0x7f7f7f7fu;
+        w[m1] = r < limit ? __ldg(src32 + static_cast<long long>(base + r) * words_per_row + ks) : 0x7f7f7f7fu;
       }
     };
     uint32_t cur[4][4], nxt[4][4];
@@ -177,6 +188,7 @@ gemm_mxfp8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
       const int m_blk = t % m_tiles, n_blk = t / m_tiles;
       if (!mbar_wait(&tmem_full[acc], acc_phase)) { *abort_flag = 1; atomicExch(p.error_flag, 34); break; }
       tc_fence_after();
+      const bool store = p.tile_expert == nullptr || p.tile_expert[m_blk] >= 0;
       const int row0 = m_blk * BM + q * 32;
       const uint32_t t_row = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + acc * BN;
       uint8_t* stage_tile = smem + kBarOff + 256 + q * 4096;
@@ -184,7 +196,7 @@ gemm_mxfp8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
 #pragma unroll 1
       for (int c2 = 0; c2 < BN / 64; ++c2) {
         const int colr = n_blk * BN + c2 * 64;
-        if (colr >= p.N) break;
+        if (colr >= p.N || !store) break;
         if (fast) {
           // 64 columns at a time through a 4 KB per-warp staging tile: every store instruction writes four full 128-byte lines
 #pragma unroll
@@ -287,11 +299,40 @@ extern "C" int mb_gemm_mxfp8(const void* A, const void* sa, const void* B, const
     if (e != cudaSuccess) return static_cast<int>(e);
     configured = true;
   }
-  Params p{static_cast<const uint8_t*>(sa), static_cast<const uint8_t*>(sb), static_cast<__nv_bfloat16*>(C), M, N, K, ldc, error_flag};
+  Params p{static_cast<const uint8_t*>(sa), static_cast<const uint8_t*>(sb), static_cast<__nv_bfloat16*>(C), M, N, K, ldc, error_flag, nullptr};
   int dev = 0, sms = 148;
   cudaGetDevice(&dev);
   cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
   const int tiles = ((M + BM - 1) / BM) * ((N + BN - 1) / BN);
+  gemm_mxfp8_kernel<<<tiles < sms ? tiles : sms, 256, kSmemTotal, stream>>>(ta, tb, p);
+  return static_cast<int>(cudaGetLastError());
+}
+
+// Grouped (MoE) form.  A [M_pad, K] e4m3, expert-sorted rows padded to 128 per expert, sa its 1×32 scales; B [E·N, K] e4m3 with
+// sb [E·N, K/32]; tile_expert [M_pad/128] (device) names the expert of every row block (−1: not in use, nothing stored);
+// C [M_pad, N] bf16.  N must be a multiple of 128 so that a B tile never straddles two experts.
+extern "C" int mb_gemm_mxfp8_grouped(const void* A, const void* sa, const void* B, const void* sb, void* C, int M_pad, int N, int K, int E,
+                                     const int* tile_expert, long long ldc, int* error_flag, cudaStream_t stream) {
+  using namespace mb::mx;
+  if (M_pad <= 0 || N <= 0 || E <= 0) return 0;
+  if (K % 128 || K == 0 || N % BN || M_pad % BM) return -1;
+  CUtensorMap ta, tb;
+  int r = make_tmap_u8_2d(&ta, A, M_pad, K, K);
+  if (r) return 1000 + r;
+  r = make_tmap_u8_2d(&tb, B, static_cast<long long>(E) * N, K, K);
+  if (r) return 2000 + r;
+  static bool configured = false;
+  if (!configured) {
+    cudaError_t e = cudaFuncSetAttribute(gemm_mxfp8_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemTotal);
+    if (e != cudaSuccess) return static_cast<int>(e);
+    configured = true;
+  }
+  Params p{static_cast<const uint8_t*>(sa), static_cast<const uint8_t*>(sb), static_cast<__nv_bfloat16*>(C), M_pad, N, K, ldc, error_flag,
+           tile_expert};
+  int dev = 0, sms = 148;
+  cudaGetDevice(&dev);
+  cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+  const int tiles = (M_pad / BM) * (N / BN);
   gemm_mxfp8_kernel<<<tiles < sms ? tiles : sms, 256, kSmemTotal, stream>>>(ta, tb, p);
   return static_cast<int>(cudaGetLastError());
 }

@@ -192,6 +192,8 @@ int mb_gather_rows_host(const void* table_dev, const long long* ids, void* out, 
 // ---- gemm_mxfp8.cu (block-scaled: e4m3 payload [rows, K] + e8m0 scales [rows, K/32]; K % 128 == 0) ----
 int mb_gemm_mxfp8(const void* A, const void* sa, const void* B, const void* sb, void* C, int M, int N, int K, long long ldc,
                   int* error_flag, cudaStream_t stream);
+int mb_gemm_mxfp8_grouped(const void* A, const void* sa, const void* B, const void* sb, void* C, int M_pad, int N, int K, int E,
+                          const int* tile_expert, long long ldc, int* error_flag, cudaStream_t stream);
 
 // ---- sparse_attn.cu ----
 int mb_sparse_attention_fwd(const void* q, const void* k, const void* v, const int* indices, const float* sink, void* out, float* lse,

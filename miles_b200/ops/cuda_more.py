@@ -193,6 +193,23 @@ def experts_forward(x_perm, w13, w2, seg, tile, bt: int = 128):
         C.swiglu_fwd(h1, act, seg[-1:])
         C.gemm_small_grouped(act, w2, y_perm, max_rows, H, F2 // 2, E, tile, seg[-1:], bt)
         return h1, y_perm
+    from . import cuda as _cuda
+
+    if _cuda.MXFP8_LINEAR and H % 128 == 0 and F2 % 256 == 0:
+        # --fp8-recipe mxfp8: the expert GEMMs of the forward run block-scaled (activations quantised per call, expert weights
+        # once per call); the backward uses the bf16 grouped GEMMs on the unquantised operands (straight-through), like the
+        # dense projections of this recipe
+        from . import extra
+
+        F = F2 // 2
+        xq, xs = mxfp8_quant(x_perm)
+        wq, ws = mxfp8_quant(w13.reshape(E * F2, H))
+        extra.gemm_mxfp8_grouped(xq, xs, wq.view(E, F2, H), ws.view(E, F2, H // 32), tile, out=h1)
+        C.swiglu_fwd(h1, act, seg[-1:])
+        aq, as_ = mxfp8_quant(act)
+        w2q, w2s = mxfp8_quant(w2.reshape(E * H, F))
+        extra.gemm_mxfp8_grouped(aq, as_, w2q.view(E, H, F), w2s.view(E, H, F // 32), tile, out=y_perm)
+        return h1, y_perm
     C.gemm_grouped(x_perm, w13, h1, max_rows, F2, H, E, tile, False, 0)
     C.swiglu_fwd(h1, act, seg[-1:])
     C.gemm_grouped(act, w2, y_perm, max_rows, H, F2 // 2, E, tile, False, 0)
@@ -254,12 +271,7 @@ class _MoEFFN(torch.autograd.Function):
         x_perm = torch.empty(max_rows, H, dtype=x.dtype, device=x.device)
         publish_limit(LIMIT_MOE_PAIRS, x.shape[0] * k)
         C.moe_gather(x, x_perm, row_src, seg, k)
-        h1 = torch.empty(max_rows, F2, dtype=x.dtype, device=x.device)
-        C.gemm_grouped(x_perm, w13, h1, max_rows, F2, H, E, tile, False, 0)
-        act = torch.empty(max_rows, F, dtype=x.dtype, device=x.device)
-        C.swiglu_fwd(h1, act, seg[-1:])
-        y_perm = torch.empty(max_rows, H, dtype=x.dtype, device=x.device)
-        C.gemm_grouped(act, w2, y_perm, max_rows, H, F, E, tile, False, 0)
+        h1, y_perm = experts_forward(x_perm, w13, w2, seg, tile)        # bf16 grouped GEMMs, or block-scaled under the MXFP8 recipe
         out = torch.empty(T, H, dtype=x.dtype, device=x.device)
         C.moe_combine(y_perm, wf, dst_row, out, k)
         ctx.save_for_backward(x, w13, w2, wf, seg, tile, row_src, dst_row, h1, y_perm)

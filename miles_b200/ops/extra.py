@@ -282,6 +282,35 @@ def gemm_mxfp8(a_q, a_s, b_q, b_s, out: torch.Tensor | None = None) -> torch.Ten
     return res
 
 
+def gemm_mxfp8_grouped(a_q, a_s, b_q, b_s, tile_expert, out: torch.Tensor | None = None) -> torch.Tensor:
+    """Grouped (MoE) block-scaled product.  a_q [M_pad, K] e4m3 with scales [M_pad, K/32]: expert-sorted rows whose segments are
+    padded to 128; b_q [E, N, K] with scales [E, N, K/32]; `tile_expert` int32 [M_pad/128] names the expert of every row block
+    (−1: block not in use, left untouched).  C [M_pad, N] bf16; N % 128 == 0, K % 128 == 0."""
+    M, K = a_q.shape
+    E, N, _ = b_q.shape
+    if a_q.is_cuda and K % 128 == 0 and N % 128 == 0 and M % 128 == 0:
+        from . import cuda
+
+        if out is None:
+            out = torch.empty(M, N, dtype=torch.bfloat16, device=a_q.device)
+        cuda.C.gemm_mxfp8_grouped(a_q.contiguous().view(torch.uint8), a_s.contiguous(), b_q.contiguous().view(torch.uint8), b_s.contiguous(),
+                                  out, tile_expert, cuda.C.error_flag(out))
+        return out
+    from . import reference as ref
+
+    res = torch.zeros(M, N, dtype=torch.float32, device=a_q.device) if out is None else out.float()
+    a = ref.mxfp8_dequant(a_q, a_s).reshape(M, K).float()
+    for blk, e in enumerate(tile_expert.tolist()):
+        if e >= 0:
+            b = ref.mxfp8_dequant(b_q[e], b_s[e]).reshape(N, K).float()
+            res[blk * 128:(blk + 1) * 128] = a[blk * 128:(blk + 1) * 128] @ b.t()
+    res = res.bfloat16()
+    if out is not None:
+        out.copy_(res)
+        return out
+    return res
+
+
 def linear_mxfp8(x: torch.Tensor, w_q: torch.Tensor, w_s: torch.Tensor) -> torch.Tensor:
     """y = x·Wᵀ with W held in MXFP8 (weights quantised once, e.g. by the weight sync) and x quantised on the fly."""
     from .. import ops

@@ -296,3 +296,60 @@ def test_extend_attention_separate_query_and_key_sequences(case, heads):
     want = ref.paged_attention(q.float(), kc.float(), vc.float(), bt, sl, q_lens=ql)
     assert _k().check_error_flag() == 0
     assert _rel(got, want) < 2e-2, _rel(got, want)
+
+
+def test_grouped_mxfp8_gemm_and_moe_forward():
+    """The grouped (MoE) block-scaled GEMM against the fp32 product of the dequantised operands, with uneven expert
+    segments, an unused expert and unused row blocks; then the MoE layer forward under the MXFP8 recipe against bf16."""
+    from miles_b200.ops import cuda as K
+    from miles_b200.ops import extra
+
+    torch.manual_seed(7)
+    E, N, Kd = 5, 256, 512
+    rows = [300, 0, 128, 17, 260]                                  # tokens per expert
+    pad = [(r + 127) // 128 * 128 for r in rows]
+    M_pad = sum(pad) + 256                                         # two unused row blocks at the end
+    tile_expert = torch.full((M_pad // 128,), -1, dtype=torch.int32)
+    a = torch.zeros(M_pad, Kd)
+    at = 0
+    for e, (r, p) in enumerate(zip(rows, pad)):
+        a[at:at + r] = torch.randn(r, Kd)
+        tile_expert[at // 128:(at + p) // 128] = e
+        at += p
+    a = a.cuda().to(torch.bfloat16)
+    b = (torch.randn(E, N, Kd) * 0.5).cuda().to(torch.bfloat16)
+    tile_expert = tile_expert.cuda()
+    aq, as_ = _k().mxfp8_quant(a)
+    bq, bs = _k().mxfp8_quant(b.reshape(E * N, Kd))
+    out = torch.full((M_pad, N), 7.0, dtype=torch.bfloat16, device="cuda")
+    extra.gemm_mxfp8_grouped(aq, as_, bq.view(E, N, Kd), bs.view(E, N, Kd // 32), tile_expert, out=out)
+    assert K.check_error_flag() == 0
+    a_d = ref.mxfp8_dequant(aq.cpu(), as_.cpu()).reshape(M_pad, Kd).float()
+    b_d = ref.mxfp8_dequant(bq.cpu(), bs.cpu()).reshape(E, N, Kd).float()
+    at = 0
+    for e, (r, p) in enumerate(zip(rows, pad)):
+        if r:
+            want = a_d[at:at + r] @ b_d[e].t()
+            assert _rel(out[at:at + r].float().cpu(), want) < 1e-2, e
+        at += p
+    assert bool((out[at:] == 7.0).all())                           # unused row blocks are not written
+    # the MoE layer under the recipe: forward close to bf16 (quantisation noise), backward identical (straight-through)
+    T, H, F, k = 700, 256, 128, 2
+    x = torch.randn(T, H, device="cuda").to(torch.bfloat16).requires_grad_()
+    w13 = (torch.randn(E, 2 * F, H, device="cuda") * 0.05).to(torch.bfloat16).requires_grad_()
+    w2 = (torch.randn(E, H, F, device="cuda") * 0.05).to(torch.bfloat16).requires_grad_()
+    idx = torch.stack([torch.randperm(E)[:k] for _ in range(T)]).cuda().to(torch.int32)
+    tw = torch.rand(T, k, device="cuda")
+    outs = {}
+    for flag in (False, True):
+        K.MXFP8_LINEAR = flag
+        try:
+            y = _k().moe_ffn(x, w13, w2, tw, idx)
+            y.float().pow(2).sum().backward()
+            outs[flag] = (y.detach().float(), x.grad.clone(), w13.grad.clone())
+            x.grad = w13.grad = w2.grad = None
+        finally:
+            K.MXFP8_LINEAR = False
+    # e4m3 keeps 3 mantissa bits: two chained products of quantised operands land within ≈ 7 % of bf16
+    assert 1e-3 < _rel(outs[True][0], outs[False][0]) < 0.1        # really quantised, and close
+    assert _rel(outs[True][1], outs[False][1]) < 0.15 and _rel(outs[True][2], outs[False][2]) < 0.15
