@@ -49,6 +49,9 @@ def parse():
                         "training activations. Too small a KV cache caps how many of the 64 requests decode at once.")
     p.add_argument("--no-fused", action="store_true", help="NCCL + separate GEMM baseline instead of the fused kernels")
     p.add_argument("--no-cuda-graph", action="store_true")
+    p.add_argument("--fp8-recipe", choices=["none", "mxfp8"], default="none",
+                   help="mxfp8: forward projections (dense and expert) on the block-scaled tensor-core path, backward in bf16 — the "
+                        "secondary MXFP8 training config; the headline run is bf16")
     p.add_argument("--quiet", action="store_true")
     return p.parse_args()
 
@@ -181,7 +184,8 @@ def main():
             f"--rollout-max-response-len {a.max_new_tokens} --num-rollout 1000000 --rm-type last_mod7 --lr 1e-6 --colocate "
             f"--advantage-estimator grpo --eps-clip 0.2 --use-dynamic-batch-size --max-tokens-per-gpu {a.max_tokens_per_gpu} "
             f"--recompute-granularity full --use-rollout-routing-replay --balance-data "
-            f"--expert-model-parallel-size {world} --rollout-temperature 1.0 --rollout-data-exchange local")
+            f"--expert-model-parallel-size {world} --rollout-temperature 1.0 --rollout-data-exchange local"
+            + (" --fp8-recipe mxfp8" if a.fp8_recipe == "mxfp8" else ""))
     args = parse_args(argv.split())
     args.rollout_stop_token_ids = stop_ids
 
@@ -296,7 +300,8 @@ def main():
         out = {
             "metric": "GRPO tokens/s/box (rollout+train+weight-sync)", "value": value, "unit": "tokens/s", "n_gpus": world,
             "steps": a.steps, "warmup": a.warmup, "ms_per_step": dev_ms / a.steps, "higher_is_better": True, "scaling": "weak",
-            "vs_baseline": (value / BASELINE_TOKENS_PER_S) if BASELINE_TOKENS_PER_S else None, "dtype": "bf16",
+            "vs_baseline": (value / BASELINE_TOKENS_PER_S) if BASELINE_TOKENS_PER_S else None,
+            "dtype": "bf16" if a.fp8_recipe == "none" else "mxfp8 forward (e4m3, 1x32 e8m0 scales) + bf16 backward",
             "data": "synthetic prompts (uniform random ids), random-init weights, rule reward (last id mod 7 == 0)",
             "config": {
                 "model": f"{cfg.name}-shaped MoE: {cfg.num_layers} layers, hidden {cfg.hidden_size}, {cfg.num_heads}q/{cfg.num_kv_heads}kv "

@@ -287,7 +287,8 @@ def linear(x, w, bias=None):
 
             y = extra.linear_mxfp8(x, reg[0].view(w.shape), reg[1].view(w.shape[0], -1))
             return y if bias is None else y + bias
-    if MXFP8_LINEAR and w.dim() == 2 and w.shape[1] % 128 == 0 and w.shape[0] >= 128:
+    # per-call weight quantisation only pays for itself on training-sized batches: decode-sized calls stay on the bf16 kernels
+    if MXFP8_LINEAR and w.dim() == 2 and w.shape[1] % 128 == 0 and w.shape[0] >= 128 and x.numel() // x.shape[-1] >= MXFP8_MIN_ROWS:
         return _LinearMXFP8.apply(x, w, bias)
     return _Linear.apply(x, w, bias)
 

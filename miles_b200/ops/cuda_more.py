@@ -195,7 +195,7 @@ def experts_forward(x_perm, w13, w2, seg, tile, bt: int = 128):
         return h1, y_perm
     from . import cuda as _cuda
 
-    if _cuda.MXFP8_LINEAR and H % 128 == 0 and F2 % 256 == 0:
+    if _cuda.MXFP8_LINEAR and H % 128 == 0 and F2 % 256 == 0 and max_rows >= 8 * _cuda.MXFP8_MIN_ROWS:
         # --fp8-recipe mxfp8: the expert GEMMs of the forward run block-scaled (activations quantised per call, expert weights
         # once per call); the backward uses the bf16 grouped GEMMs on the unquantised operands (straight-through), like the
         # dense projections of this recipe

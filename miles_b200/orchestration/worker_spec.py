@@ -99,11 +99,12 @@ class PortAllocator:
 
 
 def plan(specs: list, nodes: dict[str, int], colocate: bool = False, ports: PortAllocator | None = None,
-         master_addr: str = "127.0.0.1") -> list[PlannedWorker]:
+         master_addr: str = "127.0.0.1", first_slot: int = 0) -> list[PlannedWorker]:
     """Assign GPU slots to every worker of every pool.  `colocate`: pools overlap on the same slots (layout =
-    max over pools), otherwise pools take consecutive disjoint slot ranges (layout = sum)."""
+    max over pools), otherwise pools take consecutive disjoint slot ranges (layout = sum).  `first_slot`: slots before it
+    belong to someone else (the trainer's ranks of a disaggregated job)."""
     ports = ports or PortAllocator()
-    slots = sorted_slots(nodes)
+    slots = sorted_slots(nodes)[first_slot:]
     out: list[PlannedWorker] = []
     cursor = 0
     for spec in specs:

@@ -212,8 +212,13 @@ def engine_spec(args, n: int) -> CommandWorkerSpec:
         cmd += ["--model-name", args.model_name]
     if getattr(args, "fp32", False):
         cmd += ["--device", "cpu"]
+        return CommandWorkerSpec("engine", cmd, SchedulingSpec(num_cells=n, workers_per_cell=1, gpus_per_worker=0))
+    # every GPU stays visible to the server and it is told which one is its own: device indices then mean the same in the
+    # trainer and in the engine, which is what CUDA-IPC weight buckets rely on
+    cmd += ["--device", "cuda:{gpu_ids}"]
     gpus = float(getattr(args, "rollout_num_gpus_per_engine", 1) or 1)
-    return CommandWorkerSpec("engine", cmd, SchedulingSpec(num_cells=n, workers_per_cell=1, gpus_per_worker=0 if getattr(args, "fp32", False) else gpus))
+    return CommandWorkerSpec("engine", cmd, SchedulingSpec(num_cells=n, workers_per_cell=1, gpus_per_worker=gpus),
+                             env={"CUDA_VISIBLE_DEVICES": "__inherit__"})
 
 
 def router_spec(args) -> CommandWorkerSpec:
@@ -230,7 +235,10 @@ def launch_fleet(args, log_dir: str | None = None, on_restart=None) -> Fleet:
         specs = [engine_spec(args, int(getattr(args, "rollout_num_engines", 1) or 1))]
         if not router_url:
             specs.append(router_spec(args))
-        manager.launch(specs, colocate=True)
+        # colocated: engines share the trainer's GPUs (slot i ↔ rank i); disaggregated: they take the GPUs after the trainer's
+        trainer_gpus = 0 if getattr(args, "colocate", False) or getattr(args, "fp32", False) else \
+            int(getattr(args, "actor_num_nodes", 1) or 1) * int(getattr(args, "actor_num_gpus_per_node", 1) or 1)
+        manager.launch(specs, colocate=True, first_slot=trainer_gpus)
         cells = manager.get_cell_infos()
         for cid, c in cells.items():
             wait_healthy(c.workers[0].url(), 300.0)

@@ -58,11 +58,12 @@ class WorkerManager:
         self.ports = PortAllocator(host=host)
 
     # ---- launch ------------------------------------------------------------------------------------------------
-    def launch(self, specs: list, nodes: dict[str, int] | None = None, colocate: bool = False, dry_run: bool = False) -> list[dict]:
+    def launch(self, specs: list, nodes: dict[str, int] | None = None, colocate: bool = False, dry_run: bool = False,
+               first_slot: int = 0) -> list[dict]:
         nodes = nodes or {"local": max(1, _gpu_count())}
         described = []
         with self.lock:
-            for w in plan(specs, nodes, colocate=colocate, ports=self.ports, master_addr=self.host):
+            for w in plan(specs, nodes, colocate=colocate, ports=self.ports, master_addr=self.host, first_slot=first_slot):
                 cell = self.cells.setdefault(cell_name(w.pool, w.cell), _Cell(w.pool, w.cell))
                 cell.workers.append(_Worker(w))
                 described.append({"name": worker_name(w.pool, w.cell, w.rank), "cmd": self._command(w), "env": w.env, "ports": w.ports})
@@ -85,6 +86,11 @@ class WorkerManager:
         w = wk.planned
         env = {**os.environ, **w.env, "MILES_WORKER_NAME": worker_name(w.pool, w.cell, w.rank),
                "MILES_WORKER_GENERATION": str(cell.generation)}
+        for k in [k for k, v in env.items() if v == "__inherit__"]:      # a spec may hand a planner-set variable back to the parent's value
+            if k in os.environ:
+                env[k] = os.environ[k]
+            else:
+                del env[k]
         out = None
         if self.log_dir:
             os.makedirs(self.log_dir, exist_ok=True)

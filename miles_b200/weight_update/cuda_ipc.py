@@ -72,7 +72,12 @@ def open_bucket(blob: str, device) -> tuple[torch.Tensor, list]:
     d = pickle.loads(base64.b64decode(blob))
     if d["kind"] == "ipc":
         fn, args = d["rebuild"]
-        return fn(*args), d["manifest"]
+        flat = fn(*args)
+        if device is not None and flat.device != torch.device(device):
+            # the sender's buffer lives on another GPU: ONE device-to-device copy of the whole bucket over NVLink (a DMA
+            # transfer, no kernel reads peer memory), then everything downstream works on local memory
+            flat = flat.to(device)
+        return flat, d["manifest"]
     flat = torch.load(io.BytesIO(d["data"]), map_location=device, weights_only=True)
     return flat, d["manifest"]
 

@@ -334,7 +334,7 @@ def test_grouped_mxfp8_gemm_and_moe_forward():
         at += p
     assert bool((out[at:] == 7.0).all())                           # unused row blocks are not written
     # the MoE layer under the recipe: forward close to bf16 (quantisation noise), backward identical (straight-through)
-    T, H, F, k = 700, 256, 128, 2
+    T, H, F, k = 1400, 256, 128, 2
     x = torch.randn(T, H, device="cuda").to(torch.bfloat16).requires_grad_()
     w13 = (torch.randn(E, 2 * F, H, device="cuda") * 0.05).to(torch.bfloat16).requires_grad_()
     w2 = (torch.randn(E, H, F, device="cuda") * 0.05).to(torch.bfloat16).requires_grad_()

@@ -377,3 +377,41 @@ def _case_reshard_proxy(rank, world):
     import test_reshard
 
     test_reshard._case_reshard(rank, world)
+
+
+@pytest.mark.gpu
+def test_disaggregated_engine_process_on_another_gpu(tmp_path):
+    """Trainer on GPU 0, an engine server process on GPU 1 launched by the fleet (placed after the trainer's GPU); weights
+    travel as CUDA-IPC buckets (one device-to-device copy per bucket into the engine's GPU) and a rollout comes back."""
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs 2 GPUs")
+    from miles_b200.args import parse_args
+    from miles_b200.engine.server import weight_checksums
+    from miles_b200.orchestration.wiring import create_parallel_state, create_rollout_components, create_training_models, update_weights
+    from miles_b200.utils import object_store
+
+    args = parse_args(("--model-name tiny --rollout-batch-size 4 --n-samples-per-prompt 2 --rollout-max-response-len 8 --num-rollout 1 "
+                       "--rm-type even_fraction --lr 1e-4 --advantage-estimator grpo --actor-num-nodes 1 --actor-num-gpus-per-node 1 "
+                       "--data-source-path miles_b200.rollout.data_source.SyntheticSource --synthetic-prompt-len 4 6 "
+                       "--rollout-engine http --worker-provider local --rollout-num-engines 1 --update-weight-transfer-mode tensor "
+                       f"--worker-log-dir {tmp_path}/logs").split())
+    ps = create_parallel_state(args)
+    actor, _, _ = create_training_models(args, ps)
+    rollout = create_rollout_components(args, ps, actor)
+    fleet = rollout.fleet
+    try:
+        info = fleet.manager.get_cell_infos()["engine-c0"]
+        assert fleet.manager.cells["engine-c0"].workers[0].planned.slots[0].gpu == 1          # after the trainer's GPU
+        update_weights(args, actor, rollout)
+        eng = rollout.engines[0]
+        out = eng._post("weights_checker", {"action": "compare", "checksums": weight_checksums(actor.model)})
+        assert out == {"success": True, "mismatched": []}, (out, fleet.manager.log_tail("engine-c0-w0"))
+        assert eng.get_server_info()["weight_version"] == actor.weight_version
+        pack = rollout.executor.get(0)
+        shard = object_store.get(pack.data_ref)
+        assert len(shard["tokens"]) == 8
+        m = actor.train(0, shard)
+        assert m["train/grad_norm"] > 0 and m["train/train_rollout_logprob_abs_diff"] < 5e-2
+        del info
+    finally:
+        fleet.shutdown()
