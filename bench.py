@@ -279,6 +279,12 @@ def main():
     ev0.record()
     for i in range(a.steps):
         step(a.warmup + i)
+        if rank == 0 and not a.quiet:
+            # progress on stderr (host clock, this rank): what a reader has if the run is stopped before the JSON line
+            el = time.perf_counter() - wall0
+            print(f"[step {i + 1}/{a.steps}] elapsed={el:.1f}s s/step={el / (i + 1):.2f} tokens={counters['tokens']} "
+                  f"tokens/s={counters['tokens'] / el:.0f} rollout={counters['rollout_s']:.1f}s train={counters['train_s']:.1f}s",
+                  file=sys.stderr, flush=True)
     ev1.record()
     if world > 1:
         dist.barrier()

@@ -124,7 +124,7 @@ def plan(specs: list, nodes: dict[str, int], colocate: bool = False, ports: Port
                    "CUDA_VISIBLE_DEVICES": ",".join(str(s.gpu) for s in mine), **{k: str(v) for k, v in spec.env.items()}}
             cmd = None
             if isinstance(spec, CommandWorkerSpec):
-                fmt = dict(rank=rank, world_size=sch.workers_per_cell, gpu_ids=env["CUDA_VISIBLE_DEVICES"], master_port=master_port + cell,
+                fmt = dict(rank=rank, world_size=sch.workers_per_cell, gpu_ids=",".join(str(s.gpu) for s in mine), master_port=master_port + cell,
                            cell=cell, **wports)
                 cmd = [c.format(**fmt) for c in spec.command]
             out.append(PlannedWorker(spec.name, cell, rank, w, mine, env, cmd, wports, spec))

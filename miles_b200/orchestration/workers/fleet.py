@@ -186,12 +186,16 @@ def torch_empty_u8(n: int, device):
     return torch.empty(n, dtype=torch.uint8, device=device)
 
 
-def wait_healthy(url: str, timeout: float = 180.0):
+def wait_healthy(url: str, timeout: float = 180.0, alive=None):
+    """Poll `url`/health; `alive()` (optional) says whether the process behind it still runs — a worker that died at start-up
+    fails the wait at once instead of after the timeout."""
     import requests
 
     end = time.monotonic() + timeout
     last = None
     while time.monotonic() < end:
+        if alive is not None and not alive():
+            raise RuntimeError(f"the worker behind {url} exited before it became healthy")
         try:
             if requests.get(f"{url}/health", timeout=2).status_code == 200:
                 return
@@ -241,7 +245,12 @@ def launch_fleet(args, log_dir: str | None = None, on_restart=None) -> Fleet:
         manager.launch(specs, colocate=True, first_slot=trainer_gpus)
         cells = manager.get_cell_infos()
         for cid, c in cells.items():
-            wait_healthy(c.workers[0].url(), 300.0)
+            try:
+                wait_healthy(c.workers[0].url(), 300.0, alive=lambda cid=cid: manager.cells[cid].alive())
+            except Exception as e:
+                tail = manager.log_tail(c.workers[0].name, 30)
+                manager.stop_all()
+                raise RuntimeError(f"{cid} did not start: {e}\n{tail}") from e
             if c.pool == "engine":
                 engines[cid] = RemoteEngine(c.workers[0].url(), c.workers[0].name, c.generation)
             elif c.pool == "router":
