@@ -35,6 +35,7 @@ class PrefixCache:
         self.root = _Node(None, None, None)
         self.clock = itertools.count(1)
         self.num_nodes = 0
+        self.num_unpinned = 0                 # nodes nobody uses; kept incrementally: the scheduler asks every step
         self.stats = {"hit_tokens": 0, "lookup_tokens": 0, "inserted_blocks": 0, "evicted_blocks": 0}
 
     # ---- lookup ------------------------------------------------------------------------------------------------
@@ -55,7 +56,7 @@ class PrefixCache:
         nodes = self.match(tokens, max_blocks)
         t = next(self.clock)
         for n in nodes:
-            n.users += 1
+            self._pin(n)
             n.last_used = t
         if nodes:
             self.allocator.share([n.block for n in nodes])
@@ -67,13 +68,21 @@ class PrefixCache:
         """The request is done with the matched nodes (its allocator references are released by the caller as usual)."""
         for n in nodes:
             n.users -= 1
+            if n.users == 0 and n.parent is not None:       # nodes dropped by `reset` are no longer counted
+                self.num_unpinned += 1
+
+    def _pin(self, n: _Node) -> None:
+        if n.users == 0 and n.parent is not None:
+            self.num_unpinned -= 1
+        n.users += 1
 
     # ---- insertion -----------------------------------------------------------------------------------------------
     def insert(self, tokens: list[int], blocks: list[int]) -> list[_Node]:
         """Register the full blocks of a sequence whose KV sits in `blocks` (block i holds tokens [i·bs, (i+1)·bs)).
-        Chains that exist are kept (first writer wins: the KV is identical by construction).  Returns the nodes that own
-        one of the GIVEN blocks — a live request must `pin` those, since it keeps using them."""
-        bs, node, mine = self.bs, self.root, []
+        Chains that exist are kept (first writer wins: the KV is identical by construction).  Returns the WHOLE chain of
+        nodes for this sequence; a live request pins all of them — also those that own another request's block for the
+        same content — so that pinned nodes always form a prefix of the tree and "unpinned" means "evictable"."""
+        bs, node, chain = self.bs, self.root, []
         t = next(self.clock)
         for i in range(min(len(tokens) // bs, len(blocks))):
             key = tuple(tokens[i * bs:(i + 1) * bs])
@@ -83,34 +92,22 @@ class PrefixCache:
                 node.children[key] = child
                 self.allocator.share([blocks[i]])
                 self.num_nodes += 1
+                self.num_unpinned += 1
                 self.stats["inserted_blocks"] += 1
-            if child.block == blocks[i]:
-                mine.append(child)
-            # else: the same content lives in another block already; the caller's private copy stays private
+            chain.append(child)
             child.last_used = t
             node = child
-        return mine
+        return chain
 
     def pin(self, nodes: list[_Node]) -> None:
         for n in nodes:
-            n.users += 1
+            self._pin(n)
 
     # ---- eviction -------------------------------------------------------------------------------------------------
     def evictable(self) -> int:
-        """Blocks that could be freed now: nodes with no user in their whole subtree."""
-        return self._count_unpinned(self.root)
-
-    def _count_unpinned(self, n) -> int:
-        total = 0
-        for c in n.children.values():
-            sub = self._count_unpinned(c)
-            total += sub
-            if c.users == 0 and sub == self._size(c) - 1:
-                total += 1
-        return total
-
-    def _size(self, n) -> int:
-        return 1 + sum(self._size(c) for c in n.children.values())
+        """Blocks that could be freed now.  Requests pin prefixes of the tree, so a node nobody pins has no pinned node below
+        it: every unpinned node can go (leaves first)."""
+        return self.num_unpinned
 
     def evict(self, num_blocks: int) -> int:
         """Free up to `num_blocks` blocks, least recently used leaves first.  Returns how many were freed."""
@@ -126,6 +123,7 @@ class PrefixCache:
                 del n.parent.children[n.key]
                 self.allocator.release([n.block])
                 self.num_nodes -= 1
+                self.num_unpinned -= 1
                 freed += 1
         self.stats["evicted_blocks"] += freed
         return freed
@@ -148,7 +146,9 @@ class PrefixCache:
             node = stack.pop()
             stack.extend(node.children.values())
             self.allocator.release([node.block])
+            node.parent = None
             n += 1
         self.root = _Node(None, None, None)
         self.num_nodes = 0
+        self.num_unpinned = 0
         return n

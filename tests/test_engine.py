@@ -273,3 +273,45 @@ def test_eviction_under_pressure_keeps_serving():
     assert eng.prefix_cache.stats["evicted_blocks"] > 0 and eng.stats["retractions"] == 0
     again = eng.generate([5 + 11] * 30 + [40 + 11], dict(sp))
     assert again["output_ids"] == outs[11] and again["meta_info"]["cached_tokens"] > 0
+
+
+def test_prefix_cache_unpinned_count_stays_exact():
+    """The scheduler reads `evictable()` every step, so it is a counter: it must equal a walk of the tree through inserts,
+    pins by two requests with a common prefix, a reset under a live request, and evictions."""
+    from miles_b200.engine.prefix_cache import PrefixCache
+
+    class Alloc:
+        def __init__(self):
+            self.refs = {}
+
+        def share(self, blocks):
+            for b in blocks:
+                self.refs[b] = self.refs.get(b, 0) + 1
+
+        def release(self, blocks):
+            for b in blocks:
+                self.refs[b] -= 1
+
+    def walk(c):
+        stack, n = list(c.root.children.values()), 0
+        while stack:
+            x = stack.pop()
+            stack.extend(x.children.values())
+            n += x.users == 0
+        return n
+
+    a = Alloc()
+    c = PrefixCache(a, 2)
+    t1, t2 = [1, 2, 3, 4, 5, 6], [1, 2, 3, 4, 9, 9]
+    n1 = c.insert(t1, [10, 11, 12]); c.pin(n1)
+    n2 = c.insert(t2, [20, 21, 22]); c.pin(n2)          # shares two nodes that own request 1's blocks
+    assert c.evictable() == walk(c) == 0 and c.num_nodes == 4
+    c.unpin(n1)
+    assert c.evictable() == walk(c) == 1                 # only request 1's private tail
+    assert c.evict(5) == 1 and c.evictable() == walk(c) == 0
+    c.reset()
+    c.unpin(n2)                                          # the request finishes after the reset
+    assert c.evictable() == walk(c) == 0 and c.num_nodes == 0
+    n3 = c.insert(t1, [30, 31, 32])
+    assert c.evictable() == walk(c) == 3
+    assert c.evict(2) == 2 and c.evictable() == walk(c) == 1
