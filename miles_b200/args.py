@@ -223,10 +223,12 @@ def build_parser() -> argparse.ArgumentParser:
     _bool_flag(g, "--use-dynamic-batch-size")
     g.add_argument("--max-tokens-per-gpu", type=int, default=None)
     _bool_flag(g, "--balance-data")
-    g.add_argument("--rollout-data-exchange", choices=["gather", "local"], default="gather",
+    g.add_argument("--rollout-data-exchange", choices=["gather", "local", "balanced"], default="gather",
                    help="gather: every rank receives all samples of the step and takes its (balanced) share; local: with one "
                         "engine per data-parallel rank each rank trains on the samples it generated (whole prompt groups "
-                        "stay together, nothing but a few metric sums crosses ranks)")
+                        "stay together, nothing but a few metric sums crosses ranks); balanced: local, then the ranks with "
+                        "the most tokens hand whole prompt groups to those with the fewest (point to point) until no move "
+                        "narrows the spread: every rank waits for the slowest one at each collective of the train step")
     g.add_argument("--log-probs-max-tokens-per-gpu", type=int, default=None)
     g.add_argument("--data-source-path", type=str, default="miles_b200.rollout.data_source.RolloutDataSourceWithBuffer")
     g.add_argument("--synthetic-prompt-len", type=int, nargs=2, default=None, metavar=("MIN", "MAX"),

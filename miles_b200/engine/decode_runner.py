@@ -67,7 +67,11 @@ class DecodeRunner:
         self.h_lp = torch.zeros(R, dtype=torch.float32).pin_memory()
         self.h_routed = torch.zeros(R, max(self.n_moe, 1), max(self.topk, 1), dtype=torch.int32).pin_memory()
         # histories of a multi-step call: [step, row]
-        self.max_steps = 8
+        self.max_steps = 32
+        self.chunk_steps = 8                  # outputs come back to the host in chunks of this many steps
+        self._chunks: list = []               # [(first step not yet on the host after this chunk, event)] of the last call
+        self._on_host = 0
+        self._events = [torch.cuda.Event() for _ in range(self.max_steps // self.chunk_steps + 1)]
         S = self.max_steps
         self.hist_tok = torch.zeros(S, R, dtype=torch.int64, device=self.dev)
         self.hist_lp = torch.zeros(S, R, dtype=torch.float32, device=self.dev)
@@ -206,6 +210,7 @@ class DecodeRunner:
         e.stats["h2d_bytes"] = e.stats.get("h2d_bytes", 0) + self.h_i32.numel() * 4 + self.h_i64.numel() * 8 + 5 * self.max_rows
         key = (B, record)
         steps = max(1, min(int(steps), self.max_steps))
+        self._chunks, self._on_host = [], 0
         for k in range(steps):
             if self.use_graph:
                 if key not in self.graphs:
@@ -218,17 +223,11 @@ class DecodeRunner:
                 self._forward(B, record)
             if steps > 1:
                 self._advance(B, k, record)
+                if (k + 1) % self.chunk_steps == 0 or k + 1 == steps:
+                    self._flush_chunk(B, k + 1, record)
         if steps > 1:
-            self.hh_tok[:steps, :B].copy_(self.hist_tok[:steps, :B], non_blocking=True)
-            self.hh_lp[:steps, :B].copy_(self.hist_lp[:steps, :B], non_blocking=True)
-            nbytes = 12 * B * steps
-            if record:
-                self.hh_routed[:steps, :B].copy_(self.hist_routed[:steps, :B], non_blocking=True)
-                nbytes += self.hh_routed[:steps, :B].numel() * 4
-            e.stats["d2h_bytes"] = e.stats.get("d2h_bytes", 0) + nbytes
-            t0 = time.perf_counter()
-            torch.cuda.current_stream().synchronize()
-            e.stats["decode_wait_s"] = e.stats.get("decode_wait_s", 0.0) + time.perf_counter() - t0
+            # the copies were queued chunk by chunk behind the replays (`_flush_chunk`): the caller reads step k after
+            # `wait_step(k)` and does its bookkeeping for one chunk while the GPU runs the next ones
             return self.hh_tok.numpy(), self.hh_lp.numpy(), (self.hh_routed.numpy() if record else None)
         self.h_tok[:B].copy_(self.o_tok[:B], non_blocking=True)
         self.h_lp[:B].copy_(self.o_lp[:B], non_blocking=True)
@@ -241,6 +240,30 @@ class DecodeRunner:
         torch.cuda.current_stream().synchronize()
         e.stats["decode_wait_s"] = e.stats.get("decode_wait_s", 0.0) + time.perf_counter() - t0   # host idle, GPU busy
         return self.h_tok.numpy(), self.h_lp.numpy(), (self.h_routed.numpy() if record else None)
+
+    def _flush_chunk(self, B: int, end: int, record: bool):
+        """Queue the device→host copies of the history rows [start, end) and mark the point with an event."""
+        e = self.e
+        start = self._chunks[-1][0] if self._chunks else 0
+        self.hh_tok[start:end, :B].copy_(self.hist_tok[start:end, :B], non_blocking=True)
+        self.hh_lp[start:end, :B].copy_(self.hist_lp[start:end, :B], non_blocking=True)
+        nbytes = 12 * B * (end - start)
+        if record:
+            self.hh_routed[start:end, :B].copy_(self.hist_routed[start:end, :B], non_blocking=True)
+            nbytes += self.hh_routed[start:end, :B].numel() * 4
+        e.stats["d2h_bytes"] = e.stats.get("d2h_bytes", 0) + nbytes
+        ev = self._events[len(self._chunks)]
+        ev.record()
+        self._chunks.append((end, ev))
+
+    def wait_step(self, k: int):
+        """Block until the outputs of step `k` of the last multi-step call are in the host buffers."""
+        while self._on_host <= k and self._chunks:
+            end, ev = self._chunks.pop(0)
+            t0 = time.perf_counter()
+            ev.synchronize()
+            self.e.stats["decode_wait_s"] = self.e.stats.get("decode_wait_s", 0.0) + time.perf_counter() - t0   # host idle, GPU busy
+            self._on_host = end
 
     @torch.no_grad()
     def warmup(self):

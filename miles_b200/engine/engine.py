@@ -108,7 +108,8 @@ class Engine:
                  mem_fraction_static: float = 0.7, max_running_requests: int = 512, max_prefill_tokens: int = 16384,
                  max_context_len: int | None = None, eos_token_ids: list[int] | None = None, tokenizer=None,
                  seed: int = 0, use_cuda_graph: bool = True, record_routing: bool | None = None,
-                 share_prompt_kv: bool = True, decode_steps_per_sync: int = 8, prefix_cache: bool = True,
+                 share_prompt_kv: bool = True, decode_steps_per_sync: int = 8, decode_steps_idle: int = 32,
+                 prefix_cache: bool = True,
                  chunked_prefill_size: int | None = None):
         self.cfg = cfg
         self.ps = ps or ParallelState.single()
@@ -129,6 +130,9 @@ class Engine:
         # decode steps per host round trip on the CUDA runner (see `decode_runner`): a finished request may run up to
         # steps − 1 extra positions whose tokens are dropped; nothing waits on the host in between
         self.decode_steps_per_sync = max(1, int(decode_steps_per_sync))
+        # with no request waiting for admission nothing gains from an early return to the scheduler: the round trip then
+        # covers this many steps, and the host reads them back chunk by chunk while the GPU runs the rest
+        self.decode_steps_idle = max(self.decode_steps_per_sync, int(decode_steps_idle))
         self._agreed_steps = 1
         self.use_cuda_graph = use_cuda_graph and self.device.type == "cuda"
         hkv = cfg.num_kv_heads // self.ps.tp_size
@@ -518,7 +522,7 @@ class Engine:
 
         batch = [] if self.paused else self._schedule_prefill()
         want_decode = bool(self.running) and not self.paused and not batch
-        k = self._decode_lookahead() if want_decode else self.decode_steps_per_sync
+        k = self._decode_lookahead() if want_decode else self._steps_wanted()
         if want_decode and not self._ensure_decode_blocks(k):
             want_decode = False
         # the decode batch bucket is agreed too (the largest any rank needs): with the same row count on every rank the
@@ -527,8 +531,12 @@ class Engine:
         # the number of steps per round trip is agreed as well: the smallest any rank can take (−k under MAX)
         flags = torch.tensor([int(bool(batch)), int(want_decode), int(not self.local_done), bucket, -k], dtype=torch.int32,
                              device=self.device if self.device.type == "cuda" else "cpu")
+        t_agree = time.perf_counter()
         dist.all_reduce(flags, op=dist.ReduceOp.MAX, group=self.lockstep_group)
         any_prefill, any_decode, any_active, self._agreed_bucket, neg_k = (int(v) for v in flags.tolist())
+        # the agreement itself plus the wait for the slowest rank's host
+        self.stats["lockstep_agree_s"] = self.stats.get("lockstep_agree_s", 0.0) + time.perf_counter() - t_agree
+        self.stats["lockstep_rounds"] = self.stats.get("lockstep_rounds", 0) + 1
         self._agreed_steps = max(1, -neg_k)
         self.global_done = not any_active and not any_prefill and not any_decode
         t0 = time.perf_counter()
@@ -677,10 +685,15 @@ class Engine:
         generate and by the context limit (positions beyond either are never written)."""
         if self.runner is None or self.stateless or self.decode_steps_per_sync <= 1 or not self.running:
             return 1
-        k = self.decode_steps_per_sync
+        k = self._steps_wanted()
         for r in self.running:
             k = min(k, r.sampling.max_new_tokens - len(r.output_ids), self.max_context_len - len(r.all_ids))
         return max(1, k)
+
+    def _steps_wanted(self) -> int:
+        if self.decode_steps_per_sync <= 1:
+            return 1
+        return self.decode_steps_per_sync if (self.waiting or self.prefilling) else self.decode_steps_idle
 
     def _ensure_decode_blocks(self, lookahead: int = 1) -> bool:
         """Every running request needs slots for its next `lookahead` tokens; retract the youngest on shortage."""
@@ -934,14 +947,22 @@ class Engine:
                 self._append_token(r, int(tok[row]), float(lp[row]))
         else:
             rows = [(r, r.row) for r in reqs]      # `_finish` detaches the row; keep it for the remaining sub-steps
-            for k in range(steps):
+            ch = self.runner.chunk_steps
+            for k0 in range(0, steps, ch):
+                k1 = min(steps, k0 + ch)
+                self.runner.wait_step(k1 - 1)      # a chunk of steps at a time; the GPU is running the later chunks meanwhile
                 for r, row in rows:
                     if r.finished:
                         continue                   # what a row produced after its stop token / limit is dropped
-                    self.stats["decode_tokens"] += 1
                     if routed is not None and r.return_routed_experts:
-                        r.routed.append(routed[k, row:row + 1].copy())
-                    self._append_token(r, int(tok[k, row]), float(lp[k, row]))
+                        # [tokens, layers, top-k], one copy per chunk and row, in place before a token can finish the request
+                        # (a waiter may read the result at once); rows past the last token are cut off with the output
+                        r.routed.append(routed[k0:k1, row].copy())
+                    k = k0
+                    while k < k1 and not r.finished:
+                        self._append_token(r, int(tok[k, row]), float(lp[k, row]))
+                        k += 1
+                    self.stats["decode_tokens"] += k - k0
             self.stats["decode_extra_steps"] = self.stats.get("decode_extra_steps", 0) + steps - 1
         self.running = [r for r in reqs if not r.finished]
 

@@ -293,7 +293,7 @@ def main():
     a = p.parse_args()
     cfg = get_config(a.hf_checkpoint or a.model_name)
     dtype = torch.bfloat16 if a.device.startswith("cuda") else torch.float32
-    if a.device.startswith("cuda"):
+    if a.device.startswith("cuda") and torch.device(a.device).index is not None:
         torch.cuda.set_device(torch.device(a.device))      # kernels and allocations of this process default to its own GPU
     eng = Engine(cfg, device=a.device, dtype=dtype, mem_fraction_static=a.mem_fraction_static, max_running_requests=a.max_running_requests,
                  prefix_cache=not a.disable_radix_cache, chunked_prefill_size=a.chunked_prefill_size or None)

@@ -176,6 +176,10 @@ def logprob_entropy(hidden, lm_head_w, targets, temperature: float = 1.0, chunk:
                     with_entropy: bool = True):
     """Returns (logp [T] fp32, entropy [T] fp32) with logits = hidden·Wᵀ / temperature in fp32."""
     T = hidden.shape[0]
+    if T == 0:
+        # an empty micro-batch (a rank padded to its peers' count) still has to reach every parameter in backward
+        z = hidden.float().sum(-1) + lm_head_w.float().sum() * 0.0
+        return z, (z.clone() if with_entropy else None)
     lp = torch.empty(T, dtype=torch.float32, device=hidden.device)
     ent = torch.empty(T, dtype=torch.float32, device=hidden.device)
     for s in range(0, T, chunk):

@@ -10,6 +10,7 @@ from __future__ import annotations
 
 import json
 import os
+import pickle
 import time
 from typing import Any
 
@@ -21,6 +22,29 @@ from ..train.data import convert_samples_to_train_data, split_train_data_by_dp
 from ..types import RolloutDataPack, Sample
 from ..utils import object_store
 from ..utils.misc import load_function
+
+
+def plan_group_moves(sizes: list[list[int]], max_moves: int = 256) -> list[tuple[int, int, int]]:
+    """Which prompt groups change ranks so that the token counts even out: `sizes[r][i]` = tokens of rank r's group i →
+    [(source rank, group index on the source, destination rank)].  Greedy: the fullest rank gives the emptiest one the
+    group closest to half their difference, as long as a group smaller than the difference exists (every move then lowers
+    the pair's maximum).  Groups move at most once; deterministic, so every rank computes the same plan."""
+    loads = [sum(s) for s in sizes]
+    avail = [{i: n for i, n in enumerate(s)} for s in sizes]           # groups still at home
+    moves = []
+    while len(moves) < max_moves and len(loads) > 1:
+        hi = max(range(len(loads)), key=lambda r: (loads[r], -r))
+        lo = min(range(len(loads)), key=lambda r: (loads[r], r))
+        gap = loads[hi] - loads[lo]
+        cand = [(abs(n - gap / 2), i) for i, n in avail[hi].items() if 0 < n < gap]
+        if not cand:
+            break
+        _, i = min(cand)
+        n = avail[hi].pop(i)
+        loads[hi] -= n
+        loads[lo] += n
+        moves.append((hi, i, lo))
+    return moves
 
 
 class RolloutExecutor:
@@ -67,11 +91,14 @@ class RolloutExecutor:
         dp = self.ps.dp_size if self.ps is not None else 1
         # one engine per data-parallel rank: the rank may keep what it generated (prompt groups are never split, so group
         # normalisation is unaffected) instead of pickling every sample — routed experts included — to every rank
-        local = (getattr(args, "rollout_data_exchange", "gather") == "local" and self.rollout_dp_size > 1
+        mode = getattr(args, "rollout_data_exchange", "gather")
+        local = (mode in ("local", "balanced") and self.rollout_dp_size > 1
                  and dp == self.rollout_dp_size and dist.is_initialized() and self._is_rollout_leader())
         t_gen = time.time() - t0
         if not local:
             groups = self._exchange(groups)
+        elif mode == "balanced":
+            groups = self._rebalance(groups)
         if getattr(args, "save_debug_rollout_data", None) and (not dist.is_initialized() or dist.get_rank() == 0):
             path = args.save_debug_rollout_data.format(rollout_id=rollout_id)
             os.makedirs(os.path.dirname(path) or ".", exist_ok=True)
@@ -143,6 +170,43 @@ class RolloutExecutor:
                 out.extend(ragged_codec.decode_groups(part, Sample))
         out.sort(key=lambda g: g[0].index if g[0].index is not None else 0)
         return out
+
+    def _rebalance(self, groups: list[list[Sample]]) -> list[list[Sample]]:
+        """Local exchange with the token counts evened out: ranks agree on a plan from the per-group token counts (a few
+        integers per rank), then only the groups that move travel, point to point, as ragged-codec buffers."""
+        from ..utils import ragged_codec
+
+        g = self.gather_group if self.gather_group is not None else dist.group.WORLD
+        world, me = dist.get_world_size(g), dist.get_rank(g)
+        sizes = [sum(len(s.tokens) for s in grp) for grp in groups]
+        all_sizes: list = [None] * world
+        dist.all_gather_object(all_sizes, sizes, group=g)
+        moves = plan_group_moves(all_sizes)
+        if not moves:
+            return groups
+        dev = "cuda" if dist.get_backend(g) == "nccl" else "cpu"
+        out_blobs = {}
+        for src, idx, dst in moves:
+            if src == me:
+                blob = pickle.dumps(ragged_codec.encode_groups([groups[idx]]), protocol=5)
+                out_blobs[(idx, dst)] = torch.frombuffer(bytearray(blob), dtype=torch.uint8)
+        lens: list = [None] * world
+        dist.all_gather_object(lens, {k: int(v.numel()) for k, v in out_blobs.items()}, group=g)
+        ops, recv = [], []
+        for src, idx, dst in moves:                                    # the same order on every rank
+            if src == me:
+                ops.append(dist.P2POp(dist.isend, out_blobs[(idx, dst)].to(dev), dist.get_global_rank(g, dst), group=g))
+            elif dst == me:
+                buf = torch.empty(lens[src][(idx, dst)], dtype=torch.uint8, device=dev)
+                recv.append(buf)
+                ops.append(dist.P2POp(dist.irecv, buf, dist.get_global_rank(g, src), group=g))
+        for w in (dist.batch_isend_irecv(ops) if ops else []):
+            w.wait()
+        gone = {idx for src, idx, _ in moves if src == me}
+        kept = [grp for i, grp in enumerate(groups) if i not in gone]
+        for buf in recv:
+            kept.extend(ragged_codec.decode_groups(pickle.loads(buf.cpu().numpy().tobytes()), Sample))
+        return kept
 
     def _reduce_metrics(self, m: dict, n_samples: int, n_resp: int) -> dict:
         """Whole-job values of the per-rank rollout metrics (local exchange mode): means are re-weighted by their own

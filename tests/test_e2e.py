@@ -121,6 +121,9 @@ def _dist_hist(tmp_path, extra, world=2):
     "--model-name tiny-moe --expert-model-parallel-size 2",                 # dp2 × ep2
     "--rollout-data-exchange local",                                        # dp2, every rank trains on what it generated
     "--model-name tiny-moe --expert-model-parallel-size 2 --use-rollout-routing-replay --rollout-data-exchange local",
+    # as above, then whole prompt groups move to the rank with fewer tokens
+    "--model-name tiny-moe --expert-model-parallel-size 2 --use-rollout-routing-replay --rollout-data-exchange balanced "
+    "--synthetic-prompt-len 4 48",
     "--context-parallel-size 2 --cp-comm-type a2a",                         # cp2 (Ulysses), dp1
     "--train-backend fsdp",                                                 # dp2, parameters sharded per layer (FSDP2)
     "--offload-train --offload-train-release-process-groups",               # dp2, communicators destroyed while asleep

@@ -78,11 +78,12 @@ def test_several_decode_steps_per_round_trip_give_the_same_samples(engine, steps
     res = {}
     for k in (1, steps):
         engine.decode_steps_per_sync = k
+        engine.decode_steps_idle = 32 if k >= 4 else k      # 32: read back in chunks of 8 while the later steps run
         outs = engine.generate(prompts, [dict(sp) for sp in sps], return_routed_experts=True)
         res[k] = [(o["output_ids"], [round(x[0], 4) for x in o["meta_info"]["output_token_logprobs"]], o["meta_info"]["finish_reason"]["type"],
                    o["meta_info"].get("routed_experts")) for o in outs]
         assert engine._free_blocks() == engine.allocator.num_blocks if hasattr(engine.allocator, "num_blocks") else True
-    engine.decode_steps_per_sync = 4
+    engine.decode_steps_per_sync, engine.decode_steps_idle = 4, 32
     for a, b in zip(res[1], res[steps]):
         assert a[0] == b[0] and a[2] == b[2], (a[0], b[0], a[2], b[2])
         assert max((abs(x - y) for x, y in zip(a[1], b[1])), default=0.0) < 2e-3
@@ -196,7 +197,10 @@ def test_cuda_ipc_bucket_between_processes(tmp_path):
     proc = subprocess.Popen([sys.executable, "-m", "miles_b200.engine.server", "--model-name", "tiny", "--port", str(port),
                              "--mem-fraction-static", "0.05"], stdout=open(tmp_path / "server.log", "wb"), stderr=subprocess.STDOUT)
     try:
-        wait_healthy(f"http://127.0.0.1:{port}", 240.0)
+        try:
+            wait_healthy(f"http://127.0.0.1:{port}", 240.0, alive=lambda: proc.poll() is None)
+        except Exception as e:
+            raise AssertionError(f"{e}\n--- server log ---\n" + open(tmp_path / "server.log", errors="replace").read()[-3000:])
         cfg = PRESETS["tiny"]
         model = build_model(cfg, ParallelState.single(), dtype=torch.bfloat16, device="cuda", seed=123)
         named = [x for n, p in model.named_parameters() for x in to_hf(n, p.data, cfg)]

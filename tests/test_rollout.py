@@ -181,3 +181,74 @@ def test_recipes_build_commands_that_parse():
     with redirect_stdout(io.StringIO()) as b2:
         run.main(["list"])
     assert "qwen3-235b-a22b" in b2.getvalue()
+
+
+# ---- balanced local exchange ---------------------------------------------------------------------------------------
+
+def test_plan_group_moves_narrows_the_spread_and_is_deterministic():
+    import random
+
+    from miles_b200.orchestration.rollout_executor import plan_group_moves
+
+    rng = random.Random(3)
+    for _ in range(20):
+        sizes = [[rng.randint(4000, 22000) for _ in range(8)] for _ in range(8)]
+        moves = plan_group_moves(sizes)
+        assert moves == plan_group_moves([list(s) for s in sizes])
+        loads = [sum(s) for s in sizes]
+        before = max(loads) - min(loads)
+        seen = set()
+        for src, i, dst in moves:
+            assert (src, i) not in seen and src != dst           # a group moves at most once
+            seen.add((src, i))
+            loads[src] -= sizes[src][i]
+            loads[dst] += sizes[src][i]
+        assert sum(loads) == sum(map(sum, sizes))
+        assert max(loads) - min(loads) <= before
+        assert max(loads) / (sum(loads) / 8) < 1.06               # from ≈ 1.15 for such draws
+    assert plan_group_moves([[10, 10], [10, 10]]) == [] and plan_group_moves([[5]]) == []
+
+
+def _rebalance_body(rank, world):
+    import numpy as np
+
+    from miles_b200.orchestration.rollout_executor import RolloutExecutor
+    from miles_b200.types import Sample
+
+    def group(gid, n_tok):
+        out = []
+        for j in range(2):
+            s = Sample(index=gid * 2 + j, prompt="p", tokens=list(range(gid, gid + n_tok)), response_length=n_tok // 2,
+                       reward=float(gid), loss_mask=[1] * (n_tok // 2), rollout_log_probs=[-0.5] * (n_tok // 2))
+            s.rollout_routed_experts = np.full((n_tok - 1, 2, 2), gid, dtype=np.int32)
+            out.append(s)
+        return out
+
+    mine = [group(10 * rank + i, n) for i, n in enumerate([400, 300, 200, 50] if rank == 0 else [60, 40, 30, 20])]
+    ex = RolloutExecutor.__new__(RolloutExecutor)
+    ex.gather_group = None
+    got = ex._rebalance(mine)
+    ids = sorted(g[0].index // 2 for g in got)
+    tokens = sum(len(s.tokens) for g in got for s in g)
+    assert abs(tokens - 1100) <= 100, tokens                                       # 2200 tokens in all, 1900 of them started on rank 0
+    for g in got:
+        gid = g[0].index // 2
+        assert len(g) == 2 and g[0].tokens[0] == gid and g[1].reward == float(gid)
+        assert (np.asarray(g[0].rollout_routed_experts) == gid).all() and g[0].rollout_routed_experts.shape[1:] == (2, 2)
+    import torch.distributed as dist
+
+    everything: list = [None] * world
+    dist.all_gather_object(everything, ids)
+    assert sorted(sum(everything, [])) == [0, 1, 2, 3, 10, 11, 12, 13]             # nothing lost, nothing doubled
+    if rank == 1:
+        assert any(i < 10 for i in ids)                                            # rank 1 received a group of rank 0
+
+
+def test_balanced_exchange_moves_whole_groups_between_ranks():
+    import os
+    import sys
+
+    sys.path.insert(0, os.path.dirname(__file__))
+    from dist_utils import run_distributed
+
+    run_distributed(_rebalance_body, 2, (), timeout=300)
