@@ -71,10 +71,17 @@ class Request:
         return self.input_ids + self.output_ids
 
     @property
+    def num_tokens(self) -> int:
+        return len(self.input_ids) + len(self.output_ids)
+
+    @property
     def finished(self) -> bool:
         return self.finish_reason is not None
 
-    def to_response(self, engine: "Engine") -> dict:
+    def to_response(self, engine: "Engine", raw_routed: bool = False) -> dict:
+        """The reply of `/generate`.  `raw_routed`: a caller in this process takes the routed experts as the int32 array
+        itself instead of its base64 text (1.5 KB per token for 48 layers × top-8: the text form costs about a second per
+        hundred thousand tokens to make and to parse)."""
         meta: dict[str, Any] = {
             "id": self.rid,
             "finish_reason": self.finish_reason,
@@ -97,7 +104,7 @@ class Request:
         if self.return_routed_experts and self.routed:
             arr = np.concatenate(self.routed, axis=0)
             n = len(self.input_ids) + len(self.output_ids) - 1
-            meta["routed_experts"] = encode_routed_experts(arr[:n])
+            meta["routed_experts"] = arr[:n] if raw_routed else encode_routed_experts(arr[:n])
         text = engine.tokenizer.decode(self.output_ids) if engine.tokenizer is not None else ""
         return {"text": text, "output_ids": list(self.output_ids), "meta_info": meta}
 
@@ -451,7 +458,7 @@ class Engine:
         if r.blocks:
             if self.prefix_cache is not None and self._cacheable(r) and reason.get("type") != "abort":
                 # every position but the last sampled token has its KV written: the next turn of this conversation starts here
-                n_kv = len(r.all_ids) - 1 if r.num_cached else r.prefill_pos       # num_cached > 0: the prefill completed
+                n_kv = r.num_tokens - 1 if r.num_cached else r.prefill_pos       # num_cached > 0: the prefill completed
                 full = max(0, n_kv) // self.block_size
                 if full:
                     self.prefix_cache.insert(r.all_ids[: full * self.block_size], r.blocks[:full])
@@ -612,7 +619,7 @@ class Engine:
         budget = self.max_prefill_tokens
         piece = self.chunked_prefill_size
         for r in self.prefilling:
-            n = len(r.all_ids)
+            n = r.num_tokens
             take = min(n - r.prefill_pos, piece or n, max(budget - tokens, 0) if batch else (piece or n))
             if take <= 0:
                 break
@@ -625,7 +632,7 @@ class Engine:
         share = self.share_prompt_kv and not self.stateless
         while self.waiting and len(self.running) + len(batch) < self.max_running:
             r = self.waiting[0]
-            n = len(r.all_ids)
+            n = r.num_tokens
             key = None
             lead = None
             if share and r.logprob_start_len < 0:
@@ -687,7 +694,7 @@ class Engine:
             return 1
         k = self._steps_wanted()
         for r in self.running:
-            k = min(k, r.sampling.max_new_tokens - len(r.output_ids), self.max_context_len - len(r.all_ids))
+            k = min(k, r.sampling.max_new_tokens - len(r.output_ids), self.max_context_len - r.num_tokens)
         return max(1, k)
 
     def _steps_wanted(self) -> int:
@@ -699,7 +706,7 @@ class Engine:
         """Every running request needs slots for its next `lookahead` tokens; retract the youngest on shortage."""
         bs = self.block_size
         while True:
-            need = {id(r): max(0, self._blocks_needed(len(r.all_ids) + lookahead) - len(r.blocks)) for r in self.running}
+            need = {id(r): max(0, self._blocks_needed(r.num_tokens + lookahead) - len(r.blocks)) for r in self.running}
             if sum(need.values()) <= self._free_blocks():
                 for r in self.running:
                     if need[id(r)]:
@@ -840,13 +847,13 @@ class Engine:
         done, lead_row = [], {}
         for i, r in enumerate(lead_reqs):
             r.prefill_pos = r.chunk[1]
-            if r.prefill_pos >= len(r.all_ids):
+            if r.prefill_pos >= r.num_tokens:
                 lead_row[id(r)] = len(done)
                 done.append(i)
                 if r in self.prefilling:
                     self.prefilling.remove(r)
                 if self._cacheable(r):
-                    full = len(r.all_ids) // self.block_size
+                    full = r.num_tokens // self.block_size
                     if full:
                         # the request goes on using these blocks: pin the nodes that own them until it finishes
                         held = set(map(id, r.cache_nodes))
@@ -856,14 +863,14 @@ class Engine:
                         r.cache_nodes = r.cache_nodes + fresh
             elif r not in self.prefilling:
                 self.prefilling.append(r)
-        finished_batch = [r for r in batch if (r.leader if r.leader is not None else r).prefill_pos >= len(r.all_ids)]
+        finished_batch = [r for r in batch if (r.leader if r.leader is not None else r).prefill_pos >= r.num_tokens]
         if not finished_batch:
             return
         last = torch.tensor([cu[i + 1] - 1 for i in done], dtype=torch.int64, device=dev)
         logits = self.model.logits(hidden[last])
         for r in finished_batch:
-            r.num_cached = len(r.all_ids)
-            r.prefill_pos = len(r.all_ids)
+            r.num_cached = r.num_tokens
+            r.prefill_pos = r.num_tokens
         if followers or len(done) != len(finished_batch):
             rows = torch.tensor([lead_row[id(r.leader if r.leader is not None else r)] for r in finished_batch], dtype=torch.int64, device=dev)
             logits = logits[rows]
@@ -882,7 +889,7 @@ class Engine:
         bs = self.block_size
         src, dst = [], []
         for r in followers:
-            n = len(r.all_ids)
+            n = r.num_tokens
             if n % bs:
                 src.append(r.leader.blocks[n // bs])
                 dst.append(r.blocks[n // bs])
@@ -899,9 +906,9 @@ class Engine:
             reqs = list(self.running)
             self.stats["decode_tokens"] += len(reqs)
             for r in reqs:
-                r.chunk = (0, len(r.all_ids))             # the whole sequence, every step
+                r.chunk = (0, r.num_tokens)             # the whole sequence, every step
             self._run_prefill(reqs)                       # scores every sequence from its first token; appends one token each
-            self.stats["prefill_tokens"] -= sum(len(r.all_ids) - 1 for r in reqs)
+            self.stats["prefill_tokens"] -= sum(r.num_tokens - 1 for r in reqs)
             self.running = [r for r in self.running if not r.finished]
             return
         if self.runner is not None:
@@ -909,7 +916,7 @@ class Engine:
         reqs = self.running
         dev = self.device
         toks = [r.all_ids[-1] for r in reqs]
-        pos = [len(r.all_ids) - 1 for r in reqs]
+        pos = [r.num_tokens - 1 for r in reqs]
         slots = [self._slots(r, p, p + 1)[0] for r, p in zip(reqs, pos)]
         record = [] if any(r.return_routed_experts for r in reqs) else None
         meta = ForwardMeta(
@@ -970,7 +977,7 @@ class Engine:
         if not (0 <= t < self.cfg.vocab_size) or l != l:
             # a non-finite hidden state; stop here rather than feed the id to the next step's embedding lookup
             raise RuntimeError(f"engine step {self._step_count}: request {r.rid} sampled id {t} with log-prob {l} "
-                               f"(context {len(r.all_ids)} tokens, {len(self.running)} running)")
+                               f"(context {r.num_tokens} tokens, {len(self.running)} running)")
         r.output_ids.append(t)
         r.output_logprobs.append(l)
         if r.weight_versions and r.weight_versions[-1][0] == self.weight_version:

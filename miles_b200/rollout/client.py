@@ -104,7 +104,7 @@ class InProcEngineClient:
         finally:
             self._active[i] -= 1
             self._pending.discard(fut)
-        return req.to_response(eng)
+        return req.to_response(eng, raw_routed=True)
 
     async def abort_all(self):
         for e in self.engines:

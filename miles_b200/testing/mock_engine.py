@@ -32,7 +32,7 @@ class MockRequest:
     return_routed_experts: bool = False
     weight_versions: list[list[int]] = field(default_factory=list)
 
-    def to_response(self, engine) -> dict:
+    def to_response(self, engine, raw_routed: bool = False) -> dict:
         meta = {"id": self.rid, "finish_reason": self.finish_reason, "prompt_tokens": len(self.input_ids),
                 "completion_tokens": len(self.output_ids), "cached_tokens": 0,
                 "weight_version": str(engine.weight_version), "weight_version_spans": self.weight_versions,

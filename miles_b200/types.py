@@ -229,14 +229,17 @@ class Sample:
         return copy.deepcopy(self)
 
 
-def decode_routed_experts(b64: str, num_tokens: int, num_layers: int, topk: int) -> np.ndarray:
-    """Engine replies carry routed experts as base64 int32; shape [num_tokens-1, layers, topk].
+def decode_routed_experts(b64, num_tokens: int, num_layers: int, topk: int) -> np.ndarray:
+    """Engine replies carry routed experts as base64 int32 (an engine in this process hands over the array itself);
+    shape [num_tokens-1, layers, topk].
 
     An all-zero buffer means the engine never recorded routing and is rejected
     (reference behaviour: miles/rollout/generate_utils/generate_endpoint_utils.py:142-162).
     """
-    arr = np.frombuffer(base64.b64decode(b64), dtype=np.int32)
-    arr = arr.reshape(num_tokens - 1, num_layers, topk).copy()
+    if isinstance(b64, np.ndarray):
+        arr = np.ascontiguousarray(b64, dtype=np.int32).reshape(num_tokens - 1, num_layers, topk)
+    else:
+        arr = np.frombuffer(base64.b64decode(b64), dtype=np.int32).reshape(num_tokens - 1, num_layers, topk).copy()
     if arr.size and not arr.any():
         raise ValueError("routed_experts buffer is all zero: engine did not record routing")
     return arr
