@@ -82,6 +82,9 @@ class DecodeRunner:
         self.rows: list = [None] * R          # row → Request
         self.free_rows = list(range(R - 1, -1, -1))
         self.high = 0                         # 1 + highest occupied row
+        from .. import ops
+
+        self._err = ops._k().C.error_flag(self.d_i32)      # device error flag: raised (71) when a step samples an id outside the vocabulary
         self.graphs: dict[int, tuple] = {}
         self.launches_per_graph: dict[int, int] = {}
         self.pool = None
@@ -179,7 +182,8 @@ class DecodeRunner:
         C = ops._k().C
         C.decode_advance(self.o_tok[:B], self.o_lp[:B], self.o_routed[:B] if record else None, self.hist_tok[k, :B], self.hist_lp[k, :B],
                          self.hist_routed[k, :B] if record else None, self.d_i32[0:B], self.d_i32[R:R + B], self.d_i32[2 * R:2 * R + B],
-                         self.d_i32[3 * R:].view(R, MB)[:B], self.e.block_size, self.d_i64[0:B], self.d_i64[R:R + B])
+                         self.d_i32[3 * R:].view(R, MB)[:B], self.e.block_size, self.d_i64[0:B], self.d_i64[R:R + B],
+                         self.e.cfg.vocab_size, self._err)
 
     def step(self, reqs: list, step_no: int, min_bucket: int = 0, steps: int = 1):
         """Run `steps` decode steps for the attached requests (every request must own cache blocks for `steps` more

@@ -519,6 +519,7 @@ class Engine:
                 return False
             self.stats["steps"] += 1
             self._step_count += 1
+            self._debug_check("prefill" if batch else "decode")
             return True
 
     def _step_lockstep(self) -> bool:
@@ -560,7 +561,23 @@ class Engine:
             return False
         self.stats["steps"] += 1
         self._step_count += 1
+        self._debug_check("prefill" if any_prefill else "decode")
         return True
+
+    def _debug_check(self, where: str):
+        """Debug build of the kernels only: after each engine step read what the index checks recorded and the device error
+        flag, and stop with the step's context instead of going on with skipped accesses."""
+        if self.device.type != "cuda":
+            return
+        from ..ops import cuda as K
+
+        if not K.DEBUG_KERNELS:
+            return
+        rep, flag = K.bounds_report(), K.check_error_flag()
+        if rep or flag:
+            rows = [(r.rid, r.num_tokens, len(r.blocks), getattr(r, "row", None)) for r in self.running[:8]]
+            raise RuntimeError(f"engine {where} step {self._step_count}: index checks {rep}, error flag {flag}, "
+                               f"agreed steps {self._agreed_steps}, running {len(self.running)} {rows}")
 
     def check_fabric(self):
         """Raise if a peer-memory kernel of this process gave up a bounded wait (the step that followed is garbage)."""

@@ -24,7 +24,8 @@ inline void check(int rc, const char* what) {
 // device-side hand-over between two decode steps of one host round trip (see decode_advance_kernel)
 void decode_advance(const at::Tensor& o_tok, const at::Tensor& o_lp, const c10::optional<at::Tensor>& o_routed, at::Tensor& h_tok,
                     at::Tensor& h_lp, const c10::optional<at::Tensor>& h_routed, at::Tensor& tok, at::Tensor& pos, at::Tensor& len,
-                    const at::Tensor& block_table, int64_t block_size, at::Tensor& slot, at::Tensor& seed) {
+                    const at::Tensor& block_table, int64_t block_size, at::Tensor& slot, at::Tensor& seed, int64_t vocab,
+                    at::Tensor& error_flag) {
   c10::cuda::CUDAGuard g(o_tok.device());
   const int64_t B = tok.numel();
   const bool rec = o_routed.has_value() && o_routed->defined() && h_routed.has_value() && h_routed->defined();
@@ -34,7 +35,7 @@ void decode_advance(const at::Tensor& o_tok, const at::Tensor& o_lp, const c10::
                           h_lp.data_ptr<float>(), rec ? h_routed->data_ptr<int>() : nullptr, per, tok.data_ptr<int>(), pos.data_ptr<int>(),
                           len.data_ptr<int>(), block_table.data_ptr<int>(), block_table.size(1), block_size,
                           reinterpret_cast<long long*>(slot.data_ptr<int64_t>()), reinterpret_cast<long long*>(seed.data_ptr<int64_t>()), B,
-                          cur_stream()),
+                          static_cast<int>(vocab), error_flag.data_ptr<int>(), cur_stream()),
         "mb_decode_advance");
 }
 

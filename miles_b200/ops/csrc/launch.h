@@ -128,7 +128,7 @@ int mb_sample_logprob_split(const float* logits, const float* temperature, const
                             long long* tokens, float* logprobs, int B, int V, int parts, float* ws, int* counters, cudaStream_t s);
 int mb_decode_advance(const long long* o_tok, const float* o_lp, const int* o_routed, long long* h_tok, float* h_lp, int* h_routed,
                       int routed_per_row, int* tok, int* pos, int* len, const int* block_table, int max_blocks, int block_size,
-                      long long* slot, long long* seed, int B, cudaStream_t s);
+                      long long* slot, long long* seed, int B, int vocab, int* error_flag, cudaStream_t s);
 int mb_sample_logprob(const float* logits, const float* temperature, const uint8_t* greedy, const long long* seeds, long long step,
                       long long* tokens, float* logprobs, int B, int V, cudaStream_t s);
 int mb_logit_stats(const float* logits, long long ld, const long long* targets, float* stats, long long R, int Vc, int v0,

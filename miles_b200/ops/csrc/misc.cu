@@ -259,13 +259,18 @@ __global__ void decode_advance_kernel(const long long* __restrict__ o_tok, const
                                       long long* __restrict__ h_tok, float* __restrict__ h_lp, int* __restrict__ h_routed,
                                       int routed_per_row, int* __restrict__ tok, int* __restrict__ pos, int* __restrict__ len,
                                       const int* __restrict__ block_table, int max_blocks, int block_size,
-                                      long long* __restrict__ slot, long long* __restrict__ seed, int B) {
+                                      long long* __restrict__ slot, long long* __restrict__ seed, int B, int vocab,
+                                      int* __restrict__ error_flag) {
   pdl_trigger();
   pdl_wait();
   const int r = blockIdx.x * blockDim.x + threadIdx.x;
   if (r >= B) return;
-  const long long t = o_tok[r];
-  h_tok[r] = t;
+  long long t = o_tok[r];
+  h_tok[r] = t;                 // the host sees what was sampled, in range or not, and fails the request with its context
+  if (t < 0 || t >= vocab) {    // a non-finite hidden state upstream: never feed such an id to the next step's embedding lookup
+    if (len[r] > 0 && error_flag != nullptr) atomicCAS(error_flag, 0, 71);
+    t = 0;
+  }
   h_lp[r] = o_lp[r];
   if (h_routed != nullptr)
     for (int i = 0; i < routed_per_row; ++i) h_routed[static_cast<long long>(r) * routed_per_row + i] = o_routed[static_cast<long long>(r) * routed_per_row + i];
@@ -287,10 +292,11 @@ using namespace mb;
 
 extern "C" int mb_decode_advance(const long long* o_tok, const float* o_lp, const int* o_routed, long long* h_tok, float* h_lp,
                                  int* h_routed, int routed_per_row, int* tok, int* pos, int* len, const int* block_table, int max_blocks,
-                                 int block_size, long long* slot, long long* seed, int B, cudaStream_t s) {
+                                 int block_size, long long* slot, long long* seed, int B, int vocab, int* error_flag, cudaStream_t s) {
   if (B == 0) return 0;
   return static_cast<int>(launch_pdl(decode_advance_kernel, dim3((B + 127) / 128), dim3(128), 0, s, o_tok, o_lp, o_routed, h_tok, h_lp,
-                                     h_routed, routed_per_row, tok, pos, len, block_table, max_blocks, block_size, slot, seed, B));
+                                     h_routed, routed_per_row, tok, pos, len, block_table, max_blocks, block_size, slot, seed, B, vocab,
+                                     error_flag));
 }
 
 extern "C" int mb_sample_logprob(const float* logits, const float* temperature, const uint8_t* greedy, const long long* seeds,

@@ -24,6 +24,9 @@ from ..utils import object_store
 from ..utils.misc import load_function
 
 
+_FOREIGN_ID_STRIDE = 1 << 40
+
+
 def plan_group_moves(sizes: list[list[int]], max_moves: int = 256) -> list[tuple[int, int, int]]:
     """Which prompt groups change ranks so that the token counts even out: `sizes[r][i]` = tokens of rank r's group i →
     [(source rank, group index on the source, destination rank)].  Greedy: the fullest rank gives the emptiest one the
@@ -198,14 +201,22 @@ class RolloutExecutor:
                 ops.append(dist.P2POp(dist.isend, out_blobs[(idx, dst)].to(dev), dist.get_global_rank(g, dst), group=g))
             elif dst == me:
                 buf = torch.empty(lens[src][(idx, dst)], dtype=torch.uint8, device=dev)
-                recv.append(buf)
+                recv.append((src, buf))
                 ops.append(dist.P2POp(dist.irecv, buf, dist.get_global_rank(g, src), group=g))
         for w in (dist.batch_isend_irecv(ops) if ops else []):
             w.wait()
         gone = {idx for src, idx, _ in moves if src == me}
         kept = [grp for i, grp in enumerate(groups) if i not in gone]
-        for buf in recv:
-            kept.extend(ragged_codec.decode_groups(pickle.loads(buf.cpu().numpy().tobytes()), Sample))
+        for src, buf in recv:
+            for grp in ragged_codec.decode_groups(pickle.loads(buf.cpu().numpy().tobytes()), Sample):
+                # every rank numbers its own samples: keep the newcomers' ids apart from this rank's (rows with one
+                # rollout id are treated as segments of one rollout downstream)
+                for smp in grp:
+                    if smp.index is not None:
+                        smp.index += (src + 1) * _FOREIGN_ID_STRIDE
+                    if isinstance(smp.rollout_id, int):
+                        smp.rollout_id += (src + 1) * _FOREIGN_ID_STRIDE
+                kept.append(grp)
         return kept
 
     def _reduce_metrics(self, m: dict, n_samples: int, n_resp: int) -> dict:

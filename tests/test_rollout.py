@@ -228,6 +228,12 @@ def _rebalance_body(rank, world):
     ex = RolloutExecutor.__new__(RolloutExecutor)
     ex.gather_group = None
     got = ex._rebalance(mine)
+    stride = 1 << 40
+    assert len({s.index for g in got for s in g}) == sum(len(g) for g in got)      # ids stay unique on the receiving rank
+    assert all((s.index >= stride) == (s.tokens[0] // 10 != rank) for g in got for s in g)
+    for g in got:
+        for s in g:
+            s.index %= stride
     ids = sorted(g[0].index // 2 for g in got)
     tokens = sum(len(s.tokens) for g in got for s in g)
     assert abs(tokens - 1100) <= 100, tokens                                       # 2200 tokens in all, 1900 of them started on rank 0
