@@ -184,7 +184,7 @@ def main():
             f"--rollout-max-response-len {a.max_new_tokens} --num-rollout 1000000 --rm-type last_mod7 --lr 1e-6 --colocate "
             f"--advantage-estimator grpo --eps-clip 0.2 --use-dynamic-batch-size --max-tokens-per-gpu {a.max_tokens_per_gpu} "
             f"--recompute-granularity full --use-rollout-routing-replay --balance-data "
-            f"--expert-model-parallel-size {world} --rollout-temperature 1.0 --rollout-data-exchange balanced"
+            f"--expert-model-parallel-size {world} --rollout-temperature 1.0 --rollout-data-exchange local"
             + (" --fp8-recipe mxfp8" if a.fp8_recipe == "mxfp8" else ""))
     args = parse_args(argv.split())
     args.rollout_stop_token_ids = stop_ids

@@ -717,6 +717,8 @@ class Engine:
     def _steps_wanted(self) -> int:
         if self.decode_steps_per_sync <= 1:
             return 1
+        if self.lockstep_group is not None:
+            return self.decode_steps_per_sync          # expert-parallel ranks keep the short round trip (one chunk per agreement)
         return self.decode_steps_per_sync if (self.waiting or self.prefilling) else self.decode_steps_idle
 
     def _ensure_decode_blocks(self, lookahead: int = 1) -> bool:

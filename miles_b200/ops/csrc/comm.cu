@@ -181,7 +181,8 @@ __global__ void __launch_bounds__(256) adam_allgather_kernel(float* __restrict__
 // writes the metadata {source rank, source flat index, local expert id}.  sent_dest/sent_row remember the placement.
 __global__ void __launch_bounds__(256) moe_dispatch_kernel(const bf16* __restrict__ x, const int* __restrict__ topk_idx, long long n_pairs,
                                                            int k, int H, int e_local, int rank, PeerPtrs recv_x, PeerPtrs recv_meta,
-                                                           PeerPtrs counters, int capacity, int* __restrict__ sent_row, int* err) {
+                                                           PeerPtrs counters, int capacity, int* __restrict__ sent_row, int* err,
+                                                           int world) {
   if (fabric_poisoned()) return;
   const int lane = threadIdx.x & 31;
   const int nvec = H / 8;
@@ -189,6 +190,11 @@ __global__ void __launch_bounds__(256) moe_dispatch_kernel(const bf16* __restric
     const int e = topk_idx[pair];
     if (e < 0) {
       if (lane == 0) sent_row[pair] = -1;
+      continue;
+    }
+    if (e >= e_local * world) {
+      // an expert id no rank owns (a router row of NaNs, a corrupt replay record): the peer table must not be indexed with it
+      if (lane == 0) { atomicCAS(err, 0, 210); sent_row[pair] = -1; }
       continue;
     }
     const int dest = e / e_local;
@@ -231,6 +237,10 @@ __global__ void __launch_bounds__(256) moe_dispatch_signal_kernel(const bf16* __
       const int e = topk_idx[pair];
       if (e < 0) {
         if (lane == 0) sent_row[pair] = -1;
+        continue;
+      }
+      if (e >= e_local * world) {
+        if (lane == 0) { atomicCAS(err, 0, 210); sent_row[pair] = -1; }
         continue;
       }
       const int dest = e / e_local;
@@ -531,7 +541,7 @@ extern "C" int mb_moe_dispatch(const void* x, const int* topk_idx, long long n_p
   if (H % 8) return -1;
   moe_dispatch_kernel<<<blocks_for(n_pairs, 8), 256, 0, s>>>(reinterpret_cast<const bf16*>(x), topk_idx, n_pairs, k, H, e_local, rank,
                                                              make_ptrs(recv_x_ptrs, world), make_ptrs(recv_meta_ptrs, world),
-                                                             make_ptrs(counter_ptrs, world), capacity, sent_row, err);
+                                                             make_ptrs(counter_ptrs, world), capacity, sent_row, err, world);
   return static_cast<int>(cudaGetLastError());
 }
 

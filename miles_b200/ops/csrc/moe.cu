@@ -81,6 +81,7 @@ __global__ void __launch_bounds__(256) router_topk_kernel(const float* __restric
 #pragma unroll
     for (int i = 0; i < EPL; ++i)
       if (i * 32 + lane == bi) v[i] = -2.f;
+    if (bi == 0x7fffffff) { bv = 0.f; bi = -1; }   // a row of NaNs has no winner: slot left empty (−1), never an id out of range
     wsel += bv;
     if (lane == j) { mine_w = bv; mine_i = bi; }
   }
