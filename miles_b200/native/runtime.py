@@ -10,6 +10,7 @@ import subprocess
 
 HERE = os.path.dirname(os.path.abspath(__file__))
 SRC = os.path.join(HERE, "csrc", "runtime.cpp")
+SOURCES = [SRC, os.path.join(HERE, "csrc", "codec.cpp")]
 BUILD_DIR = os.path.join(HERE, "_build")
 LIB_PATH = os.path.join(BUILD_DIR, "libmiles_rt.so")
 
@@ -18,9 +19,9 @@ _lib = None
 
 def build(force: bool = False) -> str:
     os.makedirs(BUILD_DIR, exist_ok=True)
-    if force or not os.path.exists(LIB_PATH) or os.path.getmtime(LIB_PATH) < os.path.getmtime(SRC):
+    if force or not os.path.exists(LIB_PATH) or os.path.getmtime(LIB_PATH) < max(os.path.getmtime(f) for f in SOURCES):
         cxx = "/usr/bin/g++" if os.path.exists("/usr/bin/g++") else "g++"
-        subprocess.check_call([cxx, "-O2", "-std=c++17", "-shared", "-fPIC", SRC, "-o", LIB_PATH, "-ldl", "-lpthread"])
+        subprocess.check_call([cxx, "-O2", "-std=c++17", "-shared", "-fPIC", *SOURCES, "-o", LIB_PATH, "-ldl", "-lpthread"])
     return LIB_PATH
 
 
@@ -42,6 +43,8 @@ def lib():
             "mbrt_router_create": (vp, [i32]), "mbrt_router_destroy": (None, [vp]), "mbrt_router_add_worker": (i32, [vp]),
             "mbrt_router_set_health": (None, [vp, i32, i32]), "mbrt_router_pick": (i32, [vp, i32, cp]),
             "mbrt_router_done": (None, [vp, i32]), "mbrt_router_active": (i32, [vp, i32]),
+            "mbrt_xxh64": (u64, [vp, u64, u64]), "mbrt_delta_bound": (u64, [u64]),
+            "mbrt_delta_encode": (i64, [vp, vp, u64, i32, vp, u64]), "mbrt_delta_decode": (i64, [vp, u64, vp, vp, u64]),
         }
         for name, (res, args) in sigs.items():
             fn = getattr(L, name)
@@ -187,3 +190,44 @@ class NativeRouterCore:
             lib().mbrt_router_destroy(self._h)
         except Exception:
             pass
+
+
+# ---- byte codecs (csrc/codec.cpp) ---------------------------------------------------------------------------------
+
+def _ptr(a):
+    return ctypes.c_void_p(a.ctypes.data) if a is not None else None
+
+
+def xxh64(data, seed: int = 0) -> int:
+    """XXH64 of a bytes-like object or a numpy array's bytes."""
+    import numpy as np
+
+    a = np.frombuffer(data, dtype=np.uint8) if not isinstance(data, np.ndarray) else np.ascontiguousarray(data).view(np.uint8).reshape(-1)
+    return int(lib().mbrt_xxh64(_ptr(a) if a.size else None, a.size, seed))
+
+
+def delta_encode(cur, base=None, elem: int = 2) -> bytes:
+    """`cur` (XOR `base` when given) → byte planes → zero-run-length.  Arrays of equal byte length, a multiple of `elem`."""
+    import numpy as np
+
+    c = np.ascontiguousarray(cur).view(np.uint8).reshape(-1)
+    b = np.ascontiguousarray(base).view(np.uint8).reshape(-1) if base is not None else None
+    assert b is None or b.size == c.size, "base and current tensors differ in size"
+    out = np.empty(int(lib().mbrt_delta_bound(c.size)), dtype=np.uint8)
+    n = lib().mbrt_delta_encode(_ptr(c), _ptr(b), c.size, elem, _ptr(out), out.size)
+    if n < 0:
+        raise ValueError("delta_encode: inconsistent arguments")
+    return out[:n].tobytes()
+
+
+def delta_decode(blob: bytes, nbytes: int, base=None):
+    """Inverse of `delta_encode` → uint8 numpy array of `nbytes`."""
+    import numpy as np
+
+    e = np.frombuffer(blob, dtype=np.uint8)
+    b = np.ascontiguousarray(base).view(np.uint8).reshape(-1) if base is not None else None
+    assert b is None or b.size == nbytes
+    out = np.empty(nbytes, dtype=np.uint8)
+    if lib().mbrt_delta_decode(_ptr(e), e.size, _ptr(b), _ptr(out), nbytes) != nbytes:
+        raise ValueError("delta_decode: malformed stream")
+    return out

@@ -10,7 +10,9 @@ Delta format (one directory per version `v{N}`):
     <file>.bin      payload: `kind == "full"`  raw tensor bytes
                              `kind == "xor"`   bytes of (new XOR base) — bf16 weights move little per step, so the XOR
                                                is mostly zero bytes and compresses well
-    Payloads are compressed with zlib (level 1) when that helps; "codec" records which.
+    Payloads are compressed when that helps; "codec" records how: "zrle" (the native runtime's byte-plane + zero-run-length
+    coder, `native/csrc/codec.cpp`: one pass at hundreds of MB/s, made for XOR deltas), "zrle+zlib" (the same, then zlib: the
+    smallest), "zlib", or "raw".  Checksums: crc32 always, XXH64 ("xxh64") too when the native runtime is built.
 A reader applies deltas in order on top of the version it holds; a checksum mismatch or a missing base is an error the
 caller answers by loading the newest full snapshot.
 """
@@ -30,6 +32,15 @@ def _bytes_of(t: torch.Tensor) -> bytes:
     return t.detach().contiguous().cpu().view(torch.uint8).numpy().tobytes()
 
 
+def _native():
+    try:
+        from ..native import runtime as rt
+
+        return rt if rt.available() else None
+    except Exception:
+        return None
+
+
 def _from_bytes(b: bytes, dtype, shape) -> torch.Tensor:
     return torch.frombuffer(bytearray(b), dtype=torch.uint8).view(dtype).view(shape).clone()
 
@@ -37,8 +48,15 @@ def _from_bytes(b: bytes, dtype, shape) -> torch.Tensor:
 class DeltaWriter:
     """Trainer side: keeps the last published tensors (host memory) and writes XOR deltas against them."""
 
-    def __init__(self, root: str, full_every: int = 10, compress: bool = True):
+    def __init__(self, root: str, full_every: int = 10, compress: bool = True, codec: str = "auto"):
+        """`codec`: "auto" (zrle+zlib with the native runtime, else zlib), "zrle", "zrle+zlib", "zlib" or "raw"."""
         self.root, self.full_every, self.compress = root, full_every, compress
+        rt = _native()
+        if codec == "auto":
+            codec = "zrle+zlib" if rt is not None else "zlib"
+        if codec.startswith("zrle") and rt is None:
+            raise RuntimeError("the zrle codec needs the native runtime (miles_b200.native.runtime.build())")
+        self.codec = codec if compress else "raw"
         self.base: dict[str, torch.Tensor] = {}
         self.base_version: int | None = None
         self.published = 0
@@ -59,9 +77,19 @@ class DeltaWriter:
             if not full and name in self.base and self.base[name].shape == cur.shape and self.base[name].dtype == cur.dtype:
                 x = torch.bitwise_xor(cur.view(torch.uint8), self.base[name].view(torch.uint8))
                 payload, kind = x.numpy().tobytes(), "xor"
-            crc = zlib.crc32(_bytes_of(cur))
+            raw = _bytes_of(cur)
+            crc = zlib.crc32(raw)
+            rt = _native()
             codec = "raw"
-            if self.compress:
+            if self.codec.startswith("zrle"):
+                z = rt.delta_encode(torch.frombuffer(bytearray(payload), dtype=torch.uint8).numpy(), None, max(1, cur.element_size()))
+                if self.codec == "zrle+zlib":
+                    z2 = zlib.compress(z, 1)
+                    if len(z2) < len(payload) and len(z2) < len(z):
+                        payload, codec = z2, "zrle+zlib"
+                if codec == "raw" and len(z) < len(payload):
+                    payload, codec = z, "zrle"
+            elif self.codec == "zlib":
                 z = zlib.compress(payload, 1)
                 if len(z) < len(payload):
                     payload, codec = z, "zlib"
@@ -70,6 +98,8 @@ class DeltaWriter:
                 f.write(payload)
             manifest["tensors"][name] = {"dtype": str(cur.dtype).replace("torch.", ""), "shape": list(cur.shape), "kind": kind,
                                          "file": fn, "nbytes": len(payload), "crc32": crc, "codec": codec}
+            if rt is not None:
+                manifest["tensors"][name]["xxh64"] = f"{rt.xxh64(raw):016x}"
             raw_bytes += cur.numel() * cur.element_size()
             stored += len(payload)
             new_base[name] = cur
@@ -120,9 +150,17 @@ class DeltaReader:
             for name, e in m["tensors"].items():
                 with open(os.path.join(self.root, f"v{v}", e["file"]), "rb") as f:
                     payload = f.read()
-                if e["codec"] == "zlib":
-                    payload = zlib.decompress(payload)
                 dtype = getattr(torch, e["dtype"])
+                if e["codec"] in ("zlib", "zrle+zlib"):
+                    payload = zlib.decompress(payload)
+                if e["codec"] in ("zrle", "zrle+zlib"):
+                    rt = _native()
+                    if rt is None:
+                        raise RuntimeError("this delta was written with the zrle codec: build the native runtime to read it")
+                    n = 1
+                    for d_ in e["shape"]:
+                        n *= d_
+                    payload = rt.delta_decode(payload, n * torch.empty((), dtype=dtype).element_size()).tobytes()
                 if e["kind"] == "xor":
                     assert name in self.state and m["base_version"] == self.version, \
                         f"delta v{v} needs base v{m['base_version']}, reader holds v{self.version}"
@@ -130,8 +168,12 @@ class DeltaReader:
                     cur = torch.bitwise_xor(self.state[name].contiguous().view(torch.uint8).view(-1), x).view(dtype).view(e["shape"])
                 else:
                     cur = _from_bytes(payload, dtype, e["shape"])
-                if zlib.crc32(_bytes_of(cur)) != e["crc32"]:
+                got = _bytes_of(cur)
+                if zlib.crc32(got) != e["crc32"]:
                     raise IOError(f"checksum mismatch for {name} in v{v}")
+                rt = _native()
+                if rt is not None and "xxh64" in e and f"{rt.xxh64(got):016x}" != e["xxh64"]:
+                    raise IOError(f"xxh64 mismatch for {name} in v{v}")
                 self.state[name] = cur
             self.version = v
         return self.state

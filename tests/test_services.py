@@ -180,12 +180,47 @@ def test_parker_and_multi_policy(tmp_path):
     assert len(shared["history"]["small_lr"]) == 2 and os.path.isdir(tmp_path / "ck" / "big_lr")
 
 
-def test_delta_writer_reader_and_snapshots(tmp_path):
+def test_native_codecs_xxh64_and_zero_run_length_delta():
+    """XXH64 against the algorithm's published vectors; the byte-plane + zero-run-length coder round-trips (with and without
+    a base, every element size, empty and incompressible inputs) and rejects damaged streams without writing out of range."""
+    import numpy as np
+
+    from miles_b200.native import runtime as rt
+
+    rt.build()
+    assert rt.xxh64(b"") == 0xEF46DB3751D8E999 and rt.xxh64(b"abc") == 0x44BC2CF5AD770999
+    assert rt.xxh64(b"a" * 100, 7) != rt.xxh64(b"a" * 100, 8) and rt.xxh64(np.arange(64, dtype=np.uint8)) == rt.xxh64(bytes(range(64)))
+    rng = np.random.default_rng(0)
+    for elem in (1, 2, 4, 8):
+        base = rng.integers(0, 256, 4096 * elem, dtype=np.uint8)
+        cur = base.copy()
+        idx = rng.choice(cur.size // elem, 300, replace=False) * elem          # a few low bytes change
+        cur[idx] ^= rng.integers(1, 256, idx.size, dtype=np.uint8)
+        enc = rt.delta_encode(cur, base, elem)
+        assert len(enc) < cur.size // 4 and (rt.delta_decode(enc, cur.size, base) == cur).all()
+        plain = rt.delta_encode(cur, None, elem)                                 # no base: random bytes do not shrink
+        assert len(plain) <= cur.size + cur.size // 64 + 64 and (rt.delta_decode(plain, cur.size) == cur).all()
+        bad = bytearray(enc)
+        bad[len(bad) // 2] ^= 0xFF
+        try:
+            out = rt.delta_decode(bytes(bad), cur.size, base)                    # either rejected or a different, in-range result
+            assert out.size == cur.size
+        except ValueError:
+            pass
+        with pytest.raises(ValueError):
+            rt.delta_decode(enc[: len(enc) // 2], cur.size, base)
+    assert rt.delta_decode(rt.delta_encode(np.zeros(0, np.uint8)), 0).size == 0
+    z = np.zeros(1 << 16, np.uint8)
+    assert len(rt.delta_encode(z, z, 2)) < 32
+
+
+@pytest.mark.parametrize("codec", ["auto", "zrle", "zlib"])
+def test_delta_writer_reader_and_snapshots(tmp_path, codec):
     from miles_b200.weight_update.delta import DeltaReader, DeltaWriter, SnapshotPublisher
 
     torch.manual_seed(0)
     w = {"a.weight": torch.randn(64, 32).bfloat16(), "b.weight": torch.randn(16).float()}
-    wr = DeltaWriter(str(tmp_path / "d"), full_every=3)
+    wr = DeltaWriter(str(tmp_path / "d"), full_every=3, codec=codec)
     rd = DeltaReader(str(tmp_path / "d"))
     infos = []
     for v in range(1, 6):
