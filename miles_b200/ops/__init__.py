@@ -215,3 +215,23 @@ def int4_fake_quant(x, block_m=1, block_n=32, symmetric=True):
 
 def nvfp4_qdq(x, global_amax=None, four_over_six=False):
     return _k().nvfp4_qdq(x, global_amax, four_over_six) if x.is_cuda else ref.nvfp4_qdq(x, global_amax, four_over_six=four_over_six)
+
+
+class _StraightThrough(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, mode):
+        if x.is_cuda and x.dtype == torch.bfloat16:
+            return _k().C.block_fake_quant(x.contiguous(), {"fp8": 0, "fp4": 1, "compressed_kv": 2}[mode])
+        return ref.block_fake_quant(x, mode)
+
+    @staticmethod
+    def backward(ctx, g):
+        return g, None
+
+
+def block_fake_quant(x, mode: str = "fp8"):
+    """Quantise → dequantise per block along the last axis with a straight-through gradient: `fp8` / `fp4` (1×32 blocks,
+    power-of-two scales: MXFP8 / MXFP4 numerics for quantisation-aware training), `compressed_kv` (1×16 blocks, e4m3
+    scales, e2m1 payload)."""
+    assert mode in ("fp8", "fp4", "compressed_kv")
+    return _StraightThrough.apply(x, mode)

@@ -146,6 +146,10 @@ def bench_elementwise(a):
     ms = timeit(lambda: K.nvfp4_qdq(xq, torch.ones(1, device="cuda")), a.iters)
     b = xq.numel() * 4
     out.append({"kernel": "nvfp4_qdq", "numel": xq.numel(), "ms": ms, "gbs": b / ms / 1e6, "roofline_frac": b / (hbm * 1e9) * 1e3 / ms, "roofline": tag})
+    for mode in (0, 1, 2):                      # MXFP8 / MXFP4 / compressed-KV style fake quantisation: read 2 B, write 2 B per element
+        ms = timeit(lambda: K.C.block_fake_quant(xq, mode), a.iters)
+        out.append({"kernel": f"block_fake_quant<{mode}>", "numel": xq.numel(), "ms": ms, "gbs": b / ms / 1e6,
+                    "roofline_frac": b / (hbm * 1e9) * 1e3 / ms, "roofline": tag})
     return out
 
 

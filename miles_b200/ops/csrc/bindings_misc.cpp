@@ -110,6 +110,14 @@ std::vector<at::Tensor> fp8_block_quant(const at::Tensor& w) {
   return {q, sc};
 }
 
+at::Tensor block_fake_quant(const at::Tensor& x, int64_t mode) {
+  c10::cuda::CUDAGuard g(x.device());
+  TORCH_CHECK(x.scalar_type() == at::kBFloat16 && x.is_contiguous(), "block_fake_quant: contiguous bf16 input");
+  at::Tensor y = at::empty_like(x);
+  check(mb_block_fake_quant(x.data_ptr(), y.data_ptr(), x.numel(), static_cast<int>(mode), cur_stream()), "mb_block_fake_quant");
+  return y;
+}
+
 std::vector<at::Tensor> int4_fake_quant(const at::Tensor& x, int64_t bm, int64_t bn, bool symmetric) {
   c10::cuda::CUDAGuard g(x.device());
   const int64_t M = x.size(0), N = x.size(1);
@@ -145,6 +153,7 @@ void register_misc(pybind11::module& m) {
   m.def("mxfp8_quant", &mxfp8_quant);
   m.def("fp8_block_quant", &fp8_block_quant);
   m.def("int4_fake_quant", &int4_fake_quant);
+  m.def("block_fake_quant", &block_fake_quant);
   m.def("absmax", &absmax);
   m.def("nvfp4_qdq", &nvfp4_qdq);
   // index checks of the debug build: limits are published per kind of index (0 cache slots, 1 MoE (token, choice) pairs,

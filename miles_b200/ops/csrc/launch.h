@@ -141,6 +141,7 @@ int mb_logit_grad(const float* logits, long long ld, const long long* targets, c
 int mb_mxfp8_quant(const void* x, void* q, void* scales, long long numel, cudaStream_t s);
 int mb_fp8_block_quant(const void* w, void* q, float* scale_inv, int M, int N, cudaStream_t s);
 int mb_int4_fake_quant(const void* x, void* y, float* scales, int M, int N, int bm, int bn, int symmetric, cudaStream_t s);
+int mb_block_fake_quant(const void* x, void* y, long long numel, int mode, cudaStream_t s);
 int mb_nvfp4_qdq(const void* x, void* y, const float* global_amax, long long numel, int four_over_six, cudaStream_t s);
 int mb_absmax(const void* x, float* out, long long numel, cudaStream_t s);
 

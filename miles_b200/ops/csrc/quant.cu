@@ -3,6 +3,8 @@
 //   fp8_block_quant  128×128 blocks, e4m3 payload, fp32 scale_inv — inference weight format
 //   int4_fake_quant  quantise→dequantise to int4 per [bm, bn] block, symmetric (/7) or asymmetric (/15 + zero point)
 //   nvfp4_qdq        quantise→dequantise to e2m1 with e4m3 1×16 block scales and an fp32 tensor scale
+//   block_fake_quant quantise→dequantise in one pass: 1×32 blocks with a power-of-two scale and an e4m3 or e2m1 payload
+//                    (MXFP8 / MXFP4 style), or 1×16 blocks with an e4m3 scale and an e2m1 payload (compressed-KV style)
 //   absmax           fp32 max |x| of a tensor (tensor scale for nvfp4)
 #include <cuda_bf16.h>
 #include <cuda_fp8.h>
@@ -58,6 +60,52 @@ __global__ void __launch_bounds__(256) mxfp8_quant_kernel(const bf16* __restrict
   uint4* dst = reinterpret_cast<uint4*>(q + b * 32);
   dst[0] = make_uint4(out[0], out[1], out[2], out[3]);
   dst[1] = make_uint4(out[4], out[5], out[6], out[7]);
+}
+
+// ---- block fake quantisation: 8 elements per lane, 4 lanes per 32-block (2 per 16-block) -------------------------------
+// MODE 0: 32-block, power-of-two scale, e4m3 payload.  MODE 1: 32-block, power-of-two scale, e2m1 payload.
+// MODE 2: 16-block, e4m3 scale clamped to [2^-9, 448], e2m1 payload.
+__device__ __forceinline__ float e2m1_round(float v) {          // v already clamped to [−6, 6]; ties to even, as rint on the grid
+  const float mag = fabsf(v);
+  const float step = mag < 2.f ? 0.5f : (mag < 4.f ? 1.f : 2.f);
+  const float q = rintf(mag / step) * step;
+  return v > 0.f ? q : (v < 0.f ? -q : 0.f);
+}
+__device__ __forceinline__ float e4m3_round(float v) {
+  const __nv_fp8_storage_t b = __nv_cvt_float_to_fp8(v, __NV_SATFINITE, __NV_E4M3);
+  return __half2float(__half(__nv_cvt_fp8_to_halfraw(b, __NV_E4M3)));
+}
+template <int MODE>
+__global__ void __launch_bounds__(256) block_fake_quant_kernel(const bf16* __restrict__ x, bf16* __restrict__ y, long long n8) {
+  const long long i = blockIdx.x * 256ll + threadIdx.x;
+  const bool live = i < n8;
+  float v[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+  if (live) ld8(x + i * 8, v);
+  float amax = 0.f;
+#pragma unroll
+  for (int k = 0; k < 8; ++k) amax = fmaxf(amax, fabsf(v[k]));
+  amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 1));
+  if (MODE != 2) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 2));
+  constexpr float FMAX = MODE == 0 ? 448.f : 6.f;
+  float scale;
+  if (MODE == 2) {
+    scale = e4m3_round(fminf(fmaxf(amax * (1.f / 6.f), 0.001953125f), 448.f));
+  } else {
+    const float floor_ = MODE == 0 ? 1e-4f : 6.f * 1.17549435e-38f;
+    const uint32_t bits = __float_as_uint(fmaxf(amax, floor_) * (1.f / FMAX));
+    int e = static_cast<int>((bits >> 23) & 0xff) - 127 + ((bits & 0x7fffff) ? 1 : 0);     // ceil to a power of two
+    scale = __uint_as_float(static_cast<uint32_t>(e + 127) << 23);
+  }
+  if (!live) return;
+  __nv_bfloat162 out[4];
+#pragma unroll
+  for (int k = 0; k < 8; k += 2) {
+    float a = fminf(fmaxf(__fdiv_rn(v[k], scale), -FMAX), FMAX), b = fminf(fmaxf(__fdiv_rn(v[k + 1], scale), -FMAX), FMAX);
+    a = (MODE == 0 ? e4m3_round(a) : e2m1_round(a)) * scale;
+    b = (MODE == 0 ? e4m3_round(b) : e2m1_round(b)) * scale;
+    out[k / 2] = __floats2bfloat162_rn(a, b);
+  }
+  *reinterpret_cast<uint4*>(y + i * 8) = *reinterpret_cast<const uint4*>(out);
 }
 
 // ---- FP8 128×128 blocks: one CTA per block ----------------------------------------------------------
@@ -286,6 +334,20 @@ extern "C" int mb_nvfp4_qdq(const void* x, void* y, const float* global_amax, lo
     nvfp4_qdq_kernel<true><<<grid, 256, 0, s>>>(reinterpret_cast<const bf16*>(x), reinterpret_cast<bf16*>(y), global_amax, np);
   else
     nvfp4_qdq_kernel<false><<<grid, 256, 0, s>>>(reinterpret_cast<const bf16*>(x), reinterpret_cast<bf16*>(y), global_amax, np);
+  return static_cast<int>(cudaGetLastError());
+}
+
+// mode 0: MXFP8-style, 1: MXFP4-style, 2: compressed-KV style (see block_fake_quant_kernel); numel a multiple of 32 (16 for mode 2)
+extern "C" int mb_block_fake_quant(const void* x, void* y, long long numel, int mode, cudaStream_t s) {
+  if (numel == 0) return 0;
+  if (mode < 0 || mode > 2 || numel % (mode == 2 ? 16 : 32)) return -1;
+  const long long n8 = numel / 8;
+  const unsigned grid = static_cast<unsigned>((n8 + 255) / 256);
+  const bf16* X = reinterpret_cast<const bf16*>(x);
+  bf16* Y = reinterpret_cast<bf16*>(y);
+  if (mode == 0) block_fake_quant_kernel<0><<<grid, 256, 0, s>>>(X, Y, n8);
+  else if (mode == 1) block_fake_quant_kernel<1><<<grid, 256, 0, s>>>(X, Y, n8);
+  else block_fake_quant_kernel<2><<<grid, 256, 0, s>>>(X, Y, n8);
   return static_cast<int>(cudaGetLastError());
 }
 

@@ -334,3 +334,39 @@ def nvfp4_qdq(x: torch.Tensor, global_amax: torch.Tensor | None = None, block: i
 def allreduce_add_rmsnorm(parts: list[torch.Tensor], residual: torch.Tensor, w: torch.Tensor, eps: float):
     s = torch.stack([p.float() for p in parts]).sum(0).to(parts[0].dtype)
     return add_rmsnorm(s, residual, w, eps)
+
+
+# --------------------------------------------------------------------------------------------
+# block fake quantisation (quantise → dequantise in the input's dtype)
+# --------------------------------------------------------------------------------------------
+
+def _ceil_pow2(v: torch.Tensor) -> torch.Tensor:
+    bits = v.float().contiguous().view(torch.int32)
+    e = ((bits >> 23) & 0xFF) - 127 + ((bits & 0x7FFFFF) != 0).to(torch.int32)
+    return ((e + 127) << 23).view(torch.float32)
+
+
+def _e2m1_round(v: torch.Tensor) -> torch.Tensor:
+    mag = v.abs()
+    step = torch.where(mag < 2.0, torch.full_like(mag, 0.5), torch.where(mag < 4.0, torch.ones_like(mag), torch.full_like(mag, 2.0)))
+    return torch.round(mag / step) * step * torch.sign(v)          # torch.round: ties to even, like rint
+
+
+def block_fake_quant(x: torch.Tensor, mode: str = "fp8") -> torch.Tensor:
+    """`fp8`: 1×32 blocks, power-of-two scale, e4m3 payload (MXFP8 style).  `fp4`: the same with an e2m1 payload (MXFP4
+    style).  `compressed_kv`: 1×16 blocks, e4m3 scale in [2^-9, 448], e2m1 payload.  Blocks run along the last axis.
+    Reference behaviour: miles/kernels/quant/fake_quant.py:24-62."""
+    block = 16 if mode == "compressed_kv" else 32
+    assert x.shape[-1] % block == 0, f"last dimension must be a multiple of {block}"
+    v = x.float().reshape(-1, block)
+    amax = v.abs().amax(dim=1)
+    if mode == "compressed_kv":
+        scale = (amax * (1.0 / 6.0)).clamp(2.0 ** -9, 448.0).to(torch.float8_e4m3fn).float()
+        fmax = 6.0
+    else:
+        fmax = 448.0 if mode == "fp8" else 6.0
+        floor = 1e-4 if mode == "fp8" else 6 * 2.0 ** -126
+        scale = _ceil_pow2(amax.clamp_min(floor) * (1.0 / fmax))
+    scaled = (v / scale[:, None]).clamp(-fmax, fmax)
+    q = scaled.to(torch.float8_e4m3fn).float() if mode == "fp8" else _e2m1_round(scaled)
+    return (q * scale[:, None]).reshape(x.shape).to(x.dtype)

@@ -353,3 +353,23 @@ def test_grouped_mxfp8_gemm_and_moe_forward():
     # e4m3 keeps 3 mantissa bits: two chained products of quantised operands land within ≈ 7 % of bf16
     assert 1e-3 < _rel(outs[True][0], outs[False][0]) < 0.1        # really quantised, and close
     assert _rel(outs[True][1], outs[False][1]) < 0.15 and _rel(outs[True][2], outs[False][2]) < 0.15
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("mode", ["fp8", "fp4", "compressed_kv"])
+def test_block_fake_quant_kernel_matches_the_reference_bit_for_bit(mode):
+    """One-pass quantise → dequantise (1×32 power-of-two scales with e4m3 / e2m1 payloads, 1×16 e4m3 scales with e2m1)
+    against the fp32 PyTorch statement of the same arithmetic, over magnitudes from 1e-4 to 1e3 and exact zeros."""
+    from miles_b200 import ops
+    from miles_b200.ops import reference as ref
+
+    torch.manual_seed(3)
+    x = (torch.randn(512, 4096, device="cuda") * torch.logspace(-4, 3, 512, device="cuda")[:, None]).bfloat16()
+    x[7] = 0
+    x[9, ::3] = 0
+    want = ref.block_fake_quant(x, mode)
+    xin = x.clone().requires_grad_(True)
+    got = ops.block_fake_quant(xin, mode)
+    assert got.dtype == torch.bfloat16 and torch.equal(got, want), float((got.float() - want.float()).abs().max())
+    got.sum().backward()
+    assert torch.equal(xin.grad, torch.ones_like(x))
