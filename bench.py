@@ -52,6 +52,10 @@ def parse():
     p.add_argument("--fp8-recipe", choices=["none", "mxfp8"], default="none",
                    help="mxfp8: forward projections (dense and expert) on the block-scaled tensor-core path, backward in bf16 — the "
                         "secondary MXFP8 training config; the headline run is bf16")
+    p.add_argument("--warmup-max-new-tokens", type=int, default=256,
+                   help="response cap of the untimed warm-up steps (same pipeline, same prompts and batch: graphs, allocator pools, "
+                        "communicators and clocks are warmed by the prompt-dominated work; the cap keeps 5 warm-up steps of the "
+                        "8-GPU run inside a fixed launch window); 0 = the full cap")
     p.add_argument("--quiet", action="store_true")
     return p.parse_args()
 
@@ -256,8 +260,14 @@ def main():
                 phases[k[5:-5]] = phases.get(k[5:-5], 0.0) + float(v)
         return metrics
 
+    full_cap = args.rollout_max_response_len
+    warm_cap = min(full_cap, a.warmup_max_new_tokens) if a.warmup_max_new_tokens > 0 else full_cap
     for i in range(a.warmup):
-        m = step(i)
+        args.rollout_max_response_len = executor.local_args.rollout_max_response_len = warm_cap
+        try:
+            m = step(i)
+        finally:
+            args.rollout_max_response_len = executor.local_args.rollout_max_response_len = full_cap
         if rank == 0 and not a.quiet:
             print(f"[warmup {i}] tokens={counters['tokens']} rollout={counters['rollout_s']:.1f}s train={counters['train_s']:.1f}s "
                   f"loss={m.get('train/loss', float('nan')):.4g} grad_norm={m.get('train/grad_norm', float('nan')):.4g}",
@@ -305,7 +315,7 @@ def main():
         value = total_tokens / (dev_ms / 1e3)
         out = {
             "metric": "GRPO tokens/s/box (rollout+train+weight-sync)", "value": value, "unit": "tokens/s", "n_gpus": world,
-            "steps": a.steps, "warmup": a.warmup, "ms_per_step": dev_ms / a.steps, "higher_is_better": True, "scaling": "weak",
+            "steps": a.steps, "warmup": a.warmup, "warmup_max_new_tokens": warm_cap, "ms_per_step": dev_ms / a.steps, "higher_is_better": True, "scaling": "weak",
             "vs_baseline": (value / BASELINE_TOKENS_PER_S) if BASELINE_TOKENS_PER_S else None,
             "dtype": "bf16" if a.fp8_recipe == "none" else "mxfp8 forward (e4m3, 1x32 e8m0 scales) + bf16 backward",
             "data": "synthetic prompts (uniform random ids), random-init weights, rule reward (last id mod 7 == 0)",
@@ -320,6 +330,8 @@ def main():
                 "mean_response_len_target": a.mean_response_len, "seq_len": a.prompt_len_max + a.max_new_tokens,
                 "parallelism": f"ep{world}-dp{world}", "fused_comm": bool(ps.fabric is not None),
                 "cache": "inputs larger than L2 (weights + KV + activations ≫ 126 MB per step)",
+                "warmup_steps": ("same pipeline, prompts and batch as the timed steps"
+                                 + (f", responses capped at {warm_cap} new tokens" if warm_cap != full_cap else ", full response cap")),
             },
             "clocks": clocks,
             "e2e": {"value": total_tokens / (wall_ms / 1e3), "unit": "tokens/s", "h2d_bytes_per_step": counters["h2d"] // a.steps,
