@@ -334,6 +334,53 @@ class Qwen3Model(nn.Module):
                                               self.cfg.vocab_size)
 
 
+class VirtualStages(nn.Module):
+    """The model chunks of one pipeline rank under the interleaved schedule: with `pp` ranks and `vpp` chunks per rank the
+    layers are cut into pp · vpp virtual stages and rank r owns stages r, r + pp, r + 2·pp, …  (Megatron's virtual pipeline,
+    miles/backends/megatron_utils/model.py:395-411).  Each chunk is a `Qwen3Model` over its layer range: the chunk with layer 0
+    embeds, the one with the last layer applies the final norm and owns the head.  Parameter names are global
+    (`named_parameters_global`), so checkpoints and weight sync do not see the cut."""
+
+    def __init__(self, cfg: ModelConfig, ps: ParallelState, dtype=torch.bfloat16, device="cpu", seed: int = 0):
+        super().__init__()
+        self.cfg, self.ps, self.dtype = cfg, ps, dtype
+        n_virtual = ps.pp_size * ps.vpp_size
+        assert cfg.num_layers >= n_virtual, f"{cfg.num_layers} layers cannot fill {n_virtual} virtual stages"
+        base, rem = divmod(cfg.num_layers, n_virtual)          # the first `rem` virtual stages take one layer more
+        start = [v * base + min(v, rem) for v in range(n_virtual + 1)]
+        chunks = []
+        for c in range(ps.vpp_size):
+            v = c * ps.pp_size + ps.pp_rank
+            lo, hi = start[v], start[v + 1]
+            chunks.append(Qwen3Model(cfg, ps, dtype=dtype, device=device, seed=seed, layer_range=(lo, hi)))
+        self.chunks = nn.ModuleList(chunks)
+        self.layer_range = (chunks[0].layer_range[0], chunks[-1].layer_range[1])
+        self.has_embed, self.has_head = chunks[0].has_embed, chunks[-1].has_head
+        self.num_moe_layers = chunks[0].num_moe_layers
+
+    def forward(self, tokens, meta, hidden_in=None, inputs_embeds=None, chunk: int = 0):
+        return self.chunks[chunk](tokens, meta, hidden_in=hidden_in, inputs_embeds=inputs_embeds)
+
+    def global_name(self, name: str) -> str:
+        if name.startswith("chunks."):
+            _, c, rest = name.split(".", 2)
+            return self.chunks[int(c)].global_name(rest)
+        return name
+
+    def named_parameters_global(self):
+        for n, p in self.named_parameters():
+            yield self.global_name(n), p
+
+    def head_weight(self):
+        return self.chunks[-1].head_weight()
+
+    def logits(self, hidden):
+        return self.chunks[-1].logits(hidden)
+
+    def log_probs(self, hidden, targets, temperature: float = 1.0, with_entropy: bool = False):
+        return self.chunks[-1].log_probs(hidden, targets, temperature, with_entropy)
+
+
 def _checkpoint(layer, x, residual, meta):
     from torch.utils.checkpoint import checkpoint
 
@@ -367,6 +414,8 @@ def build_model(cfg: ModelConfig, ps: ParallelState | None = None, dtype=torch.b
 
         return build_family_model(cfg, ps, dtype=dtype, device=device, seed=seed)
     layer_range = None
+    if ps.pp_size > 1 and getattr(ps, "vpp_size", 1) > 1:
+        return VirtualStages(cfg, ps, dtype=dtype, device=device, seed=seed)
     if ps.pp_size > 1:
         per = math.ceil(cfg.num_layers / ps.pp_size)
         layer_range = (ps.pp_rank * per, min(cfg.num_layers, (ps.pp_rank + 1) * per))

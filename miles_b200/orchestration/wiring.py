@@ -35,7 +35,8 @@ def create_parallel_state(args) -> ParallelState:
         return ParallelState.single()
     ps = ParallelState.build(
         tp=args.tensor_model_parallel_size, cp=args.context_parallel_size, pp=args.pipeline_model_parallel_size,
-        ep=args.expert_model_parallel_size, sequence_parallel=args.sequence_parallel, cp_comm_type=args.cp_comm_type)
+        ep=args.expert_model_parallel_size, sequence_parallel=args.sequence_parallel, cp_comm_type=args.cp_comm_type,
+        vpp=getattr(args, "virtual_pipeline_model_parallel_size", None) or 1)
     ps.fused = not getattr(args, "disable_fused_comm", False)
     if torch.cuda.is_available() and ps.fused and (ps.tp_size > 1 or ps.ep_size > 1 or ps.dp_size > 1):
         from ..parallel.fabric import Fabric

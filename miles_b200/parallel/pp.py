@@ -9,7 +9,8 @@ Schedules (`--pp-schedule`): `1f1b` (default, `PipeStage.run_1f1b`) is Megatron'
 warm-up forwards, then one forward and one backward per step with the two directions exchanged in ONE grouped p2p call,
 then the remaining backwards — so a stage keeps at most `pp − rank` micro-batches of activations; `gpipe` runs all
 forwards and then all backwards (`recv_forward` / `send_forward` / `backward`), with sends posted asynchronously and
-completed before the next send.  Interleaved (virtual-stage) 1F1B is not built.
+completed before the next send.  With `--virtual-pipeline-model-parallel-size v` every rank owns v model chunks and the
+interleaved order runs in `train/step_runner.py` (`InterleavedStepRunner`) over `models/qwen3.py` (`VirtualStages`).
 """
 from __future__ import annotations
 

@@ -31,6 +31,7 @@ class ParallelState:
     cp_size: int = 1
     dp_size: int = 1
     pp_size: int = 1
+    vpp_size: int = 1                 # model chunks per pipeline rank (interleaved schedule)
     ep_size: int = 1
     tp_rank: int = 0
     cp_rank: int = 0
@@ -48,6 +49,8 @@ class ParallelState:
     cp_group: Any = None
     dp_group: Any = None
     pp_group: Any = None
+    pp_fwd_group: Any = None          # interleaved schedule only: activations / gradients on communicators of their own
+    pp_bwd_group: Any = None
     ep_group: Any = None
     edp_group: Any = None
     dp_cp_group: Any = None
@@ -99,7 +102,7 @@ class ParallelState:
     @staticmethod
     def build(tp: int = 1, cp: int = 1, pp: int = 1, ep: int = 1, *, sequence_parallel: bool | None = None,
               cp_comm_type: str = "p2p", create_groups: bool = True, rank: int | None = None,
-              world_size: int | None = None) -> "ParallelState":
+              world_size: int | None = None, vpp: int = 1) -> "ParallelState":
         """Create all groups.  Every rank must call this with identical arguments."""
         if world_size is None:
             world_size = dist.get_world_size() if dist.is_initialized() else 1
@@ -114,6 +117,7 @@ class ParallelState:
                            ep_size=ep, tp_rank=t, cp_rank=c, dp_rank=d, pp_rank=p,
                            sequence_parallel=(tp > 1) if sequence_parallel is None else sequence_parallel,
                            cp_comm_type=cp_comm_type)
+        ps.vpp_size = max(1, int(vpp or 1)) if pp > 1 else 1
         in_block = rank % block
         ps.ep_rank = in_block % ep
         ps.edp_size = block // ep
@@ -132,6 +136,12 @@ class ParallelState:
             "ep": [[p_ * block + g * ep + i for i in range(ep)] for p_ in range(pp) for g in range(block // ep)],
             "edp": [[p_ * block + g * ep + i for g in range(block // ep)] for p_ in range(pp) for i in range(ep)],
         }
+        if ps.vpp_size > 1:
+            # interleaved schedule: activations and gradients travel on communicators of their own, so that each ordered pair
+            # of ranks carries ONE stream per communicator (with two stages the wrap-around gradients share a direction with
+            # the activations) and message order alone matches sends to receives
+            groups["pp_fwd"] = [list(g) for g in groups["pp"]]
+            groups["pp_bwd"] = [list(g) for g in groups["pp"]]
         from .reloadable import REGISTRY
 
         for name, lists in groups.items():

@@ -131,6 +131,8 @@ def _dist_hist(tmp_path, extra, world=2):
     "--context-parallel-size 2 --allgather-cp",                             # cp2, K/V all-gathered
     "--pipeline-model-parallel-size 2 --micro-batch-size 8",                # pp2, 4 micro-batches per step, 1F1B order
     "--pipeline-model-parallel-size 2 --micro-batch-size 8 --pp-schedule gpipe",
+    # pp2 × 2 model chunks per rank (4 virtual stages of one layer), interleaved 1F1B
+    "--pipeline-model-parallel-size 2 --virtual-pipeline-model-parallel-size 2 --num-layers 4 --micro-batch-size 8",
     # the tiny plumbing config: 16 prompts of length 32 per step, groups of 4, 32 new tokens, lr 1e-5, 3 steps
     "--rollout-batch-size 16 --synthetic-prompt-len 32 32 --rollout-max-response-len 32 --lr 1e-5 --num-rollout 3 --kl-coef 0",
 ])
@@ -140,6 +142,20 @@ def test_grpo_two_ranks(tmp_path, extra):
     assert max(r["train/train_rollout_logprob_abs_diff"] for r in rows) < 1e-5
     assert abs(rows[0]["train/ppo_kl"]) < 1e-6
     assert all(r["train/grad_norm"] > 0 for r in rows)
+
+
+def test_virtual_pipeline_checkpoint_resumes_and_loads_under_a_plain_pipeline(tmp_path):
+    """A store written by pp2 × 2 virtual stages resumes under the same layout and loads under plain pp2: entry names are the
+    model's, not the cut's."""
+    d = str(tmp_path / "ckpt")
+    for sub in "abc":
+        (tmp_path / sub).mkdir()
+    vpp = "--pipeline-model-parallel-size 2 --virtual-pipeline-model-parallel-size 2 --num-layers 4 --micro-batch-size 8"
+    _dist_hist(tmp_path / "a", f"{vpp} --save {d} --save-interval 1 --num-rollout 2")
+    rows = _dist_hist(tmp_path / "b", f"{vpp} --save {d} --load {d} --save-interval 1 --num-rollout 3")
+    assert [r["rollout/step"] for r in rows] == [2] and rows[0]["train/train_rollout_logprob_abs_diff"] < 1e-5
+    rows = _dist_hist(tmp_path / "c", f"--pipeline-model-parallel-size 2 --num-layers 4 --micro-batch-size 8 --load {d} --num-rollout 4")
+    assert [r["rollout/step"] for r in rows] == [3] and rows[0]["train/train_rollout_logprob_abs_diff"] < 1e-5
 
 
 def test_fsdp_checkpoint_save_and_resume(tmp_path):

@@ -257,3 +257,93 @@ def test_custom_step_runner_is_used(tmp_path):
         assert my_runner.CALLS["fwd"] >= 1 and my_runner.CALLS["fwd_bwd"] >= 1 and h.series("train/grad_norm")[0] > 0
     finally:
         sys.path.remove(str(tmp_path))
+
+
+# ---- virtual pipeline (interleaved schedule): gradients equal the unpartitioned model's --------------------------------
+
+def _vpp_body(rank, world, out_dir):
+    import types
+
+    import torch
+
+    from miles_b200.models.config import PRESETS
+    from miles_b200.models.qwen3 import ForwardMeta, build_model
+    from miles_b200.parallel.state import ParallelState, init_distributed
+    from miles_b200.train.data import pack_micro_batch
+    from miles_b200.train.step_runner import InterleavedStepRunner
+
+    init_distributed(backend="gloo")
+    ps = ParallelState.build(pp=2, vpp=2)
+    cfg = PRESETS["tiny"].with_(num_layers=5)              # 5 layers over 4 virtual stages: the first takes two
+    model = build_model(cfg, ps, dtype=torch.float32, device="cpu", seed=3)
+    assert [c.layer_range for c in model.chunks] == ([(0, 2), (3, 4)] if rank == 0 else [(2, 3), (4, 5)])
+    g = torch.Generator().manual_seed(1)
+    shard = {"tokens": [torch.randint(3, cfg.vocab_size, (int(n),), generator=g).tolist() for n in (9, 12, 7, 10, 8, 11)],
+             "response_lengths": [4, 5, 3, 6, 2, 5]}
+    shard["total_lengths"] = [len(t) for t in shard["tokens"]]
+    shard["loss_masks"] = [[1] * r for r in shard["response_lengths"]]
+    mbs = [[0, 1], [2], [3, 4], [5]]
+
+    class A:
+        pass
+
+    a = A()
+    a.ps, a.cfg, a.model, a.device = ps, cfg, model, torch.device("cpu")
+    a._meta = lambda pb, replay: ForwardMeta(positions=pb.positions, cu_seqlens=pb.cu_seqlens, max_seqlen=pb.max_seqlen)
+
+    def score_hidden(pb, hidden, with_entropy):
+        return model.log_probs(hidden[pb.gather_index], pb.targets, 1.0, with_entropy)
+
+    a._score_hidden = score_hidden
+    runner = InterleavedStepRunner(a)
+    pack = lambda idx: pack_micro_batch(shard, idx, "cpu", pad_multiple=1)
+    weights = {0: 1.0, 1: -0.5, 2: 2.0, 3: 0.25}
+    key = {id(m): i for i, m in enumerate(mbs)}
+    runner.forward_backward_step(mbs, pack, lambda pb, idx, out, ent: out.sum() * weights[key[id(idx)]], want_ent=False, replay=False)
+    grads = {n: p.grad.clone() for n, p in model.named_parameters_global() if p.grad is not None}
+    lps = runner.forward_only_step(mbs, pack, lambda pb, idx, lp: lp.clone(), replay=False)
+    torch.save({"grads": grads, "lps": lps}, f"{out_dir}/r{rank}.pt")
+
+
+def test_interleaved_virtual_pipeline_matches_the_unpartitioned_model(tmp_path):
+    import os
+    import sys
+
+    import torch
+
+    sys.path.insert(0, os.path.dirname(__file__))
+    from dist_utils import run_distributed
+
+    from miles_b200.models.config import PRESETS
+    from miles_b200.models.qwen3 import ForwardMeta, build_model
+    from miles_b200.parallel.state import ParallelState
+    from miles_b200.train.data import pack_micro_batch
+
+    run_distributed(_vpp_body, 2, (str(tmp_path),), timeout=300)
+    cfg = PRESETS["tiny"].with_(num_layers=5)
+    model = build_model(cfg, ParallelState.single(), dtype=torch.float32, device="cpu", seed=3)
+    g = torch.Generator().manual_seed(1)
+    shard = {"tokens": [torch.randint(3, cfg.vocab_size, (int(n),), generator=g).tolist() for n in (9, 12, 7, 10, 8, 11)],
+             "response_lengths": [4, 5, 3, 6, 2, 5]}
+    shard["total_lengths"] = [len(t) for t in shard["tokens"]]
+    shard["loss_masks"] = [[1] * r for r in shard["response_lengths"]]
+    mbs, weights = [[0, 1], [2], [3, 4], [5]], [1.0, -0.5, 2.0, 0.25]
+    want_lp = []
+    for idx, w in zip(mbs, weights):
+        pb = pack_micro_batch(shard, idx, "cpu", pad_multiple=1)
+        h = model(pb.tokens, ForwardMeta(positions=pb.positions, cu_seqlens=pb.cu_seqlens, max_seqlen=pb.max_seqlen))
+        lp, _ = model.log_probs(h[pb.gather_index], pb.targets)
+        (lp.sum() * w).backward()
+        want_lp.append(lp.detach())
+    want = {n: p.grad for n, p in model.named_parameters()}
+    got = {}
+    outs = [torch.load(f"{tmp_path}/r{r}.pt") for r in range(2)]
+    for o in outs:
+        assert not (set(o["grads"]) & set(got)), "a parameter lives on one virtual stage only"
+        got.update(o["grads"])
+    assert set(got) == set(want), (sorted(set(want) - set(got)), sorted(set(got) - set(want)))
+    for n in want:
+        assert torch.allclose(got[n], want[n], rtol=1e-4, atol=1e-5), n
+    for o in outs:                                                   # forward-only: every stage ends with the same record
+        for a, b in zip(o["lps"], want_lp):
+            assert torch.allclose(a, b, rtol=1e-4, atol=1e-5)
