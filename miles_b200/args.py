@@ -126,7 +126,10 @@ def build_parser() -> argparse.ArgumentParser:
     g.add_argument("--expert-model-parallel-size", type=int, default=1)
     g.add_argument("--expert-tensor-parallel-size", type=int, default=1)
     _bool_flag(g, "--sequence-parallel")
-    g.add_argument("--cp-comm-type", choices=["p2p", "a2a", "allgather"], default="p2p")
+    g.add_argument("--cp-comm-type", choices=["p2p", "a2a", "allgather", "a2a+p2p"], default="p2p")
+    g.add_argument("--hierarchical-context-parallel-sizes", type=int, nargs=2, default=None, metavar=("A2A", "P2P"),
+                   help="with --cp-comm-type a2a+p2p: size of the inner all-to-all (head-swapping) groups and of the outer ring; "
+                        "their product is the context-parallel size")
     _bool_flag(g, "--allgather-cp")
     _bool_flag(g, "--indep-dp")
     g.add_argument("--indep-dp-num-cells", type=int, default=1, help="independent training worlds (cells) averaging gradients")

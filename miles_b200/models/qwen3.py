@@ -116,7 +116,8 @@ class Attention(nn.Module):
             if self.ps.cp_size > 1 and not self.ps.is_ulysses_cp:
                 # ring (zigzag pieces, K/V travel round the group) or all-gather context parallelism
                 from ..parallel import cp_ring as _ring
-                fn = _ring.allgather_attention if self.ps.cp_comm_type == "allgather" else _ring.ring_attention
+                fn = {"allgather": _ring.allgather_attention, "a2a+p2p": _ring.hierarchical_attention}.get(
+                    self.ps.cp_comm_type, _ring.ring_attention)
                 o = fn(q, k, v, meta.cu_seqlens, self.ps)
             elif self.ps.cp_size > 1:
                 # context parallel (Ulysses): tokens are sharded in contiguous chunks; swap to a head sharding for the

@@ -36,7 +36,8 @@ def create_parallel_state(args) -> ParallelState:
     ps = ParallelState.build(
         tp=args.tensor_model_parallel_size, cp=args.context_parallel_size, pp=args.pipeline_model_parallel_size,
         ep=args.expert_model_parallel_size, sequence_parallel=args.sequence_parallel, cp_comm_type=args.cp_comm_type,
-        vpp=getattr(args, "virtual_pipeline_model_parallel_size", None) or 1)
+        vpp=getattr(args, "virtual_pipeline_model_parallel_size", None) or 1,
+        cp_hierarchy=tuple(args.hierarchical_context_parallel_sizes) if getattr(args, "hierarchical_context_parallel_sizes", None) else None)
     ps.fused = not getattr(args, "disable_fused_comm", False)
     if torch.cuda.is_available() and ps.fused and (ps.tp_size > 1 or ps.ep_size > 1 or ps.dp_size > 1):
         from ..parallel.fabric import Fabric

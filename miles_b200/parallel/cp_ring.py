@@ -28,6 +28,8 @@ from . import cp as _cp
 
 
 def layout_mode(ps) -> str:
+    if ps.cp_comm_type == "a2a+p2p":
+        return "hier"
     return "zigzag" if ps.cp_comm_type == "p2p" else "contiguous"
 
 
@@ -40,7 +42,13 @@ def rank_token_index(total: int, cp_size: int, rank: int, mode: str, device=None
 
 
 def token_index(total: int, ps, device=None) -> torch.Tensor:
-    """Global indices of the tokens of a length-`total` packed batch held by this CP rank (layout by `cp_comm_type`)."""
+    """Global indices of the tokens of a length-`total` packed batch held by this CP rank (layout by `cp_comm_type`).
+    Hierarchical (`a2a+p2p`): the ring member's two zigzag pieces, cut evenly over the members of its all-to-all group."""
+    if layout_mode(ps) == "hier":
+        a, i, o = ps.cp_a2a_size, ps.cp_rank % ps.cp_a2a_size, ps.cp_rank // ps.cp_a2a_size
+        piece = rank_token_index(total, ps.cp_p2p_size, o, "zigzag", device)
+        n = piece.numel() // a
+        return piece[i * n:(i + 1) * n]
     return rank_token_index(total, ps.cp_size, ps.cp_rank, layout_mode(ps), device)
 
 
@@ -137,6 +145,26 @@ class _RingAttention(torch.autograd.Function):
             # the chunk and its gradient accumulators move on; after cp steps they are back at their owner
             kc, vc, dkc, dvc = _exchange([kc, vc, dkc, dvc], group, cp_size, cp_rank)
         return dq.to(q.dtype), dkc.to(k.dtype), dvc.to(v.dtype), None, None, None, None, None, None, None
+
+
+def hierarchical_attention(q, k, v, cu_seqlens, ps, scale: float | None = None):
+    """`a2a+p2p` context parallelism (the reference takes it from Megatron's hierarchical CP): inside an all-to-all group
+    the members swap their sequence slices for head groups, so each holds the whole ring piece for H / a2a heads; K/V then
+    travel round the ring of p2p members; the inverse all-to-all restores the sequence sharding."""
+    from . import cp as _cp
+
+    a, r = ps.cp_a2a_size, ps.cp_p2p_size
+    total = q.shape[0] * ps.cp_size
+    scale = scale if scale is not None else 1.0 / math.sqrt(q.shape[-1])
+    if a > 1:
+        q, k, v = (_cp._SeqToHeads.apply(t.contiguous(), ps.cp_a2a_group, a) for t in (q, k, v))
+    if r > 1:
+        o = _RingAttention.apply(q, k, v, cu_seqlens, total, ps.cp_p2p_group, r, ps.cp_rank // a, "zigzag", scale)
+    else:                                  # a ring of one: the all-to-all group holds the whole batch (plain Ulysses)
+        from .. import ops
+
+        o = ops.attention_varlen(q, k, v, cu_seqlens, int((cu_seqlens[1:] - cu_seqlens[:-1]).max()))
+    return _cp._HeadsToSeq.apply(o.contiguous(), ps.cp_a2a_group, a) if a > 1 else o
 
 
 def ring_attention(q, k, v, cu_seqlens, ps, scale: float | None = None):

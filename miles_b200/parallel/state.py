@@ -41,7 +41,11 @@ class ParallelState:
     edp_size: int = 1
     edp_rank: int = 0
     sequence_parallel: bool = False
-    cp_comm_type: str = "p2p"          # p2p (ring) | a2a (Ulysses) | allgather
+    cp_comm_type: str = "p2p"          # p2p (ring) | a2a (Ulysses) | allgather | a2a+p2p (hierarchical)
+    cp_a2a_size: int = 1               # hierarchical CP: cp rank = p2p index · a2a size + a2a index
+    cp_p2p_size: int = 1
+    cp_a2a_group: Any = None
+    cp_p2p_group: Any = None
     indep_dp_size: int = 1
     indep_dp_rank: int = 0
     # process groups (None when size 1 or not initialised)
@@ -102,7 +106,7 @@ class ParallelState:
     @staticmethod
     def build(tp: int = 1, cp: int = 1, pp: int = 1, ep: int = 1, *, sequence_parallel: bool | None = None,
               cp_comm_type: str = "p2p", create_groups: bool = True, rank: int | None = None,
-              world_size: int | None = None, vpp: int = 1) -> "ParallelState":
+              world_size: int | None = None, vpp: int = 1, cp_hierarchy: tuple[int, int] | None = None) -> "ParallelState":
         """Create all groups.  Every rank must call this with identical arguments."""
         if world_size is None:
             world_size = dist.get_world_size() if dist.is_initialized() else 1
@@ -136,6 +140,13 @@ class ParallelState:
             "ep": [[p_ * block + g * ep + i for i in range(ep)] for p_ in range(pp) for g in range(block // ep)],
             "edp": [[p_ * block + g * ep + i for g in range(block // ep)] for p_ in range(pp) for i in range(ep)],
         }
+        if cp_comm_type == "a2a+p2p":
+            a2a, p2p = cp_hierarchy or (cp, 1)
+            assert a2a * p2p == cp, f"hierarchical context parallel sizes {a2a} × {p2p} must multiply to cp = {cp}"
+            ps.cp_a2a_size, ps.cp_p2p_size = a2a, p2p
+            # inner groups: neighbouring cp ranks swap sequence for heads; outer groups: K/V travel round a ring of p2p members
+            groups["cp_a2a"] = [g[o * a2a:(o + 1) * a2a] for g in groups["cp"] for o in range(p2p)]
+            groups["cp_p2p"] = [g[i::a2a] for g in groups["cp"] for i in range(a2a)]
         if ps.vpp_size > 1:
             # interleaved schedule: activations and gradients travel on communicators of their own, so that each ordered pair
             # of ranks carries ONE stream per communicator (with two stages the wrap-around gradients share a direction with

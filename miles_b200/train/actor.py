@@ -359,7 +359,7 @@ class TrainActor:
         return [out[i] for i in sorted(out)]
 
     def _pad_multiple(self) -> int:
-        zigzag = 2 if (self.ps.cp_size > 1 and self.ps.cp_comm_type == "p2p") else 1     # ring CP: two pieces per rank
+        zigzag = 2 if (self.ps.cp_size > 1 and self.ps.cp_comm_type in ("p2p", "a2a+p2p")) else 1     # ring CP: two pieces per rank
         mult = int(getattr(self.args, "data_pad_size_multiplier", 128) or 128)
         return max(1, self.ps.tp_size) * max(1, self.ps.cp_size) * zigzag * (mult if self.device.type == "cuda" else 1)
 

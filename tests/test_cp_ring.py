@@ -17,7 +17,7 @@ def _body(rank, world, comm, cp_size):
     from miles_b200.parallel import cp_ring
     from miles_b200.parallel.state import ParallelState
 
-    ps = ParallelState.build(cp=cp_size, cp_comm_type=comm)
+    ps = ParallelState.build(cp=cp_size, cp_comm_type=comm, cp_hierarchy=(2, cp_size // 2) if comm == "a2a+p2p" else None)
     torch.manual_seed(0)                                   # same tensors on every rank
     lens = [7, 12, 5]                                      # 24 real tokens + 8 padding tokens
     T, Hq, Hkv, D = 32, 4, 2, 8
@@ -31,7 +31,7 @@ def _body(rank, world, comm, cp_size):
     own = cp_ring.token_index(T, ps)
     assert own.numel() == T // cp_size
     ql, kl, vl = (t.detach()[own].clone().requires_grad_() for t in (q, k, v))
-    fn = cp_ring.allgather_attention if comm == "allgather" else cp_ring.ring_attention
+    fn = {"allgather": cp_ring.allgather_attention, "a2a+p2p": cp_ring.hierarchical_attention}.get(comm, cp_ring.ring_attention)
     o = fn(ql, kl, vl, cu, ps)
     real = own < 24
     assert torch.allclose(o[real], o_ref.detach()[own[real]], atol=1e-5), (o[real] - o_ref.detach()[own[real]]).abs().max()
@@ -43,7 +43,7 @@ def _body(rank, world, comm, cp_size):
     assert torch.allclose(vl.grad[real], gv[own[real]], atol=1e-5)
 
 
-@pytest.mark.parametrize("comm,world", [("p2p", 2), ("allgather", 2), ("p2p", 4)])
+@pytest.mark.parametrize("comm,world", [("p2p", 2), ("allgather", 2), ("p2p", 4), ("a2a+p2p", 4), ("a2a+p2p", 2)])
 def test_cp_attention_matches_single_rank(comm, world):
     run_distributed(_body, world, (comm, world), timeout=300)
 

@@ -144,6 +144,14 @@ def test_grpo_two_ranks(tmp_path, extra):
     assert all(r["train/grad_norm"] > 0 for r in rows)
 
 
+def test_grpo_hierarchical_context_parallel_four_ranks(tmp_path):
+    """cp = 4 as all-to-all groups of 2 inside a ring of 2 (`--cp-comm-type a2a+p2p`): same invariants as the other layouts."""
+    rows = _dist_hist(tmp_path, "--context-parallel-size 4 --cp-comm-type a2a+p2p --hierarchical-context-parallel-sizes 2 2", world=4)
+    assert len(rows) == 2
+    assert max(r["train/train_rollout_logprob_abs_diff"] for r in rows) < 1e-5
+    assert abs(rows[0]["train/ppo_kl"]) < 1e-6 and all(r["train/grad_norm"] > 0 for r in rows)
+
+
 def test_virtual_pipeline_checkpoint_resumes_and_loads_under_a_plain_pipeline(tmp_path):
     """A store written by pp2 × 2 virtual stages resumes under the same layout and loads under plain pp2: entry names are the
     model's, not the cut's."""
