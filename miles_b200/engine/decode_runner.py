@@ -85,6 +85,7 @@ class DecodeRunner:
         from .. import ops
 
         self._err = ops._k().C.error_flag(self.d_i32)      # device error flag: raised (71) when a step samples an id outside the vocabulary
+        self.last_logits = None               # [B, V] logits of the last eager step (for top-k log-probs read by the host)
         self.graphs: dict[int, tuple] = {}
         self.launches_per_graph: dict[int, int] = {}
         self.pool = None
@@ -166,6 +167,8 @@ class DecodeRunner:
         hidden = e.model(tokens, meta)
         hidden = e.ps.sp_gather(hidden)
         logits = e.model.logits(hidden)
+        if not torch.cuda.is_current_stream_capturing():
+            self.last_logits = logits               # eager steps only (requests that want the k most likely tokens run eagerly)
         from .. import ops
 
         tok, lp = ops._k().sample_logprob(logits, self.d_f32[:B], self.d_u8[:B], self.d_i64[R:R + B], 0)
@@ -215,8 +218,9 @@ class DecodeRunner:
         key = (B, record)
         steps = max(1, min(int(steps), self.max_steps))
         self._chunks, self._on_host = [], 0
+        eager = any(getattr(r, "top_logprobs_num", 0) > 0 for r in reqs)      # their logits are read after the step
         for k in range(steps):
-            if self.use_graph:
+            if self.use_graph and not eager:
                 if key not in self.graphs:
                     self._capture(key)
                 self.graphs[key].replay()

@@ -60,6 +60,7 @@ class Request:
     input_logprobs: list[float] | None = None
     top_logprobs_num: int = 0      # > 0 with scoring: also the k most likely tokens (and their log-probs) at every scored position
     input_top_logprobs: list | None = None
+    output_top_logprobs: list = field(default_factory=list)     # per generated token: the k most likely (log-prob, id, None)
     leader: Any = None             # request of the same prefill batch with identical tokens whose prompt KV this one shares
     cache_nodes: list = field(default_factory=list)   # prefix-cache nodes this request pins (their blocks head its block table)
     prefill_pos: int = 0           # tokens whose KV is in place (cached prefix + chunks already run); < len(all_ids) while prefilling
@@ -101,6 +102,8 @@ class Request:
             meta["input_token_logprobs"] = [(lp, t, None) for lp, t in zip(lps, toks)]
             if self.input_top_logprobs is not None:
                 meta["input_top_logprobs"] = ([None] if start == 0 else []) + self.input_top_logprobs
+        if self.return_logprob and self.top_logprobs_num > 0:
+            meta["output_top_logprobs"] = self.output_top_logprobs[:len(self.output_ids)]
         if self.return_routed_experts and self.routed:
             arr = np.concatenate(self.routed, axis=0)
             n = len(self.input_ids) + len(self.output_ids) - 1
@@ -710,6 +713,8 @@ class Engine:
         if self.runner is None or self.stateless or self.decode_steps_per_sync <= 1 or not self.running:
             return 1
         k = self._steps_wanted()
+        if any(r.top_logprobs_num > 0 for r in self.running):
+            return 1                       # the k most likely tokens are read from the step's logits on the host side
         for r in self.running:
             k = min(k, r.sampling.max_new_tokens - len(r.output_ids), self.max_context_len - r.num_tokens)
         return max(1, k)
@@ -966,6 +971,8 @@ class Engine:
                                            min_bucket=self._agreed_bucket if self.lockstep_group is not None else 0, steps=steps)
         if steps == 1:
             self.stats["decode_tokens"] += len(reqs)
+            if any(r.top_logprobs_num > 0 for r in reqs):
+                self._collect_top_logprobs(reqs, self.runner.last_logits, [r.row for r in reqs])
             for r in reqs:
                 row = r.row
                 if routed is not None and r.return_routed_experts:
@@ -1008,6 +1015,17 @@ class Engine:
         elif len(r.output_ids) >= r.sampling.max_new_tokens:
             self._finish(r, {"type": "length", "length": len(r.output_ids)})
 
+    def _collect_top_logprobs(self, reqs: list[Request], logits: torch.Tensor, rows: list[int]):
+        """`top_logprobs_num` of a request: the k most likely next tokens under its sampling temperature, appended before the
+        sampled token is (the entry belongs to the token about to be appended)."""
+        for r, row in zip(reqs, rows):
+            if r.top_logprobs_num <= 0:
+                continue
+            t = r.sampling.temperature if r.sampling.temperature > 0 else 1.0
+            lg = torch.log_softmax(logits[row].float() / t, dim=-1)
+            v, i = lg.topk(min(r.top_logprobs_num, lg.shape[-1]))
+            r.output_top_logprobs.append([(float(x), int(y), None) for x, y in zip(v.tolist(), i.tolist())])
+
     def _sample_and_append(self, reqs: list[Request], logits: torch.Tensor):
         dev = self.device
         temp = torch.tensor([r.sampling.temperature for r in reqs], dtype=torch.float32, device=dev)
@@ -1017,6 +1035,7 @@ class Engine:
         seeds = torch.tensor([(r.seed * 1000003 + len(r.output_ids)) & 0x7FFFFFFFFFFFFFFF for r in reqs], dtype=torch.int64,
                              device=dev)
         tok, lp = sample(logits.float(), temp, top_p, top_k, seeds=seeds, step=0)
+        self._collect_top_logprobs(reqs, logits, list(range(len(reqs))))
         tok_l, lp_l = tok.tolist(), lp.tolist()
         self.stats["h2d_bytes"] = self.stats.get("h2d_bytes", 0) + 24 * len(reqs)
         self.stats["d2h_bytes"] = self.stats.get("d2h_bytes", 0) + 12 * len(reqs)

@@ -315,3 +315,30 @@ def test_prefix_cache_unpinned_count_stays_exact():
     n3 = c.insert(t1, [30, 31, 32])
     assert c.evictable() == walk(c) == 3
     assert c.evict(2) == 2 and c.evictable() == walk(c) == 1
+
+
+def test_output_top_logprobs_contain_the_sampled_token_and_are_sorted():
+    """`top_logprobs_num` on a generating request: one entry per generated token with the k most likely tokens under the
+    request's temperature; the greedy token is entry 0 and its log-prob equals the reported one."""
+    import torch
+
+    from miles_b200.engine.engine import Engine
+    from miles_b200.models.config import PRESETS
+
+    eng = Engine(PRESETS["tiny"], device="cpu", dtype=torch.float32, num_blocks=64)
+    ids = list(range(5, 25))
+    for temp in (0.0, 0.7):
+        r = eng.add_request(ids, {"temperature": temp, "max_new_tokens": 6, "seed": 3}, True, top_logprobs_num=4)
+        while not r.finished:
+            eng.step()
+        out = r.to_response(eng)
+        tops = out["meta_info"]["output_top_logprobs"]
+        assert len(tops) == 6 and all(len(t) == 4 for t in tops)
+        for (lp, tok, _), top in zip(out["meta_info"]["output_token_logprobs"], tops):
+            assert [x[0] for x in top] == sorted((x[0] for x in top), reverse=True)
+            if temp == 0.0:
+                assert top[0][1] == tok and abs(top[0][0] - lp) < 1e-4
+            hit = [x for x in top if x[1] == tok]
+            assert not hit or abs(hit[0][0] - lp) < 1e-4
+    plain = eng.generate(ids, {"temperature": 0.0, "max_new_tokens": 3})
+    assert "output_top_logprobs" not in plain["meta_info"]

@@ -217,3 +217,24 @@ def test_cuda_ipc_bucket_between_processes(tmp_path):
             proc.wait(timeout=20)
         except subprocess.TimeoutExpired:
             proc.kill()
+
+
+@pytest.mark.gpu
+def test_output_top_logprobs_on_the_cuda_runner(engine):
+    """Requests that ask for the k most likely tokens run their decode steps eagerly (the logits are read after the step);
+    other requests of the same batch are unaffected and the reported log-prob of the sampled token is among / consistent
+    with the top entries."""
+    cfg = engine.cfg
+    g = torch.Generator().manual_seed(11)
+    prompts = [torch.randint(3, cfg.vocab_size, (int(n),), generator=g).tolist() for n in (17, 40)]
+    a = engine.add_request(prompts[0], {"temperature": 0.0, "max_new_tokens": 5}, True, top_logprobs_num=3)
+    b = engine.add_request(prompts[1], {"temperature": 0.0, "max_new_tokens": 5}, True)
+    while not (a.finished and b.finished):
+        engine.step()
+    ra, rb = a.to_response(engine), b.to_response(engine)
+    tops = ra["meta_info"]["output_top_logprobs"]
+    assert len(tops) == 5 and "output_top_logprobs" not in rb["meta_info"]
+    for (lp, tok, _), top in zip(ra["meta_info"]["output_token_logprobs"], tops):
+        assert top[0][1] == tok and abs(top[0][0] - lp) < 2e-2 and top[0][0] >= top[1][0] >= top[2][0]
+    again = engine.generate(prompts[1], {"temperature": 0.0, "max_new_tokens": 5})
+    assert again["output_ids"] == rb["output_ids"]
