@@ -68,8 +68,8 @@ __global__ void __launch_bounds__(256) mxfp8_quant_kernel(const bf16* __restrict
 __device__ __forceinline__ float e2m1_round(float v) {          // v already clamped to [−6, 6]; ties to even, as rint on the grid
   const float mag = fabsf(v);
   const float step = mag < 2.f ? 0.5f : (mag < 4.f ? 1.f : 2.f);
-  const float q = rintf(mag / step) * step;
-  return v > 0.f ? q : (v < 0.f ? -q : 0.f);
+  const float q = rintf(mag * (mag < 2.f ? 2.f : (mag < 4.f ? 1.f : 0.5f))) * step;    // steps are powers of two: exact
+  return copysignf(q, v);
 }
 __device__ __forceinline__ float e4m3_round(float v) {
   const __nv_fp8_storage_t b = __nv_cvt_float_to_fp8(v, __NV_SATFINITE, __NV_E4M3);
@@ -87,7 +87,7 @@ __global__ void __launch_bounds__(256) block_fake_quant_kernel(const bf16* __res
   amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 1));
   if (MODE != 2) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 2));
   constexpr float FMAX = MODE == 0 ? 448.f : 6.f;
-  float scale;
+  float scale, inv_scale = 0.f;
   if (MODE == 2) {
     scale = e4m3_round(fminf(fmaxf(amax * (1.f / 6.f), 0.001953125f), 448.f));
   } else {
@@ -95,12 +95,15 @@ __global__ void __launch_bounds__(256) block_fake_quant_kernel(const bf16* __res
     const uint32_t bits = __float_as_uint(fmaxf(amax, floor_) * (1.f / FMAX));
     int e = static_cast<int>((bits >> 23) & 0xff) - 127 + ((bits & 0x7fffff) ? 1 : 0);     // ceil to a power of two
     scale = __uint_as_float(static_cast<uint32_t>(e + 127) << 23);
+    inv_scale = __uint_as_float(static_cast<uint32_t>(127 - e) << 23);       // the reciprocal of a power of two is exact
   }
   if (!live) return;
   __nv_bfloat162 out[4];
 #pragma unroll
   for (int k = 0; k < 8; k += 2) {
-    float a = fminf(fmaxf(__fdiv_rn(v[k], scale), -FMAX), FMAX), b = fminf(fmaxf(__fdiv_rn(v[k + 1], scale), -FMAX), FMAX);
+    float a = MODE == 2 ? __fdiv_rn(v[k], scale) : v[k] * inv_scale, b = MODE == 2 ? __fdiv_rn(v[k + 1], scale) : v[k + 1] * inv_scale;
+    a = fminf(fmaxf(a, -FMAX), FMAX);
+    b = fminf(fmaxf(b, -FMAX), FMAX);
     a = (MODE == 0 ? e4m3_round(a) : e2m1_round(a)) * scale;
     b = (MODE == 0 ? e4m3_round(b) : e2m1_round(b)) * scale;
     out[k / 2] = __floats2bfloat162_rn(a, b);
