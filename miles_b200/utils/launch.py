@@ -56,6 +56,9 @@ class ExecuteTrainConfig:
     env: dict = field(default_factory=dict)
     log_file: str | None = None
     dry_run: bool = False
+    launcher: str = "torchrun"              # torchrun | workers (ranks as supervised processes of the worker manager)
+    num_cells: int = 1                      # workers launcher: independent trainer cells (`--indep-dp`), each its own world
+    log_dir: str | None = None              # workers launcher: one log per rank and generation
 
 
 def build_command(train_args: list[str] | str, cfg: ExecuteTrainConfig) -> list[str]:
@@ -67,8 +70,51 @@ def build_command(train_args: list[str] | str, cfg: ExecuteTrainConfig) -> list[
             "--master-addr", "127.0.0.1", "--master-port", str(cfg.master_port), entry, *args]
 
 
+def trainer_spec(train_args: list[str] | str, cfg: ExecuteTrainConfig, name: str = "trainer"):
+    """The trainer as a pool of the worker layer: `num_cells` cells of `num_gpus` ranks, one process per rank, with the
+    rendezvous variables of its cell (RANK / WORLD_SIZE / LOCAL_RANK / MASTER_ADDR / MASTER_PORT) planned like any other
+    pool's.  Every GPU stays visible to every rank (the fused kernels map peers' memory); `{cell}` in the arguments is
+    the cell index (e.g. `--indep-dp-cell-id {cell}`).  The reference describes its trainer actors the same way
+    (miles/ray/trainer/trainer_spec.py: pools, per-pool environment)."""
+    from ..orchestration.worker_spec import CommandWorkerSpec, SchedulingSpec
+
+    args = shlex.split(train_args) if isinstance(train_args, str) else list(train_args)
+    return CommandWorkerSpec(name, [sys.executable, os.path.join(REPO_ROOT, cfg.entry), *args],
+                             SchedulingSpec(num_cells=cfg.num_cells, workers_per_cell=max(1, cfg.num_gpus), gpus_per_worker=1),
+                             env={"CUDA_VISIBLE_DEVICES": "__inherit__", **{k: str(v) for k, v in cfg.env.items()}}, ports=[])
+
+
+def run_trainer_pool(train_args: list[str] | str, cfg: ExecuteTrainConfig, poll_s: float = 0.2) -> int:
+    """Start the trainer pool under the worker manager and wait: 0 when every rank exited 0; the first non-zero exit code
+    otherwise, after the remaining ranks were stopped (a rank that died cannot be waited for by its peers' collectives)."""
+    import time
+
+    from ..orchestration.workers.manager import WorkerManager
+
+    mgr = WorkerManager(log_dir=cfg.log_dir)
+    mgr.launch([trainer_spec(train_args, cfg)], nodes={"local": cfg.num_cells * max(1, cfg.num_gpus)})
+    try:
+        while True:
+            codes = [wk.proc.poll() for c in mgr.cells.values() for wk in c.workers]
+            bad = [c for c in codes if c not in (None, 0)]
+            if bad:
+                return int(bad[0])
+            if all(c == 0 for c in codes):
+                return 0
+            time.sleep(poll_s)
+    finally:
+        mgr.stop_all()
+
+
 def execute_train(train_args: list[str] | str, cfg: ExecuteTrainConfig | None = None) -> int | list[str]:
     cfg = cfg or ExecuteTrainConfig()
+    if cfg.launcher == "workers":
+        if cfg.dry_run:
+            from ..orchestration.workers.manager import WorkerManager
+
+            return WorkerManager().launch([trainer_spec(train_args, cfg)], nodes={"local": cfg.num_cells * max(1, cfg.num_gpus)},
+                                          dry_run=True)
+        return run_trainer_pool(train_args, cfg)
     cmd = build_command(train_args, cfg)
     if cfg.dry_run:
         return cmd

@@ -28,6 +28,9 @@ def main(argv=None) -> int:
     p.add_argument("--wandb-project", default=None)
     p.add_argument("--master-port", type=int, default=29511)
     p.add_argument("--log-file", default=None)
+    p.add_argument("--launcher", choices=["torchrun", "workers"], default="torchrun",
+                   help="workers: the ranks run as a pool of the worker manager (one supervised process per rank, per-rank logs)")
+    p.add_argument("--worker-log-dir", default=None)
     p.add_argument("--dry-run", action="store_true", help="print the command instead of running it")
     a = p.parse_args(argv)
     if a.recipe == "list":
@@ -38,7 +41,8 @@ def main(argv=None) -> int:
                           mxfp8=a.mxfp8, true_on_policy=a.true_on_policy, dynamic_sampling=a.dynamic_sampling, use_kl_loss=a.use_kl_loss,
                           wandb_project=a.wandb_project, extra=extra)
     r = recipes.build(a.recipe, knobs)
-    cfg = ExecuteTrainConfig(num_gpus=r.num_gpus, entry=r.entry, master_port=a.master_port, env=r.env, log_file=a.log_file, dry_run=a.dry_run)
+    cfg = ExecuteTrainConfig(num_gpus=r.num_gpus, entry=r.entry, master_port=a.master_port, env=r.env, log_file=a.log_file, dry_run=a.dry_run,
+                             launcher=a.launcher, log_dir=a.worker_log_dir)
     if a.dry_run:
         print(shlex.join(build_command(r.args, cfg)))
         return 0

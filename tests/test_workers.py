@@ -263,3 +263,24 @@ def test_registration_hub_over_http():
     finally:
         server.should_exit = True
         thread.join(5)
+
+
+def test_trainer_pool_runs_grpo_ranks_under_the_worker_manager(tmp_path):
+    """The trainer as a pool of supervised processes (no torchrun): two gloo ranks get their rendezvous variables from the
+    planner, train two rollouts and exit 0; a rank that fails ends the pool with its exit code."""
+    from miles_b200.utils.launch import ExecuteTrainConfig, execute_train
+
+    args = ("--model-name tiny --fp32 --rollout-batch-size 8 --n-samples-per-prompt 4 --rollout-max-response-len 8 --num-rollout 2 "
+            "--rm-type even_fraction --lr 1e-4 --colocate --advantage-estimator grpo "
+            "--data-source-path miles_b200.rollout.data_source.SyntheticSource --synthetic-prompt-len 6 10")
+    cfg = ExecuteTrainConfig(num_gpus=2, launcher="workers", log_dir=str(tmp_path / "logs"), env={"CUDA_VISIBLE_DEVICES": ""})
+    plan = execute_train(args, ExecuteTrainConfig(num_gpus=2, launcher="workers", dry_run=True))
+    assert [p["env"]["RANK"] for p in plan] == ["0", "1"] and all(p["env"]["WORLD_SIZE"] == "2" for p in plan)
+    assert plan[0]["env"]["MASTER_PORT"] == plan[1]["env"]["MASTER_PORT"] and plan[0]["cmd"][1].endswith("train.py")
+    assert execute_train(args, cfg) == 0
+    logs = sorted(os.listdir(tmp_path / "logs"))
+    assert logs == ["trainer-0-0.g0.log", "trainer-0-1.g0.log"] or len(logs) == 2, logs
+    text = open(tmp_path / "logs" / logs[0]).read()
+    assert "rollout/step=1" in text
+    bad = ExecuteTrainConfig(num_gpus=2, launcher="workers", log_dir=str(tmp_path / "bad"), env={"CUDA_VISIBLE_DEVICES": ""})
+    assert execute_train(args + " --no-such-flag", bad) != 0
