@@ -61,6 +61,7 @@ class Request:
     top_logprobs_num: int = 0      # > 0 with scoring: also the k most likely tokens (and their log-probs) at every scored position
     input_top_logprobs: list | None = None
     output_top_logprobs: list = field(default_factory=list)     # per generated token: the k most likely (log-prob, id, None)
+    keep_kv: bool = False          # prefill / decode disaggregation: the cache blocks outlive the request until `release_kv`
     leader: Any = None             # request of the same prefill batch with identical tokens whose prompt KV this one shares
     cache_nodes: list = field(default_factory=list)   # prefix-cache nodes this request pins (their blocks head its block table)
     prefill_pos: int = 0           # tokens whose KV is in place (cached prefix + chunks already run); < len(all_ids) while prefilling
@@ -192,6 +193,7 @@ class Engine:
             REGISTRY.bind(self, "lockstep_group")
         self.local_done = True
         self.global_done = True
+        self.held_kv: dict[str, tuple[list[int], int]] = {}     # finished `keep_kv` requests: (blocks, tokens with KV)
         self.runner = None
         self._agreed_bucket = 0
         # models whose mixers keep no paged KV (latent / linear attention of the other families) are served by scoring the
@@ -208,14 +210,15 @@ class Engine:
     # ---------------------------------------------------------------------------------------
     def add_request(self, input_ids: list[int], sampling_params: dict | SamplingParams | None = None,
                     return_logprob: bool = True, return_routed_experts: bool = False, rid: str | None = None,
-                    on_done=None, logprob_start_len: int = -1, top_logprobs_num: int = 0) -> Request:
+                    on_done=None, logprob_start_len: int = -1, top_logprobs_num: int = 0, keep_kv: bool = False) -> Request:
         sp = sampling_params if isinstance(sampling_params, SamplingParams) else SamplingParams.from_dict(sampling_params)
         with self.lock:
             rid = rid or f"req-{next(self._rid)}"
             req = Request(rid=rid, input_ids=list(input_ids), sampling=sp, return_logprob=return_logprob,
                           return_routed_experts=return_routed_experts and self.cfg.is_moe,
                           seed=(sp.seed if sp.seed is not None else (self.seed * 1000003 + zlib.crc32(rid.encode())) % (2 ** 31)),
-                          on_done=on_done, logprob_start_len=int(logprob_start_len), top_logprobs_num=int(top_logprobs_num or 0))
+                          on_done=on_done, logprob_start_len=int(logprob_start_len), top_logprobs_num=int(top_logprobs_num or 0),
+                          keep_kv=bool(keep_kv))
             budget = self.max_context_len - len(input_ids)
             if budget <= 0 or sp.max_new_tokens <= 0:
                 req.finish_reason = {"type": "length", "length": 0}
@@ -227,6 +230,68 @@ class Engine:
             req.stop_set = frozenset(sp.stop_token_ids) | (frozenset() if sp.ignore_eos else frozenset(self.eos_token_ids))
             self.requests[rid] = req
             self.waiting.append(req)
+        return req
+
+    # ---- prefill / decode disaggregation: a request's KV leaves this engine or arrives from another -------------------------
+    def export_kv(self, rid: str) -> torch.Tensor:
+        """KV of a finished `keep_kv` request as one tensor [layers, 2, tokens, kv heads, head dim] (a gather over its slots)."""
+        with self.lock:
+            blocks, n = self.held_kv[rid]
+            bs = self.block_size
+            slots = torch.tensor([blocks[p // bs] * bs + p % bs for p in range(n)], dtype=torch.int64, device=self.device)
+            layers = sorted(self.kv.layers)
+            out = [torch.stack([self.kv.layers[l][0].flatten(0, 1).index_select(0, slots),
+                                self.kv.layers[l][1].flatten(0, 1).index_select(0, slots)]) for l in layers]
+            return torch.stack(out)
+
+    def release_kv(self, rid: str):
+        with self.lock:
+            blocks, _ = self.held_kv.pop(rid, ([], 0))
+            if blocks:
+                self.allocator.release(blocks)
+
+    def add_prefilled(self, input_ids: list[int], first_token: int, first_logprob: float, kv: torch.Tensor,
+                      sampling_params: dict | SamplingParams | None = None, return_logprob: bool = True,
+                      return_routed_experts: bool = False, routed: "np.ndarray | None" = None, rid: str | None = None,
+                      on_done=None, seed: int | None = None) -> Request:
+        """Continue a request whose prompt ran elsewhere: `kv` [layers, 2, len(input_ids), kv heads, head dim] is stored into
+        freshly allocated blocks, `first_token` (sampled by the prefill engine) is its first output, decoding goes on here.
+        Raises when the cache cannot take the prompt now (the caller retries or routes elsewhere)."""
+        sp = sampling_params if isinstance(sampling_params, SamplingParams) else SamplingParams.from_dict(sampling_params)
+        assert not self.stateless, "engines that re-score the whole sequence keep no KV to receive"
+        with self.lock:
+            n = len(input_ids)
+            assert kv.shape[2] == n and kv.shape[0] == len(self.kv.layers), (tuple(kv.shape), n, len(self.kv.layers))
+            rid = rid or f"req-{next(self._rid)}"
+            req = Request(rid=rid, input_ids=list(input_ids), sampling=sp, return_logprob=return_logprob,
+                          return_routed_experts=return_routed_experts and self.cfg.is_moe,
+                          seed=(seed if seed is not None else (sp.seed if sp.seed is not None else
+                                                               (self.seed * 1000003 + zlib.crc32(rid.encode())) % (2 ** 31))),
+                          on_done=on_done)
+            sp.max_new_tokens = min(sp.max_new_tokens, self.max_context_len - n)
+            req.stop_set = frozenset(sp.stop_token_ids) | (frozenset() if sp.ignore_eos else frozenset(self.eos_token_ids))
+            blocks = self._alloc_blocks(self._blocks_needed(n + 1))
+            if blocks is None:
+                raise RuntimeError(f"no room for {n} prefilled tokens ({self._free_blocks()} blocks free)")
+            req.blocks = blocks
+            bs = self.block_size
+            slots = torch.tensor([blocks[p // bs] * bs + p % bs for p in range(n)], dtype=torch.int64, device=self.device)
+            kv = kv.to(self.device)
+            for i, l in enumerate(sorted(self.kv.layers)):
+                kc, vc = self.kv.layers[l]
+                kc.flatten(0, 1).index_copy_(0, slots, kv[i, 0].to(kc.dtype))
+                vc.flatten(0, 1).index_copy_(0, slots, kv[i, 1].to(vc.dtype))
+            req.num_cached = req.prefill_pos = n
+            req.cached_tokens = n
+            if routed is not None and req.return_routed_experts:
+                req.routed.append(np.ascontiguousarray(routed[:n], dtype=np.int32))
+            self.requests[rid] = req
+            self.stats["received_kv_tokens"] = self.stats.get("received_kv_tokens", 0) + n
+            self._append_token(req, int(first_token), float(first_logprob))
+            if not req.finished:
+                self.running.append(req)
+                if self.runner is not None:
+                    self.runner.attach(req)
         return req
 
     def abort_request(self, rid: str | None = None):
@@ -292,6 +357,7 @@ class Engine:
                 return False
             if self.prefix_cache is not None:
                 self.prefix_cache.reset()
+            self.held_kv.clear()
             self.allocator.reset()
             return True
 
@@ -395,6 +461,7 @@ class Engine:
                 if self.prefix_cache is not None:
                     self.prefix_cache.reset()              # the cached KV goes with the cache's memory
                 self.kv.free()
+                self.held_kv.clear()
                 self.allocator.reset()
             if "cuda_graph" in tags:
                 self._graphs.clear()
@@ -468,7 +535,10 @@ class Engine:
             if self.prefix_cache is not None and r.cache_nodes:
                 self.prefix_cache.unpin(r.cache_nodes)
                 r.cache_nodes = []
-            self.allocator.release(r.blocks)
+            if r.keep_kv and reason.get("type") != "abort":
+                self.held_kv[r.rid] = (r.blocks, len(r.all_ids) - 1)       # every position but the last sampled token has KV
+            else:
+                self.allocator.release(r.blocks)
             r.blocks = []
         self.requests.pop(r.rid, None)
         r.done.set()

@@ -61,6 +61,58 @@ def build_app(engine, tokenizer=None):
         outs = [await _wait(r) for r in reqs]
         return JSONResponse(outs if batched else outs[0])
 
+    # ---- prefill / decode disaggregation (engine/pd.py): this server as the prefill side or as the decode side ---------
+    kv_exports: dict[str, Any] = {}
+
+    @app.post("/prefill")
+    async def prefill(request: Request):
+        """Run the prompt, sample the first token, keep the KV: the reply carries the usual fields plus `kv` (a CUDA-IPC handle
+        of the gathered tensor, or its bytes from a CPU engine) for the decode server; `/release_kv` ends the loan."""
+        from ..weight_update import cuda_ipc
+
+        body = await request.json()
+        sp = dict(body.get("sampling_params") or {})
+        req = engine.add_request(body["input_ids"], {**sp, "max_new_tokens": 1}, body.get("return_logprob", True),
+                                 body.get("return_routed_experts", False), rid=body.get("rid"),
+                                 logprob_start_len=body.get("logprob_start_len", -1), top_logprobs_num=body.get("top_logprobs_num", 0),
+                                 keep_kv=True)
+        out = await _wait(req)
+        if req.rid in engine.held_kv:
+            kv = engine.export_kv(req.rid)
+            flat, manifest = cuda_ipc.pack_bucket([("kv", kv)])
+            kv_exports[req.rid] = flat                       # alive until /release_kv: the peer maps this buffer
+            out["kv"] = cuda_ipc.export_bucket(flat, manifest) if flat.is_cuda else cuda_ipc.serialize_bucket(flat, manifest)
+            out["seed"] = req.seed
+        return JSONResponse(out)
+
+    @app.post("/release_kv")
+    async def release_kv(request: Request):
+        body = await request.json()
+        kv_exports.pop(body["rid"], None)
+        engine.release_kv(body["rid"])
+        return {"success": True}
+
+    @app.post("/generate_prefilled")
+    async def generate_prefilled(request: Request):
+        from ..weight_update import cuda_ipc
+
+        body = await request.json()
+        flat, manifest = cuda_ipc.open_bucket(body["kv"], engine.device)
+        kv = cuda_ipc.split_bucket(flat, manifest)[0][1]
+        routed = body.get("routed_experts")
+        if routed is not None:
+            from ..types import decode_routed_experts
+
+            n = len(body["input_ids"])
+            routed = decode_routed_experts(routed, n + 1, engine.model.num_moe_layers, engine.cfg.moe_topk)
+        req = engine.add_prefilled(body["input_ids"], body["first_token"], body["first_logprob"], kv, body.get("sampling_params"),
+                                   body.get("return_logprob", True), body.get("return_routed_experts", False), routed=routed,
+                                   rid=body.get("rid"), seed=body.get("seed"))
+        if flat.is_cuda:
+            torch.cuda.current_stream(flat.device).synchronize()       # the copy out of the peer's buffer is complete: it may be released
+        del kv, flat
+        return JSONResponse(await _wait(req))
+
     @app.get("/health")
     async def health():
         return engine.health()

@@ -342,3 +342,85 @@ def test_output_top_logprobs_contain_the_sampled_token_and_are_sorted():
             assert not hit or abs(hit[0][0] - lp) < 1e-4
     plain = eng.generate(ids, {"temperature": 0.0, "max_new_tokens": 3})
     assert "output_top_logprobs" not in plain["meta_info"]
+
+
+@pytest.mark.parametrize("model", ["tiny", "tiny-moe"])
+def test_prefill_decode_disaggregation_matches_one_engine(model):
+    """Prompts run on a prefill engine, the KV moves as one tensor, decoding continues on another engine: tokens, log-probs,
+    routed experts and finish reasons equal those of a single engine; both engines end with every block free."""
+    import asyncio
+
+    import torch
+
+    from miles_b200.engine.engine import Engine
+    from miles_b200.engine.pd import PDClient
+    from miles_b200.models.config import PRESETS
+
+    cfg = PRESETS[model]
+    mk = lambda: Engine(cfg, device="cpu", dtype=torch.float32, num_blocks=96, seed=5)
+    ref, P, D = mk(), mk(), mk()
+    g = torch.Generator().manual_seed(2)
+    prompts = [torch.randint(3, cfg.vocab_size, (int(n),), generator=g).tolist() for n in (5, 16, 33, 47)]
+    sps = [{"temperature": 0.0, "max_new_tokens": m, "stop_token_ids": list(range(0, cfg.vocab_size, 5)) if i == 2 else []}
+           for i, m in enumerate((6, 1, 12, 9))]
+    want = ref.generate(prompts, [dict(sp) for sp in sps], return_routed_experts=True)
+    client = PDClient([P], [D])
+
+    async def run():
+        outs = await asyncio.gather(*[client.generate({"input_ids": p, "sampling_params": dict(sp), "return_logprob": True,
+                                                       "return_routed_experts": True}) for p, sp in zip(prompts, sps)])
+        await client.finish()
+        return outs
+
+    got = asyncio.run(run())
+    from miles_b200.types import decode_routed_experts
+    for w, o, p in zip(want, got, prompts):
+        assert o["output_ids"] == w["output_ids"] and o["meta_info"]["finish_reason"]["type"] == w["meta_info"]["finish_reason"]["type"]
+        a = [x[0] for x in o["meta_info"]["output_token_logprobs"]]
+        b = [x[0] for x in w["meta_info"]["output_token_logprobs"]]
+        assert max(abs(x - y) for x, y in zip(a, b)) < 1e-5
+        if cfg.is_moe:
+            n = len(p) + len(w["output_ids"])
+            r1 = decode_routed_experts(w["meta_info"]["routed_experts"], n, ref.model.num_moe_layers, cfg.moe_topk)
+            r2 = decode_routed_experts(o["meta_info"]["routed_experts"], n, ref.model.num_moe_layers, cfg.moe_topk)
+            assert (r1 == r2).all()
+    assert client.stats["requests"] >= 2 and D.stats["received_kv_tokens"] == client.stats["handed_over_tokens"]
+    assert D.stats["prefill_tokens"] == 0                                 # the decode engine never ran a prompt
+    for e in (P, D):
+        assert not e.held_kv and not e.running and e._free_blocks() == e.allocator.num_blocks
+
+
+def test_prefill_decode_disaggregation_over_http():
+    """Two engine servers, one in each role: `/prefill` → `/generate_prefilled` → `/release_kv` give the single-engine answer
+    (the KV travels as bytes between CPU engines, as a CUDA-IPC handle between GPU ones)."""
+    import asyncio
+
+    from miles_b200.engine.pd import PDHttpClient
+    from miles_b200.engine.server import serve
+
+    ref, P, D = _engine("tiny-moe"), _engine("tiny-moe"), _engine("tiny-moe")
+    ps, _ = serve(P, port=31741, in_thread=True)
+    ds, _ = serve(D, port=31742, in_thread=True)
+    try:
+        prompt = list(range(7, 40))
+        sp = {"temperature": 0.0, "max_new_tokens": 7}
+        want = ref.generate(prompt, dict(sp), return_routed_experts=True)
+        client = PDHttpClient(["http://127.0.0.1:31741"], ["http://127.0.0.1:31742"])
+
+        async def run():
+            out = await client.generate({"input_ids": prompt, "sampling_params": dict(sp), "return_logprob": True,
+                                         "return_routed_experts": True})
+            await client.finish()
+            return out
+
+        got = asyncio.run(run())
+        assert got["output_ids"] == want["output_ids"]
+        assert got["meta_info"]["routed_experts"] == want["meta_info"]["routed_experts"]
+        a, b = ([x[0] for x in o["meta_info"]["output_token_logprobs"]] for o in (got, want))
+        assert max(abs(x - y) for x, y in zip(a, b)) < 1e-5
+        assert not P.held_kv and D.stats["received_kv_tokens"] == len(prompt) and D.stats["prefill_tokens"] == 0
+    finally:
+        ps.should_exit = True
+        ds.should_exit = True
+        P._stop_loop = D._stop_loop = True
+        time.sleep(0.1)

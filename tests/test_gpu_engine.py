@@ -237,3 +237,38 @@ def test_output_top_logprobs_on_the_cuda_runner(engine):
     for (lp, tok, _), top in zip(ra["meta_info"]["output_token_logprobs"], tops):
         assert top[0][1] == tok and abs(top[0][0] - lp) < 2e-2 and top[0][0] >= top[1][0] >= top[2][0]
     assert len(rb["output_ids"]) == 5
+
+
+@pytest.mark.gpu
+def test_prefill_decode_disaggregation_on_cuda(engine):
+    """The prompt's KV leaves one engine as a tensor and is stored into another engine's cache (on the last GPU of the box when
+    there are several: one device-to-device copy); decoding there gives the first engine's tokens up to a near-tie flip and
+    its log-probs on the common prefix."""
+    import asyncio
+
+    from miles_b200.engine.engine import Engine
+    from miles_b200.engine.pd import PDClient
+
+    cfg = engine.cfg
+    dev = torch.device("cuda", torch.cuda.device_count() - 1)
+    other = Engine(cfg, device=dev, dtype=torch.bfloat16, max_running_requests=16, max_context_len=512, num_blocks=128, seed=0)
+    g = torch.Generator().manual_seed(21)
+    prompts = [torch.randint(3, cfg.vocab_size, (int(n),), generator=g).tolist() for n in (40, 130, 65)]
+    sp = {"temperature": 0.0, "max_new_tokens": 12}
+    want = engine.generate(prompts, [dict(sp)] * 3, return_routed_experts=True)
+    client = PDClient([engine], [other])
+
+    async def run():
+        outs = await asyncio.gather(*[client.generate({"input_ids": p, "sampling_params": dict(sp), "return_logprob": True,
+                                                       "return_routed_experts": True}) for p in prompts])
+        await client.finish()
+        return outs
+
+    got = asyncio.run(run())
+    for w, o in zip(want, got):
+        n = next((i for i, (x, y) in enumerate(zip(w["output_ids"], o["output_ids"])) if x != y), len(w["output_ids"]))
+        assert n >= 1 and len(o["output_ids"]) == 12
+        a, b = ([x[0] for x in r["meta_info"]["output_token_logprobs"]][:n] for r in (w, o))
+        assert max(abs(x - y) for x, y in zip(a, b)) < 5e-2
+    assert other.stats["received_kv_tokens"] == sum(map(len, prompts)) and other.stats["prefill_tokens"] == 0
+    assert not engine.held_kv and other._free_blocks() == other.allocator.num_blocks
