@@ -226,6 +226,9 @@ def build_parser() -> argparse.ArgumentParser:
     _bool_flag(g, "--use-dynamic-batch-size")
     g.add_argument("--max-tokens-per-gpu", type=int, default=None)
     _bool_flag(g, "--balance-data")
+    g.add_argument("--rollout-pd-prefill-engines", type=int, default=0,
+                   help="prefill / decode disaggregation over an HTTP engine fleet: this many of --rollout-num-engines run prompts "
+                        "only and hand the KV to the others, which decode")
     g.add_argument("--rollout-data-exchange", choices=["gather", "local", "balanced"], default="gather",
                    help="gather: every rank receives all samples of the step and takes its (balanced) share; local: with one "
                         "engine per data-parallel rank each rank trains on the samples it generated (whole prompt groups "

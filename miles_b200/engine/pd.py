@@ -105,8 +105,21 @@ class PDHttpClient:
             r.raise_for_status()
             return await r.json()
 
+    async def start(self):
+        pass
+
     async def begin(self):
         pass
+
+    async def abort_all(self):
+        import asyncio
+
+        await asyncio.gather(*[self._post(f"{u}/abort_request", {"abort_all": True}) for u in self.prefill_urls + self.decode_urls])
+
+    async def call_all(self, endpoint: str, body: dict | None = None) -> list:
+        import asyncio
+
+        return await asyncio.gather(*[self._post(f"{u}/{endpoint.lstrip('/')}", body) for u in self.prefill_urls + self.decode_urls])
 
     async def finish(self):
         if self._session is not None:

@@ -176,8 +176,16 @@ def create_rollout_components(args, ps: ParallelState, actor=None, tracker=None)
                 box = [router_url, worker_urls]
                 torch.distributed.broadcast_object_list(box, src=0)
                 router_url, worker_urls = box
-        client = HttpEngineClient(router_url, tokenizer=tok, worker_urls=worker_urls,
-                                  num_moe_layers=sum(cfg.layer_is_moe(l) for l in range(cfg.num_layers)), moe_topk=cfg.moe_topk)
+        n_moe = sum(cfg.layer_is_moe(l) for l in range(cfg.num_layers))
+        n_prefill = int(getattr(args, "rollout_pd_prefill_engines", 0) or 0)
+        if n_prefill > 0:
+            # prefill / decode disaggregation: the first engines of the fleet run prompts, the others continue from their KV
+            from ..engine.pd import PDHttpClient
+
+            assert worker_urls and 0 < n_prefill < len(worker_urls), "--rollout-pd-prefill-engines needs a fleet with more engines than that"
+            client = PDHttpClient(worker_urls[:n_prefill], worker_urls[n_prefill:], tokenizer=tok, num_moe_layers=n_moe, moe_topk=cfg.moe_topk)
+        else:
+            client = HttpEngineClient(router_url, tokenizer=tok, worker_urls=worker_urls, num_moe_layers=n_moe, moe_topk=cfg.moe_topk)
     else:
         ek = dict(getattr(args, "engine_kwargs", {}) or {})
         device = actor.device if actor is not None else ("cuda" if torch.cuda.is_available() else "cpu")

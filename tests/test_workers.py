@@ -284,3 +284,31 @@ def test_trainer_pool_runs_grpo_ranks_under_the_worker_manager(tmp_path):
     assert "rollout/step=1" in text
     bad = ExecuteTrainConfig(num_gpus=2, launcher="workers", log_dir=str(tmp_path / "bad"), env={"CUDA_VISIBLE_DEVICES": ""})
     assert execute_train(args + " --no-such-flag", bad) != 0
+
+
+def test_engine_fleet_in_prefill_decode_roles(tmp_path):
+    """`--rollout-pd-prefill-engines 1` over a fleet of two engine servers: rollouts go prompt → engine 0 → KV → engine 1, the
+    trainer's recomputed log-probs equal the fleet's (the hand-over loses nothing), and the decode engine ran no prompt."""
+    sys.path.insert(0, ROOT)
+    from miles_b200.args import parse_args
+    from miles_b200.orchestration.wiring import (create_parallel_state, create_rollout_components, create_training_models,
+                                                 update_weights)
+    from miles_b200.utils import object_store
+
+    args = parse_args(("--model-name tiny --fp32 --rollout-batch-size 4 --n-samples-per-prompt 2 --rollout-max-response-len 6 "
+                       "--num-rollout 1 --rm-type even_fraction --lr 1e-4 --advantage-estimator grpo "
+                       "--data-source-path miles_b200.rollout.data_source.SyntheticSource --synthetic-prompt-len 20 30 "
+                       "--rollout-engine http --worker-provider local --rollout-num-engines 2 --rollout-pd-prefill-engines 1 "
+                       f"--update-weight-transfer-mode disk --update-weight-disk-dir {tmp_path}/sync --worker-log-dir {tmp_path}/logs").split())
+    ps = create_parallel_state(args)
+    actor, _, _ = create_training_models(args, ps)
+    rollout = create_rollout_components(args, ps, actor)
+    try:
+        update_weights(args, actor, rollout)
+        pack = rollout.executor.get(0)
+        shard = object_store.get(pack.data_ref)
+        assert len(shard["tokens"]) == 8 and all(r == 6 for r in shard["response_lengths"])
+        m = actor.train(0, shard)
+        assert m["train/train_rollout_logprob_abs_diff"] < 1e-4, m["train/train_rollout_logprob_abs_diff"]
+    finally:
+        rollout.fleet.shutdown()
