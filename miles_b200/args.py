@@ -435,6 +435,10 @@ def parse_args(argv: list[str] | None = None, validate: bool = True) -> argparse
     argv, engine_kwargs = _split_engine_args(argv)
     parser = build_parser()
     args = parser.parse_args(argv)
+    # `--engine-config` / `--sglang-config FILE`: the YAML serving config ({models: [{name, model_path, server_groups:
+    # [{worker_type: regular|prefill|decode, num_gpus, num_gpus_per_engine, overrides}]}]}); the policy model's groups size
+    # the HTTP engine fleet, prefill + decode groups run it in prefill / decode roles (`orchestration/wiring.apply_serving_config`)
+    args.engine_config = engine_kwargs.pop("config", None)
     args.engine_kwargs = engine_kwargs
     if args.custom_config_path:
         with open(args.custom_config_path) as f:

@@ -46,6 +46,30 @@ def create_parallel_state(args) -> ParallelState:
     return ps
 
 
+def apply_serving_config(args) -> None:
+    """`--engine-config`: the server groups of the policy model (the first model that is not eval-only) decide how many
+    engine servers the fleet starts and in which roles — `regular` engines behind the router, or `prefill` + `decode` engines
+    with the KV hand-over between them.  (One GPU per engine server: groups asking for more are refused.)"""
+    from .inference_controller import load_serving_config
+
+    models = load_serving_config(args.engine_config)
+    policy = next((m for m in models if not m.eval_only), None)
+    assert policy is not None, "--engine-config names no model that serves the policy"
+    count = {"regular": 0, "prefill": 0, "decode": 0}
+    for grp in policy.groups:
+        assert grp.num_gpus_per_engine == 1, f"{policy.name}: engine servers span one GPU here (num_gpus_per_engine {grp.num_gpus_per_engine})"
+        if grp.worker_type in count:
+            count[grp.worker_type] += grp.num_gpus // grp.num_gpus_per_engine
+    if count["prefill"]:
+        assert not count["regular"], f"{policy.name}: regular groups next to prefill / decode groups are not supported"
+        args.rollout_num_engines = count["prefill"] + count["decode"]
+        args.rollout_pd_prefill_engines = count["prefill"]
+    elif count["regular"]:
+        args.rollout_num_engines = count["regular"]
+    if policy.model_path and not getattr(args, "hf_checkpoint", None):
+        args.hf_checkpoint = policy.model_path
+
+
 def load_tokenizer(args):
     path = getattr(args, "tokenizer_path", None) or getattr(args, "hf_checkpoint", None)
     if not path or not os.path.isdir(path):
@@ -163,6 +187,8 @@ def create_rollout_components(args, ps: ParallelState, actor=None, tracker=None)
     if kind == "http":
         router_url = (getattr(args, "engine_kwargs", None) or {}).get("router_url")
         worker_urls = None
+        if getattr(args, "engine_config", None):
+            apply_serving_config(args)
         if getattr(args, "worker_provider", "none") != "none":
             # engine servers + router as supervised worker processes (or adopted from elsewhere): rank 0 owns the fleet,
             # the other ranks only learn the router's address

@@ -312,3 +312,23 @@ def test_engine_fleet_in_prefill_decode_roles(tmp_path):
         assert m["train/train_rollout_logprob_abs_diff"] < 1e-4, m["train/train_rollout_logprob_abs_diff"]
     finally:
         rollout.fleet.shutdown()
+
+
+def test_serving_config_sizes_the_fleet_and_assigns_roles(tmp_path):
+    from miles_b200.args import parse_args
+    from miles_b200.orchestration.wiring import apply_serving_config
+
+    cfg = tmp_path / "serve.yaml"
+    cfg.write_text("models:\n  - name: judge\n    eval_only: true\n    server_groups: [{worker_type: regular, num_gpus: 1}]\n"
+                   "  - name: policy\n    model_path: /models/policy\n    server_groups:\n"
+                   "      - {worker_type: prefill, num_gpus: 1}\n      - {worker_type: decode, num_gpus: 3}\n")
+    args = parse_args(f"--model-name tiny --rollout-engine http --worker-provider local --engine-config {cfg}".split())
+    apply_serving_config(args)
+    assert (args.rollout_num_engines, args.rollout_pd_prefill_engines, args.hf_checkpoint) == (4, 1, "/models/policy")
+    cfg.write_text("models:\n  - name: policy\n    server_groups: [{worker_type: regular, num_gpus: 2}]\n")
+    args = parse_args(f"--model-name tiny --rollout-engine http --worker-provider local --sglang-config {cfg}".split())
+    apply_serving_config(args)
+    assert (args.rollout_num_engines, args.rollout_pd_prefill_engines) == (2, 0)
+    cfg.write_text("models:\n  - name: policy\n    server_groups: [{worker_type: regular, num_gpus: 4, num_gpus_per_engine: 2}]\n")
+    with pytest.raises(AssertionError):
+        apply_serving_config(parse_args(f"--model-name tiny --engine-config {cfg}".split()))
