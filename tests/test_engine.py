@@ -424,3 +424,80 @@ def test_prefill_decode_disaggregation_over_http():
         ds.should_exit = True
         P._stop_loop = D._stop_loop = True
         time.sleep(0.1)
+
+
+def _multi_rank_body(rank, world, mode, port, out_dir):
+    import json
+    import threading
+
+    import torch
+
+    from miles_b200.engine import multi_rank_server as mrs
+    from miles_b200.engine.engine import Engine
+    from miles_b200.models.config import PRESETS
+    from miles_b200.parallel.state import ParallelState, init_distributed
+
+    init_distributed(backend="gloo")
+    cfg = PRESETS["tiny-moe" if mode == "ep" else "tiny"]
+    ps = ParallelState.build(tp=world if mode == "tp" else 1, ep=world if mode == "ep" else 1, sequence_parallel=False)
+    eng = Engine(cfg, ps=ps, device="cpu", dtype=torch.float32, num_blocks=96, seed=4)
+
+    def client():
+        import requests
+
+        url = f"http://127.0.0.1:{port}"
+        for _ in range(200):
+            try:
+                if requests.get(f"{url}/health", timeout=2).status_code == 200:
+                    break
+            except Exception:
+                time.sleep(0.1)
+        g = torch.Generator().manual_seed(8)
+        prompts = [torch.randint(3, cfg.vocab_size, (int(n),), generator=g).tolist() for n in (6, 19, 11, 25, 9)]
+        outs = [None] * len(prompts)
+
+        def one(i):
+            outs[i] = requests.post(f"{url}/generate", json={"input_ids": prompts[i], "return_logprob": True,
+                                                             "sampling_params": {"temperature": 0.0, "max_new_tokens": 5 + i}}, timeout=120).json()
+
+        ts = [threading.Thread(target=one, args=(i,)) for i in range(len(prompts))]
+        [t.start() for t in ts]
+        [t.join() for t in ts]
+        info = requests.get(f"{url}/health", timeout=10).json()
+        requests.post(f"{url}/update_weight_version", json={"weight_version": 3}, timeout=10)
+        time.sleep(0.2)
+        ver = requests.get(f"{url}/get_weight_version", timeout=10).json()["weight_version"]
+        with open(f"{out_dir}/out.json", "w") as f:
+            json.dump({"prompts": prompts, "outs": outs, "info": info, "version": ver}, f)
+        requests.post(f"{url}/shutdown", timeout=10)
+
+    if rank == 0:
+        threading.Thread(target=client, daemon=True).start()
+    mrs.start(eng, ps, mode, port=port)
+
+
+@pytest.mark.parametrize("mode,port", [("ep", 31751), ("tp", 31752)])
+def test_multi_rank_engine_server_matches_one_engine(tmp_path, mode, port):
+    """Two ranks behind one HTTP port: experts sharded with every rank serving its own requests (`ep`), or projections
+    sharded with every rank running every request (`tp`); answers equal a single unsharded engine's."""
+    import json
+    import os
+    import sys
+
+    import torch
+
+    sys.path.insert(0, os.path.dirname(__file__))
+    from dist_utils import run_distributed
+
+    from miles_b200.engine.engine import Engine
+    from miles_b200.models.config import PRESETS
+
+    run_distributed(_multi_rank_body, 2, (mode, port, str(tmp_path)), timeout=300)
+    rec = json.load(open(tmp_path / "out.json"))
+    assert rec["info"]["ranks"] == 2 and rec["info"]["mode"] == mode and rec["version"] == "3"
+    ref = Engine(PRESETS["tiny-moe" if mode == "ep" else "tiny"], device="cpu", dtype=torch.float32, num_blocks=96, seed=4)
+    for i, (p, o) in enumerate(zip(rec["prompts"], rec["outs"])):
+        w = ref.generate(p, {"temperature": 0.0, "max_new_tokens": 5 + i})
+        assert o["output_ids"] == w["output_ids"], (i, o["output_ids"], w["output_ids"])
+        a, b = ([x[0] for x in r["meta_info"]["output_token_logprobs"]] for r in (o, w))
+        assert max(abs(x - y) for x, y in zip(a, b)) < 1e-4
