@@ -24,6 +24,11 @@ from typing import Any
 import torch
 import torch.distributed as dist
 
+try:                                  # at module level: handler annotations are resolved against the module's globals
+    from fastapi import Request
+except Exception:                     # pragma: no cover - the control loop itself does not need FastAPI
+    Request = Any
+
 
 class ControlLoop:
     """The per-rank side: apply broadcast commands, step, return finished requests."""
@@ -118,7 +123,7 @@ class ControlLoop:
 
 
 def build_app(loop: ControlLoop):
-    from fastapi import FastAPI, Request
+    from fastapi import FastAPI
     from fastapi.responses import JSONResponse
 
     app = FastAPI(title="miles_b200 multi-GPU engine")

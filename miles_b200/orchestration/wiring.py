@@ -48,16 +48,21 @@ def create_parallel_state(args) -> ParallelState:
 
 def apply_serving_config(args) -> None:
     """`--engine-config`: the server groups of the policy model (the first model that is not eval-only) decide how many
-    engine servers the fleet starts and in which roles — `regular` engines behind the router, or `prefill` + `decode` engines
-    with the KV hand-over between them.  (One GPU per engine server: groups asking for more are refused.)"""
+    engine servers the fleet starts and in which roles — `regular` engines behind the router (over `num_gpus_per_engine` GPUs each), or
+    single-GPU `prefill` + `decode` engines with the KV hand-over between them."""
     from .inference_controller import load_serving_config
 
     models = load_serving_config(args.engine_config)
     policy = next((m for m in models if not m.eval_only), None)
     assert policy is not None, "--engine-config names no model that serves the policy"
     count = {"regular": 0, "prefill": 0, "decode": 0}
+    per = {grp.num_gpus_per_engine for grp in policy.groups if grp.worker_type in count}
+    assert len(per) <= 1, f"{policy.name}: the groups of one fleet use one engine size, got {sorted(per)}"
+    if per:
+        args.rollout_num_gpus_per_engine = per.pop()
+        assert args.rollout_num_gpus_per_engine == 1 or not any(g.worker_type == "prefill" for g in policy.groups), \
+            "prefill / decode roles run on single-GPU engine servers"
     for grp in policy.groups:
-        assert grp.num_gpus_per_engine == 1, f"{policy.name}: engine servers span one GPU here (num_gpus_per_engine {grp.num_gpus_per_engine})"
         if grp.worker_type in count:
             count[grp.worker_type] += grp.num_gpus // grp.num_gpus_per_engine
     if count["prefill"]:

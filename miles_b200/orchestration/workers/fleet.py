@@ -207,21 +207,28 @@ def wait_healthy(url: str, timeout: float = 180.0, alive=None):
 
 def engine_spec(args, n: int) -> CommandWorkerSpec:
     ek = dict(getattr(args, "engine_kwargs", {}) or {})
-    cmd = [sys.executable, "-m", "miles_b200.engine.server", "--port", "{port}", "--host", "127.0.0.1",
+    per = int(getattr(args, "rollout_num_gpus_per_engine", 1) or 1)
+    module = "miles_b200.engine.multi_rank_server" if per > 1 else "miles_b200.engine.server"
+    cmd = [sys.executable, "-m", module, "--port", "{port}", "--host", "127.0.0.1",
            "--mem-fraction-static", str(ek.get("mem_fraction_static", 0.7)),
            "--max-running-requests", str(ek.get("max_running_requests", 256))]
     if getattr(args, "hf_checkpoint", None):
         cmd += ["--hf-checkpoint", args.hf_checkpoint]
     else:
         cmd += ["--model-name", args.model_name]
+    if per > 1:
+        # one engine over `per` GPUs: a cell of `per` ranks (rendezvous variables from the planner), rank 0 owns the HTTP port;
+        # experts are sharded for MoE models, projections for dense ones (`engine/multi_rank_server.py`)
+        cpu = getattr(args, "fp32", False)
+        return CommandWorkerSpec("engine", cmd, SchedulingSpec(num_cells=n, workers_per_cell=per, gpus_per_worker=0 if cpu else 1),
+                                 env={"CUDA_VISIBLE_DEVICES": "" if cpu else "__inherit__"})
     if getattr(args, "fp32", False):
         cmd += ["--device", "cpu"]
         return CommandWorkerSpec("engine", cmd, SchedulingSpec(num_cells=n, workers_per_cell=1, gpus_per_worker=0))
     # every GPU stays visible to the server and it is told which one is its own: device indices then mean the same in the
     # trainer and in the engine, which is what CUDA-IPC weight buckets rely on
     cmd += ["--device", "cuda:{gpu_ids}"]
-    gpus = float(getattr(args, "rollout_num_gpus_per_engine", 1) or 1)
-    return CommandWorkerSpec("engine", cmd, SchedulingSpec(num_cells=n, workers_per_cell=1, gpus_per_worker=gpus),
+    return CommandWorkerSpec("engine", cmd, SchedulingSpec(num_cells=n, workers_per_cell=1, gpus_per_worker=1.0),
                              env={"CUDA_VISIBLE_DEVICES": "__inherit__"})
 
 

@@ -330,5 +330,40 @@ def test_serving_config_sizes_the_fleet_and_assigns_roles(tmp_path):
     apply_serving_config(args)
     assert (args.rollout_num_engines, args.rollout_pd_prefill_engines) == (2, 0)
     cfg.write_text("models:\n  - name: policy\n    server_groups: [{worker_type: regular, num_gpus: 4, num_gpus_per_engine: 2}]\n")
+    args = parse_args(f"--model-name tiny --engine-config {cfg}".split())
+    apply_serving_config(args)
+    assert (args.rollout_num_engines, args.rollout_num_gpus_per_engine) == (2, 2)
+    cfg.write_text("models:\n  - name: policy\n    server_groups: [{worker_type: prefill, num_gpus: 2, num_gpus_per_engine: 2}, "
+                   "{worker_type: decode, num_gpus: 2, num_gpus_per_engine: 2}]\n")
     with pytest.raises(AssertionError):
         apply_serving_config(parse_args(f"--model-name tiny --engine-config {cfg}".split()))
+
+
+def test_engine_fleet_with_a_two_rank_engine(tmp_path):
+    """`--rollout-num-gpus-per-engine 2`: the fleet's engine is a cell of two ranks (experts sharded) behind one port; weights
+    arrive through the disk protocol on both ranks and a rollout through it matches the trainer's log-probs."""
+    sys.path.insert(0, ROOT)
+    from miles_b200.args import parse_args
+    from miles_b200.orchestration.wiring import (create_parallel_state, create_rollout_components, create_training_models,
+                                                 update_weights)
+    from miles_b200.utils import object_store
+
+    args = parse_args(("--model-name tiny-moe --fp32 --rollout-batch-size 4 --n-samples-per-prompt 2 --rollout-max-response-len 6 "
+                       "--num-rollout 1 --rm-type even_fraction --lr 1e-4 --advantage-estimator grpo "
+                       "--data-source-path miles_b200.rollout.data_source.SyntheticSource --synthetic-prompt-len 8 12 "
+                       "--rollout-engine http --worker-provider local --rollout-num-engines 1 --rollout-num-gpus-per-engine 2 "
+                       f"--update-weight-transfer-mode disk --update-weight-disk-dir {tmp_path}/sync --worker-log-dir {tmp_path}/logs").split())
+    ps = create_parallel_state(args)
+    actor, _, _ = create_training_models(args, ps)
+    for p in actor.model.parameters():                      # the engine starts from its own random weights: make ours differ
+        p.data.mul_(1.01)
+    rollout = create_rollout_components(args, ps, actor)
+    try:
+        assert len(rollout.fleet.manager.cells["engine-c0"].workers) == 2
+        update_weights(args, actor, rollout)
+        time.sleep(0.5)                                     # the load is applied by the engine's next control tick
+        shard = object_store.get(rollout.executor.get(0).data_ref)
+        m = actor.train(0, shard)
+        assert len(shard["tokens"]) == 8 and m["train/train_rollout_logprob_abs_diff"] < 1e-4, m["train/train_rollout_logprob_abs_diff"]
+    finally:
+        rollout.fleet.shutdown()
