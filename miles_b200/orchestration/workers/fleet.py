@@ -21,6 +21,7 @@ import time
 from ..worker_spec import CommandWorkerSpec, SchedulingSpec
 from .manager import WorkerManager
 from .provider import CellInfo, CompositeProvider, LocalProcessProvider, StaticWorkerProvider
+from .reconcile import LookAgain
 from .registration import RegistrationHub
 
 
@@ -132,7 +133,7 @@ class Fleet:
             self.events.append(("restarted", cell_id, new.generation))
             if self.on_restart is not None:
                 self.on_restart(eng)
-            raise RuntimeError("restarted: look again")              # seen-state stays old → the next poll re-checks
+            raise LookAgain()                                         # the next poll reconciles the restarted cell
 
     def _router(self, endpoint: str, url: str):
         if not self.router_url:
@@ -167,9 +168,9 @@ class Fleet:
     async def _reconcile_quiet(self, cell_id, info):
         try:
             await self._reconcile(cell_id, info)
-        except RuntimeError as e:
-            if "look again" in str(e):
-                raise
+        except LookAgain:
+            raise
+        except Exception as e:
             self.events.append(("error", cell_id, str(e)))
 
     def shutdown(self):

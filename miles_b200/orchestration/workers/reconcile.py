@@ -220,6 +220,11 @@ class ReconcileLoop:
                     self.queue.add(p)
 
 
+class LookAgain(Exception):
+    """Raised by a reconcile handler that changed the cell it was called for (restarted it, say): the observation is not
+    recorded as handled, so the next poll reconciles the cell's new state."""
+
+
 class PollingReconcileLoop:
     """Lists cells every `interval` seconds and reconciles those whose description changed (None = disappeared).  The
     first listing is reconciled before `start` returns and its failure is raised; later failures are retried next poll."""
@@ -238,6 +243,8 @@ class PollingReconcileLoop:
                 continue
             try:
                 await reconcile(cid, info)
+            except LookAgain:       # the handler acted on the cell: what was observed is already out of date
+                continue
             except Exception as e:  # the other cells still get their turn
                 first_error = first_error or e
                 continue
