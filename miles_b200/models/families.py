@@ -119,7 +119,21 @@ class GatedAttention(Attention):
                 q, k = _rms(q, self.q_norm, cfg.rms_eps), _rms(k, self.k_norm, cfg.rms_eps)
             q = torch.cat([ops.rope(q[..., :self.rot].contiguous(), meta.positions, cfg.rope_theta), q[..., self.rot:]], -1)
             k = torch.cat([ops.rope(k[..., :self.rot].contiguous(), meta.positions, cfg.rope_theta), k[..., self.rot:]], -1)
-        o = ops.attention_varlen(q, k, v, meta.cu_seqlens, meta.max_seqlen).reshape(T, self.hq * self.d)
+        if self.ps.cp_size > 1:
+            # contiguous context-parallel chunks: swap the sequence sharding for a head sharding around the kernel (Ulysses),
+            # or gather K/V (`allgather`); the recurrent layers of the same model pass their state along the same chunks
+            from ..parallel import cp as _cp
+            from ..parallel import cp_ring as _ring
+
+            if self.ps.cp_comm_type == "a2a":
+                qh, kh, vh = (_cp.seq_to_heads(t, self.ps) for t in (q, k, v))
+                o = _cp.heads_to_seq(ops.attention_varlen(qh, kh, vh, meta.cu_seqlens, meta.max_seqlen), self.ps)
+            else:
+                assert self.ps.cp_comm_type == "allgather", "family models run context parallelism over contiguous chunks"
+                o = _ring.allgather_attention(q, k, v, meta.cu_seqlens, self.ps)
+            o = o.reshape(T, self.hq * self.d)
+        else:
+            o = ops.attention_varlen(q, k, v, meta.cu_seqlens, meta.max_seqlen).reshape(T, self.hq * self.d)
         if self.w_gate is not None:
             o = o * torch.sigmoid(ops.linear(x, self.w_gate))
         return ops.linear(o, self.wo)
@@ -195,10 +209,12 @@ class LatentAttention(nn.Module):
         return ops.linear(o.reshape(T, hd * self.dv), self.wo)
 
 
-def delta_rule(q, k, v, beta, g, cu_seqlens):
+def delta_rule(q, k, v, beta, g, cu_seqlens, S0=None, return_state: bool = False):
     """Gated delta rule over packed sequences (fp32 state, one recurrence per sequence and head):
         S ← S ⊙ exp(g_t);  S ← S + k_t ⊗ β_t (v_t − Sᵀ k_t);  o_t = Sᵀ q_t
-    q, k [T, H, dk] (already normalised / scaled), v [T, H, dv], beta [T, H], g [T, H] or [T, H, dk] (log decay ≤ 0)."""
+    q, k [T, H, dk] (already normalised / scaled), v [T, H, dv], beta [T, H], g [T, H] or [T, H, dk] (log decay ≤ 0).
+    `S0` [H, dk, dv]: the state the FIRST sequence starts from (a sequence that began on another context-parallel rank);
+    `return_state`: also return the state after the LAST sequence's final token."""
     T, H, dk = q.shape
     dv = v.shape[-1]
     qf, kf, vf, bf = q.float(), k.float(), v.float(), beta.float()
@@ -206,14 +222,70 @@ def delta_rule(q, k, v, beta, g, cu_seqlens):
     gf = gf[..., None, None] if gf.dim() == 2 else gf[..., None]               # [T, H, 1|dk, 1]
     out = []
     cu = cu_seqlens.tolist()
+    S = torch.zeros(H, dk, dv, dtype=torch.float32, device=q.device)
     for b in range(len(cu) - 1):
-        S = torch.zeros(H, dk, dv, dtype=torch.float32, device=q.device)
+        S = S0.float() if (b == 0 and S0 is not None) else torch.zeros(H, dk, dv, dtype=torch.float32, device=q.device)
         for t in range(cu[b], cu[b + 1]):
             S = S * gf[t]
             mem = torch.einsum("hkv,hk->hv", S, kf[t])
             S = S + torch.einsum("hk,hv->hkv", kf[t], (vf[t] - mem) * bf[t, :, None])
             out.append(torch.einsum("hkv,hk->hv", S, qf[t]))
-    return torch.stack(out).to(v.dtype) if out else v.new_zeros(0, H, dv)
+    o = torch.stack(out).to(v.dtype) if out else v.new_zeros(0, H, dv)
+    return (o, S) if return_state else o
+
+
+# ---- context parallelism for the recurrent mixer: the state (and the convolution's history) travels from rank to rank ----
+
+class _RecvFrom(torch.autograd.Function):
+    """Forward: receive a tensor shaped like `like` from `src`; backward: send its gradient back there."""
+
+    @staticmethod
+    def forward(ctx, like, src, group):
+        import torch.distributed as dist
+
+        ctx.src, ctx.group = src, group
+        buf = torch.empty_like(like)
+        dist.recv(buf, src=src, group=group)
+        return buf
+
+    @staticmethod
+    def backward(ctx, g):
+        import torch.distributed as dist
+
+        dist.send(g.contiguous(), dst=ctx.src, group=ctx.group)
+        return torch.zeros_like(g), None, None
+
+
+class _SendTo(torch.autograd.Function):
+    """Forward: send `t` to `dst` and return a zero scalar that ties the send into the graph; backward: receive the
+    gradient of what was sent."""
+
+    @staticmethod
+    def forward(ctx, t, dst, group):
+        import torch.distributed as dist
+
+        ctx.dst, ctx.group, ctx.shape, ctx.dtype = dst, group, t.shape, t.dtype
+        dist.send(t.detach().contiguous(), dst=dst, group=group)
+        return t.new_zeros(())
+
+    @staticmethod
+    def backward(ctx, _):
+        import torch.distributed as dist
+
+        g = torch.empty(ctx.shape, dtype=ctx.dtype, device=_.device)
+        dist.recv(g, src=ctx.dst, group=ctx.group)
+        return g, None, None
+
+
+def local_segments(cu_seqlens, lo: int, hi: int):
+    """Sequence boundaries of the packed batch inside the token range [lo, hi), relative to lo, and whether the first and the
+    last local segment continue from / into a neighbouring range."""
+    cu = [int(c) for c in cu_seqlens.tolist()]
+    if cu[-1] < hi:
+        cu.append(hi)                                    # padding tokens past the last sequence form one more segment
+    inner = [c for c in cu if lo < c < hi]
+    bounds = [lo] + inner + [hi]
+    return [b - lo for b in bounds], lo not in cu, hi not in cu
 
 
 class LinearAttention(nn.Module):
@@ -224,7 +296,7 @@ class LinearAttention(nn.Module):
     def __init__(self, cfg: FamilyConfig, ps, dtype, device, gen, tag, per_channel_decay: bool):
         super().__init__()
         assert ps.tp_size == 1, "linear attention runs with tensor parallel size 1"
-        self.cfg, self.per_channel = cfg, per_channel_decay
+        self.cfg, self.per_channel, self.ps = cfg, per_channel_decay, ps
         H, nh, dk, dv = cfg.hidden_size, cfg.linear_heads, cfg.linear_key_dim, cfg.linear_value_dim
         self.nh, self.dk, self.dv = nh, dk, dv
 
@@ -244,8 +316,15 @@ class LinearAttention(nn.Module):
         cfg, T, nh, dk, dv = self.cfg, x.shape[0], self.nh, self.dk, self.dv
         qkvz = ops.linear(x, self.w_qkvz)
         qkv_, z = qkvz[:, :nh * (2 * dk + dv)], qkvz[:, nh * (2 * dk + dv):].reshape(T, nh, dv)
+        if self.ps.cp_size > 1:
+            return self._forward_cp(x, meta, qkv_, z)
         seqlens = (meta.cu_seqlens[1:] - meta.cu_seqlens[:-1]).to(torch.int32)
         qkv_ = F.silu(X.short_conv_fp32(qkv_.contiguous(), self.conv, seqlens).float())
+        o = self._mix(x, qkv_, meta.cu_seqlens)
+        return self._finish(x, o, z)
+
+    def _mix(self, x, qkv_, cu_seqlens, S0=None, return_state: bool = False):
+        T, nh, dk, dv = x.shape[0], self.nh, self.dk, self.dv
         q, k, v = qkv_.split([nh * dk, nh * dk, nh * dv], -1)
         q = F.normalize(q.reshape(T, nh, dk), dim=-1) / math.sqrt(dk)
         k = F.normalize(k.reshape(T, nh, dk), dim=-1)
@@ -254,7 +333,52 @@ class LinearAttention(nn.Module):
         a = ba[:, nh:] + self.dt_bias
         g = -torch.exp(self.A_log)[None, :, None] * F.softplus(a.reshape(T, nh, -1))          # log decay ≤ 0
         g = g if self.per_channel else g.squeeze(-1)
-        o = delta_rule(q, k, v.reshape(T, nh, dv), beta, g, meta.cu_seqlens)
+        return delta_rule(q, k, v.reshape(T, nh, dv), beta, g, cu_seqlens, S0=S0, return_state=return_state)
+
+    def _finish(self, x, o, z):
+        cfg, T = self.cfg, x.shape[0]
+        o = _rms(o.to(x.dtype), self.o_norm, cfg.rms_eps) * F.silu(z.float()).to(x.dtype)
+        return ops.linear(o.reshape(T, self.nh * self.dv), self.wo)
+
+    def _forward_cp(self, x, meta, qkv_, z):
+        """Context parallelism with contiguous token chunks (the layout of `--cp-comm-type a2a` / `allgather`): a sequence
+        cut by a chunk boundary continues on the next rank from the state this rank ends with, and its convolution sees this
+        rank's last W − 1 inputs.  Both travel in ONE message per boundary (and their gradients in one message back), ranks
+        compute their chunks one after another along each cut sequence.  The reference does this for its linear-attention
+        families through fla's state passing (miles_plugins/models/hf_attention.py:184-199)."""
+        from ..parallel.cp import chunk_bounds
+
+        ps = self.ps
+        assert ps.cp_comm_type in ("a2a", "allgather"), "the recurrent mixer needs contiguous context-parallel chunks"
+        T, nh, dk, dv, W = x.shape[0], self.nh, self.dk, self.dv, self.conv.shape[1]
+        lo, hi = chunk_bounds(T * ps.cp_size, ps.cp_size, ps.cp_rank)
+        bounds, from_prev, to_next = local_segments(meta.cu_seqlens, lo, hi)
+        C = qkv_.shape[1]
+        n_state, n_halo = nh * dk * dv, (W - 1) * C
+        pre = qkv_.float()
+        S0, halo = None, None
+        if from_prev and ps.cp_rank > 0:
+            like = torch.zeros(n_state + n_halo, dtype=torch.float32, device=x.device, requires_grad=torch.is_grad_enabled())
+            msg = _RecvFrom.apply(like, ps.cp_ranks[ps.cp_rank - 1], ps.cp_group)
+            S0, halo = msg[:n_state].view(nh, dk, dv), msg[n_state:].view(W - 1, C)
+        # causal convolution: the first segment is extended by the neighbour's last W − 1 inputs (zeros where that sequence is shorter)
+        ext = torch.cat([halo, pre]) if halo is not None else pre
+        shift = (W - 1) if halo is not None else 0
+        seg = [b + shift for b in bounds]
+        seg[0] = 0
+        seqlens = torch.tensor([b - a for a, b in zip(seg[:-1], seg[1:])], dtype=torch.int32, device=x.device)
+        conv = X.short_conv_fp32(ext.contiguous(), self.conv, seqlens).float()[shift:]
+        cu_local = torch.tensor(bounds, dtype=torch.int32, device=x.device)
+        o, S_last = self._mix(x, F.silu(conv), cu_local, S0=S0, return_state=True)
+        out = self._finish(x, o, z)
+        if to_next and ps.cp_rank < ps.cp_size - 1:
+            first_of_last = seg[-2]                                     # the cut sequence's rows in `ext` (halo rows included)
+            tail = ext[max(first_of_last, ext.shape[0] - (W - 1)):]
+            tail = torch.cat([tail.new_zeros(W - 1 - tail.shape[0], C), tail]) if tail.shape[0] < W - 1 else tail
+            tie = _SendTo.apply(torch.cat([S_last.reshape(-1), tail.reshape(-1)]), ps.cp_ranks[ps.cp_rank + 1], ps.cp_group)
+            out = out + tie.to(out.dtype)
+        return out
+
         o = _rms(o.to(x.dtype), self.o_norm, cfg.rms_eps) * F.silu(z.float()).to(x.dtype)
         return ops.linear(o.reshape(T, nh * dv), self.wo)
 

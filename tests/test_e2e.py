@@ -125,6 +125,8 @@ def _dist_hist(tmp_path, extra, world=2):
     "--model-name tiny-moe --expert-model-parallel-size 2 --use-rollout-routing-replay --rollout-data-exchange balanced "
     "--synthetic-prompt-len 4 48",
     "--context-parallel-size 2 --cp-comm-type a2a",                         # cp2 (Ulysses), dp1
+    # linear-attention family under cp2: recurrent state + convolution history passed between the chunk owners
+    "--model-name qwen3-next-tiny --context-parallel-size 2 --cp-comm-type a2a",
     "--train-backend fsdp",                                                 # dp2, parameters sharded per layer (FSDP2)
     "--offload-train --offload-train-release-process-groups",               # dp2, communicators destroyed while asleep
     "--context-parallel-size 2",                                            # cp2, ring attention over zigzag pieces

@@ -153,3 +153,64 @@ def test_hf_names_round_trip(name):
     if cfg.attn_output_gate:
         q = next(v for k, v in hf.items() if k.endswith("self_attn.q_proj.weight"))
         assert q.shape[0] == 2 * cfg.q_size
+
+
+# ---- context parallelism of the recurrent mixer: state and convolution history passed from rank to rank ---------------
+
+def _linear_cp_body(rank, world, per_channel, cu_list):
+    import torch
+
+    from miles_b200.models.families import FamilyConfig, LinearAttention
+    from miles_b200.models.qwen3 import ForwardMeta, _Init
+    from miles_b200.parallel import cp as _cp
+    from miles_b200.parallel.state import ParallelState, init_distributed
+
+    init_distributed(backend="gloo")
+    ps = ParallelState.build(cp=world, cp_comm_type="a2a")
+    cfg = FamilyConfig(name="t", hidden_size=32, linear_heads=2, linear_key_dim=8, linear_value_dim=8, conv_kernel=4)
+    torch.manual_seed(0)
+    T = cu_list[-1]
+    x_full = torch.randn(T, 32)
+    g_full = torch.randn(T, 32)
+    cu = torch.tensor(cu_list, dtype=torch.int32)
+
+    def build(p):
+        m = LinearAttention(cfg, p, torch.float32, "cpu", _Init(7), "l0", per_channel_decay=per_channel)
+        with torch.no_grad():
+            m.A_log.fill_(0.3)
+            m.dt_bias.normal_(0, 0.5, generator=torch.Generator().manual_seed(3))
+        return m
+
+    ref = build(ParallelState.single())
+    xr = x_full.clone().requires_grad_()
+    yr = ref(xr, ForwardMeta(positions=None, cu_seqlens=cu, max_seqlen=T), 0)
+    yr.backward(g_full)
+    mod = build(ps)
+    lo, hi = _cp.chunk_bounds(T, world, rank)
+    xl = x_full[lo:hi].clone().requires_grad_()
+    yl = mod(xl, ForwardMeta(positions=None, cu_seqlens=cu, max_seqlen=T), 0)
+    assert torch.allclose(yl, yr.detach()[lo:hi], atol=1e-5), float((yl - yr.detach()[lo:hi]).abs().max())
+    yl.backward(g_full[lo:hi])
+    assert torch.allclose(xl.grad, xr.grad[lo:hi], atol=1e-5), float((xl.grad - xr.grad[lo:hi]).abs().max())
+    # parameter gradients: the ranks' contributions add up to the single-rank gradient
+    import torch.distributed as dist
+
+    for (n, p), (_, q) in zip(mod.named_parameters(), ref.named_parameters()):
+        gsum = p.grad.clone()
+        dist.all_reduce(gsum)
+        assert torch.allclose(gsum, q.grad, atol=2e-5), (n, float((gsum - q.grad).abs().max()))
+
+
+@pytest.mark.parametrize("world,per_channel,cu", [(2, False, [0, 5, 19, 24]), (2, True, [0, 12, 24]), (3, False, [0, 3, 24]),
+                                                   (3, True, [0, 7, 9, 24])])
+def test_linear_attention_context_parallel_state_passing(world, per_channel, cu):
+    """Chunks of 12 (or 8) tokens: sequences cut by a chunk boundary (one spans all three ranks; one chunk is shorter than
+    the convolution's history only together with its neighbour), a boundary that coincides with a sequence start, both decay
+    forms — outputs, input gradients and summed parameter gradients equal the single-rank layer's."""
+    import os
+    import sys
+
+    sys.path.insert(0, os.path.dirname(__file__))
+    from dist_utils import run_distributed
+
+    run_distributed(_linear_cp_body, world, (per_channel, cu), timeout=300)
