@@ -214,3 +214,36 @@ def test_linear_attention_context_parallel_state_passing(world, per_channel, cu)
     from dist_utils import run_distributed
 
     run_distributed(_linear_cp_body, world, (per_channel, cu), timeout=300)
+
+
+def test_audio_tower_is_per_clip_and_feeds_the_language_model():
+    """Clips packed along time: a clip's rows do not depend on its neighbours, row counts follow the stride and the pooling,
+    and the features merged at the audio placeholder tokens carry gradients back into the tower."""
+    import torch
+
+    from miles_b200.models.audio import AudioConfig, AudioLanguageModel, AudioTower, output_rows
+    from miles_b200.models.config import PRESETS
+    from miles_b200.models.qwen3 import ForwardMeta, build_model
+    from miles_b200.parallel.state import ParallelState
+
+    cfg = AudioConfig(n_mels=16, hidden_size=64, num_layers=2, num_heads=4, ffn_hidden_size=96, pool=2, out_hidden_size=256)
+    tower = AudioTower(cfg, dtype=torch.float32, seed=1)
+    g = torch.Generator().manual_seed(0)
+    frames = torch.tensor([13, 8, 21])
+    feats = torch.randn(int(frames.sum()), 16, generator=g)
+    rows = output_rows(frames, 2)
+    assert rows.tolist() == [4, 2, 6]
+    out = tower(feats, frames)
+    assert out.shape == (12, 256)
+    alone = tower(feats[13:21], frames[1:2])
+    assert torch.allclose(out[4:6], alone, atol=1e-5)                              # clip 1 on its own gives the same rows
+    lm = build_model(PRESETS["tiny"], ParallelState.single(), dtype=torch.float32, device="cpu", seed=0)
+    model = AudioLanguageModel(lm, tower, audio_token_id=7)
+    tokens = torch.tensor([3, 7, 7, 7, 7, 9, 11, 7, 7, 12, 7, 7, 7, 7, 7, 7, 5], dtype=torch.int32)
+    meta = ForwardMeta(positions=torch.arange(17, dtype=torch.int32), cu_seqlens=torch.tensor([0, 17], dtype=torch.int32), max_seqlen=17)
+    h = model(tokens, meta, audio_features=feats, clip_frames=frames)
+    assert h.shape == (17, 256)
+    h.float().pow(2).sum().backward()
+    assert tower.conv1_w.grad is not None and float(tower.conv1_w.grad.abs().sum()) > 0
+    plain = model(tokens.clone().fill_(3), meta)                                   # no audio inputs: the language model alone
+    assert plain.shape == (17, 256)
