@@ -56,6 +56,8 @@ def parse():
                    help="response cap of the untimed warm-up steps (same pipeline, same prompts and batch: graphs, allocator pools, "
                         "communicators and clocks are warmed by the prompt-dominated work; the cap keeps 5 warm-up steps of the "
                         "8-GPU run inside a fixed launch window); 0 = the full cap")
+    p.add_argument("--no-weight-sync-probe", action="store_true",
+                   help="skip the untimed measurement of a weight sync into an engine that holds its own copy of the weights")
     p.add_argument("--quiet", action="store_true")
     return p.parse_args()
 
@@ -131,6 +133,41 @@ class ClockSampler:
             return {}
         sm.sort()
         return {"sm_mhz": sm[len(sm) // 2], "sm_max_mhz": max(mx), "reasons": sorted(reasons), "samples": len(sm)}
+
+
+def _weight_sync_probe(args, cfg, ps, actor, dev, world):
+    """After the timed region: the trainer's weights into an engine that holds ITS OWN copy (the timed loop's engine serves the
+    trainer's parameters directly, so its hand-over is a version bump).  Pause → every bucket copied into the engine's buffers
+    by the one-kernel NVLink / device copy → resume, three times after one warm-up; device time, maximum over ranks."""
+    import torch
+    import torch.distributed as dist
+
+    try:
+        from miles_b200.engine.engine import Engine
+        from miles_b200.weight_update.updater import WeightUpdater
+
+        other = Engine(cfg, model=None, ps=ps, device=dev, dtype=torch.bfloat16, num_blocks=8, max_running_requests=8,
+                       max_context_len=512, seed=99, use_cuda_graph=False)
+        upd = WeightUpdater(args, actor, [other], mode="nvlink")
+        info = upd.update_weights()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+        t0 = time.perf_counter()
+        e0.record()
+        for _ in range(3):
+            info = upd.update_weights()
+        e1.record()
+        torch.cuda.synchronize()
+        t = torch.tensor([e0.elapsed_time(e1) / 3e3, (time.perf_counter() - t0) / 3], device=dev, dtype=torch.float64)
+        if world > 1:
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        a_, b_ = next(iter(actor.model.parameters())), next(iter(other.model.parameters()))
+        return {"seconds": float(t[0]), "seconds_wall": float(t[1]), "bytes_per_gpu": int(info.get("bytes", 0)),
+                "identical_after_sync": bool(torch.equal(a_.data, b_.data)), "mode": "nvlink (one kernel per bucket into the engine's own buffers)"}
+    except Exception as e:          # the probe must never cost the run its result line
+        return {"error": f"{type(e).__name__}: {e}"[:300]}
 
 
 def main():
@@ -311,6 +348,7 @@ def main():
     total_tokens = counters["tokens"]
     gen_tokens = counters["gen_tokens"]
     err = K.check_error_flag()
+    sync_probe = None if a.no_weight_sync_probe else _weight_sync_probe(args, cfg, ps, actor, dev, world)
     if rank == 0:
         value = total_tokens / (dev_ms / 1e3)
         out = {
@@ -341,7 +379,7 @@ def main():
             "breakdown_s_per_step": {"rollout": counters["rollout_s"] / a.steps, "train": counters["train_s"] / a.steps,
                                      "weight_sync": counters["sync_s"] / a.steps},
             "train_phases_s_per_step_rank0": {k: round(v / a.steps, 3) for k, v in sorted(phases.items())},
-            "tokens_per_step": total_tokens // a.steps, "kernel_error_flag": err,
+            "tokens_per_step": total_tokens // a.steps, "kernel_error_flag": err, "weight_sync_own_copy": sync_probe,
             # the reference's perf/tokens_per_gpu_per_sec counts response tokens only: the same quantity for the whole job
             "generated_tokens_per_s": gen_tokens / (dev_ms / 1e3), "generated_tokens_per_step": gen_tokens // a.steps,
             "engine_stats_rank0": counters.get("engine"),
