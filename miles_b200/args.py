@@ -107,6 +107,9 @@ def build_parser() -> argparse.ArgumentParser:
     _bool_flag(g, "--fp32", help="train in fp32 (CPU plumbing runs)")
     g.add_argument("--fp8-format", choices=["e4m3", "hybrid"], default=None)
     g.add_argument("--fp8-recipe", choices=["mxfp8", "blockwise", "delayed"], default=None)
+    g.add_argument("--fp8-backward", action="store_true",
+                   help="with --fp8-recipe mxfp8: dgrad and wgrad of the dense projections in MXFP8 too (operands re-quantised along "
+                        "the contraction axis); default: bf16 gradient GEMMs on the unquantised operands")
     g.add_argument("--recompute-granularity", choices=["full", "selective"], default=None)
     g.add_argument("--recompute-method", type=str, default=None)
     g.add_argument("--recompute-num-layers", type=int, default=None)

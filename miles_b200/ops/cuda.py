@@ -255,8 +255,35 @@ class _LinearMXFP8(torch.autograd.Function):
 
     @staticmethod
     def backward(ctx, gy):
-        return _Linear.backward(ctx, gy)
+        if not MXFP8_BACKWARD:
+            return _Linear.backward(ctx, gy)
+        # both gradient GEMMs block-scaled as well: the contraction runs over N (dgrad) and over the tokens (wgrad), so each
+        # operand is quantised along THAT axis — the transposed copies are made here, quantised 1×32 along their rows, and the
+        # same NT kernel serves all three products (the reference's recipe quantises the transposes the same way,
+        # miles/utils/mxfp8.py:48-78)
+        from . import extra
 
+        x2, w = ctx.saved_tensors
+        gy2 = _c(gy.reshape(-1, gy.shape[-1]))
+        M, N = gy2.shape
+        K = w.shape[1]
+        if N % 128 or M % 128 or K % 128:
+            return _Linear.backward(ctx, gy)
+        gx = gw = None
+        if ctx.needs_input_grad[0]:
+            gq, gs = mxfp8_quant(gy2)                                  # noqa: F821
+            wtq, wts = mxfp8_quant(w.t().contiguous())                 # noqa: F821   [K, N], blocks along N
+            gx = extra.gemm_mxfp8(gq, gs, wtq, wts).view(ctx.shp)
+        if ctx.needs_input_grad[1]:
+            gtq, gts = mxfp8_quant(gy2.t().contiguous())               # noqa: F821   [N, M], blocks along the tokens
+            xtq, xts = mxfp8_quant(x2.t().contiguous())                # noqa: F821   [K, M]
+            gw = extra.gemm_mxfp8(gtq, gts, xtq, xts)
+        gb = gy2.float().sum(0).to(gy.dtype) if ctx.has_bias else None
+        return gx, gw, gb
+
+
+# `--fp8-recipe mxfp8` with `--fp8-backward` (or MILES_MXFP8_BACKWARD=1): dgrad and wgrad in MXFP8 too
+MXFP8_BACKWARD = os.environ.get("MILES_MXFP8_BACKWARD", "0") == "1"
 
 # `--fp8-recipe mxfp8` (or MILES_MXFP8_LINEAR=1): projections whose K is a multiple of 128 run their forward in MXFP8
 MXFP8_LINEAR = os.environ.get("MILES_MXFP8_LINEAR", "0") == "1"

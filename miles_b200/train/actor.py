@@ -98,6 +98,8 @@ class TrainActor:
             from ..ops import cuda as _cuda_ops
 
             _cuda_ops.MXFP8_LINEAR = True       # projections run their forward on the block-scaled MXFP8 tensor-core path
+            if getattr(args, "fp8_backward", False):
+                _cuda_ops.MXFP8_BACKWARD = True  # and both gradient products, on operands quantised along the contraction axis
         self.fsdp = getattr(args, "train_backend", "native") == "fsdp" and dist.is_initialized() and dist.get_world_size() > 1
         compute_dtype = self.compute_dtype = dtype
         if self.fsdp:
