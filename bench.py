@@ -25,6 +25,7 @@ ROOT = os.path.dirname(os.path.abspath(__file__))
 if ROOT not in sys.path:
     sys.path.insert(0, ROOT)
 
+_T_PROCESS_START = time.time()
 BASELINE_TOKENS_PER_S = None  # the reference publishes no GRPO tokens/s figure for this config
 
 
@@ -56,6 +57,10 @@ def parse():
                    help="response cap of the untimed warm-up steps (same pipeline, same prompts and batch: graphs, allocator pools, "
                         "communicators and clocks are warmed by the prompt-dominated work; the cap keeps 5 warm-up steps of the "
                         "8-GPU run inside a fixed launch window); 0 = the full cap")
+    p.add_argument("--deadline-seconds", type=float, default=830.0,
+                   help="wall-clock budget of this process: when the next timed step is projected to end after it, the timed loop stops "
+                        "and the line reports the steps actually timed (`steps` < `steps_requested`, `stopped_early` set) instead of being "
+                        "lost with the process; 0 = no deadline")
     p.add_argument("--no-weight-sync-probe", action="store_true",
                    help="skip the untimed measurement of a weight sync into an engine that holds its own copy of the weights")
     p.add_argument("--quiet", action="store_true")
@@ -324,8 +329,18 @@ def main():
     ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     wall0 = time.perf_counter()
     ev0.record()
+    steps_done = 0
     for i in range(a.steps):
+        if i > 0 and a.deadline_seconds > 0:
+            # every rank takes the decision of rank 0 (one tiny all-reduce per step)
+            el = time.perf_counter() - wall0
+            late = torch.tensor([float((time.time() - _T_PROCESS_START) + 1.05 * el / i > a.deadline_seconds) if rank == 0 else 0.0], device=dev)
+            if world > 1:
+                dist.all_reduce(late, op=dist.ReduceOp.MAX)
+            if float(late) > 0:
+                break
         step(a.warmup + i)
+        steps_done = i + 1
         if rank == 0 and not a.quiet:
             # progress on stderr (host clock, this rank): what a reader has if the run is stopped before the JSON line
             el = time.perf_counter() - wall0
@@ -359,7 +374,7 @@ def main():
         value = total_tokens / (dev_ms / 1e3)
         out = {
             "metric": "GRPO tokens/s/box (rollout+train+weight-sync)", "value": value, "unit": "tokens/s", "n_gpus": world,
-            "steps": a.steps, "warmup": a.warmup, "warmup_max_new_tokens": warm_cap, "ms_per_step": dev_ms / a.steps, "higher_is_better": True, "scaling": "weak",
+            "steps": steps_done, "steps_requested": a.steps, "stopped_early": (None if steps_done == a.steps else f"deadline of {a.deadline_seconds:.0f} s for the whole process: {steps_done} of {a.steps} steps timed"), "warmup": a.warmup, "warmup_max_new_tokens": warm_cap, "ms_per_step": dev_ms / steps_done, "higher_is_better": True, "scaling": "weak",
             "vs_baseline": (value / BASELINE_TOKENS_PER_S) if BASELINE_TOKENS_PER_S else None,
             "dtype": "bf16" if a.fp8_recipe == "none" else "mxfp8 forward (e4m3, 1x32 e8m0 scales) + bf16 backward",
             "data": "synthetic prompts (uniform random ids), random-init weights, rule reward (last id mod 7 == 0)",
@@ -378,16 +393,16 @@ def main():
                                  + (f", responses capped at {warm_cap} new tokens" if warm_cap != full_cap else ", full response cap")),
             },
             "clocks": clocks,
-            "e2e": {"value": total_tokens / (wall_ms / 1e3), "unit": "tokens/s", "h2d_bytes_per_step": counters["h2d"] // a.steps,
-                    "d2h_bytes_per_step": counters["d2h"] // a.steps, "timed": "wall clock around the public-API step "
+            "e2e": {"value": total_tokens / (wall_ms / 1e3), "unit": "tokens/s", "h2d_bytes_per_step": counters["h2d"] // steps_done,
+                    "d2h_bytes_per_step": counters["d2h"] // steps_done, "timed": "wall clock around the public-API step "
                     "(RolloutExecutor.get → TrainActor.train → update_weights), max over ranks"},
             "gpu_launches": int(launches),
-            "breakdown_s_per_step": {"rollout": counters["rollout_s"] / a.steps, "train": counters["train_s"] / a.steps,
-                                     "weight_sync": counters["sync_s"] / a.steps},
-            "train_phases_s_per_step_rank0": {k: round(v / a.steps, 3) for k, v in sorted(phases.items())},
-            "tokens_per_step": total_tokens // a.steps, "kernel_error_flag": err, "weight_sync_own_copy": sync_probe,
+            "breakdown_s_per_step": {"rollout": counters["rollout_s"] / steps_done, "train": counters["train_s"] / steps_done,
+                                     "weight_sync": counters["sync_s"] / steps_done},
+            "train_phases_s_per_step_rank0": {k: round(v / steps_done, 3) for k, v in sorted(phases.items())},
+            "tokens_per_step": total_tokens // steps_done, "kernel_error_flag": err, "weight_sync_own_copy": sync_probe,
             # the reference's perf/tokens_per_gpu_per_sec counts response tokens only: the same quantity for the whole job
-            "generated_tokens_per_s": gen_tokens / (dev_ms / 1e3), "generated_tokens_per_step": gen_tokens // a.steps,
+            "generated_tokens_per_s": gen_tokens / (dev_ms / 1e3), "generated_tokens_per_step": gen_tokens // steps_done,
             "engine_stats_rank0": counters.get("engine"),
         }
         print(json.dumps(out))
