@@ -537,6 +537,9 @@ class Engine:
                 r.cache_nodes = []
             if r.keep_kv and reason.get("type") != "abort":
                 self.held_kv[r.rid] = (r.blocks, len(r.all_ids) - 1)       # every position but the last sampled token has KV
+                while len(self.held_kv) > 4 * self.max_running:           # a caller that never came back: the oldest loans end
+                    old = next(iter(self.held_kv))
+                    self.allocator.release(self.held_kv.pop(old)[0])
             else:
                 self.allocator.release(r.blocks)
             r.blocks = []
