@@ -152,3 +152,56 @@ class PDHttpClient:
             return out
         finally:
             await self._post(f"{P}/release_kv", {"rid": rid})
+
+
+def _bench_handover():
+    """`python -m miles_b200.engine.pd --tokens 2048`: device time of the KV hand-over between two engines of one GPU (or of
+    the first and the last GPU of the box) for a prompt of that many tokens — gather on the prefill side, copy, scatter on the
+    decode side — at the Qwen3-30B-A3B cache shape (48 layers, 4 KV heads of 128)."""
+    import argparse
+    import json
+
+    import torch
+
+    from ..models.config import get_config
+    from .engine import Engine
+
+    p = argparse.ArgumentParser()
+    p.add_argument("--tokens", type=int, default=2048)
+    p.add_argument("--layers", type=int, default=48)
+    p.add_argument("--iters", type=int, default=10)
+    a = p.parse_args()
+    cfg = get_config("qwen3-30B-A3B").with_(num_experts=8, num_layers=a.layers, moe_ffn_hidden_size=128, hidden_size=512)
+    d0, d1 = torch.device("cuda", 0), torch.device("cuda", torch.cuda.device_count() - 1)
+    blocks = (a.tokens + 63) // 64 + 2
+    P = Engine(cfg, device=d0, dtype=torch.bfloat16, num_blocks=2 * blocks, max_running_requests=4, max_context_len=a.tokens + 64, seed=0)
+    D = Engine(cfg, device=d1, dtype=torch.bfloat16, num_blocks=2 * blocks, max_running_requests=4, max_context_len=a.tokens + 64, seed=0)
+    for kc, vc in P.kv.layers.values():
+        kc.normal_()
+        vc.normal_()
+    ids = list(range(3, 3 + a.tokens))
+    times = []
+    for it in range(a.iters + 3):
+        held = P.allocator.alloc((a.tokens + 63) // 64)
+        P.held_kv["bench"] = (held, a.tokens)
+        torch.cuda.synchronize(d0)
+        torch.cuda.synchronize(d1)
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record(torch.cuda.current_stream(d0))
+        kv = P.export_kv("bench")
+        req = D.add_prefilled(ids, 5, -1.0, kv, {"temperature": 0.0, "max_new_tokens": 2})
+        torch.cuda.synchronize(d1)
+        e1.record(torch.cuda.current_stream(d0))
+        torch.cuda.synchronize(d0)
+        if it >= 3:
+            times.append(e0.elapsed_time(e1))
+        P.release_kv("bench")
+        D.abort_request(req.rid)
+    nbytes = kv.numel() * kv.element_size()
+    ms = sorted(times)[len(times) // 2]
+    print(json.dumps({"tokens": a.tokens, "layers": a.layers, "kv_bytes": nbytes, "ms": ms, "gbs": nbytes / ms / 1e6,
+                      "devices": [str(d0), str(d1)]}))
+
+
+if __name__ == "__main__":
+    _bench_handover()
