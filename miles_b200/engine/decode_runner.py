@@ -304,6 +304,28 @@ class DecodeRunner:
             self.pool = g.pool()
         self.graphs[key] = g
 
+    @torch.no_grad()
+    def precapture(self, records=(True,)) -> int:
+        """Capture the decode graph of every batch bucket that has none yet (for each routing-record variant asked for), on
+        padding rows only.  Serving stacks do this at start-up; here it is a call of its own so that a caller can place the
+        cost (≈ a second per graph) where it wants it — e.g. after a warm-up rollout, not inside a measured one.  A capture
+        records kernels without running them, so expert-parallel ranks may capture independently."""
+        if not self.use_graph:
+            return 0
+        self.d_i32.copy_(self.h_i32)            # padding state: rows of finished requests have length 0 and no cache slot
+        self.d_i64.copy_(self.h_i64)
+        n = 0
+        for b in BUCKETS:
+            if b > self.max_rows:
+                break
+            for rec in records:
+                key = (b, bool(rec) and self.n_moe > 0)
+                if key not in self.graphs:
+                    self._capture(key)
+                    n += 1
+        torch.cuda.synchronize()
+        return n
+
     def reset_graphs(self):
         self.graphs.clear()
         self.pool = None
