@@ -310,13 +310,6 @@ def main():
             m = step(i)
         finally:
             args.rollout_max_response_len = executor.local_args.rollout_max_response_len = full_cap
-        if i == 0 and engine.runner is not None and not a.no_cuda_graph:
-            # the short warm-up rollouts end most rows together, so the decode batch never passes through the small buckets:
-            # capture their graphs here, between warm-up steps, instead of inside the first timed step
-            try:
-                engine.runner.precapture(records=(True, False) if world > 1 else (True,))
-            except Exception as e:
-                print(f"[bench] graph pre-capture skipped: {type(e).__name__}: {e}", file=sys.stderr, flush=True)
         if rank == 0 and not a.quiet:
             print(f"[warmup {i}] tokens={counters['tokens']} rollout={counters['rollout_s']:.1f}s train={counters['train_s']:.1f}s "
                   f"loss={m.get('train/loss', float('nan')):.4g} grad_norm={m.get('train/grad_norm', float('nan')):.4g}",

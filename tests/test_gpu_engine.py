@@ -272,3 +272,24 @@ def test_prefill_decode_disaggregation_on_cuda(engine):
         assert max(abs(x - y) for x, y in zip(a, b)) < 5e-2
     assert other.stats["received_kv_tokens"] == sum(map(len, prompts)) and other.stats["prefill_tokens"] == 0
     assert not engine.held_kv and other._free_blocks() == other.allocator.num_blocks
+
+
+@pytest.mark.gpu
+def test_precapture_fills_every_bucket_and_generation_is_unchanged(engine):
+    """`DecodeRunner.precapture` records a graph for every batch bucket up to the row limit without touching any request;
+    generating afterwards replays them and gives the tokens an engine without the call gives."""
+    cfg = engine.cfg
+    g = torch.Generator().manual_seed(31)
+    prompts = [torch.randint(3, cfg.vocab_size, (int(n),), generator=g).tolist() for n in (9, 30, 50)]
+    sp = {"temperature": 0.0, "max_new_tokens": 6}
+    before = engine.generate(prompts, [dict(sp)] * 3)
+    n_before = len(engine.runner.graphs)
+    added = engine.runner.precapture(records=(True, False))
+    from miles_b200.engine.decode_runner import BUCKETS
+
+    want = {(b, r) for b in BUCKETS if b <= engine.runner.max_rows for r in (True, False)}
+    assert want <= set(engine.runner.graphs) and added == len(engine.runner.graphs) - n_before
+    assert engine.runner.precapture(records=(True, False)) == 0
+    after = engine.generate(prompts, [dict(sp)] * 3)
+    assert [o["output_ids"] for o in after] == [o["output_ids"] for o in before]
+    assert engine._free_blocks() == engine.allocator.num_blocks
