@@ -237,12 +237,17 @@ class Engine:
         """KV of a finished `keep_kv` request as one tensor [layers, 2, tokens, kv heads, head dim] (a gather over its slots)."""
         with self.lock:
             blocks, n = self.held_kv[rid]
-            bs = self.block_size
-            slots = torch.tensor([blocks[p // bs] * bs + p % bs for p in range(n)], dtype=torch.int64, device=self.device)
+            slots = self._slot_tensor(blocks, n)
             layers = sorted(self.kv.layers)
             out = [torch.stack([self.kv.layers[l][0].flatten(0, 1).index_select(0, slots),
                                 self.kv.layers[l][1].flatten(0, 1).index_select(0, slots)]) for l in layers]
             return torch.stack(out)
+
+    def _slot_tensor(self, blocks: list[int], n: int) -> torch.Tensor:
+        """Flat cache slots of positions 0 … n − 1 of a request with these blocks (built with tensor ops, not a Python loop)."""
+        bs = self.block_size
+        pos = torch.arange(n, dtype=torch.int64)
+        return (torch.tensor(blocks, dtype=torch.int64)[pos // bs] * bs + pos % bs).to(self.device)
 
     def release_kv(self, rid: str):
         with self.lock:
@@ -274,8 +279,7 @@ class Engine:
             if blocks is None:
                 raise RuntimeError(f"no room for {n} prefilled tokens ({self._free_blocks()} blocks free)")
             req.blocks = blocks
-            bs = self.block_size
-            slots = torch.tensor([blocks[p // bs] * bs + p % bs for p in range(n)], dtype=torch.int64, device=self.device)
+            slots = self._slot_tensor(blocks, n)
             kv = kv.to(self.device)
             for i, l in enumerate(sorted(self.kv.layers)):
                 kc, vc = self.kv.layers[l]
