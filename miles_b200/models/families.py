@@ -145,7 +145,7 @@ class LatentAttention(nn.Module):
     def __init__(self, cfg: FamilyConfig, ps, dtype, device, gen, tag, sparse: bool):
         super().__init__()
         assert ps.tp_size == 1, "latent attention runs with tensor parallel size 1"
-        self.cfg, self.sparse = cfg, sparse
+        self.cfg, self.sparse, self.ps = cfg, sparse, ps
         H, hd = cfg.hidden_size, cfg.num_heads
         self.dn, self.dr, self.dv = cfg.qk_nope_head_dim, cfg.qk_rope_head_dim, cfg.v_head_dim
         dq = self.dn + self.dr
@@ -181,13 +181,16 @@ class LatentAttention(nn.Module):
         kv_a = ops.linear(x, self.wkv_a)
         c_kv = _rms(kv_a[:, :cfg.kv_lora_rank].contiguous(), self.kv_a_norm, cfg.rms_eps)
         k_rope = ops.rope(kv_a[:, cfg.kv_lora_rank:].reshape(T, 1, self.dr).contiguous(), meta.positions, cfg.rope_theta)
-        kv = ops.linear(c_kv, self.wkv_b).view(T, hd, self.dn + self.dv)
         q_rope = ops.rope(q[..., self.dn:].contiguous(), meta.positions, cfg.rope_theta)
         qf = torch.cat([q[..., :self.dn], q_rope], -1)
-        kf = torch.cat([kv[..., :self.dn], k_rope.expand(T, hd, self.dr)], -1)
-        v = kv[..., self.dn:]
         scale = 1.0 / math.sqrt(self.dn + self.dr)
         self.last_index_loss = None
+        if self.ps.cp_size > 1:
+            assert not self.sparse, "the indexer-selected variant has no context-parallel path"
+            return ops.linear(self._attend_cp(qf, c_kv, k_rope, meta, scale).reshape(T, hd * self.dv), self.wo)
+        kv = ops.linear(c_kv, self.wkv_b).view(T, hd, self.dn + self.dv)
+        kf = torch.cat([kv[..., :self.dn], k_rope.expand(T, hd, self.dr)], -1)
+        v = kv[..., self.dn:]
         if not self.sparse:
             o = _dense_attention(qf, kf, v, meta, scale)
         else:
@@ -207,6 +210,36 @@ class LatentAttention(nn.Module):
                     mass = torch.nan_to_num(torch.softmax(s, -1), nan=0.0).sum(1)    # [T, K] summed over heads
                 self.last_index_loss = SA.indexer_kl_loss(logits, mass, idx)
         return ops.linear(o.reshape(T, hd * self.dv), self.wo)
+
+
+def _latent_attend_cp(self, qf, c_kv, k_rope, meta: ForwardMeta, scale: float):
+    """Context parallelism for latent attention over contiguous chunks: what crosses ranks is the LATENT — the compressed
+    key/value vector and the shared rotary key, kv_lora_rank + rope dims per token instead of heads × (nope + v) — gathered
+    over the group (gradients come back with a reduce); every rank expands the gathered latents to per-head keys and values
+    and its queries attend causally inside their sequences by global position."""
+    from ..parallel import cp_ring as _ring
+
+    ps, cfg, hd = self.ps, self.cfg, self.cfg.num_heads
+    assert ps.cp_comm_type in ("a2a", "allgather"), "latent attention needs contiguous context-parallel chunks"
+    Tl = qf.shape[0]
+    total = Tl * ps.cp_size
+    lat = torch.cat([c_kv, k_rope.reshape(Tl, self.dr)], -1)
+    lat = _ring._AllGatherTokens.apply(lat, ps.cp_group, ps.cp_size, ps.cp_rank)                 # [T, r + dr], global order
+    c_all, kr_all = lat[:, :cfg.kv_lora_rank], lat[:, cfg.kv_lora_rank:].reshape(total, 1, self.dr)
+    kv = ops.linear(c_all.contiguous(), self.wkv_b).view(total, hd, self.dn + self.dv)
+    kf = torch.cat([kv[..., :self.dn], kr_all.expand(total, hd, self.dr)], -1)
+    v = kv[..., self.dn:]
+    dev = qf.device
+    lo = ps.cp_rank * Tl
+    q_seq, q_pos = _ring._seq_pos(torch.arange(lo, lo + Tl, device=dev), meta.cu_seqlens)
+    k_seq, k_pos = _ring._seq_pos(torch.arange(total, device=dev), meta.cu_seqlens)
+    vis = (q_seq[:, None] == k_seq[None, :]) & (k_pos[None, :] <= q_pos[:, None])
+    s = torch.einsum("thd,shd->hts", qf.float(), kf.float()) * scale
+    p = torch.softmax(s.masked_fill(~vis[None], float("-inf")), -1)
+    return torch.einsum("hts,shd->thd", p, v.float()).to(qf.dtype)
+
+
+LatentAttention._attend_cp = _latent_attend_cp
 
 
 def delta_rule(q, k, v, beta, g, cu_seqlens, S0=None, return_state: bool = False):

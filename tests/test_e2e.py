@@ -127,6 +127,8 @@ def _dist_hist(tmp_path, extra, world=2):
     "--context-parallel-size 2 --cp-comm-type a2a",                         # cp2 (Ulysses), dp1
     # linear-attention family under cp2: recurrent state + convolution history passed between the chunk owners
     "--model-name qwen3-next-tiny --context-parallel-size 2 --cp-comm-type a2a",
+    # per-channel-decay linear attention + latent attention (the latent is what is gathered) under cp2
+    "--model-name kimi-linear-tiny --context-parallel-size 2 --cp-comm-type a2a",
     "--train-backend fsdp",                                                 # dp2, parameters sharded per layer (FSDP2)
     "--offload-train --offload-train-release-process-groups",               # dp2, communicators destroyed while asleep
     "--context-parallel-size 2",                                            # cp2, ring attention over zigzag pieces
