@@ -33,7 +33,10 @@ def build_parser() -> argparse.ArgumentParser:
     g.add_argument("--critic-num-gpus-per-node", type=int, default=None)
     g.add_argument("--rollout-num-gpus", type=int, default=None)
     g.add_argument("--rollout-num-gpus-per-engine", type=int, default=1)
-    g.add_argument("--worker-provider", choices=["none", "local", "static", "registration"], default="none",
+    g.add_argument("--k8s-selector", type=str, default=None, help="label selector of the engine pods (--worker-provider kubernetes)")
+    g.add_argument("--k8s-namespace", type=str, default=None)
+    g.add_argument("--k8s-kubectl", type=str, default=None, help="the command that lists pods as JSON (default: kubectl)")
+    g.add_argument("--worker-provider", choices=["none", "local", "static", "registration", "kubernetes"], default="none",
                    help="with --rollout-engine http: where engine servers come from. local: launched, watched and restarted "
                         "by this job; static: already running at --rollout-engine-addrs; registration: they announce "
                         "themselves to the hub at --registration-hub-port; none: only a router URL is given (--engine-router-url)")

@@ -273,6 +273,17 @@ def launch_fleet(args, log_dir: str | None = None, on_restart=None) -> Fleet:
             engines[w.cell_id] = RemoteEngine(w.url(), w.name, 0)
         providers.append(sp)
         assert router_url, "--worker-provider static needs --router-url (or one engine address used directly)"
+    elif kind == "kubernetes":
+        from .kubernetes import KubernetesWorkerProvider
+
+        kp = KubernetesWorkerProvider("engine", getattr(args, "k8s_selector", None) or "app=miles-engine",
+                                      namespace=getattr(args, "k8s_namespace", None), kubectl=getattr(args, "k8s_kubectl", None) or "kubectl")
+        for cid, c in asyncio.run(kp.list_cells()).items():          # pods are launched by the cluster's own tooling: adopt what runs
+            if c.alive and c.pool == "engine":
+                wait_healthy(c.workers[0].url(), 300.0)
+                engines[cid] = RemoteEngine(c.workers[0].url(), c.workers[0].name, c.generation)
+        providers.append(kp)
+        assert router_url or engines, "--worker-provider kubernetes found no ready engine pod and no --engine-router-url was given"
     if kind == "registration" or getattr(args, "registration_hub_port", None):
         hub = RegistrationHub(ttl=float(getattr(args, "registration_ttl", 30.0) or 30.0))
         hub.serve(port=int(getattr(args, "registration_hub_port", None) or 30200))

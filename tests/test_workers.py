@@ -367,3 +367,40 @@ def test_engine_fleet_with_a_two_rank_engine(tmp_path):
         assert len(shard["tokens"]) == 8 and m["train/train_rollout_logprob_abs_diff"] < 1e-4, m["train/train_rollout_logprob_abs_diff"]
     finally:
         rollout.fleet.shutdown()
+
+
+def test_kubernetes_provider_maps_pods_to_cells(tmp_path):
+    """The pod list of a `kubectl`-shaped command becomes cells: labels give pool / cell / worker / generation, the named
+    container port and the pod IP give the address, a cell is alive only when every pod is Running and ready."""
+    import json
+    import stat
+
+    from miles_b200.orchestration.workers.kubernetes import KubernetesWorkerProvider
+
+    def pod(name, ip, phase="Running", ready=True, labels=None, restarts=0, deleting=False):
+        meta = {"name": name, "labels": labels or {}}
+        if deleting:
+            meta["deletionTimestamp"] = "2026-01-01T00:00:00Z"
+        return {"metadata": meta, "spec": {"containers": [{"ports": [{"name": "metrics", "containerPort": 9000}, {"name": "http", "containerPort": 30000}]}]},
+                "status": {"phase": phase, "podIP": ip, "containerStatuses": [{"ready": ready, "restartCount": restarts}]}}
+
+    items = [pod("eng-a", "10.0.0.1", labels={"miles/cell": "0", "miles/worker": "0"}),
+             pod("eng-b", "10.0.0.2", labels={"miles/cell": "0", "miles/worker": "1"}, restarts=2),
+             pod("eng-c", "10.0.0.3", labels={"miles/cell": "1"}, ready=False),
+             pod("eng-d", "10.0.0.4", labels={"miles/cell": "2", "miles/generation": "7"}),
+             pod("eng-e", "10.0.0.5", labels={"miles/cell": "3"}, deleting=True)]
+    data = tmp_path / "pods.json"
+    data.write_text(json.dumps({"items": items}))
+    fake = tmp_path / "kubectl"
+    fake.write_text(f"#!/bin/sh\ncase \"$*\" in *'-l app=engine'*'-n rl'*) cat {data};; *) echo bad args: $* >&2; exit 3;; esac\n")
+    fake.chmod(fake.stat().st_mode | stat.S_IEXEC)
+    prov = KubernetesWorkerProvider("engine", "app=engine", namespace="rl", kubectl=str(fake))
+    cells = asyncio.run(prov.list_cells())
+    assert sorted(cells) == ["engine-c0", "engine-c1", "engine-c2", "engine-c3"]
+    c0 = cells["engine-c0"]
+    assert c0.alive and c0.generation == 2 and [w.url() for w in c0.workers] == ["http://10.0.0.1:30000", "http://10.0.0.2:30000"]
+    assert not cells["engine-c1"].alive and cells["engine-c2"].generation == 7 and not cells["engine-c3"].alive
+    assert asyncio.run(prov.get_addrs("engine-c2-w0")).host == "10.0.0.4"
+    bad = KubernetesWorkerProvider("engine", "app=other", kubectl=str(fake))
+    with pytest.raises(RuntimeError):
+        asyncio.run(bad.list_cells())
