@@ -186,8 +186,12 @@ class LatentAttention(nn.Module):
         scale = 1.0 / math.sqrt(self.dn + self.dr)
         self.last_index_loss = None
         if self.ps.cp_size > 1:
-            assert not self.sparse, "the indexer-selected variant has no context-parallel path"
-            return ops.linear(self._attend_cp(qf, c_kv, k_rope, meta, scale).reshape(T, hd * self.dv), self.wo)
+            idx_in = None
+            if self.sparse:
+                idx_in = (ops.linear(q_lat, self.wq_idx).view(T, cfg.index_heads, cfg.index_dim),
+                          _rms(ops.linear(x, self.wk_idx), self.k_idx_norm, cfg.rms_eps),
+                          ops.linear(x, self.w_idx).float() / math.sqrt(cfg.index_heads * cfg.index_dim))
+            return ops.linear(self._attend_cp(qf, c_kv, k_rope, meta, scale, idx_in).reshape(T, hd * self.dv), self.wo)
         kv = ops.linear(c_kv, self.wkv_b).view(T, hd, self.dn + self.dv)
         kf = torch.cat([kv[..., :self.dn], k_rope.expand(T, hd, self.dr)], -1)
         v = kv[..., self.dn:]
@@ -212,7 +216,7 @@ class LatentAttention(nn.Module):
         return ops.linear(o.reshape(T, hd * self.dv), self.wo)
 
 
-def _latent_attend_cp(self, qf, c_kv, k_rope, meta: ForwardMeta, scale: float):
+def _latent_attend_cp(self, qf, c_kv, k_rope, meta: ForwardMeta, scale: float, idx_in=None):
     """Context parallelism for latent attention over contiguous chunks: what crosses ranks is the LATENT — the compressed
     key/value vector and the shared rotary key, kv_lora_rank + rope dims per token instead of heads × (nope + v) — gathered
     over the group (gradients come back with a reduce); every rank expands the gathered latents to per-head keys and values
@@ -223,9 +227,11 @@ def _latent_attend_cp(self, qf, c_kv, k_rope, meta: ForwardMeta, scale: float):
     assert ps.cp_comm_type in ("a2a", "allgather"), "latent attention needs contiguous context-parallel chunks"
     Tl = qf.shape[0]
     total = Tl * ps.cp_size
-    lat = torch.cat([c_kv, k_rope.reshape(Tl, self.dr)], -1)
-    lat = _ring._AllGatherTokens.apply(lat, ps.cp_group, ps.cp_size, ps.cp_rank)                 # [T, r + dr], global order
-    c_all, kr_all = lat[:, :cfg.kv_lora_rank], lat[:, cfg.kv_lora_rank:].reshape(total, 1, self.dr)
+    parts = [c_kv, k_rope.reshape(Tl, self.dr)] + ([idx_in[1]] if idx_in is not None else [])   # + the indexer's keys
+    lat = torch.cat([t.to(c_kv.dtype) for t in parts], -1)
+    lat = _ring._AllGatherTokens.apply(lat, ps.cp_group, ps.cp_size, ps.cp_rank)                 # [T, r + dr (+ index dim)], global order
+    c_all = lat[:, :cfg.kv_lora_rank]
+    kr_all = lat[:, cfg.kv_lora_rank:cfg.kv_lora_rank + self.dr].reshape(total, 1, self.dr)
     kv = ops.linear(c_all.contiguous(), self.wkv_b).view(total, hd, self.dn + self.dv)
     kf = torch.cat([kv[..., :self.dn], kr_all.expand(total, hd, self.dr)], -1)
     v = kv[..., self.dn:]
@@ -233,6 +239,21 @@ def _latent_attend_cp(self, qf, c_kv, k_rope, meta: ForwardMeta, scale: float):
     lo = ps.cp_rank * Tl
     q_seq, q_pos = _ring._seq_pos(torch.arange(lo, lo + Tl, device=dev), meta.cu_seqlens)
     k_seq, k_pos = _ring._seq_pos(torch.arange(total, device=dev), meta.cu_seqlens)
+    if idx_in is not None:
+        # indexer-selected keys: this rank's queries choose among the keys of the whole batch; the indexer's training signal
+        # is this rank's share of the batch mean (gradients are summed over the group)
+        q_idx, _, w_idx = idx_in
+        k_idx_all = lat[:, cfg.kv_lora_rank + self.dr:]
+        o, idx, logits = SA.dsa_attention(qf, kf, v.contiguous(), q_idx, k_idx_all, w_idx, min(cfg.index_topk, total), scale,
+                                          None, q_seq, k_seq, q_pos, k_pos)
+        if torch.is_grad_enabled():
+            with torch.no_grad():
+                kg = kf.float()[idx.clamp_min(0).long()]
+                sc = torch.einsum("thd,tkhd->thk", qf.float(), kg) * scale
+                sc = sc.masked_fill((idx < 0).unsqueeze(1), float("-inf"))
+                mass = torch.nan_to_num(torch.softmax(sc, -1), nan=0.0).sum(1)
+            self.last_index_loss = SA.indexer_kl_loss(logits, mass, idx) / ps.cp_size
+        return o
     vis = (q_seq[:, None] == k_seq[None, :]) & (k_pos[None, :] <= q_pos[:, None])
     s = torch.einsum("thd,shd->hts", qf.float(), kf.float()) * scale
     p = torch.softmax(s.masked_fill(~vis[None], float("-inf")), -1)

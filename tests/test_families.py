@@ -249,7 +249,7 @@ def test_audio_tower_is_per_clip_and_feeds_the_language_model():
     assert plain.shape == (17, 256)
 
 
-def _mla_cp_body(rank, world, cu_list):
+def _mla_cp_body(rank, world, cu_list, sparse=False):
     import torch
     import torch.distributed as dist
 
@@ -261,22 +261,22 @@ def _mla_cp_body(rank, world, cu_list):
     init_distributed(backend="gloo")
     ps = ParallelState.build(cp=world, cp_comm_type="allgather")
     cfg = FamilyConfig(name="t", hidden_size=64, num_heads=4, q_lora_rank=24, kv_lora_rank=16, qk_nope_head_dim=8, qk_rope_head_dim=8,
-                       v_head_dim=8)
+                       v_head_dim=8, index_heads=2, index_dim=8, index_topk=6)
     torch.manual_seed(0)
     T = cu_list[-1]
     x_full, g_full = torch.randn(T, 64), torch.randn(T, 64)
     cu = torch.tensor(cu_list, dtype=torch.int32)
     pos_full = torch.cat([torch.arange(b - a) for a, b in zip(cu_list[:-1], cu_list[1:])]).to(torch.int32)
-    ref = LatentAttention(cfg, ParallelState.single(), torch.float32, "cpu", _Init(5), "l0", sparse=False)
+    ref = LatentAttention(cfg, ParallelState.single(), torch.float32, "cpu", _Init(5), "l0", sparse=sparse)
     xr = x_full.clone().requires_grad_()
     yr = ref(xr, ForwardMeta(positions=pos_full, cu_seqlens=cu, max_seqlen=T), 0)
-    yr.backward(g_full)
-    mod = LatentAttention(cfg, ps, torch.float32, "cpu", _Init(5), "l0", sparse=False)
+    ((yr * g_full).sum() + (ref.last_index_loss if sparse else 0.0)).backward()
+    mod = LatentAttention(cfg, ps, torch.float32, "cpu", _Init(5), "l0", sparse=sparse)
     lo, hi = _cp.chunk_bounds(T, world, rank)
     xl = x_full[lo:hi].clone().requires_grad_()
     yl = mod(xl, ForwardMeta(positions=pos_full[lo:hi], cu_seqlens=cu, max_seqlen=T), 0)
     assert torch.allclose(yl, yr.detach()[lo:hi], atol=1e-5), float((yl - yr.detach()[lo:hi]).abs().max())
-    yl.backward(g_full[lo:hi])
+    ((yl * g_full[lo:hi]).sum() + (mod.last_index_loss if sparse else 0.0)).backward()
     assert torch.allclose(xl.grad, xr.grad[lo:hi], atol=1e-5)
     for (n, p), (_, q) in zip(mod.named_parameters(), ref.named_parameters()):
         gsum = p.grad.clone()
@@ -284,8 +284,8 @@ def _mla_cp_body(rank, world, cu_list):
         assert torch.allclose(gsum, q.grad, atol=2e-5), (n, float((gsum - q.grad).abs().max()))
 
 
-@pytest.mark.parametrize("world,cu", [(2, [0, 7, 24]), (3, [0, 10, 11, 24])])
-def test_latent_attention_context_parallel_gathers_the_latent(world, cu):
+@pytest.mark.parametrize("world,cu,sparse", [(2, [0, 7, 24], False), (3, [0, 10, 11, 24], False), (2, [0, 9, 24], True)])
+def test_latent_attention_context_parallel_gathers_the_latent(world, cu, sparse):
     """Latent attention under context parallelism: the compressed KV and the rotary key are gathered (not per-head K/V);
     outputs, input gradients and summed parameter gradients equal the single-rank layer's."""
     import os
@@ -294,4 +294,4 @@ def test_latent_attention_context_parallel_gathers_the_latent(world, cu):
     sys.path.insert(0, os.path.dirname(__file__))
     from dist_utils import run_distributed
 
-    run_distributed(_mla_cp_body, world, (cu,), timeout=300)
+    run_distributed(_mla_cp_body, world, (cu, sparse), timeout=300)
